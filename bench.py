@@ -1,0 +1,329 @@
+"""Benchmark of the quantized-KV decode attention path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c4|c5]
+
+One step = one decode-attention pass of one layer over a batch of synthetic sequences whose
+compressed KV cache is resident in HBM (a ragged batch of 64 sequences with 512-8192 MXFP4 keys
+by default: 32 query heads, 8 kv heads, head dim 128, bf16 queries). The metric is the achieved HBM
+bandwidth on the algorithmic bytes of the step (packed code and scale bytes of every visible K and
+V row, plus queries and outputs), with tokens/s beside it. With N > 1 every rank holds its own
+batch (weak scaling, no data-path collective until the outputs are all-gathered over NCCL).
+
+`--impl reference` times the reference's CPU path for the same step (dequantize the cached rows to
+the cache dtype, then unfused softmax(Q K^T) V; candle-nn/src/turbo_quant.rs:947-991,
+candle-nn/src/flash_attn.rs:930-1000) through the C restatement in oracle/, on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PAYLOAD = {0: 68, 2: 68, 3: 76, 4: 132, 5: 132}  # algorithmic bytes of one packed row at head dim 128 (codes + scales)
+METRIC = "quantized_kv_decode_attention_hbm_bandwidth"
+
+WORKLOADS = {
+    # name: (batch, hq, hkv, d, format, q dtype, rotation, length rule, layers)
+    "c2": dict(b=64, hq=32, hkv=8, d=128, fmt="mxfp4", mode=2, qdt="bf16", rot="none", lens="uniform512-8192", desc="ragged MXFP4 decode, B=64, lengths uniform in [512, 8192]"),
+    "c1": dict(b=1, hq=32, hkv=8, d=128, fmt="fp8", mode=5, qdt="f16", rot="none", lens=2048, desc="single FP8 decode, 2048 keys"),
+    "c4": dict(b=32, hq=8, hkv=1, d=128, fmt="turbo4", mode=0, qdt="bf16", rot="hadamard", lens=32768, desc="TurboQuant-4 decode, one kv head of B=32 x 32768 keys per GPU"),
+    "c5": dict(b=128, hq=32, hkv=8, d=128, fmt="mxfp8", mode=4, qdt="f16", rot="none", lens=16384, desc="MXFP8 decode, B=128 x 16384 keys, one layer"),
+}
+
+
+def seq_lens(w, rank=0):
+    from oracle import oracle as O  # only the seeded generator of the reference is used here
+    if w["lens"] == "uniform512-8192":
+        return (512 + O.u64s(2002 + rank, w["b"]) % np.uint64(7681)).astype(np.int32)
+    return np.full(w["b"], w["lens"], np.int32)
+
+
+def algorithmic_bytes(w, lens):
+    qo = w["b"] * w["hq"] * w["d"] * 2 * 2  # queries read + outputs written, 16-bit
+    return int(lens.astype(np.int64).sum()) * w["hkv"] * 2 * PAYLOAD[w["mode"]] + qo
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        mhz = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": float(np.median(mhz)) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(mhz)}
+
+
+def cpu_reference_step(w, lens, nseq, reps=1):
+    """The reference's CPU path for `nseq` sequences of the batch; returns (seconds per pass, bytes)."""
+    from oracle import oracle as O
+    d, hq, hkv = w["d"], w["hq"], w["hkv"]
+    mode = w["mode"]
+    bits = 4
+    tab = O.codebook(d, 4) if mode == 0 else np.zeros(32, np.float32)
+    lens = lens[:nseq]
+    rows, qs = [], []
+    for i, L in enumerate(lens):
+        kx = O.normal(1002 + i, hkv * int(L) * d).reshape(-1, d)
+        vx = O.normal(1003 + i, hkv * int(L) * d).reshape(-1, d)
+        rows.append((O.quantize_rows(kx, mode, bits, tab), O.quantize_rows(vx, mode, bits, tab)))
+        qs.append(O.round_to(O.normal(1001 + i, hq * d).reshape(1, 1, hq, d), w["qdt"]))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        for (kw, vw), q, L in zip(rows, qs, lens):
+            L = int(L)
+            # TurboKvCache::keys_values: dequantize every cached row, cast to the cache dtype
+            k = O.round_to(O.dequantize_rows(kw, d, mode, bits, tab), w["qdt"]).reshape(1, hkv, L, d).transpose(0, 2, 1, 3)
+            v = O.round_to(O.dequantize_rows(vw, d, mode, bits, tab), w["qdt"]).reshape(1, hkv, L, d).transpose(0, 2, 1, 3)
+            O.unfused_attention(q, np.ascontiguousarray(k), np.ascontiguousarray(v), d ** -0.5, wr=0)
+    dt = (time.perf_counter() - t0) / reps
+    sub = dict(w)
+    sub["b"] = nseq
+    return dt, algorithmic_bytes(sub, lens)
+
+
+def run_reference(args, w, rank, world):
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    O.build() if not (ROOT / "oracle" / "liboracle.so").exists() else None
+    lens = seq_lens(w)
+    nseq = min(w["b"], 8 if w["lens"] == "uniform512-8192" else max(1, 65536 // int(lens[0])))
+    for _ in range(args.warmup):
+        cpu_reference_step(w, lens, min(nseq, 2))
+    times = []
+    nbytes = 0
+    for _ in range(args.steps):
+        dt, nbytes = cpu_reference_step(w, lens, nseq)
+        times.append(dt)
+    t = float(np.mean(times))
+    gbs = nbytes / t / 1e9
+    cores = O.num_threads()
+    sample = f"{nseq} of {w['b']} sequences of the batch per step ({int(lens[:nseq].sum())} keys x {w['hkv']} kv heads), dequantize + unfused attention"
+    line = {"impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": {"workload": f"{args.workload}: {w['desc']}", "sample": sample},
+            "tokens_per_s": nseq / t,
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, w, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as G
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    G.build()
+    P = G.load_package()
+    A = P._abi
+    b, hq, hkv, d = w["b"], w["hq"], w["hkv"], w["d"]
+    tdt = {"bf16": torch.bfloat16, "f16": torch.float16}[w["qdt"]]
+    lens = seq_lens(w, rank)
+    total_steps = args.steps + args.warmup + 8
+    cap = int(lens.max()) + 2 * total_steps + 4
+    kq = P.TurboQuantizer(P.QuantFormat.parse(w["fmt"]), d, w["rot"], 42, dev)
+    vq = P.TurboQuantizer(P.QuantFormat.parse(w["fmt"]), d, w["rot"], 44, dev)
+    rw = kq.row_words()
+    # several distinct caches, cycled, so that no step finds its rows in L2 (each is larger than L2 anyway for c2 / c4 / c5)
+    cache_bytes = b * hkv * cap * rw * 4 * 2
+    nbuf = int(max(2, min(4, (3 * 126e6) // cache_bytes + 1)))
+    from candle_rocm_vulkan_b200.turbo_quant import _kv_append
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    caches = []
+    for _ in range(nbuf):
+        kc = torch.zeros((b, hkv, cap, rw), dtype=torch.int32, device=dev)
+        vc = torch.zeros((b, hkv, cap, rw), dtype=torch.int32, device=dev)
+        # fill on the device in slabs: synthetic N(0, 1) keys / values with 1% outlier channels x8 (c2)
+        slab = 1024
+        chan = torch.ones((1, hkv, 1, d), device=dev, dtype=tdt)
+        if args.workload == "c2":
+            idx = torch.randperm(hkv * d, generator=g, device=dev)[: (hkv * d + 99) // 100]
+            chan.view(-1)[idx] = 8
+        for p0 in range(0, int(lens.max()), slab):
+            t = min(slab, int(lens.max()) - p0)
+            k = torch.randn((b, hkv, t, d), generator=g, device=dev, dtype=tdt) * chan
+            v = torch.randn((b, hkv, t, d), generator=g, device=dev, dtype=tdt) * chan
+            _kv_append(k, v, kc, vc, kq, vq, p0)
+        caches.append((kc, vc))
+    kv_len = torch.from_numpy(lens).to(dev)
+    q_host = torch.randn((b, hq, 1, d), dtype=tdt).pin_memory()
+    knew_host = torch.randn((b, hkv, 1, d), dtype=tdt).pin_memory()
+    vnew_host = torch.randn((b, hkv, 1, d), dtype=tdt).pin_memory()
+    out_host = torch.empty((b, hq, 1, d), dtype=tdt).pin_memory()
+    q = q_host.to(dev)
+    out = torch.empty((b, hq, 1, d), dtype=tdt, device=dev)
+    gathered = torch.empty((world * b, hq, 1, d), dtype=tdt, device=dev) if world > 1 else None
+    cfg = P.FlashAttnConfig(d ** -0.5).causal()
+
+    def step(i):
+        kc, vc = caches[i % nbuf]
+        P.attention_packed(q, kc, vc, kv_len, kq, vq, cfg, out=out)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    # ---- device-resident timing: K steps between two events, plus one event pair per step for the kernel time
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    barrier()
+    ev[0].record()
+    for i in range(args.steps):
+        step(i)
+        ev[i + 1].record()
+    barrier()
+    total_ms = ev[0].elapsed_time(ev[args.steps])
+    per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    # ---- end to end through the public API with host buffers: H2D of the step's inputs, append of the new
+    # token, attention, D2H of the outputs
+    lens_dev = kv_len.clone()
+    k_new = torch.empty((b, hkv, 1, d), dtype=tdt, device=dev)
+    v_new = torch.empty((b, hkv, 1, d), dtype=tdt, device=dev)
+
+    def e2e_step(i):
+        kc, vc = caches[i % nbuf]
+        q.copy_(q_host, non_blocking=True)
+        k_new.copy_(knew_host, non_blocking=True)
+        v_new.copy_(vnew_host, non_blocking=True)
+        _kv_append(k_new, v_new, kc, vc, kq, vq, lens_dev)
+        lens_dev.add_(1)
+        P.attention_packed(q, kc, vc, lens_dev, kq, vq, cfg, out=out)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out)
+        out_host.copy_(out, non_blocking=True)
+
+    for i in range(min(args.warmup, 3)):
+        e2e_step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # max over ranks
+    times = torch.tensor([total_ms, e2e_ms, float(np.mean(per_step))], device=dev, dtype=torch.float64)
+    nbytes = torch.tensor([algorithmic_bytes(w, lens)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(nbytes, op=dist.ReduceOp.SUM)
+    total_ms, e2e_ms, kern_ms = [float(x) for x in times.cpu()]
+    job_bytes = float(nbytes.cpu()[0])
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+        except OSError:
+            pass
+        peak, peak_kind = (peaks["hbm_gbs"], "measured copy bandwidth (MEASURED_PEAKS.json)") if "hbm_gbs" in peaks else (6650.0, "fallback")
+        ms = total_ms / args.steps
+        value = job_bytes / (ms * 1e-3) / 1e9
+        rank_bytes = algorithmic_bytes(w, lens)
+        achieved = rank_bytes / (kern_ms * 1e-3) / 1e9
+        cpu = None
+        if world == 1 or rank == 0:
+            nseq = min(b, 8 if w["lens"] == "uniform512-8192" else max(1, 65536 // int(lens[0])))
+            from oracle import oracle as O
+            cpu_reference_step(w, lens, min(2, nseq))
+            dt, cb = cpu_reference_step(w, lens, nseq)
+            cpu = {"value": cb / dt / 1e9, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+                   "sample": f"{nseq} of {b} sequences, one pass ({dt:.2f} s): dequantize rows to {w['qdt']} + unfused attention"}
+        launches_per_step = 2 if (int(lens.max()) > 128) else 1
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 mma / f32 softmax",
+            "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {w['desc']}", "batch_per_gpu": b, "hq": hq, "hkv": hkv, "head_dim": d,
+                       "kv_format": w["fmt"], "rotation": w["rot"], "total_keys_per_gpu": int(lens.sum()),
+                       "l2": f"{nbuf} caches of {cache_bytes / 1e6:.0f} MB cycled (each step reads other rows than the last; L2 is 126 MB)",
+                       "parallelism": f"batch shard x{world}, outputs all-gathered over NCCL" if world > 1 else "single GPU"},
+            "tokens_per_s": world * b / (ms * 1e-3),
+            "pct_of_8000_gbs_nominal": 100.0 * value / (8000.0 * world),
+            "e2e": {"value": job_bytes / (e2e_ms / args.steps * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": int(q_host.numel() + knew_host.numel() + vnew_host.numel()) * 2,
+                    "d2h_bytes_per_step": int(out_host.numel()) * 2, "ms_per_step": e2e_ms / args.steps,
+                    "tokens_per_s": world * b / (e2e_ms / args.steps * 1e-3)},
+            "gpu_launches": args.steps * launches_per_step,
+            "roofline": {"bound": "hbm", "kernel": "tq_decode_kernel (+ tq_combine_kernel in the same timed call)",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": peak_kind, "traffic": None},
+            "cpu_baseline": cpu, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w, rank, world)
+    else:
+        run_ours(args, w, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,207 @@
+// Host side of the attention over packed rows: argument checks, chunk planning, workspace layout,
+// format dispatch and the combine launch.
+#include <algorithm>
+#include <cstdlib>
+
+#include "tq_decode.cuh"
+
+namespace b200 {
+
+template <int KM, int VM, int HD>
+int launch_decode(const DecodeParams &p, dim3 grid, size_t smem, cudaStream_t stream);
+
+struct DecodePlan {
+    DecodeParams p;
+    uint32_t ny;
+    size_t smem;
+    size_t off_lse, off_meta, ws_bytes;
+    int hd_idx;
+};
+
+static int sm_count_cached() {
+    static thread_local int sms[16] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 16) return 148;
+    if (!sms[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        sms[dev] = n;
+    }
+    return sms[dev];
+}
+
+static int fill_decode_side(DecodeSide &s, const B200QuantSide &q, uint32_t d, const char *which) {
+    B200RowLayout l;
+    const int rc = b200_row_layout(q.mode, q.bits, (int)d, &l);
+    if (rc) return rc;
+    if (q.mode == B200_TURBO_PROD || (q.mode == B200_TURBO_MSE && q.bits != 4))
+        return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: %s format %d with %d bits is outside the fused kernel", which,
+                         q.mode, q.bits);
+    if (q.mode == B200_TURBO_MSE && !q.tab) return set_error(B200_ERR_BAD_ARG, "tq_attention: %s codebook table missing", which);
+    if (q.rotation == B200_ROT_HADAMARD) {
+        if (!q.signs) return set_error(B200_ERR_BAD_ARG, "tq_attention: %s hadamard signs missing", which);
+    } else if (q.rotation != B200_ROT_NONE) {
+        return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: only none / hadamard rotations are fused");
+    }
+    s.mode = q.mode;
+    s.code_words = l.code_words;
+    s.rsc_off = l.rsc_offset;
+    s.rot = q.rotation;
+    s.tab = q.tab;
+    s.signs = q.signs;
+    return B200_OK;
+}
+
+static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
+    if (!a) return set_error(B200_ERR_BAD_ARG, "tq_attention: null args");
+    if (a->hkv == 0 || a->hq % a->hkv != 0)
+        return set_error(B200_ERR_BAD_ARG, "tq_attention: %u query heads are not a multiple of %u kv heads", a->hq, a->hkv);
+    if (a->d != 64 && a->d != 128 && a->d != 256)
+        return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: head dim %u (fused kernel: 64, 128, 256)", a->d);
+    if (a->b > 65535) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: batch %u above 65535", a->b);
+    if (a->pages) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: paged rows are not implemented yet");
+    DecodeParams &p = pl.p;
+    memset(&p, 0, sizeof(p));
+    int rc = fill_decode_side(p.k, a->kq, a->d, "key");
+    if (rc) return rc;
+    rc = fill_decode_side(p.v, a->vq, a->d, "value");
+    if (rc) return rc;
+    for (int dt : {a->q_dtype, a->out_dtype})
+        if (dt != B200_F32 && dt != B200_F16 && dt != B200_BF16)
+            return set_error(B200_ERR_BAD_ARG, "tq_attention: q / out dtype must be f32, f16 or bf16");
+    p.q = a->q;
+    p.out = a->out;
+    p.q_dtype = a->q_dtype;
+    p.out_dtype = a->out_dtype;
+    p.q_sb = a->q_strides[0]; p.q_sh = a->q_strides[1]; p.q_ss = a->q_strides[2];
+    p.o_sb = a->out_strides[0]; p.o_sh = a->out_strides[1]; p.o_ss = a->out_strides[2];
+    p.k_rows = a->k_rows;
+    p.v_rows = a->v_rows;
+    p.k_sb = a->k_strides[0]; p.k_sh = a->k_strides[1]; p.k_ss = a->k_strides[2];
+    p.v_sb = a->v_strides[0]; p.v_sh = a->v_strides[1]; p.v_ss = a->v_strides[2];
+    B200RowLayout kl, vl;
+    b200_row_layout(a->kq.mode, a->kq.bits, (int)a->d, &kl);
+    b200_row_layout(a->vq.mode, a->vq.bits, (int)a->d, &vl);
+    if (p.k_ss < (uint64_t)kl.row_words || p.v_ss < (uint64_t)vl.row_words)
+        return set_error(B200_ERR_BAD_ARG, "tq_attention: row strides %llu / %llu below the row sizes %d / %d",
+                         (unsigned long long)p.k_ss, (unsigned long long)p.v_ss, kl.row_words, vl.row_words);
+    if (p.k_ss > 512 || p.v_ss > 512) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: row stride above 512 words");
+    p.kv_len = a->kv_len_dev;
+    p.b = a->b; p.lq = a->lq; p.lk = a->lk; p.hq = a->hq; p.hkv = a->hkv; p.d = a->d;
+    p.group = a->hq / a->hkv;
+    p.rows_per_kv = p.group * a->lq;
+    p.packs = (p.rows_per_kv + PACK - 1) / PACK;
+    p.scale = a->scale;
+    p.softcap = a->softcap;
+    p.wl = a->wl;
+    p.wr = a->wr;
+    p.alibi = a->alibi;
+    p.alibi_bs = a->alibi_bstride;
+    p.status = a->status;
+    pl.ny = a->hkv * p.packs;
+    if ((uint64_t)pl.ny > 65535) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: too many row packs");
+
+    // chunk of keys per block: enough blocks for every SM, chunks a multiple of the 128 keys
+    // that the four warps take per round
+    const uint64_t lk = std::max<uint32_t>(a->lk, 1);
+    uint64_t chunk;
+    if (a->splits > 0) {
+        chunk = (lk + a->splits - 1) / a->splits;
+    } else {
+        static const long env_chunk = [] { const char *e = getenv("B200_DECODE_CHUNK"); return e ? atol(e) : 0l; }();
+        if (env_chunk > 0) {
+            chunk = (uint64_t)env_chunk;
+        } else {
+            const uint64_t total = (uint64_t)a->b * pl.ny * lk;
+            chunk = total / ((uint64_t)sm_count_cached() * 16);
+            chunk = std::min<uint64_t>(std::max<uint64_t>(chunk, 128), 4096);
+        }
+    }
+    chunk = (chunk + DW * WK - 1) / (DW * WK) * (DW * WK);
+    p.chunk = (uint32_t)std::min<uint64_t>(chunk, 1u << 30);
+    p.max_splits = (uint32_t)((lk + p.chunk - 1) / p.chunk);
+    if (p.max_splits > 65535) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: too many key chunks");
+
+    p.k_stage_bytes = (uint32_t)((WK * p.k_ss * 4 + 16 + 15) / 16 * 16);
+    p.v_stage_bytes = (uint32_t)((WK * p.v_ss * 4 + 16 + 15) / 16 * 16);
+    pl.smem = 128 + 2048 + (size_t)DW * PACK * a->d * 4 + 2 * DW * PACK * 4 +
+              (size_t)DW * NS * (p.k_stage_bytes + p.v_stage_bytes);
+    if (pl.smem > 227 * 1024) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: %zu bytes of shared memory", pl.smem);
+
+    const size_t slots = (size_t)a->b * pl.ny * p.max_splits * PACK;
+    const size_t part_o = p.max_splits > 1 ? slots * a->d * 4 : 0;
+    const size_t part_l = p.max_splits > 1 ? slots * 4 : 0;
+    pl.off_lse = (part_o + 255) / 256 * 256;
+    pl.off_meta = (pl.off_lse + part_l + 255) / 256 * 256;
+    pl.ws_bytes = pl.off_meta + (size_t)a->b * pl.ny * 4;
+    pl.hd_idx = a->d == 64 ? 0 : (a->d == 128 ? 1 : 2);
+    return B200_OK;
+}
+
+template <int KM, int VM>
+static int dispatch_hd(const DecodePlan &pl, dim3 grid, cudaStream_t stream) {
+    switch (pl.hd_idx) {
+    case 0: return launch_decode<KM, VM, 64>(pl.p, grid, pl.smem, stream);
+    case 1: return launch_decode<KM, VM, 128>(pl.p, grid, pl.smem, stream);
+    default: return launch_decode<KM, VM, 256>(pl.p, grid, pl.smem, stream);
+    }
+}
+
+template <int KM>
+static int dispatch_v(const DecodePlan &pl, dim3 grid, cudaStream_t stream) {
+    switch (pl.p.v.mode) {
+    case B200_TURBO_MSE: return dispatch_hd<KM, B200_TURBO_MSE>(pl, grid, stream);
+    case B200_MXFP4: return dispatch_hd<KM, B200_MXFP4>(pl, grid, stream);
+    case B200_NVFP4: return dispatch_hd<KM, B200_NVFP4>(pl, grid, stream);
+    case B200_MXFP8: return dispatch_hd<KM, B200_MXFP8>(pl, grid, stream);
+    default: return dispatch_hd<KM, B200_FP8_ROW>(pl, grid, stream);
+    }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" size_t b200_tq_attention_workspace_bytes(const B200TqAttnArgs *a) {
+    DecodePlan pl;
+    if (make_plan(a, pl)) return 0;
+    return pl.ws_bytes;
+}
+
+extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_) {
+    DecodePlan pl;
+    const int rc = make_plan(a, pl);
+    if (rc) return rc;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if ((uint64_t)a->b * a->hq * a->lq == 0) return B200_OK;
+    if (!a->q || !a->out || !a->k_rows || !a->v_rows) return set_error(B200_ERR_BAD_ARG, "tq_attention: null pointer");
+    if (!a->workspace || a->workspace_bytes < pl.ws_bytes)
+        return set_error(B200_ERR_WORKSPACE, "tq_attention: workspace of %zu bytes needed, %zu given", pl.ws_bytes,
+                         a->workspace ? a->workspace_bytes : (size_t)0);
+    if (reinterpret_cast<uintptr_t>(a->workspace) & 15) return set_error(B200_ERR_BAD_ARG, "tq_attention: workspace must be 16-byte aligned");
+    DecodeParams &p = pl.p;
+    char *ws = reinterpret_cast<char *>(a->workspace);
+    p.part_o = reinterpret_cast<float *>(ws);
+    p.part_lse = reinterpret_cast<float *>(ws + pl.off_lse);
+    p.meta = reinterpret_cast<int32_t *>(ws + pl.off_meta);
+    const dim3 grid(p.max_splits, pl.ny, a->b);
+    int lrc;
+    switch (p.k.mode) {
+    case B200_TURBO_MSE: lrc = dispatch_v<B200_TURBO_MSE>(pl, grid, stream); break;
+    case B200_MXFP4: lrc = dispatch_v<B200_MXFP4>(pl, grid, stream); break;
+    case B200_NVFP4: lrc = dispatch_v<B200_NVFP4>(pl, grid, stream); break;
+    case B200_MXFP8: lrc = dispatch_v<B200_MXFP8>(pl, grid, stream); break;
+    default: lrc = dispatch_v<B200_FP8_ROW>(pl, grid, stream); break;
+    }
+    if (lrc) return lrc;
+    if (p.max_splits > 1) {
+        const size_t rows = (size_t)a->b * a->hq * a->lq;
+        const unsigned gx = (unsigned)std::min<size_t>((rows + 3) / 4, (size_t)sm_count_cached() * 16);
+        if (a->d == 64) tq_combine_kernel<64><<<gx, 128, 0, stream>>>(p);
+        else if (a->d == 128) tq_combine_kernel<128><<<gx, 128, 0, stream>>>(p);
+        else tq_combine_kernel<256><<<gx, 128, 0, stream>>>(p);
+        return check_launch("tq_combine");
+    }
+    return B200_OK;
+}

@@ -1,0 +1,37 @@
+// Instantiations of the decode kernel for one key format (B200_KM is given on the command line so
+// that the formats compile in parallel).
+#include "tq_decode.cuh"
+
+#ifndef B200_KM
+#error "define B200_KM (key format id)"
+#endif
+
+namespace b200 {
+
+template <int KM, int VM, int HD>
+int launch_decode(const DecodeParams &p, dim3 grid, size_t smem, cudaStream_t stream) {
+    auto kern = tq_decode_kernel<KM, VM, HD, false>;
+    static thread_local size_t configured[16] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 16 && configured[dev] < smem) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "tq_attention: shared memory opt-in of %zu bytes: %s", smem, cudaGetErrorString(e));
+        configured[dev] = smem;
+    }
+    kern<<<grid, DW * 32, smem, stream>>>(p);
+    return check_launch("tq_attention");
+}
+
+#define INST(VM)                                                                                \
+    template int launch_decode<B200_KM, VM, 64>(const DecodeParams &, dim3, size_t, cudaStream_t);  \
+    template int launch_decode<B200_KM, VM, 128>(const DecodeParams &, dim3, size_t, cudaStream_t); \
+    template int launch_decode<B200_KM, VM, 256>(const DecodeParams &, dim3, size_t, cudaStream_t);
+
+INST(B200_TURBO_MSE)
+INST(B200_MXFP4)
+INST(B200_NVFP4)
+INST(B200_MXFP8)
+INST(B200_FP8_ROW)
+
+}  // namespace b200

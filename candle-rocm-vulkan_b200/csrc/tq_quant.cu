@@ -1,0 +1,399 @@
+// Row quantizer / dequantizer and the fused quantize-on-append of the compressed KV cache.
+//
+// One warp owns one row (lane l holds elements l, l + 32, l + 64, ...): the row maximum and the
+// per-block maxima are warp shuffles instead of the seven-barrier shared-memory trees of the
+// reference's one-workgroup-per-row kernel (candle-core/kernels/turbo_quant_impl.h:71-159), and
+// the packed row goes straight to its slot of the capacity buffer. Codes, block scales and rsc0
+// are bit-exact with that kernel: maxima do not depend on the reduction order, the sum of
+// squares of the codebook formats reproduces the order of its 128-lane tree
+// (candle-core/kernels/accel_common.h:255-267), all divisions are IEEE.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int QW = 4;  // warps (rows in flight) per block
+
+struct QuantSideParams {
+    const void *src;
+    uint32_t *dst;
+    const float *tab;
+    const float *signs;
+    const int32_t *pos;
+    uint64_t s_b, s_h, s_t;  // source strides (elements)
+    uint64_t c_b, c_h, c_t;  // destination strides (words)
+    int32_t pos0;
+    int32_t mode, cb, code_words, aux_words, row_words;
+    int32_t rot;
+};
+
+struct QuantParams {
+    QuantSideParams side[2];
+    uint32_t nb, nh, nt, d;
+    int32_t src_dtype;
+};
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// EPL: elements per lane (D <= 32 * EPL)
+template <int EPL>
+__global__ void __launch_bounds__(QW * 32) quant_rows_kernel(const QuantParams p) {
+    __shared__ uint8_t s_codes[QW][32 * EPL];
+    __shared__ uint32_t s_scales[QW][2 * EPL];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const QuantSideParams &sp = p.side[blockIdx.y];
+    const uint32_t D = p.d;
+    const int nk = (int)((D + 31) / 32);
+    const uint64_t rows = (uint64_t)p.nb * p.nh * p.nt;
+    uint8_t *codes = s_codes[warp];
+    uint32_t *sc = s_scales[warp];
+
+    for (uint64_t row = (uint64_t)blockIdx.x * QW + warp; row < rows; row += (uint64_t)gridDim.x * QW) {
+        const uint32_t t = (uint32_t)(row % p.nt);
+        const uint32_t h = (uint32_t)((row / p.nt) % p.nh);
+        const uint32_t b = (uint32_t)(row / ((uint64_t)p.nt * p.nh));
+        const char *src = reinterpret_cast<const char *>(sp.src) +
+                          (b * sp.s_b + h * sp.s_h + t * sp.s_t) * (uint64_t)dtype_size(p.src_dtype);
+        const int64_t pos = (sp.pos ? sp.pos[b] : sp.pos0) + (int64_t)t;
+        uint32_t *orow = sp.dst + b * sp.c_b + h * sp.c_h + (uint64_t)pos * sp.c_t;
+
+        float x[EPL];
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) {
+            const uint32_t j = lane + 32 * k;
+            x[k] = (k < nk && j < D) ? load_elem_rt(src, j, p.src_dtype) : 0.0f;
+        }
+
+        if (sp.rot == B200_ROT_HADAMARD) {
+            // y = H diag(sign) x / sqrt(D): signs, Walsh-Hadamard butterflies (element index bits
+            // 0-4 across lanes, higher bits across registers), then the scale
+#pragma unroll
+            for (int k = 0; k < EPL; ++k) {
+                const uint32_t j = lane + 32 * k;
+                if (k < nk && j < D) x[k] *= sp.signs[j];
+            }
+            for (uint32_t o = 1; o < 32 && o < D; o <<= 1) {
+#pragma unroll
+                for (int k = 0; k < EPL; ++k) {
+                    const float y = __shfl_xor_sync(0xffffffffu, x[k], o);
+                    x[k] = (lane & o) ? y - x[k] : x[k] + y;
+                }
+            }
+#pragma unroll
+            for (int o = 1; o < EPL; o <<= 1) {
+                if (o < nk) {
+#pragma unroll
+                    for (int k = 0; k < EPL; ++k) {
+                        if (!(k & o)) {
+                            const float a = x[k], c = x[k | o];
+                            x[k] = a + c;
+                            x[k | o] = a - c;
+                        }
+                    }
+                }
+            }
+            const float s = 1.0f / sqrtf((float)D);
+#pragma unroll
+            for (int k = 0; k < EPL; ++k) x[k] *= s;
+        }
+
+        const uint32_t mode = sp.mode, cb = sp.cb;
+        float rsc0 = 1.0f;
+        uint32_t c[EPL];
+        if (mode <= B200_TURBO_PROD) {
+            // sum of squares in the order of the reference's 128 lanes: lane t adds j = t,
+            // t + 128, ..., then red[t] += red[t + s] for s = 64 ... 1
+            float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int k = 0; k < EPL; ++k) part[k & 3] = __fadd_rn(part[k & 3], __fmul_rn(x[k], x[k]));
+            float ss = __fadd_rn(__fadd_rn(part[0], part[2]), __fadd_rn(part[1], part[3]));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, o));
+            ss = __shfl_sync(0xffffffffu, ss, 0);
+            const float norm = __fsqrt_rn(ss);
+            const float inv = norm > 0.0f ? __fdiv_rn(1.0f, norm) : 0.0f;
+            const uint32_t nbnd = (1u << cb) - 1u;
+            rsc0 = norm;
+#pragma unroll
+            for (int k = 0; k < EPL; ++k) {
+                const float u = __fmul_rn(x[k], inv);
+                uint32_t idx = 0;
+                for (uint32_t bi = 0; bi < nbnd; ++bi) idx += u >= __ldg(sp.tab + 16 + bi) ? 1u : 0u;
+                c[k] = idx;
+            }
+        } else if (mode == B200_MXFP4 || mode == B200_MXFP8) {
+            const int emax = mode == B200_MXFP4 ? 2 : 8;
+#pragma unroll
+            for (int k = 0; k < EPL; ++k) {
+                const float bm = warp_max(fabsf(x[k]));  // block k = elements [32 k, 32 k + 32)
+                const uint32_t code = mx_scale_code(bm, emax);
+                const float s = e8m0_to_f(code);
+                const float qv = __fdiv_rn(x[k], s);
+                c[k] = code == 0 ? 0u : (mode == B200_MXFP4 ? f_to_fp4(qv) : f_to_e4m3(qv));
+                if (lane == 0 && k < nk) sc[k] = code;
+            }
+        } else {
+            float am = 0.0f;
+#pragma unroll
+            for (int k = 0; k < EPL; ++k) am = fmaxf(am, fabsf(x[k]));
+            am = warp_max(am);
+            if (mode == B200_NVFP4) {
+                const float g = am > 0.0f ? __fdiv_rn(am, 2688.0f) : 1.0f;
+                rsc0 = g;
+#pragma unroll
+                for (int k = 0; k < EPL; ++k) {
+                    float bm = fabsf(x[k]);  // blocks 2 k (lanes 0-15) and 2 k + 1 (lanes 16-31)
+#pragma unroll
+                    for (int o = 8; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+                    const uint32_t scode = f_to_e4m3(__fdiv_rn(__fdiv_rn(bm, 6.0f), g));
+                    const float eff = __fmul_rn(e4m3_to_f(scode), g);
+                    c[k] = eff > 0.0f ? f_to_fp4(__fdiv_rn(x[k], eff)) : 0u;
+                    if ((lane & 15) == 0 && k < nk) sc[2 * k + (lane >> 4)] = scode;
+                }
+            } else {
+                const float s = am > 0.0f ? __fdiv_rn(am, 448.0f) : 1.0f;
+                rsc0 = s;
+#pragma unroll
+                for (int k = 0; k < EPL; ++k) c[k] = f_to_e4m3(__fdiv_rn(x[k], s));
+            }
+        }
+
+#pragma unroll
+        for (int k = 0; k < EPL; ++k)
+            if (k < nk) codes[lane + 32 * k] = (uint8_t)c[k];
+        __syncwarp();
+
+        // pack: element e at bit e * cb of the little-endian word stream
+        const uint32_t mask = (1u << cb) - 1u;
+        for (uint32_t w = lane; w < (uint32_t)sp.code_words; w += 32) {
+            const uint32_t bit0 = w * 32u;
+            const uint32_t e0 = bit0 / cb;
+            uint32_t e1 = (bit0 + 31u) / cb + 1u;
+            e1 = min(e1, D);
+            uint32_t word = 0;
+            for (uint32_t e = e0; e < e1; ++e) {
+                const int sh = (int)(e * cb) - (int)bit0;
+                const uint32_t cc = codes[e] & mask;
+                word |= sh >= 0 ? (cc << sh) : (cc >> (-sh));
+            }
+            orow[w] = word;
+        }
+        const bool scales = mode == B200_MXFP4 || mode == B200_MXFP8 || mode == B200_NVFP4;
+        const uint32_t nblk = mode == B200_NVFP4 ? (D >> 4) : (D >> 5);
+        for (uint32_t w = lane; w < (uint32_t)sp.aux_words; w += 32) {
+            uint32_t word = 0;
+            if (scales)
+                for (uint32_t e = 0; e < 4u; ++e)
+                    if (w * 4u + e < nblk) word |= (sc[w * 4u + e] & 0xffu) << (8u * e);
+            orow[sp.code_words + w] = word;
+        }
+        if (lane == 0) {
+            orow[sp.code_words + sp.aux_words] = f2u(rsc0);
+            orow[sp.code_words + sp.aux_words + 1] = 0u;
+        }
+        __syncwarp();
+    }
+}
+
+// rsc0 * element for every element (candle-core/kernels/turbo_quant_impl.h:44-53,208-218)
+__global__ void __launch_bounds__(256) dequant_rows_kernel(const uint32_t *__restrict__ data, const float *__restrict__ tab,
+                                                          float *__restrict__ out, uint64_t rows, uint32_t D,
+                                                          uint64_t stride, uint32_t mode, uint32_t cb,
+                                                          uint32_t code_words, uint32_t rsc_off) {
+    const uint64_t n = rows * D;
+    for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t row = idx / D;
+        const uint32_t j = (uint32_t)(idx % D);
+        const uint32_t *r = data + row * stride;
+        const uint32_t pos = j * cb, wi = pos >> 5, sh = pos & 31u;
+        uint32_t c = r[wi] >> sh;
+        if (sh + cb > 32u) c |= r[wi + 1] << (32u - sh);
+        c &= (1u << cb) - 1u;
+        const uint32_t *aux = r + code_words;
+        float e;
+        if (mode <= B200_TURBO_PROD) e = tab[c];
+        else if (mode == B200_MXFP4) e = __fmul_rn(fp4_to_f(c), e8m0_to_f((aux[j >> 7] >> (((j >> 5) & 3u) * 8u)) & 0xffu));
+        else if (mode == B200_NVFP4) e = __fmul_rn(fp4_to_f(c), e4m3_to_f((aux[j >> 6] >> (((j >> 4) & 3u) * 8u)) & 0xffu));
+        else if (mode == B200_MXFP8) e = __fmul_rn(e4m3_to_f(c), e8m0_to_f((aux[j >> 7] >> (((j >> 5) & 3u) * 8u)) & 0xffu));
+        else e = e4m3_to_f(c);
+        out[idx] = __fmul_rn(u2f(r[rsc_off]), e);
+    }
+}
+
+// y = H diag(s) x / sqrt(D) (forward) or x = diag(s) H y / sqrt(D) (back), one warp per row, f32
+__global__ void __launch_bounds__(128) hadamard_rows_kernel(const float *__restrict__ in, float *__restrict__ out,
+                                                           const float *__restrict__ signs, uint64_t rows, uint32_t D,
+                                                           int inverse) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nk = (int)((D + 31) / 32);
+    for (uint64_t row = (uint64_t)blockIdx.x * 4 + warp; row < rows; row += (uint64_t)gridDim.x * 4) {
+        float x[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+            const uint32_t j = lane + 32 * k;
+            x[k] = (k < nk && j < D) ? in[row * D + j] * (inverse ? 1.0f : signs[j]) : 0.0f;
+        }
+        for (uint32_t o = 1; o < 32 && o < D; o <<= 1) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+                const float y = __shfl_xor_sync(0xffffffffu, x[k], o);
+                x[k] = (lane & o) ? y - x[k] : x[k] + y;
+            }
+        }
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            if (o < nk) {
+#pragma unroll
+                for (int k = 0; k < 32; ++k) {
+                    if (!(k & o)) {
+                        const float a = x[k], c = x[k | o];
+                        x[k] = a + c;
+                        x[k | o] = a - c;
+                    }
+                }
+            }
+        }
+        const float s = 1.0f / sqrtf((float)D);
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+            const uint32_t j = lane + 32 * k;
+            if (k < nk && j < D) out[row * D + j] = x[k] * s * (inverse ? signs[j] : 1.0f);
+        }
+    }
+}
+
+static int fill_side(QuantSideParams &sp, const B200QuantSide &q, uint32_t d) {
+    B200RowLayout l;
+    const int rc = b200_row_layout(q.mode, q.bits, (int)d, &l);
+    if (rc) return rc;
+    if (q.mode == B200_TURBO_PROD)
+        return set_error(B200_ERR_UNSUPPORTED_SHAPE, "turbo prod (QJL) rows are not implemented by the fused quantizer");
+    if (q.mode <= B200_TURBO_PROD && !q.tab) return set_error(B200_ERR_BAD_ARG, "turbo formats need the codebook table");
+    if (q.rotation == B200_ROT_HADAMARD) {
+        if (!q.signs) return set_error(B200_ERR_BAD_ARG, "hadamard rotation needs the sign vector");
+        if (d & (d - 1)) return set_error(B200_ERR_BAD_ARG, "hadamard rotation needs a power of two length, got %u", d);
+    } else if (q.rotation != B200_ROT_NONE) {
+        return set_error(B200_ERR_UNSUPPORTED_SHAPE, "only none / hadamard rotations are fused");
+    }
+    sp.tab = q.tab;
+    sp.signs = q.signs;
+    sp.rot = q.rotation;
+    sp.mode = q.mode;
+    sp.cb = l.code_bits;
+    sp.code_words = l.code_words;
+    sp.aux_words = l.aux_words;
+    sp.row_words = l.row_words;
+    return B200_OK;
+}
+
+static int launch_quant(const QuantParams &p, int sides, cudaStream_t stream) {
+    const uint64_t rows = (uint64_t)p.nb * p.nh * p.nt;
+    if (rows == 0) return B200_OK;
+    const unsigned gx = (unsigned)std::min<uint64_t>((rows + QW - 1) / QW, 148ull * 64);
+    const dim3 grid(gx, sides), block(QW * 32);
+    if (p.d <= 128) quant_rows_kernel<4><<<grid, block, 0, stream>>>(p);
+    else if (p.d <= 256) quant_rows_kernel<8><<<grid, block, 0, stream>>>(p);
+    else quant_rows_kernel<32><<<grid, block, 0, stream>>>(p);
+    return check_launch("tq_quantize");
+}
+
+} // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_tq_quantize(const B200TqQuantArgs *a, b200_stream_t stream) {
+    if (!a) return set_error(B200_ERR_BAD_ARG, "tq_quantize: null args");
+    if (a->rows == 0) return B200_OK;
+    if (!a->src || !a->out) return set_error(B200_ERR_BAD_ARG, "tq_quantize: null pointer");
+    if (a->src_dtype != B200_F32 && a->src_dtype != B200_F16 && a->src_dtype != B200_BF16)
+        return set_error(B200_ERR_BAD_ARG, "tq_quantize: source dtype must be f32, f16 or bf16");
+    QuantParams p;
+    memset(&p, 0, sizeof(p));
+    B200QuantSide q = {a->mode, a->bits, a->tab, B200_ROT_NONE, nullptr};
+    const int rc = fill_side(p.side[0], q, a->dim);
+    if (rc) return rc;
+    QuantSideParams &sp = p.side[0];
+    sp.src = a->src;
+    sp.dst = a->out;
+    sp.s_t = a->src_stride;
+    sp.c_t = a->out_stride ? a->out_stride : (uint64_t)sp.row_words;
+    if (sp.c_t < (uint64_t)sp.row_words) return set_error(B200_ERR_BAD_ARG, "tq_quantize: output stride below the row size");
+    if (a->rows > 0xffffffffull) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_quantize: too many rows");
+    p.nb = 1;
+    p.nh = 1;
+    p.nt = (uint32_t)a->rows;
+    p.d = a->dim;
+    p.src_dtype = a->src_dtype;
+    return launch_quant(p, 1, (cudaStream_t)stream);
+}
+
+extern "C" int b200_kv_append(const B200KvAppendArgs *a, b200_stream_t stream) {
+    if (!a) return set_error(B200_ERR_BAD_ARG, "kv_append: null args");
+    if ((uint64_t)a->b * a->hkv * a->t == 0) return B200_OK;
+    if (!a->k || !a->v || !a->k_cache || !a->v_cache) return set_error(B200_ERR_BAD_ARG, "kv_append: null pointer");
+    if (a->src_dtype != B200_F32 && a->src_dtype != B200_F16 && a->src_dtype != B200_BF16)
+        return set_error(B200_ERR_BAD_ARG, "kv_append: source dtype must be f32, f16 or bf16");
+    if (!a->pos && a->pos0 < 0) return set_error(B200_ERR_BAD_ARG, "kv_append: negative position");
+    QuantParams p;
+    memset(&p, 0, sizeof(p));
+    int rc = fill_side(p.side[0], a->kq, a->d);
+    if (rc) return rc;
+    rc = fill_side(p.side[1], a->vq, a->d);
+    if (rc) return rc;
+    const void *srcs[2] = {a->k, a->v};
+    uint32_t *dsts[2] = {a->k_cache, a->v_cache};
+    const uint64_t *ss[2] = {a->k_strides, a->v_strides};
+    const uint64_t *cs[2] = {a->k_cache_strides, a->v_cache_strides};
+    for (int s = 0; s < 2; ++s) {
+        QuantSideParams &sp = p.side[s];
+        sp.src = srcs[s];
+        sp.dst = dsts[s];
+        sp.s_b = ss[s][0];
+        sp.s_h = ss[s][1];
+        sp.s_t = ss[s][2];
+        sp.c_b = cs[s][0];
+        sp.c_h = cs[s][1];
+        sp.c_t = cs[s][2];
+        sp.pos = a->pos;
+        sp.pos0 = a->pos0;
+        if (sp.c_t < (uint64_t)sp.row_words) return set_error(B200_ERR_BAD_ARG, "kv_append: cache row stride below the row size");
+    }
+    p.nb = a->b;
+    p.nh = a->hkv;
+    p.nt = a->t;
+    p.d = a->d;
+    p.src_dtype = a->src_dtype;
+    return launch_quant(p, 2, (cudaStream_t)stream);
+}
+
+extern "C" int b200_tq_dequantize(const B200TqDequantArgs *a, b200_stream_t stream) {
+    if (!a) return set_error(B200_ERR_BAD_ARG, "tq_dequantize: null args");
+    if (a->rows == 0) return B200_OK;
+    if (!a->data || !a->out) return set_error(B200_ERR_BAD_ARG, "tq_dequantize: null pointer");
+    B200RowLayout l;
+    const int rc = b200_row_layout(a->mode, a->bits, (int)a->dim, &l);
+    if (rc) return rc;
+    if (a->mode <= B200_TURBO_PROD && !a->tab) return set_error(B200_ERR_BAD_ARG, "turbo formats need the codebook table");
+    const uint64_t stride = a->data_stride ? a->data_stride : (uint64_t)l.row_words;
+    const uint64_t n = a->rows * a->dim;
+    const unsigned grid = (unsigned)std::min<uint64_t>((n + 255) / 256, 148ull * 32);
+    dequant_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a->data, a->tab, a->out, a->rows, a->dim, stride, a->mode,
+                                                               l.code_bits, l.code_words, l.rsc_offset);
+    return check_launch("tq_dequantize");
+}
+
+extern "C" int b200_tq_rotate(const float *in, float *out, const float *signs, uint64_t rows, uint32_t dim, int inverse,
+                              b200_stream_t stream) {
+    if (rows == 0) return B200_OK;
+    if (!in || !out || !signs) return set_error(B200_ERR_BAD_ARG, "tq_rotate: null pointer");
+    if (dim == 0 || dim > 1024 || (dim & (dim - 1)))
+        return set_error(B200_ERR_BAD_ARG, "hadamard rotation needs a power of two length up to 1024, got %u", dim);
+    const unsigned grid = (unsigned)std::min<uint64_t>((rows + 3) / 4, 148ull * 32);
+    hadamard_rows_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(in, out, signs, rows, dim, inverse);
+    return check_launch("tq_rotate");
+}

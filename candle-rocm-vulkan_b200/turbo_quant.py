@@ -1,0 +1,391 @@
+"""Host-side mirror of the reference's compressed KV cache API over libb200attn.so.
+
+Names, argument meaning and error behaviour follow candle-nn/src/turbo_quant.rs
+(`TurboQuantizer`, `QuantizedTensor`, `TurboKvCache`, `attention_packed`) and
+candle-nn/src/flash_attn.rs (`FlashAttnConfig`), so tests written against the reference read the
+same here. torch only provides device memory and streams; every computation is a call through
+the C ABI (include/b200attn.h). There is no CPU path: tensors must live on a CUDA device.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Optional, Tuple
+
+import torch
+
+from . import _abi as A
+
+
+class QuantFormat:
+    """A quantization format: `QuantFormat.parse("mxfp4")`, `QuantFormat.turbo_mse(4)` ...
+    (candle-core/src/accel/formats.rs:21-135)."""
+
+    def __init__(self, mode: int, bits: int = 4):
+        self.mode, self.bits = mode, bits
+
+    @staticmethod
+    def turbo_mse(bits=4):
+        return QuantFormat(A.TURBO_MSE, bits)
+
+    @staticmethod
+    def parse(s: str) -> "QuantFormat":
+        t = s.strip().lower().replace("-", "").replace("_", "").replace(" ", "")
+        digits = "".join(ch for ch in t if ch.isdigit())
+        name = "".join(ch for ch in t if not ch.isdigit())
+        bits = int(digits) if digits else 0
+        if name in ("turbo", "tq", "mse", "turbomse", "tqmse", "turboquant", "lloydmax"):
+            f = QuantFormat(A.TURBO_MSE, bits or 4)
+        elif name in ("prod", "turboprod", "tqprod", "qjl", "turboqjl"):
+            f = QuantFormat(A.TURBO_PROD, bits or 4)
+        elif name == "nvfp" and digits == "4":
+            f = QuantFormat(A.NVFP4)
+        elif name == "mxfp" and digits == "4":
+            f = QuantFormat(A.MXFP4)
+        elif name == "mxfp" and digits == "8":
+            f = QuantFormat(A.MXFP8)
+        elif (name in ("fp", "nvfp") and digits == "8") or (name == "em" and digits == "43"):
+            f = QuantFormat(A.FP8_ROW)
+        else:
+            raise ValueError(f"unknown quantization format {s!r} (turbo[1-4], prod[2-5], nvfp4, mxfp4, mxfp8, fp8)")
+        return f
+
+    def name(self) -> str:
+        return {A.TURBO_MSE: f"turbo-mse{self.bits}", A.TURBO_PROD: f"turbo-prod{self.bits}", A.NVFP4: "nvfp4",
+                A.MXFP4: "mxfp4", A.MXFP8: "mxfp8", A.FP8_ROW: "fp8"}[self.mode]
+
+    def is_turbo(self) -> bool:
+        return self.mode <= A.TURBO_PROD
+
+    def __repr__(self):
+        return self.name()
+
+
+_DTYPES = {torch.float32: A.F32, torch.float16: A.F16, torch.bfloat16: A.BF16}
+
+
+def _dtype_id(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise ValueError(f"unsupported dtype {t.dtype} (f32, f16, bf16)") from None
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _need_cuda(t: torch.Tensor, what: str):
+    if not t.is_cuda:
+        raise RuntimeError(f"{what} must be on a CUDA device: this library has no CPU path")
+
+
+@dataclass
+class FlashAttnConfig:
+    """Options of one attention call (candle-nn/src/flash_attn.rs:26-123)."""
+    softmax_scale: float
+    window_size_left: Optional[int] = None
+    window_size_right: Optional[int] = None
+    softcap: Optional[float] = None
+    alibi_slopes: Optional[torch.Tensor] = None
+    k_descale: float = 1.0
+    v_descale: float = 1.0
+    splits: int = 0  # key splits per sequence (SplitKv::Fixed), 0 = chosen by the library
+
+    def causal(self):
+        self.window_size_right = 0
+        return self
+
+    def window(self, left, right):
+        self.window_size_left, self.window_size_right = left, right
+        return self
+
+    def window_i32(self) -> Tuple[int, int]:
+        cv = lambda w: -1 if w is None else min(int(w), 2**31 - 1)
+        return cv(self.window_size_left), cv(self.window_size_right)
+
+
+@dataclass
+class QuantizedTensor:
+    """A tensor quantized row by row along its last dimension (turbo_quant.rs:39-53)."""
+    data: torch.Tensor
+    shape: torch.Size
+    dtype: torch.dtype
+
+    def size_in_bytes(self) -> int:
+        return self.data.numel() * 4
+
+
+class TurboQuantizer:
+    """Quantizes vectors of a fixed length in one format (turbo_quant.rs:57-321). `rotation`:
+    "none" or "hadamard" ("auto" resolves to hadamard for powers of two, like RotationKind::Auto;
+    the dense rotation for other lengths is not offered by the fused kernels)."""
+
+    def __init__(self, format: QuantFormat, dim: int, rotation: str = "auto", seed: int = 42, device="cuda"):
+        self.format, self.dim, self.device = format, dim, torch.device(device)
+        self.layout = A.row_layout(format.mode, format.bits, dim)
+        if format.mode == A.TURBO_PROD:
+            raise A.B200Error(A.ERR_UNSUPPORTED_SHAPE, "turbo prod (QJL) rows are not implemented by the fused kernels")
+        pow2 = dim & (dim - 1) == 0
+        if rotation == "auto":
+            rotation = "hadamard" if pow2 else "none"
+        if rotation not in ("none", "hadamard"):
+            raise ValueError("rotation must be none, hadamard or auto")
+        self.rotation = rotation
+        self.seed = seed
+        tab = (C.c_float * 32)()
+        if format.is_turbo():
+            A.check(A.lib().b200_codebook(dim, format.bits, tab))
+        self.tab = torch.tensor(list(tab), dtype=torch.float32, device=self.device)
+        self.signs = None
+        if rotation == "hadamard":
+            s = (C.c_float * dim)()
+            A.check(A.lib().b200_hadamard_signs(dim, seed, s))
+            self.signs = torch.tensor(list(s), dtype=torch.float32, device=self.device)
+
+    def row_words(self) -> int:
+        return self.layout.row_words
+
+    def side(self) -> A.QuantSide:
+        return A.QuantSide(self.format.mode, self.format.bits, self.tab.data_ptr(),
+                           A.ROT_HADAMARD if self.rotation == "hadamard" else A.ROT_NONE,
+                           self.signs.data_ptr() if self.signs is not None else None)
+
+    def rotate(self, x: torch.Tensor) -> torch.Tensor:
+        """`x Pi^T` in f32 (turbo_quant.rs:182-188)."""
+        x = x.to(torch.float32).contiguous()
+        if self.rotation == "none":
+            return x
+        out = torch.empty_like(x)
+        A.check(A.lib().b200_tq_rotate(x.data_ptr(), out.data_ptr(), self.signs.data_ptr(), x.numel() // self.dim,
+                                       self.dim, 0, _stream(x.device)))
+        return out
+
+    def unrotate(self, y: torch.Tensor) -> torch.Tensor:
+        """`y Pi` (turbo_quant.rs:191-196)."""
+        if self.rotation == "none":
+            return y
+        y = y.to(torch.float32).contiguous()
+        out = torch.empty_like(y)
+        A.check(A.lib().b200_tq_rotate(y.data_ptr(), out.data_ptr(), self.signs.data_ptr(), y.numel() // self.dim,
+                                       self.dim, 1, _stream(y.device)))
+        return out
+
+    def quantize_rotated_rows(self, y: torch.Tensor) -> torch.Tensor:
+        """Rows that are already in the rotated domain -> packed rows (the reference's TqQuant op)."""
+        _need_cuda(y, "rows")
+        rows, d = y.shape
+        if d != self.dim:
+            raise ValueError(f"turbo-quant: expected rows of {self.dim} values, got {d}")
+        if y.stride(1) != 1:
+            y = y.contiguous()
+        out = torch.empty((rows, self.layout.row_words), dtype=torch.int32, device=y.device)
+        args = A.TqQuantArgs(y.data_ptr(), out.data_ptr(), self.tab.data_ptr(), rows, d, y.stride(0), 0,
+                             _dtype_id(y), self.format.mode, self.format.bits)
+        A.check(A.lib().b200_tq_quantize(C.byref(args), _stream(y.device)))
+        return out
+
+    def quantize_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """Packs `x: (rows, dim)` into `(rows, row_words)` rows, rotation included
+        (turbo_quant.rs:199-212); one launch."""
+        _need_cuda(x, "rows")
+        rows, d = x.shape
+        if d != self.dim:
+            raise ValueError(f"turbo-quant: expected rows of {self.dim} values, got {d}")
+        if self.rotation == "none":
+            return self.quantize_rotated_rows(x)
+        out = torch.empty((1, 1, rows, self.layout.row_words), dtype=torch.int32, device=x.device)
+        _kv_append(x.view(1, 1, rows, d), x.view(1, 1, rows, d), out, out.clone(), self, self, 0)
+        return out.view(rows, self.layout.row_words)
+
+    def dequantize_rows(self, data: torch.Tensor) -> torch.Tensor:
+        """`(rows, row_words)` -> `(rows, dim)` f32 in the original domain (turbo_quant.rs:250-270)."""
+        _need_cuda(data, "rows")
+        rows, rw = data.shape
+        if rw != self.layout.row_words:
+            raise ValueError(f"turbo-quant: expected rows of {self.layout.row_words} words, got {rw}")
+        data = data.contiguous()
+        out = torch.empty((rows, self.dim), dtype=torch.float32, device=data.device)
+        args = A.TqDequantArgs(data.data_ptr(), out.data_ptr(), self.tab.data_ptr(), rows, self.dim, 0,
+                               self.format.mode, self.format.bits)
+        A.check(A.lib().b200_tq_dequantize(C.byref(args), _stream(data.device)))
+        return self.unrotate(out)
+
+    def quantize(self, x: torch.Tensor) -> QuantizedTensor:
+        d = x.shape[-1]
+        if d != self.dim:
+            raise ValueError(f"turbo-quant: expected a last dim of {self.dim}, got {d}")
+        return QuantizedTensor(self.quantize_rows(x.reshape(-1, d)), x.shape, x.dtype)
+
+    def dequantize(self, q: QuantizedTensor) -> torch.Tensor:
+        return self.dequantize_rows(q.data).reshape(q.shape).to(q.dtype)
+
+
+def _kv_append(k, v, k_cache, v_cache, kq: TurboQuantizer, vq: TurboQuantizer, pos):
+    """b200_kv_append over (b, hkv, t, d) tensors and (b, hkv, cap, words) caches. `pos`: int or an
+    int32 device tensor with one position per batch entry."""
+    b, h, t, d = k.shape
+    if k.stride(3) != 1:
+        k = k.contiguous()
+    if v.stride(3) != 1:
+        v = v.contiguous()
+    pos_t = pos if isinstance(pos, torch.Tensor) else None
+    args = A.KvAppendArgs(
+        k.data_ptr(), v.data_ptr(), A.u64x3(*k.stride()[:3]), A.u64x3(*v.stride()[:3]),
+        k_cache.data_ptr(), v_cache.data_ptr(), A.u64x3(*k_cache.stride()[:3]), A.u64x3(*v_cache.stride()[:3]),
+        pos_t.data_ptr() if pos_t is not None else None, 0 if pos_t is not None else int(pos),
+        b, h, t, d, _dtype_id(k), kq.side(), vq.side())
+    A.check(A.lib().b200_kv_append(C.byref(args), _stream(k.device)))
+
+
+_WORKSPACES = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    """One growing scratch buffer per (device, stream): calls on one stream are ordered, so they
+    can share it; the reference allocates the split buffers per call (accel.rs:190-199)."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def attention_packed(q: torch.Tensor, k_rows: torch.Tensor, v_rows: torch.Tensor, kv_len, kq: TurboQuantizer,
+                     vq: TurboQuantizer, cfg: FlashAttnConfig, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of `q: (batch, q_heads, seq_q, head_dim)` over packed rows `k_rows: (batch,
+    kv_heads, capacity, k_words)`, `v_rows: (..., v_words)` (turbo_quant.rs:993-1072). `kv_len`: the
+    number of valid rows, an int (all sequences) or an int32 device tensor with one length per
+    batch entry (ragged batch). Output in `q`'s dtype and layout."""
+    _need_cuda(q, "q")
+    b, hq, lq, d = q.shape
+    bk, hkv, cap, kw = k_rows.shape
+    bv, hv, capv, vw = v_rows.shape
+    ragged = isinstance(kv_len, torch.Tensor)
+    lk = cap if ragged else int(kv_len)
+    if bk != b or bv != b or hv != hkv or capv < lk or cap < lk or (not ragged and lk == 0):
+        raise ValueError(f"turbo-quant attention: q {tuple(q.shape)} / k {tuple(k_rows.shape)} / v {tuple(v_rows.shape)}"
+                         f" / kv_len {kv_len} do not match")
+    if kw < kq.row_words() or vw < vq.row_words() or d != kq.dim or d != vq.dim:
+        raise ValueError(f"turbo-quant attention: rows of {kw} / {vw} words and head dim {d} do not match the "
+                         f"quantizers ({kq.row_words()} / {vq.row_words()} words, dim {kq.dim})")
+    if q.stride(3) != 1:
+        q = q.contiguous()
+    if k_rows.stride(3) != 1 or v_rows.stride(3) != 1:
+        raise ValueError("turbo-quant attention: packed rows must be contiguous along the words")
+    if out is None:
+        out = torch.empty((b, hq, lq, d), dtype=q.dtype, device=q.device)
+    wl, wr = cfg.window_i32()
+    alibi, abs_ = None, 0
+    if cfg.alibi_slopes is not None:
+        alibi = cfg.alibi_slopes.to(device=q.device, dtype=torch.float32).contiguous()
+        if alibi.shape == (hq,):
+            abs_ = 0
+        elif alibi.shape == (b, hq):
+            abs_ = hq
+        else:
+            raise ValueError(f"flash-attn: alibi slopes must be ({hq}) or ({b}, {hq}), got {tuple(alibi.shape)}")
+    args = A.TqAttnArgs()
+    args.q, args.out = q.data_ptr(), out.data_ptr()
+    args.q_dtype, args.out_dtype = _dtype_id(q), _dtype_id(out)
+    args.q_strides, args.out_strides = A.u64x3(*q.stride()[:3]), A.u64x3(*out.stride()[:3])
+    args.k_rows, args.v_rows = k_rows.data_ptr(), v_rows.data_ptr()
+    args.k_strides, args.v_strides = A.u64x3(*k_rows.stride()[:3]), A.u64x3(*v_rows.stride()[:3])
+    args.pages, args.n_pages = None, 0
+    args.kv_len_dev = kv_len.data_ptr() if ragged else None
+    args.b, args.lq, args.lk, args.hq, args.hkv, args.d = b, lq, lk, hq, hkv, d
+    args.kq, args.vq = kq.side(), vq.side()
+    args.scale, args.softcap = cfg.softmax_scale, cfg.softcap or 0.0
+    args.wl, args.wr = wl, wr
+    args.alibi, args.alibi_bstride = (alibi.data_ptr() if alibi is not None else None), abs_
+    args.splits = cfg.splits
+    nbytes = A.lib().b200_tq_attention_workspace_bytes(C.byref(args))
+    ws = _workspace(q.device, nbytes)
+    args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+    args.status = None
+    A.check(A.lib().b200_tq_attention(C.byref(args), _stream(q.device)))
+    return out
+
+
+class TurboKvCache:
+    """A KV cache that stores keys and values compressed and attends over them without
+    decompressing them (turbo_quant.rs:786-991). Layouts: `append(k, v)` with `(batch, kv_heads,
+    seq, head_dim)`, `attention(q)` with `(batch, q_heads, seq_q, head_dim)`.
+
+    The capacity buffers grow like the reference's `Cache` (candle-nn/src/kv_cache.rs:60-96):
+    allocated at the first append, grown by max(grow_by, capacity / 2) when full."""
+
+    def __init__(self, key: QuantFormat, value: QuantFormat, dim: int, rotation: str = "auto", seed: int = 42,
+                 grow_by: int = 1, device="cuda"):
+        if value.mode == A.TURBO_PROD:
+            raise ValueError("turbo-quant: values use the MSE codebooks, not the prod (QJL) format")
+        self.kq = TurboQuantizer(key, dim, rotation, seed, device)
+        self.vq = TurboQuantizer(value, dim, rotation, (seed + 2) & (2**64 - 1), device)
+        self.dim, self.grow_by = dim, max(int(grow_by), 1)
+        self.k: Optional[torch.Tensor] = None
+        self.v: Optional[torch.Tensor] = None
+        self.cap = self.grow_by
+        self.len = 0
+        self.dtype: Optional[torch.dtype] = None
+
+    @classmethod
+    def with_formats(cls, key, value, dim, rotation, seed, grow_by, device="cuda"):
+        return cls(key, value, dim, rotation, seed, grow_by, device)
+
+    def formats(self):
+        return self.kq.format, self.vq.format
+
+    def seq_len(self) -> int:
+        return self.len
+
+    def reset(self):
+        self.k = self.v = None
+        self.len = 0
+        self.cap = self.grow_by
+
+    def storage_bytes(self) -> int:
+        return sum(t.numel() * 4 for t in (self.k, self.v) if t is not None)
+
+    def _grown(self, need: int) -> int:
+        cap = self.cap
+        while cap < need:
+            cap += max(self.grow_by, cap // 2, 1)
+        return cap
+
+    def append(self, k: torch.Tensor, v: torch.Tensor):
+        _need_cuda(k, "k")
+        b, h, t, d = k.shape
+        if d != self.dim or tuple(v.shape) != (b, h, t, d):
+            raise ValueError(f"turbo-quant cache: k {tuple(k.shape)} / v {tuple(v.shape)} do not match head dim {self.dim}")
+        if self.dtype is None:
+            self.dtype = k.dtype
+        if self.k is None:
+            self.cap = self._grown(t)
+            self.k = torch.zeros((b, h, self.cap, self.kq.row_words()), dtype=torch.int32, device=k.device)
+            self.v = torch.zeros((b, h, self.cap, self.vq.row_words()), dtype=torch.int32, device=k.device)
+        need = self.len + t
+        cap = self._grown(need)
+        if cap > self.cap:
+            nk = torch.zeros((b, h, cap, self.kq.row_words()), dtype=torch.int32, device=k.device)
+            nv = torch.zeros((b, h, cap, self.vq.row_words()), dtype=torch.int32, device=k.device)
+            nk[:, :, : self.cap] = self.k
+            nv[:, :, : self.cap] = self.v
+            self.k, self.v, self.cap = nk, nv, cap
+        _kv_append(k, v, self.k, self.v, self.kq, self.vq, self.len)
+        self.len += t
+
+    def keys_values(self):
+        """Keys and values `(batch, kv_heads, seq, head_dim)`, dequantized (turbo_quant.rs:947-966)."""
+        if self.k is None:
+            return None
+        b, h, _, _ = self.k.shape
+        dt = self.dtype or torch.float32
+        deq = lambda q, x: q.dequantize_rows(x[:, :, : self.len].reshape(b * h * self.len, -1)).reshape(
+            b, h, self.len, self.dim).to(dt)
+        return deq(self.kq, self.k), deq(self.vq, self.v)
+
+    def attention(self, q: torch.Tensor, cfg: FlashAttnConfig) -> torch.Tensor:
+        if self.k is None:
+            raise RuntimeError("turbo-quant cache: attention on an empty cache")
+        return attention_packed(q, self.k, self.v, self.len, self.kq, self.vq, cfg)

@@ -1,0 +1,262 @@
+/*
+ * b200attn: fused attention over a compressed KV cache for NVIDIA B200 (sm_100a).
+ *
+ * C ABI of libb200attn.so. Every entry point takes plain pointers and sizes, a CUDA stream
+ * (0 = the legacy default stream, which is what candle's shared device uses:
+ * candle-core/src/cuda_backend/device.rs:191-197), returns 0 or a negative B200_ERR_* code and
+ * never aborts. The calls are re-entrant and keep no per-call global state; device pointers are
+ * borrowed for the duration of the stream-ordered call and must already include any start offset
+ * (the reference passes storage + element offset, candle-core/src/cuda_backend/accel.rs:103-130).
+ * Outputs are written completely: the caller may hand in uninitialised memory
+ * (accel.rs:132-144).
+ *
+ * Each declaration cites the interface of the reference (Qntology/candle-rocm-vulkan) that it
+ * replaces. Format ids, the packed row layout and all scalar arguments have the reference's
+ * meaning, so the reference's Rust host code can bind these symbols one to one.
+ */
+#ifndef B200ATTN_H
+#define B200ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* CUDA stream handle (cudaStream_t / CUstream) without including the CUDA headers. */
+typedef void *b200_stream_t;
+
+/* ---- status codes ------------------------------------------------------------------------ */
+#define B200_OK 0
+#define B200_ERR_BAD_ARG (-1)            /* null pointer, zero dim, inconsistent sizes */
+#define B200_ERR_UNSUPPORTED_SHAPE (-2)  /* shape / format outside the kernels (caller may fall back) */
+#define B200_ERR_LAUNCH (-3)             /* CUDA reported an error; see b200_last_error() */
+#define B200_ERR_WORKSPACE (-4)          /* workspace missing or smaller than *_workspace_bytes() */
+#define B200_ERR_DEVICE_WAIT (-5)        /* a bounded device-side wait ran out (status word set) */
+
+/* ---- element dtypes ---------------------------------------------------------------------- */
+#define B200_F32 0
+#define B200_F16 1
+#define B200_BF16 2
+#define B200_FP8 3 /* OCP E4M3FN */
+
+/* ---- quantization formats: ids of candle-core/src/accel/formats.rs:41-48 ------------------- */
+#define B200_TURBO_MSE 0
+#define B200_TURBO_PROD 1
+#define B200_MXFP4 2
+#define B200_NVFP4 3
+#define B200_MXFP8 4
+#define B200_FP8_ROW 5
+
+/* ---- rotations: candle-core/src/accel/config.rs RotationKind -------------------------------- */
+#define B200_ROT_NONE 0
+#define B200_ROT_HADAMARD 1
+
+/* Word layout of one packed row: [codes][aux][rsc0 f32][rsc1 f32], little-endian u32 words.
+ * Replaces RowLayout / row_layout (candle-core/src/accel/formats.rs:206-242). */
+typedef struct B200RowLayout {
+    int32_t dim;
+    int32_t code_bits;
+    int32_t code_words;
+    int32_t aux_words;
+    int32_t row_words;
+    int32_t rsc_offset;
+} B200RowLayout;
+
+/* `bits`: width of the TurboQuant formats (mse 1-4, prod 2-5), ignored by the float formats.
+ * Errors like QuantFormat::validate (formats.rs:166-187): dim in 1..=1024, dim % block == 0. */
+int b200_row_layout(int mode, int bits, int dim, B200RowLayout *out);
+
+/* Lloyd-Max table [16 centroids | 16 boundaries padded with +inf] of `bits` bits for unit
+ * vectors of length dim. Host memory. Replaces accel::turbo::codebook + Codebook::table
+ * (candle-core/src/accel/turbo.rs:46-55,58-146). */
+int b200_codebook(int dim, int bits, float tab[32]);
+
+/* Column signs (+1 / -1) of the randomized Hadamard rotation of `seed`, host memory, dim floats.
+ * Replaces the sign draw of accel::turbo::rotation_matrix (turbo.rs:188-195). Keys use the
+ * cache seed, values seed + 2 (candle-nn/src/turbo_quant.rs:148-153,868). */
+int b200_hadamard_signs(int dim, uint64_t seed, float *signs);
+
+/* Query heads that share one kv head per work group (8, 4, 2 or 1) and the reference's key split
+ * count for a device of `compute_units` SMs. Replace accel::attention::row_group and
+ * split_count_grouped with SplitKv::Auto (candle-core/src/accel/attention.rs:486-506,586-592). */
+int b200_row_group(int hq, int hkv);
+int b200_split_count_grouped(int64_t rows, int group, int64_t lk, int compute_units);
+
+/* ---- device report ------------------------------------------------------------------------- */
+typedef struct B200Profile {
+    int32_t cc_major, cc_minor;
+    int32_t sm_count;
+    int32_t max_smem_optin; /* bytes of dynamic shared memory a block may opt into */
+    int64_t total_mem;
+    char name[64];
+} B200Profile;
+
+/* Replaces CudaDevice::accel_profile (candle-core/src/cuda_backend/accel.rs:40-60). */
+int b200_describe(int device, B200Profile *out);
+
+/* Message of the last failing call of this thread ("" if none). Replaces the `candle::Error`
+ * strings of the launchers. */
+const char *b200_last_error(void);
+
+/* ---- one side (keys or values) of a compressed cache ------------------------------------------ */
+typedef struct B200QuantSide {
+    int32_t mode;       /* B200_TURBO_MSE ... B200_FP8_ROW */
+    int32_t bits;       /* TurboQuant width, else ignored */
+    const float *tab;   /* device, 32 floats (b200_codebook layout); may be NULL for float formats */
+    int32_t rotation;   /* B200_ROT_NONE / B200_ROT_HADAMARD */
+    const float *signs; /* device, dim floats (+1 / -1) when rotation is Hadamard */
+} B200QuantSide;
+
+/* ---- row quantizer --------------------------------------------------------------------------- */
+/* Replaces CudaStorage::tq_quantize (candle-core/src/cuda_backend/accel.rs:509-552) and the
+ * kernels tq_quant_{f32,f16,bf16} (candle-core/kernels/turbo_quant_impl.h:71-159,687-694): rows of
+ * `dim` values -> packed rows. Codes, block scales and rsc0 are bit-exact with those kernels.
+ * The rows must already be in the rotated domain (the reference rotates with a matmul before
+ * this call, candle-nn/src/turbo_quant.rs:199-212). */
+typedef struct B200TqQuantArgs {
+    const void *src;     /* device, (rows, dim) of src_dtype, row stride src_stride elements */
+    uint32_t *out;       /* device, (rows, out_stride) u32 */
+    const float *tab;    /* device, 32 floats; NULL allowed for the float formats */
+    uint64_t rows;
+    uint32_t dim;
+    uint64_t src_stride; /* elements */
+    uint64_t out_stride; /* words between output rows; 0 = row_words */
+    int32_t src_dtype;   /* B200_F32 / B200_F16 / B200_BF16 */
+    int32_t mode, bits;
+} B200TqQuantArgs;
+int b200_tq_quantize(const B200TqQuantArgs *args, b200_stream_t stream);
+
+/* Replaces CudaStorage::tq_dequantize without the QJL part (accel.rs:639-684) and the kernel
+ * tq_dequant (turbo_quant_impl.h:208-224): out[r][j] = rsc0 * element j, f32, rotated domain. */
+typedef struct B200TqDequantArgs {
+    const uint32_t *data; /* device, (rows, data_stride) */
+    float *out;           /* device, (rows, dim) contiguous */
+    const float *tab;     /* device, 32 floats (TurboQuant formats) */
+    uint64_t rows;
+    uint32_t dim;
+    uint64_t data_stride; /* words; 0 = row_words */
+    int32_t mode, bits;
+} B200TqDequantArgs;
+int b200_tq_dequantize(const B200TqDequantArgs *args, b200_stream_t stream);
+
+/* Rows into (inverse = 0: y = x Pi^T) or out of (inverse = 1: x = y Pi) the rotated domain of the
+ * randomized Hadamard rotation Pi = H diag(signs) / sqrt(dim), f32, in place allowed. Replaces the
+ * matmuls of TurboQuantizer::rotate / unrotate (candle-nn/src/turbo_quant.rs:182-196) for the
+ * Hadamard kind; the sums run as butterflies, so values agree with the matmul to rounding. */
+int b200_tq_rotate(const float *in, float *out, const float *signs, uint64_t rows, uint32_t dim, int inverse,
+                   b200_stream_t stream);
+
+/* ---- fused quantize-on-append ------------------------------------------------------------------ */
+/* Replaces TurboKvCache::append (candle-nn/src/turbo_quant.rs:916-945), i.e. per tensor the chain
+ * to_dtype(F32) -> matmul with the rotation -> tq_quant -> Cache::append / slice_set
+ * (candle-nn/src/kv_cache.rs:68-96), by one launch that reads K and V (b, hkv, t, d), rotates in
+ * registers (Hadamard) and writes the packed rows at positions [pos, pos + t) of the capacity
+ * buffers (b, hkv, cap, row_words). Without rotation the rows are bit-exact with tq_quant. */
+typedef struct B200KvAppendArgs {
+    const void *k, *v;        /* device, element strides below, last dim contiguous */
+    uint64_t k_strides[3];    /* (batch, head, token) in elements */
+    uint64_t v_strides[3];
+    uint32_t *k_cache, *v_cache;
+    uint64_t k_cache_strides[3]; /* (batch, head, row) in words */
+    uint64_t v_cache_strides[3];
+    const int32_t *pos;       /* device, one write position per batch entry, or NULL: pos0 for all */
+    int32_t pos0;
+    uint32_t b, hkv, t, d;
+    int32_t src_dtype;
+    B200QuantSide kq, vq;
+} B200KvAppendArgs;
+int b200_kv_append(const B200KvAppendArgs *args, b200_stream_t stream);
+
+/* ---- paged rows --------------------------------------------------------------------------------- */
+/* One block of a paged cache, device memory. Block i holds `rows` valid keys; k / v point at its
+ * (batch 0, kv head 0, row 0); head stride = k_cap (v_cap) rows, batch stride = hkv head strides.
+ * Same meaning as ax_pages / PageTable (candle-core/kernels/accel_common.h:109-123,
+ * candle-core/src/accel/attention.rs:296-366), but the table is an array in device memory
+ * instead of a 3 592-byte kernel argument, so it is not limited to 128 blocks. */
+typedef struct B200Page {
+    const void *k, *v;
+    uint32_t rows, k_cap, v_cap, pad;
+} B200Page;
+
+/* ---- attention over packed rows ------------------------------------------------------------------ */
+/* Replaces CudaStorage::tq_attention / tq_attention_paged (accel.rs:687-857), the kernels
+ * tq_attn* / tq_combine (turbo_quant_impl.h:232-747) and the host chain around them in
+ * fused_attention_rows / tq_prepare (candle-nn/src/turbo_quant.rs:1143-1264): query cast, query
+ * rotation, attention, split combine, output rotation back and cast, in one or two launches.
+ *
+ * q (b, hq, lq, d) -> out (b, hq, lq, d), both with (batch, head, token) element strides.
+ * Keys are the rows [0, kv_len) of k_rows / v_rows (b, hkv, cap, words); masks are aligned to the
+ * bottom right (query i sits at key position i + kv_len - lq; key j visible when
+ * pos - wl <= j <= pos + wr, negative = unbounded, wr = 0 causal). score = scale * rsc0_k *
+ * sum_d elem_k * q_d, then softcap (> 0) and ALiBi; value weight p * rsc0_v. Rows without a
+ * visible key give zeros. With kq.rotation / vq.rotation = Hadamard the query is rotated with the
+ * key signs and the output rotated back with the value signs; with B200_ROT_NONE, q_dtype =
+ * out_dtype = B200_F32 the call is exactly the reference's tq_attention.
+ *
+ * Extension for ragged batches (the reference has one seq_len per cache, turbo_quant.rs:895-897):
+ * kv_len_dev, one length per batch entry in device memory; lk is then the maximum length. */
+typedef struct B200TqAttnArgs {
+    const void *q;
+    void *out;
+    int32_t q_dtype, out_dtype;
+    uint64_t q_strides[3], out_strides[3]; /* (batch, head, token) in elements */
+    const uint32_t *k_rows, *v_rows;       /* dense rows, or NULL when pages is set */
+    uint64_t k_strides[3], v_strides[3];   /* (batch, head, row) in words */
+    const B200Page *pages;                 /* device array of n_pages blocks, or NULL */
+    uint32_t n_pages;
+    const int32_t *kv_len_dev;             /* device, b entries, or NULL */
+    uint32_t b, lq, lk, hq, hkv, d;
+    B200QuantSide kq, vq;
+    float scale, softcap;
+    int32_t wl, wr;
+    const float *alibi;                    /* device f32 slopes or NULL */
+    uint32_t alibi_bstride;                /* 0 or hq */
+    int32_t splits;                        /* key splits per sequence; 0 = chosen by the library */
+    void *workspace;                       /* device, b200_tq_attention_workspace_bytes() */
+    size_t workspace_bytes;
+    int32_t *status;                       /* optional device word, set non-zero if a device wait ran out */
+} B200TqAttnArgs;
+size_t b200_tq_attention_workspace_bytes(const B200TqAttnArgs *args);
+int b200_tq_attention(const B200TqAttnArgs *args, b200_stream_t stream);
+
+/* ---- attention over dense K / V ------------------------------------------------------------------- */
+/* Replaces CudaStorage::flash_attn / flash_attn_paged (accel.rs:254-506), the kernels fa_row*,
+ * fa2_*, fa3_*, fa_combine_* (candle-core/kernels/flash_attn_impl.h) and therefore the device
+ * side of candle_flash_attn::flash_attn / flash_attn_varlen (candle-flash-attn/src/lib.rs:149-345).
+ * Arguments are the kernel parameter list FA_PARAMS (flash_attn_impl.h:29-35): q (b, lq, hq, d),
+ * k / v (b, lk, hkv, d) with (batch, seq, head) element strides; varlen: q (total_q, hq, d) with
+ * cu_q / cu_k u32 offsets (b + 1 entries), lq / lk the maxima. o: (token, head, d) contiguous. */
+typedef struct B200FaArgs {
+    const void *q, *k, *v;
+    void *o;
+    int32_t q_dtype;  /* B200_F16 / B200_BF16 / B200_F32; o has the same dtype */
+    int32_t kv_dtype; /* q_dtype or B200_FP8 */
+    const uint32_t *cu_q, *cu_k; /* device, varlen only */
+    uint32_t b, lq, lk, hq, hkv, d;
+    uint64_t q_strides[3], k_strides[3], v_strides[3]; /* (batch, seq, head) in elements */
+    float scale, softcap;
+    int32_t wl, wr;
+    float k_descale, v_descale;
+    const float *alibi;
+    uint32_t alibi_bstride;
+    uint32_t varlen;
+    uint64_t total_q; /* output tokens: b * lq, or the varlen total */
+    void *workspace;
+    size_t workspace_bytes;
+} B200FaArgs;
+size_t b200_flash_attn_workspace_bytes(const B200FaArgs *args);
+int b200_flash_attn(const B200FaArgs *args, b200_stream_t stream);
+
+/* Causal / windowed prefill with the new keys and values written into the compressed cache in
+ * the same call. Replaces the pair flash_attn(q, k, v, scale, causal) + TurboKvCache::append(k, v)
+ * (candle-flash-attn/src/lib.rs:149-157, candle-nn/src/turbo_quant.rs:916-945). `fa` describes the
+ * attention over the uncompressed k / v (b, lk, hkv, d); `append` the cache write, whose k / v
+ * pointers and strides must describe the same tensors viewed as (b, hkv, t, d). */
+int b200_fa_prefill_append(const B200FaArgs *fa, const B200KvAppendArgs *append, b200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200ATTN_H */

