@@ -63,7 +63,7 @@ class ClockSampler:
         q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "50",
                                           "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -251,6 +251,15 @@ def run_ours(args, w, rank, world, local_rank):
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
+    # the timed regions last milliseconds: keep the same step running (untimed) until the clock sampler has seen
+    # at least half a second of this load
+    t_end = time.perf_counter() + 0.6
+    i = 0
+    while time.perf_counter() < t_end:
+        for _ in range(50):
+            step(i)
+            i += 1
+        torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
 
     # max over ranks

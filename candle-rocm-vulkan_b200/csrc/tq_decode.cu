@@ -125,8 +125,11 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
 
     p.k_stage_bytes = (uint32_t)((WK * p.k_ss * 4 + 16 + 15) / 16 * 16);
     p.v_stage_bytes = (uint32_t)((WK * p.v_ss * 4 + 16 + 15) / 16 * 16);
-    pl.smem = 128 + 2048 + (size_t)DW * PACK * a->d * 4 + 2 * DW * PACK * 4 +
-              (size_t)DW * NS * (p.k_stage_bytes + p.v_stage_bytes);
+    const size_t fixed = 128 + 2048 + (size_t)DW * PACK * a->d * 4 + 2 * DW * PACK * 4;
+    p.ns = NS_MAX;
+    // three blocks per SM when the stages allow it, else fewer stages, down to two
+    while (p.ns > 2 && fixed + (size_t)DW * p.ns * (p.k_stage_bytes + p.v_stage_bytes) > 72 * 1024) --p.ns;
+    pl.smem = fixed + (size_t)DW * p.ns * (p.k_stage_bytes + p.v_stage_bytes);
     if (pl.smem > 227 * 1024) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: %zu bytes of shared memory", pl.smem);
 
     const size_t slots = (size_t)a->b * pl.ny * p.max_splits * PACK;

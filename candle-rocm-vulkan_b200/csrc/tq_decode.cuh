@@ -31,7 +31,7 @@ namespace b200 {
 
 constexpr int DW = 4;         // warps per block
 constexpr int WK = 32;        // keys per warp tile
-constexpr int NS = 3;         // stages per warp
+constexpr int NS_MAX = 3;     // stages per warp (fewer when the rows are large)
 constexpr int PACK = 8;       // query rows per block
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
@@ -64,6 +64,7 @@ struct DecodeParams {
     int32_t *meta;     // [b][ny] live splits
     int32_t *status;
     uint32_t k_stage_bytes, v_stage_bytes;
+    uint32_t ns;       // stages per warp
 };
 
 __host__ __device__ constexpr bool fmt_is4(int m) { return m == B200_MXFP4 || m == B200_NVFP4 || m == B200_TURBO_MSE; }
@@ -298,7 +299,8 @@ template <int KM, int VM, int HD, bool QSPLIT>
 __global__ void __launch_bounds__(DW * 32) tq_decode_kernel(const DecodeParams p) {
     constexpr int STEPS = HD / 16;  // k-steps of q k^T == m-tiles of the output
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);                       // [DW][NS]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);                       // [DW][NS_MAX]
+    const int NS = (int)p.ns;
     uint32_t *lut_k = reinterpret_cast<uint32_t *>(smem + 128);                // 256
     uint32_t *lut_v = lut_k + 256;                                             // 256
     float *mbuf = reinterpret_cast<float *>(smem + 128 + 2048);                // [DW][PACK][HD]
@@ -351,7 +353,7 @@ __global__ void __launch_bounds__(DW * 32) tq_decode_kernel(const DecodeParams p
 
     // ------------------------------------------------------------------ prologue
     if (tid == 0) {
-        for (int i = 0; i < DW * NS; ++i) mbar_init(&bars[i], 1);
+        for (int i = 0; i < DW * NS_MAX; ++i) mbar_init(&bars[i], 1);
         mbar_fence_init();
     }
     if (KM == B200_TURBO_MSE)
@@ -415,7 +417,7 @@ __global__ void __launch_bounds__(DW * 32) tq_decode_kernel(const DecodeParams p
     const int ntiles = (int)((c_hi - c_lo + WK - 1) / WK);
     const int my_tiles = ntiles > warp ? (ntiles - warp + DW - 1) / DW : 0;
     uint8_t *wstage = stages + (size_t)warp * NS * stage_bytes;
-    uint64_t *wbar = bars + warp * NS;
+    uint64_t *wbar = bars + warp * NS_MAX;
     bool wait_failed = false;
 
     // copies tile n of this warp into its stage n % NS
