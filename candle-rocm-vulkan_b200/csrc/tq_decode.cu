@@ -125,11 +125,18 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
 
     p.k_stage_bytes = (uint32_t)((WK * p.k_ss * 4 + 16 + 15) / 16 * 16);
     p.v_stage_bytes = (uint32_t)((WK * p.v_ss * 4 + 16 + 15) / 16 * 16);
-    const size_t fixed = 128 + 2048 + (size_t)DW * PACK * a->d * 4 + 2 * DW * PACK * 4;
+    // shared memory: barriers and pair tables, per-warp key metadata, then the stage rings, whose area
+    // also stages the queries before and merges the warps after the key loop
+    const size_t fixed = FIXED_SMEM + (size_t)DW * meta_bytes(a->kq.mode, a->vq.mode, (int)a->d);
+    const size_t merge = (size_t)DW * PACK * a->d * 4 + 2 * DW * PACK * 4;
+    const size_t stage = (size_t)p.k_stage_bytes + p.v_stage_bytes;
     p.ns = NS_MAX;
+    static const long env_ns = [] { const char *e = getenv("B200_DECODE_STAGES"); return e ? atol(e) : 0l; }();
+    if (env_ns >= 2 && env_ns <= NS_MAX) p.ns = (uint32_t)env_ns;
     // three blocks per SM when the stages allow it, else fewer stages, down to two
-    while (p.ns > 2 && fixed + (size_t)DW * p.ns * (p.k_stage_bytes + p.v_stage_bytes) > 72 * 1024) --p.ns;
-    pl.smem = fixed + (size_t)DW * p.ns * (p.k_stage_bytes + p.v_stage_bytes);
+    while (p.ns > 2 && fixed + DW * p.ns * stage > 72 * 1024) --p.ns;
+    p.stages_bytes = (uint32_t)std::max(DW * p.ns * stage, merge);
+    pl.smem = fixed + p.stages_bytes;
     if (pl.smem > 227 * 1024) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: %zu bytes of shared memory", pl.smem);
 
     const size_t slots = (size_t)a->b * pl.ny * p.max_splits * PACK;

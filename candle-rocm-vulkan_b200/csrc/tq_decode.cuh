@@ -3,21 +3,24 @@
 // Work split: block = (key chunk, pack of up to 8 query rows that share a kv head, batch entry).
 // Each of the 4 warps streams its own 32-key tiles of the chunk through a private ring of shared
 // memory stages filled by bulk copies (cp.async.bulk + mbarrier, no multicast), so no block-wide
-// barrier sits in the key loop. Per 16 keys a warp
+// barrier sits in the key loop. Per tile the warp first derives the per-key scalars once (lane =
+// key): f32 key scales, the value scale sigma = rsc0_v * 2^(largest block exponent) with its log2,
+// and the f16 block scales of V relative to that exponent. Then per 16 keys it
 //   1. dequantizes K in registers to f16 (packed cvt from e2m1 / e4m3, or a 256-entry pair table
-//      for the codebook format; block scales relative to the row's largest block exponent, the rest
-//      of the scale stays in f32) and multiplies with the f16 query fragments on mma.sync m16n8k16
-//      (A = query rows, B = keys): lane (g, c) owns key g of an 8-key group and the quarter
-//      [c D/4, (c + 1) D/4) of its row, a permutation of the contraction index shared with the
-//      query fragments, so every byte of a row is read once, as 32-bit words;
-//   2. runs the online softmax in f32 on the accumulator fragments (log2 domain). The per-key value
-//      scale sigma_j = rsc0_v * 2^(largest block exponent) is folded into the exponent:
-//      w_j = exp2(s_j + log2 sigma_j - M) <= 1 is the f16 operand of the second product, while the
-//      normalizer sums exp2(s_j - M) in f32, so value scales of any magnitude stay exact;
-//   3. dequantizes V (lane (g, c) owns keys {2c, 2c+1, 2c+8, 2c+9} x dims [g D/8, (g+1) D/8), bytes
-//      or nibbles of two keys interleaved before the packed cvt so that the f16 pairs run along
-//      the contraction index) and accumulates O^T = V^T P^T (A = V^T, B = P^T straight from the
-//      score fragments).
+//      for the codebook format) as the A operand of mma.sync m16n8k16 (rows = keys g and g + 8 of
+//      lane (g, c)), with the f16 query fragments as B (columns = query rows). The contraction
+//      index is permuted, identically for K and Q, so that a lane reads whole 32-bit words of its
+//      rows. MX formats accumulate each 32-element block separately and apply the E8M0 block
+//      scale times rsc0 in f32; the other formats apply rsc0 in f32 after the product;
+//   2. runs the online softmax in f32 on the accumulator fragments (log2 domain). The value scale
+//      is folded into the running maximum (M tracks s_j + log2 sigma_j), so the f16 weights
+//      w_j = exp2(s_j - M) * sigma_j stay in range for value scales of any magnitude while the
+//      normalizer sums exp2(s_j - M) in f32. M only moves when a score exceeds it by 2^8 (warp
+//      vote), which keeps the cross-lane maximum out of the common path;
+//   3. transposes the weights with movmatrix into the B operand of the second product and
+//      dequantizes V as A = V^T (lane (g, c) owns keys {2c, 2c+1, 2c+8, 2c+9} x dims
+//      [g D/8, (g+1) D/8); bytes or nibbles of two keys are interleaved before the packed cvt so
+//      that the f16 pairs run along the contraction index): O^T += V^T P^T.
 // The warps' states are merged through shared memory; the block writes either the final rows
 // (one chunk) or a normalized partial and its log-sum-exp for the combine kernel.
 //
@@ -32,6 +35,7 @@ namespace b200 {
 constexpr int DW = 4;         // warps per block
 constexpr int WK = 32;        // keys per warp tile
 constexpr int NS_MAX = 3;     // stages per warp (fewer when the rows are large)
+constexpr float MAX_SLACK = 8.0f;  // log2 of how far a score may exceed the running maximum before it moves
 constexpr int PACK = 8;       // query rows per block
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
@@ -65,194 +69,63 @@ struct DecodeParams {
     int32_t *status;
     uint32_t k_stage_bytes, v_stage_bytes;
     uint32_t ns;       // stages per warp
+    uint32_t stages_bytes;  // whole stage area (also holds the query staging and the merge buffers)
 };
 
 __host__ __device__ constexpr bool fmt_is4(int m) { return m == B200_MXFP4 || m == B200_NVFP4 || m == B200_TURBO_MSE; }
+__host__ __device__ constexpr bool fmt_is_mx(int m) { return m == B200_MXFP4 || m == B200_MXFP8; }
+// f32 words of key metadata per key: one scale per 32-block (MX) or the row scale
+__host__ __device__ constexpr int kmeta_words(int km, int hd) { return fmt_is_mx(km) ? (hd / 32 < 2 ? 2 : hd / 32) : 1; }
+// f16 block scales of V per key
+__host__ __device__ constexpr int vsc_blocks(int vm, int hd) { return fmt_is_mx(vm) ? hd / 32 : (vm == B200_NVFP4 ? hd / 16 : 0); }
+__host__ __device__ constexpr int meta_bytes(int km, int vm, int hd) {
+    return WK * (kmeta_words(km, hd) * 4 + 8 + vsc_blocks(vm, hd) * 2);
+}
+constexpr int FIXED_SMEM = 128 + 2048;  // barriers, pair tables
+
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float2 lds64f(uint32_t a) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float4 lds128f(uint32_t a) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void sts32(uint32_t a, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
+__device__ __forceinline__ void sts16(uint32_t a, uint32_t v) {
+    asm volatile("{\n .reg .b16 t;\n cvt.u16.u32 t, %1;\n st.shared.u16 [%0], t;\n}" ::"r"(a), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
 
 // largest byte of a word
 __device__ __forceinline__ uint32_t max_byte(uint32_t w) {
     const uint32_t m = __vmaxu4(w, w >> 16);
     return max(m & 0xffu, (m >> 8) & 0xffu);
 }
-// f16x2 {2^da, 2^db} for da, db <= 0 (flushes to zero below 2^-14)
-__device__ __forceinline__ uint32_t pow2_f16x2(int da, int db) {
-    return ((uint32_t)max(da + 15, 0) << 10) | ((uint32_t)max(db + 15, 0) << 26);
-}
-__device__ __forceinline__ float pow2_e8m0(uint32_t e) { return u2f(max(e, 1u) << 23); }  // 2^(e-127), e >= 1
+// f16 bits of 2^d for d <= 0 (flushes to zero below 2^-14)
+__device__ __forceinline__ uint32_t pow2_f16(int d) { return (uint32_t)max(d + 15, 0) << 10; }
 
-// Largest E8M0 exponent byte over the blocks of a row (MX formats), aux words at row[cw...].
-template <int HD>
-__device__ __forceinline__ uint32_t mx_row_emax(const uint32_t *row, int cw) {
-    uint32_t w = row[cw];
-    if (HD > 128) w = __vmaxu4(w, row[cw + 1]);
-    return max_byte(w);
-}
-
-// ---------------------------------------------------------------------------------------------
-// K side: lane (g, c) holds elements [c HD/4, (c+1) HD/4) of key g: per k-step s the B fragment
-// (b0, b1) = elements 4s .. 4s+3 of that range. Returns kappa, the f32 factor of the row.
-// ---------------------------------------------------------------------------------------------
-template <int KM, int HD, bool QSPLIT>
-__device__ __forceinline__ float qk_group(const uint32_t *krow, int c, const DecodeSide &ks, const uint32_t *lut,
-                                          const uint32_t (&qh0)[HD / 16], const uint32_t (&qh2)[HD / 16],
-                                          const uint32_t (&ql0)[HD / 16], const uint32_t (&ql2)[HD / 16],
-                                          float (&acc)[4]) {
-    constexpr int STEPS = HD / 16;
-    float kappa = u2f(krow[ks.rsc_off]);
-    if (fmt_is4(KM)) {
-        constexpr int WORDS = HD / 32;  // words of this lane
-        uint32_t sc[WORDS];             // f16x2 scale per word (8 elements)
-        if (KM == B200_MXFP4) {
-            const uint32_t emax = mx_row_emax<HD>(krow, ks.code_words);
-            kappa *= pow2_e8m0(emax);
-            constexpr int NB = HD >= 128 ? HD / 128 : 1;  // 32-blocks in this lane's range
-            uint32_t sb[NB];
-#pragma unroll
-            for (int i = 0; i < NB; ++i) {
-                const int blk = HD >= 128 ? c * NB + i : c >> 1;
-                const int e = (int)((krow[ks.code_words + (blk >> 2)] >> ((blk & 3) * 8)) & 0xffu);
-                sb[i] = pow2_f16x2(e - (int)emax, e - (int)emax);
-            }
-#pragma unroll
-            for (int w = 0; w < WORDS; ++w) sc[w] = sb[(8 * w) / 32];
-        } else if (KM == B200_NVFP4) {
-            constexpr int NB = HD / 64;  // 16-blocks in this lane's range
-            uint32_t sb[NB];
-#pragma unroll
-            for (int i = 0; i < NB; ++i) {
-                const int blk = c * NB + i;
-                const uint32_t byte = (krow[ks.code_words + (blk >> 2)] >> ((blk & 3) * 8)) & 0xffu;
-                sb[i] = cvt_e4m3x2_f16x2(byte | (byte << 8));
-            }
-#pragma unroll
-            for (int w = 0; w < WORDS; ++w) sc[w] = sb[(8 * w) / 16];
-        }
-#pragma unroll
-        for (int w = 0; w < WORDS; ++w) {
-            const uint32_t x = krow[c * WORDS + w];
-            uint32_t h0, h1, h2, h3;
-            if (KM == B200_TURBO_MSE) {
-                h0 = lut[x & 0xffu];
-                h1 = lut[(x >> 8) & 0xffu];
-                h2 = lut[(x >> 16) & 0xffu];
-                h3 = lut[x >> 24];
-            } else {
-                cvt_e2m1x8_f16x2(x, h0, h1, h2, h3);
-                h0 = hmul2_u32(h0, sc[w]);
-                h1 = hmul2_u32(h1, sc[w]);
-                h2 = hmul2_u32(h2, sc[w]);
-                h3 = hmul2_u32(h3, sc[w]);
-            }
-            mma_f16_16816(acc, qh0[2 * w], 0u, qh2[2 * w], 0u, h0, h1);
-            mma_f16_16816(acc, qh0[2 * w + 1], 0u, qh2[2 * w + 1], 0u, h2, h3);
-            if (QSPLIT) {
-                mma_f16_16816(acc, ql0[2 * w], 0u, ql2[2 * w], 0u, h0, h1);
-                mma_f16_16816(acc, ql0[2 * w + 1], 0u, ql2[2 * w + 1], 0u, h2, h3);
-            }
-        }
+// f16x2 pair table lookups (codebook format) or packed cvt of the four bytes of x
+template <int M>
+__device__ __forceinline__ void dq4(uint32_t x, uint32_t lut, uint32_t &h0, uint32_t &h1, uint32_t &h2, uint32_t &h3) {
+    if constexpr (M == B200_TURBO_MSE) {
+        h0 = lds32(lut + ((x & 0xffu) << 2));
+        h1 = lds32(lut + ((x >> 6) & 0x3fcu));
+        h2 = lds32(lut + ((x >> 14) & 0x3fcu));
+        h3 = lds32(lut + ((x >> 22) & 0x3fcu));
     } else {
-        constexpr int NB = HD >= 128 ? HD / 128 : 1;  // 32-blocks in this lane's range
-        uint32_t sb[NB];
-        if (KM == B200_MXFP8) {
-            const uint32_t emax = mx_row_emax<HD>(krow, ks.code_words);
-            kappa *= pow2_e8m0(emax);
-#pragma unroll
-            for (int i = 0; i < NB; ++i) {
-                const int blk = HD >= 128 ? c * NB + i : c >> 1;
-                const int e = (int)((krow[ks.code_words + (blk >> 2)] >> ((blk & 3) * 8)) & 0xffu);
-                sb[i] = pow2_f16x2(e - (int)emax, e - (int)emax);
-            }
-        }
-#pragma unroll
-        for (int s = 0; s < STEPS; ++s) {
-            const uint32_t x = krow[c * STEPS + s];
-            uint32_t h0 = cvt_e4m3x2_f16x2(x), h1 = cvt_e4m3x2_hi_f16x2(x);
-            if (KM == B200_MXFP8) {
-                h0 = hmul2_u32(h0, sb[(4 * s) / 32]);
-                h1 = hmul2_u32(h1, sb[(4 * s) / 32]);
-            }
-            mma_f16_16816(acc, qh0[s], 0u, qh2[s], 0u, h0, h1);
-            if (QSPLIT) mma_f16_16816(acc, ql0[s], 0u, ql2[s], 0u, h0, h1);
-        }
-    }
-    return kappa;
-}
-
-// ---------------------------------------------------------------------------------------------
-// V side metadata of one key: log2 of the f32 factor sigma = rsc0 [* 2^emax] (clamped; -inf -> the
-// key adds nothing to the output) and the row's largest block exponent.
-// ---------------------------------------------------------------------------------------------
-template <int VM, int HD>
-__device__ __forceinline__ void v_meta(const uint32_t *vrow, const DecodeSide &vs, float &lsig, bool &live, uint32_t &emax) {
-    const float r0 = u2f(vrow[vs.rsc_off]);
-    emax = 0;
-    float l = fast_log2(r0);
-    if (VM == B200_MXFP4 || VM == B200_MXFP8) {
-        emax = mx_row_emax<HD>(vrow, vs.code_words);
-        l += (float)((int)max(emax, 1u) - 127);
-    }
-    live = r0 > 0.0f && r0 < INFINITY;
-    lsig = live ? fminf(fmaxf(l, -100.0f), 100.0f) : -100.0f;
-}
-
-// V fragments of one pair of keys (rows va, vb) for this lane's dims [g HD/8, (g+1) HD/8):
-// lo[mt] = {va[2 mt], vb[2 mt]}, hi[mt] = {va[2 mt + 1], vb[2 mt + 1]} as f16x2.
-template <int VM, int HD>
-__device__ __forceinline__ void v_pair(const uint32_t *va, const uint32_t *vb, int g, const DecodeSide &vs,
-                                       const uint32_t *lut, uint32_t ea, uint32_t eb, uint32_t (&lo)[HD / 16],
-                                       uint32_t (&hi)[HD / 16]) {
-    if (fmt_is4(VM)) {
-        constexpr int WORDS = HD / 64 > 0 ? HD / 64 : 1;  // words per key of this lane (8 dims = 1 word at HD 64)
-        constexpr int EPW = 8;
-#pragma unroll
-        for (int w = 0; w < WORDS; ++w) {
-            const uint32_t xa = va[g * WORDS + w], xb = vb[g * WORDS + w];
-            const uint32_t tl = (xa & 0x0f0f0f0fu) | ((xb & 0x0f0f0f0fu) << 4);
-            const uint32_t th = ((xa >> 4) & 0x0f0f0f0fu) | (xb & 0xf0f0f0f0u);
-            uint32_t l0, l1, l2, l3, h0, h1, h2, h3;
-            if (VM == B200_TURBO_MSE) {
-                l0 = lut[tl & 0xffu]; l1 = lut[(tl >> 8) & 0xffu]; l2 = lut[(tl >> 16) & 0xffu]; l3 = lut[tl >> 24];
-                h0 = lut[th & 0xffu]; h1 = lut[(th >> 8) & 0xffu]; h2 = lut[(th >> 16) & 0xffu]; h3 = lut[th >> 24];
-            } else {
-                cvt_e2m1x8_f16x2(tl, l0, l1, l2, l3);
-                cvt_e2m1x8_f16x2(th, h0, h1, h2, h3);
-                uint32_t scl;
-                const int d0 = g * (HD / 8) + EPW * w;
-                if (VM == B200_MXFP4) {
-                    const int blk = d0 / 32;
-                    const int e0 = (int)((va[vs.code_words + (blk >> 2)] >> ((blk & 3) * 8)) & 0xffu);
-                    const int e1 = (int)((vb[vs.code_words + (blk >> 2)] >> ((blk & 3) * 8)) & 0xffu);
-                    scl = pow2_f16x2(e0 - (int)ea, e1 - (int)eb);
-                } else {
-                    const int blk = d0 / 16;
-                    const uint32_t b0 = (va[vs.code_words + (blk >> 2)] >> ((blk & 3) * 8)) & 0xffu;
-                    const uint32_t b1 = (vb[vs.code_words + (blk >> 2)] >> ((blk & 3) * 8)) & 0xffu;
-                    scl = cvt_e4m3x2_f16x2(b0 | (b1 << 8));
-                }
-                l0 = hmul2_u32(l0, scl); l1 = hmul2_u32(l1, scl); l2 = hmul2_u32(l2, scl); l3 = hmul2_u32(l3, scl);
-                h0 = hmul2_u32(h0, scl); h1 = hmul2_u32(h1, scl); h2 = hmul2_u32(h2, scl); h3 = hmul2_u32(h3, scl);
-            }
-            lo[4 * w] = l0; lo[4 * w + 1] = l1; lo[4 * w + 2] = l2; lo[4 * w + 3] = l3;
-            hi[4 * w] = h0; hi[4 * w + 1] = h1; hi[4 * w + 2] = h2; hi[4 * w + 3] = h3;
-        }
-    } else {
-        constexpr int WORDS = HD / 32;  // words per key of this lane
-#pragma unroll
-        for (int w = 0; w < WORDS; ++w) {
-            const uint32_t xa = va[g * WORDS + w], xb = vb[g * WORDS + w];
-            const uint32_t t0 = __byte_perm(xa, xb, 0x5140);  // a0 b0 a1 b1
-            const uint32_t t1 = __byte_perm(xa, xb, 0x7362);  // a2 b2 a3 b3
-            uint32_t l0 = cvt_e4m3x2_f16x2(t0), h0 = cvt_e4m3x2_hi_f16x2(t0);
-            uint32_t l1 = cvt_e4m3x2_f16x2(t1), h1 = cvt_e4m3x2_hi_f16x2(t1);
-            if (VM == B200_MXFP8) {
-                const int blk = (g * (HD / 8) + 4 * w) / 32;
-                const int e0 = (int)((va[vs.code_words + (blk >> 2)] >> ((blk & 3) * 8)) & 0xffu);
-                const int e1 = (int)((vb[vs.code_words + (blk >> 2)] >> ((blk & 3) * 8)) & 0xffu);
-                const uint32_t scl = pow2_f16x2(e0 - (int)ea, e1 - (int)eb);
-                l0 = hmul2_u32(l0, scl); h0 = hmul2_u32(h0, scl); l1 = hmul2_u32(l1, scl); h1 = hmul2_u32(h1, scl);
-            }
-            lo[2 * w] = l0; hi[2 * w] = h0; lo[2 * w + 1] = l1; hi[2 * w + 1] = h1;
-        }
+        cvt_e2m1x8_f16x2(x, h0, h1, h2, h3);
     }
 }
 
@@ -295,71 +168,88 @@ __device__ __forceinline__ void warp_hadamard(float *row, int n, const float *si
     }
 }
 
-template <int KM, int VM, int HD, bool QSPLIT>
-__global__ void __launch_bounds__(DW * 32) tq_decode_kernel(const DecodeParams p) {
-    constexpr int STEPS = HD / 16;  // k-steps of q k^T == m-tiles of the output
+template <int KM, int VM, int HD>
+__global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParams p) {
+    constexpr int STEPS = HD / 16;          // k-steps of K Q^T == m-tiles of the output
+    constexpr bool K4 = fmt_is4(KM), V4 = fmt_is4(VM);
+    constexpr bool KMX = fmt_is_mx(KM);     // block-wise accumulation, contraction order A
+    constexpr int KMW = kmeta_words(KM, HD);
+    constexpr int NBK = HD / 32;            // 32-blocks per row
+    constexpr int NBV = vsc_blocks(VM, HD);
+    constexpr int META = meta_bytes(KM, VM, HD);
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);                       // [DW][NS_MAX]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);  // [DW][NS_MAX]
     const int NS = (int)p.ns;
-    uint32_t *lut_k = reinterpret_cast<uint32_t *>(smem + 128);                // 256
-    uint32_t *lut_v = lut_k + 256;                                             // 256
-    float *mbuf = reinterpret_cast<float *>(smem + 128 + 2048);                // [DW][PACK][HD]
-    float *m_M = mbuf + DW * PACK * HD;                                        // [DW][PACK]
-    float *m_L = m_M + DW * PACK;                                              // [DW][PACK]
-    uint8_t *stages = reinterpret_cast<uint8_t *>(m_L + DW * PACK);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t lut_k = sbase + 128, lut_v = lut_k + 1024;
+    uint8_t *stages = smem + FIXED_SMEM + DW * META;
+    float *mbuf = reinterpret_cast<float *>(stages);  // [DW][PACK][HD], then M and L [DW][PACK]: used before / after the key loop
     const uint32_t stage_bytes = p.k_stage_bytes + p.v_stage_bytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
     const uint32_t split = blockIdx.x, y = blockIdx.y, b = blockIdx.z;
     const uint32_t hk = y / p.packs, pack = y % p.packs;
     const uint32_t G = p.group, R = p.rows_per_kv;
-    const long long lk_b = p.kv_len ? (long long)p.kv_len[b] : (long long)p.lk;
+    const int lk_b = p.kv_len ? max(p.kv_len[b], 0) : (int)p.lk;
 
     // visible key range of query row r of this kv head (r = token * G + head in group)
-    auto row_range = [&](uint32_t r, long long &lo, long long &hi, long long &pos) {
+    auto row_range = [&](uint32_t r, int &lo, int &hi, int &pos) {
         const long long i = r / G;
-        pos = i + lk_b - (long long)p.lq;
-        lo = p.wl >= 0 ? max(pos - p.wl, 0ll) : 0ll;
-        hi = p.wr >= 0 ? min(pos + p.wr + 1, lk_b) : lk_b;
-        lo = min(lo, lk_b);
-        hi = max(hi, lo);
+        const long long ps = i + (long long)lk_b - (long long)p.lq;
+        long long l = p.wl >= 0 ? max(ps - p.wl, 0ll) : 0ll;
+        long long h = p.wr >= 0 ? min(ps + p.wr + 1, (long long)lk_b) : (long long)lk_b;
+        l = min(l, (long long)lk_b);
+        h = max(h, l);
+        lo = (int)l;
+        hi = (int)h;
+        pos = (int)max(min(ps, 2147483647ll), -2147483647ll);
     };
-    long long LO = lk_b, HI = 0;
+    int LO = lk_b, HI = 0, LOmax = 0, HImin = lk_b;
     for (uint32_t rr = 0; rr < PACK; ++rr) {
         const uint32_t r = pack * PACK + rr;
         if (r < R) {
-            long long lo, hi, pos;
+            int lo, hi, pos;
             row_range(r, lo, hi, pos);
             if (lo < hi) {
                 LO = min(LO, lo);
                 HI = max(HI, hi);
             }
+            LOmax = max(LOmax, lo);
+            HImin = min(HImin, hi);
         }
     }
     if (HI < LO) HI = LO;
-    const uint32_t nsplit = (uint32_t)((HI - LO + p.chunk - 1) / p.chunk);
-    if (split == 0 && tid == 0) p.meta[(size_t)b * gridDim.y + y] = (int32_t)nsplit;
+    const uint32_t nsplit = (uint32_t)(((long long)HI - LO + p.chunk - 1) / p.chunk);
+    if (split == 0 && tid == 0 && p.meta) p.meta[(size_t)b * gridDim.y + y] = (int32_t)nsplit;
     if (split >= max(nsplit, 1u)) return;
-    const long long c_lo = LO + (long long)split * p.chunk;
-    const long long c_hi = min(c_lo + (long long)p.chunk, HI);
+    const int c_lo = LO + (int)(split * p.chunk);
+    const int c_hi = (int)min((long long)c_lo + p.chunk, (long long)HI);
+    const bool plain = p.softcap <= 0.0f && p.alibi == nullptr;  // tiles inside every row's range take the unmasked path
 
-    // this lane's query row (row g of the pack)
-    const uint32_t my_r = pack * PACK + g;
-    const bool my_valid = my_r < R;
-    long long my_lo = 0, my_hi = 0, my_pos = 0;
-    if (my_valid) row_range(my_r, my_lo, my_hi, my_pos);
-    const uint32_t my_head = hk * G + (my_valid ? my_r % G : 0);
-    const float my_slope = (p.alibi && my_valid) ? p.alibi[(size_t)b * p.alibi_bs + my_head] : 0.0f;
+    // the two query rows whose scores this lane holds (columns 2c, 2c + 1 of the score fragments)
+    int r_lo[2], r_hi[2], r_pos[2];
+    float r_slope[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const uint32_t r = pack * PACK + 2 * c + e;
+        r_lo[e] = r_hi[e] = r_pos[e] = 0;
+        r_slope[e] = 0.0f;
+        if (r < R) {
+            row_range(r, r_lo[e], r_hi[e], r_pos[e]);
+            r_hi[e] = min(r_hi[e], c_hi);
+            if (p.alibi) r_slope[e] = p.alibi[(size_t)b * p.alibi_bs + hk * G + r % G];
+        }
+    }
 
     // ------------------------------------------------------------------ prologue
     if (tid == 0) {
         for (int i = 0; i < DW * NS_MAX; ++i) mbar_init(&bars[i], 1);
         mbar_fence_init();
     }
-    if (KM == B200_TURBO_MSE)
-        for (int i = tid; i < 256; i += DW * 32) lut_k[i] = pack_f16x2(p.k.tab[i & 15], p.k.tab[i >> 4]);
-    if (VM == B200_TURBO_MSE)
-        for (int i = tid; i < 256; i += DW * 32) lut_v[i] = pack_f16x2(p.v.tab[i & 15], p.v.tab[i >> 4]);
+    if constexpr (KM == B200_TURBO_MSE)
+        for (int i = tid; i < 256; i += DW * 32) sts32(lut_k + 4 * i, pack_f16x2(p.k.tab[i & 15], p.k.tab[i >> 4]));
+    if constexpr (VM == B200_TURBO_MSE)
+        for (int i = tid; i < 256; i += DW * 32) sts32(lut_v + 4 * i, pack_f16x2(p.v.tab[i & 15], p.v.tab[i >> 4]));
     // queries -> f32 rows in shared memory (rows of the pack; missing rows are zero)
     float *qbuf = mbuf;  // [PACK][HD]
     for (int idx = tid; idx < PACK * HD; idx += DW * 32) {
@@ -377,9 +267,10 @@ __global__ void __launch_bounds__(DW * 32) tq_decode_kernel(const DecodeParams p
         for (int rr = warp; rr < PACK; rr += DW) warp_hadamard(qbuf + rr * HD, HD, p.k.signs, true, lane);
         __syncthreads();
     }
-    // power of two normalization of row g, then f16 fragments (hi / lo halves when QSPLIT)
-    uint32_t qh0[STEPS], qh2[STEPS], ql0[STEPS], ql2[STEPS];
-    float qscale;
+    // power of two normalization of row g, then the f16 B fragments of K Q^T: per k-step the four
+    // contraction slots of this lane are the consecutive dims dbase(s) ... dbase(s) + 3
+    uint32_t qb0[STEPS], qb1[STEPS];
+    float qs[2];  // softmax scale times the row's power of two, for the rows 2c and 2c + 1
     {
         const float *qr = qbuf + g * HD;
         float am = 0.0f;
@@ -390,40 +281,39 @@ __global__ void __launch_bounds__(DW * 32) tq_decode_kernel(const DecodeParams p
         if (am > 0.0f && am < INFINITY) e = (int)((f2u(am) >> 23) & 0xffu) - 127 - 7;
         e = max(min(e, 100), -100);
         const float down = u2f((uint32_t)(127 - e) << 23), up = u2f((uint32_t)(127 + e) << 23);
-        qscale = p.scale * up;
+        const float qscale = p.scale * up;
+        qs[0] = __shfl_sync(0xffffffffu, qscale, (2 * c) * 4);
+        qs[1] = __shfl_sync(0xffffffffu, qscale, (2 * c + 1) * 4);
 #pragma unroll
         for (int s = 0; s < STEPS; ++s) {
-            const float *q4 = qr + c * (HD / 4) + 4 * s;
-            const float x0 = q4[0] * down, x1 = q4[1] * down, x2 = q4[2] * down, x3 = q4[3] * down;
-            qh0[s] = pack_f16x2(x0, x1);
-            qh2[s] = pack_f16x2(x2, x3);
-            if (QSPLIT) {
-                const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&qh0[s]));
-                const float2 f2 = __half22float2(*reinterpret_cast<const __half2 *>(&qh2[s]));
-                ql0[s] = pack_f16x2(x0 - f0.x, x1 - f0.y);
-                ql2[s] = pack_f16x2(x2 - f2.x, x3 - f2.y);
-            } else {
-                ql0[s] = 0u;
-                ql2[s] = 0u;
-            }
+            const int dbase = KMX ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : c * (HD / 4) + 4 * s;
+            const float *q4 = qr + dbase;
+            qb0[s] = pack_f16x2(q4[0] * down, q4[1] * down);
+            qb1[s] = pack_f16x2(q4[2] * down, q4[3] * down);
         }
     }
-    __syncthreads();  // qbuf is reused by the merge; barriers are initialized
+    __syncthreads();  // qbuf lives in the stage area; barriers are initialized
 
     // ------------------------------------------------------------------ per-warp key loop
     const uint32_t *kbase = p.k_rows + (size_t)b * p.k_sb + (size_t)hk * p.k_sh;
     const uint32_t *vbase = p.v_rows + (size_t)b * p.v_sb + (size_t)hk * p.v_sh;
     const uint32_t krb = (uint32_t)p.k_ss * 4u, vrb = (uint32_t)p.v_ss * 4u;  // row bytes
-    const int ntiles = (int)((c_hi - c_lo + WK - 1) / WK);
+    const int ntiles = (c_hi - c_lo + WK - 1) / WK;
     const int my_tiles = ntiles > warp ? (ntiles - warp + DW - 1) / DW : 0;
     uint8_t *wstage = stages + (size_t)warp * NS * stage_bytes;
+    const uint32_t wstage_s = smem_u32(wstage);
     uint64_t *wbar = bars + warp * NS_MAX;
+    const uint32_t meta_s = sbase + FIXED_SMEM + warp * META;    // [WK][KMW] f32
+    const uint32_t vmeta_s = meta_s + WK * KMW * 4;              // [WK] (sigma, log2 sigma)
+    const uint32_t vsc_s = vmeta_s + WK * 8;                     // [NBV][WK] f16
+    const uint32_t k_cw4 = (uint32_t)p.k.code_words * 4u, k_rsc4 = (uint32_t)p.k.rsc_off * 4u;
+    const uint32_t v_cw4 = (uint32_t)p.v.code_words * 4u, v_rsc4 = (uint32_t)p.v.rsc_off * 4u;
     bool wait_failed = false;
 
     // copies tile n of this warp into its stage n % NS
     auto issue = [&](int n) {
-        const long long key0 = c_lo + (long long)(warp + n * DW) * WK;
-        const int nkeys = (int)min((long long)WK, c_hi - key0);
+        const int key0 = c_lo + (warp + n * DW) * WK;
+        const int nkeys = min(WK, c_hi - key0);
         uint8_t *st = wstage + (size_t)(n % NS) * stage_bytes;
         const uintptr_t ka = reinterpret_cast<uintptr_t>(kbase) + (uintptr_t)key0 * krb;
         const uintptr_t va = reinterpret_cast<uintptr_t>(vbase) + (uintptr_t)key0 * vrb;
@@ -454,10 +344,15 @@ __global__ void __launch_bounds__(DW * 32) tq_decode_kernel(const DecodeParams p
         }
     };
 
-    float M = -INFINITY, lsum = 0.0f;  // row g: running max (log2 domain, value scale folded in), partial normalizer
+    // running maxima (log2 domain, value scale folded in) and partial normalizers of rows 2c, 2c + 1
+    float M[2] = {-1e30f, -1e30f}, lsum[2] = {0.0f, 0.0f};
     float oacc[STEPS][4];
 #pragma unroll
     for (int mt = 0; mt < STEPS; ++mt) oacc[mt][0] = oacc[mt][1] = oacc[mt][2] = oacc[mt][3] = 0.0f;
+
+    // lane offsets inside a tile: K rows g (and g + 8), V rows 2c (and 2c + 1, 2c + 8, 2c + 9)
+    const uint32_t k_lane = g * krb + (KMX ? (K4 ? 4u * c : 8u * c) : (K4 ? c * (HD / 8) : c * (HD / 4)));
+    const uint32_t v_lane = 2 * c * vrb + (V4 ? g * (HD / 16) : g * (HD / 8));
 
     for (int n = 0; n < min(NS, my_tiles); ++n) issue(n);
 
@@ -466,91 +361,249 @@ __global__ void __launch_bounds__(DW * 32) tq_decode_kernel(const DecodeParams p
             wait_failed = true;
             break;
         }
-        const long long key0 = c_lo + (long long)(warp + n * DW) * WK;
-        const int nkeys = (int)min((long long)WK, c_hi - key0);
-        uint8_t *st = wstage + (size_t)(n % NS) * stage_bytes;
-        const uint32_t koff = (uint32_t)((reinterpret_cast<uintptr_t>(kbase) + (uintptr_t)key0 * krb) & 15u);
-        const uint32_t voff = (uint32_t)((reinterpret_cast<uintptr_t>(vbase) + (uintptr_t)key0 * vrb) & 15u);
-        uint32_t *ktile = reinterpret_cast<uint32_t *>(st + koff);
-        uint32_t *vtile = reinterpret_cast<uint32_t *>(st + p.k_stage_bytes + voff);
+        const int key0 = c_lo + (warp + n * DW) * WK;
+        const int nkeys = min(WK, c_hi - key0);
+        const uint32_t st_s = wstage_s + (uint32_t)(n % NS) * stage_bytes;
+        const uint32_t kt = st_s + (uint32_t)((reinterpret_cast<uintptr_t>(kbase) + (uintptr_t)key0 * krb) & 15u);
+        const uint32_t vt = st_s + p.k_stage_bytes + (uint32_t)((reinterpret_cast<uintptr_t>(vbase) + (uintptr_t)key0 * vrb) & 15u);
         if (nkeys < WK) {
             // rows past the chunk hold stale bytes: clear them so that masked keys decode to finite values
-            const int nround = ((nkeys + 15) & ~15);
-            for (uint32_t w = nkeys * p.k_ss + lane; w < nround * p.k_ss; w += 32) ktile[w] = 0u;
-            for (uint32_t w = nkeys * p.v_ss + lane; w < nround * p.v_ss; w += 32) vtile[w] = 0u;
+            const uint32_t nround = (uint32_t)((nkeys + 15) & ~15);
+            for (uint32_t w = nkeys * (krb >> 2) + lane; w < nround * (krb >> 2); w += 32) sts32(kt + 4 * w, 0u);
+            for (uint32_t w = nkeys * (vrb >> 2) + lane; w < nround * (vrb >> 2); w += 32) sts32(vt + 4 * w, 0u);
             __syncwarp();
         }
-#pragma unroll 1
-        for (int u = 0; u < WK / 16; ++u) {
-            if (u * 16 >= nkeys) break;
-            // ---- scores of 16 keys: two groups of 8 (lane's key: g)
-            float sacc[2][4];
-            float kap[2];
+        // ---- per-key scalars of the tile, lane = key
+        {
+            const bool have = lane < ((nkeys + 15) & ~15);
+            const uint32_t kr = kt + lane * krb, vr = vt + lane * vrb;
+            const float k0 = have ? u2f(lds32(kr + k_rsc4)) : 0.0f;
+            if constexpr (KMX) {
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.0f;
-                const uint32_t *krow = ktile + (size_t)(16 * u + 8 * nt + g) * p.k_ss;
-                kap[nt] = qk_group<KM, HD, QSPLIT>(krow, c, p.k, lut_k, qh0, qh2, ql0, ql2, sacc[nt]);
+                for (int w = 0; w < (NBK + 3) / 4; ++w) {
+                    const uint32_t aux = have ? lds32(kr + k_cw4 + 4 * w) : 0u;
+#pragma unroll
+                    for (int i = 0; i < 4 && 4 * w + i < KMW; ++i) {
+                        const uint32_t e = (aux >> (8 * i)) & 0xffu;
+                        sts32(meta_s + (lane * KMW + 4 * w + i) * 4, f2u(e ? k0 * u2f(e << 23) : 0.0f));
+                    }
+                }
+            } else {
+                sts32(meta_s + lane * 4, f2u(k0));
             }
-            // ---- value rows of this lane: keys 2c, 2c+1, 2c+8, 2c+9 of the 16
-            const uint32_t *vr[4];
-            float lsig[4];
-            bool live[4];
-            uint32_t vemax[4];
+            const float v0 = have ? u2f(lds32(vr + v_rsc4)) : 0.0f;
+            float sigma = v0;
+            if constexpr (fmt_is_mx(VM)) {
+                uint32_t aux[(NBV + 3) / 4];
+                uint32_t em = 0;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int kk = 16 * u + 2 * c + (i & 1) + 8 * (i >> 1);
-                vr[i] = vtile + (size_t)kk * p.v_ss;
-                v_meta<VM, HD>(vr[i], p.v, lsig[i], live[i], vemax[i]);
-            }
-            // ---- online softmax for row g over the columns 2c, 2c+1 (group 0) and 8+2c, 9+2c (group 1)
-            float s2[4], t2[4];
-            float cmax = -INFINITY;
+                for (int w = 0; w < (NBV + 3) / 4; ++w) {
+                    aux[w] = have ? lds32(vr + v_cw4 + 4 * w) : 0u;
+                    em = w == 0 ? aux[w] : __vmaxu4(em, aux[w]);
+                }
+                const uint32_t emax = max_byte(em);
+                sigma = emax ? v0 * u2f(emax << 23) : 0.0f;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int nt = i >> 1, e = i & 1;
-                const float kappa = __shfl_sync(0xffffffffu, kap[nt], (2 * c + e) * 4);
-                const long long j = key0 + 16 * u + 8 * nt + 2 * c + e;
-                float s = sacc[nt][e] * kappa * qscale;
-                if (p.softcap > 0.0f) s = p.softcap * tanhf(s / p.softcap);
-                if (my_slope != 0.0f) s -= my_slope * fabsf((float)(my_pos - j));
-                const bool vis = my_valid && j >= my_lo && j < my_hi && j < c_hi;
-                s2[i] = vis ? s * LOG2E : -INFINITY;
-                t2[i] = vis ? s2[i] + lsig[i] : -INFINITY;
-                cmax = fmaxf(cmax, t2[i]);
-            }
-            cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, 1));
-            cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, 2));
-            const float m_new = fmaxf(M, cmax);
-            const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-            const bool grew = m_new > M;
-            if (__any_sync(0xffffffffu, grew)) {
-                const float alpha = fast_exp2(M - m_use);  // 0 when M was -inf
-                lsum *= alpha;
-                const float a0 = __shfl_sync(0xffffffffu, alpha, (2 * c) * 4);
-                const float a1 = __shfl_sync(0xffffffffu, alpha, (2 * c + 1) * 4);
+                for (int bk = 0; bk < NBV; ++bk) {
+                    const int e = (int)((aux[bk >> 2] >> (8 * (bk & 3))) & 0xffu);
+                    sts16(vsc_s + (bk * WK + lane) * 2, pow2_f16(e - (int)emax));
+                }
+            } else if constexpr (VM == B200_NVFP4) {
 #pragma unroll
-                for (int mt = 0; mt < STEPS; ++mt) {
-                    oacc[mt][0] *= a0;
-                    oacc[mt][1] *= a1;
-                    oacc[mt][2] *= a0;
-                    oacc[mt][3] *= a1;
+                for (int w = 0; w < NBV / 4; ++w) {
+                    const uint32_t aux = have ? lds32(vr + v_cw4 + 4 * w) : 0u;
+                    const uint32_t lo = cvt_e4m3x2_f16x2(aux), hi = cvt_e4m3x2_hi_f16x2(aux);
+                    sts16(vsc_s + ((4 * w) * WK + lane) * 2, lo & 0xffffu);
+                    sts16(vsc_s + ((4 * w + 1) * WK + lane) * 2, lo >> 16);
+                    sts16(vsc_s + ((4 * w + 2) * WK + lane) * 2, hi & 0xffffu);
+                    sts16(vsc_s + ((4 * w + 3) * WK + lane) * 2, hi >> 16);
                 }
             }
-            M = m_new;
-            float wgt[4];
+            const bool live = sigma > 0.0f && sigma < INFINITY;
+            const float sc = live ? fminf(fmaxf(sigma, 7.8886091e-31f), 1.2676506e30f) : 0.0f;  // 2^-100 ... 2^100
+            sts32(vmeta_s + lane * 8, f2u(sc));
+            sts32(vmeta_s + lane * 8 + 4, f2u(live ? fast_log2(sc) : -100.0f));
+            __syncwarp();
+        }
+        const bool full = plain && nkeys == WK && key0 >= LOmax && key0 + WK <= HImin;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                lsum += fast_exp2(s2[i] - m_use);
-                wgt[i] = live[i] ? fast_exp2(t2[i] - m_use) : 0.0f;
+        for (int u = 0; u < WK / 16; ++u) {
+            if (u * 16 < nkeys) {
+                // ---- scores of keys g and g + 8 of the 16 against the rows 2c, 2c + 1
+                const uint32_t ka = kt + k_lane + u * 16 * krb, ka8 = ka + 8 * krb;
+                float sr[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                if constexpr (KMX) {
+                    float ks0[KMW], ks8[KMW];
+                    if constexpr (KMW == 2) {
+                        const float2 a = lds64f(meta_s + (16 * u + g) * 8), b8 = lds64f(meta_s + (16 * u + 8 + g) * 8);
+                        ks0[0] = a.x; ks0[1] = a.y; ks8[0] = b8.x; ks8[1] = b8.y;
+                    } else {
+#pragma unroll
+                        for (int w = 0; w < KMW / 4; ++w) {
+                            const float4 a = lds128f(meta_s + ((16 * u + g) * KMW + 4 * w) * 4);
+                            const float4 b8 = lds128f(meta_s + ((16 * u + 8 + g) * KMW + 4 * w) * 4);
+                            ks0[4 * w] = a.x; ks0[4 * w + 1] = a.y; ks0[4 * w + 2] = a.z; ks0[4 * w + 3] = a.w;
+                            ks8[4 * w] = b8.x; ks8[4 * w + 1] = b8.y; ks8[4 * w + 2] = b8.z; ks8[4 * w + 3] = b8.w;
+                        }
+                    }
+#pragma unroll
+                    for (int bk = 0; bk < NBK; ++bk) {
+                        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        if constexpr (K4) {
+                            const uint32_t x0 = lds32(ka + 16 * bk), x8 = lds32(ka8 + 16 * bk);
+                            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                            cvt_e2m1x8_f16x2(x0, a0, a1, a2, a3);
+                            cvt_e2m1x8_f16x2(x8, b0, b1, b2, b3);
+                            mma_f16_16816(acc, a0, b0, a1, b1, qb0[2 * bk], qb1[2 * bk]);
+                            mma_f16_16816(acc, a2, b2, a3, b3, qb0[2 * bk + 1], qb1[2 * bk + 1]);
+                        } else {
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                const uint32_t x0 = lds32(ka + 32 * bk + 4 * h), x8 = lds32(ka8 + 32 * bk + 4 * h);
+                                mma_f16_16816(acc, cvt_e4m3x2_f16x2(x0), cvt_e4m3x2_f16x2(x8), cvt_e4m3x2_hi_f16x2(x0),
+                                              cvt_e4m3x2_hi_f16x2(x8), qb0[2 * bk + h], qb1[2 * bk + h]);
+                            }
+                        }
+                        sr[0] = fmaf(acc[0], ks0[bk], sr[0]);
+                        sr[1] = fmaf(acc[1], ks0[bk], sr[1]);
+                        sr[2] = fmaf(acc[2], ks8[bk], sr[2]);
+                        sr[3] = fmaf(acc[3], ks8[bk], sr[3]);
+                    }
+                } else {
+                    if constexpr (K4) {
+                        constexpr int WPL = HD / 32;  // words of this lane per key
+                        uint32_t sg[WPL > 1 ? WPL / 2 : 1], sg8[WPL > 1 ? WPL / 2 : 1];
+                        if constexpr (KM == B200_NVFP4) {
+                            // E4M3 block scales of the lane's 16-blocks c * (HD / 64) ..., as f16x2 {s, s}
+#pragma unroll
+                            for (int i = 0; i < HD / 64; ++i) {
+                                const int blk = c * (HD / 64) + i;
+                                const uint32_t off = k_cw4 + (uint32_t)(blk & ~3) - c * (HD / 8);  // from the lane's first code byte
+                                const uint32_t w0 = lds32(ka + off), w8 = lds32(ka8 + off);
+                                const uint32_t b0 = (w0 >> (8 * (blk & 3))) & 0xffu, b8 = (w8 >> (8 * (blk & 3))) & 0xffu;
+                                sg[i] = cvt_e4m3x2_f16x2(b0 | (b0 << 8));
+                                sg8[i] = cvt_e4m3x2_f16x2(b8 | (b8 << 8));
+                            }
+                        }
+#pragma unroll
+                        for (int w = 0; w < WPL; ++w) {
+                            const uint32_t x0 = lds32(ka + 4 * w), x8 = lds32(ka8 + 4 * w);
+                            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                            dq4<KM>(x0, lut_k, a0, a1, a2, a3);
+                            dq4<KM>(x8, lut_k, b0, b1, b2, b3);
+                            if constexpr (KM == B200_NVFP4) {
+                                const uint32_t s0 = sg[w / 2], s8 = sg8[w / 2];
+                                a0 = hmul2_u32(a0, s0); a1 = hmul2_u32(a1, s0); a2 = hmul2_u32(a2, s0); a3 = hmul2_u32(a3, s0);
+                                b0 = hmul2_u32(b0, s8); b1 = hmul2_u32(b1, s8); b2 = hmul2_u32(b2, s8); b3 = hmul2_u32(b3, s8);
+                            }
+                            mma_f16_16816(sr, a0, b0, a1, b1, qb0[2 * w], qb1[2 * w]);
+                            mma_f16_16816(sr, a2, b2, a3, b3, qb0[2 * w + 1], qb1[2 * w + 1]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int s = 0; s < STEPS; ++s) {
+                            const uint32_t x0 = lds32(ka + 4 * s), x8 = lds32(ka8 + 4 * s);
+                            mma_f16_16816(sr, cvt_e4m3x2_f16x2(x0), cvt_e4m3x2_f16x2(x8), cvt_e4m3x2_hi_f16x2(x0),
+                                          cvt_e4m3x2_hi_f16x2(x8), qb0[s], qb1[s]);
+                        }
+                    }
+                    const float kp0 = u2f(lds32(meta_s + (16 * u + g) * 4)), kp8 = u2f(lds32(meta_s + (16 * u + 8 + g) * 4));
+                    sr[0] *= kp0; sr[1] *= kp0; sr[2] *= kp8; sr[3] *= kp8;
+                }
+                // ---- online softmax: sr[2 k + e] = key (g + 8 k), row 2c + e
+                const float2 vm0 = lds64f(vmeta_s + (16 * u + g) * 8), vm8 = lds64f(vmeta_s + (16 * u + 8 + g) * 8);
+                float s2[4];
+                if (full) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) s2[i] = sr[i] * (qs[i & 1] * LOG2E);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int e = i & 1, j = key0 + 16 * u + g + 8 * (i >> 1);
+                        float s = sr[i] * qs[e];
+                        if (p.softcap > 0.0f) s = p.softcap * tanhf(s / p.softcap);
+                        if (r_slope[e] != 0.0f) s -= r_slope[e] * fabsf((float)(r_pos[e] - j));
+                        s2[i] = (j >= r_lo[e] && j < r_hi[e]) ? s * LOG2E : -INFINITY;
+                    }
+                }
+                const float t0 = s2[0] + vm0.y, t1 = s2[1] + vm0.y, t2 = s2[2] + vm8.y, t3 = s2[3] + vm8.y;
+                const bool grow = fmaxf(t0, t2) > M[0] + MAX_SLACK || fmaxf(t1, t3) > M[1] + MAX_SLACK;
+                if (__any_sync(0xffffffffu, grow)) {
+                    float c0 = fmaxf(t0, t2), c1 = fmaxf(t1, t3);
+#pragma unroll
+                    for (int o = 4; o < 32; o <<= 1) {
+                        c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, o));
+                        c1 = fmaxf(c1, __shfl_xor_sync(0xffffffffu, c1, o));
+                    }
+                    const float n0 = fmaxf(M[0], c0), n1 = fmaxf(M[1], c1);
+                    const float al0 = fast_exp2(M[0] - n0), al1 = fast_exp2(M[1] - n1);
+                    M[0] = n0;
+                    M[1] = n1;
+                    lsum[0] *= al0;
+                    lsum[1] *= al1;
+#pragma unroll
+                    for (int mt = 0; mt < STEPS; ++mt) {
+                        oacc[mt][0] *= al0;
+                        oacc[mt][1] *= al1;
+                        oacc[mt][2] *= al0;
+                        oacc[mt][3] *= al1;
+                    }
+                }
+                const float p0 = fast_exp2(s2[0] - M[0]), p1 = fast_exp2(s2[1] - M[1]);
+                const float p2 = fast_exp2(s2[2] - M[0]), p3 = fast_exp2(s2[3] - M[1]);
+                lsum[0] += p0 + p2;
+                lsum[1] += p1 + p3;
+                const uint32_t pb0 = movmatrix_trans(pack_f16x2(p0 * vm0.x, p1 * vm0.x));
+                const uint32_t pb1 = movmatrix_trans(pack_f16x2(p2 * vm8.x, p3 * vm8.x));
+                // ---- O^T += V^T P^T: keys 2c, 2c+1 | 2c+8, 2c+9 of the 16, dims [g HD/8, (g+1) HD/8)
+                const uint32_t va = vt + v_lane + u * 16 * vrb;
+#pragma unroll
+                for (int w = 0; w < (V4 ? (HD / 64 > 0 ? HD / 64 : 1) : HD / 32); ++w) {
+                    const uint32_t xa = lds32(va + 4 * w), xb = lds32(va + vrb + 4 * w);
+                    const uint32_t xc = lds32(va + 8 * vrb + 4 * w), xd = lds32(va + 9 * vrb + 4 * w);
+                    if constexpr (V4) {
+                        // nibbles of two keys side by side: byte i = (a[2i], b[2i]) and (a[2i+1], b[2i+1])
+                        const uint32_t tl0 = (xa & 0x0f0f0f0fu) | ((xb & 0x0f0f0f0fu) << 4);
+                        const uint32_t th0 = ((xa >> 4) & 0x0f0f0f0fu) | (xb & 0xf0f0f0f0u);
+                        const uint32_t tl1 = (xc & 0x0f0f0f0fu) | ((xd & 0x0f0f0f0fu) << 4);
+                        const uint32_t th1 = ((xc >> 4) & 0x0f0f0f0fu) | (xd & 0xf0f0f0f0u);
+                        uint32_t l0[4], h0[4], l1[4], h1[4];
+                        dq4<VM>(tl0, lut_v, l0[0], l0[1], l0[2], l0[3]);
+                        dq4<VM>(th0, lut_v, h0[0], h0[1], h0[2], h0[3]);
+                        dq4<VM>(tl1, lut_v, l1[0], l1[1], l1[2], l1[3]);
+                        dq4<VM>(th1, lut_v, h1[0], h1[1], h1[2], h1[3]);
+                        if constexpr (NBV > 0) {
+                            const int d0 = g * (HD / 8) + 8 * w;  // first dim of this word
+                            const int blk = d0 / (HD / NBV);
+                            const uint32_t sa = lds32(vsc_s + (blk * WK + 16 * u + 2 * c) * 2);
+                            const uint32_t sb = lds32(vsc_s + (blk * WK + 16 * u + 8 + 2 * c) * 2);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                l0[i] = hmul2_u32(l0[i], sa); h0[i] = hmul2_u32(h0[i], sa);
+                                l1[i] = hmul2_u32(l1[i], sb); h1[i] = hmul2_u32(h1[i], sb);
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) mma_f16_16816(oacc[4 * w + i], l0[i], h0[i], l1[i], h1[i], pb0, pb1);
+                    } else {
+                        const uint32_t ta0 = __byte_perm(xa, xb, 0x5140), ta1 = __byte_perm(xa, xb, 0x7362);
+                        const uint32_t tb0 = __byte_perm(xc, xd, 0x5140), tb1 = __byte_perm(xc, xd, 0x7362);
+                        uint32_t l0 = cvt_e4m3x2_f16x2(ta0), h0 = cvt_e4m3x2_hi_f16x2(ta0);
+                        uint32_t l1 = cvt_e4m3x2_f16x2(tb0), h1 = cvt_e4m3x2_hi_f16x2(tb0);
+                        uint32_t l2 = cvt_e4m3x2_f16x2(ta1), h2 = cvt_e4m3x2_hi_f16x2(ta1);
+                        uint32_t l3 = cvt_e4m3x2_f16x2(tb1), h3 = cvt_e4m3x2_hi_f16x2(tb1);
+                        if constexpr (NBV > 0) {
+                            const int blk = (g * (HD / 8) + 4 * w) / 32;
+                            const uint32_t sa = lds32(vsc_s + (blk * WK + 16 * u + 2 * c) * 2);
+                            const uint32_t sb = lds32(vsc_s + (blk * WK + 16 * u + 8 + 2 * c) * 2);
+                            l0 = hmul2_u32(l0, sa); h0 = hmul2_u32(h0, sa); l2 = hmul2_u32(l2, sa); h2 = hmul2_u32(h2, sa);
+                            l1 = hmul2_u32(l1, sb); h1 = hmul2_u32(h1, sb); l3 = hmul2_u32(l3, sb); h3 = hmul2_u32(h3, sb);
+                        }
+                        mma_f16_16816(oacc[2 * w], l0, h0, l1, h1, pb0, pb1);
+                        mma_f16_16816(oacc[2 * w + 1], l2, h2, l3, h3, pb0, pb1);
+                    }
+                }
             }
-            const uint32_t pb0 = pack_f16x2(wgt[0], wgt[1]), pb1 = pack_f16x2(wgt[2], wgt[3]);
-            // ---- O^T += V^T P^T
-            uint32_t lo0[STEPS], hi0[STEPS], lo1[STEPS], hi1[STEPS];
-            v_pair<VM, HD>(vr[0], vr[1], g, p.v, lut_v, vemax[0], vemax[1], lo0, hi0);
-            v_pair<VM, HD>(vr[2], vr[3], g, p.v, lut_v, vemax[2], vemax[3], lo1, hi1);
-#pragma unroll
-            for (int mt = 0; mt < STEPS; ++mt) mma_f16_16816(oacc[mt], lo0[mt], hi0[mt], lo1[mt], hi1[mt], pb0, pb1);
         }
         // the stage was read (and possibly patched) through the generic proxy: order that before the
         // bulk copy of the next tile into it
@@ -561,12 +614,18 @@ __global__ void __launch_bounds__(DW * 32) tq_decode_kernel(const DecodeParams p
     if (wait_failed && p.status) atomicExch(p.status, 1);
 
     // ------------------------------------------------------------------ merge the warps
-    lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
-    lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
-    __syncthreads();
-    if (c == 0) {
-        m_M[warp * PACK + g] = M;
-        m_L[warp * PACK + g] = lsum;
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+        lsum[0] += __shfl_xor_sync(0xffffffffu, lsum[0], o);
+        lsum[1] += __shfl_xor_sync(0xffffffffu, lsum[1], o);
+    }
+    __syncthreads();  // every warp is done with its stages: the area becomes the merge buffer
+    float *m_M = mbuf + DW * PACK * HD, *m_L = m_M + DW * PACK;
+    if (g == 0) {
+        m_M[warp * PACK + 2 * c] = M[0];
+        m_M[warp * PACK + 2 * c + 1] = M[1];
+        m_L[warp * PACK + 2 * c] = lsum[0];
+        m_L[warp * PACK + 2 * c + 1] = lsum[1];
     }
 #pragma unroll
     for (int mt = 0; mt < STEPS; ++mt) {
@@ -577,18 +636,17 @@ __global__ void __launch_bounds__(DW * 32) tq_decode_kernel(const DecodeParams p
         *reinterpret_cast<float2 *>(o1) = make_float2(oacc[mt][1], oacc[mt][3]);
     }
     __syncthreads();
-    // thread -> (row, slice of dims); the result of row rr goes to mbuf[rr] of warp slot 0
+    // thread -> (row, slice of dims)
     constexpr int TPR = DW * 32 / PACK;  // threads per row
     constexpr int DPT = HD / TPR;        // dims per thread
     const int rr = tid / TPR, dsl = (tid % TPR) * DPT;
-    float mstar = -INFINITY;
+    float mstar = -1e30f;
 #pragma unroll
     for (int w = 0; w < DW; ++w) mstar = fmaxf(mstar, m_M[w * PACK + rr]);
     float L = 0.0f, f[DW];
 #pragma unroll
     for (int w = 0; w < DW; ++w) {
-        const float mw = m_M[w * PACK + rr];
-        f[w] = mw == -INFINITY ? 0.0f : fast_exp2(mw - mstar);
+        f[w] = fast_exp2(m_M[w * PACK + rr] - mstar);
         L += f[w] * m_L[w * PACK + rr];
     }
     const float invL = L > 0.0f ? 1.0f / L : 0.0f;

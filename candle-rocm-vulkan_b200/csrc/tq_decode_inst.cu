@@ -10,7 +10,7 @@ namespace b200 {
 
 template <int KM, int VM, int HD>
 int launch_decode(const DecodeParams &p, dim3 grid, size_t smem, cudaStream_t stream) {
-    auto kern = tq_decode_kernel<KM, VM, HD, false>;
+    auto kern = tq_decode_kernel<KM, VM, HD>;
     static thread_local size_t configured[16] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
