@@ -15,6 +15,7 @@ struct DecodePlan {
     uint32_t ny;
     size_t smem;
     size_t off_lse, off_meta, ws_bytes;
+    uint32_t blocks;
     int hd_idx;
 };
 
@@ -59,7 +60,6 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
         return set_error(B200_ERR_BAD_ARG, "tq_attention: %u query heads are not a multiple of %u kv heads", a->hq, a->hkv);
     if (a->d != 64 && a->d != 128 && a->d != 256)
         return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: head dim %u (fused kernel: 64, 128, 256)", a->d);
-    if (a->b > 65535) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: batch %u above 65535", a->b);
     if (a->pages) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: paged rows are not implemented yet");
     DecodeParams &p = pl.p;
     memset(&p, 0, sizeof(p));
@@ -100,51 +100,42 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
     p.alibi_bs = a->alibi_bstride;
     p.status = a->status;
     pl.ny = a->hkv * p.packs;
-    if ((uint64_t)pl.ny > 65535) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: too many row packs");
-
-    // chunk of keys per block: enough blocks for every SM, chunks a multiple of the 128 keys
-    // that the four warps take per round
-    const uint64_t lk = std::max<uint32_t>(a->lk, 1);
-    uint64_t chunk;
-    if (a->splits > 0) {
-        chunk = (lk + a->splits - 1) / a->splits;
-    } else {
-        static const long env_chunk = [] { const char *e = getenv("B200_DECODE_CHUNK"); return e ? atol(e) : 0l; }();
-        if (env_chunk > 0) {
-            chunk = (uint64_t)env_chunk;
-        } else {
-            const uint64_t total = (uint64_t)a->b * pl.ny * lk;
-            chunk = total / ((uint64_t)sm_count_cached() * 16);
-            chunk = std::min<uint64_t>(std::max<uint64_t>(chunk, 128), 4096);
-        }
-    }
-    chunk = (chunk + DW * WK - 1) / (DW * WK) * (DW * WK);
-    p.chunk = (uint32_t)std::min<uint64_t>(chunk, 1u << 30);
-    p.max_splits = (uint32_t)((lk + p.chunk - 1) / p.chunk);
-    if (p.max_splits > 65535) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: too many key chunks");
 
     p.k_stage_bytes = (uint32_t)((WK * p.k_ss * 4 + 16 + 15) / 16 * 16);
     p.v_stage_bytes = (uint32_t)((WK * p.v_ss * 4 + 16 + 15) / 16 * 16);
-    // shared memory: barriers and pair tables, per-warp key metadata, then the stage rings, whose area
-    // also stages the queries before and merges the warps after the key loop
-    const size_t fixed = FIXED_SMEM + (size_t)DW * meta_bytes(a->kq.mode, a->vq.mode, (int)a->d);
-    const size_t merge = (size_t)DW * PACK * a->d * 4 + 2 * DW * PACK * 4;
+    // shared memory: barriers and pair tables, per-warp key metadata, the merge / query staging
+    // buffer, then the stage rings
+    const size_t fixed = FIXED_SMEM + (size_t)DW * meta_bytes(a->kq.mode, a->vq.mode, (int)a->d) + merge_bytes((int)a->d);
     const size_t stage = (size_t)p.k_stage_bytes + p.v_stage_bytes;
     p.ns = NS_MAX;
     static const long env_ns = [] { const char *e = getenv("B200_DECODE_STAGES"); return e ? atol(e) : 0l; }();
     if (env_ns >= 2 && env_ns <= NS_MAX) p.ns = (uint32_t)env_ns;
     // three blocks per SM when the stages allow it, else fewer stages, down to two
-    while (p.ns > 2 && fixed + DW * p.ns * stage > 72 * 1024) --p.ns;
-    p.stages_bytes = (uint32_t)std::max(DW * p.ns * stage, merge);
+    while (p.ns > 2 && fixed + DW * p.ns * stage > 75 * 1024) --p.ns;
+    p.stages_bytes = (uint32_t)(DW * p.ns * stage);
     pl.smem = fixed + p.stages_bytes;
     if (pl.smem > 227 * 1024) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: %zu bytes of shared memory", pl.smem);
 
-    const size_t slots = (size_t)a->b * pl.ny * p.max_splits * PACK;
-    const size_t part_o = p.max_splits > 1 ? slots * a->d * 4 : 0;
-    const size_t part_l = p.max_splits > 1 ? slots * 4 : 0;
+    static const long env_cc = [] { const char *e = getenv("B200_DECODE_COL_COST"); return e ? atol(e) : -1l; }();
+    p.col_cost = env_cc >= 0 ? (uint32_t)env_cc : 4u;
+    // persistent blocks: as many as fit on the device at once, at most one per unit of 128 keys
+    static const long env_bps = [] { const char *e = getenv("B200_DECODE_BLOCKS_PER_SM"); return e ? atol(e) : 0l; }();
+    int bps = (int)std::min<size_t>(3, (227 * 1024) / (pl.smem + 1024));
+    if (env_bps > 0) bps = (int)env_bps;
+    bps = std::max(bps, 1);
+    const uint64_t lk = std::max<uint32_t>(a->lk, 1);
+    const uint64_t max_units = (uint64_t)a->b * pl.ny * ((lk + DW * WK - 1) / (DW * WK));
+    uint64_t nblocks = (uint64_t)sm_count_cached() * bps;
+    if (a->splits > 0) nblocks = std::min<uint64_t>(nblocks, (uint64_t)a->b * pl.ny * a->splits);
+    pl.blocks = (uint32_t)std::max<uint64_t>(std::min(nblocks, max_units), 1);
+
+    const size_t ncols = (size_t)a->b * pl.ny;
+    const size_t slots = ((size_t)pl.blocks + ncols) * PACK;
+    const size_t part_o = slots * a->d * 4;
+    const size_t part_l = slots * 4;
     pl.off_lse = (part_o + 255) / 256 * 256;
     pl.off_meta = (pl.off_lse + part_l + 255) / 256 * 256;
-    pl.ws_bytes = pl.off_meta + (size_t)a->b * pl.ny * 4;
+    pl.ws_bytes = pl.off_meta + ncols * 8;
     pl.hd_idx = a->d == 64 ? 0 : (a->d == 128 ? 1 : 2);
     return B200_OK;
 }
@@ -195,7 +186,7 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
     p.part_o = reinterpret_cast<float *>(ws);
     p.part_lse = reinterpret_cast<float *>(ws + pl.off_lse);
     p.meta = reinterpret_cast<int32_t *>(ws + pl.off_meta);
-    const dim3 grid(p.max_splits, pl.ny, a->b);
+    const dim3 grid(pl.blocks);
     int lrc;
     switch (p.k.mode) {
     case B200_TURBO_MSE: lrc = dispatch_v<B200_TURBO_MSE>(pl, grid, stream); break;
@@ -205,7 +196,7 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
     default: lrc = dispatch_v<B200_FP8_ROW>(pl, grid, stream); break;
     }
     if (lrc) return lrc;
-    if (p.max_splits > 1) {
+    {
         const size_t rows = (size_t)a->b * a->hq * a->lq;
         const unsigned gx = (unsigned)std::min<size_t>((rows + 3) / 4, (size_t)sm_count_cached() * 16);
         if (a->d == 64) tq_combine_kernel<64><<<gx, 128, 0, stream>>>(p);
@@ -213,5 +204,4 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
         else tq_combine_kernel<256><<<gx, 128, 0, stream>>>(p);
         return check_launch("tq_combine");
     }
-    return B200_OK;
 }
