@@ -107,22 +107,42 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
     // buffer, then the stage rings
     const size_t fixed = FIXED_SMEM + (size_t)DW * meta_bytes(a->kq.mode, a->vq.mode, (int)a->d) + merge_bytes((int)a->d);
     const size_t stage = (size_t)p.k_stage_bytes + p.v_stage_bytes;
-    p.ns = NS_MAX;
+    // stages per warp and blocks per SM: as many bytes in flight as possible (a warp computes on one
+    // stage while the others load), more blocks on a tie
     static const long env_ns = [] { const char *e = getenv("B200_DECODE_STAGES"); return e ? atol(e) : 0l; }();
-    if (env_ns >= 2 && env_ns <= NS_MAX) p.ns = (uint32_t)env_ns;
-    // three blocks per SM when the stages allow it, else fewer stages, down to two
-    while (p.ns > 2 && fixed + DW * p.ns * stage > 75 * 1024) --p.ns;
+    static const long env_bps = [] { const char *e = getenv("B200_DECODE_BLOCKS_PER_SM"); return e ? atol(e) : 0l; }();
+    int bps = 1;
+    p.ns = 2;
+    size_t best = 0;
+    for (int ns = 2; ns <= NS_MAX; ++ns) {
+        const size_t sm = fixed + DW * ns * stage;
+        if (sm > 227 * 1024) break;
+        const int fit = (int)std::min<size_t>(3, (228 * 1024) / (sm + 1024));
+        if (fit < 1) break;
+        const size_t flight = (size_t)fit * DW * (ns - 1) * stage;
+        if (flight > best || (flight == best && fit > bps)) {
+            best = flight;
+            p.ns = (uint32_t)ns;
+            bps = fit;
+        }
+    }
+    if (env_ns >= 2 && env_ns <= NS_MAX) {
+        p.ns = (uint32_t)env_ns;
+        bps = (int)std::min<size_t>(3, (228 * 1024) / (fixed + DW * p.ns * stage + 1024));
+    }
+    if (env_bps > 0) bps = (int)env_bps;
+    bps = std::max(bps, 1);
     p.stages_bytes = (uint32_t)(DW * p.ns * stage);
     pl.smem = fixed + p.stages_bytes;
     if (pl.smem > 227 * 1024) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: %zu bytes of shared memory", pl.smem);
+    // rows that certainly exist after the visible ones: the head stride spans them
+    p.rows_cap = 0;
+    if (p.k_ss && p.v_ss && p.k_sh % p.k_ss == 0 && p.v_sh % p.v_ss == 0 && (a->hkv > 1 || a->b > 1))
+        p.rows_cap = (uint32_t)std::min<uint64_t>(std::min(p.k_sh / p.k_ss, p.v_sh / p.v_ss), 0x7fffffffu);
 
     static const long env_cc = [] { const char *e = getenv("B200_DECODE_COL_COST"); return e ? atol(e) : -1l; }();
     p.col_cost = env_cc >= 0 ? (uint32_t)env_cc : 4u;
     // persistent blocks: as many as fit on the device at once, at most one per unit of 128 keys
-    static const long env_bps = [] { const char *e = getenv("B200_DECODE_BLOCKS_PER_SM"); return e ? atol(e) : 0l; }();
-    int bps = (int)std::min<size_t>(3, (227 * 1024) / (pl.smem + 1024));
-    if (env_bps > 0) bps = (int)env_bps;
-    bps = std::max(bps, 1);
     const uint64_t lk = std::max<uint32_t>(a->lk, 1);
     const uint64_t max_units = (uint64_t)a->b * pl.ny * ((lk + DW * WK - 1) / (DW * WK));
     uint64_t nblocks = (uint64_t)sm_count_cached() * bps;

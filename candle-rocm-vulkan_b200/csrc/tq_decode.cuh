@@ -68,6 +68,7 @@ struct DecodeParams {
     int32_t *status;
     uint32_t k_stage_bytes, v_stage_bytes;
     uint32_t ns;       // stages per warp
+    uint32_t rows_cap;      // rows that exist in every (batch, head) slab of both caches (0 = only the visible ones)
     uint32_t col_cost;      // cost of starting a column, in units, for the split of the work between blocks
     uint32_t stages_bytes;  // whole stage area (also holds the query staging and the merge buffers)
 };
@@ -82,7 +83,7 @@ __host__ __device__ constexpr int meta_bytes(int km, int vm, int hd) {
     return WK * (kmeta_words(km, hd) * 4 + 8 + vsc_blocks(vm, hd) * 2);
 }
 constexpr int FIXED_SMEM = 128 + 2048;  // barriers, pair tables
-__host__ __device__ constexpr int merge_bytes(int hd) { return DW * PACK * hd * 4 + 2 * DW * PACK * 4; }
+__host__ __device__ constexpr int merge_bytes(int hd) { return 2 * PACK * hd * 4 + 2 * DW * PACK * 4; }
 
 __device__ __forceinline__ uint32_t lds32(uint32_t a) {
     uint32_t v;
@@ -171,7 +172,7 @@ __device__ __forceinline__ void warp_hadamard(float *row, int n, const float *si
 
 // One column = the keys of one (batch entry, kv head, pack of query rows). Its visible keys
 // [lo, hi) are cut into units of DW * WK keys; the units of all columns, in (batch, column, unit)
-// order, form the work list that the persistent blocks share evenly.
+// order, form the work list that the persistent blocks share.
 struct Column {
     int lo, hi, lk, units;
 };
@@ -191,9 +192,37 @@ __device__ __forceinline__ Column make_column(const DecodeParams &p, uint32_t b)
     return c;
 }
 
-// block that owns unit u when `total` units are shared by `nc` blocks (block i starts at floor(i total / nc))
-__device__ __forceinline__ uint32_t owner_of_unit(uint64_t u, uint64_t total, uint32_t nc) {
-    return (uint32_t)(((u + 1) * nc - 1) / total);
+// block that owns cost position x when `total` is shared by `nc` blocks (block i starts at floor(i total / nc))
+__device__ __forceinline__ uint32_t owner_of_unit(uint64_t x, uint64_t total, uint32_t nc) {
+    return (uint32_t)(((x + 1) * nc - 1) / total);
+}
+
+// A block's share of the work is a list of segments: units [t0, t1) of column y of batch entry b.
+// Cost space: every column takes col_cost (its set up and merge) plus one per unit, laid out in
+// (batch, column) order; block i takes the units whose cost position lies in
+// [i total / nc, (i + 1) total / nc). Columns without units cost nothing.
+struct Segment {
+    uint32_t b, y, t0, t1;
+    uint64_t x;  // cost position of unit t0
+    Column col;
+};
+
+// next segment of the share that ends at x_end; false when the share is exhausted
+__device__ __forceinline__ bool next_segment(Segment &s, const DecodeParams &p, uint32_t ny, uint64_t x_end) {
+    if (s.t1 < (uint32_t)s.col.units) return false;  // the share ended inside the column
+    const uint64_t x = s.x + (s.t1 - s.t0) + p.col_cost;
+    if (x >= x_end) return false;
+    if (++s.y == ny) {
+        s.y = 0;
+        do {
+            if (++s.b >= p.b) return false;
+            s.col = make_column(p, s.b);
+        } while (s.col.units == 0);
+    }
+    s.x = x;
+    s.t0 = 0;
+    s.t1 = (uint32_t)min((uint64_t)s.col.units, x_end - x);
+    return true;
 }
 
 template <int KM, int VM, int HD>
@@ -211,7 +240,8 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
     const int NS = (int)p.ns;
     const uint32_t sbase = smem_u32(smem);
     const uint32_t lut_k = sbase + 128, lut_v = lut_k + 1024;
-    float *mbuf = reinterpret_cast<float *>(smem + FIXED_SMEM + DW * META);  // [DW][PACK][HD], M and L [DW][PACK]; also the query staging
+    float *mbuf = reinterpret_cast<float *>(smem + FIXED_SMEM + DW * META);  // 2 x [PACK][HD], then M and L [DW][PACK]; also the query staging
+    float *m_M = mbuf + 2 * PACK * HD, *m_L = m_M + DW * PACK;
     uint8_t *stages = reinterpret_cast<uint8_t *>(mbuf) + merge_bytes(HD);
     const uint32_t stage_bytes = p.k_stage_bytes + p.v_stage_bytes;
 
@@ -219,9 +249,6 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
     const uint32_t G = p.group, R = p.rows_per_kv, ny = p.hkv * p.packs, nc = gridDim.x;
 
     // ------------------------------------------------------------------ this block's share of the work
-    // Cost space: every column takes col_cost (its set up and merge) plus one per unit, laid out in
-    // (batch, column) order; block i takes the units whose cost position lies in
-    // [i total / nc, (i + 1) total / nc). Columns without units cost nothing.
     const uint32_t cc = p.col_cost;
     auto batch_cost = [&](uint32_t bb) -> uint32_t {
         const uint32_t t = (uint32_t)make_column(p, bb).units;
@@ -269,19 +296,21 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
             carry += __shfl_sync(0xffffffffu, incl, 31);
         }
     }
-    // first unit at or after x_begin: column y0 of b0, unit t0 (a position inside a column's set up
-    // cost snaps to its first unit). col_x = cost position of the column's first unit.
-    uint32_t y0, t0;
-    uint64_t col_x;
+    // first segment: the first unit at or after x_begin (a position inside a column's set up cost
+    // snaps to the column's first unit)
+    Segment seg0;
     {
-        const uint32_t tb = (uint32_t)make_column(p, b0).units;
+        seg0.b = b0;
+        seg0.col = make_column(p, b0);
+        const uint32_t tb = (uint32_t)seg0.col.units;
         const uint64_t rem = x_begin - b0_start;
-        y0 = (uint32_t)(rem / (tb + cc));
+        seg0.y = (uint32_t)(rem / (tb + cc));
         const uint32_t in_col = (uint32_t)(rem % (tb + cc));
-        t0 = in_col > cc ? in_col - cc : 0u;
-        col_x = b0_start + (uint64_t)y0 * (tb + cc) + cc;
+        seg0.t0 = in_col > cc ? in_col - cc : 0u;
+        seg0.x = b0_start + (uint64_t)seg0.y * (tb + cc) + cc + seg0.t0;
+        if (seg0.x >= x_end) return;  // the share lies inside a set up gap: no unit
+        seg0.t1 = (uint32_t)min((uint64_t)tb, seg0.t0 + (x_end - seg0.x));
     }
-    if (col_x + t0 >= x_end) return;  // the share lies inside a set up gap: no unit
 
     // ------------------------------------------------------------------ one time set up
     if (tid == 0) {
@@ -295,9 +324,8 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
     __syncthreads();
 
     const uint32_t krb = (uint32_t)p.k_ss * 4u, vrb = (uint32_t)p.v_ss * 4u;  // row bytes
-    uint8_t *wstage = stages + (size_t)warp * NS * stage_bytes;
-    const uint32_t wstage_s = smem_u32(wstage);
-    uint64_t *wbar = bars + warp * NS_MAX;
+    const uint32_t wstage_s = smem_u32(stages + (size_t)warp * NS * stage_bytes);
+    const uint32_t wbar_s = smem_u32(bars + warp * NS_MAX);
     const uint32_t meta_s = sbase + FIXED_SMEM + warp * META;    // [WK][KMW] f32
     const uint32_t vmeta_s = meta_s + WK * KMW * 4;              // [WK] (sigma, log2 sigma)
     const uint32_t vsc_s = vmeta_s + WK * 8;                     // [NBV][WK] f16
@@ -306,107 +334,104 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
     const bool plain = p.softcap <= 0.0f && p.alibi == nullptr;  // tiles inside every row's range take the unmasked path
     bool wait_failed = false;
 
-    // ------------------------------------------------------------------ the copy side runs NS tiles ahead
-    // position of the next tile to copy: batch entry, column, unit, and the column's geometry
-    uint32_t ib = b0;
-    Column icol = make_column(p, ib);
-    uint32_t iy = y0, it = t0;
-    uint64_t ix = col_x + t0;  // cost position of the unit at the copy position
-    int isidx = 0;
-    // byte addresses of row 0 of the column at the copy position (its kv head: iy / packs)
-    uintptr_t ik = reinterpret_cast<uintptr_t>(p.k_rows + (size_t)ib * p.k_sb + (size_t)(iy / p.packs) * p.k_sh);
-    uintptr_t iv = reinterpret_cast<uintptr_t>(p.v_rows + (size_t)ib * p.v_sb + (size_t)(iy / p.packs) * p.v_sh);
-    uint32_t ipack = iy % p.packs;
-    // copies this warp's tile of the unit at the copy position (nothing when the tile is empty) and advances
-    auto issue_next = [&]() {
-        const int key0 = icol.lo + (int)it * UNIT + warp * WK;
-        const int nkeys = min(WK, icol.hi - key0);
-        if (nkeys > 0) {
-            uint8_t *st = wstage + (size_t)isidx * stage_bytes;
-            const uintptr_t ka = ik + (uint32_t)key0 * (uint64_t)krb;
-            const uintptr_t va = iv + (uint32_t)key0 * (uint64_t)vrb;
-            const uintptr_t ka0 = ka & ~(uintptr_t)15, va0 = va & ~(uintptr_t)15;
-            const uintptr_t ke = ka + (uintptr_t)nkeys * krb, ve = va + (uintptr_t)nkeys * vrb;
-            // Rows below lk are readable, so the 16-byte round up of a copy may run into the next
-            // row. Only the last tile of a sequence copies the round down and fetches the few
-            // remaining words with plain loads.
-            const bool last = key0 + nkeys >= icol.lk;
-            const uintptr_t ke1 = last ? (ke & ~(uintptr_t)15) : ((ke + 15) & ~(uintptr_t)15);
-            const uintptr_t ve1 = last ? (ve & ~(uintptr_t)15) : ((ve + 15) & ~(uintptr_t)15);
-            const uint32_t kb = ke1 > ka0 ? (uint32_t)(ke1 - ka0) : 0u, vb = ve1 > va0 ? (uint32_t)(ve1 - va0) : 0u;
-            if (last) {
-                if (lane < 4) {
-                    const uintptr_t a = ke1 + 4u * lane;
-                    if (a >= ka && a < ke) *reinterpret_cast<uint32_t *>(st + (a - ka0)) = *reinterpret_cast<const uint32_t *>(a);
-                } else if (lane < 8) {
-                    const uintptr_t a = ve1 + 4u * (lane - 4);
-                    if (a >= va && a < ve)
-                        *reinterpret_cast<uint32_t *>(st + p.k_stage_bytes + (a - va0)) = *reinterpret_cast<const uint32_t *>(a);
-                }
-                __syncwarp();
+    // this warp's tiles of a segment: tile t of the column holds the keys lo + t UNIT + warp WK ...
+    auto warp_tiles = [&](const Segment &s) -> int {
+        const int span = s.col.hi - s.col.lo - warp * WK;
+        const int tw = span > 0 ? (span + UNIT - 1) / UNIT : 0;  // tiles of this warp in the column
+        return max(min((int)s.t1, tw) - (int)s.t0, 0);
+    };
+
+    // ------------------------------------------------------------------ the copy side
+    // runs up to NS tiles ahead of the compute side through the same list of segments
+    Segment iseg = seg0;
+    int i_left = 0;          // tiles of this warp still to copy in the copy side's segment
+    bool i_more = true;      // the copy side has segments left
+    uintptr_t i_k = 0, i_v = 0;        // 16-byte aligned global addresses of the next tile's copies
+    uint32_t i_koff = 0, i_voff = 0;   // offset of the tile's first row inside its copy
+    int i_key = 0;                     // first key of the next tile
+    uint32_t i_st = wstage_s, i_bar = wbar_s;  // stage and barrier of the next copy
+    int i_stage = 0;
+    auto copy_enter = [&]() {  // per-segment constants of the copy side
+        i_left = warp_tiles(iseg);
+        const uint32_t hk = iseg.y / p.packs;
+        i_key = iseg.col.lo + (int)iseg.t0 * UNIT + warp * WK;
+        const uintptr_t ka = reinterpret_cast<uintptr_t>(p.k_rows + (size_t)iseg.b * p.k_sb + (size_t)hk * p.k_sh) + (uintptr_t)(uint32_t)i_key * krb;
+        const uintptr_t va = reinterpret_cast<uintptr_t>(p.v_rows + (size_t)iseg.b * p.v_sb + (size_t)hk * p.v_sh) + (uintptr_t)(uint32_t)i_key * vrb;
+        i_koff = (uint32_t)(ka & 15u);
+        i_voff = (uint32_t)(va & 15u);
+        i_k = ka - i_koff;
+        i_v = va - i_voff;
+    };
+    copy_enter();
+    while (i_left == 0 && i_more) {
+        i_more = next_segment(iseg, p, ny, x_end);
+        if (i_more) copy_enter();
+    }
+    // copies the next tile of this warp (the caller checked i_left > 0) and moves on
+    auto copy_tile = [&]() {
+        const int nkeys = min(WK, iseg.col.hi - i_key);
+        // Rows below lk are readable, and so is the row after a tile when the cache has spare rows
+        // (rows_cap): the 16-byte round up of a copy may then run into the next row. Otherwise the
+        // last tile of a sequence copies the round down and fetches the few remaining words with
+        // plain loads.
+        const bool tail = i_key + nkeys >= iseg.col.lk && i_key + nkeys >= (int)p.rows_cap;
+        uint32_t kb = (i_koff + (uint32_t)nkeys * krb + 15u) & ~15u, vb = (i_voff + (uint32_t)nkeys * vrb + 15u) & ~15u;
+        if (tail) {
+            const uint32_t ke = i_koff + (uint32_t)nkeys * krb, ve = i_voff + (uint32_t)nkeys * vrb;  // ends, from the copy start
+            kb = ke & ~15u;
+            vb = ve & ~15u;
+            if (lane < 4) {
+                const uint32_t o = kb + 4u * lane;
+                if (o >= i_koff && o < ke) sts32(i_st + o, *reinterpret_cast<const uint32_t *>(i_k + o));
+            } else if (lane < 8) {
+                const uint32_t o = vb + 4u * (lane - 4);
+                if (o >= i_voff && o < ve) sts32(i_st + p.k_stage_bytes + o, *reinterpret_cast<const uint32_t *>(i_v + o));
             }
-            if (lane == 0) {
-                mbar_expect_tx(&wbar[isidx], kb + vb);
-                if (kb) bulk_g2s(st, reinterpret_cast<const void *>(ka0), kb, &wbar[isidx]);
-                if (vb) bulk_g2s(st + p.k_stage_bytes, reinterpret_cast<const void *>(va0), vb, &wbar[isidx]);
-            }
-            if (++isidx == NS) isidx = 0;
+            __syncwarp();
         }
-        ++ix;
-        if (++it == (uint32_t)icol.units) {
-            it = 0;
-            ix += cc;
-            ++iy;
-            if (++ipack == p.packs) {  // next kv head
-                ipack = 0;
-                ik += (uintptr_t)p.k_sh * 4u;
-                iv += (uintptr_t)p.v_sh * 4u;
-            }
-            if (iy == ny) {
-                iy = 0;
-                do {
-                    ++ib;
-                    if (ib < p.b) icol = make_column(p, ib);
-                } while (ib < p.b && icol.units == 0);
-                if (ib >= p.b) ix = x_end;
-                ik = reinterpret_cast<uintptr_t>(p.k_rows + (size_t)ib * p.k_sb);
-                iv = reinterpret_cast<uintptr_t>(p.v_rows + (size_t)ib * p.v_sb);
-            }
+        if (lane == 0) {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(i_bar), "r"(kb + vb) : "memory");
+            if (kb)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(i_st),
+                             "l"(i_k), "r"(kb), "r"(i_bar)
+                             : "memory");
+            if (vb)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 i_st + p.k_stage_bytes),
+                             "l"(i_v), "r"(vb), "r"(i_bar)
+                             : "memory");
+        }
+        // UNIT rows are a multiple of 16 bytes: the next tile keeps its offset inside its copy
+        i_k += (uintptr_t)UNIT * krb;
+        i_v += (uintptr_t)UNIT * vrb;
+        i_key += UNIT;
+        i_st += stage_bytes;
+        i_bar += 8;
+        if (++i_stage == NS) {
+            i_stage = 0;
+            i_st = wstage_s;
+            i_bar = wbar_s;
+        }
+        --i_left;
+        while (i_left == 0 && i_more) {
+            i_more = next_segment(iseg, p, ny, x_end);
+            if (i_more) copy_enter();
         }
     };
-    // tiles in flight are counted per warp: empty tiles take no stage
-    int inflight = 0;
-    while (ix < x_end && inflight < NS) {
-        const int key0 = icol.lo + (int)it * UNIT + warp * WK;
-        if (key0 < icol.hi) ++inflight;
-        issue_next();
-    }
+    for (int n = 0; n < NS && i_left > 0; ++n) copy_tile();
 
     // ------------------------------------------------------------------ the compute side
-    uint32_t cb = b0;
-    Column ccol = make_column(p, cb);
-    uint32_t cy = y0, ct = t0;
-    int sidx = 0;
-    uint32_t phases = 0;  // bit s: parity to wait for on stage s
-    uint32_t hk = cy / p.packs, pack = cy % p.packs;
-    // low address bits of row 0 of the column (the offset of a tile inside its 16-byte aligned copy)
-    uint32_t ck16 = 0, cv16 = 0;
-
     // lane offsets inside a tile: K rows g (and g + 8), V rows 2c (and 2c + 1, 2c + 8, 2c + 9)
     const uint32_t k_lane = g * krb + (KMX ? (K4 ? 4u * c : 8u * c) : (K4 ? c * (HD / 8) : c * (HD / 4)));
     const uint32_t v_lane = 2 * c * vrb + (V4 ? g * (HD / 16) : g * (HD / 8));
     const uint32_t mrow_g = meta_s + g * KMW * 4, vmeta_g = vmeta_s + g * 8, vsc_c = vsc_s + 4 * c;
+    uint32_t c_st = wstage_s, c_bar = wbar_s;
+    int c_stage = 0;
+    uint32_t phases = 0;  // bit s: parity to wait for on stage s
 
-    // per column: query fragments, row ranges, softmax state
     uint32_t qb0[STEPS], qb1[STEPS];
     float qs[2], qs2[2];
-    int r_lo[2], r_hi[2], r_pos[2];
-    float r_slope[2];
-    int LOmax = 0, HImin = 0;
-    float M[2], lsum[2];
     float oacc[STEPS][4];
-    uint32_t seg_first_unit = 0;  // unit (inside the column) at which this block's segment of the column starts
-    bool fresh = true;            // the next unit starts a segment
 
     // scores of keys g and g + 8 of the 16 keys at `ka` against the rows 2c, 2c + 1:
     // sr[2 k + e] = key g + 8 k, row 2c + e
@@ -548,105 +573,118 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
     };
 
 
-    for (uint64_t x = col_x + t0; x < x_end; ++x) {
-        if (fresh) {
-            fresh = false;
-            seg_first_unit = ct;
-            ck16 = (uint32_t)(reinterpret_cast<uintptr_t>(p.k_rows + (size_t)cb * p.k_sb + (size_t)hk * p.k_sh) & 15u);
-            cv16 = (uint32_t)(reinterpret_cast<uintptr_t>(p.v_rows + (size_t)cb * p.v_sb + (size_t)hk * p.v_sh) & 15u);
-            // ---- segment prologue: row ranges of the two query rows whose scores this lane holds
-            auto row_range = [&](uint32_t r, int &lo, int &hi, int &pos) {
-                const long long i = r / G;
-                const long long ps = i + (long long)ccol.lk - (long long)p.lq;
-                long long l = p.wl >= 0 ? max(ps - p.wl, 0ll) : 0ll;
-                long long h = p.wr >= 0 ? min(ps + p.wr + 1, (long long)ccol.lk) : (long long)ccol.lk;
-                l = min(l, (long long)ccol.lk);
-                h = max(h, l);
-                lo = (int)l;
-                hi = (int)h;
-                pos = (int)max(min(ps, 2147483647ll), -2147483647ll);
-            };
-            LOmax = 0;
-            HImin = ccol.lk;
-            {   // rows are ordered by token: the first valid row has the lowest, the last the highest range
-                int lo, hi, pos;
-                const uint32_t rfirst = pack * PACK, rlast = min(pack * PACK + PACK, R) - 1;
-                row_range(rlast, lo, hi, pos);
-                LOmax = lo;
-                row_range(rfirst, lo, hi, pos);
-                HImin = hi;
-            }
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const uint32_t r = pack * PACK + 2 * c + e;
-                r_lo[e] = r_hi[e] = r_pos[e] = 0;
-                r_slope[e] = 0.0f;
-                if (r < R) {
-                    row_range(r, r_lo[e], r_hi[e], r_pos[e]);
-                    if (p.alibi) r_slope[e] = p.alibi[(size_t)cb * p.alibi_bs + hk * G + r % G];
-                }
-            }
-            // queries -> f32 rows in shared memory (rows of the pack; missing rows are zero)
-            float *qbuf = mbuf;  // [PACK][HD]
-            __syncthreads();     // the previous segment's merge is done with the buffer
-            for (int idx = tid; idx < PACK * HD; idx += DW * 32) {
-                const uint32_t rr = idx / HD, dd = idx % HD;
-                const uint32_t r = pack * PACK + rr;
-                float v = 0.0f;
-                if (r < R) {
-                    const uint32_t i = r / G, h = hk * G + r % G;
-                    v = load_elem_rt(p.q, cb * p.q_sb + h * p.q_sh + i * p.q_ss + dd, p.q_dtype);
-                }
-                qbuf[idx] = v;
-            }
-            __syncthreads();
-            if (p.k.rot == B200_ROT_HADAMARD) {
-                for (int rr = warp; rr < PACK; rr += DW) warp_hadamard(qbuf + rr * HD, HD, p.k.signs, true, lane);
-                __syncthreads();
-            }
-            // power of two normalization of row g, then the f16 B fragments of K Q^T: per k-step the four
-            // contraction slots of this lane are the consecutive dims dbase(s) ... dbase(s) + 3
-            {
-                const float *qr = qbuf + g * HD;
-                float am = 0.0f;
-                for (int dd = c; dd < HD; dd += 4) am = fmaxf(am, fabsf(qr[dd]));
-                am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
-                am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
-                int e = 0;
-                if (am > 0.0f && am < INFINITY) e = (int)((f2u(am) >> 23) & 0xffu) - 127 - 7;
-                e = max(min(e, 100), -100);
-                const float down = u2f((uint32_t)(127 - e) << 23), up = u2f((uint32_t)(127 + e) << 23);
-                const float qscale = p.scale * up;
-                qs[0] = __shfl_sync(0xffffffffu, qscale, (2 * c) * 4);
-                qs[1] = __shfl_sync(0xffffffffu, qscale, (2 * c + 1) * 4);
-                qs2[0] = qs[0] * LOG2E;
-                qs2[1] = qs[1] * LOG2E;
-#pragma unroll
-                for (int s = 0; s < STEPS; ++s) {
-                    const int dbase = KMX ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : c * (HD / 4) + 4 * s;
-                    const float *q4 = qr + dbase;
-                    qb0[s] = pack_f16x2(q4[0] * down, q4[1] * down);
-                    qb1[s] = pack_f16x2(q4[2] * down, q4[3] * down);
-                }
-            }
-            M[0] = M[1] = -1e30f;
-            lsum[0] = lsum[1] = 0.0f;
-#pragma unroll
-            for (int mt = 0; mt < STEPS; ++mt) oacc[mt][0] = oacc[mt][1] = oacc[mt][2] = oacc[mt][3] = 0.0f;
-            __syncthreads();  // the staging buffer becomes the merge buffer again
-        }
 
-        // ---- this warp's tile of the unit
-        const int key0 = ccol.lo + (int)ct * UNIT + warp * WK;
-        const int nkeys = min(WK, ccol.hi - key0);
-        if (nkeys > 0 && !wait_failed) {
-            if (!mbar_wait_bounded(&wbar[sidx], (phases >> sidx) & 1u)) wait_failed = true;
-            phases ^= 1u << sidx;
+    Segment seg = seg0;
+    bool more = true;
+    while (more) {
+        // ================================================================ segment set up
+        const uint32_t hk = seg.y / p.packs, pack = seg.y % p.packs;
+        const Column &col = seg.col;
+        auto row_range = [&](uint32_t r, int &lo, int &hi, int &pos) {
+            const long long i = p.lq == 1 ? 0 : r / G;
+            const long long ps = i + (long long)col.lk - (long long)p.lq;
+            long long l = p.wl >= 0 ? max(ps - p.wl, 0ll) : 0ll;
+            long long h = p.wr >= 0 ? min(ps + p.wr + 1, (long long)col.lk) : (long long)col.lk;
+            l = min(l, (long long)col.lk);
+            h = max(h, l);
+            lo = (int)l;
+            hi = (int)h;
+            pos = (int)max(min(ps, 2147483647ll), -2147483647ll);
+        };
+        // rows are ordered by token: the last row of the pack has the highest lower bound, the first the lowest upper bound
+        int LOmax, HImin;
+        {
+            int lo, hi, pos;
+            row_range(min(pack * PACK + PACK, R) - 1, lo, hi, pos);
+            LOmax = lo;
+            row_range(pack * PACK, lo, hi, pos);
+            HImin = hi;
         }
-        if (nkeys > 0 && !wait_failed) {
-            const uint32_t st_s = wstage_s + (uint32_t)sidx * stage_bytes;
-            const uint32_t koff = (ck16 + (uint32_t)key0 * krb) & 15u, voff = (cv16 + (uint32_t)key0 * vrb) & 15u;
-            const uint32_t kt_off = koff + k_lane, vt_off = p.k_stage_bytes + voff + v_lane;
+        // the two query rows whose scores this lane holds (columns 2c, 2c + 1 of the score fragments)
+        int r_lo[2], r_hi[2], r_pos[2];
+        float r_slope[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const uint32_t r = pack * PACK + 2 * c + e;
+            r_lo[e] = r_hi[e] = r_pos[e] = 0;
+            r_slope[e] = 0.0f;
+            if (r < R) {
+                row_range(r, r_lo[e], r_hi[e], r_pos[e]);
+                if (p.alibi) r_slope[e] = p.alibi[(size_t)seg.b * p.alibi_bs + hk * G + (p.lq == 1 ? r : r % G)];
+            }
+        }
+        // queries -> f32 rows in shared memory (rows of the pack; missing rows are zero)
+        float *qbuf = mbuf;  // [PACK][HD]
+        __syncthreads();     // the previous segment's merge is done with the buffer
+        for (int idx = tid; idx < PACK * HD; idx += DW * 32) {
+            const uint32_t rr = idx / HD, dd = idx % HD;
+            const uint32_t r = pack * PACK + rr;
+            float v = 0.0f;
+            if (r < R) {
+                const uint32_t i = p.lq == 1 ? 0u : r / G, h = hk * G + (p.lq == 1 ? r : r % G);
+                v = load_elem_rt(p.q, seg.b * p.q_sb + h * p.q_sh + i * p.q_ss + dd, p.q_dtype);
+            }
+            qbuf[idx] = v;
+        }
+        __syncthreads();
+        if (p.k.rot == B200_ROT_HADAMARD) {
+            for (int rr = warp; rr < PACK; rr += DW) warp_hadamard(qbuf + rr * HD, HD, p.k.signs, true, lane);
+            __syncthreads();
+        }
+        // power of two normalization of row g, then the f16 B fragments of K Q^T: per k-step the four
+        // contraction slots of this lane are the consecutive dims dbase(s) ... dbase(s) + 3
+        {
+            const float *qr = qbuf + g * HD;
+            float am = 0.0f;
+            for (int dd = c; dd < HD; dd += 4) am = fmaxf(am, fabsf(qr[dd]));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+            int e = 0;
+            if (am > 0.0f && am < INFINITY) e = (int)((f2u(am) >> 23) & 0xffu) - 127 - 7;
+            e = max(min(e, 100), -100);
+            const float down = u2f((uint32_t)(127 - e) << 23), up = u2f((uint32_t)(127 + e) << 23);
+            const float qscale = p.scale * up;
+            qs[0] = __shfl_sync(0xffffffffu, qscale, (2 * c) * 4);
+            qs[1] = __shfl_sync(0xffffffffu, qscale, (2 * c + 1) * 4);
+            qs2[0] = qs[0] * LOG2E;
+            qs2[1] = qs[1] * LOG2E;
+#pragma unroll
+            for (int s = 0; s < STEPS; ++s) {
+                const int dbase = KMX ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : c * (HD / 4) + 4 * s;
+                const float *q4 = qr + dbase;
+                qb0[s] = pack_f16x2(q4[0] * down, q4[1] * down);
+                qb1[s] = pack_f16x2(q4[2] * down, q4[3] * down);
+            }
+        }
+        // running maxima (log2 domain, value scale folded in) and partial normalizers of rows 2c, 2c + 1
+        float M[2] = {-1e30f, -1e30f}, lsum[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int mt = 0; mt < STEPS; ++mt) oacc[mt][0] = oacc[mt][1] = oacc[mt][2] = oacc[mt][3] = 0.0f;
+
+        // ================================================================ this warp's tiles of the segment
+        const int n_w = warp_tiles(seg);
+        int key0 = col.lo + (int)seg.t0 * UNIT + warp * WK;
+        const uint32_t koff = (uint32_t)((reinterpret_cast<uintptr_t>(p.k_rows + (size_t)seg.b * p.k_sb + (size_t)hk * p.k_sh) + (uintptr_t)(uint32_t)key0 * krb) & 15u);
+        const uint32_t voff = (uint32_t)((reinterpret_cast<uintptr_t>(p.v_rows + (size_t)seg.b * p.v_sb + (size_t)hk * p.v_sh) + (uintptr_t)(uint32_t)key0 * vrb) & 15u);
+        const uint32_t kt_off = koff + k_lane, vt_off = p.k_stage_bytes + voff + v_lane;
+        const uint32_t kr_off = koff + lane * krb, vr_off = p.k_stage_bytes + voff + lane * vrb;
+        for (int n = 0; n < n_w && !wait_failed; ++n, key0 += UNIT) {
+            {
+                const uint32_t par = (phases >> c_stage) & 1u;
+                uint32_t ok = 0;
+                for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin)
+                    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                                 : "=r"(ok)
+                                 : "r"(c_bar), "r"(par)
+                                 : "memory");
+                if (!ok) {
+                    wait_failed = true;
+                    break;
+                }
+                phases ^= 1u << c_stage;
+            }
+            const uint32_t st_s = c_st;
+            const int nkeys = min(WK, col.hi - key0);
             if (nkeys < WK) {
                 // rows past the column hold stale bytes: clear them so that masked keys decode to finite values
                 const uint32_t kt = st_s + koff, vt = st_s + p.k_stage_bytes + voff;
@@ -654,228 +692,221 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
                 for (uint32_t w = nkeys * (vrb >> 2) + lane; w < WK * (vrb >> 2); w += 32) sts32(vt + 4 * w, 0u);
                 __syncwarp();
             }
-        // ---- per-key scalars of the tile, lane = key
-        {
-            const uint32_t kr = st_s + koff + lane * krb, vr = st_s + p.k_stage_bytes + voff + lane * vrb;
-            const float k0 = u2f(lds32(kr + k_rsc4));
-            if constexpr (KMX) {
+            // ---- per-key scalars of the tile, lane = key
+            {
+                const uint32_t kr = st_s + kr_off, vr = st_s + vr_off;
+                const float k0 = u2f(lds32(kr + k_rsc4));
+                if constexpr (KMX) {
 #pragma unroll
-                for (int w = 0; w < (NBK + 3) / 4; ++w) {
-                    const uint32_t aux = lds32(kr + k_cw4 + 4 * w);
+                    for (int w = 0; w < (NBK + 3) / 4; ++w) {
+                        const uint32_t aux = lds32(kr + k_cw4 + 4 * w);
+                        // rsc0 * 2^(e - 127); a zero code gives +0 (its block holds zero codes)
 #pragma unroll
-                    for (int i = 0; i < 4 && 4 * w + i < KMW; ++i) {
-                        const uint32_t e = (aux >> (8 * i)) & 0xffu;
-                        sts32(meta_s + (lane * KMW + 4 * w + i) * 4, f2u(e ? k0 * u2f(e << 23) : 0.0f));
+                        for (int i = 0; i < 4 && 4 * w + i < KMW; ++i)
+                            sts32(meta_s + (lane * KMW + 4 * w + i) * 4, f2u(k0 * u2f(((aux >> (8 * i)) & 0xffu) << 23)));
+                    }
+                } else {
+                    sts32(meta_s + lane * 4, f2u(k0));
+                }
+                float sigma = u2f(lds32(vr + v_rsc4));
+                if constexpr (fmt_is_mx(VM)) {
+                    uint32_t aux[(NBV + 3) / 4];
+                    uint32_t em = 0;
+#pragma unroll
+                    for (int w = 0; w < (NBV + 3) / 4; ++w) {
+                        aux[w] = lds32(vr + v_cw4 + 4 * w);
+                        em = w == 0 ? aux[w] : __vmaxu4(em, aux[w]);
+                    }
+                    const uint32_t emax = max_byte(em);
+                    sigma *= u2f(emax << 23);
+#pragma unroll
+                    for (int bk = 0; bk < NBV; ++bk) {
+                        const int e = (int)((aux[bk >> 2] >> (8 * (bk & 3))) & 0xffu);
+                        sts16(vsc_s + (bk * WK + lane) * 2, pow2_f16(e - (int)emax));
+                    }
+                } else if constexpr (VM == B200_NVFP4) {
+#pragma unroll
+                    for (int w = 0; w < NBV / 4; ++w) {
+                        const uint32_t aux = lds32(vr + v_cw4 + 4 * w);
+                        const uint32_t lo = cvt_e4m3x2_f16x2(aux), hi = cvt_e4m3x2_hi_f16x2(aux);
+                        sts16(vsc_s + ((4 * w) * WK + lane) * 2, lo & 0xffffu);
+                        sts16(vsc_s + ((4 * w + 1) * WK + lane) * 2, lo >> 16);
+                        sts16(vsc_s + ((4 * w + 2) * WK + lane) * 2, hi & 0xffffu);
+                        sts16(vsc_s + ((4 * w + 3) * WK + lane) * 2, hi >> 16);
                     }
                 }
+                // sigma in [2^-100, 2^100], or 0 (then log2 = -inf: the key only counts in the normalizer)
+                float sc = fminf(fmaxf(sigma, 7.8886091e-31f), 1.2676506e30f);
+                sc = sigma > 0.0f ? sc : 0.0f;
+                sts32(vmeta_s + lane * 8, f2u(sc));
+                sts32(vmeta_s + lane * 8 + 4, f2u(fast_log2(sc)));
+                __syncwarp();
+            }
+            // ---- scores of the 32 keys: sr[u][2 k + e] = key 16 u + g + 8 k, row 2c + e
+            float sr[2][4];
+            k_scores(st_s + kt_off, mrow_g, sr[0]);
+            k_scores(st_s + kt_off + 16 * krb, mrow_g + 16 * KMW * 4, sr[1]);
+            // ---- online softmax
+            float2 vm[4];  // (sigma, log2 sigma) of the keys g, g + 8, g + 16, g + 24
+#pragma unroll
+            for (int k = 0; k < 4; ++k) vm[k] = lds64f(vmeta_g + k * 64);
+            float s2[8];  // s2[2 k + e]
+            if (plain && nkeys == WK && key0 >= LOmax && key0 + WK <= HImin) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s2[i] = sr[i >> 2][i & 3] * qs2[i & 1];
             } else {
-                sts32(meta_s + lane * 4, f2u(k0));
-            }
-            const float v0 = u2f(lds32(vr + v_rsc4));
-            float sigma = v0;
-            if constexpr (fmt_is_mx(VM)) {
-                uint32_t aux[(NBV + 3) / 4];
-                uint32_t em = 0;
 #pragma unroll
-                for (int w = 0; w < (NBV + 3) / 4; ++w) {
-                    aux[w] = lds32(vr + v_cw4 + 4 * w);
-                    em = w == 0 ? aux[w] : __vmaxu4(em, aux[w]);
-                }
-                const uint32_t emax = max_byte(em);
-                sigma = emax ? v0 * u2f(emax << 23) : 0.0f;
-#pragma unroll
-                for (int bk = 0; bk < NBV; ++bk) {
-                    const int e = (int)((aux[bk >> 2] >> (8 * (bk & 3))) & 0xffu);
-                    sts16(vsc_s + (bk * WK + lane) * 2, pow2_f16(e - (int)emax));
-                }
-            } else if constexpr (VM == B200_NVFP4) {
-#pragma unroll
-                for (int w = 0; w < NBV / 4; ++w) {
-                    const uint32_t aux = lds32(vr + v_cw4 + 4 * w);
-                    const uint32_t lo = cvt_e4m3x2_f16x2(aux), hi = cvt_e4m3x2_hi_f16x2(aux);
-                    sts16(vsc_s + ((4 * w) * WK + lane) * 2, lo & 0xffffu);
-                    sts16(vsc_s + ((4 * w + 1) * WK + lane) * 2, lo >> 16);
-                    sts16(vsc_s + ((4 * w + 2) * WK + lane) * 2, hi & 0xffffu);
-                    sts16(vsc_s + ((4 * w + 3) * WK + lane) * 2, hi >> 16);
+                for (int i = 0; i < 8; ++i) {
+                    const int e = i & 1, j = key0 + g + 8 * (i >> 1);
+                    float sx = sr[i >> 2][i & 3] * qs[e];
+                    if (p.softcap > 0.0f) sx = p.softcap * tanhf(sx / p.softcap);
+                    if (r_slope[e] != 0.0f) sx -= r_slope[e] * fabsf((float)(r_pos[e] - j));
+                    s2[i] = (j >= r_lo[e] && j < r_hi[e]) ? sx * LOG2E : -INFINITY;
                 }
             }
-            const bool live = sigma > 0.0f && sigma < INFINITY;
-            const float sc = live ? fminf(fmaxf(sigma, 7.8886091e-31f), 1.2676506e30f) : 0.0f;  // 2^-100 ... 2^100
-            sts32(vmeta_s + lane * 8, f2u(sc));
-            sts32(vmeta_s + lane * 8 + 4, f2u(live ? fast_log2(sc) : -100.0f));
-            __syncwarp();
-        }
-        // ---- scores of the 32 keys: sr[u][2 k + e] = key 16 u + g + 8 k, row 2c + e
-        float sr[2][4];
-        k_scores(st_s + kt_off, mrow_g, sr[0]);
-        k_scores(st_s + kt_off + 16 * krb, mrow_g + 16 * KMW * 4, sr[1]);
-        // ---- online softmax
-        float2 vm[4];  // (sigma, log2 sigma) of the keys g, g + 8, g + 16, g + 24
+            float c0 = fmaxf(fmaxf(s2[0] + vm[0].y, s2[2] + vm[1].y), fmaxf(s2[4] + vm[2].y, s2[6] + vm[3].y));
+            float c1 = fmaxf(fmaxf(s2[1] + vm[0].y, s2[3] + vm[1].y), fmaxf(s2[5] + vm[2].y, s2[7] + vm[3].y));
+            if (__any_sync(0xffffffffu, c0 > M[0] + MAX_SLACK || c1 > M[1] + MAX_SLACK)) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) vm[k] = lds64f(vmeta_g + k * 64);
-        float s2[8];  // s2[2 k + e]
-        if (plain && nkeys == WK && key0 >= LOmax && key0 + WK <= HImin) {
+                for (int o = 4; o < 32; o <<= 1) {
+                    c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, o));
+                    c1 = fmaxf(c1, __shfl_xor_sync(0xffffffffu, c1, o));
+                }
+                const float n0 = fmaxf(M[0], c0), n1 = fmaxf(M[1], c1);
+                const float al0 = fast_exp2(M[0] - n0), al1 = fast_exp2(M[1] - n1);
+                M[0] = n0;
+                M[1] = n1;
+                lsum[0] *= al0;
+                lsum[1] *= al1;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) s2[i] = sr[i >> 2][i & 3] * qs2[i & 1];
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int e = i & 1, j = key0 + g + 8 * (i >> 1);
-                float sx = sr[i >> 2][i & 3] * qs[e];
-                if (p.softcap > 0.0f) sx = p.softcap * tanhf(sx / p.softcap);
-                if (r_slope[e] != 0.0f) sx -= r_slope[e] * fabsf((float)(r_pos[e] - j));
-                s2[i] = (j >= r_lo[e] && j < r_hi[e]) ? sx * LOG2E : -INFINITY;
+                for (int mt = 0; mt < STEPS; ++mt) {
+                    oacc[mt][0] *= al0;
+                    oacc[mt][1] *= al1;
+                    oacc[mt][2] *= al0;
+                    oacc[mt][3] *= al1;
+                }
             }
-        }
-        float c0 = fmaxf(fmaxf(s2[0] + vm[0].y, s2[2] + vm[1].y), fmaxf(s2[4] + vm[2].y, s2[6] + vm[3].y));
-        float c1 = fmaxf(fmaxf(s2[1] + vm[0].y, s2[3] + vm[1].y), fmaxf(s2[5] + vm[2].y, s2[7] + vm[3].y));
-        if (__any_sync(0xffffffffu, c0 > M[0] + MAX_SLACK || c1 > M[1] + MAX_SLACK)) {
+            uint32_t pb[4];
 #pragma unroll
-            for (int o = 4; o < 32; o <<= 1) {
-                c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, o));
-                c1 = fmaxf(c1, __shfl_xor_sync(0xffffffffu, c1, o));
+            for (int k = 0; k < 4; ++k) {
+                const float pa = fast_exp2(s2[2 * k] - M[0]), pc = fast_exp2(s2[2 * k + 1] - M[1]);
+                lsum[0] += pa;
+                lsum[1] += pc;
+                pb[k] = movmatrix_trans(pack_f16x2(pa * vm[k].x, pc * vm[k].x));
             }
-            const float n0 = fmaxf(M[0], c0), n1 = fmaxf(M[1], c1);
-            const float al0 = fast_exp2(M[0] - n0), al1 = fast_exp2(M[1] - n1);
-            M[0] = n0;
-            M[1] = n1;
-            lsum[0] *= al0;
-            lsum[1] *= al1;
-#pragma unroll
-            for (int mt = 0; mt < STEPS; ++mt) {
-                oacc[mt][0] *= al0;
-                oacc[mt][1] *= al1;
-                oacc[mt][2] *= al0;
-                oacc[mt][3] *= al1;
-            }
-        }
-        uint32_t pb[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float pa = fast_exp2(s2[2 * k] - M[0]), pc = fast_exp2(s2[2 * k + 1] - M[1]);
-            lsum[0] += pa;
-            lsum[1] += pc;
-            pb[k] = movmatrix_trans(pack_f16x2(pa * vm[k].x, pc * vm[k].x));
-        }
-        // ---- O^T += V^T P^T
-        v_accum(st_s + vt_off, vsc_c, pb[0], pb[1]);
-        v_accum(st_s + vt_off + 16 * vrb, vsc_c + 32, pb[2], pb[3]);
+            // ---- O^T += V^T P^T
+            v_accum(st_s + vt_off, vsc_c, pb[0], pb[1]);
+            v_accum(st_s + vt_off + 16 * vrb, vsc_c + 32, pb[2], pb[3]);
             // the stage was read (and possibly patched) through the generic proxy: order that before the
             // bulk copy of the next tile into it
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (++sidx == NS) sidx = 0;
-            // refill: copy tiles until this warp has NS in flight again (empty tiles take no stage)
-            --inflight;
-        }
-        while (ix < x_end && inflight < NS) {
-            const int k0i = icol.lo + (int)it * UNIT + warp * WK;
-            if (k0i < icol.hi) ++inflight;
-            issue_next();
+            c_st += stage_bytes;
+            c_bar += 8;
+            if (++c_stage == NS) {
+                c_stage = 0;
+                c_st = wstage_s;
+                c_bar = wbar_s;
+            }
+            if (i_left > 0) copy_tile();
         }
 
-        // ---- advance; at the end of the column (or of this block's share) merge the warps and write
-        const bool col_done = ct + 1 == (uint32_t)ccol.units;
-        if (col_done || x + 1 >= x_end) {
+        // ================================================================ merge the warps, write
+        // Warps 0 and 1 store their accumulators, scaled to the common maximum, into two buffers;
+        // warps 2 and 3 add theirs; the sum of the two buffers is the segment's result (fixed order).
 #pragma unroll
-            for (int o = 4; o < 32; o <<= 1) {
-                lsum[0] += __shfl_xor_sync(0xffffffffu, lsum[0], o);
-                lsum[1] += __shfl_xor_sync(0xffffffffu, lsum[1], o);
-            }
-            float *m_M = mbuf + DW * PACK * HD, *m_L = m_M + DW * PACK;
-            if (g == 0) {
-                m_M[warp * PACK + 2 * c] = M[0];
-                m_M[warp * PACK + 2 * c + 1] = M[1];
-                m_L[warp * PACK + 2 * c] = lsum[0];
-                m_L[warp * PACK + 2 * c + 1] = lsum[1];
-            }
-#pragma unroll
-            for (int mt = 0; mt < STEPS; ++mt) {
-                const int d0 = g * (HD / 8) + 2 * mt;
-                float *o0 = mbuf + ((size_t)warp * PACK + 2 * c) * HD + d0;
-                float *o1 = o0 + HD;
-                *reinterpret_cast<float2 *>(o0) = make_float2(oacc[mt][0], oacc[mt][2]);
-                *reinterpret_cast<float2 *>(o1) = make_float2(oacc[mt][1], oacc[mt][3]);
-            }
-            __syncthreads();
-            // thread -> (row, slice of dims)
-            constexpr int TPR = DW * 32 / PACK;  // threads per row
-            constexpr int DPT = HD / TPR;        // dims per thread
-            const int rr = tid / TPR, dsl = (tid % TPR) * DPT;
-            float mstar = -1e30f;
-#pragma unroll
-            for (int w = 0; w < DW; ++w) mstar = fmaxf(mstar, m_M[w * PACK + rr]);
-            float L = 0.0f, f[DW];
+        for (int o = 4; o < 32; o <<= 1) {
+            lsum[0] += __shfl_xor_sync(0xffffffffu, lsum[0], o);
+            lsum[1] += __shfl_xor_sync(0xffffffffu, lsum[1], o);
+        }
+        __syncthreads();  // every warp has its query fragments: the staging buffer becomes the merge buffer
+        if (g == 0) {
+            m_M[warp * PACK + 2 * c] = M[0];
+            m_M[warp * PACK + 2 * c + 1] = M[1];
+            m_L[warp * PACK + 2 * c] = lsum[0];
+            m_L[warp * PACK + 2 * c + 1] = lsum[1];
+        }
+        __syncthreads();
+        {
+            float ms0 = -1e30f, ms1 = -1e30f;
 #pragma unroll
             for (int w = 0; w < DW; ++w) {
-                f[w] = fast_exp2(m_M[w * PACK + rr] - mstar);
-                L += f[w] * m_L[w * PACK + rr];
+                ms0 = fmaxf(ms0, m_M[w * PACK + 2 * c]);
+                ms1 = fmaxf(ms1, m_M[w * PACK + 2 * c + 1]);
             }
-            const float invL = L > 0.0f ? 1.0f / L : 0.0f;
-            float res[DPT];
+            const float f0 = fast_exp2(M[0] - ms0), f1 = fast_exp2(M[1] - ms1);
+            float *dst = mbuf + (warp & 1) * PACK * HD;
 #pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                float a = 0.0f;
+            for (int round = 0; round < DW / 2; ++round) {
+                if ((warp >> 1) == round) {
 #pragma unroll
-                for (int w = 0; w < DW; ++w) a += f[w] * mbuf[((size_t)w * PACK + rr) * HD + dsl + i];
-                res[i] = a * invL;
-            }
-            const uint32_t r = pack * PACK + rr;
-            const uint32_t col = cb * ny + cy;
-            const bool whole = seg_first_unit == 0 && col_done;  // this block saw every unit of the column
-            if (seg_first_unit == 0 && tid == 0 && p.meta) {
-                // the block that owns the first unit of a column publishes where its segments are
-                const uint64_t first_x = x - ct;
-                const uint32_t last_owner = owner_of_unit(first_x + ccol.units - 1, total, nc);
-                p.meta[2 * (size_t)col] = (int32_t)(blockIdx.x + col);
-                p.meta[2 * (size_t)col + 1] = (int32_t)(last_owner - blockIdx.x + 1);
-            }
-            if (!whole) {
-                if (r < R) {
-                    const size_t slot = ((size_t)blockIdx.x + col) * PACK + rr;
-                    float *po = p.part_o + slot * HD + dsl;
-#pragma unroll
-                    for (int i = 0; i < DPT; ++i) po[i] = res[i];
-                    if (tid % TPR == 0) p.part_lse[slot] = L > 0.0f ? mstar * LN2 + logf(L) : -INFINITY;
+                    for (int mt = 0; mt < STEPS; ++mt) {
+                        const int d0 = g * (HD / 8) + 2 * mt;
+                        float2 *o0 = reinterpret_cast<float2 *>(dst + (2 * c) * HD + d0);
+                        float2 *o1 = reinterpret_cast<float2 *>(dst + (2 * c + 1) * HD + d0);
+                        float2 a = make_float2(oacc[mt][0] * f0, oacc[mt][2] * f0), b = make_float2(oacc[mt][1] * f1, oacc[mt][3] * f1);
+                        if (round) {
+                            const float2 pa = *o0, pc = *o1;
+                            a.x += pa.x; a.y += pa.y; b.x += pc.x; b.y += pc.y;
+                        }
+                        *o0 = a;
+                        *o1 = b;
+                    }
                 }
-            } else {
-                // the whole column in one segment: final rows (rotated back with the value signs when the cache is rotated)
+                __syncthreads();
+            }
+        }
+        // thread -> (row, slice of dims)
+        constexpr int TPR = DW * 32 / PACK;  // threads per row
+        constexpr int DPT = HD / TPR;        // dims per thread
+        const int rr = tid / TPR, dsl = (tid % TPR) * DPT;
+        float mstar = -1e30f;
+#pragma unroll
+        for (int w = 0; w < DW; ++w) mstar = fmaxf(mstar, m_M[w * PACK + rr]);
+        float L = 0.0f;
+#pragma unroll
+        for (int w = 0; w < DW; ++w) L += fast_exp2(m_M[w * PACK + rr] - mstar) * m_L[w * PACK + rr];
+        const float invL = L > 0.0f ? 1.0f / L : 0.0f;
+        float res[DPT];
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) res[i] = (mbuf[(size_t)rr * HD + dsl + i] + mbuf[(size_t)(PACK + rr) * HD + dsl + i]) * invL;
+        const uint32_t r = pack * PACK + rr;
+        const uint32_t colidx = seg.b * ny + seg.y;
+        const bool whole = seg.t0 == 0 && seg.t1 == (uint32_t)col.units;  // this block saw every unit of the column
+        if (seg.t0 == 0 && tid == 0 && p.meta) {
+            // the block that owns the first unit of a column publishes where its segments are
+            const uint32_t last_owner = owner_of_unit(seg.x + col.units - 1, total, nc);
+            p.meta[2 * (size_t)colidx] = (int32_t)(blockIdx.x + colidx);
+            p.meta[2 * (size_t)colidx + 1] = (int32_t)(last_owner - blockIdx.x + 1);
+        }
+        if (!whole) {
+            if (r < R) {
+                const size_t slot = ((size_t)blockIdx.x + colidx) * PACK + rr;
+                float *po = p.part_o + slot * HD + dsl;
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) po[i] = res[i];
+                if (tid % TPR == 0) p.part_lse[slot] = L > 0.0f ? mstar * LN2 + logf(L) : -INFINITY;
+            }
+        } else {
+            // the whole column in one segment: final rows (rotated back with the value signs when the cache is rotated)
+            if (p.v.rot == B200_ROT_HADAMARD) {
                 __syncthreads();
 #pragma unroll
                 for (int i = 0; i < DPT; ++i) mbuf[(size_t)rr * HD + dsl + i] = res[i];
                 __syncthreads();
-                if (p.v.rot == B200_ROT_HADAMARD) {
-                    for (int q = warp; q < PACK; q += DW) warp_hadamard(mbuf + q * HD, HD, p.v.signs, false, lane);
-                    __syncthreads();
-                }
-                if (r < R) {
-                    const uint32_t i0 = r / G, h = hk * G + r % G;
-                    const size_t obase = cb * p.o_sb + h * p.o_sh + i0 * p.o_ss;
+                for (int q = warp; q < PACK; q += DW) warp_hadamard(mbuf + q * HD, HD, p.v.signs, false, lane);
+                __syncthreads();
 #pragma unroll
-                    for (int i = 0; i < DPT; ++i)
-                        store_elem_rt(p.out, obase + dsl + i, mbuf[(size_t)rr * HD + dsl + i], p.out_dtype);
-                }
+                for (int i = 0; i < DPT; ++i) res[i] = mbuf[(size_t)rr * HD + dsl + i];
             }
-            fresh = true;
-        }
-        if (++ct == (uint32_t)ccol.units) {
-            ct = 0;
-            x += cc;
-            ++cy;
-            if (++pack == p.packs) {
-                pack = 0;
-                ++hk;
-            }
-            if (cy == ny) {
-                cy = 0;
-                hk = 0;
-                do {
-                    ++cb;
-                    if (cb < p.b) ccol = make_column(p, cb);
-                } while (cb < p.b && ccol.units == 0);
-                if (cb >= p.b) break;
+            if (r < R) {
+                const uint32_t i0 = p.lq == 1 ? 0u : r / G, h = hk * G + (p.lq == 1 ? r : r % G);
+                const size_t obase = seg.b * p.o_sb + h * p.o_sh + i0 * p.o_ss;
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) store_elem_rt(p.out, obase + dsl + i, res[i], p.out_dtype);
             }
         }
+        more = next_segment(seg, p, ny, x_end);
     }
     if (wait_failed && p.status) atomicExch(p.status, 1);
 }
