@@ -15,6 +15,7 @@ OK, ERR_BAD_ARG, ERR_UNSUPPORTED_SHAPE, ERR_LAUNCH, ERR_WORKSPACE, ERR_DEVICE_WA
 F32, F16, BF16, FP8 = 0, 1, 2, 3
 TURBO_MSE, TURBO_PROD, MXFP4, NVFP4, MXFP8, FP8_ROW = range(6)
 ROT_NONE, ROT_HADAMARD = 0, 1
+STATIC_SCRATCH_BYTES = 8 << 20
 
 u64x3 = C.c_uint64 * 3
 
@@ -83,7 +84,7 @@ class FaArgs(C.Structure):
 SYMBOLS = [
     "b200_row_layout", "b200_codebook", "b200_hadamard_signs", "b200_row_group", "b200_split_count_grouped",
     "b200_describe", "b200_last_error", "b200_tq_rotate", "b200_tq_quantize", "b200_tq_dequantize", "b200_kv_append",
-    "b200_tq_attention_workspace_bytes", "b200_tq_attention", "b200_flash_attn_workspace_bytes",
+    "b200_tq_attention_workspace_bytes", "b200_tq_attention", "b200_tq_attention_static", "b200_flash_attn_workspace_bytes",
     "b200_flash_attn", "b200_fa_prefill_append",
 ]
 
@@ -118,6 +119,7 @@ def lib():
         l.b200_tq_attention_workspace_bytes.argtypes = [C.POINTER(TqAttnArgs)]
         l.b200_tq_attention_workspace_bytes.restype = C.c_size_t
         l.b200_tq_attention.argtypes = [C.POINTER(TqAttnArgs), C.c_void_p]
+        l.b200_tq_attention_static.argtypes = [C.POINTER(TqAttnArgs), C.c_void_p]
         l.b200_flash_attn_workspace_bytes.argtypes = [C.POINTER(FaArgs)]
         l.b200_flash_attn_workspace_bytes.restype = C.c_size_t
         l.b200_flash_attn.argtypes = [C.POINTER(FaArgs), C.c_void_p]

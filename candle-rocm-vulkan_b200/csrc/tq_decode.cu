@@ -2,6 +2,7 @@
 // format dispatch and the combine launch.
 #include <algorithm>
 #include <cstdlib>
+#include <mutex>
 
 #include "tq_decode.cuh"
 
@@ -224,4 +225,47 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
         else tq_combine_kernel<256><<<gx, 128, 0, stream>>>(p);
         return check_launch("tq_combine");
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Attention over packed rows for callers that must not allocate device memory
+// ---------------------------------------------------------------------------------------------
+// Scratch of b200_tq_attention_static: lives in the library image, so every GPU that loads the
+// library holds these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[B200_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch per device ordinal. In host code the array's name is only a
+// handle for the runtime, never a pointer a kernel can use: the address comes from
+// cudaGetSymbolAddress, asked once per device while that device is current.
+static void *g_static_scratch_ptr[64] = {nullptr};
+static std::mutex g_static_scratch_mutex;
+
+extern "C" int b200_tq_attention_static(const B200TqAttnArgs *a, b200_stream_t stream) {
+    if (!a) return set_error(B200_ERR_BAD_ARG, "tq_attention_static: null args");
+    B200TqAttnArgs args = *a;
+    args.workspace = nullptr;
+    args.workspace_bytes = 0;
+    const size_t need = b200_tq_attention_workspace_bytes(&args);
+    if (need > (size_t)B200_STATIC_SCRATCH_BYTES)
+        return set_error(B200_ERR_WORKSPACE,
+                         "tq_attention_static: this call needs %zu bytes of scratch, the built-in buffer holds %zu; use "
+                         "b200_tq_attention with a caller-provided workspace",
+                         need, (size_t)B200_STATIC_SCRATCH_BYTES);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64)
+        return set_error(B200_ERR_LAUNCH, "tq_attention_static: no usable current device (%s)", cudaGetErrorString(e));
+    {
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        if (!g_static_scratch_ptr[dev]) {
+            void *sym = nullptr;
+            e = cudaGetSymbolAddress(&sym, g_static_scratch);
+            if (e != cudaSuccess || !sym)
+                return set_error(B200_ERR_LAUNCH, "tq_attention_static: address of the built-in scratch: %s", cudaGetErrorString(e));
+            g_static_scratch_ptr[dev] = sym;
+        }
+        args.workspace = g_static_scratch_ptr[dev];
+    }
+    args.workspace_bytes = (size_t)B200_STATIC_SCRATCH_BYTES;
+    return b200_tq_attention(&args, stream);
 }

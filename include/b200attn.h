@@ -221,6 +221,32 @@ typedef struct B200TqAttnArgs {
 size_t b200_tq_attention_workspace_bytes(const B200TqAttnArgs *args);
 int b200_tq_attention(const B200TqAttnArgs *args, b200_stream_t stream);
 
+/* Same call as b200_tq_attention for hosts that cannot give the library a workspace. It has no
+ * counterpart in the reference, whose launcher allocates its split buffers on every call
+ * (candle-core/src/cuda_backend/accel.rs:190-199 is the behaviour this avoids, not an interface it
+ * replaces).
+ *
+ * Who needs it: a serving process that handed all of HBM to its own pool at start-up and has no
+ * allocator handle to pass down through an FFI layer; a decode loop in which a cudaMalloc or
+ * cudaFree is forbidden because both synchronize the whole device; a binding that runs while
+ * another thread holds the host allocator's lock. For those, the split partials, their
+ * log-sum-exps and the column table live in a buffer of B200_STATIC_SCRATCH_BYTES that is part
+ * of the library image: every GPU that loads libb200attn.so holds that many bytes until the
+ * process exits, whether or not this entry point is ever called. The call itself allocates
+ * nothing: no cudaMalloc, cudaFree or allocating library routine.
+ *
+ * args->workspace and args->workspace_bytes are ignored; inputs and outputs are passed as usual.
+ * A call whose b200_tq_attention_workspace_bytes() exceeds B200_STATIC_SCRATCH_BYTES is refused
+ * with B200_ERR_WORKSPACE and a message that names both sizes (use b200_tq_attention then).
+ * The first call on each device looks up the buffer's device address (with that device current)
+ * and keeps it; make that first call before any stream capture begins on that device.
+ * Every call on a device shares the one buffer, which keeps the previous call's contents. Nothing
+ * in it has to start at zero (each call writes every word it later reads), but two calls that
+ * overlap on the GPU, from different streams or threads, race on it: keep calls to this entry
+ * point ordered on one stream per device. */
+#define B200_STATIC_SCRATCH_BYTES (8u << 20)
+int b200_tq_attention_static(const B200TqAttnArgs *args, b200_stream_t stream);
+
 /* ---- attention over dense K / V ------------------------------------------------------------------- */
 /* Replaces CudaStorage::flash_attn / flash_attn_paged (accel.rs:254-506), the kernels fa_row*,
  * fa2_*, fa3_*, fa_combine_* (candle-core/kernels/flash_attn_impl.h) and therefore the device
