@@ -104,9 +104,10 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
 
     p.k_stage_bytes = (uint32_t)((WK * p.k_ss * 4 + 16 + 15) / 16 * 16);
     p.v_stage_bytes = (uint32_t)((WK * p.v_ss * 4 + 16 + 15) / 16 * 16);
-    // shared memory: barriers and pair tables, per-warp key metadata, the merge / query staging
-    // buffer, then the stage rings
-    const size_t fixed = FIXED_SMEM + (size_t)DW * meta_bytes(a->kq.mode, a->vq.mode, (int)a->d) + merge_bytes((int)a->d);
+    // shared memory: barriers and pair tables, per-warp key metadata, per-warp query staging (rotated
+    // caches only), then the stage rings
+    p.qstage_bytes = a->kq.rotation == B200_ROT_HADAMARD ? (uint32_t)(DW * PACK * a->d * 4) : 0u;
+    const size_t fixed = FIXED_SMEM + (size_t)DW * meta_bytes(a->kq.mode, a->vq.mode, (int)a->d) + p.qstage_bytes;
     const size_t stage = (size_t)p.k_stage_bytes + p.v_stage_bytes;
     // stages per warp and blocks per SM: as many bytes in flight as possible (a warp computes on one
     // stage while the others load), more blocks on a tie
@@ -118,7 +119,7 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
     for (int ns = 2; ns <= NS_MAX; ++ns) {
         const size_t sm = fixed + DW * ns * stage;
         if (sm > 227 * 1024) break;
-        const int fit = (int)std::min<size_t>(3, (228 * 1024) / (sm + 1024));
+        const int fit = (int)std::min<size_t>(B200_DECODE_MIN_BLOCKS, (228 * 1024) / (sm + 1024));
         if (fit < 1) break;
         const size_t flight = (size_t)fit * DW * (ns - 1) * stage;
         if (flight > best || (flight == best && fit > bps)) {
@@ -129,12 +130,11 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
     }
     if (env_ns >= 2 && env_ns <= NS_MAX) {
         p.ns = (uint32_t)env_ns;
-        bps = (int)std::min<size_t>(3, (228 * 1024) / (fixed + DW * p.ns * stage + 1024));
+        bps = (int)std::min<size_t>(B200_DECODE_MIN_BLOCKS, (228 * 1024) / (fixed + DW * p.ns * stage + 1024));
     }
     if (env_bps > 0) bps = (int)env_bps;
     bps = std::max(bps, 1);
-    p.stages_bytes = (uint32_t)(DW * p.ns * stage);
-    pl.smem = fixed + p.stages_bytes;
+    pl.smem = fixed + DW * p.ns * stage;
     if (pl.smem > 227 * 1024) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: %zu bytes of shared memory", pl.smem);
     // rows that certainly exist after the visible ones: the head stride spans them
     p.rows_cap = 0;
@@ -143,15 +143,17 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
 
     static const long env_cc = [] { const char *e = getenv("B200_DECODE_COL_COST"); return e ? atol(e) : -1l; }();
     p.col_cost = env_cc >= 0 ? (uint32_t)env_cc : 4u;
-    // persistent blocks: as many as fit on the device at once, at most one per unit of 128 keys
+    // persistent blocks of DW independent warps: as many as fit on the device at once, at most one
+    // warp per tile of keys
     const uint64_t lk = std::max<uint32_t>(a->lk, 1);
-    const uint64_t max_units = (uint64_t)a->b * pl.ny * ((lk + DW * WK - 1) / (DW * WK));
+    const uint64_t max_tiles = (uint64_t)a->b * pl.ny * ((lk + WK - 1) / WK);
     uint64_t nblocks = (uint64_t)sm_count_cached() * bps;
-    if (a->splits > 0) nblocks = std::min<uint64_t>(nblocks, (uint64_t)a->b * pl.ny * a->splits);
-    pl.blocks = (uint32_t)std::max<uint64_t>(std::min(nblocks, max_units), 1);
+    if (a->splits > 0) nblocks = std::min<uint64_t>(nblocks, ((uint64_t)a->b * pl.ny * a->splits + DW - 1) / DW);
+    pl.blocks = (uint32_t)std::max<uint64_t>(std::min(nblocks, (max_tiles + DW - 1) / DW), 1);
 
     const size_t ncols = (size_t)a->b * pl.ny;
-    const size_t slots = ((size_t)pl.blocks + ncols) * PACK;
+    const size_t prow = std::min<size_t>(PACK, p.rows_per_kv);
+    const size_t slots = ((size_t)pl.blocks * DW + ncols) * prow;
     const size_t part_o = slots * a->d * 4;
     const size_t part_l = slots * 4;
     pl.off_lse = (part_o + 255) / 256 * 256;

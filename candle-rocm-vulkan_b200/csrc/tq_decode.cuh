@@ -34,6 +34,9 @@ namespace b200 {
 
 constexpr int DW = 4;         // warps per block
 constexpr int WK = 32;        // keys per warp tile
+#ifndef B200_DECODE_MIN_BLOCKS
+#define B200_DECODE_MIN_BLOCKS 3
+#endif
 constexpr int NS_MAX = 3;     // stages per warp (fewer when the rows are large)
 constexpr float MAX_SLACK = 8.0f;  // log2 of how far a score may exceed the running maximum before it moves
 constexpr int PACK = 8;       // query rows per block
@@ -62,15 +65,15 @@ struct DecodeParams {
     int32_t wl, wr;
     const float *alibi;
     uint32_t alibi_bs;
-    float *part_o;     // [slot][PACK][d], slot = block + column
-    float *part_lse;   // [slot][PACK]
+    float *part_o;     // [slot][rows][d], slot = worker + column, rows = min(PACK, query rows per kv head)
+    float *part_lse;   // [slot][rows]
     int32_t *meta;     // [column] (first slot, number of segments)
     int32_t *status;
     uint32_t k_stage_bytes, v_stage_bytes;
     uint32_t ns;       // stages per warp
     uint32_t rows_cap;      // rows that exist in every (batch, head) slab of both caches (0 = only the visible ones)
-    uint32_t col_cost;      // cost of starting a column, in units, for the split of the work between blocks
-    uint32_t stages_bytes;  // whole stage area (also holds the query staging and the merge buffers)
+    uint32_t col_cost;      // cost of starting a column, in tiles, for the split of the work between the warps
+    uint32_t qstage_bytes;  // query staging for the rotation (0 without it)
 };
 
 __host__ __device__ constexpr bool fmt_is4(int m) { return m == B200_MXFP4 || m == B200_NVFP4 || m == B200_TURBO_MSE; }
@@ -83,7 +86,6 @@ __host__ __device__ constexpr int meta_bytes(int km, int vm, int hd) {
     return WK * (kmeta_words(km, hd) * 4 + 8 + vsc_blocks(vm, hd) * 2);
 }
 constexpr int FIXED_SMEM = 128 + 2048;  // barriers, pair tables
-__host__ __device__ constexpr int merge_bytes(int hd) { return 2 * PACK * hd * 4 + 2 * DW * PACK * 4; }
 
 __device__ __forceinline__ uint32_t lds32(uint32_t a) {
     uint32_t v;
@@ -171,10 +173,12 @@ __device__ __forceinline__ void warp_hadamard(float *row, int n, const float *si
 }
 
 // One column = the keys of one (batch entry, kv head, pack of query rows). Its visible keys
-// [lo, hi) are cut into units of DW * WK keys; the units of all columns, in (batch, column, unit)
-// order, form the work list that the persistent blocks share.
+// [lo, hi) are cut into tiles of WK keys; the tiles of all columns, in (batch, column, tile) order,
+// form the work list that the warps of the persistent blocks share: every warp is a worker of
+// its own, with its own copy ring, segments and partial results, so no block-wide barrier or merge
+// sits between the warps.
 struct Column {
-    int lo, hi, lk, units;
+    int lo, hi, lk, tiles;
 };
 
 __device__ __forceinline__ Column make_column(const DecodeParams &p, uint32_t b) {
@@ -188,28 +192,28 @@ __device__ __forceinline__ Column make_column(const DecodeParams &p, uint32_t b)
     hi = max(hi, lo);
     c.lo = (int)lo;
     c.hi = (int)hi;
-    c.units = (c.hi - c.lo + DW * WK - 1) / (DW * WK);
+    c.tiles = (c.hi - c.lo + WK - 1) / WK;
     return c;
 }
 
-// block that owns cost position x when `total` is shared by `nc` blocks (block i starts at floor(i total / nc))
-__device__ __forceinline__ uint32_t owner_of_unit(uint64_t x, uint64_t total, uint32_t nc) {
-    return (uint32_t)(((x + 1) * nc - 1) / total);
+// worker that owns cost position x when `total` is shared by `nw` workers (worker i starts at floor(i total / nw))
+__device__ __forceinline__ uint32_t owner_of(uint64_t x, uint64_t total, uint32_t nw) {
+    return (uint32_t)(((x + 1) * nw - 1) / total);
 }
 
-// A block's share of the work is a list of segments: units [t0, t1) of column y of batch entry b.
-// Cost space: every column takes col_cost (its set up and merge) plus one per unit, laid out in
-// (batch, column) order; block i takes the units whose cost position lies in
-// [i total / nc, (i + 1) total / nc). Columns without units cost nothing.
+// A worker's share is a list of segments: tiles [t0, t1) of column y of batch entry b.
+// Cost space: every column takes col_cost (its set up and its partial result) plus one per tile, laid
+// out in (batch, column) order; worker i takes the tiles whose cost position lies in
+// [i total / nw, (i + 1) total / nw). Columns without tiles cost nothing.
 struct Segment {
     uint32_t b, y, t0, t1;
-    uint64_t x;  // cost position of unit t0
+    uint64_t x;  // cost position of tile t0
     Column col;
 };
 
 // next segment of the share that ends at x_end; false when the share is exhausted
 __device__ __forceinline__ bool next_segment(Segment &s, const DecodeParams &p, uint32_t ny, uint64_t x_end) {
-    if (s.t1 < (uint32_t)s.col.units) return false;  // the share ended inside the column
+    if (s.t1 < (uint32_t)s.col.tiles) return false;  // the share ended inside the column
     const uint64_t x = s.x + (s.t1 - s.t0) + p.col_cost;
     if (x >= x_end) return false;
     if (++s.y == ny) {
@@ -217,16 +221,16 @@ __device__ __forceinline__ bool next_segment(Segment &s, const DecodeParams &p, 
         do {
             if (++s.b >= p.b) return false;
             s.col = make_column(p, s.b);
-        } while (s.col.units == 0);
+        } while (s.col.tiles == 0);
     }
     s.x = x;
     s.t0 = 0;
-    s.t1 = (uint32_t)min((uint64_t)s.col.units, x_end - x);
+    s.t1 = (uint32_t)min((uint64_t)s.col.tiles, x_end - x);
     return true;
 }
 
 template <int KM, int VM, int HD>
-__global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_kernel(const DecodeParams p) {
     constexpr int STEPS = HD / 16;          // k-steps of K Q^T == m-tiles of the output
     constexpr bool K4 = fmt_is4(KM), V4 = fmt_is4(VM);
     constexpr bool KMX = fmt_is_mx(KM);     // block-wise accumulation, contraction order A
@@ -234,24 +238,32 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
     constexpr int NBK = HD / 32;            // 32-blocks per row
     constexpr int NBV = vsc_blocks(VM, HD);
     constexpr int META = meta_bytes(KM, VM, HD);
-    constexpr int UNIT = DW * WK;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem);  // [DW][NS_MAX]
     const int NS = (int)p.ns;
     const uint32_t sbase = smem_u32(smem);
     const uint32_t lut_k = sbase + 128, lut_v = lut_k + 1024;
-    float *mbuf = reinterpret_cast<float *>(smem + FIXED_SMEM + DW * META);  // 2 x [PACK][HD], then M and L [DW][PACK]; also the query staging
-    float *m_M = mbuf + 2 * PACK * HD, *m_L = m_M + DW * PACK;
-    uint8_t *stages = reinterpret_cast<uint8_t *>(mbuf) + merge_bytes(HD);
     const uint32_t stage_bytes = p.k_stage_bytes + p.v_stage_bytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
-    const uint32_t G = p.group, R = p.rows_per_kv, ny = p.hkv * p.packs, nc = gridDim.x;
+    const uint32_t G = p.group, R = p.rows_per_kv, ny = p.hkv * p.packs;
+    const uint32_t nw = gridDim.x * DW, wid = blockIdx.x * DW + warp;
 
-    // ------------------------------------------------------------------ this block's share of the work
+    // ------------------------------------------------------------------ one time set up (the only block barrier)
+    if (tid == 0) {
+        for (int i = 0; i < DW * NS_MAX; ++i) mbar_init(&bars[i], 1);
+        mbar_fence_init();
+    }
+    if constexpr (KM == B200_TURBO_MSE)
+        for (int i = tid; i < 256; i += DW * 32) sts32(lut_k + 4 * i, pack_f16x2(p.k.tab[i & 15], p.k.tab[i >> 4]));
+    if constexpr (VM == B200_TURBO_MSE)
+        for (int i = tid; i < 256; i += DW * 32) sts32(lut_v + 4 * i, pack_f16x2(p.v.tab[i & 15], p.v.tab[i >> 4]));
+    __syncthreads();
+
+    // ------------------------------------------------------------------ this warp's share of the work
     const uint32_t cc = p.col_cost;
     auto batch_cost = [&](uint32_t bb) -> uint32_t {
-        const uint32_t t = (uint32_t)make_column(p, bb).units;
+        const uint32_t t = (uint32_t)make_column(p, bb).tiles;
         return t ? (t + cc) * ny : 0u;
     };
     uint64_t total = 0;
@@ -267,7 +279,7 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
         }
     }
     if (total == 0) return;
-    const uint64_t x_begin = total * blockIdx.x / nc, x_end = total * (blockIdx.x + 1) / nc;
+    const uint64_t x_begin = total * wid / nw, x_end = total * (wid + 1) / nw;
     // batch entry that holds cost position x_begin, and the position of its first column
     uint32_t b0 = 0;
     uint64_t b0_start = 0;
@@ -296,55 +308,39 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
             carry += __shfl_sync(0xffffffffu, incl, 31);
         }
     }
-    // first segment: the first unit at or after x_begin (a position inside a column's set up cost
-    // snaps to the column's first unit)
-    Segment seg0;
+    // first segment: the first tile at or after x_begin (a position inside a column's set up cost
+    // snaps to the column's first tile)
+    Segment seg;
     {
-        seg0.b = b0;
-        seg0.col = make_column(p, b0);
-        const uint32_t tb = (uint32_t)seg0.col.units;
+        seg.b = b0;
+        seg.col = make_column(p, b0);
+        const uint32_t tb = (uint32_t)seg.col.tiles;
         const uint64_t rem = x_begin - b0_start;
-        seg0.y = (uint32_t)(rem / (tb + cc));
+        seg.y = (uint32_t)(rem / (tb + cc));
         const uint32_t in_col = (uint32_t)(rem % (tb + cc));
-        seg0.t0 = in_col > cc ? in_col - cc : 0u;
-        seg0.x = b0_start + (uint64_t)seg0.y * (tb + cc) + cc + seg0.t0;
-        if (seg0.x >= x_end) return;  // the share lies inside a set up gap: no unit
-        seg0.t1 = (uint32_t)min((uint64_t)tb, seg0.t0 + (x_end - seg0.x));
+        seg.t0 = in_col > cc ? in_col - cc : 0u;
+        seg.x = b0_start + (uint64_t)seg.y * (tb + cc) + cc + seg.t0;
+        if (seg.x >= x_end) return;  // the share lies inside a set up gap: no tile
+        seg.t1 = (uint32_t)min((uint64_t)tb, seg.t0 + (x_end - seg.x));
     }
-
-    // ------------------------------------------------------------------ one time set up
-    if (tid == 0) {
-        for (int i = 0; i < DW * NS_MAX; ++i) mbar_init(&bars[i], 1);
-        mbar_fence_init();
-    }
-    if constexpr (KM == B200_TURBO_MSE)
-        for (int i = tid; i < 256; i += DW * 32) sts32(lut_k + 4 * i, pack_f16x2(p.k.tab[i & 15], p.k.tab[i >> 4]));
-    if constexpr (VM == B200_TURBO_MSE)
-        for (int i = tid; i < 256; i += DW * 32) sts32(lut_v + 4 * i, pack_f16x2(p.v.tab[i & 15], p.v.tab[i >> 4]));
-    __syncthreads();
 
     const uint32_t krb = (uint32_t)p.k_ss * 4u, vrb = (uint32_t)p.v_ss * 4u;  // row bytes
-    const uint32_t wstage_s = smem_u32(stages + (size_t)warp * NS * stage_bytes);
-    const uint32_t wbar_s = smem_u32(bars + warp * NS_MAX);
     const uint32_t meta_s = sbase + FIXED_SMEM + warp * META;    // [WK][KMW] f32
     const uint32_t vmeta_s = meta_s + WK * KMW * 4;              // [WK] (sigma, log2 sigma)
     const uint32_t vsc_s = vmeta_s + WK * 8;                     // [NBV][WK] f16
+    float *qstage = reinterpret_cast<float *>(smem + FIXED_SMEM + DW * META) + (size_t)warp * PACK * HD;  // only with a rotated cache
+    const uint32_t wstage_s = sbase + FIXED_SMEM + DW * META + p.qstage_bytes + (uint32_t)warp * NS * stage_bytes;
+    const uint32_t wbar_s = smem_u32(bars + warp * NS_MAX);
     const uint32_t k_cw4 = (uint32_t)p.k.code_words * 4u, k_rsc4 = (uint32_t)p.k.rsc_off * 4u;
     const uint32_t v_cw4 = (uint32_t)p.v.code_words * 4u, v_rsc4 = (uint32_t)p.v.rsc_off * 4u;
     const bool plain = p.softcap <= 0.0f && p.alibi == nullptr;  // tiles inside every row's range take the unmasked path
+    const uint32_t prow = min((uint32_t)PACK, R);                // rows of a partial result
     bool wait_failed = false;
-
-    // this warp's tiles of a segment: tile t of the column holds the keys lo + t UNIT + warp WK ...
-    auto warp_tiles = [&](const Segment &s) -> int {
-        const int span = s.col.hi - s.col.lo - warp * WK;
-        const int tw = span > 0 ? (span + UNIT - 1) / UNIT : 0;  // tiles of this warp in the column
-        return max(min((int)s.t1, tw) - (int)s.t0, 0);
-    };
 
     // ------------------------------------------------------------------ the copy side
     // runs up to NS tiles ahead of the compute side through the same list of segments
-    Segment iseg = seg0;
-    int i_left = 0;          // tiles of this warp still to copy in the copy side's segment
+    Segment iseg = seg;
+    int i_left = 0;          // tiles still to copy in the copy side's segment
     bool i_more = true;      // the copy side has segments left
     uintptr_t i_k = 0, i_v = 0;        // 16-byte aligned global addresses of the next tile's copies
     uint32_t i_koff = 0, i_voff = 0;   // offset of the tile's first row inside its copy
@@ -352,9 +348,9 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
     uint32_t i_st = wstage_s, i_bar = wbar_s;  // stage and barrier of the next copy
     int i_stage = 0;
     auto copy_enter = [&]() {  // per-segment constants of the copy side
-        i_left = warp_tiles(iseg);
+        i_left = (int)(iseg.t1 - iseg.t0);
         const uint32_t hk = iseg.y / p.packs;
-        i_key = iseg.col.lo + (int)iseg.t0 * UNIT + warp * WK;
+        i_key = iseg.col.lo + (int)iseg.t0 * WK;
         const uintptr_t ka = reinterpret_cast<uintptr_t>(p.k_rows + (size_t)iseg.b * p.k_sb + (size_t)hk * p.k_sh) + (uintptr_t)(uint32_t)i_key * krb;
         const uintptr_t va = reinterpret_cast<uintptr_t>(p.v_rows + (size_t)iseg.b * p.v_sb + (size_t)hk * p.v_sh) + (uintptr_t)(uint32_t)i_key * vrb;
         i_koff = (uint32_t)(ka & 15u);
@@ -363,11 +359,7 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
         i_v = va - i_voff;
     };
     copy_enter();
-    while (i_left == 0 && i_more) {
-        i_more = next_segment(iseg, p, ny, x_end);
-        if (i_more) copy_enter();
-    }
-    // copies the next tile of this warp (the caller checked i_left > 0) and moves on
+    // copies the next tile (the caller checked i_left > 0) and moves on
     auto copy_tile = [&]() {
         const int nkeys = min(WK, iseg.col.hi - i_key);
         // Rows below lk are readable, and so is the row after a tile when the cache has spare rows
@@ -401,10 +393,10 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
                              "l"(i_v), "r"(vb), "r"(i_bar)
                              : "memory");
         }
-        // UNIT rows are a multiple of 16 bytes: the next tile keeps its offset inside its copy
-        i_k += (uintptr_t)UNIT * krb;
-        i_v += (uintptr_t)UNIT * vrb;
-        i_key += UNIT;
+        // WK rows are a multiple of 16 bytes: the next tile keeps its offset inside its copy
+        i_k += (uintptr_t)WK * krb;
+        i_v += (uintptr_t)WK * vrb;
+        i_key += WK;
         i_st += stage_bytes;
         i_bar += 8;
         if (++i_stage == NS) {
@@ -412,8 +404,7 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
             i_st = wstage_s;
             i_bar = wbar_s;
         }
-        --i_left;
-        while (i_left == 0 && i_more) {
+        if (--i_left == 0 && i_more) {
             i_more = next_segment(iseg, p, ny, x_end);
             if (i_more) copy_enter();
         }
@@ -574,7 +565,6 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
 
 
 
-    Segment seg = seg0;
     bool more = true;
     while (more) {
         // ================================================================ segment set up
@@ -600,43 +590,47 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
             row_range(pack * PACK, lo, hi, pos);
             HImin = hi;
         }
-        // the two query rows whose scores this lane holds (columns 2c, 2c + 1 of the score fragments)
-        int r_lo[2], r_hi[2], r_pos[2];
-        float r_slope[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            const uint32_t r = pack * PACK + 2 * c + e;
-            r_lo[e] = r_hi[e] = r_pos[e] = 0;
-            r_slope[e] = 0.0f;
-            if (r < R) {
-                row_range(r, r_lo[e], r_hi[e], r_pos[e]);
-                if (p.alibi) r_slope[e] = p.alibi[(size_t)seg.b * p.alibi_bs + hk * G + (p.lq == 1 ? r : r % G)];
-            }
-        }
-        // queries -> f32 rows in shared memory (rows of the pack; missing rows are zero)
-        float *qbuf = mbuf;  // [PACK][HD]
-        __syncthreads();     // the previous segment's merge is done with the buffer
-        for (int idx = tid; idx < PACK * HD; idx += DW * 32) {
-            const uint32_t rr = idx / HD, dd = idx % HD;
-            const uint32_t r = pack * PACK + rr;
-            float v = 0.0f;
-            if (r < R) {
-                const uint32_t i = p.lq == 1 ? 0u : r / G, h = hk * G + (p.lq == 1 ? r : r % G);
-                v = load_elem_rt(p.q, seg.b * p.q_sb + h * p.q_sh + i * p.q_ss + dd, p.q_dtype);
-            }
-            qbuf[idx] = v;
-        }
-        __syncthreads();
-        if (p.k.rot == B200_ROT_HADAMARD) {
-            for (int rr = warp; rr < PACK; rr += DW) warp_hadamard(qbuf + rr * HD, HD, p.k.signs, true, lane);
-            __syncthreads();
-        }
-        // power of two normalization of row g, then the f16 B fragments of K Q^T: per k-step the four
-        // contraction slots of this lane are the consecutive dims dbase(s) ... dbase(s) + 3
+        // query row g of the pack: power of two normalization, then the f16 B fragments of K Q^T. Per
+        // k-step the four contraction slots of this lane are the consecutive dims dbase(s) ... + 3,
+        // so the four lanes of a quad hold the whole row between them.
         {
-            const float *qr = qbuf + g * HD;
+            const uint32_t r = pack * PACK + g;
+            float qv[STEPS][4];
+            if (p.k.rot == B200_ROT_HADAMARD) {
+                __syncwarp();
+                for (int idx = lane; idx < PACK * HD; idx += 32) {
+                    const uint32_t rr = idx / HD, dd = idx % HD, r2 = pack * PACK + rr;
+                    float v = 0.0f;
+                    if (r2 < R) {
+                        const uint32_t i = p.lq == 1 ? 0u : r2 / G, h = hk * G + (p.lq == 1 ? r2 : r2 % G);
+                        v = load_elem_rt(p.q, seg.b * p.q_sb + h * p.q_sh + i * p.q_ss + dd, p.q_dtype);
+                    }
+                    qstage[idx] = v;
+                }
+                __syncwarp();
+                for (int rr = 0; rr < PACK; ++rr) warp_hadamard(qstage + rr * HD, HD, p.k.signs, true, lane);
+                __syncwarp();
+#pragma unroll
+                for (int s = 0; s < STEPS; ++s) {
+                    const int dbase = KMX ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : c * (HD / 4) + 4 * s;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) qv[s][j] = qstage[g * HD + dbase + j];
+                }
+            } else {
+                const uint32_t i = p.lq == 1 ? 0u : r / G, h = hk * G + (p.lq == 1 ? r : r % G);
+                const size_t qoff = seg.b * p.q_sb + h * p.q_sh + i * p.q_ss;
+#pragma unroll
+                for (int s = 0; s < STEPS; ++s) {
+                    const int dbase = KMX ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : c * (HD / 4) + 4 * s;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) qv[s][j] = r < R ? load_elem_rt(p.q, qoff + dbase + j, p.q_dtype) : 0.0f;
+                }
+            }
             float am = 0.0f;
-            for (int dd = c; dd < HD; dd += 4) am = fmaxf(am, fabsf(qr[dd]));
+#pragma unroll
+            for (int s = 0; s < STEPS; ++s)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) am = fmaxf(am, fabsf(qv[s][j]));
             am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
             am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
             int e = 0;
@@ -650,10 +644,8 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
             qs2[1] = qs[1] * LOG2E;
 #pragma unroll
             for (int s = 0; s < STEPS; ++s) {
-                const int dbase = KMX ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : c * (HD / 4) + 4 * s;
-                const float *q4 = qr + dbase;
-                qb0[s] = pack_f16x2(q4[0] * down, q4[1] * down);
-                qb1[s] = pack_f16x2(q4[2] * down, q4[3] * down);
+                qb0[s] = pack_f16x2(qv[s][0] * down, qv[s][1] * down);
+                qb1[s] = pack_f16x2(qv[s][2] * down, qv[s][3] * down);
             }
         }
         // running maxima (log2 domain, value scale folded in) and partial normalizers of rows 2c, 2c + 1
@@ -661,14 +653,14 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
 #pragma unroll
         for (int mt = 0; mt < STEPS; ++mt) oacc[mt][0] = oacc[mt][1] = oacc[mt][2] = oacc[mt][3] = 0.0f;
 
-        // ================================================================ this warp's tiles of the segment
-        const int n_w = warp_tiles(seg);
-        int key0 = col.lo + (int)seg.t0 * UNIT + warp * WK;
+        // ================================================================ the tiles of the segment
+        const int n_t = (int)(seg.t1 - seg.t0);
+        int key0 = col.lo + (int)seg.t0 * WK;
         const uint32_t koff = (uint32_t)((reinterpret_cast<uintptr_t>(p.k_rows + (size_t)seg.b * p.k_sb + (size_t)hk * p.k_sh) + (uintptr_t)(uint32_t)key0 * krb) & 15u);
         const uint32_t voff = (uint32_t)((reinterpret_cast<uintptr_t>(p.v_rows + (size_t)seg.b * p.v_sb + (size_t)hk * p.v_sh) + (uintptr_t)(uint32_t)key0 * vrb) & 15u);
         const uint32_t kt_off = koff + k_lane, vt_off = p.k_stage_bytes + voff + v_lane;
         const uint32_t kr_off = koff + lane * krb, vr_off = p.k_stage_bytes + voff + lane * vrb;
-        for (int n = 0; n < n_w && !wait_failed; ++n, key0 += UNIT) {
+        for (int n = 0; n < n_t && !wait_failed; ++n, key0 += WK) {
             {
                 const uint32_t par = (phases >> c_stage) & 1u;
                 uint32_t ok = 0;
@@ -750,49 +742,92 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
             float2 vm[4];  // (sigma, log2 sigma) of the keys g, g + 8, g + 16, g + 24
 #pragma unroll
             for (int k = 0; k < 4; ++k) vm[k] = lds64f(vmeta_g + k * 64);
-            float s2[8];  // s2[2 k + e]
-            if (plain && nkeys == WK && key0 >= LOmax && key0 + WK <= HImin) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) s2[i] = sr[i >> 2][i & 3] * qs2[i & 1];
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int e = i & 1, j = key0 + g + 8 * (i >> 1);
-                    float sx = sr[i >> 2][i & 3] * qs[e];
-                    if (p.softcap > 0.0f) sx = p.softcap * tanhf(sx / p.softcap);
-                    if (r_slope[e] != 0.0f) sx -= r_slope[e] * fabsf((float)(r_pos[e] - j));
-                    s2[i] = (j >= r_lo[e] && j < r_hi[e]) ? sx * LOG2E : -INFINITY;
-                }
-            }
-            float c0 = fmaxf(fmaxf(s2[0] + vm[0].y, s2[2] + vm[1].y), fmaxf(s2[4] + vm[2].y, s2[6] + vm[3].y));
-            float c1 = fmaxf(fmaxf(s2[1] + vm[0].y, s2[3] + vm[1].y), fmaxf(s2[5] + vm[2].y, s2[7] + vm[3].y));
-            if (__any_sync(0xffffffffu, c0 > M[0] + MAX_SLACK || c1 > M[1] + MAX_SLACK)) {
-#pragma unroll
-                for (int o = 4; o < 32; o <<= 1) {
-                    c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, o));
-                    c1 = fmaxf(c1, __shfl_xor_sync(0xffffffffu, c1, o));
-                }
-                const float n0 = fmaxf(M[0], c0), n1 = fmaxf(M[1], c1);
-                const float al0 = fast_exp2(M[0] - n0), al1 = fast_exp2(M[1] - n1);
-                M[0] = n0;
-                M[1] = n1;
-                lsum[0] *= al0;
-                lsum[1] *= al1;
-#pragma unroll
-                for (int mt = 0; mt < STEPS; ++mt) {
-                    oacc[mt][0] *= al0;
-                    oacc[mt][1] *= al1;
-                    oacc[mt][2] *= al0;
-                    oacc[mt][3] *= al1;
-                }
-            }
             uint32_t pb[4];
+            if (plain && nkeys == WK && key0 >= LOmax && key0 + WK <= HImin) {
+                // every key visible to every row: scale, maximum check and exponent in fused multiply-adds
+                float c0 = fmaxf(fmaxf(fmaf(sr[0][0], qs2[0], vm[0].y), fmaf(sr[0][2], qs2[0], vm[1].y)),
+                                 fmaxf(fmaf(sr[1][0], qs2[0], vm[2].y), fmaf(sr[1][2], qs2[0], vm[3].y)));
+                float c1 = fmaxf(fmaxf(fmaf(sr[0][1], qs2[1], vm[0].y), fmaf(sr[0][3], qs2[1], vm[1].y)),
+                                 fmaxf(fmaf(sr[1][1], qs2[1], vm[2].y), fmaf(sr[1][3], qs2[1], vm[3].y)));
+                if (__any_sync(0xffffffffu, c0 > M[0] + MAX_SLACK || c1 > M[1] + MAX_SLACK)) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float pa = fast_exp2(s2[2 * k] - M[0]), pc = fast_exp2(s2[2 * k + 1] - M[1]);
-                lsum[0] += pa;
-                lsum[1] += pc;
-                pb[k] = movmatrix_trans(pack_f16x2(pa * vm[k].x, pc * vm[k].x));
+                    for (int o = 4; o < 32; o <<= 1) {
+                        c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, o));
+                        c1 = fmaxf(c1, __shfl_xor_sync(0xffffffffu, c1, o));
+                    }
+                    const float n0 = fmaxf(M[0], c0), n1 = fmaxf(M[1], c1);
+                    const float al0 = fast_exp2(M[0] - n0), al1 = fast_exp2(M[1] - n1);
+                    M[0] = n0;
+                    M[1] = n1;
+                    lsum[0] *= al0;
+                    lsum[1] *= al1;
+#pragma unroll
+                    for (int mt = 0; mt < STEPS; ++mt) {
+                        oacc[mt][0] *= al0;
+                        oacc[mt][1] *= al1;
+                        oacc[mt][2] *= al0;
+                        oacc[mt][3] *= al1;
+                    }
+                }
+                const float nm0 = -M[0], nm1 = -M[1];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float pa = fast_exp2(fmaf(sr[k >> 1][2 * (k & 1)], qs2[0], nm0));
+                    const float pc = fast_exp2(fmaf(sr[k >> 1][2 * (k & 1) + 1], qs2[1], nm1));
+                    lsum[0] += pa;
+                    lsum[1] += pc;
+                    pb[k] = movmatrix_trans(pack_f16x2(pa * vm[k].x, pc * vm[k].x));
+                }
+            } else {
+                // masks, soft-capping, ALiBi: the two query rows whose scores this lane holds (columns 2c, 2c + 1)
+                float s2[8];  // s2[2 k + e]
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const uint32_t r = pack * PACK + 2 * c + e;
+                    int r_lo = 0, r_hi = 0, r_pos = 0;
+                    float slope = 0.0f;
+                    if (r < R) {
+                        row_range(r, r_lo, r_hi, r_pos);
+                        if (p.alibi) slope = p.alibi[(size_t)seg.b * p.alibi_bs + hk * G + (p.lq == 1 ? r : r % G)];
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int j = key0 + g + 8 * k;
+                        float sx = sr[k >> 1][2 * (k & 1) + e] * qs[e];
+                        if (p.softcap > 0.0f) sx = p.softcap * tanhf(sx / p.softcap);
+                        if (slope != 0.0f) sx -= slope * fabsf((float)(r_pos - j));
+                        s2[2 * k + e] = (j >= r_lo && j < r_hi) ? sx * LOG2E : -INFINITY;
+                    }
+                }
+                float c0 = fmaxf(fmaxf(s2[0] + vm[0].y, s2[2] + vm[1].y), fmaxf(s2[4] + vm[2].y, s2[6] + vm[3].y));
+                float c1 = fmaxf(fmaxf(s2[1] + vm[0].y, s2[3] + vm[1].y), fmaxf(s2[5] + vm[2].y, s2[7] + vm[3].y));
+                if (__any_sync(0xffffffffu, c0 > M[0] + MAX_SLACK || c1 > M[1] + MAX_SLACK)) {
+#pragma unroll
+                    for (int o = 4; o < 32; o <<= 1) {
+                        c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, o));
+                        c1 = fmaxf(c1, __shfl_xor_sync(0xffffffffu, c1, o));
+                    }
+                    const float n0 = fmaxf(M[0], c0), n1 = fmaxf(M[1], c1);
+                    const float al0 = fast_exp2(M[0] - n0), al1 = fast_exp2(M[1] - n1);
+                    M[0] = n0;
+                    M[1] = n1;
+                    lsum[0] *= al0;
+                    lsum[1] *= al1;
+#pragma unroll
+                    for (int mt = 0; mt < STEPS; ++mt) {
+                        oacc[mt][0] *= al0;
+                        oacc[mt][1] *= al1;
+                        oacc[mt][2] *= al0;
+                        oacc[mt][3] *= al1;
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float pa = fast_exp2(s2[2 * k] - M[0]), pc = fast_exp2(s2[2 * k + 1] - M[1]);
+                    lsum[0] += pa;
+                    lsum[1] += pc;
+                    pb[k] = movmatrix_trans(pack_f16x2(pa * vm[k].x, pc * vm[k].x));
+                }
             }
             // ---- O^T += V^T P^T
             v_accum(st_s + vt_off, vsc_c, pb[0], pb[1]);
@@ -811,99 +846,34 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
             if (i_left > 0) copy_tile();
         }
 
-        // ================================================================ merge the warps, write
-        // Warps 0 and 1 store their accumulators, scaled to the common maximum, into two buffers;
-        // warps 2 and 3 add theirs; the sum of the two buffers is the segment's result (fixed order).
+        // ================================================================ this warp's partial result of the column
 #pragma unroll
         for (int o = 4; o < 32; o <<= 1) {
             lsum[0] += __shfl_xor_sync(0xffffffffu, lsum[0], o);
             lsum[1] += __shfl_xor_sync(0xffffffffu, lsum[1], o);
         }
-        __syncthreads();  // every warp has its query fragments: the staging buffer becomes the merge buffer
-        if (g == 0) {
-            m_M[warp * PACK + 2 * c] = M[0];
-            m_M[warp * PACK + 2 * c + 1] = M[1];
-            m_L[warp * PACK + 2 * c] = lsum[0];
-            m_L[warp * PACK + 2 * c + 1] = lsum[1];
-        }
-        __syncthreads();
-        {
-            float ms0 = -1e30f, ms1 = -1e30f;
-#pragma unroll
-            for (int w = 0; w < DW; ++w) {
-                ms0 = fmaxf(ms0, m_M[w * PACK + 2 * c]);
-                ms1 = fmaxf(ms1, m_M[w * PACK + 2 * c + 1]);
-            }
-            const float f0 = fast_exp2(M[0] - ms0), f1 = fast_exp2(M[1] - ms1);
-            float *dst = mbuf + (warp & 1) * PACK * HD;
-#pragma unroll
-            for (int round = 0; round < DW / 2; ++round) {
-                if ((warp >> 1) == round) {
-#pragma unroll
-                    for (int mt = 0; mt < STEPS; ++mt) {
-                        const int d0 = g * (HD / 8) + 2 * mt;
-                        float2 *o0 = reinterpret_cast<float2 *>(dst + (2 * c) * HD + d0);
-                        float2 *o1 = reinterpret_cast<float2 *>(dst + (2 * c + 1) * HD + d0);
-                        float2 a = make_float2(oacc[mt][0] * f0, oacc[mt][2] * f0), b = make_float2(oacc[mt][1] * f1, oacc[mt][3] * f1);
-                        if (round) {
-                            const float2 pa = *o0, pc = *o1;
-                            a.x += pa.x; a.y += pa.y; b.x += pc.x; b.y += pc.y;
-                        }
-                        *o0 = a;
-                        *o1 = b;
-                    }
-                }
-                __syncthreads();
-            }
-        }
-        // thread -> (row, slice of dims)
-        constexpr int TPR = DW * 32 / PACK;  // threads per row
-        constexpr int DPT = HD / TPR;        // dims per thread
-        const int rr = tid / TPR, dsl = (tid % TPR) * DPT;
-        float mstar = -1e30f;
-#pragma unroll
-        for (int w = 0; w < DW; ++w) mstar = fmaxf(mstar, m_M[w * PACK + rr]);
-        float L = 0.0f;
-#pragma unroll
-        for (int w = 0; w < DW; ++w) L += fast_exp2(m_M[w * PACK + rr] - mstar) * m_L[w * PACK + rr];
-        const float invL = L > 0.0f ? 1.0f / L : 0.0f;
-        float res[DPT];
-#pragma unroll
-        for (int i = 0; i < DPT; ++i) res[i] = (mbuf[(size_t)rr * HD + dsl + i] + mbuf[(size_t)(PACK + rr) * HD + dsl + i]) * invL;
-        const uint32_t r = pack * PACK + rr;
         const uint32_t colidx = seg.b * ny + seg.y;
-        const bool whole = seg.t0 == 0 && seg.t1 == (uint32_t)col.units;  // this block saw every unit of the column
-        if (seg.t0 == 0 && tid == 0 && p.meta) {
-            // the block that owns the first unit of a column publishes where its segments are
-            const uint32_t last_owner = owner_of_unit(seg.x + col.units - 1, total, nc);
-            p.meta[2 * (size_t)colidx] = (int32_t)(blockIdx.x + colidx);
-            p.meta[2 * (size_t)colidx + 1] = (int32_t)(last_owner - blockIdx.x + 1);
+        if (seg.t0 == 0 && lane == 0) {
+            // the worker that owns the first tile of a column publishes where its segments are
+            const uint32_t last_owner = owner_of(seg.x + col.tiles - 1, total, nw);
+            p.meta[2 * (size_t)colidx] = (int32_t)(wid + colidx);
+            p.meta[2 * (size_t)colidx + 1] = (int32_t)(last_owner - wid + 1);
         }
-        if (!whole) {
-            if (r < R) {
-                const size_t slot = ((size_t)blockIdx.x + colidx) * PACK + rr;
-                float *po = p.part_o + slot * HD + dsl;
+        {
+            const size_t slot = (size_t)wid + colidx;
+            const float inv0 = lsum[0] > 0.0f ? 1.0f / lsum[0] : 0.0f, inv1 = lsum[1] > 0.0f ? 1.0f / lsum[1] : 0.0f;
+            const uint32_t rr0 = 2 * c, rr1 = 2 * c + 1;
+            const bool w0 = rr0 < prow && pack * PACK + rr0 < R, w1 = rr1 < prow && pack * PACK + rr1 < R;
+            float *po0 = p.part_o + (slot * prow + rr0) * HD + g * (HD / 8);
+            float *po1 = p.part_o + (slot * prow + rr1) * HD + g * (HD / 8);
 #pragma unroll
-                for (int i = 0; i < DPT; ++i) po[i] = res[i];
-                if (tid % TPR == 0) p.part_lse[slot] = L > 0.0f ? mstar * LN2 + logf(L) : -INFINITY;
+            for (int mt = 0; mt < STEPS; ++mt) {
+                if (w0) *reinterpret_cast<float2 *>(po0 + 2 * mt) = make_float2(oacc[mt][0] * inv0, oacc[mt][2] * inv0);
+                if (w1) *reinterpret_cast<float2 *>(po1 + 2 * mt) = make_float2(oacc[mt][1] * inv1, oacc[mt][3] * inv1);
             }
-        } else {
-            // the whole column in one segment: final rows (rotated back with the value signs when the cache is rotated)
-            if (p.v.rot == B200_ROT_HADAMARD) {
-                __syncthreads();
-#pragma unroll
-                for (int i = 0; i < DPT; ++i) mbuf[(size_t)rr * HD + dsl + i] = res[i];
-                __syncthreads();
-                for (int q = warp; q < PACK; q += DW) warp_hadamard(mbuf + q * HD, HD, p.v.signs, false, lane);
-                __syncthreads();
-#pragma unroll
-                for (int i = 0; i < DPT; ++i) res[i] = mbuf[(size_t)rr * HD + dsl + i];
-            }
-            if (r < R) {
-                const uint32_t i0 = p.lq == 1 ? 0u : r / G, h = hk * G + (p.lq == 1 ? r : r % G);
-                const size_t obase = seg.b * p.o_sb + h * p.o_sh + i0 * p.o_ss;
-#pragma unroll
-                for (int i = 0; i < DPT; ++i) store_elem_rt(p.out, obase + dsl + i, res[i], p.out_dtype);
+            if (g == 0) {
+                if (w0) p.part_lse[slot * prow + rr0] = lsum[0] > 0.0f ? M[0] * LN2 + logf(lsum[0]) : -INFINITY;
+                if (w1) p.part_lse[slot * prow + rr1] = lsum[1] > 0.0f ? M[1] * LN2 + logf(lsum[1]) : -INFINITY;
             }
         }
         more = next_segment(seg, p, ny, x_end);
@@ -911,15 +881,15 @@ __global__ void __launch_bounds__(DW * 32, 3) tq_decode_kernel(const DecodeParam
     if (wait_failed && p.status) atomicExch(p.status, 1);
 }
 
-// Merges the segments of one output row (candle-core/kernels/turbo_quant_impl.h:659-685), rotates it
-// back and casts it. Rows whose block wrote the final result itself (one segment) are skipped; rows
-// of columns without any visible key are zeroed here.
+// Merges the partial results of one output row (candle-core/kernels/turbo_quant_impl.h:659-685),
+// rotates it back and casts it; rows of columns without any visible key are zeroed here.
 template <int HD>
 __global__ void __launch_bounds__(128) tq_combine_kernel(const DecodeParams p) {
     __shared__ float rowbuf[4][HD];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t rows = (size_t)p.b * p.hq * p.lq;
     const uint32_t ny = p.hkv * p.packs;
+    const uint32_t prow = min((uint32_t)PACK, p.rows_per_kv);
     for (size_t row = (size_t)blockIdx.x * 4 + warp; row < rows; row += (size_t)gridDim.x * 4) {
         const uint32_t i = (uint32_t)(row % p.lq);
         const uint32_t h = (uint32_t)((row / p.lq) % p.hq);
@@ -927,27 +897,26 @@ __global__ void __launch_bounds__(128) tq_combine_kernel(const DecodeParams p) {
         const uint32_t hk = h / p.group, r = i * p.group + h % p.group;
         const uint32_t y = hk * p.packs + r / PACK, rr = r % PACK;
         const size_t obase = b * p.o_sb + h * p.o_sh + i * p.o_ss;
-        if (make_column(p, b).units == 0) {
+        if (make_column(p, b).tiles == 0) {
 #pragma unroll
             for (int k = 0; k < HD / 32; ++k) store_elem_rt(p.out, obase + lane + 32 * k, 0.0f, p.out_dtype);
             continue;
         }
         const size_t col = (size_t)b * ny + y;
         const int first = p.meta[2 * col], ns = p.meta[2 * col + 1];
-        if (ns <= 1) continue;
-        const size_t slot0 = (size_t)first * PACK + rr;
+        const size_t slot0 = (size_t)first * prow + rr;
         float mx = -INFINITY;
-        for (int s = 0; s < ns; ++s) mx = fmaxf(mx, p.part_lse[slot0 + (size_t)s * PACK]);
+        for (int s = 0; s < ns; ++s) mx = fmaxf(mx, p.part_lse[slot0 + (size_t)s * prow]);
         float acc[HD / 32];
 #pragma unroll
         for (int k = 0; k < HD / 32; ++k) acc[k] = 0.0f;
         float wsum = 0.0f;
         for (int s = 0; s < ns; ++s) {
-            const float e = p.part_lse[slot0 + (size_t)s * PACK];
+            const float e = p.part_lse[slot0 + (size_t)s * prow];
             const float w = e == -INFINITY ? 0.0f : expf(e - mx);
             wsum += w;
             if (w != 0.0f) {
-                const float *po = p.part_o + (slot0 + (size_t)s * PACK) * HD;
+                const float *po = p.part_o + (slot0 + (size_t)s * prow) * HD;
 #pragma unroll
                 for (int k = 0; k < HD / 32; ++k) acc[k] += w * po[lane + 32 * k];
             }
