@@ -6,5 +6,5 @@ path of Qntology/candle-rocm-vulkan).
 so load it with `__graft_entry__.load_package()`, which registers it as `candle_rocm_vulkan_b200`.
 """
 from . import _abi  # noqa: F401
-from .turbo_quant import (FlashAttnConfig, QuantFormat, QuantizedTensor, TurboKvCache, TurboQuantizer,  # noqa: F401
-                          attention_packed)
+from .turbo_quant import (FlashAttnConfig, PackedAttention, QuantFormat, QuantizedTensor, TurboKvCache,  # noqa: F401
+                          TurboQuantizer, attention_packed)

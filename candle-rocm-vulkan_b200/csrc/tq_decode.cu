@@ -222,9 +222,22 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
     {
         const size_t rows = (size_t)a->b * a->hq * a->lq;
         const unsigned gx = (unsigned)std::min<size_t>((rows + 3) / 4, (size_t)sm_count_cached() * 16);
-        if (a->d == 64) tq_combine_kernel<64><<<gx, 128, 0, stream>>>(p);
-        else if (a->d == 128) tq_combine_kernel<128><<<gx, 128, 0, stream>>>(p);
-        else tq_combine_kernel<256><<<gx, 128, 0, stream>>>(p);
+        // the combine grid is launched while the decode grid still runs and waits on the device for
+        // its completion (programmatic dependent launch): its launch latency is off the critical path
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(gx);
+        cfg.blockDim = dim3(128);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e;
+        if (a->d == 64) e = cudaLaunchKernelEx(&cfg, tq_combine_kernel<64>, p);
+        else if (a->d == 128) e = cudaLaunchKernelEx(&cfg, tq_combine_kernel<128>, p);
+        else e = cudaLaunchKernelEx(&cfg, tq_combine_kernel<256>, p);
+        if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "tq_combine: %s", cudaGetErrorString(e));
         return check_launch("tq_combine");
     }
 }

@@ -259,6 +259,8 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
     if constexpr (VM == B200_TURBO_MSE)
         for (int i = tid; i < 256; i += DW * 32) sts32(lut_v + 4 * i, pack_f16x2(p.v.tab[i & 15], p.v.tab[i >> 4]));
     __syncthreads();
+    // the combine kernel may be scheduled from here on; it waits for this grid's completion itself
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // ------------------------------------------------------------------ this warp's share of the work
     const uint32_t cc = p.col_cost;
@@ -890,6 +892,9 @@ __global__ void __launch_bounds__(128) tq_combine_kernel(const DecodeParams p) {
     const size_t rows = (size_t)p.b * p.hq * p.lq;
     const uint32_t ny = p.hkv * p.packs;
     const uint32_t prow = min((uint32_t)PACK, p.rows_per_kv);
+    // launched with programmatic stream serialization: wait here until the decode grid has finished
+    // and its partial results are visible
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (size_t row = (size_t)blockIdx.x * 4 + warp; row < rows; row += (size_t)gridDim.x * 4) {
         const uint32_t i = (uint32_t)(row % p.lq);
         const uint32_t h = (uint32_t)((row / p.lq) % p.hq);

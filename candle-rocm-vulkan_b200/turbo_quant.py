@@ -252,60 +252,79 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
     return ws
 
 
+class PackedAttention:
+    """A prepared `attention_packed` call: arguments checked and marshalled once, `run()` only
+    launches (a few microseconds of host time, and capturable in a CUDA graph after one warm-up
+    call). The tensors given here are read / written by every `run()`; keep them alive."""
+
+    def __init__(self, q: torch.Tensor, k_rows: torch.Tensor, v_rows: torch.Tensor, kv_len, kq: TurboQuantizer,
+                 vq: TurboQuantizer, cfg: FlashAttnConfig, out: Optional[torch.Tensor] = None):
+        _need_cuda(q, "q")
+        b, hq, lq, d = q.shape
+        bk, hkv, cap, kw = k_rows.shape
+        bv, hv, capv, vw = v_rows.shape
+        ragged = isinstance(kv_len, torch.Tensor)
+        lk = cap if ragged else int(kv_len)
+        if bk != b or bv != b or hv != hkv or capv < lk or cap < lk or (not ragged and lk == 0):
+            raise ValueError(f"turbo-quant attention: q {tuple(q.shape)} / k {tuple(k_rows.shape)} / v {tuple(v_rows.shape)}"
+                             f" / kv_len {kv_len} do not match")
+        if kw < kq.row_words() or vw < vq.row_words() or d != kq.dim or d != vq.dim:
+            raise ValueError(f"turbo-quant attention: rows of {kw} / {vw} words and head dim {d} do not match the "
+                             f"quantizers ({kq.row_words()} / {vq.row_words()} words, dim {kq.dim})")
+        if q.stride(3) != 1:
+            q = q.contiguous()
+        if k_rows.stride(3) != 1 or v_rows.stride(3) != 1:
+            raise ValueError("turbo-quant attention: packed rows must be contiguous along the words")
+        if out is None:
+            out = torch.empty((b, hq, lq, d), dtype=q.dtype, device=q.device)
+        wl, wr = cfg.window_i32()
+        alibi, abs_ = None, 0
+        if cfg.alibi_slopes is not None:
+            alibi = cfg.alibi_slopes.to(device=q.device, dtype=torch.float32).contiguous()
+            if alibi.shape == (hq,):
+                abs_ = 0
+            elif alibi.shape == (b, hq):
+                abs_ = hq
+            else:
+                raise ValueError(f"flash-attn: alibi slopes must be ({hq}) or ({b}, {hq}), got {tuple(alibi.shape)}")
+        args = A.TqAttnArgs()
+        args.q, args.out = q.data_ptr(), out.data_ptr()
+        args.q_dtype, args.out_dtype = _dtype_id(q), _dtype_id(out)
+        args.q_strides, args.out_strides = A.u64x3(*q.stride()[:3]), A.u64x3(*out.stride()[:3])
+        args.k_rows, args.v_rows = k_rows.data_ptr(), v_rows.data_ptr()
+        args.k_strides, args.v_strides = A.u64x3(*k_rows.stride()[:3]), A.u64x3(*v_rows.stride()[:3])
+        args.pages, args.n_pages = None, 0
+        args.kv_len_dev = kv_len.data_ptr() if ragged else None
+        args.b, args.lq, args.lk, args.hq, args.hkv, args.d = b, lq, lk, hq, hkv, d
+        args.kq, args.vq = kq.side(), vq.side()
+        args.scale, args.softcap = cfg.softmax_scale, cfg.softcap or 0.0
+        args.wl, args.wr = wl, wr
+        args.alibi, args.alibi_bstride = (alibi.data_ptr() if alibi is not None else None), abs_
+        args.splits = cfg.splits
+        nbytes = A.lib().b200_tq_attention_workspace_bytes(C.byref(args))
+        if nbytes == 0:
+            A.check(A.lib().b200_tq_attention(C.byref(args), None))  # reports why the call cannot be planned
+        ws = _workspace(q.device, nbytes)
+        args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+        args.status = None
+        self.args, self.out, self.device = args, out, q.device
+        self._keep = (q, k_rows, v_rows, kv_len, kq, vq, alibi, ws)
+        self._fn, self._ref = A.lib().b200_tq_attention, C.byref(args)
+
+    def run(self) -> torch.Tensor:
+        rc = self._fn(self._ref, torch.cuda.current_stream(self.device).cuda_stream)
+        if rc:
+            A.check(rc)
+        return self.out
+
+
 def attention_packed(q: torch.Tensor, k_rows: torch.Tensor, v_rows: torch.Tensor, kv_len, kq: TurboQuantizer,
                      vq: TurboQuantizer, cfg: FlashAttnConfig, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of `q: (batch, q_heads, seq_q, head_dim)` over packed rows `k_rows: (batch,
     kv_heads, capacity, k_words)`, `v_rows: (..., v_words)` (turbo_quant.rs:993-1072). `kv_len`: the
     number of valid rows, an int (all sequences) or an int32 device tensor with one length per
     batch entry (ragged batch). Output in `q`'s dtype and layout."""
-    _need_cuda(q, "q")
-    b, hq, lq, d = q.shape
-    bk, hkv, cap, kw = k_rows.shape
-    bv, hv, capv, vw = v_rows.shape
-    ragged = isinstance(kv_len, torch.Tensor)
-    lk = cap if ragged else int(kv_len)
-    if bk != b or bv != b or hv != hkv or capv < lk or cap < lk or (not ragged and lk == 0):
-        raise ValueError(f"turbo-quant attention: q {tuple(q.shape)} / k {tuple(k_rows.shape)} / v {tuple(v_rows.shape)}"
-                         f" / kv_len {kv_len} do not match")
-    if kw < kq.row_words() or vw < vq.row_words() or d != kq.dim or d != vq.dim:
-        raise ValueError(f"turbo-quant attention: rows of {kw} / {vw} words and head dim {d} do not match the "
-                         f"quantizers ({kq.row_words()} / {vq.row_words()} words, dim {kq.dim})")
-    if q.stride(3) != 1:
-        q = q.contiguous()
-    if k_rows.stride(3) != 1 or v_rows.stride(3) != 1:
-        raise ValueError("turbo-quant attention: packed rows must be contiguous along the words")
-    if out is None:
-        out = torch.empty((b, hq, lq, d), dtype=q.dtype, device=q.device)
-    wl, wr = cfg.window_i32()
-    alibi, abs_ = None, 0
-    if cfg.alibi_slopes is not None:
-        alibi = cfg.alibi_slopes.to(device=q.device, dtype=torch.float32).contiguous()
-        if alibi.shape == (hq,):
-            abs_ = 0
-        elif alibi.shape == (b, hq):
-            abs_ = hq
-        else:
-            raise ValueError(f"flash-attn: alibi slopes must be ({hq}) or ({b}, {hq}), got {tuple(alibi.shape)}")
-    args = A.TqAttnArgs()
-    args.q, args.out = q.data_ptr(), out.data_ptr()
-    args.q_dtype, args.out_dtype = _dtype_id(q), _dtype_id(out)
-    args.q_strides, args.out_strides = A.u64x3(*q.stride()[:3]), A.u64x3(*out.stride()[:3])
-    args.k_rows, args.v_rows = k_rows.data_ptr(), v_rows.data_ptr()
-    args.k_strides, args.v_strides = A.u64x3(*k_rows.stride()[:3]), A.u64x3(*v_rows.stride()[:3])
-    args.pages, args.n_pages = None, 0
-    args.kv_len_dev = kv_len.data_ptr() if ragged else None
-    args.b, args.lq, args.lk, args.hq, args.hkv, args.d = b, lq, lk, hq, hkv, d
-    args.kq, args.vq = kq.side(), vq.side()
-    args.scale, args.softcap = cfg.softmax_scale, cfg.softcap or 0.0
-    args.wl, args.wr = wl, wr
-    args.alibi, args.alibi_bstride = (alibi.data_ptr() if alibi is not None else None), abs_
-    args.splits = cfg.splits
-    nbytes = A.lib().b200_tq_attention_workspace_bytes(C.byref(args))
-    ws = _workspace(q.device, nbytes)
-    args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
-    args.status = None
-    A.check(A.lib().b200_tq_attention(C.byref(args), _stream(q.device)))
-    return out
+    return PackedAttention(q, k_rows, v_rows, kv_len, kq, vq, cfg, out).run()
 
 
 class TurboKvCache:

@@ -31,10 +31,15 @@ def fmt(P, mode, bits=4):
     return P.QuantFormat(mode, bits)
 
 
-def assert_close(got, want, atol=ATOL, rtol=RTOL, what=""):
+# half an ulp of the output dtype, relative: the kernels round their f32 result once to that dtype
+HALF_ULP = {"f32": 0.0, "f16": 2.0 ** -12, "bf16": 2.0 ** -9}
+
+
+def assert_close(got, want, atol=ATOL, rtol=RTOL, what="", out="f32"):
+    """|got - want| <= atol + rtol |want| on the f32 result, plus the final rounding to `out`."""
     got = np.asarray(got, dtype=np.float32)
     want = np.asarray(want, dtype=np.float32)
     err = np.abs(got - want)
-    bad = err > atol + rtol * np.abs(want)
+    bad = err > atol + (rtol + HALF_ULP[out]) * np.abs(want)
     assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} out of tolerance, max abs err {err.max():.3e}"
     return float(err.max())

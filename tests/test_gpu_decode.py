@@ -93,7 +93,7 @@ def test_all_format_pairs_d128(P, oracle, kf, vf):
     q = oracle.normal(77, b * hq * d).reshape(b, hq, 1, d)
     want = oracle.tq_attention(oracle.round_to(q, "bf16"), kd, vd, lk, kf, vf, 0.0884, tab, wr=0)
     got = run_packed(P, q, kd, vd, lk, kf, vf, 0.0884, qdt="bf16", wr=0)
-    assert_close(got, want, what=f"k{kf} v{vf}")
+    assert_close(got, want, what=f"k{kf} v{vf}", out="bf16")
 
 
 @pytest.mark.parametrize("d", [64, 256])
@@ -104,7 +104,7 @@ def test_other_head_dims(P, oracle, d, f):
     q = oracle.normal(78, b * hq * 2 * d).reshape(b, hq, 2, d)
     want = oracle.tq_attention(oracle.round_to(q, "f16"), kd, vd, lk, f, f, d ** -0.5, tab, wr=0)
     got = run_packed(P, q, kd, vd, lk, f, f, d ** -0.5, qdt="f16", wr=0)
-    assert_close(got, want, what=f"d{d} m{f}")
+    assert_close(got, want, what=f"d{d} m{f}", out="f16")
 
 
 @pytest.mark.parametrize("lk", [1, 2, 15, 16, 17, 31, 32, 33, 127, 128, 129, 255, 257, 511, 640, 1025])
@@ -126,7 +126,7 @@ def test_ragged_batch_is_per_sequence_attention(P, oracle):
     q = oracle.normal(80, b * hq * d).reshape(b, hq, 1, d)
     got = run_packed(P, q, kd, vd, lens, (2, 4), (2, 4), 0.0884, qdt="bf16", wr=0)
     want = oracle.tq_attention(oracle.round_to(q, "bf16"), kd, vd, cap, (2, 4), (2, 4), 0.0884, tab, kv_len=lens, wr=0)
-    assert_close(got, want, what="ragged")
+    assert_close(got, want, what="ragged", out="bf16")
     for bi in (0, 2, 5):  # and each sequence alone gives the same bits as inside the batch
         one = run_packed(P, q[bi:bi + 1], kd[bi:bi + 1], vd[bi:bi + 1], int(lens[bi]), (2, 4), (2, 4), 0.0884, qdt="bf16", wr=0)
         assert_close(one, got[bi:bi + 1], atol=1e-2, rtol=8e-3, what=f"sequence {bi}")  # one bf16 ulp
@@ -211,7 +211,7 @@ def test_hadamard_cache_end_to_end(P, oracle, f):
     qr = oracle.rotate_rows(oracle.round_to(q, "bf16").reshape(-1, d), pk).reshape(q.shape)
     o = oracle.tq_attention(qr, kd, vd, lk, f, f, 0.0884, np.concatenate([tab, tab]), wr=0)
     want = oracle.rotate_rows(o.reshape(-1, d), pv, transpose=True).reshape(o.shape)
-    assert_close(got, want, what=f"hadamard {f}")
+    assert_close(got, want, what=f"hadamard {f}", out="bf16")
 
 
 def test_config1_fp8_single_decode(P, oracle):
@@ -227,12 +227,12 @@ def test_config1_fp8_single_decode(P, oracle):
     vd = oracle.quantize_rows(oracle.round_to(vx, "f16").reshape(-1, d), 5).reshape(b, hkv, lk, -1)
     assert np.array_equal(words(cache.k), kd) and np.array_equal(words(cache.v), vd)
     want = oracle.tq_attention(oracle.round_to(q, "f16"), kd, vd, lk, (5, 4), (5, 4), d ** -0.5, wr=0)
-    assert_close(got, want, what="config 1")
+    assert_close(got, want, what="config 1", out="f16")
     # the unfused CPU path of the reference: dequantize to the cache dtype, then matmul softmax matmul
     kdq = oracle.round_to(oracle.dequantize_rows(kd.reshape(-1, 34), d, 5), "f16").reshape(b, hkv, lk, d).transpose(0, 2, 1, 3)
     vdq = oracle.round_to(oracle.dequantize_rows(vd.reshape(-1, 34), d, 5), "f16").reshape(b, hkv, lk, d).transpose(0, 2, 1, 3)
     unf = oracle.unfused_attention(oracle.round_to(q, "f16").transpose(0, 2, 1, 3), kdq, vdq, d ** -0.5, wr=0).transpose(0, 2, 1, 3)
-    assert_close(got, unf, what="config 1 vs the unfused path")
+    assert_close(got, unf, what="config 1 vs the unfused path", out="f16")
 
 
 def test_full_size_properties_config2(P, oracle):
@@ -257,7 +257,7 @@ def test_full_size_properties_config2(P, oracle):
         kx = k[bi, :, :L].float().cpu().numpy().reshape(-1, d)
         assert np.array_equal(kd.reshape(-1, 19), oracle.quantize_rows(kx, 2))
         want = oracle.tq_attention(q[bi:bi + 1].float().cpu().numpy(), kd, vd, L, (2, 4), (2, 4), d ** -0.5, wr=0)
-        assert_close(out[bi:bi + 1].float().cpu().numpy(), want, what=f"sequence {bi}")
+        assert_close(out[bi:bi + 1].float().cpu().numpy(), want, what=f"sequence {bi}", out="bf16")
     # 2. the split count does not change the result beyond rounding
     cfg2 = P.FlashAttnConfig(d ** -0.5).causal()
     cfg2.splits = 3
