@@ -316,6 +316,11 @@ def run_ours(args, w, rank, world, local_rank):
             cpu = {"value": cb / dt / 1e9, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
                    "sample": f"{nseq} of {b} sequences, one pass ({dt:.2f} s): dequantize rows to {w['qdt']} + unfused attention"}
         launches_per_step = 2 if (int(lens.max()) > 128) else 1
+        # dram__bytes_read.sum + dram__bytes_write.sum of one tq_decode_kernel launch, from the ncu capture of this same
+        # workload (profiles/tq_decode_kernel_c2_mxfp4.md): 360.75 MB read + 7.54 MB written
+        traffic, traffic_src = None, None
+        if args.workload == "c2" and not args.uniform_len and world == 1:
+            traffic, traffic_src = 368_288_000, "ncu capture of this workload, profiles/tq_decode_kernel_c2_mxfp4.md"
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 mma / f32 softmax",
@@ -334,7 +339,8 @@ def run_ours(args, w, rank, world, local_rank):
             "gpu_launches": args.steps * launches_per_step,
             "roofline": {"bound": "hbm", "kernel": "tq_decode_kernel (+ tq_combine_kernel in the same timed call)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": peak_kind, "traffic": None},
+                         "peak_source": peak_kind, "traffic": traffic, "traffic_unit": "bytes per launch",
+                         "traffic_source": traffic_src},
             "cpu_baseline": cpu, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
