@@ -6,5 +6,6 @@ path of Qntology/candle-rocm-vulkan).
 so load it with `__graft_entry__.load_package()`, which registers it as `candle_rocm_vulkan_b200`.
 """
 from . import _abi  # noqa: F401
+from . import flash_attn  # noqa: F401
 from .turbo_quant import (FlashAttnConfig, PackedAttention, QuantFormat, QuantizedTensor, TurboKvCache,  # noqa: F401
                           TurboQuantizer, attention_packed)

@@ -1,0 +1,226 @@
+"""GPU parity of the attention over dense K / V (b200_flash_attn, b200_fa_prefill_append) through the C
+ABI: against the outputs of the reference's fa_row / fa2 / fa3 kernels (golden fixtures), against the
+CPU oracle on seeded inputs, and through properties at prefill sizes."""
+import importlib.util
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import assert_close, fmt, pkg, to_dev, words
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+spec = importlib.util.spec_from_file_location("make_golden", ROOT / "tests" / "golden" / "make_golden.py")
+MG = importlib.util.module_from_spec(spec)
+spec.loader.exec_module(MG)
+QN = {0: "f32", 1: "f16", 2: "bf16"}
+
+
+@pytest.fixture(scope="module")
+def P():
+    return pkg()
+
+
+def fp8_dev(oracle, x):
+    """f32 -> E4M3 codes on the device (uint8) and the values they decode to."""
+    codes = oracle.f32_to_e4m3(x).astype(np.uint8).reshape(x.shape)
+    return torch.from_numpy(codes).to("cuda:0"), oracle.e4m3_to_f32(codes).reshape(x.shape)
+
+
+def cfg_of(P, d, wl=-1, wr=-1, softcap=0.0, alibi=None, kd=1.0, vd=1.0, scale=None):
+    c = P.FlashAttnConfig(scale if scale is not None else 1.0 / np.sqrt(d))
+    c.window_size_left = None if wl < 0 else wl
+    c.window_size_right = None if wr < 0 else wr
+    c.softcap = softcap or None
+    c.k_descale, c.v_descale = kd, vd
+    if alibi is not None:
+        c.alibi_slopes = to_dev(alibi)
+    return c
+
+
+@pytest.mark.parametrize("case", MG.FA_CASES, ids=lambda c: c[0])
+def test_against_reference_kernel_outputs(P, oracle, golden, case):
+    name, qd, kvd, kind, version, b, lq, lk, hq, hkv, d, splits, group, wl, wr, softcap, varlen = case
+    q, k, v = MG.fa_inputs(case)
+    qn = QN[qd]
+    F = P.flash_attn
+    qt = to_dev(q, qn)
+    kdesc = 1.0
+    if kvd == 1:
+        kt, _ = fp8_dev(oracle, k)
+        vt, _ = fp8_dev(oracle, v)
+        kdesc = 0.5
+    else:
+        kt, vt = to_dev(k, qn), to_dev(v, qn)
+    c = cfg_of(P, d, wl, wr, softcap, kd=kdesc)
+    if varlen:
+        cu_q = torch.from_numpy(MG.VARLEN_Q.astype(np.int32)).to("cuda:0")
+        cu_k = torch.from_numpy(MG.VARLEN_K.astype(np.int32)).to("cuda:0")
+        out = F.flash_attn_varlen_with_config(qt, kt, vt, cu_q, cu_k, 52, 70, c)
+    else:
+        out = F.flash_attn_with_config(qt, kt, vt, c)
+    torch.cuda.synchronize()
+    assert out.dtype == qt.dtype and out.shape == qt.shape
+    # the fixture holds the reference kernel's output rounded to the output dtype: one more half ulp
+    assert_close(out.float().cpu().numpy(), golden["flash_attn"][name], what=name, out=qn,
+                 rtol=2e-3 + {"f32": 0.0, "f16": 2.0 ** -12, "bf16": 2.0 ** -9}[qn])
+
+
+ORACLE_CASES = [
+    # name, qdt, b, lq, lk, hq, hkv, d, wl, wr, softcap, alibi, fp8
+    ("decode_split", "bf16", 2, 1, 3000, 8, 2, 128, -1, 0, 0.0, False, False),
+    ("decode_lq3_g8", "f16", 1, 3, 1500, 16, 2, 128, -1, 0, 0.0, False, False),
+    ("prefill_causal", "bf16", 2, 300, 300, 8, 2, 128, -1, 0, 0.0, False, False),
+    ("prefill_chunk", "f16", 1, 130, 450, 4, 4, 64, -1, 0, 0.0, False, False),
+    ("window_left", "bf16", 1, 200, 260, 4, 2, 128, 33, 0, 0.0, False, False),
+    ("window_both", "f16", 1, 150, 150, 2, 1, 64, 10, 7, 0.0, False, False),
+    ("softcap_alibi", "f16", 2, 70, 90, 4, 2, 128, -1, 0, 20.0, True, False),
+    ("full_noncausal", "f32", 1, 65, 129, 6, 3, 128, -1, -1, 0.0, False, False),
+    ("fp8_prefill", "bf16", 1, 100, 164, 8, 2, 128, -1, 0, 0.0, False, True),
+    ("fp8_decode_d64", "f16", 3, 1, 2100, 4, 1, 64, -1, 0, 0.0, False, True),
+    ("lq_longer_than_lk", "f16", 1, 80, 50, 2, 2, 64, -1, 0, 0.0, False, False),
+]
+
+
+@pytest.mark.parametrize("case", ORACLE_CASES, ids=lambda c: c[0])
+def test_against_oracle(P, oracle, case):
+    name, qn, b, lq, lk, hq, hkv, d, wl, wr, softcap, use_alibi, fp8 = case
+    seed = 500 + sum(ord(ch) for ch in name)
+    q = oracle.round_to(oracle.normal(seed, b * lq * hq * d).reshape(b, lq, hq, d), qn)
+    k = oracle.normal(seed + 1, b * lk * hkv * d).reshape(b, lk, hkv, d)
+    v = oracle.normal(seed + 2, b * lk * hkv * d).reshape(b, lk, hkv, d)
+    alibi = (0.05 * np.abs(oracle.normal(seed + 3, b * hq))).reshape(b, hq).astype(np.float32) if use_alibi else None
+    kd, vd = (0.75, 1.5) if fp8 else (1.0, 1.0)
+    if fp8:
+        kt, k = fp8_dev(oracle, k)
+        vt, v = fp8_dev(oracle, v)
+    else:
+        k, v = oracle.round_to(k, qn), oracle.round_to(v, qn)
+        kt, vt = to_dev(k, qn), to_dev(v, qn)
+    want = oracle.reference_attention(q, k, v, 1.0 / np.sqrt(d), wl=wl, wr=wr, softcap=softcap, alibi=alibi, k_descale=kd, v_descale=vd)
+    out = P.flash_attn.flash_attn_with_config(to_dev(q, qn), kt, vt, cfg_of(P, d, wl, wr, softcap, alibi, kd, vd))
+    torch.cuda.synchronize()
+    assert_close(out.float().cpu().numpy(), want, what=name, out=qn)
+
+
+def test_rows_without_visible_keys_are_zero(P, oracle):
+    # lq > lk under a causal window: the first lq - lk query rows see no key (flash_attn_impl.h: zeros)
+    b, lq, lk, hq, hkv, d = 1, 80, 50, 2, 2, 64
+    q = torch.randn((b, lq, hq, d), device="cuda:0", dtype=torch.float16)
+    k = torch.randn((b, lk, hkv, d), device="cuda:0", dtype=torch.float16)
+    v = torch.randn((b, lk, hkv, d), device="cuda:0", dtype=torch.float16)
+    out = P.flash_attn.flash_attn(q, k, v, 0.125, True)
+    torch.cuda.synchronize()
+    assert torch.count_nonzero(out[:, : lq - lk]) == 0
+    assert torch.isfinite(out).all()
+
+
+def test_bhsd_views_and_named_entry_points(P, oracle):
+    b, s, hq, hkv, d = 2, 96, 4, 2, 128
+    q = oracle.round_to(oracle.normal(1, b * hq * s * d).reshape(b, hq, s, d), "bf16")
+    k = oracle.round_to(oracle.normal(2, b * hkv * s * d).reshape(b, hkv, s, d), "bf16")
+    v = oracle.round_to(oracle.normal(3, b * hkv * s * d).reshape(b, hkv, s, d), "bf16")
+    F = P.flash_attn
+    qt, kt, vt = to_dev(q, "bf16"), to_dev(k, "bf16"), to_dev(v, "bf16")
+    want = oracle.reference_attention(q.transpose(0, 2, 1, 3), k.transpose(0, 2, 1, 3), v.transpose(0, 2, 1, 3), 0.1, wr=0)
+    got = F.flash_attn_bhsd(qt, kt, vt, P.FlashAttnConfig(0.1).causal())
+    torch.cuda.synchronize()
+    assert got.shape == qt.shape
+    assert_close(got.float().cpu().numpy().transpose(0, 2, 1, 3), want, what="bhsd", out="bf16")
+    a = F.flash_attn(qt.transpose(1, 2), kt.transpose(1, 2), vt.transpose(1, 2), 0.1, True)
+    w = F.flash_attn_windowed(qt.transpose(1, 2), kt.transpose(1, 2), vt.transpose(1, 2), 0.1, None, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(a, w) and torch.equal(a, got.transpose(1, 2))
+
+
+def test_varlen_equals_per_sequence_calls(P):
+    torch.manual_seed(5)
+    hq, hkv, d = 8, 2, 128
+    lens_q, lens_k = [5, 130, 1, 64], [70, 130, 900, 64]
+    cu_q = torch.tensor([0] + list(np.cumsum(lens_q)), dtype=torch.int32, device="cuda:0")
+    cu_k = torch.tensor([0] + list(np.cumsum(lens_k)), dtype=torch.int32, device="cuda:0")
+    q = torch.randn((sum(lens_q), hq, d), device="cuda:0", dtype=torch.bfloat16)
+    k = torch.randn((sum(lens_k), hkv, d), device="cuda:0", dtype=torch.bfloat16)
+    v = torch.randn((sum(lens_k), hkv, d), device="cuda:0", dtype=torch.bfloat16)
+    F = P.flash_attn
+    out = F.flash_attn_varlen(q, k, v, cu_q, cu_k, max(lens_q), max(lens_k), d ** -0.5, True)
+    for i in range(len(lens_q)):
+        qs, ks = slice(int(cu_q[i]), int(cu_q[i + 1])), slice(int(cu_k[i]), int(cu_k[i + 1]))
+        one = F.flash_attn(q[qs][None], k[ks][None], v[ks][None], d ** -0.5, True)[0]
+        assert_close(out[qs].float().cpu().numpy(), one.float().cpu().numpy(), atol=2e-3, what=f"sequence {i}", out="bf16")
+
+
+def test_fp8_helper_close_to_bf16_attention(P):
+    torch.manual_seed(6)
+    q = torch.randn((1, 64, 8, 128), device="cuda:0", dtype=torch.bfloat16)
+    k = torch.randn((1, 256, 2, 128), device="cuda:0", dtype=torch.bfloat16)
+    v = torch.randn((1, 256, 2, 128), device="cuda:0", dtype=torch.bfloat16)
+    F = P.flash_attn
+    cfg = P.FlashAttnConfig(128 ** -0.5).causal()
+    a, b8 = F.flash_attn_with_config(q, k, v, cfg), F.flash_attn_fp8(q, k, v, cfg)
+    assert (a.float() - b8.float()).abs().max() < 0.08  # E4M3 rounding of K and V: 2^-4 relative per element
+
+
+def test_prefill_at_full_size_matches_sampled_rows(P, oracle):
+    """The prefill chunk of the third benchmark configuration at a quarter of its batch: rows sampled
+    over the sequence are compared with the oracle run on exactly those query rows."""
+    b, s, hq, hkv, d = 1, 4096, 32, 8, 128
+    torch.manual_seed(7)
+    q = torch.randn((b, s, hq, d), device="cuda:0", dtype=torch.bfloat16)
+    k = torch.randn((b, s, hkv, d), device="cuda:0", dtype=torch.bfloat16)
+    v = torch.randn((b, s, hkv, d), device="cuda:0", dtype=torch.bfloat16)
+    out = P.flash_attn.flash_attn(q, k, v, d ** -0.5, True)
+    torch.cuda.synchronize()
+    kn, vn = k.float().cpu().numpy(), v.float().cpu().numpy()
+    for i in (0, 1, 63, 64, 1000, 2047, 4095):
+        # query row i sees keys 0..=i: one query over lk = i + 1 keys, causal
+        want = oracle.reference_attention(q[:, i:i + 1].float().cpu().numpy(), kn[:, : i + 1], vn[:, : i + 1], d ** -0.5, wr=0)
+        assert_close(out[:, i:i + 1].float().cpu().numpy(), want, what=f"row {i}", out="bf16")
+
+
+@pytest.mark.parametrize("rotation", ["none", "hadamard"])
+def test_prefill_append_gives_both_reference_results(P, oracle, rotation):
+    b, s, hq, hkv, d = 2, 200, 8, 2, 128
+    q = oracle.round_to(oracle.normal(11, b * s * hq * d).reshape(b, s, hq, d), "bf16")
+    k = oracle.round_to(oracle.normal(12, b * s * hkv * d).reshape(b, s, hkv, d), "bf16")
+    v = oracle.round_to(oracle.normal(13, b * s * hkv * d).reshape(b, s, hkv, d), "bf16")
+    nv = fmt(P, 3)
+    kq, vq = P.TurboQuantizer(nv, d, rotation, 42), P.TurboQuantizer(nv, d, rotation, 44)
+    cap, pos = 256, 16
+    kc = torch.zeros((b, hkv, cap, kq.row_words()), dtype=torch.int32, device="cuda:0")
+    vc = torch.zeros_like(kc)
+    out = P.flash_attn.prefill_append(to_dev(q, "bf16"), to_dev(k, "bf16"), to_dev(v, "bf16"), P.FlashAttnConfig(d ** -0.5).causal(),
+                                      kc, vc, kq, vq, pos)
+    torch.cuda.synchronize()
+    want = oracle.reference_attention(q, k, v, d ** -0.5, wr=0)
+    assert_close(out.float().cpu().numpy(), want, what="prefill output", out="bf16")
+    # cache rows: bit-exact with the reference's quantizer on the same (rotated) rows
+    # (with the Hadamard rotation: on the rows the device butterflies give, which agree with the
+    # reference's matmul to rounding; tests/test_gpu_quant.py checks that stage by itself)
+    for t, cache, qz in ((k, kc, kq), (v, vc, vq)):
+        rows = t.transpose(0, 2, 1, 3).reshape(-1, d)
+        if rotation == "hadamard":
+            rows = qz.rotate(to_dev(rows, "bf16")).cpu().numpy()
+        want_rows = oracle.quantize_rows(rows, 3).reshape(b, hkv, s, -1)
+        got = words(cache)
+        assert np.array_equal(got[:, :, pos:pos + s], want_rows)
+        assert not got[:, :, :pos].any() and not got[:, :, pos + s:].any()
+
+
+def test_argument_errors(P):
+    A = P._abi
+    F = P.flash_attn
+    q = torch.zeros((1, 4, 6, 128), device="cuda:0", dtype=torch.float16)
+    k = torch.zeros((1, 4, 4, 128), device="cuda:0", dtype=torch.float16)
+    with pytest.raises(ValueError, match="not a multiple"):
+        F.flash_attn(q, k, k, 1.0, False)
+    q96 = torch.zeros((1, 4, 4, 96), device="cuda:0", dtype=torch.float16)
+    with pytest.raises(A.B200Error) as e:
+        F.flash_attn(q96, q96, q96, 1.0, False)
+    assert e.value.code == A.ERR_UNSUPPORTED_SHAPE
+    with pytest.raises(A.B200Error, match="must match q"):
+        F.flash_attn(q[:, :, :4], k.to(torch.bfloat16), k.to(torch.bfloat16), 1.0, False)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        F.flash_attn(q.cpu(), k.cpu(), k.cpu(), 1.0, False)
