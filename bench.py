@@ -114,6 +114,24 @@ def cpu_reference_step(w, lens, nseq, reps=1):
     return dt, algorithmic_bytes(sub, lens)
 
 
+def aggregate_over_ranks(times_ms, nbytes, world, dev):
+    """(max over ranks of each time, sum over ranks of the bytes); every rank gets the same result."""
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor(list(times_ms), device=dev, dtype=torch.float64)
+    n = torch.tensor([float(nbytes)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(n, op=dist.ReduceOp.SUM)
+    return [float(x) for x in t.cpu()], float(n.cpu()[0])
+
+
+def clock_sample_steps(ms_per_step, seconds=0.6, cap=20000):
+    """Untimed steps that keep the device under the measured load while nvidia-smi samples its clocks. Computed
+    from the time already reduced over the ranks, so that all ranks run the same number of collectives."""
+    return int(min(cap, max(50, seconds * 1e3 / max(ms_per_step, 1e-3))))
+
+
 def run_reference(args, w, rank, world):
     if rank != 0:
         return
@@ -277,25 +295,17 @@ def run_ours(args, w, rank, world, local_rank):
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
+    # max over ranks of the times, sum over ranks of the bytes
+    (total_ms, e2e_ms, kern_ms), job_bytes = aggregate_over_ranks(
+        [total_ms, e2e_ms, float(np.mean(per_step))], algorithmic_bytes(w, lens), world, dev)
     # the timed regions last milliseconds: keep the same step running (untimed) until the clock sampler has seen
-    # at least half a second of this load
-    t_end = time.perf_counter() + 0.6
-    i = 0
-    while time.perf_counter() < t_end:
-        for _ in range(50):
-            step(i)
-            i += 1
-        torch.cuda.synchronize()
+    # about half a second of this load. Every rank runs the same number of steps (they hold a collective).
+    for i in range(clock_sample_steps(total_ms / args.steps)):
+        step(i)
+        if i % 50 == 49:
+            torch.cuda.synchronize()
+    torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
-
-    # max over ranks
-    times = torch.tensor([total_ms, e2e_ms, float(np.mean(per_step))], device=dev, dtype=torch.float64)
-    nbytes = torch.tensor([algorithmic_bytes(w, lens)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-        dist.all_reduce(nbytes, op=dist.ReduceOp.SUM)
-    total_ms, e2e_ms, kern_ms = [float(x) for x in times.cpu()]
-    job_bytes = float(nbytes.cpu()[0])
     if rank == 0:
         peaks = {}
         try:
