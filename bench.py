@@ -89,6 +89,9 @@ class ClockSampler:
 def cpu_reference_step(w, lens, nseq, reps=1):
     """The reference's CPU path for `nseq` sequences of the batch; returns (seconds per pass, bytes)."""
     from oracle import oracle as O
+    if os.environ.get("OMP_NUM_THREADS") == "1" and "LOCAL_RANK" in os.environ:
+        # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm runs on one rank and may use the host's cores
+        O.set_num_threads(len(os.sched_getaffinity(0)))
     d, hq, hkv = w["d"], w["hq"], w["hkv"]
     mode = w["mode"]
     bits = 4
@@ -165,14 +168,22 @@ def run_ours(args, w, rank, world, local_rank):
 
     import __graft_entry__ as G
 
+    t_start = time.perf_counter()
+
+    def stage(msg):
+        if args.verbose:
+            print(f"[bench rank {rank} +{time.perf_counter() - t_start:6.1f}s] {msg}", file=sys.stderr, flush=True)
+
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    stage("process group up")
     G.build()
     P = G.load_package()
+    stage("library loaded")
     A = P._abi
     b, hq, hkv, d = w["b"], w["hq"], w["hkv"], w["d"]
     tdt = {"bf16": torch.bfloat16, "f16": torch.float16}[w["qdt"]]
@@ -203,6 +214,7 @@ def run_ours(args, w, rank, world, local_rank):
             v = torch.randn((b, hkv, t, d), generator=g, device=dev, dtype=tdt) * chan
             _kv_append(k, v, kc, vc, kq, vq, p0)
         caches.append((kc, vc))
+    stage("caches filled")
     kv_len = torch.from_numpy(lens).to(dev)
     q_host = torch.randn((b, hq, 1, d), dtype=tdt).pin_memory()
     knew_host = torch.randn((b, hkv, 1, d), dtype=tdt).pin_memory()
@@ -225,6 +237,7 @@ def run_ours(args, w, rank, world, local_rank):
     for i in range(nbuf):
         eager_step(i)
     torch.cuda.synchronize()
+    stage("eager steps done")
     graphs = []
     use_graphs = os.environ.get("B200_BENCH_GRAPHS", "1") != "0"
     if use_graphs:
@@ -238,6 +251,8 @@ def run_ours(args, w, rank, world, local_rank):
             print(f"bench: CUDA graph capture failed ({e}); timing eager launches", file=sys.stderr)
             graphs = []
             torch.cuda.synchronize()
+
+    stage(f"graphs captured: {len(graphs)}")
 
     def step(i):
         if graphs:
@@ -266,6 +281,7 @@ def run_ours(args, w, rank, world, local_rank):
         ev[i + 1].record()
     barrier()
     total_ms = ev[0].elapsed_time(ev[args.steps])
+    stage("timed region done")
     per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
     # ---- end to end through the public API with host buffers: H2D of the step's inputs, append of the new
     # token, attention, D2H of the outputs
@@ -295,6 +311,7 @@ def run_ours(args, w, rank, world, local_rank):
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
+    stage("end-to-end region done")
     # max over ranks of the times, sum over ranks of the bytes
     (total_ms, e2e_ms, kern_ms), job_bytes = aggregate_over_ranks(
         [total_ms, e2e_ms, float(np.mean(per_step))], algorithmic_bytes(w, lens), world, dev)
@@ -306,6 +323,7 @@ def run_ours(args, w, rank, world, local_rank):
             torch.cuda.synchronize()
     torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
+    stage("clock sampling done")
     if rank == 0:
         peaks = {}
         try:
@@ -355,7 +373,21 @@ def run_ours(args, w, rank, world, local_rank):
         }
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # The captured graphs hold NCCL kernels of this communicator: release them, drain the device and meet the
+        # other ranks before the communicator goes. The teardown itself runs beside a deadline, so that a rank
+        # whose peers are already gone still exits.
+        graphs.clear()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        stage("tearing down the process group")
+        th = threading.Thread(target=dist.destroy_process_group, daemon=True)
+        th.start()
+        th.join(timeout=20.0)
+        sys.stdout.flush()
+        sys.stderr.flush()
+        # leave without the interpreter's own teardown of CUDA and NCCL objects, which can wait on a peer that is gone
+        os._exit(0)
 
 
 def main():
@@ -365,6 +397,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--verbose", action="store_true", help="print stage markers to stderr")
     ap.add_argument("--uniform-len", type=int, default=0, help="give every sequence this many keys (diagnostic)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

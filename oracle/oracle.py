@@ -287,6 +287,10 @@ def num_threads():
     return lib().orc_num_threads()
 
 
+def set_num_threads(n: int):
+    lib().orc_set_num_threads(int(n))
+
+
 # ------------------------------------------------------------------ the reference's own kernels (oracle/_ref)
 
 REF_BIN = HERE / "_ref" / "accel_host_test"

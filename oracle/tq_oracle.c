@@ -703,6 +703,16 @@ int orc_split_count_grouped(long long rows, int group, long long lk, int compute
     return (int)n;
 }
 
+/* test / benchmark infrastructure: threads of the OpenMP loops (launchers may export OMP_NUM_THREADS=1) */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    extern void omp_set_num_threads(int);
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int orc_num_threads(void) {
     int n = 1;
 #ifdef _OPENMP
