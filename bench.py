@@ -238,7 +238,10 @@ def run_ours(args, w, rank, world, local_rank):
         eager_step(i)
     torch.cuda.synchronize()
     stage("eager steps done")
-    graphs = []
+    # CUDA graphs: one per cache (a single step), and one of `group` consecutive steps (cache after cache), so
+    # that steps of a few microseconds are not bound by the host's replay rate
+    graphs, long_graph = [], None
+    group = nbuf * max(1, 16 // nbuf)
     use_graphs = os.environ.get("B200_BENCH_GRAPHS", "1") != "0"
     if use_graphs:
         try:
@@ -247,9 +250,13 @@ def run_ours(args, w, rank, world, local_rank):
                 with torch.cuda.graph(gr):
                     eager_step(i)
                 graphs.append(gr)
+            long_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(long_graph):
+                for i in range(group):
+                    eager_step(i)
         except Exception as e:  # report and time the eager launches instead
             print(f"bench: CUDA graph capture failed ({e}); timing eager launches", file=sys.stderr)
-            graphs = []
+            graphs, long_graph = [], None
             torch.cuda.synchronize()
 
     stage(f"graphs captured: {len(graphs)}")
@@ -260,29 +267,37 @@ def run_ours(args, w, rank, world, local_rank):
         else:
             eager_step(i)
 
+    def run_steps(k):
+        """Exactly k steps: whole groups through the long graph, the rest one by one."""
+        i = 0
+        while long_graph is not None and k - i >= group:
+            long_graph.replay()
+            i += group
+        while i < k:
+            step(i)
+            i += 1
+
     def barrier():
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        step(i)
+    run_steps(args.warmup)
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    # ---- device-resident timing: K steps between two events, plus one event pair per step for the kernel time
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    # ---- device-resident timing: exactly K steps between two events on the launching stream
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    ev[0].record()
-    for i in range(args.steps):
-        step(i)
-        ev[i + 1].record()
+    ev0.record()
+    run_steps(args.steps)
+    ev1.record()
     barrier()
-    total_ms = ev[0].elapsed_time(ev[args.steps])
+    total_ms = ev0.elapsed_time(ev1)
     stage("timed region done")
-    per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    per_step = [total_ms / args.steps]
     # ---- end to end through the public API with host buffers: H2D of the step's inputs, append of the new
     # token, attention, D2H of the outputs
     lens_dev = kv_len.clone()
@@ -317,11 +332,10 @@ def run_ours(args, w, rank, world, local_rank):
         [total_ms, e2e_ms, float(np.mean(per_step))], algorithmic_bytes(w, lens), world, dev)
     # the timed regions last milliseconds: keep the same step running (untimed) until the clock sampler has seen
     # about half a second of this load. Every rank runs the same number of steps (they hold a collective).
-    for i in range(clock_sample_steps(total_ms / args.steps)):
-        step(i)
-        if i % 50 == 49:
-            torch.cuda.synchronize()
-    torch.cuda.synchronize()
+    extra = clock_sample_steps(total_ms / args.steps)
+    for i in range(0, extra, 256):
+        run_steps(min(256, extra - i))
+        torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
     stage("clock sampling done")
     if rank == 0:
@@ -355,7 +369,7 @@ def run_ours(args, w, rank, world, local_rank):
             "data": "synthetic",
             "config": {"workload": f"{args.workload}: {w['desc']}", "batch_per_gpu": b, "hq": hq, "hkv": hkv, "head_dim": d,
                        "kv_format": w["fmt"], "rotation": w["rot"], "total_keys_per_gpu": int(lens.sum()),
-                       "launch": "CUDA graph replay" if graphs else "eager C ABI calls",
+                       "launch": f"CUDA graph replay ({group} steps per graph)" if graphs else "eager C ABI calls",
                        "l2": f"{nbuf} caches of {cache_bytes / 1e6:.0f} MB cycled (each step reads other rows than the last; L2 is 126 MB)",
                        "parallelism": f"batch shard x{world}, outputs all-gathered over NCCL" if world > 1 else "single GPU"},
             "tokens_per_s": world * b / (ms * 1e-3),
@@ -377,6 +391,7 @@ def run_ours(args, w, rank, world, local_rank):
         # other ranks before the communicator goes. The teardown itself runs beside a deadline, so that a rank
         # whose peers are already gone still exits.
         graphs.clear()
+        long_graph = None
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()

@@ -221,7 +221,7 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
     if (lrc) return lrc;
     {
         const size_t rows = (size_t)a->b * a->hq * a->lq;
-        const unsigned gx = (unsigned)std::min<size_t>((rows + 3) / 4, (size_t)sm_count_cached() * 16);
+        const unsigned gx = (unsigned)std::max<size_t>(std::min<size_t>(rows, (size_t)sm_count_cached() * 16), 1);
         // the combine grid is launched while the decode grid still runs and waits on the device for
         // its completion (programmatic dependent launch): its launch latency is off the critical path
         cudaLaunchConfig_t cfg = {};

@@ -85,7 +85,7 @@ __host__ __device__ constexpr int vsc_blocks(int vm, int hd) { return fmt_is_mx(
 __host__ __device__ constexpr int meta_bytes(int km, int vm, int hd) {
     return WK * (kmeta_words(km, hd) * 4 + 8 + vsc_blocks(vm, hd) * 2);
 }
-constexpr int FIXED_SMEM = 128 + 2048;  // barriers, pair tables
+constexpr int FIXED_SMEM = 128 + 2048 + 64;  // barriers, pair tables, byte-plane tables
 
 __device__ __forceinline__ uint32_t lds32(uint32_t a) {
     uint32_t v;
@@ -119,6 +119,47 @@ __device__ __forceinline__ uint32_t max_byte(uint32_t w) {
 }
 // f16 bits of 2^d for d <= 0 (flushes to zero below 2^-14)
 __device__ __forceinline__ uint32_t pow2_f16(int d) { return (uint32_t)max(d + 15, 0) << 10; }
+
+// The 16 f16 centroids of a codebook as byte planes: lo[i] holds the low bytes of entries 4i .. 4i+3,
+// hi[i] the high bytes. A byte permute with four codes as its selector then looks four entries up at once,
+// in registers: the pair table in shared memory costs one access per two codes, and codes are random, so
+// those accesses collide on the banks (3 wavefronts per access measured) and bound the kernel on the
+// load/store pipe.
+struct Tab16 {
+    uint32_t lo[4], hi[4];
+};
+__device__ __forceinline__ Tab16 load_tab16(uint32_t addr) {
+    Tab16 t;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.lo[0]), "=r"(t.lo[1]), "=r"(t.lo[2]), "=r"(t.lo[3]) : "r"(addr));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.hi[0]), "=r"(t.hi[1]), "=r"(t.hi[2]), "=r"(t.hi[3]) : "r"(addr + 16));
+    return t;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+// four codes (the nibbles of the low 16 bits of `sel`, bit 3 of each cleared) with `m` = 0xff in the bytes
+// of the codes >= 8: f16x2 (codes 0, 1) and (codes 2, 3)
+__device__ __forceinline__ void tab16_lookup4(const Tab16 &t, uint32_t sel, uint32_t m, uint32_t &h01, uint32_t &h23) {
+    const uint32_t lo_a = prmt(t.lo[0], t.lo[1], sel), lo_b = prmt(t.lo[2], t.lo[3], sel);
+    const uint32_t hi_a = prmt(t.hi[0], t.hi[1], sel), hi_b = prmt(t.hi[2], t.hi[3], sel);
+    const uint32_t lo = (lo_a & ~m) | (lo_b & m), hi = (hi_a & ~m) | (hi_b & m);
+    h01 = prmt(lo, hi, 0x5140u);
+    h23 = prmt(lo, hi, 0x7362u);
+}
+// the eight codes of x -> four f16x2, in the order of the pair table (low nibble in the low half)
+__device__ __forceinline__ void tab16_dq8(const Tab16 &t, uint32_t x, uint32_t &h0, uint32_t &h1, uint32_t &h2, uint32_t &h3) {
+    const uint32_t x4 = x << 4;
+    // sign-replicating selectors: bit 3 of every nibble, spread over its byte
+    const uint32_t m_lo = prmt(x4, x, 0xd9c8u), m_hi = prmt(x4, x, 0xfbeau);
+    tab16_lookup4(t, x & 0x7777u, m_lo, h0, h1);
+    tab16_lookup4(t, (x >> 16) & 0x7777u, m_hi, h2, h3);
+}
+
+#ifndef B200_TURBO_PRMT
+#define B200_TURBO_PRMT 2  // bit 0: keys, bit 1: values decode codebook rows in registers instead of by table loads (measured: the mix of both keeps either pipe from saturating)
+#endif
 
 // f16x2 pair table lookups (codebook format) or packed cvt of the four bytes of x
 template <int M>
@@ -242,7 +283,7 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem);  // [DW][NS_MAX]
     const int NS = (int)p.ns;
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t lut_k = sbase + 128, lut_v = lut_k + 1024;
+    const uint32_t lut_k = sbase + 128, lut_v = lut_k + 1024, plane_k = lut_v + 1024, plane_v = plane_k + 32;
     const uint32_t stage_bytes = p.k_stage_bytes + p.v_stage_bytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
@@ -258,6 +299,14 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
         for (int i = tid; i < 256; i += DW * 32) sts32(lut_k + 4 * i, pack_f16x2(p.k.tab[i & 15], p.k.tab[i >> 4]));
     if constexpr (VM == B200_TURBO_MSE)
         for (int i = tid; i < 256; i += DW * 32) sts32(lut_v + 4 * i, pack_f16x2(p.v.tab[i & 15], p.v.tab[i >> 4]));
+    if (tid < 16 && ((tid < 8) ? KM == B200_TURBO_MSE : VM == B200_TURBO_MSE)) {
+        // byte planes of the codebook: words 0..3 low bytes, 4..7 high bytes
+        const float *tab = tid < 8 ? p.k.tab : p.v.tab;
+        const int w = tid & 7, sh = w < 4 ? 0 : 8;
+        uint32_t v = 0;
+        for (int j = 0; j < 4; ++j) v |= ((pack_f16x2(tab[4 * (w & 3) + j], 0.0f) >> sh) & 0xffu) << (8 * j);
+        sts32(plane_k + 4 * tid, v);
+    }
     __syncthreads();
     // the combine kernel may be scheduled from here on; it waits for this grid's completion itself
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -486,12 +535,20 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                         sg8[i] = cvt_e4m3x2_f16x2(b8 | (b8 << 8));
                     }
                 }
+                constexpr bool KPL = KM == B200_TURBO_MSE && (B200_TURBO_PRMT & 1);
+                Tab16 kt;
+                if constexpr (KPL) kt = load_tab16(plane_k);
 #pragma unroll
                 for (int w = 0; w < WPL; ++w) {
                     const uint32_t x0 = lds32(ka + 4 * w), x8 = lds32(ka8 + 4 * w);
                     uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
-                    dq4<KM>(x0, lut_k, a0, a1, a2, a3);
-                    dq4<KM>(x8, lut_k, b0, b1, b2, b3);
+                    if constexpr (KPL) {
+                        tab16_dq8(kt, x0, a0, a1, a2, a3);
+                        tab16_dq8(kt, x8, b0, b1, b2, b3);
+                    } else {
+                        dq4<KM>(x0, lut_k, a0, a1, a2, a3);
+                        dq4<KM>(x8, lut_k, b0, b1, b2, b3);
+                    }
                     if constexpr (KM == B200_NVFP4) {
                         const uint32_t s0 = sg[w / 2], s8 = sg8[w / 2];
                         a0 = hmul2_u32(a0, s0); a1 = hmul2_u32(a1, s0); a2 = hmul2_u32(a2, s0); a3 = hmul2_u32(a3, s0);
@@ -531,10 +588,18 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                 const uint32_t tl1 = (xc & 0x0f0f0f0fu) | ((xd & 0x0f0f0f0fu) << 4);
                 const uint32_t th1 = ((xc >> 4) & 0x0f0f0f0fu) | (xd & 0xf0f0f0f0u);
                 uint32_t l0[4], h0[4], l1[4], h1[4];
-                dq4<VM>(tl0, lut_v, l0[0], l0[1], l0[2], l0[3]);
-                dq4<VM>(th0, lut_v, h0[0], h0[1], h0[2], h0[3]);
-                dq4<VM>(tl1, lut_v, l1[0], l1[1], l1[2], l1[3]);
-                dq4<VM>(th1, lut_v, h1[0], h1[1], h1[2], h1[3]);
+                if constexpr (VM == B200_TURBO_MSE && (B200_TURBO_PRMT & 2)) {
+                    const Tab16 vt = load_tab16(plane_v);
+                    tab16_dq8(vt, tl0, l0[0], l0[1], l0[2], l0[3]);
+                    tab16_dq8(vt, th0, h0[0], h0[1], h0[2], h0[3]);
+                    tab16_dq8(vt, tl1, l1[0], l1[1], l1[2], l1[3]);
+                    tab16_dq8(vt, th1, h1[0], h1[1], h1[2], h1[3]);
+                } else {
+                    dq4<VM>(tl0, lut_v, l0[0], l0[1], l0[2], l0[3]);
+                    dq4<VM>(th0, lut_v, h0[0], h0[1], h0[2], h0[3]);
+                    dq4<VM>(tl1, lut_v, l1[0], l1[1], l1[2], l1[3]);
+                    dq4<VM>(th1, lut_v, h1[0], h1[1], h1[2], h1[3]);
+                }
                 if constexpr (NBV > 0) {
                     const int blk = (g * (HD / 8) + 8 * w) / (HD / NBV);
                     const uint32_t sa = lds32(vsc_row + blk * WK * 2), sb = lds32(vsc_row + blk * WK * 2 + 16);
@@ -885,9 +950,14 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
 
 // Merges the partial results of one output row (candle-core/kernels/turbo_quant_impl.h:659-685),
 // rotates it back and casts it; rows of columns without any visible key are zeroed here.
+// One block per output row: warp w merges the segments w, w + 4, ... with vector loads that do not
+// depend on one another (a column of a short batch can have dozens of one-tile segments), then warp 0
+// adds the four sums.
 template <int HD>
 __global__ void __launch_bounds__(128) tq_combine_kernel(const DecodeParams p) {
-    __shared__ float rowbuf[4][HD];
+    constexpr int EPL = HD / 32;  // consecutive elements of a row per lane
+    __shared__ __align__(16) float part[4][HD];
+    __shared__ float wsums[4];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t rows = (size_t)p.b * p.hq * p.lq;
     const uint32_t ny = p.hkv * p.packs;
@@ -895,48 +965,88 @@ __global__ void __launch_bounds__(128) tq_combine_kernel(const DecodeParams p) {
     // launched with programmatic stream serialization: wait here until the decode grid has finished
     // and its partial results are visible
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    for (size_t row = (size_t)blockIdx.x * 4 + warp; row < rows; row += (size_t)gridDim.x * 4) {
+    for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const uint32_t i = (uint32_t)(row % p.lq);
         const uint32_t h = (uint32_t)((row / p.lq) % p.hq);
         const uint32_t b = (uint32_t)(row / ((size_t)p.lq * p.hq));
         const uint32_t hk = h / p.group, r = i * p.group + h % p.group;
         const uint32_t y = hk * p.packs + r / PACK, rr = r % PACK;
         const size_t obase = b * p.o_sb + h * p.o_sh + i * p.o_ss;
-        if (make_column(p, b).tiles == 0) {
+        if (make_column(p, b).tiles == 0) {  // the same for the whole block
+            if (warp == 0) {
 #pragma unroll
-            for (int k = 0; k < HD / 32; ++k) store_elem_rt(p.out, obase + lane + 32 * k, 0.0f, p.out_dtype);
+                for (int k = 0; k < EPL; ++k) store_elem_rt(p.out, obase + lane + 32 * k, 0.0f, p.out_dtype);
+            }
             continue;
         }
         const size_t col = (size_t)b * ny + y;
         const int first = p.meta[2 * col], ns = p.meta[2 * col + 1];
         const size_t slot0 = (size_t)first * prow + rr;
         float mx = -INFINITY;
-        for (int s = 0; s < ns; ++s) mx = fmaxf(mx, p.part_lse[slot0 + (size_t)s * prow]);
-        float acc[HD / 32];
+        for (int s = lane; s < ns; s += 32) mx = fmaxf(mx, p.part_lse[slot0 + (size_t)s * prow]);
 #pragma unroll
-        for (int k = 0; k < HD / 32; ++k) acc[k] = 0.0f;
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float acc[EPL];
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) acc[k] = 0.0f;
         float wsum = 0.0f;
-        for (int s = 0; s < ns; ++s) {
-            const float e = p.part_lse[slot0 + (size_t)s * prow];
-            const float w = e == -INFINITY ? 0.0f : expf(e - mx);
-            wsum += w;
-            if (w != 0.0f) {
-                const float *po = p.part_o + (slot0 + (size_t)s * prow) * HD;
+        for (int base = warp; base < ns; base += 128) {  // lane l of this warp weighs segment base + 4 l
+            const int sl = base + 4 * lane;
+            float wl = 0.0f;
+            if (sl < ns) {
+                const float e = p.part_lse[slot0 + (size_t)sl * prow];
+                wl = e == -INFINITY ? 0.0f : expf(e - mx);
+            }
+            wsum += wl;
+            const int cnt = min(32, (ns - base + 3) / 4);
+            const float *po = p.part_o + (slot0 + (size_t)base * prow) * HD + lane * EPL;
+#pragma unroll 8
+            for (int j = 0; j < cnt; ++j) {
+                const float w = __shfl_sync(0xffffffffu, wl, j);
+                const float *src = po + (size_t)(4 * j) * prow * HD;
+                if constexpr (EPL == 2) {
+                    const float2 v = *reinterpret_cast<const float2 *>(src);
+                    acc[0] = fmaf(w, v.x, acc[0]);
+                    acc[1] = fmaf(w, v.y, acc[1]);
+                } else {
 #pragma unroll
-                for (int k = 0; k < HD / 32; ++k) acc[k] += w * po[lane + 32 * k];
+                    for (int q = 0; q < EPL / 4; ++q) {
+                        const float4 v = *reinterpret_cast<const float4 *>(src + 4 * q);
+                        acc[4 * q] = fmaf(w, v.x, acc[4 * q]);
+                        acc[4 * q + 1] = fmaf(w, v.y, acc[4 * q + 1]);
+                        acc[4 * q + 2] = fmaf(w, v.z, acc[4 * q + 2]);
+                        acc[4 * q + 3] = fmaf(w, v.w, acc[4 * q + 3]);
+                    }
+                }
             }
         }
-        float *rb = rowbuf[warp];
 #pragma unroll
-        for (int k = 0; k < HD / 32; ++k) rb[lane + 32 * k] = wsum > 0.0f ? acc[k] / wsum : 0.0f;
-        __syncwarp();
-        if (p.v.rot == B200_ROT_HADAMARD) {
-            warp_hadamard(rb, HD, p.v.signs, false, lane);
+        for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) part[warp][lane * EPL + k] = acc[k];
+        if (lane == 0) wsums[warp] = wsum;
+        __syncthreads();
+        if (warp == 0) {
+            const float wt = wsums[0] + wsums[1] + wsums[2] + wsums[3];
+            float *rb = part[0];
+            float v[EPL];
+#pragma unroll
+            for (int k = 0; k < EPL; ++k) {
+                const int d = lane + 32 * k;
+                v[k] = part[0][d] + part[1][d] + part[2][d] + part[3][d];
+            }
             __syncwarp();
-        }
 #pragma unroll
-        for (int k = 0; k < HD / 32; ++k) store_elem_rt(p.out, obase + lane + 32 * k, rb[lane + 32 * k], p.out_dtype);
-        __syncwarp();
+            for (int k = 0; k < EPL; ++k) rb[lane + 32 * k] = wt > 0.0f ? v[k] / wt : 0.0f;
+            __syncwarp();
+            if (p.v.rot == B200_ROT_HADAMARD) {
+                warp_hadamard(rb, HD, p.v.signs, false, lane);
+                __syncwarp();
+            }
+#pragma unroll
+            for (int k = 0; k < EPL; ++k) store_elem_rt(p.out, obase + lane + 32 * k, rb[lane + 32 * k], p.out_dtype);
+        }
+        __syncthreads();
     }
 }
 
