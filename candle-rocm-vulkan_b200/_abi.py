@@ -85,7 +85,7 @@ SYMBOLS = [
     "b200_row_layout", "b200_codebook", "b200_hadamard_signs", "b200_row_group", "b200_split_count_grouped",
     "b200_describe", "b200_last_error", "b200_tq_rotate", "b200_tq_quantize", "b200_tq_dequantize", "b200_kv_append",
     "b200_tq_attention_workspace_bytes", "b200_tq_attention", "b200_tq_attention_static", "b200_flash_attn_workspace_bytes",
-    "b200_flash_attn", "b200_fa_prefill_append",
+    "b200_flash_attn", "b200_fa_prefill_append", "b200_device_wait_status",
 ]
 
 _lib = None

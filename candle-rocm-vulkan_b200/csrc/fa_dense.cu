@@ -16,27 +16,12 @@
 #include <cuda_bf16.h>
 
 #include "common.cuh"
+#include "fa_params.cuh"
 
 namespace b200 {
 
 constexpr int FA_BM = 64, FA_BN = 64, FA_WARPS = 4;
 constexpr float LOG2E_F = 1.4426950408889634f;
-
-struct FaParams {
-    const void *q, *k, *v;
-    void *o;
-    float *part_o, *part_lse;
-    const uint32_t *cu_q, *cu_k;
-    const float *alibi;
-    uint32_t b, lq, lk, hq, hkv, d, group;
-    uint64_t q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh;
-    float scale, softcap, kd, vd;
-    int32_t wl, wr;
-    uint32_t alibi_bs, varlen, n_splits;
-    int32_t q_dtype;  // dtype of q and o
-    int32_t kv_kind;  // 0: 16-bit elements of the mma type, 1: E4M3 bytes, 2: f32
-    uint64_t rows_total;  // total_q * hq
-};
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool pred) {
     const int n = pred ? 16 : 0;  // zero fill when the row is outside the tile
@@ -437,7 +422,9 @@ static int fa_plan(const B200FaArgs *a, FaPlan &pl) {
         const uint64_t by_occ = (2ull * sms + ctas - 1) / ctas, by_keys = (a->lk + 4 * FA_BN - 1) / (4 * FA_BN);
         splits = (uint32_t)std::min<uint64_t>(std::min(by_occ, by_keys), 64);
     }
-    p.n_splits = std::max(splits, 1u);
+    p.n_splits = 1;
+    // long chunks run as whole tiles on the tcgen05 kernel and are never split along the keys
+    if (!fa_prefill_sm100_supported(p, kv16)) p.n_splits = std::max(splits, 1u);
     if ((uint64_t)a->b * p.n_splits > 65535) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "flash_attn: batch x splits too large");
     pl.grid = dim3(row_tiles, a->hkv, a->b * p.n_splits);
     const size_t rowb = a->d * 2 + 16;
@@ -495,6 +482,8 @@ extern "C" int b200_flash_attn(const B200FaArgs *a, b200_stream_t stream_) {
     }
     cudaStream_t stream = (cudaStream_t)stream_;
     const bool bf = pl.bf16;
+    // long prefill chunks: tiles on the tcgen05 tensor cores
+    if (fa_prefill_sm100_supported(pl.p, pl.p.kv_kind == 0)) return fa_prefill_sm100_launch(pl.p, bf, stream);
     if (a->d == 64) return bf ? fa_launch<64, true>(pl, stream) : fa_launch<64, false>(pl, stream);
     return bf ? fa_launch<128, true>(pl, stream) : fa_launch<128, false>(pl, stream);
 }

@@ -1,0 +1,447 @@
+// Prefill attention tiles on the 5th generation tensor cores (tcgen05, accumulators in tensor memory).
+//
+// One block = 128 packed query rows (row = token * group + head in group, so the heads that share a
+// kv head also share every K / V tile) of one (batch entry, kv head), head dim 128, f16 or bf16.
+//   warps 0-3  softmax: thread = row. Reads its row of S from tensor memory, keeps the running
+//              maximum and sum in registers, writes P (16-bit pairs) back to tensor memory and, when the
+//              maximum moved by more than 2^8, rescales its row of O in tensor memory.
+//   warp 4     loader: K / V tiles of 64 keys, cp.async 16-byte chunks laid out as the 8 x 16 byte
+//              core matrices the tensor core reads without swizzling; two stages.
+//   warp 5     issues S = Q K^T (M 128, N 64, 8 k-steps; both operands from shared memory) and
+//              O += P V (M 128, N 128, 4 k-steps; P from tensor memory, V from shared memory, N-major),
+//              and owns the tensor memory allocation (256 columns: S 64, P 32, O 128).
+// Two blocks fit one SM (96 KB of shared memory and 256 of the 512 columns each): while one runs its
+// softmax the other runs its matrix products.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out raises a flag that ends all roles, the
+// block frees its tensor memory and the host can read the flag (b200_device_wait_status).
+//
+// Semantics as fa_dense.cu (candle-core/kernels/flash_attn_impl.h:330-443: FA2-order tiles, bottom
+// right aligned windows, zeros for rows without a visible key).
+#include <algorithm>
+
+#include "common.cuh"
+#include "fa_params.cuh"
+
+namespace b200 {
+
+constexpr int PF_BM = 128, PF_BN = 64, PF_D = 128, PF_THREADS = 192;
+constexpr uint32_t PF_TMEM_COLS = 256, PF_S_COL = 0, PF_P_COL = 64, PF_O_COL = 128;
+// shared memory, bytes. K-major operands (Q, K): addr(row, chunk) = (row / 8) * 2048 + chunk * 128 + (row % 8) * 16
+// (chunk = 8 elements of the head dim); N-major operand (V): addr(key, chunk) = chunk * 1024 + (key / 8) * 128 + (key % 8) * 16
+constexpr uint32_t PF_Q_BYTES = 32768, PF_KT_BYTES = 16384, PF_VT_BYTES = 16384;
+constexpr uint32_t PF_SM_Q = 0, PF_SM_K = PF_Q_BYTES, PF_SM_V = PF_SM_K + 2 * PF_KT_BYTES, PF_SM_BAR = PF_SM_V + 2 * PF_VT_BYTES;
+constexpr uint32_t PF_SMEM = PF_SM_BAR + 128;
+constexpr float PF_LOG2E = 1.4426950408889634f, PF_SLACK = 8.0f;
+
+__device__ int g_wait_failed = 0;  // set when a bounded wait ran out in any kernel of this file
+
+// ---- tcgen05 wrappers -------------------------------------------------------------------------------
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// shared memory matrix descriptor, no swizzle: start address, K-direction stride (between core
+// matrices that follow one another along the contraction), M/N-direction stride, all in 16-byte units
+__device__ __forceinline__ uint64_t tc_desc(uint32_t saddr, uint32_t k_stride, uint32_t mn_stride) {
+    uint64_t d = (uint64_t)((saddr & 0x3ffffu) >> 4);
+    d |= (uint64_t)((k_stride >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((mn_stride >> 4) & 0x3fffu) << 32;
+    d |= 1ull << 46;  // descriptor version of this architecture
+    return d;
+}
+// instruction descriptor, kind::f16: f32 accumulator, A and B of one 16-bit type, B N-major or K-major
+__host__ __device__ constexpr uint32_t tc_idesc(bool bf16, bool b_n_major, uint32_t m, uint32_t n) {
+    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((b_n_major ? 1u : 0u) << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem), "l"(a),
+                 "l"(b), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(d_tmem),
+                 "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+// 32 consecutive 32-bit columns of this thread's lane
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+          "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
+        "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+        "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void pf_cp16(uint32_t dst, const void *src, bool pred) {
+    const int n = pred ? 16 : 0;  // zero fill for rows outside the tile
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t pf_pack2(float lo, float hi) {
+    uint32_t d;
+    if (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+
+// bounded wait that also ends when another role gave up; false = give up
+__device__ __forceinline__ bool pf_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t i = 0; i < (1u << 20); ++i) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok)
+                     : "r"(bar), "r"(parity)
+                     : "memory");
+        if (ok) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    return false;
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(PF_THREADS, 2) fa_prefill_sm100_kernel(const FaParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t sbase = smem_u32(smem);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + PF_SM_BAR);
+    // barriers: 0,1 kv_full; 2,3 kv_empty; 4 s_full; 5 p_full; 6 o_full; 7 drain
+    const uint32_t bar0 = sbase + PF_SM_BAR;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + PF_SM_BAR + 64);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + PF_SM_BAR + 72);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    const uint32_t hk = blockIdx.y, b = blockIdx.z, G = p.group;
+    uint32_t lq = p.lq, lk = p.lk;
+    uint64_t q0 = (uint64_t)b * p.lq, k0 = 0;
+    if (p.varlen) {
+        q0 = p.cu_q[b];
+        lq = p.cu_q[b + 1] - p.cu_q[b];
+        k0 = p.cu_k[b];
+        lk = p.cu_k[b + 1] - p.cu_k[b];
+    }
+    const uint32_t R = lq * G;
+    // the row tiles with the most keys first
+    const uint32_t row0 = (gridDim.x - 1 - blockIdx.x) * PF_BM;
+    if (row0 >= R) return;
+    // a wait that ran out in an earlier block means something is wrong with the device or this build:
+    // later blocks leave at once instead of each waiting out its own limit
+    if (*reinterpret_cast<volatile int *>(&g_wait_failed)) return;
+    const char *qb = reinterpret_cast<const char *>(p.q);
+    const char *kb = reinterpret_cast<const char *>(p.k) + (p.varlen ? k0 * p.k_ss + hk * p.k_sh : b * p.k_sb + hk * p.k_sh) * 2;
+    const char *vb = reinterpret_cast<const char *>(p.v) + (p.varlen ? k0 * p.v_ss + hk * p.v_sh : b * p.v_sb + hk * p.v_sh) * 2;
+    auto range_of = [&](uint32_t r, long long &lo, long long &hi) {
+        const long long i = r / G;
+        const long long pos = i + (long long)lk - (long long)lq;
+        lo = p.wl >= 0 ? max(pos - p.wl, 0ll) : 0ll;
+        hi = p.wr >= 0 ? min(pos + p.wr + 1, (long long)lk) : (long long)lk;
+        lo = min(lo, (long long)lk);
+        hi = max(hi, lo);
+    };
+    long long t_lo, t_hi, tmp;
+    range_of(row0, t_lo, tmp);
+    range_of(min(row0 + PF_BM, R) - 1, tmp, t_hi);
+    if (t_hi < t_lo) t_hi = t_lo;
+    const int ntiles = (int)((t_hi - t_lo + PF_BN - 1) / PF_BN);
+
+    // ---- set up: barriers, tensor memory, the Q tile
+    if (tid == 0) {
+        mbar_init(&bars[0], 32);
+        mbar_init(&bars[1], 32);
+        mbar_init(&bars[2], 1);
+        mbar_init(&bars[3], 1);
+        mbar_init(&bars[4], 1);
+        mbar_init(&bars[5], 128);
+        mbar_init(&bars[6], 1);
+        mbar_init(&bars[7], 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(PF_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // Q: 128 rows x 16 chunks; lanes 0-7 take the 8 rows of one core matrix, lane / 8 four chunks in a row
+    for (int idx = tid; idx < PF_BM * 16; idx += PF_THREADS) {
+        const int blk = idx >> 5, l = idx & 31;          // 32 chunks = 4 core matrices per step
+        const int grp = blk >> 2, kc = (blk & 3) * 4 + (l >> 3), rr = grp * 8 + (l & 7);
+        const uint32_t r = row0 + rr;
+        const bool ok = r < R;
+        const uint32_t i = ok ? r / G : 0, h = hk * G + (ok ? r % G : 0);
+        const uint64_t off = (p.varlen ? (q0 + i) * p.q_ss : b * p.q_sb + i * p.q_ss) + h * p.q_sh;
+        pf_cp16(sbase + PF_SM_Q + grp * 2048 + kc * 128 + (rr & 7) * 16, qb + off * 2 + kc * 16, ok);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 4) {
+        // ================================================================ loader
+        auto load_tile = [&](int t) {
+            const long long j0 = t_lo + (long long)t * PF_BN;
+            const uint32_t dk = sbase + PF_SM_K + (t & 1) * PF_KT_BYTES, dv = sbase + PF_SM_V + (t & 1) * PF_VT_BYTES;
+            // K: 64 keys x 16 chunks, as Q
+#pragma unroll 4
+            for (int blk = 0; blk < 32; ++blk) {
+                const int grp = blk >> 2, kc = (blk & 3) * 4 + (lane >> 3), rr = grp * 8 + (lane & 7);
+                const long long j = j0 + rr;
+                const bool ok = j < t_hi;
+                pf_cp16(dk + grp * 2048 + kc * 128 + (rr & 7) * 16, kb + (uint64_t)(ok ? j : t_lo) * p.k_ss * 2 + kc * 16, ok);
+            }
+            // V: per chunk of 8 head dims, 64 keys = 8 core matrices of 8 keys; 32 lanes take 32 keys
+#pragma unroll 4
+            for (int blk = 0; blk < 32; ++blk) {
+                const int dc = blk >> 1, key = (blk & 1) * 32 + lane;
+                const long long j = j0 + key;
+                const bool ok = j < t_hi;
+                pf_cp16(dv + dc * 1024 + (key >> 3) * 128 + (key & 7) * 16, vb + (uint64_t)(ok ? j : t_lo) * p.v_ss * 2 + dc * 16, ok);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        // Two tiles in flight. A tile is announced as soon as it has landed; only then does the loader
+        // wait for the products that free the stage it refills (the issuing warp, in turn, waits for a
+        // tile only after it has issued the products of the tile before).
+        bool ok = true;
+        if (ntiles > 0) load_tile(0);
+        if (ntiles > 1) load_tile(1);
+        for (int t = 0; t < ntiles && ok; ++t) {
+            if (t + 1 < ntiles) asm volatile("cp.async.wait_group 1;" ::: "memory");
+            else asm volatile("cp.async.wait_group 0;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(&bars[t & 1]);
+            if (t + 2 < ntiles) {
+                ok = pf_wait(bar0 + 8 * (2 + (t & 1)), (t >> 1) & 1, abort_flag);  // O += P(t) V(t) has read the stage
+                ok = __all_sync(0xffffffffu, ok);
+                if (ok) load_tile(t + 2);
+            }
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (!ok) *abort_flag = 1;
+    } else if (warp == 5) {
+        // ================================================================ matrix products (one lane issues)
+        if (lane == 0) {
+            constexpr uint32_t IQK = tc_idesc(BF16, false, PF_BM, PF_BN), IPV = tc_idesc(BF16, true, PF_BM, PF_D);
+            bool ok = true;
+            auto issue_pv = [&](int t) {  // O += P(t) V(t)
+                const uint32_t vs = sbase + PF_SM_V + (t & 1) * PF_VT_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < PF_BN / 16; ++ks)
+                    tc_mma_ts(tmem + PF_O_COL, tmem + PF_P_COL + ks * 8, tc_desc(vs + ks * 256, 128, 1024), IPV, (t > 0 || ks > 0) ? 1u : 0u);
+                tc_commit(bar0 + 8 * (2 + (t & 1)));  // the stage is free once these have read it
+            };
+            for (int t = 0; t < ntiles && ok; ++t) {
+                if (t > 0) {
+                    ok = pf_wait(bar0 + 8 * 5, (t - 1) & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(t - 1);
+                }
+                ok = pf_wait(bar0 + 8 * (t & 1), (t >> 1) & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t ks_ = sbase + PF_SM_K + (t & 1) * PF_KT_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < PF_D / 16; ++ks)
+                    tc_mma_ss(tmem + PF_S_COL, tc_desc(sbase + PF_SM_Q + ks * 256, 128, 2048), tc_desc(ks_ + ks * 256, 128, 2048), IQK, ks > 0 ? 1u : 0u);
+                tc_commit(bar0 + 8 * 4);
+            }
+            if (ok && ntiles > 0) {
+                ok = pf_wait(bar0 + 8 * 5, (ntiles - 1) & 1, abort_flag);
+                if (ok) {
+                    tc_fence_after();
+                    issue_pv(ntiles - 1);
+                    tc_commit(bar0 + 8 * 6);
+                }
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                // let the products already issued finish before the tensor memory goes
+                tc_commit(bar0 + 8 * 7);
+                for (uint32_t i = 0; i < (1u << 20); ++i) {
+                    uint32_t done;
+                    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                                 : "=r"(done)
+                                 : "r"(bar0 + 8 * 7), "r"(0u)
+                                 : "memory");
+                    if (done) break;
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ================================================================ softmax, thread = row
+        const uint32_t rr = warp * 32 + lane, r = row0 + rr;
+        const bool r_ok = r < R;
+        long long r_lo = 0, r_hi = 0;
+        if (r_ok) range_of(r, r_lo, r_hi);
+        // the tightest bounds over the block's rows decide which tiles need masks
+        long long lomax, himin;
+        {
+            long long a, c2;
+            range_of(min(row0 + PF_BM, R) - 1, lomax, a);
+            range_of(row0, c2, himin);
+            if (row0 + PF_BM > R) himin = -1;  // rows past the sequence: always masked
+        }
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        const float sl2 = p.scale * p.kd * PF_LOG2E;
+        float mref = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int t = 0; t < ntiles; ++t) {
+            ok = pf_wait(bar0 + 8 * 4, t & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t sa[32], sb[32];
+            tc_ld32(lane_base + PF_S_COL, sa);
+            tc_ld32(lane_base + PF_S_COL + 32, sb);
+            tc_wait_ld();
+            const long long j0 = t_lo + (long long)t * PF_BN;
+            const bool full = j0 >= lomax && j0 + PF_BN <= himin && j0 + PF_BN <= t_hi;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                float x0 = u2f(sa[i]) * sl2, x1 = u2f(sb[i]) * sl2;
+                if (!full) {
+                    const long long ja = j0 + i, jb = j0 + 32 + i;
+                    if (!(r_ok && ja >= r_lo && ja < r_hi)) x0 = -INFINITY;
+                    if (!(r_ok && jb >= r_lo && jb < r_hi)) x1 = -INFINITY;
+                }
+                sa[i] = f2u(x0);
+                sb[i] = f2u(x1);
+                mx = fmaxf(mx, fmaxf(x0, x1));
+            }
+            bool need = false;
+            if (t == 0) mref = mx;
+            else need = mx > mref + PF_SLACK;
+            if (__any_sync(0xffffffffu, need)) {
+                // rows whose maximum moved: O and the running sum go to the new reference
+                const float f = need ? fast_exp2(mref - mx) : 1.0f;
+                if (need) {
+                    mref = mx;
+                    l *= f;
+                }
+#pragma unroll 1
+                for (int ch = 0; ch < 4; ++ch) {
+                    uint32_t o[32];
+                    tc_ld32(lane_base + PF_O_COL + 32 * ch, o);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = f2u(u2f(o[i]) * f);
+                    tc_st32(lane_base + PF_O_COL + 32 * ch, o);
+                }
+                tc_wait_st();
+            }
+            const float ms = mref == -INFINITY ? 0.0f : mref;
+            uint32_t pr[32];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float a0 = fast_exp2(u2f(sa[2 * i]) - ms), a1 = fast_exp2(u2f(sa[2 * i + 1]) - ms);
+                const float b0 = fast_exp2(u2f(sb[2 * i]) - ms), b1 = fast_exp2(u2f(sb[2 * i + 1]) - ms);
+                l += (a0 + a1) + (b0 + b1);
+                pr[i] = pf_pack2<BF16>(a0, a1);
+                pr[16 + i] = pf_pack2<BF16>(b0, b1);
+            }
+            tc_st32(lane_base + PF_P_COL, pr);
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(&bars[5]);
+        }
+        if (ok && ntiles > 0) {
+            ok = pf_wait(bar0 + 8 * 6, 0, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (!ok) *abort_flag = 1;
+        // ---- the row of the output: O / l, or zeros
+        const float inv = (ok && ntiles > 0 && l > 0.0f) ? p.vd / l : 0.0f;
+        const uint32_t i_tok = r_ok ? r / G : 0, h = hk * G + (r_ok ? r % G : 0);
+        uint16_t *orow = reinterpret_cast<uint16_t *>(p.o) + ((q0 + i_tok) * p.hq + h) * PF_D;
+        if (ok && ntiles > 0) tc_fence_after();
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+            uint32_t o[32];
+            if (ok && ntiles > 0) {
+                tc_ld32(lane_base + PF_O_COL + 32 * ch, o);
+                tc_wait_ld();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = 0u;
+            }
+            if (r_ok) {
+#pragma unroll
+                for (int v4 = 0; v4 < 4; ++v4) {
+                    uint4 w;
+                    w.x = pf_pack2<BF16>(u2f(o[8 * v4]) * inv, u2f(o[8 * v4 + 1]) * inv);
+                    w.y = pf_pack2<BF16>(u2f(o[8 * v4 + 2]) * inv, u2f(o[8 * v4 + 3]) * inv);
+                    w.z = pf_pack2<BF16>(u2f(o[8 * v4 + 4]) * inv, u2f(o[8 * v4 + 5]) * inv);
+                    w.w = pf_pack2<BF16>(u2f(o[8 * v4 + 6]) * inv, u2f(o[8 * v4 + 7]) * inv);
+                    *reinterpret_cast<uint4 *>(orow + 32 * ch + 8 * v4) = w;
+                }
+            }
+        }
+    }
+    // ---- tear down
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(PF_TMEM_COLS) : "memory");
+    if (tid == 0 && *abort_flag) atomicExch(&g_wait_failed, 1);
+}
+
+bool fa_prefill_sm100_supported(const FaParams &p, bool kv16) {
+    if (!kv16 || p.kv_kind != 0 || p.d != PF_D || p.n_splits != 1) return false;
+    if (p.q_dtype != B200_F16 && p.q_dtype != B200_BF16) return false;
+    if (p.softcap > 0.0f || p.alibi != nullptr) return false;
+    if ((uint64_t)p.lq * p.group < 4 * PF_BM) return false;  // short chunks and decode stay on the mma.sync kernel
+    // 16-byte chunks of q rows
+    if ((reinterpret_cast<uintptr_t>(p.q) & 15) || ((p.q_sb | p.q_ss | p.q_sh) & 7)) return false;
+    static const bool off = [] { const char *e = getenv("B200_FA_NO_TCGEN05"); return e && *e == '1'; }();
+    return !off;
+}
+
+int fa_prefill_sm100_launch(const FaParams &p, bool bf16, cudaStream_t stream) {
+    static thread_local bool done[16][2] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 16 && !done[dev][bf16]) {
+        const cudaError_t e = bf16 ? cudaFuncSetAttribute(fa_prefill_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM)
+                                   : cudaFuncSetAttribute(fa_prefill_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM);
+        if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "flash_attn (tcgen05 tiles): shared memory opt-in: %s", cudaGetErrorString(e));
+        done[dev][bf16] = true;
+    }
+    const uint64_t rows = (uint64_t)p.lq * p.group;
+    const dim3 grid((unsigned)((rows + PF_BM - 1) / PF_BM), p.hkv, p.b);
+    if (bf16) fa_prefill_sm100_kernel<true><<<grid, PF_THREADS, PF_SMEM, stream>>>(p);
+    else fa_prefill_sm100_kernel<false><<<grid, PF_THREADS, PF_SMEM, stream>>>(p);
+    return check_launch("flash_attn (tcgen05 tiles)");
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// 1 when a bounded device-side wait of the attention kernels has run out since the library was
+// loaded (the call that met it wrote zeros or partial rows); synchronizes the device.
+extern "C" int b200_device_wait_status(void) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_wait_failed, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}

@@ -282,6 +282,12 @@ int b200_flash_attn(const B200FaArgs *args, b200_stream_t stream);
  * pointers and strides must describe the same tensors viewed as (b, hkv, t, d). */
 int b200_fa_prefill_append(const B200FaArgs *fa, const B200KvAppendArgs *append, b200_stream_t stream);
 
+/* Health check: 1 when a bounded device-side wait of the attention kernels (an mbarrier that a copy or
+ * a tensor core commit should have completed) has run out since the library was loaded, 0 otherwise,
+ * -1 when the device cannot be read. Synchronizes the device. The reference has no counterpart: its
+ * kernels hold no device-side waits (candle-core/kernels/flash_attn_impl.h uses block barriers only). */
+int b200_device_wait_status(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -81,6 +81,11 @@ ORACLE_CASES = [
     ("fp8_prefill", "bf16", 1, 100, 164, 8, 2, 128, -1, 0, 0.0, False, True),
     ("fp8_decode_d64", "f16", 3, 1, 2100, 4, 1, 64, -1, 0, 0.0, False, True),
     ("lq_longer_than_lk", "f16", 1, 80, 50, 2, 2, 64, -1, 0, 0.0, False, False),
+    # 512 packed rows and more with head dim 128: the tcgen05 tiles (many key tiles, windows, ragged ends)
+    ("tc_chunked_prefill", "bf16", 2, 333, 1000, 8, 2, 128, -1, 0, 0.0, False, False),
+    ("tc_f16_noncausal", "f16", 1, 130, 777, 4, 1, 128, -1, -1, 0.0, False, False),
+    ("tc_window", "bf16", 1, 700, 700, 2, 2, 128, 100, 0, 0.0, False, False),
+    ("tc_lq_longer", "f16", 1, 600, 450, 4, 4, 128, -1, 0, 0.0, False, False),
 ]
 
 
@@ -224,3 +229,8 @@ def test_argument_errors(P):
         F.flash_attn(q[:, :, :4], k.to(torch.bfloat16), k.to(torch.bfloat16), 1.0, False)
     with pytest.raises(RuntimeError, match="no CPU path"):
         F.flash_attn(q.cpu(), k.cpu(), k.cpu(), 1.0, False)
+
+
+def test_no_device_wait_ran_out(P):
+    """Collected after the attention tests of this file: the bounded waits of the tcgen05 prefill tiles all completed."""
+    assert P._abi.lib().b200_device_wait_status() == 0
