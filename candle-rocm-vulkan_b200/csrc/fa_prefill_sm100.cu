@@ -210,7 +210,8 @@ __global__ void __launch_bounds__(PF_THREADS, 2) fa_prefill_sm100_kernel(const F
             // V: per chunk of 8 head dims, 64 keys = 8 core matrices of 8 keys; 32 lanes take 32 keys
 #pragma unroll 4
             for (int blk = 0; blk < 32; ++blk) {
-                const int dc = blk >> 1, key = (blk & 1) * 32 + lane;
+                // two neighbouring chunks of 16 keys each per step: every key row gives a whole 32-byte sector
+                const int dc = (blk >> 2) * 2 + (lane & 1), key = (blk & 3) * 16 + (lane >> 1);
                 const long long j = j0 + key;
                 const bool ok = j < t_hi;
                 pf_cp16(dv + dc * 1024 + (key >> 3) * 128 + (key & 7) * 16, vb + (uint64_t)(ok ? j : t_lo) * p.v_ss * 2 + dc * 16, ok);
@@ -406,6 +407,315 @@ __global__ void __launch_bounds__(PF_THREADS, 2) fa_prefill_sm100_kernel(const F
     if (tid == 0 && *abort_flag) atomicExch(&g_wait_failed, 1);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Two row tiles per block: 256 packed rows share every K / V tile, and the two softmax groups take
+// turns with the tensor core (while group A runs its softmax the products of group B execute).
+//   warps 0-3 softmax of rows 0-127 (A), warps 4-7 of rows 128-255 (B), warp 8 loader (three stages),
+//   warp 9 issues the products and owns the tensor memory: 512 columns = S_A 64, S_B 64, P_A 32, P_B 32,
+//   O_A 128, O_B 128. One block per SM.
+// ---------------------------------------------------------------------------------------------
+constexpr int P2_THREADS = 320, P2_ROWS = 256, P2_STAGES = 3;
+constexpr uint32_t P2_TMEM_COLS = 512;
+constexpr uint32_t P2_SM_Q = 0, P2_SM_K = 2 * PF_Q_BYTES, P2_SM_V = P2_SM_K + P2_STAGES * PF_KT_BYTES;
+constexpr uint32_t P2_SM_BAR = P2_SM_V + P2_STAGES * PF_VT_BYTES, P2_SMEM = P2_SM_BAR + 256;
+__host__ __device__ constexpr uint32_t p2_s_col(int g) { return 64u * g; }
+__host__ __device__ constexpr uint32_t p2_p_col(int g) { return 128u + 32u * g; }
+__host__ __device__ constexpr uint32_t p2_o_col(int g) { return 192u + 128u * g; }
+
+template <bool BF16>
+__global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const FaParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t sbase = smem_u32(smem);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + P2_SM_BAR);
+    // barriers: 0-2 kv_full; 3-5 kv_empty; 6,7 s_full; 8,9 p_full; 10 o_full; 11 drain
+    const uint32_t bar0 = sbase + P2_SM_BAR;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + P2_SM_BAR + 128);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + P2_SM_BAR + 136);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    const uint32_t hk = blockIdx.y, b = blockIdx.z, G = p.group;
+    uint32_t lq = p.lq, lk = p.lk;
+    uint64_t q0 = (uint64_t)b * p.lq, k0 = 0;
+    if (p.varlen) {
+        q0 = p.cu_q[b];
+        lq = p.cu_q[b + 1] - p.cu_q[b];
+        k0 = p.cu_k[b];
+        lk = p.cu_k[b + 1] - p.cu_k[b];
+    }
+    const uint32_t R = lq * G;
+    const uint32_t row0 = (gridDim.x - 1 - blockIdx.x) * P2_ROWS;  // the row tiles with the most keys first
+    if (row0 >= R) return;
+    if (*reinterpret_cast<volatile int *>(&g_wait_failed)) return;
+    const char *qb = reinterpret_cast<const char *>(p.q);
+    const char *kb = reinterpret_cast<const char *>(p.k) + (p.varlen ? k0 * p.k_ss + hk * p.k_sh : b * p.k_sb + hk * p.k_sh) * 2;
+    const char *vb = reinterpret_cast<const char *>(p.v) + (p.varlen ? k0 * p.v_ss + hk * p.v_sh : b * p.v_sb + hk * p.v_sh) * 2;
+    auto range_of = [&](uint32_t r, long long &lo, long long &hi) {
+        const long long i = r / G;
+        const long long pos = i + (long long)lk - (long long)lq;
+        lo = p.wl >= 0 ? max(pos - p.wl, 0ll) : 0ll;
+        hi = p.wr >= 0 ? min(pos + p.wr + 1, (long long)lk) : (long long)lk;
+        lo = min(lo, (long long)lk);
+        hi = max(hi, lo);
+    };
+    long long t_lo, t_hi, tmp;
+    range_of(row0, t_lo, tmp);
+    range_of(min(row0 + P2_ROWS, R) - 1, tmp, t_hi);
+    if (t_hi < t_lo) t_hi = t_lo;
+    const int ntiles = (int)((t_hi - t_lo + PF_BN - 1) / PF_BN);
+
+    if (tid == 0) {
+        for (int i = 0; i < 3; ++i) mbar_init(&bars[i], 32);
+        for (int i = 3; i < 8; ++i) mbar_init(&bars[i], 1);
+        mbar_init(&bars[8], 128);
+        mbar_init(&bars[9], 128);
+        mbar_init(&bars[10], 1);
+        mbar_init(&bars[11], 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(P2_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // Q: 256 rows x 16 chunks (two K-major operands of 128 rows)
+    for (int idx = tid; idx < P2_ROWS * 16; idx += P2_THREADS) {
+        const int blk = idx >> 5, l = idx & 31;
+        const int grp = blk >> 2, kc = (blk & 3) * 4 + (l >> 3), rr = grp * 8 + (l & 7);
+        const uint32_t r = row0 + rr;
+        const bool ok = r < R;
+        const uint32_t i = ok ? r / G : 0, h = hk * G + (ok ? r % G : 0);
+        const uint64_t off = (p.varlen ? (q0 + i) * p.q_ss : b * p.q_sb + i * p.q_ss) + h * p.q_sh;
+        pf_cp16(sbase + P2_SM_Q + grp * 2048 + kc * 128 + (rr & 7) * 16, qb + off * 2 + kc * 16, ok);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 8) {
+        // ================================================================ loader
+        auto load_tile = [&](int t) {
+            const long long j0 = t_lo + (long long)t * PF_BN;
+            const int st = t % P2_STAGES;
+            const uint32_t dk = sbase + P2_SM_K + st * PF_KT_BYTES, dv = sbase + P2_SM_V + st * PF_VT_BYTES;
+#pragma unroll 4
+            for (int blk = 0; blk < 32; ++blk) {
+                const int grp = blk >> 2, kc = (blk & 3) * 4 + (lane >> 3), rr = grp * 8 + (lane & 7);
+                const long long j = j0 + rr;
+                const bool ok = j < t_hi;
+                pf_cp16(dk + grp * 2048 + kc * 128 + (rr & 7) * 16, kb + (uint64_t)(ok ? j : t_lo) * p.k_ss * 2 + kc * 16, ok);
+            }
+#pragma unroll 4
+            for (int blk = 0; blk < 32; ++blk) {
+                const int dc = (blk >> 2) * 2 + (lane & 1), key = (blk & 3) * 16 + (lane >> 1);
+                const long long j = j0 + key;
+                const bool ok = j < t_hi;
+                pf_cp16(dv + dc * 1024 + (key >> 3) * 128 + (key & 7) * 16, vb + (uint64_t)(ok ? j : t_lo) * p.v_ss * 2 + dc * 16, ok);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        // Tile t is announced as soon as it has landed; only then does the loader wait for the stage that
+        // tile t + 2 goes into (read last by the products of tile t - 1, which the issuing warp issues
+        // after it has seen tile t). Tiles t + 1 and t + 2 are in flight while tile t is consumed.
+        bool ok = true;
+        if (ntiles > 0) load_tile(0);
+        if (ntiles > 1) load_tile(1);
+        for (int t = 0; t < ntiles && ok; ++t) {
+            if (t + 1 < ntiles) asm volatile("cp.async.wait_group 1;" ::: "memory");
+            else asm volatile("cp.async.wait_group 0;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(&bars[t % P2_STAGES]);
+            if (t + 2 < ntiles) {
+                if (t >= 1) {
+                    ok = pf_wait(bar0 + 8 * (3 + (t - 1) % P2_STAGES), ((t - 1) / P2_STAGES) & 1, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
+                }
+                if (ok) load_tile(t + 2);
+            }
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (!ok) *abort_flag = 1;
+    } else if (warp == 9) {
+        // ================================================================ matrix products (one lane issues)
+        if (lane == 0) {
+            constexpr uint32_t IQK = tc_idesc(BF16, false, PF_BM, PF_BN), IPV = tc_idesc(BF16, true, PF_BM, PF_D);
+            bool ok = true;
+            auto issue_qk = [&](int g, int t) {  // S_g = Q_g K(t)^T
+                const uint32_t ks_ = sbase + P2_SM_K + (t % P2_STAGES) * PF_KT_BYTES, qs_ = sbase + P2_SM_Q + g * PF_Q_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < PF_D / 16; ++ks)
+                    tc_mma_ss(tmem + p2_s_col(g), tc_desc(qs_ + ks * 256, 128, 2048), tc_desc(ks_ + ks * 256, 128, 2048), IQK, ks > 0 ? 1u : 0u);
+                tc_commit(bar0 + 8 * (6 + g));
+            };
+            auto issue_pv = [&](int g, int t) {  // O_g += P_g(t) V(t)
+                const uint32_t vs = sbase + P2_SM_V + (t % P2_STAGES) * PF_VT_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < PF_BN / 16; ++ks)
+                    tc_mma_ts(tmem + p2_o_col(g), tmem + p2_p_col(g) + ks * 8, tc_desc(vs + ks * 256, 128, 1024), IPV, (t > 0 || ks > 0) ? 1u : 0u);
+            };
+            if (ntiles > 0) {
+                ok = pf_wait(bar0, 0, abort_flag);
+                if (ok) {
+                    tc_fence_after();
+                    issue_qk(0, 0);
+                    issue_qk(1, 0);
+                }
+            }
+            for (int t = 0; t < ntiles && ok; ++t) {
+                ok = pf_wait(bar0 + 8 * 8, t & 1, abort_flag);  // P_A(t) is in tensor memory, S_A is free
+                if (!ok) break;
+                tc_fence_after();
+                issue_pv(0, t);
+                if (t + 1 < ntiles) {
+                    ok = pf_wait(bar0 + 8 * ((t + 1) % P2_STAGES), ((t + 1) / P2_STAGES) & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(0, t + 1);
+                }
+                ok = pf_wait(bar0 + 8 * 9, t & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                issue_pv(1, t);
+                tc_commit(bar0 + 8 * (3 + t % P2_STAGES));  // the stage is free once both have read it
+                if (t + 1 < ntiles) issue_qk(1, t + 1);
+            }
+            if (ok && ntiles > 0) tc_commit(bar0 + 8 * 10);
+            if (!ok) {
+                *abort_flag = 1;
+                tc_commit(bar0 + 8 * 11);
+                for (uint32_t i = 0; i < (1u << 20); ++i) {
+                    uint32_t done;
+                    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                                 : "=r"(done)
+                                 : "r"(bar0 + 8 * 11), "r"(0u)
+                                 : "memory");
+                    if (done) break;
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ================================================================ softmax, thread = row
+        const int g = warp >> 2, w4 = warp & 3;
+        const uint32_t g_row0 = row0 + g * PF_BM;
+        const uint32_t r = g_row0 + w4 * 32 + lane;
+        const bool r_ok = r < R;
+        long long r_lo = 0, r_hi = 0;
+        if (r_ok) range_of(r, r_lo, r_hi);
+        long long lomax = 0, himin = -1;  // a group without rows: every tile masked
+        if (g_row0 < R) {
+            long long a, c2;
+            range_of(min(g_row0 + PF_BM, R) - 1, lomax, a);
+            range_of(g_row0, c2, himin);
+            if (g_row0 + PF_BM > R) himin = -1;
+        }
+        const uint32_t lane_base = tmem + ((uint32_t)(w4 * 32) << 16);
+        const uint32_t s_col = p2_s_col(g), p_col = p2_p_col(g), o_col = p2_o_col(g);
+        const float sl2 = p.scale * p.kd * PF_LOG2E;
+        float mref = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int t = 0; t < ntiles; ++t) {
+            ok = pf_wait(bar0 + 8 * (6 + g), t & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t sa[32], sb[32];
+            tc_ld32(lane_base + s_col, sa);
+            tc_ld32(lane_base + s_col + 32, sb);
+            tc_wait_ld();
+            const long long j0 = t_lo + (long long)t * PF_BN;
+            const bool full = j0 >= lomax && j0 + PF_BN <= himin && j0 + PF_BN <= t_hi;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                float x0 = u2f(sa[i]) * sl2, x1 = u2f(sb[i]) * sl2;
+                if (!full) {
+                    const long long ja = j0 + i, jb = j0 + 32 + i;
+                    if (!(r_ok && ja >= r_lo && ja < r_hi)) x0 = -INFINITY;
+                    if (!(r_ok && jb >= r_lo && jb < r_hi)) x1 = -INFINITY;
+                }
+                sa[i] = f2u(x0);
+                sb[i] = f2u(x1);
+                mx = fmaxf(mx, fmaxf(x0, x1));
+            }
+            bool need = false;
+            if (t == 0) mref = mx;
+            else need = mx > mref + PF_SLACK;
+            if (__any_sync(0xffffffffu, need)) {
+                const float f = need ? fast_exp2(mref - mx) : 1.0f;
+                if (need) {
+                    mref = mx;
+                    l *= f;
+                }
+#pragma unroll 1
+                for (int ch = 0; ch < 4; ++ch) {
+                    uint32_t o[32];
+                    tc_ld32(lane_base + o_col + 32 * ch, o);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = f2u(u2f(o[i]) * f);
+                    tc_st32(lane_base + o_col + 32 * ch, o);
+                }
+                tc_wait_st();
+            }
+            const float ms = mref == -INFINITY ? 0.0f : mref;
+            uint32_t pr[32];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float a0 = fast_exp2(u2f(sa[2 * i]) - ms), a1 = fast_exp2(u2f(sa[2 * i + 1]) - ms);
+                const float b0 = fast_exp2(u2f(sb[2 * i]) - ms), b1 = fast_exp2(u2f(sb[2 * i + 1]) - ms);
+                l += (a0 + a1) + (b0 + b1);
+                pr[i] = pf_pack2<BF16>(a0, a1);
+                pr[16 + i] = pf_pack2<BF16>(b0, b1);
+            }
+            tc_st32(lane_base + p_col, pr);
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(&bars[8 + g]);
+        }
+        if (ok && ntiles > 0) {
+            ok = pf_wait(bar0 + 8 * 10, 0, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (!ok) *abort_flag = 1;
+        const float inv = (ok && ntiles > 0 && l > 0.0f) ? p.vd / l : 0.0f;
+        const uint32_t i_tok = r_ok ? r / G : 0, h = hk * G + (r_ok ? r % G : 0);
+        uint16_t *orow = reinterpret_cast<uint16_t *>(p.o) + ((q0 + i_tok) * p.hq + h) * PF_D;
+        if (ok && ntiles > 0) tc_fence_after();
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+            uint32_t o[32];
+            if (ok && ntiles > 0) {
+                tc_ld32(lane_base + o_col + 32 * ch, o);
+                tc_wait_ld();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = 0u;
+            }
+            if (r_ok) {
+#pragma unroll
+                for (int v4 = 0; v4 < 4; ++v4) {
+                    uint4 w;
+                    w.x = pf_pack2<BF16>(u2f(o[8 * v4]) * inv, u2f(o[8 * v4 + 1]) * inv);
+                    w.y = pf_pack2<BF16>(u2f(o[8 * v4 + 2]) * inv, u2f(o[8 * v4 + 3]) * inv);
+                    w.z = pf_pack2<BF16>(u2f(o[8 * v4 + 4]) * inv, u2f(o[8 * v4 + 5]) * inv);
+                    w.w = pf_pack2<BF16>(u2f(o[8 * v4 + 6]) * inv, u2f(o[8 * v4 + 7]) * inv);
+                    *reinterpret_cast<uint4 *>(orow + 32 * ch + 8 * v4) = w;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 9) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(P2_TMEM_COLS) : "memory");
+    if (tid == 0 && *abort_flag) atomicExch(&g_wait_failed, 1);
+}
+
+
 bool fa_prefill_sm100_supported(const FaParams &p, bool kv16) {
     if (!kv16 || p.kv_kind != 0 || p.d != PF_D || p.n_splits != 1) return false;
     if (p.q_dtype != B200_F16 && p.q_dtype != B200_BF16) return false;
@@ -422,15 +732,30 @@ int fa_prefill_sm100_launch(const FaParams &p, bool bf16, cudaStream_t stream) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 16 && !done[dev][bf16]) {
-        const cudaError_t e = bf16 ? cudaFuncSetAttribute(fa_prefill_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM)
-                                   : cudaFuncSetAttribute(fa_prefill_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM);
+        cudaError_t e = bf16 ? cudaFuncSetAttribute(fa_prefill_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM)
+                             : cudaFuncSetAttribute(fa_prefill_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM);
+        if (e == cudaSuccess)
+            e = bf16 ? cudaFuncSetAttribute(fa_prefill_sm100_kernel2<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM)
+                     : cudaFuncSetAttribute(fa_prefill_sm100_kernel2<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM);
         if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "flash_attn (tcgen05 tiles): shared memory opt-in: %s", cudaGetErrorString(e));
         done[dev][bf16] = true;
     }
     const uint64_t rows = (uint64_t)p.lq * p.group;
-    const dim3 grid((unsigned)((rows + PF_BM - 1) / PF_BM), p.hkv, p.b);
-    if (bf16) fa_prefill_sm100_kernel<true><<<grid, PF_THREADS, PF_SMEM, stream>>>(p);
-    else fa_prefill_sm100_kernel<false><<<grid, PF_THREADS, PF_SMEM, stream>>>(p);
+    static const long force = [] { const char *e = getenv("B200_FA_TC_ROWS"); return e ? atol(e) : 0l; }();  // 128 or 256: tile height
+    // 256-row blocks halve the K / V traffic per product and overlap softmax with products inside the block; they
+    // need enough blocks to fill the device
+    bool two = rows >= 1024;
+    if (force == 128) two = false;
+    if (force == 256) two = true;
+    if (two) {
+        const dim3 grid((unsigned)((rows + P2_ROWS - 1) / P2_ROWS), p.hkv, p.b);
+        if (bf16) fa_prefill_sm100_kernel2<true><<<grid, P2_THREADS, P2_SMEM, stream>>>(p);
+        else fa_prefill_sm100_kernel2<false><<<grid, P2_THREADS, P2_SMEM, stream>>>(p);
+    } else {
+        const dim3 grid((unsigned)((rows + PF_BM - 1) / PF_BM), p.hkv, p.b);
+        if (bf16) fa_prefill_sm100_kernel<true><<<grid, PF_THREADS, PF_SMEM, stream>>>(p);
+        else fa_prefill_sm100_kernel<false><<<grid, PF_THREADS, PF_SMEM, stream>>>(p);
+    }
     return check_launch("flash_attn (tcgen05 tiles)");
 }
 

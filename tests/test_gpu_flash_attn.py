@@ -86,6 +86,9 @@ ORACLE_CASES = [
     ("tc_f16_noncausal", "f16", 1, 130, 777, 4, 1, 128, -1, -1, 0.0, False, False),
     ("tc_window", "bf16", 1, 700, 700, 2, 2, 128, 100, 0, 0.0, False, False),
     ("tc_lq_longer", "f16", 1, 600, 450, 4, 4, 128, -1, 0, 0.0, False, False),
+    # 1024 packed rows and more: blocks of two row tiles
+    ("tc2_ragged_rows", "bf16", 1, 530, 900, 4, 2, 128, -1, 0, 0.0, False, False),
+    ("tc2_window", "f16", 2, 300, 640, 8, 2, 128, 70, 0, 0.0, False, False),
 ]
 
 
