@@ -1,6 +1,6 @@
 """Benchmark of the quantized-KV decode attention path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c4|c5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c3|c4|c5]
 
 One step = one decode-attention pass of one layer over a batch of synthetic sequences whose
 compressed KV cache is resident in HBM (a ragged batch of 64 sequences with 512-8192 MXFP4 keys
@@ -405,13 +405,142 @@ def run_ours(args, w, rank, world, local_rank):
         os._exit(0)
 
 
+def run_prefill(args, rank, world, local_rank):
+    """Workload c3: causal prefill of B=4 x S=4096 (Hq 32, Hkv 8, D 128, bf16) with the new K / V written into an
+    NVFP4 cache in the same call. Metric: attention TFLOP/s (4 B Hq S^2 D / 2 flop per step); single GPU."""
+    import torch
+
+    import __graft_entry__ as G
+
+    if args.impl == "reference" or rank != 0:
+        if rank == 0:
+            cpu, flops = cpu_prefill_sample()
+            print(json.dumps({"impl": "reference", "metric": "prefill_attention_tflops", "value": cpu["value"], "unit": "TFLOP/s",
+                              "n_gpus": args.gpus, "steps": 1, "warmup": 0, "higher_is_better": True, "config": {"workload": "c3 (sample)"},
+                              "cpu_baseline": cpu, "e2e": {"value": cpu["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}),
+                  flush=True)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    G.build()
+    P = G.load_package()
+    F = P.flash_attn
+    b, s, hq, hkv, d = 4, 4096, 32, 8, 128
+    nv = P.QuantFormat.parse("nvfp4")
+    kq, vq = P.TurboQuantizer(nv, d, "none", 42, dev), P.TurboQuantizer(nv, d, "none", 44, dev)
+    cfg = P.FlashAttnConfig(d ** -0.5).causal()
+    nbuf = 3  # q/k/v/out sets cycled: 3 x 335 MB, so that no step finds its inputs in L2
+    sets = []
+    for i in range(nbuf):
+        g = torch.Generator(device=dev).manual_seed(77 + i)
+        sets.append((torch.randn((b, s, hq, d), generator=g, device=dev, dtype=torch.bfloat16),
+                     torch.randn((b, s, hkv, d), generator=g, device=dev, dtype=torch.bfloat16),
+                     torch.randn((b, s, hkv, d), generator=g, device=dev, dtype=torch.bfloat16)))
+    kc = torch.zeros((b, hkv, s, kq.row_words()), dtype=torch.int32, device=dev)
+    vc = torch.zeros_like(kc)
+
+    def step(i):
+        q, k, v = sets[i % nbuf]
+        return F.prefill_append(q, k, v, cfg, kc, vc, kq, vq, 0)
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    # attention alone (the dominant kernel), for the roofline
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record()
+    for i in range(args.steps):
+        q, k, v = sets[i % nbuf]
+        F.flash_attn_with_config(q, k, v, cfg)
+    a1.record()
+    torch.cuda.synchronize()
+    attn_ms = a0.elapsed_time(a1) / args.steps
+    # end to end: host q / k / v in, host output back
+    hq_, hk_, hv_ = [t.cpu().pin_memory() for t in sets[0]]
+    out_host = torch.empty((b, s, hq, d), dtype=torch.bfloat16).pin_memory()
+    dq, dk, dv = [torch.empty_like(t) for t in sets[0]]
+
+    def e2e_step():
+        dq.copy_(hq_, non_blocking=True)
+        dk.copy_(hk_, non_blocking=True)
+        dv.copy_(hv_, non_blocking=True)
+        out_host.copy_(F.prefill_append(dq, dk, dv, cfg, kc, vc, kq, vq, 0), non_blocking=True)
+
+    e2e_step()
+    torch.cuda.synchronize()
+    n_e2e = max(2, min(args.steps, 5))
+    e0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / n_e2e
+    for i in range(clock_sample_steps(ms, seconds=0.5, cap=400)):
+        step(i)
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    if P._abi.lib().b200_device_wait_status() != 0:
+        raise SystemExit("bench: a bounded device wait ran out; the numbers are void")
+    flops = 4.0 * b * hq * s * s * d / 2
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except OSError:
+        pass
+    peak, kind = (peaks["bf16_tflops"], "measured cuBLAS bf16 burst (MEASURED_PEAKS.json)") if "bf16_tflops" in peaks else (1590.0, "fallback")
+    cpu, _ = cpu_prefill_sample()
+    line = {"metric": "prefill_attention_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 mma / f32 softmax", "data": "synthetic",
+            "config": {"workload": "c3: causal prefill B=4 S=4096 Hq=32 Hkv=8 D=128 bf16 + NVFP4 cache append",
+                       "l2": f"{nbuf} input sets of 335 MB cycled (L2 is 126 MB)", "parallelism": "single GPU"},
+            "tokens_per_s": b * s / (ms * 1e-3),
+            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": int(sum(t.numel() for t in sets[0])) * 2, "d2h_bytes_per_step": int(out_host.numel()) * 2},
+            "gpu_launches": args.steps * 3,
+            "roofline": {"bound": "tensor", "kernel": "fa_prefill_sm100_kernel2 (attention alone)", "achieved": flops / (attn_ms * 1e-3) / 1e12,
+                         "peak": peak, "unit": "TFLOP/s", "frac": flops / (attn_ms * 1e-3) / 1e12 / peak, "peak_source": kind, "traffic": None},
+            "cpu_baseline": cpu, "clocks": clocks}
+    print(json.dumps(line), flush=True)
+
+
+def cpu_prefill_sample():
+    """The reference's CPU attention on a bounded sample of c3: the last 64 query tokens of one sequence, all heads,
+    over the full 4096 keys (causal)."""
+    from oracle import oracle as O
+    if os.environ.get("OMP_NUM_THREADS") == "1" and "LOCAL_RANK" in os.environ:
+        O.set_num_threads(len(os.sched_getaffinity(0)))
+    s, hq, hkv, d, lq = 4096, 32, 8, 128, 64
+    q = O.round_to(O.normal(1001, lq * hq * d).reshape(1, lq, hq, d), "bf16")
+    k = O.round_to(O.normal(1002, s * hkv * d).reshape(1, s, hkv, d), "bf16")
+    v = O.round_to(O.normal(1003, s * hkv * d).reshape(1, s, hkv, d), "bf16")
+    O.reference_attention(q[:, :4], k, v, d ** -0.5, wr=0)
+    t0 = time.perf_counter()
+    O.reference_attention(q, k, v, d ** -0.5, wr=0)
+    dt = time.perf_counter() - t0
+    flops = 4.0 * hq * d * sum(s - lq + i + 1 for i in range(lq))
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port",
+            "sample": f"last {lq} query tokens of one sequence, all heads, {s} keys ({dt:.2f} s)"}, flops
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c3"])
     ap.add_argument("--verbose", action="store_true", help="print stage markers to stderr")
     ap.add_argument("--uniform-len", type=int, default=0, help="give every sequence this many keys (diagnostic)")
     args = ap.parse_args()
@@ -419,6 +548,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload == "c3":
+        return run_prefill(args, rank, world, local_rank)
     w = dict(WORKLOADS[args.workload])
     if args.uniform_len:
         w["lens"] = args.uniform_len

@@ -101,6 +101,82 @@ __device__ __forceinline__ uint32_t pf_pack2(float lo, float hi) {
     return d;
 }
 
+// ---- packed f32 pairs (fma.rn.f32x2 / add.rn.f32x2) and the three-input maximum ----------------------
+__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void upk2(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// One row's 64 scores of a tile (raw dot products in sa, sb; the softmax scale sl2 > 0 carries log2 e):
+// masks, the row maximum, the decision to move the reference maximum (`need`, with the factor `f` that
+// takes O and the running sum to the new reference) and P as 16-bit pairs. Three instructions per score
+// besides the exponential: a shared three-input maximum, a packed multiply-add and a packed sum.
+template <bool BF16>
+__device__ __forceinline__ void pf_softmax_row(uint32_t (&sa)[32], uint32_t (&sb)[32], bool full, int lo_rel, int hi_rel, float sl2, bool first,
+                                               float &mref, float &l, bool &need, float &f, uint32_t (&pr)[32]) {
+    if (!full) {
+        // keys lo_rel <= i < hi_rel of the tile are visible to this row (sa: keys 0-31, sb: keys 32-63)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (!(i >= lo_rel && i < hi_rel)) sa[i] = 0xff800000u;
+            if (!(i + 32 >= lo_rel && i + 32 < hi_rel)) sb[i] = 0xff800000u;
+        }
+    }
+    float m0 = fmax3(u2f(sa[0]), u2f(sa[1]), u2f(sb[0])), m1 = u2f(sb[1]);
+#pragma unroll
+    for (int i = 2; i < 32; i += 2) {
+        m0 = fmax3(m0, u2f(sa[i]), u2f(sa[i + 1]));
+        m1 = fmax3(m1, u2f(sb[i]), u2f(sb[i + 1]));
+    }
+    const float mx = fmaxf(m0, m1) * sl2;  // sl2 > 0: the maximum commutes with the scale
+    need = false;
+    if (first) mref = mx;
+    else need = mx > mref + PF_SLACK;
+    f = need ? fast_exp2(mref - mx) : 1.0f;
+    if (need) {
+        mref = mx;
+        l *= f;
+    }
+    const float ms = mref == -INFINITY ? 0.0f : mref;
+    const uint64_t sc2 = pk2(sl2, sl2), nm2 = pk2(-ms, -ms);
+    uint64_t acc_a = pk2(0.0f, 0.0f), acc_b = acc_a;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float a0, a1, b0, b1;
+        upk2(ffma2(pk2(u2f(sa[2 * i]), u2f(sa[2 * i + 1])), sc2, nm2), a0, a1);
+        upk2(ffma2(pk2(u2f(sb[2 * i]), u2f(sb[2 * i + 1])), sc2, nm2), b0, b1);
+        a0 = fast_exp2(a0);
+        a1 = fast_exp2(a1);
+        b0 = fast_exp2(b0);
+        b1 = fast_exp2(b1);
+        acc_a = fadd2(acc_a, pk2(a0, a1));
+        acc_b = fadd2(acc_b, pk2(b0, b1));
+        pr[i] = pf_pack2<BF16>(a0, a1);
+        pr[16 + i] = pf_pack2<BF16>(b0, b1);
+    }
+    float s0, s1, s2, s3;
+    upk2(acc_a, s0, s1);
+    upk2(acc_b, s2, s3);
+    l += (s0 + s1) + (s2 + s3);
+}
+
 // bounded wait that also ends when another role gave up; false = give up
 __device__ __forceinline__ bool pf_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     for (uint32_t i = 0; i < (1u << 20); ++i) {
@@ -317,29 +393,14 @@ __global__ void __launch_bounds__(PF_THREADS, 2) fa_prefill_sm100_kernel(const F
             tc_wait_ld();
             const long long j0 = t_lo + (long long)t * PF_BN;
             const bool full = j0 >= lomax && j0 + PF_BN <= himin && j0 + PF_BN <= t_hi;
-            float mx = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                float x0 = u2f(sa[i]) * sl2, x1 = u2f(sb[i]) * sl2;
-                if (!full) {
-                    const long long ja = j0 + i, jb = j0 + 32 + i;
-                    if (!(r_ok && ja >= r_lo && ja < r_hi)) x0 = -INFINITY;
-                    if (!(r_ok && jb >= r_lo && jb < r_hi)) x1 = -INFINITY;
-                }
-                sa[i] = f2u(x0);
-                sb[i] = f2u(x1);
-                mx = fmaxf(mx, fmaxf(x0, x1));
-            }
-            bool need = false;
-            if (t == 0) mref = mx;
-            else need = mx > mref + PF_SLACK;
+            const int lo_rel = r_ok ? (int)max(min(r_lo - j0, (long long)PF_BN), 0ll) : PF_BN;
+            const int hi_rel = r_ok ? (int)max(min(min(r_hi, t_hi) - j0, (long long)PF_BN), 0ll) : 0;
+            bool need;
+            float f;
+            uint32_t pr[32];
+            pf_softmax_row<BF16>(sa, sb, full, lo_rel, hi_rel, sl2, t == 0, mref, l, need, f, pr);
             if (__any_sync(0xffffffffu, need)) {
-                // rows whose maximum moved: O and the running sum go to the new reference
-                const float f = need ? fast_exp2(mref - mx) : 1.0f;
-                if (need) {
-                    mref = mx;
-                    l *= f;
-                }
+                // rows whose maximum moved: O goes to the new reference
 #pragma unroll 1
                 for (int ch = 0; ch < 4; ++ch) {
                     uint32_t o[32];
@@ -350,16 +411,6 @@ __global__ void __launch_bounds__(PF_THREADS, 2) fa_prefill_sm100_kernel(const F
                     tc_st32(lane_base + PF_O_COL + 32 * ch, o);
                 }
                 tc_wait_st();
-            }
-            const float ms = mref == -INFINITY ? 0.0f : mref;
-            uint32_t pr[32];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float a0 = fast_exp2(u2f(sa[2 * i]) - ms), a1 = fast_exp2(u2f(sa[2 * i + 1]) - ms);
-                const float b0 = fast_exp2(u2f(sb[2 * i]) - ms), b1 = fast_exp2(u2f(sb[2 * i + 1]) - ms);
-                l += (a0 + a1) + (b0 + b1);
-                pr[i] = pf_pack2<BF16>(a0, a1);
-                pr[16 + i] = pf_pack2<BF16>(b0, b1);
             }
             tc_st32(lane_base + PF_P_COL, pr);
             tc_wait_st();
@@ -628,28 +679,14 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
             tc_wait_ld();
             const long long j0 = t_lo + (long long)t * PF_BN;
             const bool full = j0 >= lomax && j0 + PF_BN <= himin && j0 + PF_BN <= t_hi;
-            float mx = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                float x0 = u2f(sa[i]) * sl2, x1 = u2f(sb[i]) * sl2;
-                if (!full) {
-                    const long long ja = j0 + i, jb = j0 + 32 + i;
-                    if (!(r_ok && ja >= r_lo && ja < r_hi)) x0 = -INFINITY;
-                    if (!(r_ok && jb >= r_lo && jb < r_hi)) x1 = -INFINITY;
-                }
-                sa[i] = f2u(x0);
-                sb[i] = f2u(x1);
-                mx = fmaxf(mx, fmaxf(x0, x1));
-            }
-            bool need = false;
-            if (t == 0) mref = mx;
-            else need = mx > mref + PF_SLACK;
+            const int lo_rel = r_ok ? (int)max(min(r_lo - j0, (long long)PF_BN), 0ll) : PF_BN;
+            const int hi_rel = r_ok ? (int)max(min(min(r_hi, t_hi) - j0, (long long)PF_BN), 0ll) : 0;
+            bool need;
+            float f;
+            uint32_t pr[32];
+            pf_softmax_row<BF16>(sa, sb, full, lo_rel, hi_rel, sl2, t == 0, mref, l, need, f, pr);
             if (__any_sync(0xffffffffu, need)) {
-                const float f = need ? fast_exp2(mref - mx) : 1.0f;
-                if (need) {
-                    mref = mx;
-                    l *= f;
-                }
+                // rows whose maximum moved: O goes to the new reference
 #pragma unroll 1
                 for (int ch = 0; ch < 4; ++ch) {
                     uint32_t o[32];
@@ -660,16 +697,6 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
                     tc_st32(lane_base + o_col + 32 * ch, o);
                 }
                 tc_wait_st();
-            }
-            const float ms = mref == -INFINITY ? 0.0f : mref;
-            uint32_t pr[32];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float a0 = fast_exp2(u2f(sa[2 * i]) - ms), a1 = fast_exp2(u2f(sa[2 * i + 1]) - ms);
-                const float b0 = fast_exp2(u2f(sb[2 * i]) - ms), b1 = fast_exp2(u2f(sb[2 * i + 1]) - ms);
-                l += (a0 + a1) + (b0 + b1);
-                pr[i] = pf_pack2<BF16>(a0, a1);
-                pr[16 + i] = pf_pack2<BF16>(b0, b1);
             }
             tc_st32(lane_base + p_col, pr);
             tc_wait_st();
@@ -720,6 +747,7 @@ bool fa_prefill_sm100_supported(const FaParams &p, bool kv16) {
     if (!kv16 || p.kv_kind != 0 || p.d != PF_D || p.n_splits != 1) return false;
     if (p.q_dtype != B200_F16 && p.q_dtype != B200_BF16) return false;
     if (p.softcap > 0.0f || p.alibi != nullptr) return false;
+    if (!(p.scale * p.kd > 0.0f)) return false;  // the row maximum is taken before the scale is applied
     if ((uint64_t)p.lq * p.group < 4 * PF_BM) return false;  // short chunks and decode stay on the mma.sync kernel
     // 16-byte chunks of q rows
     if ((reinterpret_cast<uintptr_t>(p.q) & 15) || ((p.q_sb | p.q_ss | p.q_sh) & 7)) return false;
