@@ -548,44 +548,63 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
 
     if (warp == 8) {
         // ================================================================ loader
+        // Per lane constants: the lane's row and chunk inside a step of 32 chunks (K: 8 rows x 4 chunks of one
+        // core-matrix row group; V: 16 keys x 2 chunks), so that a copy costs an add or two besides itself.
+        const uint64_t k_row8 = 8ull * p.k_ss * 2, v_row16 = 16ull * p.v_ss * 2;           // bytes between steps
+        const uint64_t k_lane = (uint64_t)(lane & 7) * p.k_ss * 2 + (uint64_t)(lane >> 3) * 16;
+        const uint64_t v_lane = (uint64_t)(lane >> 1) * p.v_ss * 2 + (uint64_t)(lane & 1) * 16;
+        const uint32_t k_dst_lane = (uint32_t)(lane >> 3) * 128 + (uint32_t)(lane & 7) * 16;
+        const uint32_t v_key = (uint32_t)(lane >> 1);
+        const uint32_t v_dst_lane = (uint32_t)(lane & 1) * 1024 + (v_key >> 3) * 128 + (v_key & 7) * 16;
         auto load_tile = [&](int t) {
             const long long j0 = t_lo + (long long)t * PF_BN;
             const int st = t % P2_STAGES;
-            const uint32_t dk = sbase + P2_SM_K + st * PF_KT_BYTES, dv = sbase + P2_SM_V + st * PF_VT_BYTES;
+            const uint32_t dk = sbase + P2_SM_K + st * PF_KT_BYTES + k_dst_lane, dv = sbase + P2_SM_V + st * PF_VT_BYTES + v_dst_lane;
+            const char *ks = kb + (uint64_t)j0 * p.k_ss * 2 + k_lane, *vs = vb + (uint64_t)j0 * p.v_ss * 2 + v_lane;
+            if (j0 + PF_BN <= t_hi) {
+                // whole tile: K step = row group g (8 keys) x chunks 4 q .. 4 q + 3; V step = keys 16 q .. 16 q + 15 x chunks 2 c, 2 c + 1
+#pragma unroll
+                for (int g8 = 0; g8 < 8; ++g8) {
+                    const char *src = ks + g8 * k_row8;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) pf_cp16(dk + g8 * 2048 + q4 * 512, src + q4 * 64, true);
+                }
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const char *src = vs + q4 * v_row16;
+#pragma unroll
+                    for (int c8 = 0; c8 < 8; ++c8) pf_cp16(dv + c8 * 2048 + q4 * 256, src + c8 * 32, true);
+                }
+            } else {
+                // ragged last tile: rows past the end are zero filled
 #pragma unroll 4
-            for (int blk = 0; blk < 32; ++blk) {
-                const int grp = blk >> 2, kc = (blk & 3) * 4 + (lane >> 3), rr = grp * 8 + (lane & 7);
-                const long long j = j0 + rr;
-                const bool ok = j < t_hi;
-                pf_cp16(dk + grp * 2048 + kc * 128 + (rr & 7) * 16, kb + (uint64_t)(ok ? j : t_lo) * p.k_ss * 2 + kc * 16, ok);
-            }
+                for (int blk = 0; blk < 32; ++blk) {
+                    const int g8 = blk >> 2, q4 = blk & 3;
+                    const bool ok = j0 + g8 * 8 + (lane & 7) < t_hi;
+                    pf_cp16(dk + g8 * 2048 + q4 * 512, ok ? ks + g8 * k_row8 + q4 * 64 : kb, ok);
+                }
 #pragma unroll 4
-            for (int blk = 0; blk < 32; ++blk) {
-                const int dc = (blk >> 2) * 2 + (lane & 1), key = (blk & 3) * 16 + (lane >> 1);
-                const long long j = j0 + key;
-                const bool ok = j < t_hi;
-                pf_cp16(dv + dc * 1024 + (key >> 3) * 128 + (key & 7) * 16, vb + (uint64_t)(ok ? j : t_lo) * p.v_ss * 2 + dc * 16, ok);
+                for (int blk = 0; blk < 32; ++blk) {
+                    const int q4 = blk >> 3, c8 = blk & 7;
+                    const bool ok = j0 + q4 * 16 + (lane >> 1) < t_hi;
+                    pf_cp16(dv + c8 * 2048 + q4 * 256, ok ? vs + q4 * v_row16 + c8 * 32 : vb, ok);
+                }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        // Tile t is announced as soon as it has landed; only then does the loader wait for the stage that
-        // tile t + 2 goes into (read last by the products of tile t - 1, which the issuing warp issues
-        // after it has seen tile t). Tiles t + 1 and t + 2 are in flight while tile t is consumed.
+        // Three tiles in flight. Nothing here waits for a copy: every lane leaves an asynchronous arrival on
+        // the tile's barrier that fires when its own copies have landed, so a tile is announced the moment
+        // it is complete, however busy this warp is with the next one. The only wait is for the stage a
+        // tile goes into (read last by the products of tile t - 3).
         bool ok = true;
-        if (ntiles > 0) load_tile(0);
-        if (ntiles > 1) load_tile(1);
         for (int t = 0; t < ntiles && ok; ++t) {
-            if (t + 1 < ntiles) asm volatile("cp.async.wait_group 1;" ::: "memory");
-            else asm volatile("cp.async.wait_group 0;" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(&bars[t % P2_STAGES]);
-            if (t + 2 < ntiles) {
-                if (t >= 1) {
-                    ok = pf_wait(bar0 + 8 * (3 + (t - 1) % P2_STAGES), ((t - 1) / P2_STAGES) & 1, abort_flag);
-                    ok = __all_sync(0xffffffffu, ok);
-                }
-                if (ok) load_tile(t + 2);
+            if (t >= P2_STAGES) {
+                ok = pf_wait(bar0 + 8 * (3 + t % P2_STAGES), ((t / P2_STAGES) - 1) & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
             }
+            load_tile(t);
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar0 + 8 * (t % P2_STAGES)) : "memory");
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         if (!ok) *abort_flag = 1;
@@ -610,6 +629,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
             if (ntiles > 0) {
                 ok = pf_wait(bar0, 0, abort_flag);
                 if (ok) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copies wrote through the generic proxy
                     tc_fence_after();
                     issue_qk(0, 0);
                     issue_qk(1, 0);
@@ -623,6 +643,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
                 if (t + 1 < ntiles) {
                     ok = pf_wait(bar0 + 8 * ((t + 1) % P2_STAGES), ((t + 1) / P2_STAGES) & 1, abort_flag);
                     if (!ok) break;
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     tc_fence_after();
                     issue_qk(0, t + 1);
                 }
