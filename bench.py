@@ -316,16 +316,35 @@ def run_ours(args, w, rank, world, local_rank):
             dist.all_gather_into_tensor(gathered, out)
         out_host.copy_(out, non_blocking=True)
 
-    for i in range(min(args.warmup, 3)):
+    for i in range(max(min(args.warmup, 3), nbuf)):
         e2e_step(i)
     barrier()
+    # the same calls captured once per cache: a serving loop replays its step (copies included) instead of paying the
+    # host's call path every token
+    e2e_graphs = []
+    if graphs:
+        try:
+            for i in range(nbuf):
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr):
+                    e2e_step(i)
+                e2e_graphs.append(gr)
+        except Exception as e:
+            print(f"bench: capture of the end-to-end step failed ({e}); timing eager calls", file=sys.stderr)
+            e2e_graphs = []
+            torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
     e0.record()
     for i in range(args.steps):
-        e2e_step(i)
+        if e2e_graphs:
+            e2e_graphs[i % nbuf].replay()
+        else:
+            e2e_step(i)
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
+    e2e_graphs.clear()
     stage("end-to-end region done")
     # max over ranks of the times, sum over ranks of the bytes
     (total_ms, e2e_ms, kern_ms), job_bytes = aggregate_over_ranks(
