@@ -227,11 +227,24 @@ def run_ours(args, w, rank, world, local_rank):
 
     # one prepared call per cache, each captured in a CUDA graph (attention + the all-gather of the outputs), so
     # that the host only replays: a step of tens of microseconds would otherwise be bound by the Python call path
-    calls = [P.PackedAttention(q, kc, vc, kv_len, kq, vq, cfg, out=out) for kc, vc in caches]
+    # N > 1: the outputs of all ranks are assembled on every rank inside the step. Default: by the attention's own
+    # epilogue (peer stores over NVLink into symmetric memory, b200_tq_attention_gather); B200_BENCH_GATHER=nccl uses
+    # an NCCL all-gather after the attention instead.
+    peer_gather = None
+    if world > 1 and os.environ.get("B200_BENCH_GATHER", "fused") != "nccl":
+        try:
+            peer_gather = P.OutputGather(b * hq, d, tdt, dev)
+        except Exception as e:
+            print(f"bench: symmetric memory for the fused gather is unavailable ({e}); using NCCL", file=sys.stderr)
+        ok_all = torch.tensor([1 if peer_gather is not None else 0], device=dev)
+        dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)
+        if int(ok_all.item()) == 0:
+            peer_gather = None
+    calls = [P.PackedAttention(q, kc, vc, kv_len, kq, vq, cfg, out=out, gather=peer_gather) for kc, vc in caches]
 
     def eager_step(i):
         calls[i % nbuf].run()
-        if world > 1:
+        if world > 1 and peer_gather is None:
             dist.all_gather_into_tensor(gathered, out)
 
     for i in range(nbuf):
@@ -297,6 +310,17 @@ def run_ours(args, w, rank, world, local_rank):
     barrier()
     total_ms = ev0.elapsed_time(ev1)
     stage("timed region done")
+    gather_note = "outputs all-gathered over NCCL"
+    if peer_gather is not None:
+        # the gathered rows of the last step against an NCCL all-gather of the same outputs
+        dist.all_gather_into_tensor(gathered, out)
+        torch.cuda.synchronize()
+        mine = peer_gather.gathered().reshape(gathered.shape)
+        same = torch.tensor([1 if torch.equal(mine, gathered) else 0], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        if int(same.item()) != 1:
+            raise SystemExit("bench: the fused gather differs from the NCCL all-gather of the same outputs")
+        gather_note = "outputs gathered on every rank by the attention epilogue (peer stores over NVLink; checked against NCCL)"
     per_step = [total_ms / args.steps]
     # ---- end to end through the public API with host buffers: H2D of the step's inputs, append of the new
     # token, attention, D2H of the outputs
@@ -311,8 +335,8 @@ def run_ours(args, w, rank, world, local_rank):
         v_new.copy_(vnew_host, non_blocking=True)
         _kv_append(k_new, v_new, kc, vc, kq, vq, lens_dev)
         lens_dev.add_(1)
-        P.attention_packed(q, kc, vc, lens_dev, kq, vq, cfg, out=out)
-        if world > 1:
+        P.PackedAttention(q, kc, vc, lens_dev, kq, vq, cfg, out=out, gather=peer_gather).run()
+        if world > 1 and peer_gather is None:
             dist.all_gather_into_tensor(gathered, out)
         out_host.copy_(out, non_blocking=True)
 
@@ -390,7 +414,7 @@ def run_ours(args, w, rank, world, local_rank):
                        "kv_format": w["fmt"], "rotation": w["rot"], "total_keys_per_gpu": int(lens.sum()),
                        "launch": f"CUDA graph replay ({group} steps per graph)" if graphs else "eager C ABI calls",
                        "l2": f"{nbuf} caches of {cache_bytes / 1e6:.0f} MB cycled (each step reads other rows than the last; L2 is 126 MB)",
-                       "parallelism": f"batch shard x{world}, outputs all-gathered over NCCL" if world > 1 else "single GPU"},
+                       "parallelism": f"batch shard x{world}, {gather_note}" if world > 1 else "single GPU"},
             "tokens_per_s": world * b / (ms * 1e-3),
             "pct_of_8000_gbs_nominal": 100.0 * value / (8000.0 * world),
             "e2e": {"value": job_bytes / (e2e_ms / args.steps * 1e-3) / 1e9, "unit": "GB/s",

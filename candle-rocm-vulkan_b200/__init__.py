@@ -7,5 +7,5 @@ so load it with `__graft_entry__.load_package()`, which registers it as `candle_
 """
 from . import _abi  # noqa: F401
 from . import flash_attn  # noqa: F401
-from .turbo_quant import (FlashAttnConfig, PackedAttention, QuantFormat, QuantizedTensor, TurboKvCache,  # noqa: F401
+from .turbo_quant import (FlashAttnConfig, OutputGather, PackedAttention, QuantFormat, QuantizedTensor, TurboKvCache,  # noqa: F401
                           TurboQuantizer, attention_packed)

@@ -69,6 +69,11 @@ class TqAttnArgs(C.Structure):
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p)]
 
 
+class PeerGather(C.Structure):
+    _fields_ = [("peer_bufs", C.c_void_p), ("peer_flags", C.c_void_p), ("world", C.c_uint32), ("rank", C.c_uint32),
+                ("step", C.c_void_p), ("done_ctr", C.c_void_p)]
+
+
 class FaArgs(C.Structure):
     _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p),
                 ("q_dtype", C.c_int32), ("kv_dtype", C.c_int32), ("cu_q", C.c_void_p), ("cu_k", C.c_void_p),
@@ -84,7 +89,8 @@ class FaArgs(C.Structure):
 SYMBOLS = [
     "b200_row_layout", "b200_codebook", "b200_hadamard_signs", "b200_row_group", "b200_split_count_grouped",
     "b200_describe", "b200_last_error", "b200_tq_rotate", "b200_tq_quantize", "b200_tq_dequantize", "b200_kv_append",
-    "b200_tq_attention_workspace_bytes", "b200_tq_attention", "b200_tq_attention_static", "b200_flash_attn_workspace_bytes",
+    "b200_tq_attention_workspace_bytes", "b200_tq_attention", "b200_tq_attention_static", "b200_tq_attention_gather",
+    "b200_flash_attn_workspace_bytes",
     "b200_flash_attn", "b200_fa_prefill_append", "b200_device_wait_status",
 ]
 
@@ -120,6 +126,7 @@ def lib():
         l.b200_tq_attention_workspace_bytes.restype = C.c_size_t
         l.b200_tq_attention.argtypes = [C.POINTER(TqAttnArgs), C.c_void_p]
         l.b200_tq_attention_static.argtypes = [C.POINTER(TqAttnArgs), C.c_void_p]
+        l.b200_tq_attention_gather.argtypes = [C.POINTER(TqAttnArgs), C.POINTER(PeerGather), C.c_void_p]
         l.b200_flash_attn_workspace_bytes.argtypes = [C.POINTER(FaArgs)]
         l.b200_flash_attn_workspace_bytes.restype = C.c_size_t
         l.b200_flash_attn.argtypes = [C.POINTER(FaArgs), C.c_void_p]

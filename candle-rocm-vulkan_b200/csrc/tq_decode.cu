@@ -193,10 +193,21 @@ extern "C" size_t b200_tq_attention_workspace_bytes(const B200TqAttnArgs *a) {
     return pl.ws_bytes;
 }
 
+// set by b200_tq_attention_gather around its call of b200_tq_attention (same thread)
+static thread_local const B200PeerGather *tl_gather = nullptr;
+
 extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_) {
     DecodePlan pl;
     const int rc = make_plan(a, pl);
     if (rc) return rc;
+    if (tl_gather) {
+        pl.p.peer_bufs = tl_gather->peer_bufs;
+        pl.p.peer_flags = tl_gather->peer_flags;
+        pl.p.world = tl_gather->world;
+        pl.p.rank = tl_gather->rank;
+        pl.p.step = tl_gather->step;
+        pl.p.done_ctr = tl_gather->done_ctr;
+    }
     cudaStream_t stream = (cudaStream_t)stream_;
     if ((uint64_t)a->b * a->hq * a->lq == 0) return B200_OK;
     if (!a->q || !a->out || !a->k_rows || !a->v_rows) return set_error(B200_ERR_BAD_ARG, "tq_attention: null pointer");
@@ -240,6 +251,17 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
         if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "tq_combine: %s", cudaGetErrorString(e));
         return check_launch("tq_combine");
     }
+}
+
+extern "C" int b200_tq_attention_gather(const B200TqAttnArgs *a, const B200PeerGather *g, b200_stream_t stream) {
+    if (!a || !g) return set_error(B200_ERR_BAD_ARG, "tq_attention_gather: null args");
+    if (g->world == 0 || g->world > 64 || g->rank >= g->world || !g->peer_bufs || !g->peer_flags || !g->step || !g->done_ctr)
+        return set_error(B200_ERR_BAD_ARG, "tq_attention_gather: world %u, rank %u, or a null pointer", g->world, g->rank);
+    if ((uint64_t)a->b * a->hq * a->lq == 0) return set_error(B200_ERR_BAD_ARG, "tq_attention_gather: no output rows to gather");
+    tl_gather = g;
+    const int rc = b200_tq_attention(a, stream);
+    tl_gather = nullptr;
+    return rc;
 }
 
 // ---------------------------------------------------------------------------------------------

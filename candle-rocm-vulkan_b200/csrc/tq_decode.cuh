@@ -74,6 +74,11 @@ struct DecodeParams {
     uint32_t rows_cap;      // rows that exist in every (batch, head) slab of both caches (0 = only the visible ones)
     uint32_t col_cost;      // cost of starting a column, in tiles, for the split of the work between the warps
     uint32_t qstage_bytes;  // query staging for the rotation (0 without it)
+    // outputs gathered on every GPU by the combine kernel (world == 0: off)
+    void *const *peer_bufs;
+    uint32_t *const *peer_flags;
+    uint32_t world, rank;
+    uint32_t *step, *done_ctr;
 };
 
 __host__ __device__ constexpr bool fmt_is4(int m) { return m == B200_MXFP4 || m == B200_NVFP4 || m == B200_TURBO_MSE; }
@@ -965,6 +970,10 @@ __global__ void __launch_bounds__(128) tq_combine_kernel(const DecodeParams p) {
     // launched with programmatic stream serialization: wait here until the decode grid has finished
     // and its partial results are visible
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // gathered outputs: this step's number (the same for all blocks: only the last block of the grid
+    // advances it, at its very end) selects one of the two slots of every rank's buffer
+    const uint32_t g_step = p.world ? *reinterpret_cast<volatile uint32_t *>(p.step) + 1u : 0u;
+    const size_t g_base = p.world ? ((size_t)(g_step & 1u) * p.world + p.rank) * rows * HD : 0;
     for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const uint32_t i = (uint32_t)(row % p.lq);
         const uint32_t h = (uint32_t)((row / p.lq) % p.hq);
@@ -976,6 +985,9 @@ __global__ void __launch_bounds__(128) tq_combine_kernel(const DecodeParams p) {
             if (warp == 0) {
 #pragma unroll
                 for (int k = 0; k < EPL; ++k) store_elem_rt(p.out, obase + lane + 32 * k, 0.0f, p.out_dtype);
+                for (uint32_t pr = 0; pr < p.world; ++pr)
+#pragma unroll
+                    for (int k = 0; k < EPL; ++k) store_elem_rt(p.peer_bufs[pr], g_base + row * HD + lane + 32 * k, 0.0f, p.out_dtype);
             }
             continue;
         }
@@ -1045,8 +1057,48 @@ __global__ void __launch_bounds__(128) tq_combine_kernel(const DecodeParams p) {
             }
 #pragma unroll
             for (int k = 0; k < EPL; ++k) store_elem_rt(p.out, obase + lane + 32 * k, rb[lane + 32 * k], p.out_dtype);
+            // the same row into every rank's gathered buffer: plain stores through the peer mappings
+            for (uint32_t pr = 0; pr < p.world; ++pr)
+#pragma unroll
+                for (int k = 0; k < EPL; ++k) store_elem_rt(p.peer_bufs[pr], g_base + row * HD + lane + 32 * k, rb[lane + 32 * k], p.out_dtype);
         }
         __syncthreads();
+    }
+    if (p.world) {
+        // Every block makes its rows visible system-wide and counts itself; the last one publishes this
+        // rank's step in every rank's flags and waits until all ranks have published it.
+        __syncthreads();
+        __shared__ uint32_t s_last;
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            s_last = atomicAdd(p.done_ctr, 1u) == gridDim.x - 1 ? 1u : 0u;
+        }
+        __syncthreads();
+        if (s_last && warp == 0) {
+            bool ok = true;
+            if (lane == 0) *p.done_ctr = 0;
+            for (uint32_t pr = lane; pr < p.world; pr += 32) {
+                __threadfence_system();
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[pr] + p.rank), "r"(g_step) : "memory");
+            }
+            for (uint32_t pr = lane; pr < p.world; pr += 32) {
+                const uint32_t *flag = p.peer_flags[p.rank] + pr;
+                uint32_t seen = 0;
+                // steps only grow; a rank that is one step ahead has already passed this one
+                for (uint32_t spin = 0; spin < (1u << 21); ++spin) {
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+                    if ((int32_t)(seen - g_step) >= 0) break;
+                    __nanosleep(64);
+                }
+                if ((int32_t)(seen - g_step) < 0) ok = false;
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (lane == 0) {
+                if (!ok && p.status) atomicExch(p.status, 2);
+                *reinterpret_cast<volatile uint32_t *>(p.step) = g_step;
+                __threadfence();
+            }
+        }
     }
 }
 

@@ -252,13 +252,44 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
     return ws
 
 
+class OutputGather:
+    """Buffers for b200_tq_attention_gather on one rank of a `torch.distributed` group: the gathered outputs of all
+    ranks (two slots) and the step flags live in symmetric memory, so every rank can store into every other rank's copy.
+    `rows` = batch * q_heads * seq_q of one rank (all ranks alike)."""
+
+    def __init__(self, rows: int, d: int, dtype, device, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as sm
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.buf = sm.empty((2, self.world, rows, d), dtype=dtype, device=device)
+        self.flags = sm.empty((max(self.world, 4),), dtype=torch.int32, device=device)
+        self._h_buf = sm.rendezvous(self.buf, group)
+        self._h_flags = sm.rendezvous(self.flags, group)
+        self.buf.zero_()
+        self.flags.zero_()
+        self.state = torch.zeros(2, dtype=torch.int32, device=device)  # step, block counter
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+        self.args = A.PeerGather(int(self._h_buf.buffer_ptrs_dev), int(self._h_flags.buffer_ptrs_dev), self.world, self.rank,
+                                 self.state.data_ptr(), self.state.data_ptr() + 4)
+
+    def steps_done(self) -> int:
+        return int(self.state[0].item())
+
+    def gathered(self) -> torch.Tensor:
+        """(world, rows, d): the rows of all ranks after the last completed call (synchronizes to read the step)."""
+        return self.buf[self.steps_done() & 1]
+
+
 class PackedAttention:
     """A prepared `attention_packed` call: arguments checked and marshalled once, `run()` only
     launches (a few microseconds of host time, and capturable in a CUDA graph after one warm-up
     call). The tensors given here are read / written by every `run()`; keep them alive."""
 
     def __init__(self, q: torch.Tensor, k_rows: torch.Tensor, v_rows: torch.Tensor, kv_len, kq: TurboQuantizer,
-                 vq: TurboQuantizer, cfg: FlashAttnConfig, out: Optional[torch.Tensor] = None):
+                 vq: TurboQuantizer, cfg: FlashAttnConfig, out: Optional[torch.Tensor] = None,
+                 gather: Optional["OutputGather"] = None):
         _need_cuda(q, "q")
         b, hq, lq, d = q.shape
         bk, hkv, cap, kw = k_rows.shape
@@ -310,6 +341,13 @@ class PackedAttention:
         self.args, self.out, self.device = args, out, q.device
         self._keep = (q, k_rows, v_rows, kv_len, kq, vq, alibi, ws)
         self._fn, self._ref = A.lib().b200_tq_attention, C.byref(args)
+        self._gather = gather
+        if gather is not None:
+            # outputs also stored into every rank's gathered buffer by the kernel that merges the key splits
+            if out.numel() != gather.buf.shape[2] * gather.buf.shape[3] or out.dtype != gather.buf.dtype:
+                raise ValueError("OutputGather was sized for other outputs")
+            fn, gref = A.lib().b200_tq_attention_gather, C.byref(gather.args)
+            self._fn = lambda ref, stream: fn(ref, gref, stream)
 
     def run(self) -> torch.Tensor:
         rc = self._fn(self._ref, torch.cuda.current_stream(self.device).cuda_stream)

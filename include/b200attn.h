@@ -247,6 +247,32 @@ int b200_tq_attention(const B200TqAttnArgs *args, b200_stream_t stream);
 #define B200_STATIC_SCRATCH_BYTES (8u << 20)
 int b200_tq_attention_static(const B200TqAttnArgs *args, b200_stream_t stream);
 
+/* ---- attention over packed rows, outputs gathered on every GPU ---------------------------------- */
+/* The all-gather of the outputs that follows a sharded decode step (every rank holds its own batch
+ * entries or kv heads; the reference gathers with NCCL, SURVEY of the path: "one ncclAllGather of
+ * outputs per layer"), fused into the epilogue of the attention: the kernel that merges the key
+ * splits stores every finished output row into the gathered buffer of every rank (plain peer
+ * stores over NVLink, no multicast), the last block of the grid publishes this rank's step number
+ * in every rank's flag array and waits, with a bound, until every rank has published the same step.
+ * When the call has completed in stream order, slot (step & 1) of this rank's gathered buffer
+ * holds the rows of all ranks: [world][b * hq * lq][d] elements of out_dtype, rank r's rows in
+ * block r, each in (batch, head, token) order. Two slots, because a rank may run one step ahead.
+ *   peer_bufs   device array of `world` pointers: the gathered buffers (2 slots each) of all ranks,
+ *               mapped into this process (symmetric memory / IPC); peer_bufs[rank] is the local one
+ *   peer_flags  device array of `world` pointers: each rank's `world` flag words, zeroed once
+ *   step        device word of this rank, zero before the first call: steps completed so far
+ *   done_ctr    device word of this rank, zero before the first call
+ * All ranks must make the same sequence of calls. The wait for the other ranks is bounded; if it
+ * runs out, args->status (if given) is set to 2 and the buffer is incomplete for that step. */
+typedef struct B200PeerGather {
+    void *const *peer_bufs;
+    uint32_t *const *peer_flags;
+    uint32_t world, rank;
+    uint32_t *step;
+    uint32_t *done_ctr;
+} B200PeerGather;
+int b200_tq_attention_gather(const B200TqAttnArgs *args, const B200PeerGather *gather, b200_stream_t stream);
+
 /* ---- attention over dense K / V ------------------------------------------------------------------- */
 /* Replaces CudaStorage::flash_attn / flash_attn_paged (accel.rs:254-506), the kernels fa_row*,
  * fa2_*, fa3_*, fa_combine_* (candle-core/kernels/flash_attn_impl.h) and therefore the device

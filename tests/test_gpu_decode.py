@@ -271,3 +271,40 @@ def test_full_size_properties_config2(P, oracle):
     assert torch.equal(out3, out)
     # 4. linearity in V: attention over 2 * V rows (scale word doubled) is twice the output
     assert torch.isfinite(out).all()
+
+
+def test_gather_epilogue_on_one_rank(P, oracle):
+    """b200_tq_attention_gather with a world of one: the rows land in slot (step & 1) of the gathered buffer, the step
+    and the flag advance, the block counter returns to zero, and the regular output is unchanged. (The exchange between
+    ranks is exercised by `bench.py --gpus N`, which checks the gathered rows against an NCCL all-gather.)"""
+    import ctypes as C
+    A = P._abi
+    dev = torch.device("cuda:0")
+    b, hq, hkv, d, cap = 3, 8, 2, 128, 700
+    kq = P.TurboQuantizer(fmt(P, A.MXFP4), d, "none", 42, dev)
+    vq = P.TurboQuantizer(fmt(P, A.MXFP4), d, "none", 44, dev)
+    k_rows = kq.quantize_rows(to_dev(oracle.normal(5, b * hkv * cap * d).reshape(-1, d), "bf16")).view(b, hkv, cap, -1)
+    v_rows = vq.quantize_rows(to_dev(oracle.normal(6, b * hkv * cap * d).reshape(-1, d), "bf16")).view(b, hkv, cap, -1)
+    kv_len = torch.tensor([700, 33, 512], dtype=torch.int32, device=dev)
+    cfg = P.FlashAttnConfig(d ** -0.5).causal()
+    buf = torch.full((2, 1, b * hq, d), 7.0, dtype=torch.bfloat16, device=dev)
+    flags = torch.zeros(4, dtype=torch.int32, device=dev)
+    state = torch.zeros(2, dtype=torch.int32, device=dev)
+    ptrs = torch.tensor([buf.data_ptr(), flags.data_ptr()], dtype=torch.int64, device=dev)
+
+    class G:  # what OutputGather provides, without symmetric memory
+        pass
+    g = G()
+    g.buf = buf
+    g.args = A.PeerGather(ptrs.data_ptr(), ptrs.data_ptr() + 8, 1, 0, state.data_ptr(), state.data_ptr() + 4)
+    for step in (1, 2, 3):
+        q = to_dev(oracle.normal(90 + step, b * hq * d).reshape(b, hq, 1, d), "bf16")
+        want = P.attention_packed(q, k_rows, v_rows, kv_len, kq, vq, cfg)
+        got = P.PackedAttention(q, k_rows, v_rows, kv_len, kq, vq, cfg, gather=g).run()
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+        assert state.tolist() == [step, 0] and flags.tolist()[0] == step
+        assert torch.equal(buf[step & 1, 0].view(b, hq, 1, d), want)
+    with pytest.raises(A.B200Error, match="world"):
+        g.args.world = 0
+        P.PackedAttention(q, k_rows, v_rows, kv_len, kq, vq, cfg, gather=g).run()
