@@ -44,7 +44,9 @@ WORKLOADS = {
 def seq_lens(w, rank=0):
     from oracle import oracle as O  # only the seeded generator of the reference is used here
     if w["lens"] == "uniform512-8192":
-        return (512 + O.u64s(2002 + rank, w["b"]) % np.uint64(7681)).astype(np.int32)
+        # every rank gets the same multiset of lengths (weak scaling: the work per GPU is fixed), in its own order
+        lens = (512 + O.u64s(2002, w["b"]) % np.uint64(7681)).astype(np.int32)
+        return np.roll(lens, 7 * rank)
     return np.full(w["b"], w["lens"], np.int32)
 
 
@@ -240,6 +242,17 @@ def run_ours(args, w, rank, world, local_rank):
         dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)
         if int(ok_all.item()) == 0:
             peer_gather = None
+    if world == 1 and os.environ.get("B200_BENCH_SELF_GATHER") == "1":
+        # diagnostic: the gather epilogue with a world of one (plain device buffers), to time its protocol alone
+        class _Self:
+            pass
+        peer_gather = _Self()
+        peer_gather.buf = torch.zeros((2, 1, b * hq, d), dtype=tdt, device=dev)
+        peer_gather._flags = torch.zeros(4, dtype=torch.int32, device=dev)
+        peer_gather._state = torch.zeros(2, dtype=torch.int32, device=dev)
+        peer_gather._ptrs = torch.tensor([peer_gather.buf.data_ptr(), peer_gather._flags.data_ptr()], dtype=torch.int64, device=dev)
+        peer_gather.args = A.PeerGather(peer_gather._ptrs.data_ptr(), peer_gather._ptrs.data_ptr() + 8, 1, 0,
+                                        peer_gather._state.data_ptr(), peer_gather._state.data_ptr() + 4)
     calls = [P.PackedAttention(q, kc, vc, kv_len, kq, vq, cfg, out=out, gather=peer_gather) for kc, vc in caches]
 
     def eager_step(i):
@@ -311,7 +324,7 @@ def run_ours(args, w, rank, world, local_rank):
     total_ms = ev0.elapsed_time(ev1)
     stage("timed region done")
     gather_note = "outputs all-gathered over NCCL"
-    if peer_gather is not None:
+    if peer_gather is not None and world > 1:
         # the gathered rows of the last step against an NCCL all-gather of the same outputs
         dist.all_gather_into_tensor(gathered, out)
         torch.cuda.synchronize()

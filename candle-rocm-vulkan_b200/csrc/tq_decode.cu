@@ -183,6 +183,39 @@ static int dispatch_v(const DecodePlan &pl, dim3 grid, cudaStream_t stream) {
     }
 }
 
+// Launched behind the combine grid when the outputs are gathered: one warp publishes this rank's step in
+// every rank's flags and waits, with a bound, until all ranks have published it. The rows stored by the
+// combine grid (a completed grid) are visible system-wide before anything this kernel writes.
+__global__ void __launch_bounds__(32) tq_gather_publish_kernel(uint32_t *const *peer_flags, uint32_t world, uint32_t rank, uint32_t *step,
+                                                                int32_t *status) {
+    const int lane = threadIdx.x;
+    // launched with programmatic stream serialization: the combine grid has completed, and its stores are visible,
+    // once this returns
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t g_step = *reinterpret_cast<volatile uint32_t *>(step) + 1u;
+    bool ok = true;
+    for (uint32_t pr = lane; pr < world; pr += 32) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flags[pr] + rank), "r"(g_step) : "memory");
+    }
+    for (uint32_t pr = lane; pr < world; pr += 32) {
+        const uint32_t *flag = peer_flags[rank] + pr;
+        uint32_t seen = 0;
+        // steps only grow; a rank that is one step ahead has already passed this one
+        for (uint32_t spin = 0; spin < (1u << 21); ++spin) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+            if ((int32_t)(seen - g_step) >= 0) break;
+            __nanosleep(32);
+        }
+        if ((int32_t)(seen - g_step) < 0) ok = false;
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (lane == 0) {
+        if (!ok && status) atomicExch(status, 2);
+        *reinterpret_cast<volatile uint32_t *>(step) = g_step;
+    }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -249,6 +282,13 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
         else if (a->d == 128) e = cudaLaunchKernelEx(&cfg, tq_combine_kernel<128>, p);
         else e = cudaLaunchKernelEx(&cfg, tq_combine_kernel<256>, p);
         if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "tq_combine: %s", cudaGetErrorString(e));
+        if (p.world) {
+            cfg.gridDim = dim3(1);
+            cfg.blockDim = dim3(32);
+            e = cudaLaunchKernelEx(&cfg, tq_gather_publish_kernel, p.peer_flags, p.world, p.rank, p.step, p.status);
+            if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "tq_gather_publish: %s", cudaGetErrorString(e));
+            return check_launch("tq_gather_publish");
+        }
         return check_launch("tq_combine");
     }
 }

@@ -970,6 +970,9 @@ __global__ void __launch_bounds__(128) tq_combine_kernel(const DecodeParams p) {
     // launched with programmatic stream serialization: wait here until the decode grid has finished
     // and its partial results are visible
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // a grid launched as this one's programmatic dependent (the gather's publish step) may be scheduled now; it waits
+    // for this grid's completion itself
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // gathered outputs: this step's number (the same for all blocks: only the last block of the grid
     // advances it, at its very end) selects one of the two slots of every rank's buffer
     const uint32_t g_step = p.world ? *reinterpret_cast<volatile uint32_t *>(p.step) + 1u : 0u;
@@ -1063,42 +1066,6 @@ __global__ void __launch_bounds__(128) tq_combine_kernel(const DecodeParams p) {
                 for (int k = 0; k < EPL; ++k) store_elem_rt(p.peer_bufs[pr], g_base + row * HD + lane + 32 * k, rb[lane + 32 * k], p.out_dtype);
         }
         __syncthreads();
-    }
-    if (p.world) {
-        // Every block makes its rows visible system-wide and counts itself; the last one publishes this
-        // rank's step in every rank's flags and waits until all ranks have published it.
-        __syncthreads();
-        __shared__ uint32_t s_last;
-        if (threadIdx.x == 0) {
-            __threadfence_system();
-            s_last = atomicAdd(p.done_ctr, 1u) == gridDim.x - 1 ? 1u : 0u;
-        }
-        __syncthreads();
-        if (s_last && warp == 0) {
-            bool ok = true;
-            if (lane == 0) *p.done_ctr = 0;
-            for (uint32_t pr = lane; pr < p.world; pr += 32) {
-                __threadfence_system();
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[pr] + p.rank), "r"(g_step) : "memory");
-            }
-            for (uint32_t pr = lane; pr < p.world; pr += 32) {
-                const uint32_t *flag = p.peer_flags[p.rank] + pr;
-                uint32_t seen = 0;
-                // steps only grow; a rank that is one step ahead has already passed this one
-                for (uint32_t spin = 0; spin < (1u << 21); ++spin) {
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
-                    if ((int32_t)(seen - g_step) >= 0) break;
-                    __nanosleep(64);
-                }
-                if ((int32_t)(seen - g_step) < 0) ok = false;
-            }
-            ok = __all_sync(0xffffffffu, ok);
-            if (lane == 0) {
-                if (!ok && p.status) atomicExch(p.status, 2);
-                *reinterpret_cast<volatile uint32_t *>(p.step) = g_step;
-                __threadfence();
-            }
-        }
     }
 }
 

@@ -275,7 +275,7 @@ def test_full_size_properties_config2(P, oracle):
 
 def test_gather_epilogue_on_one_rank(P, oracle):
     """b200_tq_attention_gather with a world of one: the rows land in slot (step & 1) of the gathered buffer, the step
-    and the flag advance, the block counter returns to zero, and the regular output is unchanged. (The exchange between
+    and the flag advance, and the regular output is unchanged. (The exchange between
     ranks is exercised by `bench.py --gpus N`, which checks the gathered rows against an NCCL all-gather.)"""
     import ctypes as C
     A = P._abi
