@@ -177,6 +177,42 @@ __device__ __forceinline__ void pf_softmax_row(uint32_t (&sa)[32], uint32_t (&sb
     l += (s0 + s1) + (s2 + s3);
 }
 
+// The same for the 128 scores of a tile of 128 keys (four chunks of 32 columns), in pieces: the maximum
+// over all four chunks first, then the exponentials of two chunks at a time, so that the first half of P
+// is on its way to tensor memory while the second is computed.
+__device__ __forceinline__ void pf_mask32(uint32_t (&s)[32], int base, int lo_rel, int hi_rel) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+        if (!(base + i >= lo_rel && base + i < hi_rel)) s[i] = 0xff800000u;
+}
+__device__ __forceinline__ float pf_max64(const uint32_t (&sa)[32], const uint32_t (&sb)[32]) {
+    float m0 = fmax3(u2f(sa[0]), u2f(sa[1]), u2f(sb[0])), m1 = u2f(sb[1]);
+#pragma unroll
+    for (int i = 2; i < 32; i += 2) {
+        m0 = fmax3(m0, u2f(sa[i]), u2f(sa[i + 1]));
+        m1 = fmax3(m1, u2f(sb[i]), u2f(sb[i + 1]));
+    }
+    return fmaxf(m0, m1);
+}
+template <bool BF16>
+__device__ __forceinline__ void pf_exp64(const uint32_t (&sa)[32], const uint32_t (&sb)[32], uint64_t sc2, uint64_t nm2, uint64_t &acc_a,
+                                         uint64_t &acc_b, uint32_t (&pr)[32]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float a0, a1, b0, b1;
+        upk2(ffma2(pk2(u2f(sa[2 * i]), u2f(sa[2 * i + 1])), sc2, nm2), a0, a1);
+        upk2(ffma2(pk2(u2f(sb[2 * i]), u2f(sb[2 * i + 1])), sc2, nm2), b0, b1);
+        a0 = fast_exp2(a0);
+        a1 = fast_exp2(a1);
+        b0 = fast_exp2(b0);
+        b1 = fast_exp2(b1);
+        acc_a = fadd2(acc_a, pk2(a0, a1));
+        acc_b = fadd2(acc_b, pk2(b0, b1));
+        pr[i] = pf_pack2<BF16>(a0, a1);
+        pr[16 + i] = pf_pack2<BF16>(b0, b1);
+    }
+}
+
 // bounded wait that also ends when another role gave up; false = give up
 __device__ __forceinline__ bool pf_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     for (uint32_t i = 0; i < (1u << 20); ++i) {
@@ -461,24 +497,29 @@ __global__ void __launch_bounds__(PF_THREADS, 2) fa_prefill_sm100_kernel(const F
 // ---------------------------------------------------------------------------------------------
 // Two row tiles per block: 256 packed rows share every K / V tile, and the two softmax groups take
 // turns with the tensor core (while group A runs its softmax the products of group B execute).
-//   warps 0-3 softmax of rows 0-127 (A), warps 4-7 of rows 128-255 (B), warp 8 loader (three stages),
-//   warp 9 issues the products and owns the tensor memory: 512 columns = S_A 64, S_B 64, P_A 32, P_B 32,
-//   O_A 128, O_B 128. One block per SM.
+//   warps 0-3 softmax of rows 0-127 (A), warps 4-7 of rows 128-255 (B), warp 8 loader (two stages of
+//   128 keys), warp 9 issues the products and owns the tensor memory: 512 columns = S_A 128, S_B 128 (P_g
+//   overwrites the first 64 columns of S_g once the scores are in registers), O_A 128, O_B 128.
+//   Tiles of 128 keys: a tcgen05.mma costs the issuing thread about 90 cycles whatever its shape
+//   (measured), so S = Q K^T runs as 8 products of N = 128 instead of 16 of N = 64. One block per SM.
 // ---------------------------------------------------------------------------------------------
-constexpr int P2_THREADS = 320, P2_ROWS = 256, P2_STAGES = 3;
+constexpr int P2_THREADS = 320, P2_ROWS = 256, P2_STAGES = 2, P2_BN = 128;
+constexpr uint32_t P2_KT_BYTES = 32768, P2_VT_BYTES = 32768;  // 128 keys x 128 dims x 2 bytes
 constexpr uint32_t P2_TMEM_COLS = 512;
-constexpr uint32_t P2_SM_Q = 0, P2_SM_K = 2 * PF_Q_BYTES, P2_SM_V = P2_SM_K + P2_STAGES * PF_KT_BYTES;
-constexpr uint32_t P2_SM_BAR = P2_SM_V + P2_STAGES * PF_VT_BYTES, P2_SMEM = P2_SM_BAR + 256;
-__host__ __device__ constexpr uint32_t p2_s_col(int g) { return 64u * g; }
-__host__ __device__ constexpr uint32_t p2_p_col(int g) { return 128u + 32u * g; }
-__host__ __device__ constexpr uint32_t p2_o_col(int g) { return 192u + 128u * g; }
+constexpr uint32_t P2_SM_Q = 0, P2_SM_K = 2 * PF_Q_BYTES, P2_SM_V = P2_SM_K + P2_STAGES * P2_KT_BYTES;
+constexpr uint32_t P2_SM_BAR = P2_SM_V + P2_STAGES * P2_VT_BYTES, P2_SMEM = P2_SM_BAR + 256;
+__host__ __device__ constexpr uint32_t p2_s_col(int g) { return 128u * g; }
+__host__ __device__ constexpr uint32_t p2_p_col(int g) { return 128u * g; }  // over S_g
+__host__ __device__ constexpr uint32_t p2_o_col(int g) { return 256u + 128u * g; }
+// barriers
+constexpr int B_KF = 0, B_VF = P2_STAGES, B_KE = 2 * P2_STAGES, B_VE = 3 * P2_STAGES, B_S = 4 * P2_STAGES, B_P = B_S + 2, B_O = B_P + 2, B_DRAIN = B_O + 1;
 
 template <bool BF16>
 __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const FaParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + P2_SM_BAR);
-    // barriers: 0-2 kv_full; 3-5 kv_empty; 6,7 s_full; 8,9 p_full; 10 o_full; 11 drain
+    // barriers: k_full, v_full, k_empty, v_empty per stage, s_full and p_full per group, o_full, drain (B_* above)
     const uint32_t bar0 = sbase + P2_SM_BAR;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + P2_SM_BAR + 128);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + P2_SM_BAR + 136);
@@ -512,15 +553,21 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
     range_of(row0, t_lo, tmp);
     range_of(min(row0 + P2_ROWS, R) - 1, tmp, t_hi);
     if (t_hi < t_lo) t_hi = t_lo;
-    const int ntiles = (int)((t_hi - t_lo + PF_BN - 1) / PF_BN);
+    const int ntiles = (int)((t_hi - t_lo + P2_BN - 1) / P2_BN);
 
     if (tid == 0) {
-        for (int i = 0; i < 3; ++i) mbar_init(&bars[i], 32);
-        for (int i = 3; i < 8; ++i) mbar_init(&bars[i], 1);
-        mbar_init(&bars[8], 128);
-        mbar_init(&bars[9], 128);
-        mbar_init(&bars[10], 1);
-        mbar_init(&bars[11], 1);
+        for (int i = 0; i < P2_STAGES; ++i) {
+            mbar_init(&bars[B_KF + i], 32);
+            mbar_init(&bars[B_VF + i], 32);
+            mbar_init(&bars[B_KE + i], 1);
+            mbar_init(&bars[B_VE + i], 1);
+        }
+        mbar_init(&bars[B_S], 1);
+        mbar_init(&bars[B_S + 1], 1);
+        mbar_init(&bars[B_P], 128);
+        mbar_init(&bars[B_P + 1], 128);
+        mbar_init(&bars[B_O], 1);
+        mbar_init(&bars[B_DRAIN], 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -555,114 +602,134 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
         const uint64_t v_lane = (uint64_t)(lane >> 1) * p.v_ss * 2 + (uint64_t)(lane & 1) * 16;
         const uint32_t k_dst_lane = (uint32_t)(lane >> 3) * 128 + (uint32_t)(lane & 7) * 16;
         const uint32_t v_key = (uint32_t)(lane >> 1);
-        const uint32_t v_dst_lane = (uint32_t)(lane & 1) * 1024 + (v_key >> 3) * 128 + (v_key & 7) * 16;
-        auto load_tile = [&](int t) {
-            const long long j0 = t_lo + (long long)t * PF_BN;
-            const int st = t % P2_STAGES;
-            const uint32_t dk = sbase + P2_SM_K + st * PF_KT_BYTES + k_dst_lane, dv = sbase + P2_SM_V + st * PF_VT_BYTES + v_dst_lane;
-            const char *ks = kb + (uint64_t)j0 * p.k_ss * 2 + k_lane, *vs = vb + (uint64_t)j0 * p.v_ss * 2 + v_lane;
-            if (j0 + PF_BN <= t_hi) {
-                // whole tile: K step = row group g (8 keys) x chunks 4 q .. 4 q + 3; V step = keys 16 q .. 16 q + 15 x chunks 2 c, 2 c + 1
-#pragma unroll
-                for (int g8 = 0; g8 < 8; ++g8) {
+        const uint32_t v_dst_lane = (uint32_t)(lane & 1) * 2048 + (v_key >> 3) * 128 + (v_key & 7) * 16;
+        auto load_k = [&](int t) {
+            const long long j0 = t_lo + (long long)t * P2_BN;
+            const uint32_t dk = sbase + P2_SM_K + (t % P2_STAGES) * P2_KT_BYTES + k_dst_lane;
+            const char *ks = kb + (uint64_t)j0 * p.k_ss * 2 + k_lane;
+            if (j0 + P2_BN <= t_hi) {
+                // whole tile: step = row group g (8 keys) x chunks 4 q .. 4 q + 3
+#pragma unroll 4
+                for (int g8 = 0; g8 < 16; ++g8) {
                     const char *src = ks + g8 * k_row8;
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) pf_cp16(dk + g8 * 2048 + q4 * 512, src + q4 * 64, true);
                 }
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const char *src = vs + q4 * v_row16;
-#pragma unroll
-                    for (int c8 = 0; c8 < 8; ++c8) pf_cp16(dv + c8 * 2048 + q4 * 256, src + c8 * 32, true);
-                }
             } else {
                 // ragged last tile: rows past the end are zero filled
 #pragma unroll 4
-                for (int blk = 0; blk < 32; ++blk) {
+                for (int blk = 0; blk < 64; ++blk) {
                     const int g8 = blk >> 2, q4 = blk & 3;
                     const bool ok = j0 + g8 * 8 + (lane & 7) < t_hi;
                     pf_cp16(dk + g8 * 2048 + q4 * 512, ok ? ks + g8 * k_row8 + q4 * 64 : kb, ok);
                 }
+            }
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar0 + 8 * (B_KF + t % P2_STAGES)) : "memory");
+        };
+        auto load_v = [&](int t) {
+            const long long j0 = t_lo + (long long)t * P2_BN;
+            const uint32_t dv = sbase + P2_SM_V + (t % P2_STAGES) * P2_VT_BYTES + v_dst_lane;
+            const char *vs = vb + (uint64_t)j0 * p.v_ss * 2 + v_lane;
+            if (j0 + P2_BN <= t_hi) {
+                // whole tile: step = keys 16 q .. 16 q + 15 x chunks 2 c, 2 c + 1
+#pragma unroll 2
+                for (int q8 = 0; q8 < 8; ++q8) {
+                    const char *src = vs + q8 * v_row16;
+#pragma unroll
+                    for (int c8 = 0; c8 < 8; ++c8) pf_cp16(dv + c8 * 4096 + q8 * 256, src + c8 * 32, true);
+                }
+            } else {
 #pragma unroll 4
-                for (int blk = 0; blk < 32; ++blk) {
-                    const int q4 = blk >> 3, c8 = blk & 7;
-                    const bool ok = j0 + q4 * 16 + (lane >> 1) < t_hi;
-                    pf_cp16(dv + c8 * 2048 + q4 * 256, ok ? vs + q4 * v_row16 + c8 * 32 : vb, ok);
+                for (int blk = 0; blk < 64; ++blk) {
+                    const int q8 = blk >> 3, c8 = blk & 7;
+                    const bool ok = j0 + q8 * 16 + (lane >> 1) < t_hi;
+                    pf_cp16(dv + c8 * 4096 + q8 * 256, ok ? vs + q8 * v_row16 + c8 * 32 : vb, ok);
                 }
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar0 + 8 * (B_VF + t % P2_STAGES)) : "memory");
         };
-        // Three tiles in flight. Nothing here waits for a copy: every lane leaves an asynchronous arrival on
-        // the tile's barrier that fires when its own copies have landed, so a tile is announced the moment
-        // it is complete, however busy this warp is with the next one. The only wait is for the stage a
-        // tile goes into (read last by the products of tile t - 3).
+        // K and V tiles of 128 keys, two stages each, released separately: the K stage of tile t is free as soon as
+        // both S = Q K^T of that tile are done (early in the tile's life), the V stage after both O += P V. Nothing
+        // here waits for a copy: every lane leaves an asynchronous arrival on the tile's barrier that fires when its
+        // copies have landed.
         bool ok = true;
         for (int t = 0; t < ntiles && ok; ++t) {
             if (t >= P2_STAGES) {
-                ok = pf_wait(bar0 + 8 * (3 + t % P2_STAGES), ((t / P2_STAGES) - 1) & 1, abort_flag);
+                ok = pf_wait(bar0 + 8 * (B_KE + t % P2_STAGES), ((t / P2_STAGES) - 1) & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
             }
-            load_tile(t);
-            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar0 + 8 * (t % P2_STAGES)) : "memory");
+            load_k(t);
+            if (t >= P2_STAGES) {
+                ok = pf_wait(bar0 + 8 * (B_VE + t % P2_STAGES), ((t / P2_STAGES) - 1) & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
+            load_v(t);
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         if (!ok) *abort_flag = 1;
     } else if (warp == 9) {
         // ================================================================ matrix products (one lane issues)
         if (lane == 0) {
-            constexpr uint32_t IQK = tc_idesc(BF16, false, PF_BM, PF_BN), IPV = tc_idesc(BF16, true, PF_BM, PF_D);
+            constexpr uint32_t IQK = tc_idesc(BF16, false, PF_BM, P2_BN), IPV = tc_idesc(BF16, true, PF_BM, PF_D);
             bool ok = true;
             auto issue_qk = [&](int g, int t) {  // S_g = Q_g K(t)^T
-                const uint32_t ks_ = sbase + P2_SM_K + (t % P2_STAGES) * PF_KT_BYTES, qs_ = sbase + P2_SM_Q + g * PF_Q_BYTES;
+                const uint32_t ks_ = sbase + P2_SM_K + (t % P2_STAGES) * P2_KT_BYTES, qs_ = sbase + P2_SM_Q + g * PF_Q_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < PF_D / 16; ++ks)
                     tc_mma_ss(tmem + p2_s_col(g), tc_desc(qs_ + ks * 256, 128, 2048), tc_desc(ks_ + ks * 256, 128, 2048), IQK, ks > 0 ? 1u : 0u);
-                tc_commit(bar0 + 8 * (6 + g));
+                tc_commit(bar0 + 8 * (B_S + g));
             };
             auto issue_pv = [&](int g, int t) {  // O_g += P_g(t) V(t)
-                const uint32_t vs = sbase + P2_SM_V + (t % P2_STAGES) * PF_VT_BYTES;
+                const uint32_t vs = sbase + P2_SM_V + (t % P2_STAGES) * P2_VT_BYTES;
 #pragma unroll
-                for (int ks = 0; ks < PF_BN / 16; ++ks)
-                    tc_mma_ts(tmem + p2_o_col(g), tmem + p2_p_col(g) + ks * 8, tc_desc(vs + ks * 256, 128, 1024), IPV, (t > 0 || ks > 0) ? 1u : 0u);
+                for (int ks = 0; ks < P2_BN / 16; ++ks)
+                    tc_mma_ts(tmem + p2_o_col(g), tmem + p2_p_col(g) + ks * 8, tc_desc(vs + ks * 256, 128, 2048), IPV, (t > 0 || ks > 0) ? 1u : 0u);
             };
             if (ntiles > 0) {
-                ok = pf_wait(bar0, 0, abort_flag);
+                ok = pf_wait(bar0 + 8 * B_KF, 0, abort_flag);
                 if (ok) {
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copies wrote through the generic proxy
                     tc_fence_after();
                     issue_qk(0, 0);
                     issue_qk(1, 0);
+                    tc_commit(bar0 + 8 * B_KE);
                 }
             }
             for (int t = 0; t < ntiles && ok; ++t) {
-                ok = pf_wait(bar0 + 8 * 8, t & 1, abort_flag);  // P_A(t) is in tensor memory, S_A is free
+                ok = pf_wait(bar0 + 8 * B_P, t & 1, abort_flag) &&  // P_A(t) is in tensor memory, S_A is free
+                     pf_wait(bar0 + 8 * (B_VF + t % P2_STAGES), (t / P2_STAGES) & 1, abort_flag);
                 if (!ok) break;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 tc_fence_after();
                 issue_pv(0, t);
                 if (t + 1 < ntiles) {
-                    ok = pf_wait(bar0 + 8 * ((t + 1) % P2_STAGES), ((t + 1) / P2_STAGES) & 1, abort_flag);
+                    ok = pf_wait(bar0 + 8 * (B_KF + (t + 1) % P2_STAGES), ((t + 1) / P2_STAGES) & 1, abort_flag);
                     if (!ok) break;
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     tc_fence_after();
                     issue_qk(0, t + 1);
                 }
-                ok = pf_wait(bar0 + 8 * 9, t & 1, abort_flag);
+                ok = pf_wait(bar0 + 8 * (B_P + 1), t & 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
                 issue_pv(1, t);
-                tc_commit(bar0 + 8 * (3 + t % P2_STAGES));  // the stage is free once both have read it
-                if (t + 1 < ntiles) issue_qk(1, t + 1);
+                tc_commit(bar0 + 8 * (B_VE + t % P2_STAGES));  // the V stage is free once both have read it
+                if (t + 1 < ntiles) {
+                    issue_qk(1, t + 1);
+                    tc_commit(bar0 + 8 * (B_KE + (t + 1) % P2_STAGES));  // and the K stage of the next tile
+                }
             }
-            if (ok && ntiles > 0) tc_commit(bar0 + 8 * 10);
+            if (ok && ntiles > 0) tc_commit(bar0 + 8 * B_O);
             if (!ok) {
                 *abort_flag = 1;
-                tc_commit(bar0 + 8 * 11);
+                tc_commit(bar0 + 8 * B_DRAIN);
                 for (uint32_t i = 0; i < (1u << 20); ++i) {
                     uint32_t done;
                     asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
                                  : "=r"(done)
-                                 : "r"(bar0 + 8 * 11), "r"(0u)
+                                 : "r"(bar0 + 8 * B_DRAIN), "r"(0u)
                                  : "memory");
                     if (done) break;
                 }
@@ -690,22 +757,35 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
         float mref = -INFINITY, l = 0.0f;
         bool ok = true;
         for (int t = 0; t < ntiles; ++t) {
-            ok = pf_wait(bar0 + 8 * (6 + g), t & 1, abort_flag);
+            ok = pf_wait(bar0 + 8 * (B_S + g), t & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            uint32_t sa[32], sb[32];
-            tc_ld32(lane_base + s_col, sa);
-            tc_ld32(lane_base + s_col + 32, sb);
+            uint32_t s0[32], s1[32], s2[32], s3[32];
+            tc_ld32(lane_base + s_col, s0);
+            tc_ld32(lane_base + s_col + 32, s1);
+            tc_ld32(lane_base + s_col + 64, s2);
+            tc_ld32(lane_base + s_col + 96, s3);
             tc_wait_ld();
-            const long long j0 = t_lo + (long long)t * PF_BN;
-            const bool full = j0 >= lomax && j0 + PF_BN <= himin && j0 + PF_BN <= t_hi;
-            const int lo_rel = r_ok ? (int)max(min(r_lo - j0, (long long)PF_BN), 0ll) : PF_BN;
-            const int hi_rel = r_ok ? (int)max(min(min(r_hi, t_hi) - j0, (long long)PF_BN), 0ll) : 0;
-            bool need;
-            float f;
-            uint32_t pr[32];
-            pf_softmax_row<BF16>(sa, sb, full, lo_rel, hi_rel, sl2, t == 0, mref, l, need, f, pr);
+            const long long j0 = t_lo + (long long)t * P2_BN;
+            const bool full = j0 >= lomax && j0 + P2_BN <= himin && j0 + P2_BN <= t_hi;
+            if (!full) {
+                const int lo_rel = r_ok ? (int)max(min(r_lo - j0, (long long)P2_BN), 0ll) : P2_BN;
+                const int hi_rel = r_ok ? (int)max(min(min(r_hi, t_hi) - j0, (long long)P2_BN), 0ll) : 0;
+                pf_mask32(s0, 0, lo_rel, hi_rel);
+                pf_mask32(s1, 32, lo_rel, hi_rel);
+                pf_mask32(s2, 64, lo_rel, hi_rel);
+                pf_mask32(s3, 96, lo_rel, hi_rel);
+            }
+            const float mx = fmaxf(pf_max64(s0, s1), pf_max64(s2, s3)) * sl2;  // sl2 > 0: the maximum commutes with the scale
+            bool need = false;
+            if (t == 0) mref = mx;
+            else need = mx > mref + PF_SLACK;
+            const float f = need ? fast_exp2(mref - mx) : 1.0f;
+            if (need) {
+                mref = mx;
+                l *= f;
+            }
             if (__any_sync(0xffffffffu, need)) {
                 // rows whose maximum moved: O goes to the new reference
 #pragma unroll 1
@@ -719,13 +799,31 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
                 }
                 tc_wait_st();
             }
-            tc_st32(lane_base + p_col, pr);
+            const float ms = mref == -INFINITY ? 0.0f : mref;
+            const uint64_t sc2 = pk2(sl2, sl2), nm2 = pk2(-ms, -ms);
+            uint64_t acc_a = pk2(0.0f, 0.0f), acc_b = acc_a;
+            {
+                uint32_t pr[32];
+                pf_exp64<BF16>(s0, s1, sc2, nm2, acc_a, acc_b, pr);
+                tc_st32(lane_base + p_col, pr);  // over the first columns of S, which are in registers
+            }
+            {
+                uint32_t pr[32];
+                pf_exp64<BF16>(s2, s3, sc2, nm2, acc_a, acc_b, pr);
+                tc_st32(lane_base + p_col + 32, pr);
+            }
+            {
+                float a0, a1, b0, b1;
+                upk2(acc_a, a0, a1);
+                upk2(acc_b, b0, b1);
+                l += (a0 + a1) + (b0 + b1);
+            }
             tc_wait_st();
             tc_fence_before();
-            mbar_arrive(&bars[8 + g]);
+            mbar_arrive(&bars[B_P + g]);
         }
         if (ok && ntiles > 0) {
-            ok = pf_wait(bar0 + 8 * 10, 0, abort_flag);
+            ok = pf_wait(bar0 + 8 * B_O, 0, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
         }
         if (!ok) *abort_flag = 1;
