@@ -220,7 +220,14 @@ __global__ void __launch_bounds__(32) tq_gather_publish_kernel(uint32_t *const *
 
 using namespace b200;
 
+namespace b200 {
+// tq_generic.cu: formats and head dims outside the tensor-core kernel
+int tq_generic_launch(const B200TqAttnArgs *a, cudaStream_t stream);
+bool tq_generic_takes(const B200TqAttnArgs *a);
+}  // namespace b200
+
 extern "C" size_t b200_tq_attention_workspace_bytes(const B200TqAttnArgs *a) {
+    if (tq_generic_takes(a)) return 16;  // the general kernel needs no scratch; 0 is reserved for "cannot be planned"
     DecodePlan pl;
     if (make_plan(a, pl)) return 0;
     return pl.ws_bytes;
@@ -230,6 +237,10 @@ extern "C" size_t b200_tq_attention_workspace_bytes(const B200TqAttnArgs *a) {
 static thread_local const B200PeerGather *tl_gather = nullptr;
 
 extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_) {
+    if (tq_generic_takes(a)) {
+        if (tl_gather) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention_gather: not available for shapes of the general kernel");
+        return tq_generic_launch(a, (cudaStream_t)stream_);
+    }
     DecodePlan pl;
     const int rc = make_plan(a, pl);
     if (rc) return rc;

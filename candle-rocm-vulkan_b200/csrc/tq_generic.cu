@@ -1,0 +1,174 @@
+// Attention over packed rows for the shapes outside the tensor-core kernel: codebook formats with 1-3 bit
+// codes and head dims that are multiples of 32 other than 64 / 128 / 256 (up to 256). Same semantics as
+// tq_decode.cuh (candle-core/kernels/turbo_quant_impl.h:232-619), plain f32 arithmetic: one block per output
+// row, its 8 warps take every 8th key, a lane holds the dims lane, lane + 32, ...; scores by warp reduction,
+// one online softmax per warp, the 8 partial results merged in shared memory. Not a fast path: it exists so
+// that every row format the quantizer can write can also be attended over.
+#include "common.cuh"
+#include "tq_decode.cuh"
+
+namespace b200 {
+
+constexpr int GW = 8;       // warps per block
+constexpr int GMAX = 8;     // dims per lane: head dim <= 256
+
+struct GenericSide {
+    int32_t mode, bits, code_words, rsc_off;
+};
+
+// element j of a packed row without its row scale (candle-core/kernels/turbo_quant_impl.h:44-53)
+__device__ __forceinline__ float tq_elem(const uint32_t *r, uint32_t j, const GenericSide &s, const float *tab) {
+    const uint32_t pos = j * s.bits, wi = pos >> 5, sh = pos & 31u;
+    uint32_t c = r[wi] >> sh;
+    if (sh + s.bits > 32u) c |= r[wi + 1] << (32u - sh);
+    c &= (1u << s.bits) - 1u;
+    const uint32_t *aux = r + s.code_words;
+    if (s.mode == B200_TURBO_MSE) return tab[c];
+    if (s.mode == B200_MXFP4) return __fmul_rn(fp4_to_f(c), e8m0_to_f((aux[j >> 7] >> (((j >> 5) & 3u) * 8u)) & 0xffu));
+    if (s.mode == B200_NVFP4) return __fmul_rn(fp4_to_f(c), e4m3_to_f((aux[j >> 6] >> (((j >> 4) & 3u) * 8u)) & 0xffu));
+    if (s.mode == B200_MXFP8) return __fmul_rn(e4m3_to_f(c), e8m0_to_f((aux[j >> 7] >> (((j >> 5) & 3u) * 8u)) & 0xffu));
+    return e4m3_to_f(c);
+}
+
+__global__ void __launch_bounds__(GW * 32) tq_generic_kernel(const DecodeParams p, const GenericSide ks, const GenericSide vs) {
+    __shared__ float qrow[GMAX * 32];
+    __shared__ float part[GW][GMAX * 32 + 2];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t D = p.d, nk = D / 32;
+    const size_t row = blockIdx.x;
+    const uint32_t i = (uint32_t)(row % p.lq), h = (uint32_t)((row / p.lq) % p.hq), b = (uint32_t)(row / ((size_t)p.lq * p.hq));
+    const uint32_t hk = h / p.group;
+    const int lk = p.kv_len ? max(p.kv_len[b], 0) : (int)p.lk;
+    // the row's visible keys (bottom right aligned)
+    const long long pos = (long long)i + lk - (long long)p.lq;
+    long long lo = p.wl >= 0 ? max(pos - p.wl, 0ll) : 0ll, hi = p.wr >= 0 ? min(pos + p.wr + 1, (long long)lk) : (long long)lk;
+    lo = min(lo, (long long)lk);
+    hi = max(hi, lo);
+    // query row, rotated like the keys
+    if (warp == 0) {
+        for (uint32_t k = 0; k < nk; ++k)
+            qrow[lane + 32 * k] = load_elem_rt(p.q, b * p.q_sb + h * p.q_sh + i * p.q_ss + lane + 32 * k, p.q_dtype);
+        __syncwarp();
+        if (p.k.rot == B200_ROT_HADAMARD) warp_hadamard(qrow, (int)D, p.k.signs, true, lane);
+    }
+    __syncthreads();
+    float q[GMAX];
+#pragma unroll
+    for (int k = 0; k < GMAX; ++k) q[k] = (uint32_t)k < nk ? qrow[lane + 32 * k] * p.scale : 0.0f;
+    const float slope = p.alibi ? p.alibi[(size_t)b * p.alibi_bs + h] : 0.0f;
+    const uint32_t *kbase = p.k_rows + (size_t)b * p.k_sb + (size_t)hk * p.k_sh;
+    const uint32_t *vbase = p.v_rows + (size_t)b * p.v_sb + (size_t)hk * p.v_sh;
+    float m = -INFINITY, l = 0.0f, acc[GMAX];
+#pragma unroll
+    for (int k = 0; k < GMAX; ++k) acc[k] = 0.0f;
+    for (long long j = lo + warp; j < hi; j += GW) {
+        const uint32_t *kr = kbase + (size_t)j * p.k_ss, *vr = vbase + (size_t)j * p.v_ss;
+        float s = 0.0f;
+#pragma unroll
+        for (int k = 0; k < GMAX; ++k)
+            if ((uint32_t)k < nk) s = fmaf(tq_elem(kr, lane + 32 * k, ks, p.k.tab), q[k], s);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        s *= u2f(kr[ks.rsc_off]);
+        if (p.softcap > 0.0f) s = p.softcap * tanhf(s / p.softcap);
+        if (slope != 0.0f) s -= slope * fabsf((float)(pos - j));
+        const float mn = fmaxf(m, s);
+        const float al = m == -INFINITY ? 0.0f : expf(m - mn), pj = expf(s - mn);
+        m = mn;
+        l = l * al + pj;
+        const float pv = pj * u2f(vr[vs.rsc_off]);
+#pragma unroll
+        for (int k = 0; k < GMAX; ++k)
+            if ((uint32_t)k < nk) acc[k] = fmaf(pv, tq_elem(vr, lane + 32 * k, vs, p.v.tab), acc[k] * al);
+    }
+    // merge the warps
+#pragma unroll
+    for (int k = 0; k < GMAX; ++k)
+        if ((uint32_t)k < nk) part[warp][lane + 32 * k] = acc[k];
+    if (lane == 0) {
+        part[warp][GMAX * 32] = m;
+        part[warp][GMAX * 32 + 1] = l;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        float mx = -INFINITY;
+        for (int w = 0; w < GW; ++w) mx = fmaxf(mx, part[w][GMAX * 32]);
+        float lt = 0.0f, o[GMAX];
+#pragma unroll
+        for (int k = 0; k < GMAX; ++k) o[k] = 0.0f;
+        for (int w = 0; w < GW; ++w) {
+            const float mw = part[w][GMAX * 32];
+            const float f = mw == -INFINITY ? 0.0f : expf(mw - mx);
+            lt += f * part[w][GMAX * 32 + 1];
+#pragma unroll
+            for (int k = 0; k < GMAX; ++k)
+                if ((uint32_t)k < nk) o[k] = fmaf(f, part[w][lane + 32 * k], o[k]);
+        }
+        const float inv = lt > 0.0f ? 1.0f / lt : 0.0f;
+        for (uint32_t k = 0; k < nk; ++k) qrow[lane + 32 * k] = o[k] * inv;
+        __syncwarp();
+        if (p.v.rot == B200_ROT_HADAMARD) {
+            warp_hadamard(qrow, (int)D, p.v.signs, false, lane);
+            __syncwarp();
+        }
+        const size_t obase = b * p.o_sb + h * p.o_sh + i * p.o_ss;
+        for (uint32_t k = 0; k < nk; ++k) store_elem_rt(p.out, obase + lane + 32 * k, qrow[lane + 32 * k], p.out_dtype);
+    }
+}
+
+// 0 when the call is one this kernel takes (and the tensor-core kernel does not)
+int tq_generic_plan(const B200TqAttnArgs *a, DecodeParams &p, GenericSide &ks, GenericSide &vs) {
+    if (!a || a->hkv == 0 || a->hq % a->hkv != 0 || a->pages) return 1;
+    if (a->d == 0 || a->d % 32 != 0 || a->d > GMAX * 32) return 1;
+    const B200QuantSide *sides[2] = {&a->kq, &a->vq};
+    GenericSide *gs[2] = {&ks, &vs};
+    bool needed = a->d != 64 && a->d != 128 && a->d != 256;
+    for (int s = 0; s < 2; ++s) {
+        const B200QuantSide &q = *sides[s];
+        if (q.mode == B200_TURBO_PROD) return 1;
+        B200RowLayout lay;
+        if (b200_row_layout(q.mode, q.bits, (int)a->d, &lay)) return 1;
+        if (q.mode == B200_TURBO_MSE && !q.tab) return 1;
+        if (q.rotation == B200_ROT_HADAMARD ? (!q.signs || (a->d & (a->d - 1))) : q.rotation != B200_ROT_NONE) return 1;
+        if (q.mode == B200_TURBO_MSE && q.bits != 4) needed = true;
+        gs[s]->mode = q.mode;
+        gs[s]->bits = lay.code_bits;
+        gs[s]->code_words = lay.code_words;
+        gs[s]->rsc_off = lay.rsc_offset;
+    }
+    if (!needed) return 1;
+    memset(&p, 0, sizeof(p));
+    p.q = a->q; p.out = a->out; p.q_dtype = a->q_dtype; p.out_dtype = a->out_dtype;
+    p.q_sb = a->q_strides[0]; p.q_sh = a->q_strides[1]; p.q_ss = a->q_strides[2];
+    p.o_sb = a->out_strides[0]; p.o_sh = a->out_strides[1]; p.o_ss = a->out_strides[2];
+    p.k_rows = a->k_rows; p.v_rows = a->v_rows;
+    p.k_sb = a->k_strides[0]; p.k_sh = a->k_strides[1]; p.k_ss = a->k_strides[2];
+    p.v_sb = a->v_strides[0]; p.v_sh = a->v_strides[1]; p.v_ss = a->v_strides[2];
+    p.kv_len = a->kv_len_dev;
+    p.b = a->b; p.lq = a->lq; p.lk = a->lk; p.hq = a->hq; p.hkv = a->hkv; p.d = a->d; p.group = a->hq / a->hkv;
+    p.k.rot = a->kq.rotation; p.k.tab = a->kq.tab; p.k.signs = a->kq.signs;
+    p.v.rot = a->vq.rotation; p.v.tab = a->vq.tab; p.v.signs = a->vq.signs;
+    p.scale = a->scale; p.softcap = a->softcap; p.wl = a->wl; p.wr = a->wr;
+    p.alibi = a->alibi; p.alibi_bs = a->alibi_bstride;
+    return 0;
+}
+
+int tq_generic_launch(const B200TqAttnArgs *a, cudaStream_t stream) {
+    DecodeParams p;
+    GenericSide ks, vs;
+    if (tq_generic_plan(a, p, ks, vs)) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: shape outside both kernels");
+    const uint64_t rows = (uint64_t)a->b * a->hq * a->lq;
+    if (rows == 0) return B200_OK;
+    if (!a->q || !a->out || !a->k_rows || !a->v_rows) return set_error(B200_ERR_BAD_ARG, "tq_attention: null pointer");
+    if (rows > 0x7fffffffull) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: too many output rows");
+    tq_generic_kernel<<<(unsigned)rows, GW * 32, 0, stream>>>(p, ks, vs);
+    return check_launch("tq_attention (general kernel)");
+}
+
+bool tq_generic_takes(const B200TqAttnArgs *a) {
+    DecodeParams p;
+    GenericSide ks, vs;
+    return tq_generic_plan(a, p, ks, vs) == 0;
+}
+
+}  // namespace b200

@@ -40,7 +40,7 @@ def run_packed(P, q, kd, vd, kv_len, kf, vf, scale, qdt="f32", rotation="none", 
     return out.float().cpu().numpy()
 
 
-SUPPORTED = [c for c in MG.ATTN_CASES if not (c[1][0] == 0 and c[1][1] != 4) and not (c[2][0] == 0 and c[2][1] != 4)]
+SUPPORTED = list(MG.ATTN_CASES)  # codebook rows with 1-3 bit codes run on the general kernel
 
 
 @pytest.mark.parametrize("case", SUPPORTED, ids=lambda c: c[0])
@@ -54,12 +54,53 @@ def test_against_reference_kernel_outputs(P, golden, case):
 
 def test_unsupported_formats_are_reported(P):
     A = P._abi
-    d = 128
+    d = 512  # above both kernels
     kq = P.TurboQuantizer(fmt(P, 0, 3), d, "none", 1)
     rows = torch.zeros((1, 1, 8, kq.row_words()), dtype=torch.int32, device="cuda:0")
     with pytest.raises(A.B200Error) as e:
         P.attention_packed(torch.zeros((1, 2, 1, d), device="cuda:0"), rows, rows, 8, kq, kq, P.FlashAttnConfig(1.0))
     assert e.value.code == A.ERR_UNSUPPORTED_SHAPE
+
+
+GENERAL_CASES = [
+    # name, key format, value format, b, lq, lk, hq, hkv, d, wl, wr, softcap, rotation
+    ("turbo2_turbo3_ragged", (0, 2), (0, 3), 3, 1, 300, 8, 2, 128, -1, 0, 0.0, "none"),
+    ("turbo3_hadamard_gqa", (0, 3), (0, 3), 2, 2, 150, 8, 2, 128, -1, 0, 0.0, "hadamard"),
+    ("turbo1_turbo4_d64", (0, 1), (0, 4), 1, 3, 90, 2, 1, 64, 20, 0, 0.0, "none"),
+    ("mxfp4_d96", (2, 4), (2, 4), 2, 1, 200, 4, 2, 96, -1, 0, 15.0, "none"),
+    ("fp8_nvfp4_d32", (5, 4), (3, 4), 1, 2, 77, 2, 2, 32, -1, -1, 0.0, "none"),
+]
+
+
+@pytest.mark.parametrize("case", GENERAL_CASES, ids=lambda c: c[0])
+def test_general_kernel_against_oracle(P, oracle, case):
+    """Formats and head dims outside the tensor-core kernel: 1-3 bit codebook rows, head dims 32 and 96."""
+    name, kf, vf, b, lq, lk, hq, hkv, d, wl, wr, softcap, rotation = case
+    seed = 300 + sum(ord(ch) for ch in name)
+    kx = oracle.normal(seed, b * hkv * lk * d).reshape(-1, d)
+    vx = oracle.normal(seed + 1, b * hkv * lk * d).reshape(-1, d)
+    q = oracle.normal(seed + 2, b * hq * lq * d).reshape(b, hq, lq, d)
+    kq = P.TurboQuantizer(fmt(P, *kf), d, rotation, 42)
+    vq = P.TurboQuantizer(fmt(P, *vf), d, rotation, 44)
+    kd = kq.quantize_rows(to_dev(kx)).view(b, hkv, lk, -1)
+    vd = vq.quantize_rows(to_dev(vx)).view(b, hkv, lk, -1)
+    lens = np.array([lk, max(1, lk // 3), lk - 1][:b], np.int32)
+    c = P.FlashAttnConfig(d ** -0.5)
+    c.window_size_left = None if wl < 0 else wl
+    c.window_size_right = None if wr < 0 else wr
+    c.softcap = softcap or None
+    got = P.attention_packed(to_dev(q), kd, vd, torch.from_numpy(lens).to("cuda:0"), kq, vq, c).cpu().numpy()
+    # the oracle attends in the rotated space over the same packed rows, then rotates back
+    tab = np.zeros(64, np.float32)
+    tab[:32] = MG.tab_for(kf[0], kf[1], d)
+    tab[32:] = MG.tab_for(vf[0], vf[1], d)
+    qr = q
+    if rotation == "hadamard":
+        qr = oracle.rotate_rows(q.reshape(-1, d), oracle.rotation_matrix(d, 1, 42)).reshape(q.shape)
+    want = oracle.tq_attention(qr, words(kd), words(vd), lk, kf, vf, d ** -0.5, tab, kv_len=lens, wl=wl, wr=wr, softcap=softcap)
+    if rotation == "hadamard":
+        want = oracle.rotate_rows(want.reshape(-1, d), oracle.rotation_matrix(d, 1, 44), transpose=True).reshape(want.shape)
+    assert_close(got, want, what=name)
 
 
 def make_rows(oracle, seed, b, hkv, lk, d, kf, vf, outliers=False, cap=None):
