@@ -61,7 +61,7 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
         return set_error(B200_ERR_BAD_ARG, "tq_attention: %u query heads are not a multiple of %u kv heads", a->hq, a->hkv);
     if (a->d != 64 && a->d != 128 && a->d != 256)
         return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: head dim %u (fused kernel: 64, 128, 256)", a->d);
-    if (a->pages) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: paged rows are not implemented yet");
+    if (a->pages) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: paged rows with per-sequence lengths or without blocks");
     DecodeParams &p = pl.p;
     memset(&p, 0, sizeof(p));
     int rc = fill_decode_side(p.k, a->kq, a->d, "key");

@@ -1,5 +1,7 @@
 // Attention over packed rows for the shapes outside the tensor-core kernel: codebook formats with 1-3 bit
-// codes and head dims that are multiples of 32 other than 64 / 128 / 256 (up to 256). Same semantics as
+// codes, head dims that are multiples of 32 other than 64 / 128 / 256 (up to 256), and paged rows (a table of
+// cache blocks in device memory, read in place: candle-core/src/accel/attention.rs:296-366,
+// candle-core/kernels/turbo_quant_impl.h tq_attnp*). Same semantics as
 // tq_decode.cuh (candle-core/kernels/turbo_quant_impl.h:232-619), plain f32 arithmetic: one block per output
 // row, its 8 warps take every 8th key, a lane holds the dims lane, lane + 32, ...; scores by warp reduction,
 // one online softmax per warp, the 8 partial results merged in shared memory. Not a fast path: it exists so
@@ -30,7 +32,8 @@ __device__ __forceinline__ float tq_elem(const uint32_t *r, uint32_t j, const Ge
     return e4m3_to_f(c);
 }
 
-__global__ void __launch_bounds__(GW * 32) tq_generic_kernel(const DecodeParams p, const GenericSide ks, const GenericSide vs) {
+__global__ void __launch_bounds__(GW * 32) tq_generic_kernel(const DecodeParams p, const GenericSide ks, const GenericSide vs,
+                                                             const B200Page *__restrict__ pages, const uint32_t n_pages) {
     __shared__ float qrow[GMAX * 32];
     __shared__ float part[GW][GMAX * 32 + 2];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -38,7 +41,12 @@ __global__ void __launch_bounds__(GW * 32) tq_generic_kernel(const DecodeParams 
     const size_t row = blockIdx.x;
     const uint32_t i = (uint32_t)(row % p.lq), h = (uint32_t)((row / p.lq) % p.hq), b = (uint32_t)(row / ((size_t)p.lq * p.hq));
     const uint32_t hk = h / p.group;
-    const int lk = p.kv_len ? max(p.kv_len[b], 0) : (int)p.lk;
+    int lk = p.kv_len ? max(p.kv_len[b], 0) : (int)p.lk;
+    if (pages) {  // the keys of a paged call are the valid rows of all blocks, one after the other
+        long long total = 0;
+        for (uint32_t pg = 0; pg < n_pages; ++pg) total += pages[pg].rows;
+        lk = (int)min(total, 2147483647ll);
+    }
     // the row's visible keys (bottom right aligned)
     const long long pos = (long long)i + lk - (long long)p.lq;
     long long lo = p.wl >= 0 ? max(pos - p.wl, 0ll) : 0ll, hi = p.wr >= 0 ? min(pos + p.wr + 1, (long long)lk) : (long long)lk;
@@ -56,13 +64,31 @@ __global__ void __launch_bounds__(GW * 32) tq_generic_kernel(const DecodeParams 
 #pragma unroll
     for (int k = 0; k < GMAX; ++k) q[k] = (uint32_t)k < nk ? qrow[lane + 32 * k] * p.scale : 0.0f;
     const float slope = p.alibi ? p.alibi[(size_t)b * p.alibi_bs + h] : 0.0f;
-    const uint32_t *kbase = p.k_rows + (size_t)b * p.k_sb + (size_t)hk * p.k_sh;
-    const uint32_t *vbase = p.v_rows + (size_t)b * p.v_sb + (size_t)hk * p.v_sh;
     float m = -INFINITY, l = 0.0f, acc[GMAX];
 #pragma unroll
     for (int k = 0; k < GMAX; ++k) acc[k] = 0.0f;
-    for (long long j = lo + warp; j < hi; j += GW) {
-        const uint32_t *kr = kbase + (size_t)j * p.k_ss, *vr = vbase + (size_t)j * p.v_ss;
+    // blocks of keys: the whole dense cache, or one cache block after the other
+    const uint32_t n_blk = pages ? n_pages : 1u;
+    long long blk0 = 0;  // key index of the block's first row
+    for (uint32_t pg = 0; pg < n_blk; ++pg) {
+    const uint32_t *kbase, *vbase;
+    long long blk_rows;
+    if (pages) {
+        const B200Page pgd = pages[pg];
+        blk_rows = pgd.rows;
+        // block layout (batch, kv head, capacity, words): head stride = capacity rows, batch stride = hkv heads
+        kbase = reinterpret_cast<const uint32_t *>(pgd.k) + ((size_t)b * p.hkv + hk) * pgd.k_cap * p.k_ss;
+        vbase = reinterpret_cast<const uint32_t *>(pgd.v) + ((size_t)b * p.hkv + hk) * pgd.v_cap * p.v_ss;
+    } else {
+        blk_rows = lk;
+        kbase = p.k_rows + (size_t)b * p.k_sb + (size_t)hk * p.k_sh;
+        vbase = p.v_rows + (size_t)b * p.v_sb + (size_t)hk * p.v_sh;
+    }
+    const long long j_lo = max(lo, blk0), j_hi = min(hi, blk0 + blk_rows);
+    // every warp keeps its residue class of the global key index, so results do not depend on the paging
+    long long j_first = j_lo + ((warp - j_lo) % GW + GW) % GW;
+    for (long long j = j_first; j < j_hi; j += GW) {
+        const uint32_t *kr = kbase + (size_t)(j - blk0) * p.k_ss, *vr = vbase + (size_t)(j - blk0) * p.v_ss;
         float s = 0.0f;
 #pragma unroll
         for (int k = 0; k < GMAX; ++k)
@@ -80,6 +106,8 @@ __global__ void __launch_bounds__(GW * 32) tq_generic_kernel(const DecodeParams 
 #pragma unroll
         for (int k = 0; k < GMAX; ++k)
             if ((uint32_t)k < nk) acc[k] = fmaf(pv, tq_elem(vr, lane + 32 * k, vs, p.v.tab), acc[k] * al);
+    }
+    blk0 += blk_rows;
     }
     // merge the warps
 #pragma unroll
@@ -118,11 +146,12 @@ __global__ void __launch_bounds__(GW * 32) tq_generic_kernel(const DecodeParams 
 
 // 0 when the call is one this kernel takes (and the tensor-core kernel does not)
 int tq_generic_plan(const B200TqAttnArgs *a, DecodeParams &p, GenericSide &ks, GenericSide &vs) {
-    if (!a || a->hkv == 0 || a->hq % a->hkv != 0 || a->pages) return 1;
+    if (!a || a->hkv == 0 || a->hq % a->hkv != 0) return 1;
+    if (a->pages && (a->n_pages == 0 || a->kv_len_dev)) return 1;
     if (a->d == 0 || a->d % 32 != 0 || a->d > GMAX * 32) return 1;
     const B200QuantSide *sides[2] = {&a->kq, &a->vq};
     GenericSide *gs[2] = {&ks, &vs};
-    bool needed = a->d != 64 && a->d != 128 && a->d != 256;
+    bool needed = (a->d != 64 && a->d != 128 && a->d != 256) || a->pages != nullptr;
     for (int s = 0; s < 2; ++s) {
         const B200QuantSide &q = *sides[s];
         if (q.mode == B200_TURBO_PROD) return 1;
@@ -159,9 +188,9 @@ int tq_generic_launch(const B200TqAttnArgs *a, cudaStream_t stream) {
     if (tq_generic_plan(a, p, ks, vs)) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: shape outside both kernels");
     const uint64_t rows = (uint64_t)a->b * a->hq * a->lq;
     if (rows == 0) return B200_OK;
-    if (!a->q || !a->out || !a->k_rows || !a->v_rows) return set_error(B200_ERR_BAD_ARG, "tq_attention: null pointer");
+    if (!a->q || !a->out || (!a->pages && (!a->k_rows || !a->v_rows))) return set_error(B200_ERR_BAD_ARG, "tq_attention: null pointer");
     if (rows > 0x7fffffffull) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: too many output rows");
-    tq_generic_kernel<<<(unsigned)rows, GW * 32, 0, stream>>>(p, ks, vs);
+    tq_generic_kernel<<<(unsigned)rows, GW * 32, 0, stream>>>(p, ks, vs, a->pages, a->n_pages);
     return check_launch("tq_attention (general kernel)");
 }
 

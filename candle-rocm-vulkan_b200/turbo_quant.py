@@ -12,6 +12,7 @@ import ctypes as C
 from dataclasses import dataclass, field
 from typing import Optional, Tuple
 
+import numpy as np
 import torch
 
 from . import _abi as A
@@ -363,6 +364,72 @@ def attention_packed(q: torch.Tensor, k_rows: torch.Tensor, v_rows: torch.Tensor
     number of valid rows, an int (all sequences) or an int32 device tensor with one length per
     batch entry (ragged batch). Output in `q`'s dtype and layout."""
     return PackedAttention(q, k_rows, v_rows, kv_len, kq, vq, cfg, out).run()
+
+
+@dataclass
+class KvBlockRef:
+    """One block of a paged cache: `k` / `v` are (batch, kv_heads, capacity, words) int32 tensors of packed rows of
+    which the first `rows` positions of the third axis are valid (candle-nn/src/flash_attn.rs:608-613)."""
+    k: torch.Tensor
+    v: torch.Tensor
+    rows: int
+
+
+def attention_packed_blocks(q: torch.Tensor, blocks, kq: TurboQuantizer, vq: TurboQuantizer, cfg: FlashAttnConfig) -> torch.Tensor:
+    """Attention of `q: (batch, q_heads, seq_q, head_dim)` over packed rows that live in paged cache blocks, read in
+    place through a block table in device memory (candle-nn/src/turbo_quant.rs:1074-1114; no limit of 128 blocks).
+    The keys are the valid rows of the blocks, one block after the other; masks are bottom-right aligned over them."""
+    _need_cuda(q, "q")
+    if len(blocks) == 0:
+        raise ValueError("turbo-quant blocks: no blocks")
+    b, hq, lq, d = q.shape
+    hkv = blocks[0].k.shape[1]
+    kw, vw = blocks[0].k.shape[3], blocks[0].v.shape[3]
+    if kw != kq.row_words() or vw != vq.row_words() or d != kq.dim or d != vq.dim:
+        raise ValueError(f"turbo-quant blocks: rows of {kw} / {vw} words and head dim {d} do not match the quantizers "
+                         f"({kq.row_words()} / {vq.row_words()} words, dim {kq.dim})")
+    table = np.zeros(len(blocks), dtype=np.dtype([("k", "<u8"), ("v", "<u8"), ("rows", "<u4"), ("k_cap", "<u4"), ("v_cap", "<u4"), ("pad", "<u4")]))
+    lk = 0
+    for n, blk in enumerate(blocks):
+        for t, w, what in ((blk.k, kw, "k"), (blk.v, vw, "v")):
+            # paged_block_layout (flash_attn.rs:618-646): contiguous rows, head stride = whole rows, batch stride = hkv heads
+            if t.dtype != torch.int32 or t.dim() != 4 or t.shape[0] != b or t.shape[1] != hkv or t.shape[3] != w or not t.is_contiguous():
+                raise ValueError(f"turbo-quant blocks: block {n} ({what}) must be a contiguous int32 ({b}, {hkv}, capacity, {w}) tensor")
+            if t.device != q.device:
+                raise ValueError("turbo-quant blocks: blocks live on another device")
+        if not 0 <= blk.rows <= min(blk.k.shape[2], blk.v.shape[2]):
+            raise ValueError(f"turbo-quant blocks: block {n} holds {blk.rows} rows, capacity {blk.k.shape[2]} / {blk.v.shape[2]}")
+        table[n] = (blk.k.data_ptr(), blk.v.data_ptr(), blk.rows, blk.k.shape[2], blk.v.shape[2], 0)
+        lk += blk.rows
+    if lk == 0:
+        raise ValueError("turbo-quant blocks: no valid rows")
+    pages = torch.from_numpy(table.view(np.uint8)).to(q.device)
+    if q.stride(3) != 1:
+        q = q.contiguous()
+    out = torch.empty((b, hq, lq, d), dtype=q.dtype, device=q.device)
+    wl, wr = cfg.window_i32()
+    alibi, abs_ = None, 0
+    if cfg.alibi_slopes is not None:
+        alibi = cfg.alibi_slopes.to(device=q.device, dtype=torch.float32).contiguous()
+        if alibi.shape not in ((hq,), (b, hq)):
+            raise ValueError(f"flash-attn: alibi slopes must be ({hq}) or ({b}, {hq}), got {tuple(alibi.shape)}")
+        abs_ = hq if alibi.dim() == 2 else 0
+    args = A.TqAttnArgs()
+    args.q, args.out = q.data_ptr(), out.data_ptr()
+    args.q_dtype = args.out_dtype = _dtype_id(q)
+    args.q_strides, args.out_strides = A.u64x3(*q.stride()[:3]), A.u64x3(*out.stride()[:3])
+    args.k_rows = args.v_rows = None
+    args.k_strides, args.v_strides = A.u64x3(0, 0, kw), A.u64x3(0, 0, vw)  # only the row stride is common to the blocks
+    args.pages, args.n_pages = pages.data_ptr(), len(blocks)
+    args.kv_len_dev = None
+    args.b, args.lq, args.lk, args.hq, args.hkv, args.d = b, lq, lk, hq, hkv, d
+    args.kq, args.vq = kq.side(), vq.side()
+    args.scale, args.softcap = cfg.softmax_scale, cfg.softcap or 0.0
+    args.wl, args.wr = wl, wr
+    args.alibi, args.alibi_bstride = (alibi.data_ptr() if alibi is not None else None), abs_
+    args.workspace, args.workspace_bytes, args.status = None, 0, None
+    A.check(A.lib().b200_tq_attention(C.byref(args), _stream(q.device)))
+    return out
 
 
 class TurboKvCache:

@@ -349,3 +349,37 @@ def test_gather_epilogue_on_one_rank(P, oracle):
     with pytest.raises(A.B200Error, match="world"):
         g.args.world = 0
         P.PackedAttention(q, k_rows, v_rows, kv_len, kq, vq, cfg, gather=g).run()
+
+
+@pytest.mark.parametrize("kf,vf", [((2, 4), (2, 4)), ((0, 4), (0, 3)), ((5, 4), (4, 4))])
+def test_paged_blocks_equal_the_concatenated_rows(P, oracle, kf, vf):
+    """attention_packed_blocks over four cache blocks of different capacities and fill levels (one of them empty)
+    against the oracle on the concatenated valid rows (candle-nn/src/turbo_quant.rs:1536-1563 tests the same way)."""
+    b, hq, hkv, d, lq = 2, 4, 2, 128, 2
+    kq = P.TurboQuantizer(fmt(P, *kf), d, "none", 42)
+    vq = P.TurboQuantizer(fmt(P, *vf), d, "none", 44)
+    caps, fills = [16, 64, 8, 128], [16, 9, 0, 100]
+    blocks, kcat, vcat = [], [], []
+    for n, (cap, rows) in enumerate(zip(caps, fills)):
+        kx = oracle.normal(700 + n, b * hkv * cap * d).reshape(-1, d)
+        vx = oracle.normal(800 + n, b * hkv * cap * d).reshape(-1, d)
+        kb = kq.quantize_rows(to_dev(kx)).view(b, hkv, cap, -1).contiguous()
+        vb = vq.quantize_rows(to_dev(vx)).view(b, hkv, cap, -1).contiguous()
+        blocks.append(P.KvBlockRef(kb, vb, rows))
+        kcat.append(words(kb)[:, :, :rows])
+        vcat.append(words(vb)[:, :, :rows])
+    kd, vd = np.concatenate(kcat, axis=2), np.concatenate(vcat, axis=2)
+    lk = sum(fills)
+    q = oracle.normal(9, b * hq * lq * d).reshape(b, hq, lq, d)
+    tab = np.zeros(64, np.float32)
+    tab[:32] = MG.tab_for(kf[0], kf[1], d)
+    tab[32:] = MG.tab_for(vf[0], vf[1], d)
+    for wl, wr in ((-1, 0), (30, 0), (-1, -1)):
+        c = P.FlashAttnConfig(d ** -0.5)
+        c.window_size_left = None if wl < 0 else wl
+        c.window_size_right = None if wr < 0 else wr
+        got = P.attention_packed_blocks(to_dev(q), blocks, kq, vq, c).cpu().numpy()
+        want = oracle.tq_attention(q, np.ascontiguousarray(kd), np.ascontiguousarray(vd), lk, kf, vf, d ** -0.5, tab, wl=wl, wr=wr)
+        assert_close(got, want, what=f"paged wl={wl} wr={wr}")
+    with pytest.raises(ValueError, match="no blocks"):
+        P.attention_packed_blocks(to_dev(q), [], kq, vq, c)
