@@ -86,6 +86,12 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
         "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
+                 "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                 : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -193,6 +199,28 @@ __device__ __forceinline__ float pf_max64(const uint32_t (&sa)[32], const uint32
         m1 = fmax3(m1, u2f(sb[i]), u2f(sb[i + 1]));
     }
     return fmaxf(m0, m1);
+}
+__device__ __forceinline__ float pf_max32(const uint32_t (&s)[32]) {
+    float m0 = fmax3(u2f(s[0]), u2f(s[1]), u2f(s[2])), m1 = fmax3(u2f(s[3]), u2f(s[4]), u2f(s[5]));
+#pragma unroll
+    for (int i = 6; i < 30; i += 4) {
+        m0 = fmax3(m0, u2f(s[i]), u2f(s[i + 1]));
+        m1 = fmax3(m1, u2f(s[i + 2]), u2f(s[i + 3]));
+    }
+    return fmax3(m0, m1, fmaxf(u2f(s[30]), u2f(s[31])));
+}
+// 32 scores -> 16 columns of P (16-bit pairs), sums into acc
+template <bool BF16>
+__device__ __forceinline__ void pf_exp32(const uint32_t (&s)[32], uint64_t sc2, uint64_t nm2, uint64_t &acc, uint32_t (&pr)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float a0, a1;
+        upk2(ffma2(pk2(u2f(s[2 * i]), u2f(s[2 * i + 1])), sc2, nm2), a0, a1);
+        a0 = fast_exp2(a0);
+        a1 = fast_exp2(a1);
+        acc = fadd2(acc, pk2(a0, a1));
+        pr[i] = pf_pack2<BF16>(a0, a1);
+    }
 }
 template <bool BF16>
 __device__ __forceinline__ void pf_exp64(const uint32_t (&sa)[32], const uint32_t (&sb)[32], uint64_t sc2, uint64_t nm2, uint64_t &acc_a,
@@ -497,22 +525,28 @@ __global__ void __launch_bounds__(PF_THREADS, 2) fa_prefill_sm100_kernel(const F
 // ---------------------------------------------------------------------------------------------
 // Two row tiles per block: 256 packed rows share every K / V tile, and the two softmax groups take
 // turns with the tensor core (while group A runs its softmax the products of group B execute).
-//   warps 0-3 softmax of rows 0-127 (A), warps 4-7 of rows 128-255 (B), warp 8 loader (two stages of
-//   128 keys), warp 9 issues the products and owns the tensor memory: 512 columns = S_A 128, S_B 128 (P_g
-//   overwrites the first 64 columns of S_g once the scores are in registers), O_A 128, O_B 128.
+//   16 softmax warps: two threads per row, each with 64 of the 128 scores of a key tile (warps 0-3 / 8-11: rows
+//   0-127 (A), first / second half of the tile; warps 4-7 / 12-15: rows 128-255 (B)); the halves exchange their
+//   maxima through shared memory once per tile. Twice the warps to hide the latency of the exponentials and of
+//   the tensor memory round trips: with one thread per row the softmax of a tile took 3300-4800 cycles and the
+//   tensor core sat idle three quarters of the time. Warp 16 loader (two stages of 128 keys), warp 17 issues the
+//   products and owns the tensor memory: 512 columns = S_A 128, S_B 128 (P_g overwrites the first 64 columns of
+//   S_g once the scores are in registers), O_A 128, O_B 128.
 //   Tiles of 128 keys: a tcgen05.mma costs the issuing thread about 90 cycles whatever its shape
 //   (measured), so S = Q K^T runs as 8 products of N = 128 instead of 16 of N = 64. One block per SM.
 // ---------------------------------------------------------------------------------------------
-constexpr int P2_THREADS = 320, P2_ROWS = 256, P2_STAGES = 2, P2_BN = 128;
+constexpr int P2_THREADS = 576, P2_ROWS = 256, P2_STAGES = 2, P2_BN = 128, P2_LOADER = 16, P2_ISSUER = 17;
 constexpr uint32_t P2_KT_BYTES = 32768, P2_VT_BYTES = 32768;  // 128 keys x 128 dims x 2 bytes
 constexpr uint32_t P2_TMEM_COLS = 512;
 constexpr uint32_t P2_SM_Q = 0, P2_SM_K = 2 * PF_Q_BYTES, P2_SM_V = P2_SM_K + P2_STAGES * P2_KT_BYTES;
-constexpr uint32_t P2_SM_BAR = P2_SM_V + P2_STAGES * P2_VT_BYTES, P2_SMEM = P2_SM_BAR + 256;
+constexpr uint32_t P2_SM_BAR = P2_SM_V + P2_STAGES * P2_VT_BYTES, P2_SM_X = P2_SM_BAR + 256;  // exchange: [2][2][2][128] maxima, [2][2][128] sums
+constexpr uint32_t P2_SMEM = P2_SM_X + 6144;
 __host__ __device__ constexpr uint32_t p2_s_col(int g) { return 128u * g; }
 __host__ __device__ constexpr uint32_t p2_p_col(int g) { return 128u * g; }  // over S_g
 __host__ __device__ constexpr uint32_t p2_o_col(int g) { return 256u + 128u * g; }
 // barriers
-constexpr int B_KF = 0, B_VF = P2_STAGES, B_KE = 2 * P2_STAGES, B_VE = 3 * P2_STAGES, B_S = 4 * P2_STAGES, B_P = B_S + 2, B_O = B_P + 2, B_DRAIN = B_O + 1;
+constexpr int B_KF = 0, B_VF = P2_STAGES, B_KE = 2 * P2_STAGES, B_VE = 3 * P2_STAGES, B_S = 4 * P2_STAGES, B_P = B_S + 2, B_O = B_P + 2, B_DRAIN = B_O + 1,
+              B_X = B_DRAIN + 1;  // per group: both halves of the rows have published their maxima (or sums)
 
 template <bool BF16>
 __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const FaParams p) {
@@ -564,14 +598,16 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
         }
         mbar_init(&bars[B_S], 1);
         mbar_init(&bars[B_S + 1], 1);
-        mbar_init(&bars[B_P], 128);
-        mbar_init(&bars[B_P + 1], 128);
+        mbar_init(&bars[B_P], 256);
+        mbar_init(&bars[B_P + 1], 256);
+        mbar_init(&bars[B_X], 256);
+        mbar_init(&bars[B_X + 1], 256);
         mbar_init(&bars[B_O], 1);
         mbar_init(&bars[B_DRAIN], 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 9) {
+    if (warp == P2_ISSUER) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(P2_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -593,7 +629,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 8) {
+    if (warp == P2_LOADER) {
         // ================================================================ loader
         // Per lane constants: the lane's row and chunk inside a step of 32 chunks (K: 8 rows x 4 chunks of one
         // core-matrix row group; V: 16 keys x 2 chunks), so that a copy costs an add or two besides itself.
@@ -669,7 +705,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         if (!ok) *abort_flag = 1;
-    } else if (warp == 9) {
+    } else if (warp == P2_ISSUER) {
         // ================================================================ matrix products (one lane issues)
         if (lane == 0) {
             constexpr uint32_t IQK = tc_idesc(BF16, false, PF_BM, P2_BN), IPV = tc_idesc(BF16, true, PF_BM, PF_D);
@@ -685,7 +721,8 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
                 const uint32_t vs = sbase + P2_SM_V + (t % P2_STAGES) * P2_VT_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < P2_BN / 16; ++ks)
-                    tc_mma_ts(tmem + p2_o_col(g), tmem + p2_p_col(g) + ks * 8, tc_desc(vs + ks * 256, 128, 2048), IPV, (t > 0 || ks > 0) ? 1u : 0u);
+                    tc_mma_ts(tmem + p2_o_col(g), tmem + p2_s_col(g) + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8), tc_desc(vs + ks * 256, 128, 2048), IPV,
+                              (t > 0 || ks > 0) ? 1u : 0u);  // P of keys 0-63 / 64-127 sits in the first columns of each half of S
             };
             if (ntiles > 0) {
                 ok = pf_wait(bar0 + 8 * B_KF, 0, abort_flag);
@@ -737,10 +774,10 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
         }
         __syncwarp();
     } else {
-        // ================================================================ softmax, thread = row
-        const int g = warp >> 2, w4 = warp & 3;
-        const uint32_t g_row0 = row0 + g * PF_BM;
-        const uint32_t r = g_row0 + w4 * 32 + lane;
+        // ================================================================ softmax, two threads per row
+        const int half = warp >> 3, g = (warp >> 2) & 1, w4 = warp & 3;
+        const uint32_t g_row0 = row0 + g * PF_BM, rr = w4 * 32 + lane;
+        const uint32_t r = g_row0 + rr;
         const bool r_ok = r < R;
         long long r_lo = 0, r_hi = 0;
         if (r_ok) range_of(r, r_lo, r_hi);
@@ -752,7 +789,10 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
             if (g_row0 + PF_BM > R) himin = -1;
         }
         const uint32_t lane_base = tmem + ((uint32_t)(w4 * 32) << 16);
-        const uint32_t s_col = p2_s_col(g), p_col = p2_p_col(g), o_col = p2_o_col(g);
+        // each half keeps its P inside its own 64 columns of S (first 32 of them), so no half overwrites scores the other still reads
+        const uint32_t s_col = p2_s_col(g) + 64 * half, p_col = s_col, o_col = p2_o_col(g) + 64 * half;
+        float *xmax = reinterpret_cast<float *>(smem + P2_SM_X);           // [tile & 1][group][half][row]
+        float *xsum = reinterpret_cast<float *>(smem + P2_SM_X + 4096);    // [group][half][row]
         const float sl2 = p.scale * p.kd * PF_LOG2E;
         float mref = -INFINITY, l = 0.0f;
         bool ok = true;
@@ -761,23 +801,34 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            uint32_t s0[32], s1[32], s2[32], s3[32];
-            tc_ld32(lane_base + s_col, s0);
-            tc_ld32(lane_base + s_col + 32, s1);
-            tc_ld32(lane_base + s_col + 64, s2);
-            tc_ld32(lane_base + s_col + 96, s3);
-            tc_wait_ld();
             const long long j0 = t_lo + (long long)t * P2_BN;
             const bool full = j0 >= lomax && j0 + P2_BN <= himin && j0 + P2_BN <= t_hi;
+            int lo_rel = 0, hi_rel = P2_BN;
             if (!full) {
-                const int lo_rel = r_ok ? (int)max(min(r_lo - j0, (long long)P2_BN), 0ll) : P2_BN;
-                const int hi_rel = r_ok ? (int)max(min(min(r_hi, t_hi) - j0, (long long)P2_BN), 0ll) : 0;
-                pf_mask32(s0, 0, lo_rel, hi_rel);
-                pf_mask32(s1, 32, lo_rel, hi_rel);
-                pf_mask32(s2, 64, lo_rel, hi_rel);
-                pf_mask32(s3, 96, lo_rel, hi_rel);
+                lo_rel = r_ok ? (int)max(min(r_lo - j0, (long long)P2_BN), 0ll) : P2_BN;
+                hi_rel = r_ok ? (int)max(min(min(r_hi, t_hi) - j0, (long long)P2_BN), 0ll) : 0;
             }
-            const float mx = fmaxf(pf_max64(s0, s1), pf_max64(s2, s3)) * sl2;  // sl2 > 0: the maximum commutes with the scale
+            // pass 1: this half's maximum, 32 columns at a time (the scores are read again below: a second
+            // tensor memory load is cheaper than 64 registers held across the exchange)
+            float hmax;
+            {
+                uint32_t sa[32];
+                tc_ld32(lane_base + s_col, sa);
+                tc_wait_ld();
+                if (!full) pf_mask32(sa, 64 * half, lo_rel, hi_rel);
+                hmax = pf_max32(sa);
+                tc_ld32(lane_base + s_col + 32, sa);
+                tc_wait_ld();
+                if (!full) pf_mask32(sa, 64 * half + 32, lo_rel, hi_rel);
+                hmax = fmaxf(hmax, pf_max32(sa));
+            }
+            // the row's maximum over both halves: through shared memory and the group's exchange barrier
+            xmax[(((t & 1) * 2 + g) * 2 + half) * PF_BM + rr] = hmax;
+            mbar_arrive(&bars[B_X + g]);
+            ok = pf_wait(bar0 + 8 * (B_X + g), t & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const float mx = fmaxf(hmax, xmax[(((t & 1) * 2 + g) * 2 + (half ^ 1)) * PF_BM + rr]) * sl2;  // sl2 > 0
             bool need = false;
             if (t == 0) mref = mx;
             else need = mx > mref + PF_SLACK;
@@ -787,9 +838,9 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
                 l *= f;
             }
             if (__any_sync(0xffffffffu, need)) {
-                // rows whose maximum moved: O goes to the new reference
+                // rows whose maximum moved: this half's 64 columns of O go to the new reference
 #pragma unroll 1
-                for (int ch = 0; ch < 4; ++ch) {
+                for (int ch = 0; ch < 2; ++ch) {
                     uint32_t o[32];
                     tc_ld32(lane_base + o_col + 32 * ch, o);
                     tc_wait_ld();
@@ -799,24 +850,29 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
                 }
                 tc_wait_st();
             }
+            // pass 2: exponentials, 32 scores -> 16 columns of P at a time
             const float ms = mref == -INFINITY ? 0.0f : mref;
             const uint64_t sc2 = pk2(sl2, sl2), nm2 = pk2(-ms, -ms);
-            uint64_t acc_a = pk2(0.0f, 0.0f), acc_b = acc_a;
+            uint64_t acc = pk2(0.0f, 0.0f);
             {
-                uint32_t pr[32];
-                pf_exp64<BF16>(s0, s1, sc2, nm2, acc_a, acc_b, pr);
-                tc_st32(lane_base + p_col, pr);  // over the first columns of S, which are in registers
+                // P goes over columns 0-31 of this half's scores; columns 32-63 are read after the first store, which
+                // does not touch them
+                uint32_t sa[32], pr[16];
+                tc_ld32(lane_base + s_col, sa);
+                tc_wait_ld();
+                if (!full) pf_mask32(sa, 64 * half, lo_rel, hi_rel);
+                pf_exp32<BF16>(sa, sc2, nm2, acc, pr);
+                tc_st16(lane_base + p_col, pr);
+                tc_ld32(lane_base + s_col + 32, sa);
+                tc_wait_ld();
+                if (!full) pf_mask32(sa, 64 * half + 32, lo_rel, hi_rel);
+                pf_exp32<BF16>(sa, sc2, nm2, acc, pr);
+                tc_st16(lane_base + p_col + 16, pr);
             }
             {
-                uint32_t pr[32];
-                pf_exp64<BF16>(s2, s3, sc2, nm2, acc_a, acc_b, pr);
-                tc_st32(lane_base + p_col + 32, pr);
-            }
-            {
-                float a0, a1, b0, b1;
-                upk2(acc_a, a0, a1);
-                upk2(acc_b, b0, b1);
-                l += (a0 + a1) + (b0 + b1);
+                float a0, a1;
+                upk2(acc, a0, a1);
+                l += a0 + a1;
             }
             tc_wait_st();
             tc_fence_before();
@@ -826,13 +882,22 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
             ok = pf_wait(bar0 + 8 * B_O, 0, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
         }
+        // the row's sum over both halves
+        float ltot = l;
+        if (ok) {
+            xsum[(g * 2 + half) * PF_BM + rr] = l;
+            mbar_arrive(&bars[B_X + g]);
+            ok = pf_wait(bar0 + 8 * (B_X + g), ntiles & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) ltot = l + xsum[(g * 2 + (half ^ 1)) * PF_BM + rr];
+        }
         if (!ok) *abort_flag = 1;
-        const float inv = (ok && ntiles > 0 && l > 0.0f) ? p.vd / l : 0.0f;
+        const float inv = (ok && ntiles > 0 && ltot > 0.0f) ? p.vd / ltot : 0.0f;
         const uint32_t i_tok = r_ok ? r / G : 0, h = hk * G + (r_ok ? r % G : 0);
-        uint16_t *orow = reinterpret_cast<uint16_t *>(p.o) + ((q0 + i_tok) * p.hq + h) * PF_D;
+        uint16_t *orow = reinterpret_cast<uint16_t *>(p.o) + ((q0 + i_tok) * p.hq + h) * PF_D + 64 * half;
         if (ok && ntiles > 0) tc_fence_after();
 #pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = 0; ch < 2; ++ch) {
             uint32_t o[32];
             if (ok && ntiles > 0) {
                 tc_ld32(lane_base + o_col + 32 * ch, o);
@@ -857,7 +922,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 9) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(P2_TMEM_COLS) : "memory");
+    if (warp == P2_ISSUER) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(P2_TMEM_COLS) : "memory");
     if (tid == 0 && *abort_flag) atomicExch(&g_wait_failed, 1);
 }
 
