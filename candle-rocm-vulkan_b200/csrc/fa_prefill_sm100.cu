@@ -546,7 +546,8 @@ __host__ __device__ constexpr uint32_t p2_p_col(int g) { return 128u * g; }  // 
 __host__ __device__ constexpr uint32_t p2_o_col(int g) { return 256u + 128u * g; }
 // barriers
 constexpr int B_KF = 0, B_VF = P2_STAGES, B_KE = 2 * P2_STAGES, B_VE = 3 * P2_STAGES, B_S = 4 * P2_STAGES, B_P = B_S + 2, B_O = B_P + 2, B_DRAIN = B_O + 1,
-              B_X = B_DRAIN + 1;  // per group: both halves of the rows have published their maxima (or sums)
+              B_X = B_DRAIN + 1,  // per group: both halves of the rows have published their maxima (or sums)
+              B_Q = B_X + 2;      // the Q tile has landed
 
 template <bool BF16>
 __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const FaParams p) {
@@ -555,8 +556,8 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + P2_SM_BAR);
     // barriers: k_full, v_full, k_empty, v_empty per stage, s_full and p_full per group, o_full, drain (B_* above)
     const uint32_t bar0 = sbase + P2_SM_BAR;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + P2_SM_BAR + 128);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + P2_SM_BAR + 136);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + P2_SM_BAR + 192);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + P2_SM_BAR + 200);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     const uint32_t hk = blockIdx.y, b = blockIdx.z, G = p.group;
@@ -604,6 +605,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
         mbar_init(&bars[B_X + 1], 256);
         mbar_init(&bars[B_O], 1);
         mbar_init(&bars[B_DRAIN], 1);
+        mbar_init(&bars[B_Q], P2_THREADS);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -611,7 +613,12 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(P2_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // Q: 256 rows x 16 chunks (two K-major operands of 128 rows)
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    // Q: 256 rows x 16 chunks (two K-major operands of 128 rows). Nobody waits for it here: every thread leaves an
+    // asynchronous arrival on the Q barrier, which the issuing thread waits for before its first product, so the first
+    // K / V tiles load at the same time.
     for (int idx = tid; idx < P2_ROWS * 16; idx += P2_THREADS) {
         const int blk = idx >> 5, l = idx & 31;
         const int grp = blk >> 2, kc = (blk & 3) * 4 + (l >> 3), rr = grp * 8 + (l & 7);
@@ -621,12 +628,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
         const uint64_t off = (p.varlen ? (q0 + i) * p.q_ss : b * p.q_sb + i * p.q_ss) + h * p.q_sh;
         pf_cp16(sbase + P2_SM_Q + grp * 2048 + kc * 128 + (rr & 7) * 16, qb + off * 2 + kc * 16, ok);
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar0 + 8 * B_Q) : "memory");
     const uint32_t tmem = *tmem_slot;
 
     if (warp == P2_LOADER) {
@@ -725,7 +727,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
                               (t > 0 || ks > 0) ? 1u : 0u);  // P of keys 0-63 / 64-127 sits in the first columns of each half of S
             };
             if (ntiles > 0) {
-                ok = pf_wait(bar0 + 8 * B_KF, 0, abort_flag);
+                ok = pf_wait(bar0 + 8 * B_Q, 0, abort_flag) && pf_wait(bar0 + 8 * B_KF, 0, abort_flag);
                 if (ok) {
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copies wrote through the generic proxy
                     tc_fence_after();
