@@ -13,6 +13,7 @@
 // right aligned windows, softcap, ALiBi, k / v descale, varlen through cumulative offsets, zeros
 // for rows without a visible key; output row (token, head) of d contiguous elements.
 #include <algorithm>
+#include <mutex>
 #include <cuda_bf16.h>
 
 #include "common.cuh"
@@ -488,11 +489,46 @@ extern "C" int b200_flash_attn(const B200FaArgs *a, b200_stream_t stream_) {
     return bf ? fa_launch<128, true>(pl, stream) : fa_launch<128, false>(pl, stream);
 }
 
-extern "C" int b200_fa_prefill_append(const B200FaArgs *fa, const B200KvAppendArgs *append, b200_stream_t stream) {
-    // The attention reads the uncompressed k / v; the cache write reads the same tensors once more.
-    // Both are launched back to back on the stream: the second pass finds k / v in L2 for the sizes
-    // of a prefill chunk (B x S x Hkv x D x 2 x 2 bytes = 67 MB for 4 x 4096 x 8 x 128, L2 holds 126 MB).
-    int rc = b200_flash_attn(fa, stream);
-    if (rc) return rc;
-    return b200_kv_append(append, stream);
+// One auxiliary stream and two events per device for b200_fa_prefill_append (created on first use, kept for the life
+// of the process).
+struct PrefillFork {
+    cudaStream_t aux = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+static PrefillFork g_fork[16];
+static std::mutex g_fork_mutex;
+
+extern "C" int b200_fa_prefill_append(const B200FaArgs *fa, const B200KvAppendArgs *append, b200_stream_t stream_) {
+    // The attention reads the uncompressed k / v and is bound by the tensor core; the cache write reads the same
+    // tensors once more and is bound by memory. They do not depend on one another, so the cache write runs on an
+    // auxiliary stream beside the attention (its blocks fit into the registers and shared memory the attention blocks
+    // leave free) and joins the caller's stream at the end. Both orderings are expressed with events, so the call
+    // can be captured in a CUDA graph.
+    cudaStream_t stream = (cudaStream_t)stream_;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) {
+        const int rc = b200_flash_attn(fa, stream_);
+        return rc ? rc : b200_kv_append(append, stream_);
+    }
+    PrefillFork *f = &g_fork[dev];
+    {
+        std::lock_guard<std::mutex> lock(g_fork_mutex);
+        if (!f->aux) {
+            if (cudaStreamCreateWithFlags(&f->aux, cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&f->fork, cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&f->join, cudaEventDisableTiming) != cudaSuccess) {
+                f->aux = nullptr;
+                return set_error(B200_ERR_LAUNCH, "fa_prefill_append: cannot create the auxiliary stream");
+            }
+        }
+    }
+    if (cudaEventRecord(f->fork, stream) != cudaSuccess || cudaStreamWaitEvent(f->aux, f->fork, 0) != cudaSuccess)
+        return set_error(B200_ERR_LAUNCH, "fa_prefill_append: fork: %s", cudaGetErrorString(cudaGetLastError()));
+    // the attention first: its blocks (one per SM) take their place, the blocks of the cache write fill in beside them
+    const int rc_attn = b200_flash_attn(fa, stream_);
+    const int rc_append = b200_kv_append(append, (b200_stream_t)f->aux);
+    // join in any case, so that the auxiliary stream never outlives the call in the caller's ordering
+    if (cudaEventRecord(f->join, f->aux) != cudaSuccess || cudaStreamWaitEvent(stream, f->join, 0) != cudaSuccess)
+        return set_error(B200_ERR_LAUNCH, "fa_prefill_append: join: %s", cudaGetErrorString(cudaGetLastError()));
+    return rc_attn ? rc_attn : rc_append;
 }
