@@ -144,6 +144,8 @@ def run_reference(args, w, rank, world):
     O.build() if not (ROOT / "oracle" / "liboracle.so").exists() else None
     lens = seq_lens(w)
     nseq = min(w["b"], 8 if w["lens"] == "uniform512-8192" else max(1, 65536 // int(lens[0])))
+    # about a minute of CPU work for the whole run: fewer sequences per step when many steps are asked for
+    nseq = max(1, min(nseq, int(60.0 / max(args.steps + args.warmup, 1) / 0.17)))
     for _ in range(args.warmup):
         cpu_reference_step(w, lens, min(nseq, 2))
     times = []
