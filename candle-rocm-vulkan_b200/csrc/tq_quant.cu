@@ -40,10 +40,10 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
-// EPL: elements per lane (D <= 32 * EPL)
-template <int EPL>
+// EPL: elements per lane (D <= 32 * EPL); DT: source dtype
+template <int EPL, int DT>
 __global__ void __launch_bounds__(QW * 32) quant_rows_kernel(const QuantParams p) {
-    __shared__ uint8_t s_codes[QW][32 * EPL];
+    __shared__ __align__(16) uint8_t s_codes[QW][32 * EPL];
     __shared__ uint32_t s_scales[QW][2 * EPL];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const QuantSideParams &sp = p.side[blockIdx.y];
@@ -53,12 +53,20 @@ __global__ void __launch_bounds__(QW * 32) quant_rows_kernel(const QuantParams p
     uint8_t *codes = s_codes[warp];
     uint32_t *sc = s_scales[warp];
 
+    const bool small = rows < 0x80000000ull;  // 32-bit row arithmetic (the 64-bit divisions cost more than the codecs)
     for (uint64_t row = (uint64_t)blockIdx.x * QW + warp; row < rows; row += (uint64_t)gridDim.x * QW) {
-        const uint32_t t = (uint32_t)(row % p.nt);
-        const uint32_t h = (uint32_t)((row / p.nt) % p.nh);
-        const uint32_t b = (uint32_t)(row / ((uint64_t)p.nt * p.nh));
-        const char *src = reinterpret_cast<const char *>(sp.src) +
-                          (b * sp.s_b + h * sp.s_h + t * sp.s_t) * (uint64_t)dtype_size(p.src_dtype);
+        uint32_t t, h, b;
+        if (small) {
+            const uint32_t r32 = (uint32_t)row, bh = r32 / p.nt;
+            t = r32 - bh * p.nt;
+            b = bh / p.nh;
+            h = bh - b * p.nh;
+        } else {
+            t = (uint32_t)(row % p.nt);
+            h = (uint32_t)((row / p.nt) % p.nh);
+            b = (uint32_t)(row / ((uint64_t)p.nt * p.nh));
+        }
+        const char *src = reinterpret_cast<const char *>(sp.src) + (b * sp.s_b + h * sp.s_h + t * sp.s_t) * (uint64_t)dtype_size(DT);
         const int64_t pos = (sp.pos ? sp.pos[b] : sp.pos0) + (int64_t)t;
         uint32_t *orow = sp.dst + b * sp.c_b + h * sp.c_h + (uint64_t)pos * sp.c_t;
 
@@ -66,7 +74,7 @@ __global__ void __launch_bounds__(QW * 32) quant_rows_kernel(const QuantParams p
 #pragma unroll
         for (int k = 0; k < EPL; ++k) {
             const uint32_t j = lane + 32 * k;
-            x[k] = (k < nk && j < D) ? load_elem_rt(src, j, p.src_dtype) : 0.0f;
+            x[k] = (k < nk && j < D) ? load_elem<DT>(src, j) : 0.0f;
         }
 
         if (sp.rot == B200_ROT_HADAMARD) {
@@ -170,6 +178,18 @@ __global__ void __launch_bounds__(QW * 32) quant_rows_kernel(const QuantParams p
 
         // pack: element e at bit e * cb of the little-endian word stream
         const uint32_t mask = (1u << cb) - 1u;
+        if (cb == 8 && (D & 3u) == 0) {
+            // a word = four code bytes
+            for (uint32_t w = lane; w < (uint32_t)sp.code_words; w += 32) orow[w] = reinterpret_cast<const uint32_t *>(codes)[w];
+        } else if (cb == 4 && (D & 7u) == 0) {
+            // a word = the low nibbles of eight code bytes
+            for (uint32_t w = lane; w < (uint32_t)sp.code_words; w += 32) {
+                const uint2 v = reinterpret_cast<const uint2 *>(codes)[w];
+                const uint32_t a = v.x & 0x0f0f0f0fu, c4 = v.y & 0x0f0f0f0fu;
+                const uint32_t lo = (a | (a >> 4)) & 0x00ff00ffu, hi = (c4 | (c4 >> 4)) & 0x00ff00ffu;
+                orow[w] = ((lo | (lo >> 8)) & 0xffffu) | (((hi | (hi >> 8)) & 0xffffu) << 16);
+            }
+        } else
         for (uint32_t w = lane; w < (uint32_t)sp.code_words; w += 32) {
             const uint32_t bit0 = w * 32u;
             const uint32_t e0 = bit0 / cb;
@@ -296,9 +316,16 @@ static int launch_quant(const QuantParams &p, int sides, cudaStream_t stream) {
     if (rows == 0) return B200_OK;
     const unsigned gx = (unsigned)std::min<uint64_t>((rows + QW - 1) / QW, 148ull * 64);
     const dim3 grid(gx, sides), block(QW * 32);
-    if (p.d <= 128) quant_rows_kernel<4><<<grid, block, 0, stream>>>(p);
-    else if (p.d <= 256) quant_rows_kernel<8><<<grid, block, 0, stream>>>(p);
-    else quant_rows_kernel<32><<<grid, block, 0, stream>>>(p);
+#define B200_QUANT_LAUNCH(EPL)                                                                      \
+    do {                                                                                            \
+        if (p.src_dtype == B200_F32) quant_rows_kernel<EPL, B200_F32><<<grid, block, 0, stream>>>(p);      \
+        else if (p.src_dtype == B200_F16) quant_rows_kernel<EPL, B200_F16><<<grid, block, 0, stream>>>(p); \
+        else quant_rows_kernel<EPL, B200_BF16><<<grid, block, 0, stream>>>(p);                          \
+    } while (0)
+    if (p.d <= 128) B200_QUANT_LAUNCH(4);
+    else if (p.d <= 256) B200_QUANT_LAUNCH(8);
+    else B200_QUANT_LAUNCH(32);
+#undef B200_QUANT_LAUNCH
     return check_launch("tq_quantize");
 }
 
