@@ -220,11 +220,16 @@ def run_ours(args, w, rank, world, local_rank):
         caches.append((kc, vc))
     stage("caches filled")
     kv_len = torch.from_numpy(lens).to(dev)
-    q_host = torch.randn((b, hq, 1, d), dtype=tdt).pin_memory()
-    knew_host = torch.randn((b, hkv, 1, d), dtype=tdt).pin_memory()
-    vnew_host = torch.randn((b, hkv, 1, d), dtype=tdt).pin_memory()
+    # the step's inputs (queries and the new token's keys and values) are packed into one pinned host buffer, so that
+    # the end-to-end step pays for one host-to-device copy
+    nq, nkv = b * hq * d, b * hkv * d
+    step_host = torch.randn(nq + 2 * nkv, dtype=tdt).pin_memory()
+    q_host = step_host[:nq].view(b, hq, 1, d)
+    knew_host = step_host[nq:nq + nkv].view(b, hkv, 1, d)
+    vnew_host = step_host[nq + nkv:].view(b, hkv, 1, d)
+    step_dev = step_host.to(dev)
     out_host = torch.empty((b, hq, 1, d), dtype=tdt).pin_memory()
-    q = q_host.to(dev)
+    q = step_dev[:nq].view(b, hq, 1, d)
     out = torch.empty((b, hq, 1, d), dtype=tdt, device=dev)
     gathered = torch.empty((world * b, hq, 1, d), dtype=tdt, device=dev) if world > 1 else None
     cfg = P.FlashAttnConfig(d ** -0.5).causal()
@@ -339,51 +344,86 @@ def run_ours(args, w, rank, world, local_rank):
     per_step = [total_ms / args.steps]
     # ---- end to end through the public API with host buffers: H2D of the step's inputs, append of the new
     # token, attention, D2H of the outputs
+    # A serving loop overlaps the copies of neighbouring steps with the kernels: inputs and outputs are double
+    # buffered, the host-to-device copy of step i + 1 and the device-to-host copy of step i - 1 run on their own
+    # streams beside the kernels of step i. Every step still copies its own inputs in and its own result out.
     lens_dev = kv_len.clone()
-    k_new = torch.empty((b, hkv, 1, d), dtype=tdt, device=dev)
-    v_new = torch.empty((b, hkv, 1, d), dtype=tdt, device=dev)
+    in_dev = [step_dev, torch.empty_like(step_dev)]
+    out_dev = [out, torch.empty_like(out)]
+    out_hosts = [out_host, torch.empty_like(out_host).pin_memory()]
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
 
-    def e2e_step(i):
-        kc, vc = caches[i % nbuf]
-        q.copy_(q_host, non_blocking=True)
-        k_new.copy_(knew_host, non_blocking=True)
-        v_new.copy_(vnew_host, non_blocking=True)
-        _kv_append(k_new, v_new, kc, vc, kq, vq, lens_dev)
-        lens_dev.add_(1)
-        P.PackedAttention(q, kc, vc, lens_dev, kq, vq, cfg, out=out, gather=peer_gather).run()
-        if world > 1 and peer_gather is None:
-            dist.all_gather_into_tensor(gathered, out)
-        out_host.copy_(out, non_blocking=True)
+    def e2e_steps(first, count):
+        """Steps first .. first + count - 1 as a three-stage pipeline over the current stream and two copy streams."""
+        main = torch.cuda.current_stream(dev)
+        fork = torch.cuda.Event()
+        fork.record(main)
+        s_in.wait_event(fork)
+        s_out.wait_event(fork)
+        ev_in, ev_done, ev_out = {}, {}, {}
+        for i in range(first, first + count):
+            pb = i & 1
+            kc, vc = caches[i % nbuf]
+            qv = in_dev[pb][:nq].view(b, hq, 1, d)
+            kn = in_dev[pb][nq:nq + nkv].view(b, hkv, 1, d)
+            vn = in_dev[pb][nq + nkv:].view(b, hkv, 1, d)
+            with torch.cuda.stream(s_in):
+                if i - 2 in ev_done:
+                    s_in.wait_event(ev_done[i - 2])       # the kernels of step i - 2 have read this input buffer
+                in_dev[pb].copy_(step_host, non_blocking=True)
+                ev_in[i] = torch.cuda.Event()
+                ev_in[i].record(s_in)
+            main.wait_event(ev_in[i])
+            if i - 2 in ev_out:
+                main.wait_event(ev_out[i - 2])            # the result of step i - 2 has left this output buffer
+            _kv_append(kn, vn, kc, vc, kq, vq, lens_dev)
+            lens_dev.add_(1)
+            P.PackedAttention(qv, kc, vc, lens_dev, kq, vq, cfg, out=out_dev[pb], gather=peer_gather).run()
+            if world > 1 and peer_gather is None:
+                dist.all_gather_into_tensor(gathered, out_dev[pb])
+            ev_done[i] = torch.cuda.Event()
+            ev_done[i].record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_done[i])
+                out_hosts[pb].copy_(out_dev[pb], non_blocking=True)
+                ev_out[i] = torch.cuda.Event()
+                ev_out[i].record(s_out)
+        last = first + count - 1
+        main.wait_event(ev_in[last])
+        main.wait_event(ev_out[last])
+        if last - 1 in ev_out:
+            main.wait_event(ev_out[last - 1])
 
-    for i in range(max(min(args.warmup, 3), nbuf)):
-        e2e_step(i)
+    e2e_steps(0, max(min(args.warmup, 3), nbuf))
     barrier()
-    # the same calls captured once per cache: a serving loop replays its step (copies included) instead of paying the
-    # host's call path every token
-    e2e_graphs = []
+    # the same calls captured once (copies and stream dependencies included): a serving loop replays its steps instead
+    # of paying the host's call path every token
+    e2e_group = nbuf * max(1, 8 // nbuf)
+    e2e_graph = None
     if graphs:
         try:
-            for i in range(nbuf):
-                gr = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(gr):
-                    e2e_step(i)
-                e2e_graphs.append(gr)
+            e2e_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(e2e_graph):
+                e2e_steps(0, e2e_group)
         except Exception as e:
-            print(f"bench: capture of the end-to-end step failed ({e}); timing eager calls", file=sys.stderr)
-            e2e_graphs = []
+            print(f"bench: capture of the end-to-end steps failed ({e}); timing eager calls", file=sys.stderr)
+            e2e_graph = None
             torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    for i in range(args.steps):
-        if e2e_graphs:
-            e2e_graphs[i % nbuf].replay()
+    i = 0
+    while i < args.steps:
+        if e2e_graph is not None and args.steps - i >= e2e_group:
+            e2e_graph.replay()
+            i += e2e_group
         else:
-            e2e_step(i)
+            e2e_steps(i, 1)
+            i += 1
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
-    e2e_graphs.clear()
+    e2e_graph = None
     stage("end-to-end region done")
     # max over ranks of the times, sum over ranks of the bytes
     (total_ms, e2e_ms, kern_ms), job_bytes = aggregate_over_ranks(
