@@ -314,6 +314,73 @@ def test_full_size_properties_config2(P, oracle):
     assert torch.isfinite(out).all()
 
 
+def _fill_cache(P, cache, b, hkv, ctx, d, dtype, seed):
+    """Synthetic keys / values generated and quantized on the device in slabs (the caches of configs 4 and 5 are too
+    large to come from the host); returns the slabs of the first two sequences for the oracle."""
+    g = torch.Generator(device="cuda:0").manual_seed(seed)
+    keep_k, keep_v = [], []
+    for p0 in range(0, ctx, 2048):
+        t = min(2048, ctx - p0)
+        k = torch.randn((b, hkv, t, d), generator=g, device="cuda:0", dtype=dtype)
+        v = torch.randn((b, hkv, t, d), generator=g, device="cuda:0", dtype=dtype)
+        cache.append(k, v)
+        keep_k.append(k[:2].float().cpu().numpy())
+        keep_v.append(v[:2].float().cpu().numpy())
+    return np.concatenate(keep_k, axis=2), np.concatenate(keep_v, axis=2)
+
+
+def test_full_size_config4_turboquant(P, oracle):
+    """One GPU's share of the long-context TurboQuant configuration (one kv head of B=32, Hq=64/8, context 32768,
+    4-bit codebook rows, seeded Hadamard rotation): two sequences over the full context against the oracle on the
+    rows copied back, the batch through split invariance."""
+    b, hq, hkv, d, ctx = 32, 8, 1, 128, 32768
+    cache = P.TurboKvCache(fmt(P, 0, 4), fmt(P, 0, 4), d, "hadamard", 42, ctx)
+    kx, vx = _fill_cache(P, cache, b, hkv, ctx, d, torch.bfloat16, 41)
+    assert cache.seq_len() == ctx
+    q = torch.randn((b, hq, 1, d), generator=torch.Generator(device="cuda:0").manual_seed(3), device="cuda:0", dtype=torch.bfloat16)
+    cfg = P.FlashAttnConfig(d ** -0.5).causal()
+    out = cache.attention(q, cfg)
+    kd, vd = words(cache.k[:2]), words(cache.v[:2])
+    # rows: bit-exact with the reference quantizer on the rows the device butterflies give
+    rot = cache.kq.rotate(to_dev(kx[:, :, :256].reshape(-1, d), "bf16")).cpu().numpy()
+    tab = MG.tab_for(0, 4, d)
+    assert np.array_equal(kd[:, :, :256].reshape(-1, 18), oracle.quantize_rows(rot, 0, 4, tab))
+    # attention in the rotated space over the same rows, rotated back
+    qr = oracle.rotate_rows(q[:2].float().cpu().numpy().reshape(-1, d), oracle.rotation_matrix(d, 1, 42)).reshape(2, hq, 1, d)
+    tabs = np.zeros(64, np.float32)
+    tabs[:32] = tab
+    tabs[32:] = tab
+    want = oracle.tq_attention(qr, kd, vd, ctx, (0, 4), (0, 4), d ** -0.5, tabs, wr=0)
+    want = oracle.rotate_rows(want.reshape(-1, d), oracle.rotation_matrix(d, 1, 44), transpose=True).reshape(want.shape)
+    assert_close(out[:2].float().cpu().numpy(), want, what="config 4, two sequences", out="bf16")
+    cfg2 = P.FlashAttnConfig(d ** -0.5).causal()
+    cfg2.splits = 5
+    out2 = cache.attention(q, cfg2)
+    assert_close(out2.float().cpu().numpy(), out.float().cpu().numpy(), atol=4e-3, rtol=8e-3, what="split invariance")
+
+
+def test_full_size_config5_mxfp8_layer(P, oracle):
+    """One layer of the MXFP8 sweep (B=128, Hq=32, Hkv=8, context 16384, f16): 4.7 GB of packed rows on the device; two
+    sequences against the oracle on the rows copied back, all of them finite and independent of the split count."""
+    b, hq, hkv, d, ctx = 128, 32, 8, 128, 16384
+    cache = P.TurboKvCache(fmt(P, 4), fmt(P, 4), d, "none", 42, ctx)
+    kx, vx = _fill_cache(P, cache, b, hkv, ctx, d, torch.float16, 51)
+    q = torch.randn((b, hq, 1, d), generator=torch.Generator(device="cuda:0").manual_seed(4), device="cuda:0", dtype=torch.float16)
+    cfg = P.FlashAttnConfig(d ** -0.5).causal()
+    out = cache.attention(q, cfg)
+    kd, vd = words(cache.k[:2]), words(cache.v[:2])
+    assert np.array_equal(kd[0, 0, :512], oracle.quantize_rows(kx[0, 0, :512], 4))
+    want = oracle.tq_attention(q[:2].float().cpu().numpy(), kd, vd, ctx, (4, 4), (4, 4), d ** -0.5, wr=0)
+    assert_close(out[:2].float().cpu().numpy(), want, what="config 5, two sequences", out="f16")
+    assert torch.isfinite(out).all()
+    cfg2 = P.FlashAttnConfig(d ** -0.5).causal()
+    cfg2.splits = 2
+    out2 = cache.attention(q, cfg2)
+    assert_close(out2.float().cpu().numpy(), out.float().cpu().numpy(), atol=4e-3, rtol=8e-3, what="split invariance")
+    del cache
+    torch.cuda.empty_cache()
+
+
 def test_gather_epilogue_on_one_rank(P, oracle):
     """b200_tq_attention_gather with a world of one: the rows land in slot (step & 1) of the gathered buffer, the step
     and the flag advance, and the regular output is unchanged. (The exchange between
