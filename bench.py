@@ -455,7 +455,8 @@ def run_ours(args, w, rank, world, local_rank):
             dt, cb = cpu_reference_step(w, lens, nseq)
             cpu = {"value": cb / dt / 1e9, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
                    "sample": f"{nseq} of {b} sequences, one pass ({dt:.2f} s): dequantize rows to {w['qdt']} + unfused attention"}
-        launches_per_step = 2 if (int(lens.max()) > 128) else 1
+        # the decode grid, the combine grid, and with N > 1 the one-warp kernel that publishes the gathered step
+        launches_per_step = 2 + (1 if (peer_gather is not None and world > 1) else 0)
         # dram__bytes_read.sum + dram__bytes_write.sum of one tq_decode_kernel launch, from the ncu capture of this same
         # workload (profiles/tq_decode_kernel_c2_mxfp4.md): 360.75 MB read + 7.54 MB written
         traffic, traffic_src = None, None
