@@ -249,8 +249,8 @@ int b200_tq_attention_static(const B200TqAttnArgs *args, b200_stream_t stream);
 
 /* ---- attention over packed rows, outputs gathered on every GPU ---------------------------------- */
 /* The all-gather of the outputs that follows a sharded decode step (every rank holds its own batch
- * entries or kv heads; the reference gathers with NCCL, SURVEY of the path: "one ncclAllGather of
- * outputs per layer"), fused into the epilogue of the attention: the kernel that merges the key
+ * entries or kv heads, and the layer's outputs are assembled on every rank: one all-gather per
+ * layer when done with NCCL), fused into the epilogue of the attention: the kernel that merges the key
  * splits stores every finished output row into the gathered buffer of every rank (plain peer
  * stores over NVLink, no multicast), the last block of the grid publishes this rank's step number
  * in every rank's flag array and waits, with a bound, until every rank has published the same step.

@@ -107,7 +107,7 @@ def test_rotations_orthogonal(oracle):
     assert np.array_equal(np.sign(m[0]), s)  # row 0 of H is all +
 
 
-def test_survey_known_answers(oracle):
+def test_known_answers_of_the_reference_unit_tests(oracle):
     # words produced by the reference's tq_quant kernels for a closed-form input
     i = np.arange(512)
     x = (((i * 37) % 101 - 50) / 10).astype(np.float32).reshape(4, 128)
