@@ -18,6 +18,8 @@
 //
 // Semantics as fa_dense.cu (candle-core/kernels/flash_attn_impl.h:330-443: FA2-order tiles, bottom
 // right aligned windows, zeros for rows without a visible key).
+#include <cuda.h>
+
 #include <algorithm>
 
 #include "common.cuh"
@@ -50,6 +52,23 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t saddr, uint32_t k_stride, u
     d |= (uint64_t)((mn_stride >> 4) & 0x3fffu) << 32;
     d |= 1ull << 46;  // descriptor version of this architecture
     return d;
+}
+// The same for tiles that a tensor copy wrote with the 128-byte swizzle (rows of 128 bytes, 8-row atoms of 1024 bytes,
+// tile base aligned to 1024 bytes): `lbo` is the distance between the two 64-element halves of an M/N-major operand
+// (unused for a K-major one), `sbo` the distance between 8-row atoms.
+__device__ __forceinline__ uint64_t tc_desc_sw128(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = (uint64_t)((saddr & 0x3ffffu) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3fffu) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;  // layout type: 128-byte swizzle
+    return d;
+}
+// one box of a tiled tensor map -> shared memory, completion counted in bytes on `bar` (no multicast)
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, int c3, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+                 : "memory");
 }
 // instruction descriptor, kind::f16: f32 accumulator, A and B of one 16-bit type, B N-major or K-major
 __host__ __device__ constexpr uint32_t tc_idesc(bool bf16, bool b_n_major, uint32_t m, uint32_t n) {
@@ -253,6 +272,17 @@ __device__ __forceinline__ bool pf_wait(uint32_t bar, uint32_t parity, volatile 
         if ((i & 255u) == 255u && *abort_flag) return false;
     }
     return false;
+}
+// bounded wait that ignores the abort flag: for copies in flight that must land before the block leaves
+__device__ __forceinline__ void pf_wait_landed(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < (1u << 16); ++i) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok)
+                     : "r"(bar), "r"(parity)
+                     : "memory");
+        if (ok) return;
+    }
 }
 
 template <bool BF16>
@@ -549,8 +579,11 @@ constexpr int B_KF = 0, B_VF = P2_STAGES, B_KE = 2 * P2_STAGES, B_VE = 3 * P2_ST
               B_X = B_DRAIN + 1,  // per group: both halves of the rows have published their maxima (or sums)
               B_Q = B_X + 2;      // the Q tile has landed
 
-template <bool BF16>
-__global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const FaParams p) {
+// TMA: K / V tiles arrive through two tensor copies each (boxes of 64 head-dim elements x 128 keys, 128-byte swizzle)
+// that one lane issues, instead of 8192 16-byte cp.async chunks per tile from the whole loader warp.
+template <bool BF16, bool TMA>
+__global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const FaParams p, const __grid_constant__ CUtensorMap tm_k,
+                                                                           const __grid_constant__ CUtensorMap tm_v, const uint32_t tm_order) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + P2_SM_BAR);
@@ -592,8 +625,8 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
 
     if (tid == 0) {
         for (int i = 0; i < P2_STAGES; ++i) {
-            mbar_init(&bars[B_KF + i], 32);
-            mbar_init(&bars[B_VF + i], 32);
+            mbar_init(&bars[B_KF + i], TMA ? 1 : 32);
+            mbar_init(&bars[B_VF + i], TMA ? 1 : 32);
             mbar_init(&bars[B_KE + i], 1);
             mbar_init(&bars[B_VE + i], 1);
         }
@@ -631,8 +664,42 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar0 + 8 * B_Q) : "memory");
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == P2_LOADER) {
-        // ================================================================ loader
+    if (warp == P2_LOADER && TMA) {
+        // ================================================================ loader (tensor copies)
+        // coordinates: the head-dim element, then kv head, key and batch entry in the order of their strides (tm_order: two
+        // bits each for the places of head, key and batch entry; K in bits 0-5, V in bits 8-13); keys past the end of the
+        // tensor read as zeros
+        if (lane == 0) {
+            auto load = [&](const CUtensorMap *map, uint32_t ord, uint32_t dst, int j0, uint32_t bar) {
+                const uint32_t ph = ord & 3u, pk = (ord >> 2) & 3u;
+                const int c1 = ph == 0 ? (int)hk : (pk == 0 ? j0 : (int)b), c2 = ph == 1 ? (int)hk : (pk == 1 ? j0 : (int)b),
+                          c3 = ph == 2 ? (int)hk : (pk == 2 ? j0 : (int)b);
+                tma_load_4d(dst, map, 0, c1, c2, c3, bar);
+                tma_load_4d(dst + P2_KT_BYTES / 2, map, 64, c1, c2, c3, bar);
+            };
+            bool ok = true;
+            int issued_k = 0, issued_v = 0;
+            for (int t = 0; t < ntiles; ++t) {
+                const int st = t % P2_STAGES, j0 = (int)(t_lo + (long long)t * P2_BN);
+                if (t >= P2_STAGES && !(ok = pf_wait(bar0 + 8 * (B_KE + st), ((t / P2_STAGES) - 1) & 1, abort_flag))) break;
+                const uint32_t dk = sbase + P2_SM_K + st * P2_KT_BYTES, dv = sbase + P2_SM_V + st * P2_VT_BYTES;
+                mbar_expect_tx(&bars[B_KF + st], P2_KT_BYTES);
+                load(&tm_k, tm_order & 0x3fu, dk, j0, bar0 + 8 * (B_KF + st));
+                issued_k = t + 1;
+                if (t >= P2_STAGES && !(ok = pf_wait(bar0 + 8 * (B_VE + st), ((t / P2_STAGES) - 1) & 1, abort_flag))) break;
+                mbar_expect_tx(&bars[B_VF + st], P2_VT_BYTES);
+                load(&tm_v, (tm_order >> 8) & 0x3fu, dv, j0, bar0 + 8 * (B_VF + st));
+                issued_v = t + 1;
+            }
+            if (!ok) {
+                // gave up: the copies already issued must land before the block may leave (bounded)
+                *abort_flag = 1;
+                for (int t = max(issued_k - P2_STAGES, 0); t < issued_k; ++t) pf_wait_landed(bar0 + 8 * (B_KF + t % P2_STAGES), (t / P2_STAGES) & 1);
+                for (int t = max(issued_v - P2_STAGES, 0); t < issued_v; ++t) pf_wait_landed(bar0 + 8 * (B_VF + t % P2_STAGES), (t / P2_STAGES) & 1);
+            }
+        }
+    } else if (warp == P2_LOADER) {
+        // ================================================================ loader (16-byte chunks)
         // Per lane constants: the lane's row and chunk inside a step of 32 chunks (K: 8 rows x 4 chunks of one
         // core-matrix row group; V: 16 keys x 2 chunks), so that a copy costs an add or two besides itself.
         const uint64_t k_row8 = 8ull * p.k_ss * 2, v_row16 = 16ull * p.v_ss * 2;           // bytes between steps
@@ -716,14 +783,16 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
                 const uint32_t ks_ = sbase + P2_SM_K + (t % P2_STAGES) * P2_KT_BYTES, qs_ = sbase + P2_SM_Q + g * PF_Q_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < PF_D / 16; ++ks)
-                    tc_mma_ss(tmem + p2_s_col(g), tc_desc(qs_ + ks * 256, 128, 2048), tc_desc(ks_ + ks * 256, 128, 2048), IQK, ks > 0 ? 1u : 0u);
+                    tc_mma_ss(tmem + p2_s_col(g), tc_desc(qs_ + ks * 256, 128, 2048),
+                              TMA ? tc_desc_sw128(ks_ + (ks >> 2) * (P2_KT_BYTES / 2) + (ks & 3) * 32, 16, 1024) : tc_desc(ks_ + ks * 256, 128, 2048), IQK,
+                              ks > 0 ? 1u : 0u);
                 tc_commit(bar0 + 8 * (B_S + g));
             };
             auto issue_pv = [&](int g, int t) {  // O_g += P_g(t) V(t)
                 const uint32_t vs = sbase + P2_SM_V + (t % P2_STAGES) * P2_VT_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < P2_BN / 16; ++ks)
-                    tc_mma_ts(tmem + p2_o_col(g), tmem + p2_s_col(g) + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8), tc_desc(vs + ks * 256, 128, 2048), IPV,
+                    tc_mma_ts(tmem + p2_o_col(g), tmem + p2_s_col(g) + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8), TMA ? tc_desc_sw128(vs + ks * 2048, P2_VT_BYTES / 2, 1024) : tc_desc(vs + ks * 256, 128, 2048), IPV,
                               (t > 0 || ks > 0) ? 1u : 0u);  // P of keys 0-63 / 64-127 sits in the first columns of each half of S
             };
             if (ntiles > 0) {
@@ -941,6 +1010,53 @@ bool fa_prefill_sm100_supported(const FaParams &p, bool kv16) {
     return !off;
 }
 
+// ---- tensor maps of K / V for the tensor-copy loader -------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+    static const EncodeTiledFn fn = [] {
+        void *f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) f = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(f);
+    }();
+    return fn;
+}
+// A (batch, kv head, key, 128) tensor of 16-bit elements with element strides s_b, s_h, s_s and contiguous head dim as
+// a rank-4 map: head dim first, the other three in ascending order of stride (entries of extent 1 last). Boxes of
+// 64 x 128 keys, 128-byte swizzle. `order` gets the places of head, key and batch (two bits each). False when the tensor
+// cannot be described (alignment, strides) or the driver refuses.
+static bool make_kv_map(CUtensorMap *m, uint32_t *order, const void *base, bool bf16, uint64_t nb, uint64_t hkv, uint64_t lk, uint64_t s_b, uint64_t s_h,
+                        uint64_t s_s) {
+    const EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc || (reinterpret_cast<uintptr_t>(base) & 15)) return false;
+    struct Dim {
+        uint64_t size, stride;
+        int role;
+    } d[3] = {{hkv, s_h * 2, 0}, {lk, s_s * 2, 1}, {nb, s_b * 2, 2}};
+    std::stable_sort(d, d + 3, [](const Dim &a, const Dim &c) {
+        if ((a.size == 1) != (c.size == 1)) return c.size == 1;  // entries of extent 1 go last
+        return a.size > 1 && a.stride < c.stride;
+    });
+    uint64_t prev = PF_D * 2;
+    for (int i = 0; i < 3; ++i) {
+        if (d[i].size == 1) d[i].stride = prev;  // any legal value: the coordinate is always 0
+        if ((d[i].stride & 15) || d[i].stride < prev || d[i].stride >= (1ull << 40) || d[i].size > (1ull << 31)) return false;
+        prev = d[i].stride * d[i].size;
+    }
+    uint32_t ord = 0;
+    for (int i = 0; i < 3; ++i) ord |= (uint32_t)i << (2 * d[i].role);
+    const cuuint64_t dims[4] = {(cuuint64_t)PF_D, d[0].size, d[1].size, d[2].size};
+    const cuuint64_t strides[3] = {d[0].stride, d[1].stride, d[2].stride};
+    cuuint32_t box[4] = {64, 1, 1, 1};
+    box[1 + ((ord >> 2) & 3u)] = P2_BN;
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = enc(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    *order = ord;
+    return r == CUDA_SUCCESS;
+}
+
 int fa_prefill_sm100_launch(const FaParams &p, bool bf16, cudaStream_t stream) {
     static thread_local bool done[16][2] = {};
     int dev = 0;
@@ -949,8 +1065,11 @@ int fa_prefill_sm100_launch(const FaParams &p, bool bf16, cudaStream_t stream) {
         cudaError_t e = bf16 ? cudaFuncSetAttribute(fa_prefill_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM)
                              : cudaFuncSetAttribute(fa_prefill_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM);
         if (e == cudaSuccess)
-            e = bf16 ? cudaFuncSetAttribute(fa_prefill_sm100_kernel2<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM)
-                     : cudaFuncSetAttribute(fa_prefill_sm100_kernel2<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM);
+            e = bf16 ? cudaFuncSetAttribute(fa_prefill_sm100_kernel2<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM)
+                     : cudaFuncSetAttribute(fa_prefill_sm100_kernel2<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM);
+        if (e == cudaSuccess)
+            e = bf16 ? cudaFuncSetAttribute(fa_prefill_sm100_kernel2<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM)
+                     : cudaFuncSetAttribute(fa_prefill_sm100_kernel2<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P2_SMEM);
         if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "flash_attn (tcgen05 tiles): shared memory opt-in: %s", cudaGetErrorString(e));
         done[dev][bf16] = true;
     }
@@ -963,8 +1082,19 @@ int fa_prefill_sm100_launch(const FaParams &p, bool bf16, cudaStream_t stream) {
     if (force == 256) two = true;
     if (two) {
         const dim3 grid((unsigned)((rows + P2_ROWS - 1) / P2_ROWS), p.hkv, p.b);
-        if (bf16) fa_prefill_sm100_kernel2<true><<<grid, P2_THREADS, P2_SMEM, stream>>>(p);
-        else fa_prefill_sm100_kernel2<false><<<grid, P2_THREADS, P2_SMEM, stream>>>(p);
+        // K / V through tensor copies when the tensors can be described by a map (fixed-length batches, 16-byte aligned
+        // strides); otherwise 16-byte chunks
+        static const bool no_tma = [] { const char *e = getenv("B200_FA_NO_TMA"); return e && *e == '1'; }();
+        CUtensorMap tm_k, tm_v;
+        uint32_t ok_ = 0, ov_ = 0;
+        const bool tma = !no_tma && !p.varlen && make_kv_map(&tm_k, &ok_, p.k, bf16, p.b, p.hkv, p.lk, p.k_sb, p.k_sh, p.k_ss) &&
+                         make_kv_map(&tm_v, &ov_, p.v, bf16, p.b, p.hkv, p.lk, p.v_sb, p.v_sh, p.v_ss);
+        const uint32_t order = ok_ | (ov_ << 8);
+        if (!tma) memset(&tm_k, 0, sizeof(tm_k)), memset(&tm_v, 0, sizeof(tm_v));
+        if (tma && bf16) fa_prefill_sm100_kernel2<true, true><<<grid, P2_THREADS, P2_SMEM, stream>>>(p, tm_k, tm_v, order);
+        else if (tma) fa_prefill_sm100_kernel2<false, true><<<grid, P2_THREADS, P2_SMEM, stream>>>(p, tm_k, tm_v, order);
+        else if (bf16) fa_prefill_sm100_kernel2<true, false><<<grid, P2_THREADS, P2_SMEM, stream>>>(p, tm_k, tm_v, order);
+        else fa_prefill_sm100_kernel2<false, false><<<grid, P2_THREADS, P2_SMEM, stream>>>(p, tm_k, tm_v, order);
     } else {
         const dim3 grid((unsigned)((rows + PF_BM - 1) / PF_BM), p.hkv, p.b);
         if (bf16) fa_prefill_sm100_kernel<true><<<grid, PF_THREADS, PF_SMEM, stream>>>(p);

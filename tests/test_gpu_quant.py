@@ -69,6 +69,42 @@ def test_quantize_edge_rows(P, oracle):
     assert tuple(empty.shape) == (0, 34)
 
 
+def boundary_rows(mode, dim=128):
+    """Rows whose effective scale is exactly 1, filled with every midpoint between two neighbouring codes and the floats on
+    either side of it, both signs: the ties-to-even cases of the 4-bit and 8-bit element codecs."""
+    up = lambda a: np.nextafter(a, np.float32(np.inf), dtype=np.float32)
+    dn = lambda a: np.nextafter(a, np.float32(0), dtype=np.float32)
+    if mode in (2, 3):
+        vals, top = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], np.float32), 6.0
+    else:  # every non-negative finite e4m3 value: subnormals m / 512, normals (1 + m / 8) 2^(e - 7)
+        vals = np.array([m / 512.0 for m in range(8)] + [(1 + m / 8.0) * 2.0 ** (e - 7) for e in range(1, 16) for m in range(8)][:-1], np.float32)
+        top = 448.0
+    mids = ((vals[:-1].astype(np.float64) + vals[1:].astype(np.float64)) / 2).astype(np.float32)
+    pts = np.concatenate([mids, up(mids), dn(mids), vals, up(vals), dn(np.maximum(vals, np.float32(1e-30)))])
+    pts = np.clip(np.concatenate([pts, -pts]), -top, top).astype(np.float32)
+    # NVFP4: element 0 makes the global scale 1 and blocks 1-3 (block maximum 6) get a block scale of 1; the others:
+    # element 0 makes the scale of the row (FP8) or of block 0 (MX) exactly 1
+    slots = [16 * blk + j for blk in (1, 2, 3) for j in range(1, 16)] if mode == 3 else list(range(1, 32))
+    nrow = (len(pts) + len(slots) - 1) // len(slots)
+    x = np.zeros((nrow, dim), np.float32)
+    x[:, 0] = 2688.0 if mode == 3 else top
+    if mode == 3:
+        x[:, 16:64:16] = top
+    flat = np.zeros(nrow * len(slots), np.float32)
+    flat[: len(pts)] = pts
+    x[:, slots] = flat.reshape(nrow, len(slots))
+    return x
+
+
+@pytest.mark.parametrize("mode", [2, 3, 4, 5])
+def test_quantize_rounding_boundaries(P, oracle, mode):
+    x = boundary_rows(mode)
+    qz = P.TurboQuantizer(fmt(P, mode), 128, "none", 5)
+    got = words(qz.quantize_rows(to_dev(x)))
+    want = oracle.quantize_rows(x, mode)
+    assert np.array_equal(got, want), f"mode {mode}: {(got != want).sum()} words differ"
+
+
 def test_append_positions_strides_and_growth(P, oracle):
     b, h, d = 3, 2, 128
     cache = P.TurboKvCache(fmt(P, 2), fmt(P, 4), d, "none", 42, 4)
