@@ -70,6 +70,11 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
                  "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
                  : "memory");
 }
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, int c3, int c4, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
+                 : "memory");
+}
 // instruction descriptor, kind::f16: f32 accumulator, A and B of one 16-bit type, B N-major or K-major
 __host__ __device__ constexpr uint32_t tc_idesc(bool bf16, bool b_n_major, uint32_t m, uint32_t n) {
     return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((b_n_major ? 1u : 0u) << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
@@ -583,7 +588,8 @@ constexpr int B_KF = 0, B_VF = P2_STAGES, B_KE = 2 * P2_STAGES, B_VE = 3 * P2_ST
 // that one lane issues, instead of 8192 16-byte cp.async chunks per tile from the whole loader warp.
 template <bool BF16, bool TMA>
 __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const FaParams p, const __grid_constant__ CUtensorMap tm_k,
-                                                                           const __grid_constant__ CUtensorMap tm_v, const uint32_t tm_order) {
+                                                                           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_q,
+                                                                           const uint32_t tm_order) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + P2_SM_BAR);
@@ -592,6 +598,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + P2_SM_BAR + 192);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + P2_SM_BAR + 200);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool q_tma = TMA && (tm_order >> 16) != 0;  // the Q tile comes by tensor copies too (bit 16)
 
     const uint32_t hk = blockIdx.y, b = blockIdx.z, G = p.group;
     uint32_t lq = p.lq, lk = p.lk;
@@ -638,7 +645,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
         mbar_init(&bars[B_X + 1], 256);
         mbar_init(&bars[B_O], 1);
         mbar_init(&bars[B_DRAIN], 1);
-        mbar_init(&bars[B_Q], P2_THREADS);
+        mbar_init(&bars[B_Q], q_tma ? 1 : P2_THREADS);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -652,7 +659,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
     // Q: 256 rows x 16 chunks (two K-major operands of 128 rows). Nobody waits for it here: every thread leaves an
     // asynchronous arrival on the Q barrier, which the issuing thread waits for before its first product, so the first
     // K / V tiles load at the same time.
-    for (int idx = tid; idx < P2_ROWS * 16; idx += P2_THREADS) {
+    for (int idx = tid; idx < P2_ROWS * 16 && !q_tma; idx += P2_THREADS) {
         const int blk = idx >> 5, l = idx & 31;
         const int grp = blk >> 2, kc = (blk & 3) * 4 + (l >> 3), rr = grp * 8 + (l & 7);
         const uint32_t r = row0 + rr;
@@ -661,7 +668,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
         const uint64_t off = (p.varlen ? (q0 + i) * p.q_ss : b * p.q_sb + i * p.q_ss) + h * p.q_sh;
         pf_cp16(sbase + P2_SM_Q + grp * 2048 + kc * 128 + (rr & 7) * 16, qb + off * 2 + kc * 16, ok);
     }
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar0 + 8 * B_Q) : "memory");
+    if (!q_tma) asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar0 + 8 * B_Q) : "memory");
     const uint32_t tmem = *tmem_slot;
 
     if (warp == P2_LOADER && TMA) {
@@ -679,6 +686,14 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
             };
             bool ok = true;
             int issued_k = 0, issued_v = 0;
+            if (q_tma && ntiles > 0) {
+                // Q: coordinates (element, head in group, kv head, token, batch entry); a box is 64 elements of all heads
+                // of the group for 256 / G tokens = 256 packed rows (row = token * G + head), one box per half of the
+                // head dim: [half][row tile of 128][row][128 bytes, swizzled]
+                mbar_expect_tx(&bars[B_Q], 2 * PF_Q_BYTES);
+                tma_load_5d(sbase + P2_SM_Q, &tm_q, 0, 0, (int)hk, (int)(row0 / G), (int)b, bar0 + 8 * B_Q);
+                tma_load_5d(sbase + P2_SM_Q + PF_Q_BYTES, &tm_q, 64, 0, (int)hk, (int)(row0 / G), (int)b, bar0 + 8 * B_Q);
+            }
             for (int t = 0; t < ntiles; ++t) {
                 const int st = t % P2_STAGES, j0 = (int)(t_lo + (long long)t * P2_BN);
                 if (t >= P2_STAGES && !(ok = pf_wait(bar0 + 8 * (B_KE + st), ((t / P2_STAGES) - 1) & 1, abort_flag))) break;
@@ -694,6 +709,7 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
             if (!ok) {
                 // gave up: the copies already issued must land before the block may leave (bounded)
                 *abort_flag = 1;
+                if (q_tma) pf_wait_landed(bar0 + 8 * B_Q, 0);
                 for (int t = max(issued_k - P2_STAGES, 0); t < issued_k; ++t) pf_wait_landed(bar0 + 8 * (B_KF + t % P2_STAGES), (t / P2_STAGES) & 1);
                 for (int t = max(issued_v - P2_STAGES, 0); t < issued_v; ++t) pf_wait_landed(bar0 + 8 * (B_VF + t % P2_STAGES), (t / P2_STAGES) & 1);
             }
@@ -783,7 +799,9 @@ __global__ void __launch_bounds__(P2_THREADS, 1) fa_prefill_sm100_kernel2(const 
                 const uint32_t ks_ = sbase + P2_SM_K + (t % P2_STAGES) * P2_KT_BYTES, qs_ = sbase + P2_SM_Q + g * PF_Q_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < PF_D / 16; ++ks)
-                    tc_mma_ss(tmem + p2_s_col(g), tc_desc(qs_ + ks * 256, 128, 2048),
+                    tc_mma_ss(tmem + p2_s_col(g),
+                              q_tma ? tc_desc_sw128(sbase + P2_SM_Q + (ks >> 2) * PF_Q_BYTES + g * (PF_Q_BYTES / 2) + (ks & 3) * 32, 16, 1024)
+                                    : tc_desc(qs_ + ks * 256, 128, 2048),
                               TMA ? tc_desc_sw128(ks_ + (ks >> 2) * (P2_KT_BYTES / 2) + (ks & 3) * 32, 16, 1024) : tc_desc(ks_ + ks * 256, 128, 2048), IQK,
                               ks > 0 ? 1u : 0u);
                 tc_commit(bar0 + 8 * (B_S + g));
@@ -1057,6 +1075,25 @@ static bool make_kv_map(CUtensorMap *m, uint32_t *order, const void *base, bool 
     return r == CUDA_SUCCESS;
 }
 
+// The (batch, token, head, 128) query tensor as a rank-5 map (element, head in group, kv head, token, batch entry) whose
+// box of 64 x G x 1 x 256 / G lands as 256 packed rows (row = token * G + head in group).
+static bool make_q_map(CUtensorMap *m, const FaParams &p, bool bf16) {
+    const EncodeTiledFn enc = encode_tiled_fn();
+    const uint64_t G = p.group;
+    if (!enc || G == 0 || G > 256 || (G & (G - 1)) || (reinterpret_cast<uintptr_t>(p.q) & 15)) return false;
+    const cuuint64_t dims[5] = {(cuuint64_t)PF_D, G, p.hkv, p.lq, p.b};
+    cuuint64_t strides[4] = {p.q_sh * 2, G * p.q_sh * 2, p.q_ss * 2, p.q_sb * 2};
+    if (G == 1) strides[0] = PF_D * 2;
+    if (p.hkv == 1) strides[1] = strides[0] * G;
+    if (p.b == 1) strides[3] = strides[2] * p.lq;
+    for (int i = 0; i < 4; ++i)
+        if ((strides[i] & 15) || strides[i] < PF_D * 2 || strides[i] >= (1ull << 40)) return false;
+    const cuuint32_t box[5] = {64, (cuuint32_t)G, 1, (cuuint32_t)(P2_ROWS / G), 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    return enc(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void *>(p.q), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int fa_prefill_sm100_launch(const FaParams &p, bool bf16, cudaStream_t stream) {
     static thread_local bool done[16][2] = {};
     int dev = 0;
@@ -1085,16 +1122,19 @@ int fa_prefill_sm100_launch(const FaParams &p, bool bf16, cudaStream_t stream) {
         // K / V through tensor copies when the tensors can be described by a map (fixed-length batches, 16-byte aligned
         // strides); otherwise 16-byte chunks
         static const bool no_tma = [] { const char *e = getenv("B200_FA_NO_TMA"); return e && *e == '1'; }();
-        CUtensorMap tm_k, tm_v;
+        static const bool no_qtma = [] { const char *e = getenv("B200_FA_NO_QTMA"); return e && *e == '1'; }();
+        CUtensorMap tm_k, tm_v, tm_q;
         uint32_t ok_ = 0, ov_ = 0;
         const bool tma = !no_tma && !p.varlen && make_kv_map(&tm_k, &ok_, p.k, bf16, p.b, p.hkv, p.lk, p.k_sb, p.k_sh, p.k_ss) &&
                          make_kv_map(&tm_v, &ov_, p.v, bf16, p.b, p.hkv, p.lk, p.v_sb, p.v_sh, p.v_ss);
-        const uint32_t order = ok_ | (ov_ << 8);
+        const bool qtma = tma && !no_qtma && make_q_map(&tm_q, p, bf16);
+        const uint32_t order = ok_ | (ov_ << 8) | (qtma ? 1u << 16 : 0u);
         if (!tma) memset(&tm_k, 0, sizeof(tm_k)), memset(&tm_v, 0, sizeof(tm_v));
-        if (tma && bf16) fa_prefill_sm100_kernel2<true, true><<<grid, P2_THREADS, P2_SMEM, stream>>>(p, tm_k, tm_v, order);
-        else if (tma) fa_prefill_sm100_kernel2<false, true><<<grid, P2_THREADS, P2_SMEM, stream>>>(p, tm_k, tm_v, order);
-        else if (bf16) fa_prefill_sm100_kernel2<true, false><<<grid, P2_THREADS, P2_SMEM, stream>>>(p, tm_k, tm_v, order);
-        else fa_prefill_sm100_kernel2<false, false><<<grid, P2_THREADS, P2_SMEM, stream>>>(p, tm_k, tm_v, order);
+        if (!qtma) memset(&tm_q, 0, sizeof(tm_q));
+        if (tma && bf16) fa_prefill_sm100_kernel2<true, true><<<grid, P2_THREADS, P2_SMEM, stream>>>(p, tm_k, tm_v, tm_q, order);
+        else if (tma) fa_prefill_sm100_kernel2<false, true><<<grid, P2_THREADS, P2_SMEM, stream>>>(p, tm_k, tm_v, tm_q, order);
+        else if (bf16) fa_prefill_sm100_kernel2<true, false><<<grid, P2_THREADS, P2_SMEM, stream>>>(p, tm_k, tm_v, tm_q, order);
+        else fa_prefill_sm100_kernel2<false, false><<<grid, P2_THREADS, P2_SMEM, stream>>>(p, tm_k, tm_v, tm_q, order);
     } else {
         const dim3 grid((unsigned)((rows + PF_BM - 1) / PF_BM), p.hkv, p.b);
         if (bf16) fa_prefill_sm100_kernel<true><<<grid, PF_THREADS, PF_SMEM, stream>>>(p);
