@@ -33,6 +33,7 @@ struct QuantParams {
     QuantSideParams side[2];
     uint32_t nb, nh, nt, d;
     int32_t src_dtype;
+    uint32_t nt_mul, nt_shr, nh_mul, nh_shr;  // fastdiv invariants of nt and nh (rows128 kernel)
 };
 
 __device__ __forceinline__ float warp_max(float v) {
@@ -222,14 +223,16 @@ __global__ void __launch_bounds__(QW * 32) quant_rows_kernel(const QuantParams p
 }
 
 // ---------------------------------------------------------------------------------------------
-// Rows of 128 elements in the block-scaled formats. Lane l owns elements 4 l .. 4 l + 3 (one 8- or 16-byte load), so a
-// scale block is 4 (NVFP4) or 8 (MX) neighbouring lanes, the block arithmetic runs once per lane instead of once per
-// element register, and a lane's codes are already the 16 or 32 bits of the row that it stores. The codes come from the
-// hardware conversions (cvt.rn.satfinite.e2m1x2 / e4m3x2: round to nearest even, saturating), which agree with the integer
-// codecs of common.cuh on every input that is not a NaN; NaN inputs get those codecs' codes explicitly. Maxima do not
-// depend on the order of the reduction, every division is IEEE, so rows are bit-identical to quant_rows_kernel's.
+// Rows of 128 elements in the block-scaled formats. Eight lanes share a row (four rows per warp): lane l of the eight owns
+// elements 16 l .. 16 l + 15 (two or four 16-byte loads), which is exactly one NVFP4 scale block and half an MX block, so the
+// block arithmetic runs once per 16 elements, the row maximum is three shuffles, and a lane's codes are already the 8 or
+// 16 bytes of the row that it stores. The codes come from the hardware conversions (cvt.rn.satfinite.e2m1x2 /
+// e4m3x2: round to nearest even, saturating), which agree with the integer codecs of common.cuh on every input that is
+// not a NaN; a lane that holds a NaN or an infinity (the only sources of a NaN quotient) gives NaNs those codecs' codes
+// explicitly. Maxima do not depend on the order of the reduction, every division is IEEE, so rows are bit-identical to
+// quant_rows_kernel's. Row -> (batch entry, head, token) uses multiply-high division by the launch's invariants.
 // ---------------------------------------------------------------------------------------------
-constexpr int Q128_WARPS = 8;
+constexpr int Q128_WARPS = 8, Q128_RPW = 4;  // warps per block, rows per warp
 
 // one value -> its e4m3 code
 __device__ __forceinline__ uint32_t e4m3_hw(float f) {
@@ -238,129 +241,199 @@ __device__ __forceinline__ uint32_t e4m3_hw(float f) {
     d &= 0xffu;
     return f != f ? (((f2u(f) >> 24) & 0x80u) | 0x7fu) : d;
 }
-// two values -> two e4m3 codes (lo in the low byte)
+// two values -> two e4m3 codes (lo in the low byte); FIX: NaNs get the sign of the input and 0x7f
+template <bool FIX>
 __device__ __forceinline__ uint32_t e4m3x2_hw(float lo, float hi) {
     uint32_t d;
     asm("{\n .reg .b16 t;\n cvt.rn.satfinite.e4m3x2.f32 t, %1, %2;\n cvt.u32.u16 %0, t;\n}" : "=r"(d) : "f"(hi), "f"(lo));
-    if (lo != lo) d = (d & 0xff00u) | ((f2u(lo) >> 24) & 0x80u) | 0x7fu;
-    if (hi != hi) d = (d & 0x00ffu) | ((((f2u(hi) >> 24) & 0x80u) | 0x7fu) << 8);
+    if (FIX) {
+        if (lo != lo) d = (d & 0xff00u) | ((f2u(lo) >> 24) & 0x80u) | 0x7fu;
+        if (hi != hi) d = (d & 0x00ffu) | ((((f2u(hi) >> 24) & 0x80u) | 0x7fu) << 8);
+    }
     return d;
 }
-// two values -> one byte of e2m1 codes (lo in the low nibble); a NaN keeps its sign and gets magnitude 0
+// two values -> one byte of e2m1 codes (lo in the low nibble); FIX: a NaN keeps its sign and gets magnitude 0
+template <bool FIX>
 __device__ __forceinline__ uint32_t fp4x2_hw(float lo, float hi) {
-    lo = lo != lo ? u2f(f2u(lo) & 0x80000000u) : lo;
-    hi = hi != hi ? u2f(f2u(hi) & 0x80000000u) : hi;
+    if (FIX) {
+        lo = lo != lo ? u2f(f2u(lo) & 0x80000000u) : lo;
+        hi = hi != hi ? u2f(f2u(hi) & 0x80000000u) : hi;
+    }
     uint32_t d;
     asm("{\n .reg .b8 t;\n cvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n cvt.u32.u8 %0, t;\n}" : "=r"(d) : "f"(hi), "f"(lo));
     return d;
 }
-__device__ __forceinline__ uint32_t fp4x4_div(const float (&x)[4], float s) {
-    return fp4x2_hw(__fdiv_rn(x[0], s), __fdiv_rn(x[1], s)) | (fp4x2_hw(__fdiv_rn(x[2], s), __fdiv_rn(x[3], s)) << 8);
+// the lane's 16 elements divided by s -> 16 e2m1 codes (two words)
+template <bool FIX>
+__device__ __forceinline__ void fp4x16_div(const float (&x)[16], float s, uint32_t (&w)[2]) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint32_t v = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v |= fp4x2_hw<FIX>(__fdiv_rn(x[8 * h + 2 * i], s), __fdiv_rn(x[8 * h + 2 * i + 1], s)) << (8 * i);
+        w[h] = v;
+    }
 }
-__device__ __forceinline__ uint32_t e4m3x4_div(const float (&x)[4], float s) {
-    return e4m3x2_hw(__fdiv_rn(x[0], s), __fdiv_rn(x[1], s)) | (e4m3x2_hw(__fdiv_rn(x[2], s), __fdiv_rn(x[3], s)) << 16);
+// ... -> 16 e4m3 codes (four words)
+template <bool FIX>
+__device__ __forceinline__ void e4m3x16_div(const float (&x)[16], float s, uint32_t (&w)[4]) {
+#pragma unroll
+    for (int h = 0; h < 4; ++h)
+        w[h] = e4m3x2_hw<FIX>(__fdiv_rn(x[4 * h], s), __fdiv_rn(x[4 * h + 1], s)) |
+               (e4m3x2_hw<FIX>(__fdiv_rn(x[4 * h + 2], s), __fdiv_rn(x[4 * h + 3], s)) << 16);
 }
 
 template <int DT>
-__device__ __forceinline__ void load4(const char *src, int lane, float (&x)[4]) {
+__device__ __forceinline__ void load16(const char *src, int l8, float (&x)[16]) {
     if (DT == B200_F32) {
-        const float4 v = __ldg(reinterpret_cast<const float4 *>(src) + lane);
-        x[0] = v.x, x[1] = v.y, x[2] = v.z, x[3] = v.w;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(src) + 4 * l8 + q);
+            x[4 * q] = v.x, x[4 * q + 1] = v.y, x[4 * q + 2] = v.z, x[4 * q + 3] = v.w;
+        }
     } else {
-        const uint2 v = __ldg(reinterpret_cast<const uint2 *>(src) + lane);
-        if (DT == B200_BF16) {
-            x[0] = u2f(v.x << 16), x[1] = u2f(v.x & 0xffff0000u), x[2] = u2f(v.y << 16), x[3] = u2f(v.y & 0xffff0000u);
-        } else {
-            x[0] = f16_bits_to_f((uint16_t)v.x), x[1] = f16_bits_to_f((uint16_t)(v.x >> 16));
-            x[2] = f16_bits_to_f((uint16_t)v.y), x[3] = f16_bits_to_f((uint16_t)(v.y >> 16));
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(src) + 2 * l8 + q);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (DT == B200_BF16) {
+                    x[8 * q + 2 * i] = u2f(w[i] << 16);
+                    x[8 * q + 2 * i + 1] = u2f(w[i] & 0xffff0000u);
+                } else {
+                    x[8 * q + 2 * i] = f16_bits_to_f((uint16_t)w[i]);
+                    x[8 * q + 2 * i + 1] = f16_bits_to_f((uint16_t)(w[i] >> 16));
+                }
+            }
         }
     }
 }
 
+// n / d for n < 2^31 with the invariants of fastdiv_init
+__device__ __forceinline__ uint32_t fastdiv(uint32_t n, uint32_t mul, uint32_t shr) { return (__umulhi(n, mul) + n) >> shr; }
+
 template <int DT>
 __global__ void __launch_bounds__(Q128_WARPS * 32) quant_rows128_kernel(const QuantParams p) {
     const QuantSideParams &sp = p.side[blockIdx.y];
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, l8 = lane & 7;
     const uint32_t rows = p.nb * p.nh * p.nt;
     const uint32_t mode = sp.mode;
-    for (uint32_t row = blockIdx.x * Q128_WARPS + (threadIdx.x >> 5); row < rows; row += gridDim.x * Q128_WARPS) {
-        const uint32_t bh = row / p.nt, t = row - bh * p.nt, b = bh / p.nh, h = bh - b * p.nh;
+    for (uint32_t base = (blockIdx.x * Q128_WARPS + (threadIdx.x >> 5)) * Q128_RPW; base < rows; base += gridDim.x * Q128_WARPS * Q128_RPW) {
+        const bool live = base + (lane >> 3) < rows;  // a row past the end repeats the last one and stores nothing
+        const uint32_t row = live ? base + (lane >> 3) : rows - 1;
+        const uint32_t bh = fastdiv(row, p.nt_mul, p.nt_shr), t = row - bh * p.nt, b = fastdiv(bh, p.nh_mul, p.nh_shr), h = bh - b * p.nh;
         const char *src = reinterpret_cast<const char *>(sp.src) + (b * sp.s_b + h * sp.s_h + t * sp.s_t) * (uint64_t)dtype_size(DT);
         const int64_t pos = (sp.pos ? sp.pos[b] : sp.pos0) + (int64_t)t;
         uint32_t *orow = sp.dst + b * sp.c_b + h * sp.c_h + (uint64_t)pos * sp.c_t;
-        float x[4];
-        load4<DT>(src, lane, x);
+        float x[16];
+        load16<DT>(src, l8, x);
 
         if (sp.rot == B200_ROT_HADAMARD) {
-            // element index bits 0-1 across the registers, bits 2-6 across the lanes: the butterflies run in the same
+            // element index bits 0-3 across the registers, bits 4-6 across the lanes: the butterflies run in the same
             // order (bit 0 first) as in quant_rows_kernel
-            const float4 sg = __ldg(reinterpret_cast<const float4 *>(sp.signs) + lane);
-            x[0] *= sg.x, x[1] *= sg.y, x[2] *= sg.z, x[3] *= sg.w;
-            {
-                const float a0 = x[0], c0 = x[1], a1 = x[2], c1 = x[3];
-                x[0] = a0 + c0, x[1] = a0 - c0, x[2] = a1 + c1, x[3] = a1 - c1;
-            }
-            {
-                const float a0 = x[0], c0 = x[2], a1 = x[1], c1 = x[3];
-                x[0] = a0 + c0, x[2] = a0 - c0, x[1] = a1 + c1, x[3] = a1 - c1;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 sg = __ldg(reinterpret_cast<const float4 *>(sp.signs) + 4 * l8 + q);
+                x[4 * q] *= sg.x, x[4 * q + 1] *= sg.y, x[4 * q + 2] *= sg.z, x[4 * q + 3] *= sg.w;
             }
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
+            for (int o = 1; o < 16; o <<= 1) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
+                for (int k = 0; k < 16; ++k) {
+                    if (!(k & o)) {
+                        const float a = x[k], c = x[k | o];
+                        x[k] = a + c;
+                        x[k | o] = a - c;
+                    }
+                }
+            }
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) {
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
                     const float y = __shfl_xor_sync(0xffffffffu, x[k], o);
                     x[k] = (lane & o) ? y - x[k] : x[k] + y;
                 }
             }
             const float s = 1.0f / sqrtf(128.0f);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) x[k] *= s;
+            for (int k = 0; k < 16; ++k) x[k] *= s;
         }
 
-        // the lane's maximum; a NaN survives only if all four are NaNs (fmaxf drops a NaN operand)
-        float bm = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+        // the lane's maximum; a NaN survives only if all sixteen are NaNs (fmaxf drops a NaN operand). z is a NaN when
+        // the lane holds a NaN or an infinity.
+        float bm = fabsf(x[0]), z = x[0] * 0.0f;
+#pragma unroll
+        for (int k = 1; k < 16; ++k) {
+            bm = fmaxf(bm, fabsf(x[k]));
+            z = fmaf(x[k], 0.0f, z);
+        }
+        const bool special = z != z;
         float rsc0 = 1.0f;
         uint32_t cw;  // words of codes before the scales
         if (mode == B200_NVFP4) {
             cw = 16;
-            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
-            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));  // block of 16 = lanes 4 q .. 4 q + 3
             float am = fmaxf(0.0f, bm);
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
             am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 4));
-            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 8));
-            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 16));
             const float g = am > 0.0f ? __fdiv_rn(am, 2688.0f) : 1.0f;
             rsc0 = g;
-            const uint32_t scode = e4m3_hw(__fdiv_rn(__fdiv_rn(bm, 6.0f), g));
+            const uint32_t scode = e4m3_hw(__fdiv_rn(__fdiv_rn(bm, 6.0f), g));  // the lane's 16 elements are one scale block
             const float eff = __fmul_rn(e4m3_to_f(scode), g);
-            const uint32_t c16 = eff > 0.0f ? fp4x4_div(x, eff) : 0u;
-            reinterpret_cast<uint16_t *>(orow)[lane] = (uint16_t)c16;
-            if ((lane & 3) == 0) reinterpret_cast<uint8_t *>(orow + 16)[lane >> 2] = (uint8_t)scode;
+            uint32_t w[2] = {0u, 0u};
+            if (eff > 0.0f) {
+                if (special) fp4x16_div<true>(x, eff, w);
+                else fp4x16_div<false>(x, eff, w);
+            }
+            if (live) {
+                *reinterpret_cast<uint2 *>(orow + 2 * l8) = make_uint2(w[0], w[1]);
+                reinterpret_cast<uint8_t *>(orow + 16)[l8] = (uint8_t)scode;
+            }
         } else if (mode == B200_FP8) {
             cw = 32;
             float am = fmaxf(0.0f, bm);
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 4));
             const float s = am > 0.0f ? __fdiv_rn(am, 448.0f) : 1.0f;
             rsc0 = s;
-            orow[lane] = e4m3x4_div(x, s);
+            uint32_t w[4];
+            if (special) e4m3x16_div<true>(x, s, w);
+            else e4m3x16_div<false>(x, s, w);
+            if (live) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) orow[4 * l8 + i] = w[i];
+            }
         } else {
-            // MXFP4 / MXFP8: block of 32 = lanes 8 q .. 8 q + 7
+            // MXFP4 / MXFP8: a block of 32 = two neighbouring lanes
             bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
-            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
-            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
             const uint32_t code = mx_scale_code(bm, mode == B200_MXFP4 ? 2 : 8);
             const float s = e8m0_to_f(code);
             if (mode == B200_MXFP4) {
                 cw = 16;
-                reinterpret_cast<uint16_t *>(orow)[lane] = (uint16_t)(code == 0 ? 0u : fp4x4_div(x, s));
+                uint32_t w[2] = {0u, 0u};
+                if (code != 0) {
+                    if (special) fp4x16_div<true>(x, s, w);
+                    else fp4x16_div<false>(x, s, w);
+                }
+                if (live) orow[2 * l8] = w[0], orow[2 * l8 + 1] = w[1];  // rows of 19 words: 4-byte alignment only
             } else {
                 cw = 32;
-                orow[lane] = code == 0 ? 0u : e4m3x4_div(x, s);
+                uint32_t w[4] = {0u, 0u, 0u, 0u};
+                if (code != 0) {
+                    if (special) e4m3x16_div<true>(x, s, w);
+                    else e4m3x16_div<false>(x, s, w);
+                }
+                if (live) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) orow[4 * l8 + i] = w[i];
+                }
             }
-            if ((lane & 7) == 0) reinterpret_cast<uint8_t *>(orow + cw)[lane >> 3] = (uint8_t)code;
+            if (live && (l8 & 1) == 0) reinterpret_cast<uint8_t *>(orow + cw)[l8 >> 1] = (uint8_t)code;
         }
-        if (lane < 2) orow[cw + (uint32_t)sp.aux_words + lane] = lane ? 0u : f2u(rsc0);
+        if (live && l8 < 2) orow[cw + (uint32_t)sp.aux_words + l8] = l8 ? 0u : f2u(rsc0);
     }
 }
 
@@ -455,16 +528,26 @@ static int fill_side(QuantSideParams &sp, const B200QuantSide &q, uint32_t d) {
     return B200_OK;
 }
 
-// rows of 128 block-scaled elements whose source rows can be read as vectors
+// n / d == (umulhi(n, mul) + n) >> shr for every n < 2^31: mul = ceil(2^(32 + shr) / d) - 2^32, shr = ceil(log2 d)
+static void fastdiv_init(uint32_t d, uint32_t &mul, uint32_t &shr) {
+    shr = 0;
+    while ((1ull << shr) < d) ++shr;
+    const unsigned __int128 one = 1;
+    mul = (uint32_t)((((one << (32 + shr)) + d - 1) / d) - (one << 32));
+}
+
+// rows of 128 block-scaled elements whose source rows can be read as 16-byte vectors
 static bool rows128_takes(const QuantParams &p, int sides) {
     static const bool off = getenv("B200_QUANT_GENERIC") != nullptr;
-    if (off || p.d != 128 || (uint64_t)p.nb * p.nh * p.nt >= 0x80000000ull) return false;
-    const uint64_t vec = p.src_dtype == B200_F32 ? 16 : 8;
+    if (off || p.d != 128 || (uint64_t)p.nb * p.nh * p.nt >= 0x7fffff00ull) return false;
+    const uint64_t vec = p.src_dtype == B200_F32 ? 3 : 7;  // elements per 16 bytes - 1
     for (int s = 0; s < sides; ++s) {
         const QuantSideParams &sp = p.side[s];
         if (sp.mode != B200_MXFP4 && sp.mode != B200_NVFP4 && sp.mode != B200_MXFP8 && sp.mode != B200_FP8) return false;
-        if (((uintptr_t)sp.src % vec) || (sp.s_b & 3) || (sp.s_h & 3) || (sp.s_t & 3)) return false;
+        if (((uintptr_t)sp.src & 15) || (sp.s_b & vec) || (sp.s_h & vec) || (sp.s_t & vec)) return false;
         if (sp.rot == B200_ROT_HADAMARD && ((uintptr_t)sp.signs & 15)) return false;
+        // NVFP4 code words are stored in pairs
+        if (sp.mode == B200_NVFP4 && (((uintptr_t)sp.dst & 7) || (sp.c_b & 1) || (sp.c_h & 1) || (sp.c_t & 1))) return false;
     }
     return true;
 }
@@ -473,10 +556,22 @@ static int launch_quant(const QuantParams &p, int sides, cudaStream_t stream) {
     const uint64_t rows = (uint64_t)p.nb * p.nh * p.nt;
     if (rows == 0) return B200_OK;
     if (rows128_takes(p, sides)) {
-        const dim3 grid((unsigned)std::min<uint64_t>((rows + Q128_WARPS - 1) / Q128_WARPS, 148ull * 4), sides), block(Q128_WARPS * 32);
-        if (p.src_dtype == B200_F32) quant_rows128_kernel<B200_F32><<<grid, block, 0, stream>>>(p);
-        else if (p.src_dtype == B200_F16) quant_rows128_kernel<B200_F16><<<grid, block, 0, stream>>>(p);
-        else quant_rows128_kernel<B200_BF16><<<grid, block, 0, stream>>>(p);
+        QuantParams q = p;
+        fastdiv_init(p.nt, q.nt_mul, q.nt_shr);
+        fastdiv_init(p.nh, q.nh_mul, q.nh_shr);
+        const uint64_t per_block = Q128_WARPS * Q128_RPW;
+        // as many blocks as are resident at once, shared by the sides
+        static const int resident = [] {
+            int per_sm = 4, sms = 148, dev = 0;
+            cudaGetDevice(&dev);
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_rows128_kernel<B200_BF16>, Q128_WARPS * 32, 0);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            return std::max(per_sm, 1) * std::max(sms, 1);
+        }();
+        const dim3 grid((unsigned)std::min<uint64_t>((rows + per_block - 1) / per_block, (uint64_t)std::max(resident / sides, 1)), sides), block(Q128_WARPS * 32);
+        if (p.src_dtype == B200_F32) quant_rows128_kernel<B200_F32><<<grid, block, 0, stream>>>(q);
+        else if (p.src_dtype == B200_F16) quant_rows128_kernel<B200_F16><<<grid, block, 0, stream>>>(q);
+        else quant_rows128_kernel<B200_BF16><<<grid, block, 0, stream>>>(q);
         return check_launch("tq_quantize");
     }
     const unsigned gx = (unsigned)std::min<uint64_t>((rows + QW - 1) / QW, 148ull * 64);
