@@ -216,6 +216,51 @@ __global__ void __launch_bounds__(32) tq_gather_publish_kernel(uint32_t *const *
     }
 }
 
+// Paged rows -> dense rows: block (page, batch entry * kv heads + kv head) copies the valid rows of its page behind the
+// rows of the pages before it, into slabs of `cap` rows per (batch entry, kv head). Block (0, 0) also writes the total
+// number of keys (at most lk) once per batch entry: the attention that follows reads its lengths from there, so a
+// table whose rows do not add up to lk cannot make it read rows that were never written.
+__global__ void __launch_bounds__(256) tq_gather_pages_kernel(const B200Page *__restrict__ pages, uint32_t n_pages, uint32_t nb, uint32_t lk,
+                                                               uint32_t cap, uint32_t kw, uint32_t vw, uint32_t *__restrict__ k_dst,
+                                                               uint32_t *__restrict__ v_dst, int32_t *__restrict__ kv_len) {
+    __shared__ uint32_t red[256];
+    const uint32_t pg = blockIdx.x, bh = blockIdx.y, tid = threadIdx.x;
+    const bool totals = pg == 0 && bh == 0;
+    uint32_t acc = 0;
+    for (uint32_t i = tid; i < pg; i += 256) acc += pages[i].rows;
+    // rows before this page; block (0, 0) needs the sum over all pages too
+    uint32_t all = 0;
+    if (totals)
+        for (uint32_t i = tid; i < n_pages; i += 256) all += pages[i].rows;
+    __syncthreads();
+    red[tid] = acc;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (tid < o) red[tid] += red[tid + o];
+        __syncthreads();
+    }
+    const uint32_t start = red[0];
+    __syncthreads();
+    if (totals) {
+        red[tid] = all;
+        __syncthreads();
+        for (int o = 128; o > 0; o >>= 1) {
+            if (tid < o) red[tid] += red[tid + o];
+            __syncthreads();
+        }
+        const uint32_t total = min(red[0], lk);
+        for (uint32_t i = tid; i < nb; i += 256) kv_len[i] = (int32_t)total;
+    }
+    const B200Page pgd = pages[pg];
+    if (start >= lk) return;
+    const uint32_t rows = min(pgd.rows, lk - start);
+    const uint32_t *ks = reinterpret_cast<const uint32_t *>(pgd.k) + (size_t)bh * pgd.k_cap * kw;
+    const uint32_t *vs = reinterpret_cast<const uint32_t *>(pgd.v) + (size_t)bh * pgd.v_cap * vw;
+    uint32_t *kd = k_dst + ((size_t)bh * cap + start) * kw, *vd = v_dst + ((size_t)bh * cap + start) * vw;
+    for (uint32_t w = tid; w < rows * kw; w += 256) kd[w] = ks[w];
+    for (uint32_t w = tid; w < rows * vw; w += 256) vd[w] = vs[w];
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -226,7 +271,51 @@ int tq_generic_launch(const B200TqAttnArgs *a, cudaStream_t stream);
 bool tq_generic_takes(const B200TqAttnArgs *a);
 }  // namespace b200
 
+// A paged call that the tensor-core kernel can serve once the blocks are compacted: the dense twin of the call (rows in
+// the workspace, lengths from device memory), the bytes of the compacted rows and the whole workspace need. False when
+// the shape belongs to the general kernel anyway.
+struct PagedFast {
+    B200TqAttnArgs dense;
+    size_t k_bytes, v_bytes, len_bytes, gather_bytes, need;
+    uint32_t cap, kw, vw;
+};
+static bool paged_fast_plan(const B200TqAttnArgs *a, PagedFast &f) {
+    static const bool off = getenv("B200_PAGED_IN_PLACE") != nullptr;
+    if (off || !a || !a->pages || a->n_pages == 0 || a->kv_len_dev || a->lk == 0 || a->b == 0 || a->hkv == 0) return false;
+    B200RowLayout kl, vl;
+    if (b200_row_layout(a->kq.mode, a->kq.bits, (int)a->d, &kl) || b200_row_layout(a->vq.mode, a->vq.bits, (int)a->d, &vl)) return false;
+    f.kw = (uint32_t)kl.row_words;
+    f.vw = (uint32_t)vl.row_words;
+    f.cap = a->lk + 1;  // one spare row per slab: the 16-byte round up of the last tile's copy stays inside the slab
+    const size_t slabs = (size_t)a->b * a->hkv;
+    auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+    f.k_bytes = up(slabs * f.cap * f.kw * 4);
+    f.v_bytes = up(slabs * f.cap * f.vw * 4);
+    f.len_bytes = up((size_t)a->b * 4);
+    f.gather_bytes = f.k_bytes + f.v_bytes + f.len_bytes;
+    f.dense = *a;
+    f.dense.pages = nullptr;
+    f.dense.n_pages = 0;
+    f.dense.k_rows = f.dense.v_rows = reinterpret_cast<const uint32_t *>(a->q);  // placeholders, set at launch
+    f.dense.k_strides[0] = (uint64_t)a->hkv * f.cap * f.kw, f.dense.k_strides[1] = (uint64_t)f.cap * f.kw, f.dense.k_strides[2] = f.kw;
+    f.dense.v_strides[0] = (uint64_t)a->hkv * f.cap * f.vw, f.dense.v_strides[1] = (uint64_t)f.cap * f.vw, f.dense.v_strides[2] = f.vw;
+    f.dense.kv_len_dev = reinterpret_cast<const int32_t *>(a->q);
+    f.dense.workspace = nullptr;
+    f.dense.workspace_bytes = 0;
+    if (tq_generic_takes(&f.dense)) return false;
+    DecodePlan pl;
+    if (make_plan(&f.dense, pl)) return false;
+    f.need = f.gather_bytes + pl.ws_bytes;
+    return true;
+}
+
 extern "C" size_t b200_tq_attention_workspace_bytes(const B200TqAttnArgs *a) {
+    {
+        // paged rows: with this much workspace the blocks are compacted into it and the tensor-core kernel runs; with
+        // less (16 bytes are enough) the general kernel reads the blocks in place
+        PagedFast f;
+        if (paged_fast_plan(a, f)) return f.need;
+    }
     if (tq_generic_takes(a)) return 16;  // the general kernel needs no scratch; 0 is reserved for "cannot be planned"
     DecodePlan pl;
     if (make_plan(a, pl)) return 0;
@@ -237,6 +326,26 @@ extern "C" size_t b200_tq_attention_workspace_bytes(const B200TqAttnArgs *a) {
 static thread_local const B200PeerGather *tl_gather = nullptr;
 
 extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_) {
+    {
+        PagedFast f;
+        if (paged_fast_plan(a, f) && a->workspace && a->workspace_bytes >= f.need && !(reinterpret_cast<uintptr_t>(a->workspace) & 255) &&
+            (uint64_t)a->b * a->hq * a->lq != 0 && a->q && a->out) {
+            char *ws = reinterpret_cast<char *>(a->workspace);
+            uint32_t *kd = reinterpret_cast<uint32_t *>(ws), *vd = reinterpret_cast<uint32_t *>(ws + f.k_bytes);
+            int32_t *len = reinterpret_cast<int32_t *>(ws + f.k_bytes + f.v_bytes);
+            const dim3 grid(a->n_pages, a->b * a->hkv);
+            if (grid.y > 65535u) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: too many (batch, kv head) slabs for the page gather");
+            tq_gather_pages_kernel<<<grid, 256, 0, (cudaStream_t)stream_>>>(a->pages, a->n_pages, a->b, a->lk, f.cap, f.kw, f.vw, kd, vd, len);
+            const int rc = check_launch("tq_gather_pages");
+            if (rc) return rc;
+            f.dense.k_rows = kd;
+            f.dense.v_rows = vd;
+            f.dense.kv_len_dev = len;
+            f.dense.workspace = ws + f.gather_bytes;
+            f.dense.workspace_bytes = a->workspace_bytes - f.gather_bytes;
+            return b200_tq_attention(&f.dense, stream_);
+        }
+    }
     if (tq_generic_takes(a)) {
         if (tl_gather) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention_gather: not available for shapes of the general kernel");
         return tq_generic_launch(a, (cudaStream_t)stream_);
@@ -333,7 +442,9 @@ extern "C" int b200_tq_attention_static(const B200TqAttnArgs *a, b200_stream_t s
     B200TqAttnArgs args = *a;
     args.workspace = nullptr;
     args.workspace_bytes = 0;
-    const size_t need = b200_tq_attention_workspace_bytes(&args);
+    size_t need = b200_tq_attention_workspace_bytes(&args);
+    const bool in_place = args.pages != nullptr && need > (size_t)B200_STATIC_SCRATCH_BYTES;  // too large to compact: read in place
+    if (in_place) need = 16;
     if (need > (size_t)B200_STATIC_SCRATCH_BYTES)
         return set_error(B200_ERR_WORKSPACE,
                          "tq_attention_static: this call needs %zu bytes of scratch, the built-in buffer holds %zu; use "
@@ -354,6 +465,6 @@ extern "C" int b200_tq_attention_static(const B200TqAttnArgs *a, b200_stream_t s
         }
         args.workspace = g_static_scratch_ptr[dev];
     }
-    args.workspace_bytes = (size_t)B200_STATIC_SCRATCH_BYTES;
+    args.workspace_bytes = in_place ? (size_t)16 : (size_t)B200_STATIC_SCRATCH_BYTES;
     return b200_tq_attention(&args, stream);
 }

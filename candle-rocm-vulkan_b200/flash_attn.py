@@ -166,6 +166,88 @@ def flash_attn_varlen_alibi(q, k, v, alibi_slopes, seqlens_q, seqlens_k, max_seq
     return flash_attn_varlen_with_config(q, k, v, seqlens_q, seqlens_k, max_seqlen_q, max_seqlen_k, cfg.causal() if causal else cfg)
 
 
+def _check_blocks(blocks, batch: int, what: str):
+    """Shapes of paged blocks against (batch, kv_heads, _, row) of the first one; returns (kv_heads, total rows)
+    (candle-nn/src/flash_attn.rs:650-689)."""
+    if len(blocks) == 0:
+        raise ValueError(f"{what}: no blocks")
+    _, hkv, _, kw = blocks[0].k.shape
+    vw = blocks[0].v.shape[3]
+    lk = 0
+    for i, blk in enumerate(blocks):
+        bk, hk, ck, wk = blk.k.shape
+        bv, hv, cv, wv = blk.v.shape
+        if bk != batch or bv != batch or hk != hkv or hv != hkv or wk != kw or wv != vw:
+            raise ValueError(f"{what}: block {i} k {tuple(blk.k.shape)} / v {tuple(blk.v.shape)} do not match batch {batch}, "
+                             f"{hkv} kv heads, rows of {kw} / {vw}")
+        if blk.rows > ck or blk.rows > cv:
+            raise ValueError(f"{what}: block {i} has {blk.rows} rows but capacities {ck} / {cv}")
+        if blk.k.dtype != blocks[0].k.dtype or blk.v.dtype != blocks[0].v.dtype:
+            raise ValueError(f"{what}: block {i} has another dtype than block 0")
+        lk += blk.rows
+    if lk == 0:
+        raise ValueError(f"{what}: the blocks hold no keys")
+    return hkv, lk
+
+
+def flash_attn_blocks(q, blocks, cfg: FlashAttnConfig) -> torch.Tensor:
+    """Attention of `q: (batch, q_heads, seq_q, head_dim)` over the dense K / V of paged cache blocks (`KvBlockRef` with
+    (batch, kv_heads, capacity, head_dim) tensors of which the first `rows` positions are valid); masks, soft-capping
+    and ALiBi are bottom-right aligned over the concatenated keys; output (batch, q_heads, seq_q, head_dim) in the query
+    dtype (candle-nn/src/flash_attn.rs:691-727). The valid rows are concatenated on the device and the call runs
+    `flash_attn_bhsd`: the path the reference takes for every call that its in-place row kernel does not serve (more
+    than 4 query tokens, more than 128 blocks, other layouts), with the same results up to the summation order."""
+    if q.dim() != 4:
+        raise ValueError(f"flash-attn blocks: q must be (batch, q_heads, seq_q, head_dim), got {tuple(q.shape)}")
+    b, _, _, d = q.shape
+    _check_blocks(blocks, b, "flash-attn blocks")
+    if blocks[0].k.shape[3] != d or blocks[0].v.shape[3] != d:
+        raise ValueError(f"flash-attn blocks: k {tuple(blocks[0].k.shape)} / v {tuple(blocks[0].v.shape)} do not match the head dim {d} of q")
+    live = [blk for blk in blocks if blk.rows > 0]
+    if len(live) == 1:
+        k, v = live[0].k[:, :, : live[0].rows], live[0].v[:, :, : live[0].rows]
+    else:
+        k = torch.cat([blk.k[:, :, : blk.rows].to(q.device) for blk in live], dim=2)
+        v = torch.cat([blk.v[:, :, : blk.rows].to(q.device) for blk in live], dim=2)
+    return flash_attn_bhsd(q, k, v, cfg)
+
+
+def flash_attn_varlen_paged_windowed(q, k, v, seqlens_q, seqlens_k, block_table, mm_prefix_ranges, max_seqlen_q: int, max_seqlen_k: int,
+                                     softmax_scale: float, window_size_left: Optional[int], window_size_right: Optional[int],
+                                     page_block_size: int, softcap: Optional[float] = None) -> torch.Tensor:
+    """Variable length attention over a paged KV cache: `k`, `v` are (num_blocks, page_block_size, kv_heads, head_dim) and
+    `block_table` (batch, max_blocks_per_seq) lists the blocks of each sequence; `seqlens_q` / `seqlens_k` are the
+    cumulative lengths of the varlen calls. The pages of every sequence are gathered, then the varlen kernel runs
+    (candle-flash-attn/src/lib.rs:341-420, which gathers on the host sequence by sequence; here one index over all
+    tokens is built on the device). `mm_prefix_ranges` is not supported, as in the reference."""
+    if mm_prefix_ranges is not None:
+        raise ValueError("flash-attn: mm_prefix_ranges is not supported by this implementation")
+    if k.dim() != 4 or v.shape != k.shape:
+        raise ValueError(f"flash-attn: paged k / v must be (num_blocks, page, kv_heads, head_dim), got {tuple(k.shape)} / {tuple(v.shape)}")
+    nblk, page, hkv, d = k.shape
+    if page != page_block_size:
+        raise ValueError(f"flash-attn: k has pages of {page} tokens, page_block_size is {page_block_size}")
+    batch = seqlens_k.numel() - 1
+    if block_table.dim() != 2 or block_table.shape[0] < batch:
+        raise ValueError(f"flash-attn: block_table has {block_table.shape[0] if block_table.dim() == 2 else 0} rows for {batch} sequences")
+    cu = seqlens_k.to(device=k.device, dtype=torch.int64).clamp_min(0)
+    lens = cu[1:] - cu[:-1]
+    total, longest = (int(x) for x in torch.stack([cu[-1], lens.max() if batch > 0 else cu[-1]]).tolist())
+    need = (longest + page - 1) // page
+    if need > block_table.shape[1]:
+        raise ValueError(f"flash-attn: a sequence needs {need} blocks, block_table has {block_table.shape[1]}")
+    pos = torch.arange(total, device=k.device, dtype=torch.int64)
+    seq = torch.searchsorted(cu[1:].contiguous(), pos, right=True)
+    off = pos - cu[seq]
+    blk = block_table.to(device=k.device, dtype=torch.int64)[seq, off // page]
+    rows = blk * page + off % page
+    kf = k.reshape(nblk * page, hkv, d).index_select(0, rows)
+    vf = v.reshape(nblk * page, hkv, d).index_select(0, rows)
+    cfg = FlashAttnConfig(softmax_scale, softcap=softcap if softcap is not None and softcap > 0.0 else None)
+    cfg = cfg.window(window_size_left, window_size_right)
+    return flash_attn_varlen_with_config(q, kf, vf, seqlens_q, seqlens_k, max_seqlen_q, max_seqlen_k, cfg)
+
+
 def flash_attn_fp8(q, k, v, cfg: FlashAttnConfig) -> torch.Tensor:
     """K and V rounded to E4M3 with one scale per tensor (amax / 448), queries kept in their dtype
     (candle-nn/src/flash_attn.rs:867-894, without the optional Hadamard pre-rotation)."""

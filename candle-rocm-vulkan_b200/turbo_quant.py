@@ -375,10 +375,12 @@ class KvBlockRef:
     rows: int
 
 
-def attention_packed_blocks(q: torch.Tensor, blocks, kq: TurboQuantizer, vq: TurboQuantizer, cfg: FlashAttnConfig) -> torch.Tensor:
-    """Attention of `q: (batch, q_heads, seq_q, head_dim)` over packed rows that live in paged cache blocks, read in
-    place through a block table in device memory (candle-nn/src/turbo_quant.rs:1074-1114; no limit of 128 blocks).
-    The keys are the valid rows of the blocks, one block after the other; masks are bottom-right aligned over them."""
+def attention_packed_blocks(q: torch.Tensor, blocks, kq: TurboQuantizer, vq: TurboQuantizer, cfg: FlashAttnConfig, in_place: bool = False) -> torch.Tensor:
+    """Attention of `q: (batch, q_heads, seq_q, head_dim)` over packed rows that live in paged cache blocks, given as
+    a block table in device memory (candle-nn/src/turbo_quant.rs:1074-1114; no limit of 128 blocks). The keys are the
+    valid rows of the blocks, one block after the other; masks are bottom-right aligned over them. Formats and head
+    dims of the tensor-core kernel: the blocks are compacted into the workspace by one copy kernel and that kernel
+    runs; everything else, and `in_place=True`: the general kernel reads the blocks where they are."""
     _need_cuda(q, "q")
     if len(blocks) == 0:
         raise ValueError("turbo-quant blocks: no blocks")
@@ -428,6 +430,13 @@ def attention_packed_blocks(q: torch.Tensor, blocks, kq: TurboQuantizer, vq: Tur
     args.wl, args.wr = wl, wr
     args.alibi, args.alibi_bstride = (alibi.data_ptr() if alibi is not None else None), abs_
     args.workspace, args.workspace_bytes, args.status = None, 0, None
+    # with the workspace the library asks for, the blocks are compacted into it and the tensor-core kernel runs;
+    # `in_place=True` keeps the general kernel that reads the blocks where they are
+    need = 16 if in_place else int(A.lib().b200_tq_attention_workspace_bytes(C.byref(args)))
+    if need == 0:
+        A.check(A.lib().b200_tq_attention(C.byref(args), _stream(q.device)))  # raises with the library's reason
+    ws = _workspace(q.device, need)
+    args.workspace, args.workspace_bytes = ws.data_ptr(), need
     A.check(A.lib().b200_tq_attention(C.byref(args), _stream(q.device)))
     return out
 

@@ -218,6 +218,9 @@ typedef struct B200TqAttnArgs {
     size_t workspace_bytes;
     int32_t *status;                       /* optional device word, set non-zero if a device wait ran out */
 } B200TqAttnArgs;
+/* Paged calls (pages != NULL): the size returned covers a compacted copy of all valid rows; with that much workspace
+ * (256-byte aligned) one copy kernel gathers the blocks and the tensor-core kernel runs, with less (16 bytes are
+ * enough) the general kernel reads the blocks in place. lk is an upper bound of the sum of the blocks' rows. */
 size_t b200_tq_attention_workspace_bytes(const B200TqAttnArgs *args);
 int b200_tq_attention(const B200TqAttnArgs *args, b200_stream_t stream);
 

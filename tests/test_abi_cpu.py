@@ -99,6 +99,36 @@ def test_argument_errors_without_gpu(pkg):
     assert lib.b200_tq_attention_workspace_bytes(C.byref(args)) == 0
 
 
+def test_paged_dense_attention_argument_errors_without_gpu(pkg):
+    """The checks of the paged entry points run before anything touches the device (candle-nn/src/flash_attn.rs:650-689,
+    candle-flash-attn/src/lib.rs:357-392)."""
+    import pytest
+    import torch
+    F, Ref = pkg.flash_attn, pkg.KvBlockRef
+    q = torch.zeros((2, 4, 1, 64))
+    kv = lambda b=2, h=2, c=8, d=64: torch.zeros((b, h, c, d))
+    with pytest.raises(ValueError, match="no blocks"):
+        F.flash_attn_blocks(q, [], pkg.FlashAttnConfig(0.1))
+    with pytest.raises(ValueError, match="do not match batch"):
+        F.flash_attn_blocks(q, [Ref(kv(), kv(), 4), Ref(kv(b=3), kv(b=3), 4)], pkg.FlashAttnConfig(0.1))
+    with pytest.raises(ValueError, match="rows but capacities"):
+        F.flash_attn_blocks(q, [Ref(kv(), kv(), 9)], pkg.FlashAttnConfig(0.1))
+    with pytest.raises(ValueError, match="hold no keys"):
+        F.flash_attn_blocks(q, [Ref(kv(), kv(), 0)], pkg.FlashAttnConfig(0.1))
+    with pytest.raises(ValueError, match="head dim"):
+        F.flash_attn_blocks(q, [Ref(kv(d=32), kv(d=32), 4)], pkg.FlashAttnConfig(0.1))
+    with pytest.raises(RuntimeError, match="CUDA"):  # valid blocks: the call reaches the device check
+        F.flash_attn_blocks(q, [Ref(kv(), kv(), 4)], pkg.FlashAttnConfig(0.1))
+    pages = torch.zeros((4, 16, 2, 64))
+    cu = torch.tensor([0, 20], dtype=torch.int32)
+    with pytest.raises(ValueError, match="mm_prefix_ranges"):
+        F.flash_attn_varlen_paged_windowed(q, pages, pages, cu, cu, torch.zeros((1, 2), dtype=torch.int32), cu, 1, 20, 0.1, None, None, 16)
+    with pytest.raises(ValueError, match="needs 2 blocks"):
+        F.flash_attn_varlen_paged_windowed(q, pages, pages, cu, cu, torch.zeros((1, 1), dtype=torch.int32), None, 1, 20, 0.1, None, None, 16)
+    with pytest.raises(ValueError, match="rows for 1 sequences"):
+        F.flash_attn_varlen_paged_windowed(q, pages, pages, cu, cu, torch.zeros((0, 2), dtype=torch.int32), None, 1, 20, 0.1, None, None, 16)
+
+
 def test_product_does_not_import_the_oracle():
     for p in (ROOT / "candle-rocm-vulkan_b200").glob("*.py"):
         assert "oracle" not in p.read_text().replace("no CPU path", ""), p

@@ -445,8 +445,10 @@ def test_paged_blocks_equal_the_concatenated_rows(P, oracle, kf, vf):
         c = P.FlashAttnConfig(d ** -0.5)
         c.window_size_left = None if wl < 0 else wl
         c.window_size_right = None if wr < 0 else wr
-        got = P.attention_packed_blocks(to_dev(q), blocks, kq, vq, c).cpu().numpy()
         want = oracle.tq_attention(q, np.ascontiguousarray(kd), np.ascontiguousarray(vd), lk, kf, vf, d ** -0.5, tab, wl=wl, wr=wr)
-        assert_close(got, want, what=f"paged wl={wl} wr={wr}")
+        # blocks compacted into the workspace for the tensor-core kernel (where the format has one), and read in place
+        for in_place in (False, True):
+            got = P.attention_packed_blocks(to_dev(q), blocks, kq, vq, c, in_place=in_place).cpu().numpy()
+            assert_close(got, want, what=f"paged wl={wl} wr={wr} in_place={in_place}")
     with pytest.raises(ValueError, match="no blocks"):
         P.attention_packed_blocks(to_dev(q), [], kq, vq, c)

@@ -160,6 +160,62 @@ def test_varlen_equals_per_sequence_calls(P):
         assert_close(out[qs].float().cpu().numpy(), one.float().cpu().numpy(), atol=2e-3, what=f"sequence {i}", out="bf16")
 
 
+def test_blocks_match_the_oracle_on_the_concatenated_rows(P, oracle):
+    """Dense K / V in paged blocks (decode of 2 tokens and a chunk of 70): the keys are the valid rows of the blocks in
+    order; capacity rows past `rows` hold garbage that must not be read."""
+    b, hq, hkv, d = 2, 8, 2, 128
+    rows = [37, 0, 128, 5]
+    caps = [64, 16, 128, 8]
+    lk = sum(rows)
+    k = oracle.round_to(oracle.normal(11, b * hkv * lk * d).reshape(b, hkv, lk, d), "bf16")
+    v = oracle.round_to(oracle.normal(12, b * hkv * lk * d).reshape(b, hkv, lk, d), "bf16")
+    blocks, at = [], 0
+    for r, c in zip(rows, caps):
+        kb = torch.full((b, hkv, c, d), 1e4, device="cuda:0", dtype=torch.bfloat16)
+        vb = torch.full((b, hkv, c, d), -1e4, device="cuda:0", dtype=torch.bfloat16)
+        kb[:, :, :r] = to_dev(k[:, :, at : at + r], "bf16")
+        vb[:, :, :r] = to_dev(v[:, :, at : at + r], "bf16")
+        blocks.append(P.KvBlockRef(kb, vb, r))
+        at += r
+    for lq in (2, 70):
+        q = oracle.round_to(oracle.normal(13 + lq, b * hq * lq * d).reshape(b, hq, lq, d), "bf16")
+        want = oracle.reference_attention(q.transpose(0, 2, 1, 3), k.transpose(0, 2, 1, 3), v.transpose(0, 2, 1, 3), d ** -0.5, wr=0)
+        got = P.flash_attn.flash_attn_blocks(to_dev(q, "bf16"), blocks, P.FlashAttnConfig(d ** -0.5).causal())
+        torch.cuda.synchronize()
+        assert got.shape == (b, hq, lq, d)
+        assert_close(got.float().cpu().numpy().transpose(0, 2, 1, 3), want, what=f"blocks lq={lq}", out="bf16")
+
+
+def test_paged_varlen_equals_varlen_on_gathered_pages(P):
+    torch.manual_seed(9)
+    hq, hkv, d, page, nblk = 8, 2, 128, 16, 40
+    lens_q, lens_k = [3, 40, 1], [33, 40, 130]
+    cu_q = torch.tensor([0] + list(np.cumsum(lens_q)), dtype=torch.int32, device="cuda:0")
+    cu_k = torch.tensor([0] + list(np.cumsum(lens_k)), dtype=torch.int32, device="cuda:0")
+    kp = torch.randn((nblk, page, hkv, d), device="cuda:0", dtype=torch.float16)
+    vp = torch.randn((nblk, page, hkv, d), device="cuda:0", dtype=torch.float16)
+    perm = torch.randperm(nblk)[: sum((n + page - 1) // page for n in lens_k)].tolist()
+    table = torch.zeros((3, 9), dtype=torch.int32)
+    ks, vs, at = [], [], 0
+    for i, n in enumerate(lens_k):
+        nb = (n + page - 1) // page
+        ids = perm[at : at + nb]
+        at += nb
+        table[i, :nb] = torch.tensor(ids, dtype=torch.int32)
+        ks.append(kp[ids].reshape(nb * page, hkv, d)[:n])
+        vs.append(vp[ids].reshape(nb * page, hkv, d)[:n])
+    q = torch.randn((sum(lens_q), hq, d), device="cuda:0", dtype=torch.float16)
+    F = P.flash_attn
+    got = F.flash_attn_varlen_paged_windowed(q, kp, vp, cu_q, cu_k, table.to("cuda:0"), None, max(lens_q), max(lens_k), d ** -0.5, 64, 0, page)
+    want = F.flash_attn_varlen_windowed(q, torch.cat(ks), torch.cat(vs), cu_q, cu_k, max(lens_q), max(lens_k), d ** -0.5, 64, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    with pytest.raises(ValueError, match="needs 9 blocks"):
+        F.flash_attn_varlen_paged_windowed(q, kp, vp, cu_q, cu_k, table[:, :8].to("cuda:0"), None, 40, 130, 0.1, None, 0, page)
+    with pytest.raises(ValueError, match="page_block_size"):
+        F.flash_attn_varlen_paged_windowed(q, kp, vp, cu_q, cu_k, table.to("cuda:0"), None, 40, 130, 0.1, None, 0, 32)
+
+
 def test_fp8_helper_close_to_bf16_attention(P):
     torch.manual_seed(6)
     q = torch.randn((1, 64, 8, 128), device="cuda:0", dtype=torch.bfloat16)
