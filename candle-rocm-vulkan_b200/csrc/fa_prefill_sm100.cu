@@ -64,7 +64,7 @@ __device__ __forceinline__ uint64_t tc_desc_sw128(uint32_t saddr, uint32_t lbo, 
     d |= 2ull << 61;  // layout type: 128-byte swizzle
     return d;
 }
-// one box of a tiled tensor map -> shared memory, completion counted in bytes on `bar` (no multicast)
+// one box of a tiled tensor map -> shared memory, completion counted in bytes on `bar`; one destination block
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, int c3, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
                  "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
