@@ -609,7 +609,11 @@ def run_prefill(args, rank, world, local_rank):
                     "h2d_bytes_per_step": int(sum(t.numel() for t in sets[0])) * 2, "d2h_bytes_per_step": int(out_host.numel()) * 2},
             "gpu_launches": args.steps * 2,  # the attention kernel and the quantize-on-append kernel (K and V in one grid)
             "roofline": {"bound": "tensor", "kernel": "fa_prefill_sm100_kernel2 (attention alone)", "achieved": flops / (attn_ms * 1e-3) / 1e12,
-                         "peak": peak, "unit": "TFLOP/s", "frac": flops / (attn_ms * 1e-3) / 1e12 / peak, "peak_source": kind, "traffic": None},
+                         "peak": peak, "unit": "TFLOP/s", "frac": flops / (attn_ms * 1e-3) / 1e12 / peak, "peak_source": kind,
+                         # dram read + write of one launch at B = 1 (50.4 + 3.0 MB, part of q / k / v still in L2 from the
+                         # call before), times the 4 batch entries of c3, whose blocks do not share data
+                         "traffic": 4 * 53_400_000, "traffic_unit": "bytes per launch",
+                         "traffic_source": "ncu capture at B=1 scaled by 4, profiles/fa_prefill_sm100_kernel2_b1_s4096.md"},
             "cpu_baseline": cpu, "clocks": clocks}
     print(json.dumps(line), flush=True)
 
