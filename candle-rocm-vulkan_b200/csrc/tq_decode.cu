@@ -216,6 +216,22 @@ __global__ void __launch_bounds__(32) tq_gather_publish_kernel(uint32_t *const *
     }
 }
 
+// n words from src to dst by the 256 threads of a block: 16-byte vectors where both sides sit at the same offset inside
+// a 16-byte line, words at the ragged ends and everywhere else
+__device__ __forceinline__ void copy_words(uint32_t *__restrict__ dst, const uint32_t *__restrict__ src, uint32_t n, uint32_t tid) {
+    const uint32_t ph = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15u);
+    if (ph != (uint32_t)(reinterpret_cast<uintptr_t>(dst) & 15u)) {
+        for (uint32_t w = tid; w < n; w += 256) dst[w] = src[w];
+        return;
+    }
+    const uint32_t head = min(n, ((16u - ph) & 15u) >> 2), body = (n - head) >> 2;
+    if (tid < head) dst[tid] = src[tid];
+    const uint4 *s4 = reinterpret_cast<const uint4 *>(src + head);
+    uint4 *d4 = reinterpret_cast<uint4 *>(dst + head);
+    for (uint32_t i = tid; i < body; i += 256) d4[i] = s4[i];
+    for (uint32_t w = head + 4 * body + tid; w < n; w += 256) dst[w] = src[w];
+}
+
 // Paged rows -> dense rows: block (page, batch entry * kv heads + kv head) copies the valid rows of its page behind the
 // rows of the pages before it, into slabs of `cap` rows per (batch entry, kv head). Block (0, 0) also writes the total
 // number of keys (at most lk) once per batch entry: the attention that follows reads its lengths from there, so a
@@ -257,8 +273,8 @@ __global__ void __launch_bounds__(256) tq_gather_pages_kernel(const B200Page *__
     const uint32_t *ks = reinterpret_cast<const uint32_t *>(pgd.k) + (size_t)bh * pgd.k_cap * kw;
     const uint32_t *vs = reinterpret_cast<const uint32_t *>(pgd.v) + (size_t)bh * pgd.v_cap * vw;
     uint32_t *kd = k_dst + ((size_t)bh * cap + start) * kw, *vd = v_dst + ((size_t)bh * cap + start) * vw;
-    for (uint32_t w = tid; w < rows * kw; w += 256) kd[w] = ks[w];
-    for (uint32_t w = tid; w < rows * vw; w += 256) vd[w] = vs[w];
+    copy_words(kd, ks, rows * kw, tid);
+    copy_words(vd, vs, rows * vw, tid);
 }
 
 }  // namespace b200
@@ -286,7 +302,9 @@ static bool paged_fast_plan(const B200TqAttnArgs *a, PagedFast &f) {
     if (b200_row_layout(a->kq.mode, a->kq.bits, (int)a->d, &kl) || b200_row_layout(a->vq.mode, a->vq.bits, (int)a->d, &vl)) return false;
     f.kw = (uint32_t)kl.row_words;
     f.vw = (uint32_t)vl.row_words;
-    f.cap = a->lk + 1;  // one spare row per slab: the 16-byte round up of the last tile's copy stays inside the slab
+    // at least one spare row per slab (the 16-byte round up of the last tile's copy stays inside the slab), and a
+    // multiple of four rows, so that every slab starts on a 16-byte line
+    f.cap = (a->lk + 4) & ~3u;
     const size_t slabs = (size_t)a->b * a->hkv;
     auto up = [](size_t x) { return (x + 255) / 256 * 256; };
     f.k_bytes = up(slabs * f.cap * f.kw * 4);
