@@ -403,7 +403,12 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
     if (lrc) return lrc;
     {
         const size_t rows = (size_t)a->b * a->hq * a->lq;
-        const unsigned gx = (unsigned)std::max<size_t>(std::min<size_t>(rows, (size_t)sm_count_cached() * 16), 1);
+        // Few segments per row (the workers outnumber the columns by less than eight to one): one warp per row, four
+        // rows per block, a grid that is resident at once (further rows are looped over). Many segments per row: one
+        // block per row, its warps share the segments.
+        const bool per_row = (size_t)pl.blocks * DW < 8 * (size_t)a->b * pl.ny;
+        const unsigned gx = per_row ? (unsigned)std::max<size_t>(std::min<size_t>((rows + 3) / 4, (size_t)sm_count_cached() * 6), 1)
+                                    : (unsigned)std::max<size_t>(std::min<size_t>(rows, (size_t)sm_count_cached() * 16), 1);
         // the combine grid is launched while the decode grid still runs and waits on the device for
         // its completion (programmatic dependent launch): its launch latency is off the critical path
         cudaLaunchConfig_t cfg = {};
@@ -416,7 +421,11 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         cudaError_t e;
-        if (a->d == 64) e = cudaLaunchKernelEx(&cfg, tq_combine_kernel<64>, p);
+        if (per_row) {
+            if (a->d == 64) e = cudaLaunchKernelEx(&cfg, tq_combine_rows_kernel<64>, p);
+            else if (a->d == 128) e = cudaLaunchKernelEx(&cfg, tq_combine_rows_kernel<128>, p);
+            else e = cudaLaunchKernelEx(&cfg, tq_combine_rows_kernel<256>, p);
+        } else if (a->d == 64) e = cudaLaunchKernelEx(&cfg, tq_combine_kernel<64>, p);
         else if (a->d == 128) e = cudaLaunchKernelEx(&cfg, tq_combine_kernel<128>, p);
         else e = cudaLaunchKernelEx(&cfg, tq_combine_kernel<256>, p);
         if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "tq_combine: %s", cudaGetErrorString(e));

@@ -317,14 +317,37 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // ------------------------------------------------------------------ this warp's share of the work
+
     const uint32_t cc = p.col_cost;
     auto batch_cost = [&](uint32_t bb) -> uint32_t {
         const uint32_t t = (uint32_t)make_column(p, bb).tiles;
         return t ? (t + cc) * ny : 0u;
     };
     uint64_t total = 0;
+    // up to 128 ragged entries: one round of loads (four entries per lane) serves the total and the search below
+    const bool few = p.kv_len != nullptr && p.b <= 128;
+    uint32_t fu[4], fincl[4];
+    uint64_t fpre[4];
     if (p.kv_len == nullptr) {
         total = (uint64_t)batch_cost(0) * p.b;
+    } else if (few) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t bb = 32 * k + lane;
+            fu[k] = bb < p.b ? batch_cost(bb) : 0u;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            uint32_t incl = fu[k];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            fincl[k] = incl;
+            fpre[k] = total;
+            total += __shfl_sync(0xffffffffu, incl, 31);
+        }
     } else {
         for (uint32_t base = 0; base < p.b; base += 32) {
             const uint32_t bb = base + lane;
@@ -343,6 +366,18 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
         const uint64_t per_b = batch_cost(0);
         b0 = (uint32_t)(x_begin / per_b);
         b0_start = (uint64_t)b0 * per_b;
+    } else if (few) {
+        bool found = false;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t hit = __ballot_sync(0xffffffffu, fpre[k] + fincl[k] > x_begin);
+            if (hit && !found) {
+                const int l = __ffs(hit) - 1;
+                b0 = 32 * k + l;
+                b0_start = fpre[k] + __shfl_sync(0xffffffffu, fincl[k] - fu[k], l);
+                found = true;
+            }
+        }
     } else {
         uint64_t carry = 0;
         for (uint32_t base = 0; base < p.b; base += 32) {
@@ -635,8 +670,6 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
         }
     };
 
-
-
     bool more = true;
     while (more) {
         // ================================================================ segment set up
@@ -691,11 +724,37 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
             } else {
                 const uint32_t i = p.lq == 1 ? 0u : r / G, h = hk * G + (p.lq == 1 ? r : r % G);
                 const size_t qoff = seg.b * p.q_sb + h * p.q_sh + i * p.q_ss;
+                const bool q16 = p.q_dtype == B200_F16 || p.q_dtype == B200_BF16;
+                if (q16 && r < R && ((reinterpret_cast<uintptr_t>(p.q) + 2 * qoff) & 7u) == 0) {
+                    // 16-bit rows on an 8-byte boundary: the four contraction slots of a k-step in one load, all
+                    // loads of the row issued before the first conversion
+                    const uint16_t *q16p = reinterpret_cast<const uint16_t *>(p.q) + qoff;
+                    uint2 raw[STEPS];
 #pragma unroll
-                for (int s = 0; s < STEPS; ++s) {
-                    const int dbase = KMX ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : c * (HD / 4) + 4 * s;
+                    for (int s = 0; s < STEPS; ++s) {
+                        const int dbase = KMX ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : c * (HD / 4) + 4 * s;
+                        raw[s] = __ldg(reinterpret_cast<const uint2 *>(q16p + dbase));
+                    }
+                    if (p.q_dtype == B200_BF16) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) qv[s][j] = r < R ? load_elem_rt(p.q, qoff + dbase + j, p.q_dtype) : 0.0f;
+                        for (int s = 0; s < STEPS; ++s) {
+                            qv[s][0] = u2f(raw[s].x << 16); qv[s][1] = u2f(raw[s].x & 0xffff0000u);
+                            qv[s][2] = u2f(raw[s].y << 16); qv[s][3] = u2f(raw[s].y & 0xffff0000u);
+                        }
+                    } else {
+#pragma unroll
+                        for (int s = 0; s < STEPS; ++s) {
+                            qv[s][0] = f16_bits_to_f((uint16_t)(raw[s].x & 0xffffu)); qv[s][1] = f16_bits_to_f((uint16_t)(raw[s].x >> 16));
+                            qv[s][2] = f16_bits_to_f((uint16_t)(raw[s].y & 0xffffu)); qv[s][3] = f16_bits_to_f((uint16_t)(raw[s].y >> 16));
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int s = 0; s < STEPS; ++s) {
+                        const int dbase = KMX ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : c * (HD / 4) + 4 * s;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) qv[s][j] = r < R ? load_elem_rt(p.q, qoff + dbase + j, p.q_dtype) : 0.0f;
+                    }
                 }
             }
             float am = 0.0f;
@@ -720,6 +779,7 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                 qb1[s] = pack_f16x2(qv[s][2] * down, qv[s][3] * down);
             }
         }
+
         // running maxima (log2 domain, value scale folded in) and partial normalizers of rows 2c, 2c + 1
         float M[2] = {-1e30f, -1e30f}, lsum[2] = {0.0f, 0.0f};
 #pragma unroll
@@ -747,6 +807,7 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                 }
                 phases ^= 1u << c_stage;
             }
+
             const uint32_t st_s = c_st;
             const int nkeys = min(WK, col.hi - key0);
             if (nkeys < WK) {
@@ -948,6 +1009,7 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                 if (w1) p.part_lse[slot * prow + rr1] = lsum[1] > 0.0f ? M[1] * LN2 + logf(lsum[1]) : -INFINITY;
             }
         }
+
         more = next_segment(seg, p, ny, x_end);
     }
     if (wait_failed && p.status) atomicExch(p.status, 1);
@@ -1066,6 +1128,147 @@ __global__ void __launch_bounds__(128) tq_combine_kernel(const DecodeParams p) {
                 for (int k = 0; k < EPL; ++k) store_elem_rt(p.peer_bufs[pr], g_base + row * HD + lane + 32 * k, rb[lane + 32 * k], p.out_dtype);
         }
         __syncthreads();
+    }
+}
+
+// The same merge for rows with few segments (the host picks it when the workers outnumber the columns by less
+// than eight to one). One warp per output row, four rows per block: lane l owns the elements [l HD/32, (l + 1) HD/32)
+// of the row, so a
+// segment's partial row is one vector load per lane, the loads of the first segments are issued before the
+// weights are known, and no barrier or shared memory sits between the warps. The grid fits on the device at once
+// (rows beyond that are looped over): the blocks are resident, waiting, when the decode grid ends.
+
+// EPL consecutive elements of a row, cast to the output type: one vector store for 16-bit types on an 8-byte boundary
+template <int EPL>
+__device__ __forceinline__ void store_row_piece(void *out, size_t off, const float (&v)[EPL], int dt) {
+    if constexpr (EPL % 4 == 0) {
+        if ((dt == B200_F16 || dt == B200_BF16) && ((reinterpret_cast<uintptr_t>(out) + 2 * off) & 7u) == 0) {
+            uint16_t *o16 = reinterpret_cast<uint16_t *>(out) + off;
+#pragma unroll
+            for (int q = 0; q < EPL / 4; ++q) {
+                uint32_t w[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t lo = dt == B200_F16 ? f_to_f16_bits(v[4 * q + 2 * h]) : f_to_bf16_bits(v[4 * q + 2 * h]);
+                    const uint32_t hi = dt == B200_F16 ? f_to_f16_bits(v[4 * q + 2 * h + 1]) : f_to_bf16_bits(v[4 * q + 2 * h + 1]);
+                    w[h] = lo | (hi << 16);
+                }
+                *reinterpret_cast<uint2 *>(o16 + 4 * q) = make_uint2(w[0], w[1]);
+            }
+            return;
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) store_elem_rt(out, off + k, v[k], dt);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(128) tq_combine_rows_kernel(const DecodeParams p) {
+    constexpr int EPL = HD / 32;  // consecutive elements of a row per lane
+    constexpr int CW = 4;         // warps (rows) per block
+    __shared__ __align__(16) float rot[CW][HD];  // used only when the values were rotated
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t rows = (size_t)p.b * p.hq * p.lq;
+    const uint32_t ny = p.hkv * p.packs;
+    const uint32_t prow = min((uint32_t)PACK, p.rows_per_kv);
+    // launched with programmatic stream serialization: wait here until the decode grid has finished
+    // and its partial results are visible
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // a grid launched as this one's programmatic dependent (the gather's publish step) may be scheduled now; it waits
+    // for this grid's completion itself
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // gathered outputs: this step's number (the same for all blocks: only the publish step that follows this grid
+    // advances it) selects one of the two slots of every rank's buffer
+    const uint32_t g_step = p.world ? *reinterpret_cast<volatile uint32_t *>(p.step) + 1u : 0u;
+    const size_t g_base = p.world ? ((size_t)(g_step & 1u) * p.world + p.rank) * rows * HD : 0;
+    for (size_t row = (size_t)blockIdx.x * CW + warp; row < rows; row += (size_t)gridDim.x * CW) {
+        const uint32_t i = (uint32_t)(row % p.lq);
+        const uint32_t h = (uint32_t)((row / p.lq) % p.hq);
+        const uint32_t b = (uint32_t)(row / ((size_t)p.lq * p.hq));
+        const uint32_t hk = h / p.group, r = i * p.group + h % p.group;
+        const uint32_t y = hk * p.packs + r / PACK, rr = r % PACK;
+        const size_t obase = b * p.o_sb + h * p.o_sh + i * p.o_ss + (size_t)lane * EPL;
+        const size_t col = (size_t)b * ny + y;
+        float acc[EPL];
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) acc[k] = 0.0f;
+        if (make_column(p, b).tiles != 0) {  // otherwise nothing was written for the row: zeros
+            const int2 fm = *reinterpret_cast<const int2 *>(p.meta + 2 * col);
+            const int first = fm.x, ns = fm.y;
+            const size_t slot0 = (size_t)first * prow + rr;
+            const float *po = p.part_o + slot0 * HD + lane * EPL;
+            const size_t seg_stride = (size_t)prow * HD;
+            // the first four segments' rows are requested before the log-sum-exps are looked at
+            float pre[4][EPL];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (j < ns) {
+#pragma unroll
+                    for (int q = 0; q < EPL / 2; ++q) {
+                        const float2 v = *reinterpret_cast<const float2 *>(po + (size_t)j * seg_stride + 2 * q);
+                        pre[j][2 * q] = v.x;
+                        pre[j][2 * q + 1] = v.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < EPL; ++k) pre[j][k] = 0.0f;
+                }
+            }
+            float mx = -INFINITY;
+            for (int s0 = lane; s0 < ns; s0 += 32) mx = fmaxf(mx, p.part_lse[slot0 + (size_t)s0 * prow]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            float wsum = 0.0f;
+            for (int base = 0; base < ns; base += 32) {  // lane l weighs segment base + l
+                const int sl = base + lane;
+                float wl = 0.0f;
+                if (sl < ns) {
+                    const float e = p.part_lse[slot0 + (size_t)sl * prow];
+                    wl = e == -INFINITY ? 0.0f : expf(e - mx);
+                }
+                wsum += wl;
+                const int cnt = min(32, ns - base);
+                int j = 0;
+                if (base == 0) {
+                    // the four rows in registers (segments past the last one weigh nothing)
+#pragma unroll
+                    for (; j < 4; ++j) {
+                        const float w = __shfl_sync(0xffffffffu, wl, j);
+#pragma unroll
+                        for (int k = 0; k < EPL; ++k) acc[k] = fmaf(w, pre[j][k], acc[k]);
+                    }
+                }
+#pragma unroll 4
+                for (; j < cnt; ++j) {
+                    const float w = __shfl_sync(0xffffffffu, wl, j);
+                    const float *src = po + (size_t)(base + j) * seg_stride;
+#pragma unroll
+                    for (int q = 0; q < EPL / 2; ++q) {
+                        const float2 v = *reinterpret_cast<const float2 *>(src + 2 * q);
+                        acc[2 * q] = fmaf(w, v.x, acc[2 * q]);
+                        acc[2 * q + 1] = fmaf(w, v.y, acc[2 * q + 1]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+#pragma unroll
+            for (int k = 0; k < EPL; ++k) acc[k] = wsum > 0.0f ? acc[k] / wsum : 0.0f;
+            if (p.v.rot == B200_ROT_HADAMARD) {
+                float *rb = rot[warp];
+                __syncwarp();
+#pragma unroll
+                for (int k = 0; k < EPL; ++k) rb[lane * EPL + k] = acc[k];
+                __syncwarp();
+                warp_hadamard(rb, HD, p.v.signs, false, lane);
+                __syncwarp();
+#pragma unroll
+                for (int k = 0; k < EPL; ++k) acc[k] = rb[lane * EPL + k];
+            }
+        }
+        store_row_piece<EPL>(p.out, obase, acc, p.out_dtype);
+        // the same row into every rank's gathered buffer: plain stores through the peer mappings
+        for (uint32_t pr = 0; pr < p.world; ++pr) store_row_piece<EPL>(p.peer_bufs[pr], g_base + row * HD + (size_t)lane * EPL, acc, p.out_dtype);
     }
 }
 
