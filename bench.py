@@ -478,7 +478,7 @@ def run_ours(args, w, rank, world, local_rank):
                     "d2h_bytes_per_step": int(out_host.numel()) * 2, "ms_per_step": e2e_ms / args.steps,
                     "tokens_per_s": world * b / (e2e_ms / args.steps * 1e-3)},
             "gpu_launches": args.steps * launches_per_step,
-            "roofline": {"bound": "hbm", "kernel": "tq_decode_kernel (+ tq_combine_kernel in the same timed call)",
+            "roofline": {"bound": "hbm", "kernel": "tq_decode_kernel (+ the combine kernel in the same timed call)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_kind, "traffic": traffic, "traffic_unit": "bytes per launch",
                          "traffic_source": traffic_src},
