@@ -173,6 +173,43 @@ def test_ragged_batch_is_per_sequence_attention(P, oracle):
         assert_close(one, got[bi:bi + 1], atol=1e-2, rtol=8e-3, what=f"sequence {bi}")  # one bf16 ulp
 
 
+@pytest.mark.parametrize("d,qdt", [(64, "f16"), (128, "bf16"), (128, "f32"), (256, "bf16")])
+def test_many_short_columns_take_the_row_per_warp_combine(P, oracle, d, qdt):
+    """More columns than an eighth of the decode grid's warps: the combine runs one warp per output row (every other
+    case in this file has few columns and takes the block per row). Ragged lengths with an empty sequence."""
+    b, hq, hkv = 96, 8, 4
+    rng = np.random.default_rng(d)
+    lens = rng.integers(1, 200, size=b).astype(np.int32)
+    lens[5], lens[17] = 0, 199
+    lk = int(lens.max())
+    kd, vd, tab = make_rows(oracle, 7000 + d, b, hkv, lk, d, (2, 4), (5, 4), cap=lk + 2)
+    q = oracle.normal(81, b * hq * d).reshape(b, hq, 1, d)
+    want = oracle.tq_attention(oracle.round_to(q, qdt), kd, vd, lk, (2, 4), (5, 4), d ** -0.5, tab, kv_len=lens, wr=0)
+    got = run_packed(P, q, kd, vd, lens, (2, 4), (5, 4), d ** -0.5, qdt=qdt, wr=0)
+    assert np.all(got[5] == 0)
+    assert_close(got, want, what=f"many columns d{d} {qdt}", out=qdt)
+
+
+def test_many_short_columns_with_a_rotated_cache(P, oracle):
+    """The row-per-warp combine rotates the merged rows back (Hadamard cache, 192 columns of 100 keys)."""
+    b, hq, hkv, d, lk = 48, 8, 4, 128, 100
+    kx = oracle.normal(15, b * hkv * lk * d).reshape(b, hkv, lk, d)
+    vx = oracle.normal(16, b * hkv * lk * d).reshape(b, hkv, lk, d)
+    q = oracle.normal(17, b * hq * d).reshape(b, hq, 1, d)
+    f = (0, 4)
+    cache = P.TurboKvCache(fmt(P, *f), fmt(P, *f), d, "hadamard", 42, lk)
+    cache.append(to_dev(kx, "bf16"), to_dev(vx, "bf16"))
+    got = cache.attention(to_dev(q, "bf16"), P.FlashAttnConfig(0.0884).causal()).float().cpu().numpy()
+    pk, pv = oracle.rotation_matrix(d, 1, 42), oracle.rotation_matrix(d, 1, 44)
+    tab = MG.tab_for(f[0], f[1], d)
+    kd = oracle.quantize_rows(oracle.rotate_rows(oracle.round_to(kx, "bf16").reshape(-1, d), pk), f[0], f[1], tab).reshape(b, hkv, lk, -1)
+    vd = oracle.quantize_rows(oracle.rotate_rows(oracle.round_to(vx, "bf16").reshape(-1, d), pv), f[0], f[1], tab).reshape(b, hkv, lk, -1)
+    qr = oracle.rotate_rows(oracle.round_to(q, "bf16").reshape(-1, d), pk).reshape(q.shape)
+    o = oracle.tq_attention(qr, kd, vd, lk, f, f, 0.0884, np.concatenate([tab, tab]), wr=0)
+    want = oracle.rotate_rows(o.reshape(-1, d), pv, transpose=True).reshape(o.shape)
+    assert_close(got, want, what="hadamard, many columns", out="bf16")
+
+
 @pytest.mark.parametrize("lq,wl,wr,softcap,use_alibi", [(3, -1, 0, 0.0, False), (4, 50, 0, 0.0, False), (2, -1, -1, 15.0, False),
                                                          (1, -1, 0, 0.0, True), (5, 20, 3, 30.0, True), (3, 0, 0, 0.0, False)])
 def test_masks_softcap_alibi_multi_query(P, oracle, lq, wl, wr, softcap, use_alibi):
