@@ -500,7 +500,10 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
             if (i_more) copy_enter();
         }
     };
-    for (int n = 0; n < NS && i_left > 0; ++n) copy_tile();
+    // The first tile alone, the other stages once the first query rows are loaded: with every worker of the grid asking
+    // for all its stages at once, the first tiles would arrive behind 26 MB of later ones.
+    int prime = NS - 1;
+    if (i_left > 0) copy_tile();
 
     // ------------------------------------------------------------------ the compute side
     // lane offsets inside a tile: K rows g (and g + 8), V rows 2c (and 2c + 1, 2c + 8, 2c + 9)
@@ -780,6 +783,8 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
             }
         }
 
+        for (; prime > 0; --prime)
+            if (i_left > 0) copy_tile();
         // running maxima (log2 domain, value scale folded in) and partial normalizers of rows 2c, 2c + 1
         float M[2] = {-1e30f, -1e30f}, lsum[2] = {0.0f, 0.0f};
 #pragma unroll
