@@ -58,6 +58,9 @@ class Page(C.Structure):
                 ("v_cap", C.c_uint32), ("pad", C.c_uint32)]
 
 
+TQ_AFTER_PREV = 1  # B200_TQ_AFTER_PREV
+
+
 class TqAttnArgs(C.Structure):
     _fields_ = [("q", C.c_void_p), ("out", C.c_void_p), ("q_dtype", C.c_int32), ("out_dtype", C.c_int32),
                 ("q_strides", u64x3), ("out_strides", u64x3), ("k_rows", C.c_void_p), ("v_rows", C.c_void_p),
@@ -66,7 +69,7 @@ class TqAttnArgs(C.Structure):
                 ("hq", C.c_uint32), ("hkv", C.c_uint32), ("d", C.c_uint32), ("kq", QuantSide), ("vq", QuantSide),
                 ("scale", C.c_float), ("softcap", C.c_float), ("wl", C.c_int32), ("wr", C.c_int32),
                 ("alibi", C.c_void_p), ("alibi_bstride", C.c_uint32), ("splits", C.c_int32),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p)]
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p), ("flags", C.c_uint32)]
 
 
 class PeerGather(C.Structure):

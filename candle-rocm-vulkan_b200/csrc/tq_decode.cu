@@ -151,6 +151,8 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
     if (a->splits > 0) nblocks = std::min<uint64_t>(nblocks, ((uint64_t)a->b * pl.ny * a->splits + DW - 1) / DW);
     pl.blocks = (uint32_t)std::max<uint64_t>(std::min(nblocks, (max_tiles + DW - 1) / DW), 1);
 
+    // paged rows: the compaction kernel of this call writes the lengths right before the attention
+    p.after_prev = (a->flags & B200_TQ_AFTER_PREV) && !a->pages ? 1u : 0u;
     const size_t ncols = (size_t)a->b * pl.ny;
     const size_t prow = std::min<size_t>(PACK, p.rows_per_kv);
     const size_t slots = ((size_t)pl.blocks * DW + ncols) * prow;

@@ -74,6 +74,7 @@ struct DecodeParams {
     uint32_t rows_cap;      // rows that exist in every (batch, head) slab of both caches (0 = only the visible ones)
     uint32_t col_cost;      // cost of starting a column, in tiles, for the split of the work between the warps
     uint32_t qstage_bytes;  // query staging for the rotation (0 without it)
+    uint32_t after_prev;    // launched as a programmatic dependent of the stream's previous kernel
     // outputs gathered on every GPU by the combine kernel (world == 0: off)
     void *const *peer_bufs;
     uint32_t *const *peer_flags;
@@ -415,6 +416,10 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
         seg.t1 = (uint32_t)min((uint64_t)tb, seg.t0 + (x_end - seg.x));
     }
 
+    // Launched as a programmatic dependent (after_prev), the grid got here, with nothing read but the lengths, while the
+    // stream's previous kernel was still running: the query, the rows and the partial results may be in its hands
+    // until this returns. A no-op after a plain launch.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t krb = (uint32_t)p.k_ss * 4u, vrb = (uint32_t)p.v_ss * 4u;  // row bytes
     const uint32_t meta_s = sbase + FIXED_SMEM + warp * META;    // [WK][KMW] f32
     const uint32_t vmeta_s = meta_s + WK * KMW * 4;              // [WK] (sigma, log2 sigma)

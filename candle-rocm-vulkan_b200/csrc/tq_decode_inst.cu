@@ -19,6 +19,21 @@ int launch_decode(const DecodeParams &p, dim3 grid, size_t smem, cudaStream_t st
         if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "tq_attention: shared memory opt-in of %zu bytes: %s", smem, cudaGetErrorString(e));
         configured[dev] = smem;
     }
+    if (p.after_prev) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(DW * 32);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+        if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "tq_attention: %s", cudaGetErrorString(e));
+        return check_launch("tq_attention");
+    }
     kern<<<grid, DW * 32, smem, stream>>>(p);
     return check_launch("tq_attention");
 }

@@ -290,7 +290,9 @@ class PackedAttention:
 
     def __init__(self, q: torch.Tensor, k_rows: torch.Tensor, v_rows: torch.Tensor, kv_len, kq: TurboQuantizer,
                  vq: TurboQuantizer, cfg: FlashAttnConfig, out: Optional[torch.Tensor] = None,
-                 gather: Optional["OutputGather"] = None):
+                 gather: Optional["OutputGather"] = None, after_prev: bool = False):
+        # after_prev: B200_TQ_AFTER_PREV of include/b200attn.h (the call may start while the stream's previous kernel
+        # still runs; only for callers whose kv_len is not written by that kernel)
         _need_cuda(q, "q")
         b, hq, lq, d = q.shape
         bk, hkv, cap, kw = k_rows.shape
@@ -339,6 +341,7 @@ class PackedAttention:
         ws = _workspace(q.device, nbytes)
         args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
         args.status = None
+        args.flags = A.TQ_AFTER_PREV if after_prev else 0
         self.args, self.out, self.device = args, out, q.device
         self._keep = (q, k_rows, v_rows, kv_len, kq, vq, alibi, ws)
         self._fn, self._ref = A.lib().b200_tq_attention, C.byref(args)

@@ -217,7 +217,15 @@ typedef struct B200TqAttnArgs {
     void *workspace;                       /* device, b200_tq_attention_workspace_bytes() */
     size_t workspace_bytes;
     int32_t *status;                       /* optional device word, set non-zero if a device wait ran out */
+    uint32_t flags;                        /* B200_TQ_* below; 0 = none */
 } B200TqAttnArgs;
+/* The attention may start while the stream's previous kernel is still running (programmatic dependent launch): its
+ * blocks take their places and work out their shares of the keys from kv_len_dev during that kernel's last
+ * microseconds, and wait for its completion before they touch q, the rows, alibi or the workspace. For the layers of
+ * one decode step, whose lengths were final before the step began. Do not set it when the previous kernel in the
+ * stream writes kv_len_dev (or the page table: paged calls ignore the flag). The reference has no counterpart: it
+ * launches every kernel after the previous one has finished (candle-core/src/cuda_backend/accel.rs:190-252). */
+#define B200_TQ_AFTER_PREV 1u
 /* Paged calls (pages != NULL): the size returned covers a compacted copy of all valid rows; with that much workspace
  * (256-byte aligned) one copy kernel gathers the blocks and the tensor-core kernel runs, with less (16 bytes are
  * enough) the general kernel reads the blocks in place. lk is an upper bound of the sum of the blocks' rows. */

@@ -210,6 +210,44 @@ def test_many_short_columns_with_a_rotated_cache(P, oracle):
     assert_close(got, want, what="hadamard, many columns", out="bf16")
 
 
+def test_launch_behind_a_running_kernel_gives_the_same_rows(P, oracle):
+    """B200_TQ_AFTER_PREV: the attention takes its place while the stream's previous kernel still runs and waits for
+    it before reading the query and the rows. Here that kernel is the append that writes the very rows (and a copy
+    that writes the query): the outputs must be those of the plain launch, call after call."""
+    b, hq, hkv, d, lk = 8, 16, 4, 128, 2000
+    f = fmt(P, 2, 4)
+    kq, vq = P.TurboQuantizer(f, d, "none", 42), P.TurboQuantizer(f, d, "none", 44)
+    g = torch.Generator(device="cuda:0").manual_seed(5)
+    kx = torch.randn((b, hkv, lk, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    vx = torch.randn((b, hkv, lk, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    kc = torch.zeros((b, hkv, lk, kq.row_words()), dtype=torch.int32, device="cuda:0")
+    vc = torch.zeros_like(kc)
+    lens = torch.tensor([2000, 1, 777, 1500, 64, 1999, 33, 1024], dtype=torch.int32, device="cuda:0")
+    q_src = [torch.randn((b, hq, 1, d), generator=g, device="cuda:0", dtype=torch.bfloat16) for _ in range(3)]
+    q = torch.empty_like(q_src[0])
+    cfg = P.FlashAttnConfig(d ** -0.5).causal()
+    plain = P.PackedAttention(q, kc, vc, lens, kq, vq, cfg)
+    behind = P.PackedAttention(q, kc, vc, lens, kq, vq, cfg, out=torch.empty_like(plain.out), after_prev=True)
+    from candle_rocm_vulkan_b200.turbo_quant import _kv_append
+    for it in range(3):
+        scale = float(it + 1)
+        kc.zero_(); vc.zero_()
+        q.copy_(q_src[it])
+        _kv_append(kx * scale, vx, kc, vc, kq, vq, 0)
+        plain.run()
+        torch.cuda.synchronize()
+        want = plain.out.clone()
+        kc.zero_(); vc.zero_(); q.zero_()
+        torch.cuda.synchronize()
+        q.copy_(q_src[it])                          # the kernels right before the attention write what it reads
+        _kv_append(kx * scale, vx, kc, vc, kq, vq, 0)
+        behind.run()
+        behind.run()                                # and once more behind its own combine
+        torch.cuda.synchronize()
+        assert torch.equal(behind.out, want), f"call {it}"
+    assert P._abi.lib().b200_device_wait_status() == 0
+
+
 @pytest.mark.parametrize("lq,wl,wr,softcap,use_alibi", [(3, -1, 0, 0.0, False), (4, 50, 0, 0.0, False), (2, -1, -1, 15.0, False),
                                                          (1, -1, 0, 0.0, True), (5, 20, 3, 30.0, True), (3, 0, 0, 0.0, False)])
 def test_masks_softcap_alibi_multi_query(P, oracle, lq, wl, wr, softcap, use_alibi):
