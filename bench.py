@@ -378,9 +378,12 @@ def run_ours(args, w, rank, world, local_rank):
             main.wait_event(ev_in[i])
             if i - 2 in ev_out:
                 main.wait_event(ev_out[i - 2])            # the result of step i - 2 has left this output buffer
-            _kv_append(kn, vn, kc, vc, kq, vq, lens_dev)
-            lens_dev.add_(1)
-            P.PackedAttention(qv, kc, vc, lens_dev, kq, vq, cfg, out=out_dev[pb], gather=peer_gather).run()
+            # the device lengths are those at the start of this group of steps: step j appends at lens + j and attends
+            # to lens + j + 1 keys (offsets in the call arguments), so no kernel sits between append and attention
+            j = i - first
+            _kv_append(kn, vn, kc, vc, kq, vq, lens_dev, pos_add=j)
+            P.PackedAttention(qv, kc, vc, lens_dev, kq, vq, cfg, out=out_dev[pb], gather=peer_gather, kv_len_add=j + 1,
+                              after_prev=True).run()
             if world > 1 and peer_gather is None:
                 dist.all_gather_into_tensor(gathered, out_dev[pb])
             ev_done[i] = torch.cuda.Event()
@@ -390,6 +393,7 @@ def run_ours(args, w, rank, world, local_rank):
                 out_hosts[pb].copy_(out_dev[pb], non_blocking=True)
                 ev_out[i] = torch.cuda.Event()
                 ev_out[i].record(s_out)
+        lens_dev.add_(count)                              # one length update per group of steps
         last = first + count - 1
         main.wait_event(ev_in[last])
         main.wait_event(ev_out[last])

@@ -69,7 +69,7 @@ class TqAttnArgs(C.Structure):
                 ("hq", C.c_uint32), ("hkv", C.c_uint32), ("d", C.c_uint32), ("kq", QuantSide), ("vq", QuantSide),
                 ("scale", C.c_float), ("softcap", C.c_float), ("wl", C.c_int32), ("wr", C.c_int32),
                 ("alibi", C.c_void_p), ("alibi_bstride", C.c_uint32), ("splits", C.c_int32),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p), ("flags", C.c_uint32)]
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p), ("flags", C.c_uint32), ("kv_len_add", C.c_int32)]
 
 
 class PeerGather(C.Structure):

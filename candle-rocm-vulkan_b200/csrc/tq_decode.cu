@@ -89,6 +89,7 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
                          (unsigned long long)p.k_ss, (unsigned long long)p.v_ss, kl.row_words, vl.row_words);
     if (p.k_ss > 512 || p.v_ss > 512) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: row stride above 512 words");
     p.kv_len = a->kv_len_dev;
+    p.kv_len_add = a->kv_len_dev ? a->kv_len_add : 0;
     p.b = a->b; p.lq = a->lq; p.lk = a->lk; p.hq = a->hq; p.hkv = a->hkv; p.d = a->d;
     p.group = a->hq / a->hkv;
     p.rows_per_kv = p.group * a->lq;

@@ -58,6 +58,7 @@ struct DecodeParams {
     const uint32_t *k_rows, *v_rows;
     uint64_t k_sb, k_sh, k_ss, v_sb, v_sh, v_ss;  // words
     const int32_t *kv_len;
+    int32_t kv_len_add;     // added to every entry of kv_len
     uint32_t b, lq, lk, hq, hkv, d, group;
     uint32_t rows_per_kv, packs;
     DecodeSide k, v;
@@ -230,7 +231,7 @@ struct Column {
 
 __device__ __forceinline__ Column make_column(const DecodeParams &p, uint32_t b) {
     Column c;
-    c.lk = p.kv_len ? max(p.kv_len[b], 0) : (int)p.lk;
+    c.lk = p.kv_len ? min(max(p.kv_len[b] + p.kv_len_add, 0), (int)p.lk) : (int)p.lk;
     // union of the rows' ranges: first query token gives the lowest, the last the highest key
     const long long pos0 = (long long)c.lk - (long long)p.lq, pos1 = (long long)c.lk - 1;
     long long lo = p.wl >= 0 ? max(pos0 - p.wl, 0ll) : 0ll;

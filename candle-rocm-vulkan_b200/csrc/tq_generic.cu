@@ -41,7 +41,7 @@ __global__ void __launch_bounds__(GW * 32) tq_generic_kernel(const DecodeParams 
     const size_t row = blockIdx.x;
     const uint32_t i = (uint32_t)(row % p.lq), h = (uint32_t)((row / p.lq) % p.hq), b = (uint32_t)(row / ((size_t)p.lq * p.hq));
     const uint32_t hk = h / p.group;
-    int lk = p.kv_len ? max(p.kv_len[b], 0) : (int)p.lk;
+    int lk = p.kv_len ? min(max(p.kv_len[b] + p.kv_len_add, 0), (int)p.lk) : (int)p.lk;
     if (pages) {  // the keys of a paged call are the valid rows of all blocks, one after the other
         long long total = 0;
         for (uint32_t pg = 0; pg < n_pages; ++pg) total += pages[pg].rows;
@@ -174,6 +174,7 @@ int tq_generic_plan(const B200TqAttnArgs *a, DecodeParams &p, GenericSide &ks, G
     p.k_sb = a->k_strides[0]; p.k_sh = a->k_strides[1]; p.k_ss = a->k_strides[2];
     p.v_sb = a->v_strides[0]; p.v_sh = a->v_strides[1]; p.v_ss = a->v_strides[2];
     p.kv_len = a->kv_len_dev;
+    p.kv_len_add = a->kv_len_dev ? a->kv_len_add : 0;
     p.b = a->b; p.lq = a->lq; p.lk = a->lk; p.hq = a->hq; p.hkv = a->hkv; p.d = a->d; p.group = a->hq / a->hkv;
     p.k.rot = a->kq.rotation; p.k.tab = a->kq.tab; p.k.signs = a->kq.signs;
     p.v.rot = a->vq.rotation; p.v.tab = a->vq.tab; p.v.signs = a->vq.signs;

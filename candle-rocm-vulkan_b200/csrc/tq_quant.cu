@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(QW * 32) quant_rows_kernel(const QuantParams p
             b = (uint32_t)(row / ((uint64_t)p.nt * p.nh));
         }
         const char *src = reinterpret_cast<const char *>(sp.src) + (b * sp.s_b + h * sp.s_h + t * sp.s_t) * (uint64_t)dtype_size(DT);
-        const int64_t pos = (sp.pos ? sp.pos[b] : sp.pos0) + (int64_t)t;
+        const int64_t pos = (sp.pos ? (int64_t)sp.pos[b] + sp.pos0 : (int64_t)sp.pos0) + (int64_t)t;
         uint32_t *orow = sp.dst + b * sp.c_b + h * sp.c_h + (uint64_t)pos * sp.c_t;
 
         float x[EPL];
@@ -324,7 +324,7 @@ __global__ void __launch_bounds__(Q128_WARPS * 32) quant_rows128_kernel(const Qu
         const uint32_t row = live ? base + (lane >> 3) : rows - 1;
         const uint32_t bh = fastdiv(row, p.nt_mul, p.nt_shr), t = row - bh * p.nt, b = fastdiv(bh, p.nh_mul, p.nh_shr), h = bh - b * p.nh;
         const char *src = reinterpret_cast<const char *>(sp.src) + (b * sp.s_b + h * sp.s_h + t * sp.s_t) * (uint64_t)dtype_size(DT);
-        const int64_t pos = (sp.pos ? sp.pos[b] : sp.pos0) + (int64_t)t;
+        const int64_t pos = (sp.pos ? (int64_t)sp.pos[b] + sp.pos0 : (int64_t)sp.pos0) + (int64_t)t;
         uint32_t *orow = sp.dst + b * sp.c_b + h * sp.c_h + (uint64_t)pos * sp.c_t;
         float x[16];
         load16<DT>(src, l8, x);

@@ -222,9 +222,9 @@ class TurboQuantizer:
         return self.dequantize_rows(q.data).reshape(q.shape).to(q.dtype)
 
 
-def _kv_append(k, v, k_cache, v_cache, kq: TurboQuantizer, vq: TurboQuantizer, pos):
+def _kv_append(k, v, k_cache, v_cache, kq: TurboQuantizer, vq: TurboQuantizer, pos, pos_add: int = 0):
     """b200_kv_append over (b, hkv, t, d) tensors and (b, hkv, cap, words) caches. `pos`: int or an
-    int32 device tensor with one position per batch entry."""
+    int32 device tensor with one position per batch entry, to which `pos_add` is added."""
     b, h, t, d = k.shape
     if k.stride(3) != 1:
         k = k.contiguous()
@@ -234,7 +234,7 @@ def _kv_append(k, v, k_cache, v_cache, kq: TurboQuantizer, vq: TurboQuantizer, p
     args = A.KvAppendArgs(
         k.data_ptr(), v.data_ptr(), A.u64x3(*k.stride()[:3]), A.u64x3(*v.stride()[:3]),
         k_cache.data_ptr(), v_cache.data_ptr(), A.u64x3(*k_cache.stride()[:3]), A.u64x3(*v_cache.stride()[:3]),
-        pos_t.data_ptr() if pos_t is not None else None, 0 if pos_t is not None else int(pos),
+        pos_t.data_ptr() if pos_t is not None else None, int(pos_add) if pos_t is not None else int(pos) + int(pos_add),
         b, h, t, d, _dtype_id(k), kq.side(), vq.side())
     A.check(A.lib().b200_kv_append(C.byref(args), _stream(k.device)))
 
@@ -290,7 +290,7 @@ class PackedAttention:
 
     def __init__(self, q: torch.Tensor, k_rows: torch.Tensor, v_rows: torch.Tensor, kv_len, kq: TurboQuantizer,
                  vq: TurboQuantizer, cfg: FlashAttnConfig, out: Optional[torch.Tensor] = None,
-                 gather: Optional["OutputGather"] = None, after_prev: bool = False):
+                 gather: Optional["OutputGather"] = None, after_prev: bool = False, kv_len_add: int = 0):
         # after_prev: B200_TQ_AFTER_PREV of include/b200attn.h (the call may start while the stream's previous kernel
         # still runs; only for callers whose kv_len is not written by that kernel)
         _need_cuda(q, "q")
@@ -342,6 +342,7 @@ class PackedAttention:
         args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
         args.status = None
         args.flags = A.TQ_AFTER_PREV if after_prev else 0
+        args.kv_len_add = int(kv_len_add) if ragged else 0  # tokens appended since the device lengths were written
         self.args, self.out, self.device = args, out, q.device
         self._keep = (q, k_rows, v_rows, kv_len, kq, vq, alibi, ws)
         self._fn, self._ref = A.lib().b200_tq_attention, C.byref(args)

@@ -162,7 +162,7 @@ typedef struct B200KvAppendArgs {
     uint64_t k_cache_strides[3]; /* (batch, head, row) in words */
     uint64_t v_cache_strides[3];
     const int32_t *pos;       /* device, one write position per batch entry, or NULL: pos0 for all */
-    int32_t pos0;
+    int32_t pos0;             /* with pos: added to every entry (tokens appended since pos was written) */
     uint32_t b, hkv, t, d;
     int32_t src_dtype;
     B200QuantSide kq, vq;
@@ -218,6 +218,9 @@ typedef struct B200TqAttnArgs {
     size_t workspace_bytes;
     int32_t *status;                       /* optional device word, set non-zero if a device wait ran out */
     uint32_t flags;                        /* B200_TQ_* below; 0 = none */
+    int32_t kv_len_add;                    /* added to every kv_len_dev entry: the tokens appended since the device
+                                            * lengths were written (a serving loop updates them once per graph of
+                                            * steps, not per token); sums must not exceed lk; unused without kv_len_dev */
 } B200TqAttnArgs;
 /* The attention may start while the stream's previous kernel is still running (programmatic dependent launch): its
  * blocks take their places and work out their shares of the keys from kv_len_dev during that kernel's last

@@ -248,6 +248,46 @@ def test_launch_behind_a_running_kernel_gives_the_same_rows(P, oracle):
     assert P._abi.lib().b200_device_wait_status() == 0
 
 
+def test_length_and_position_offsets(P, oracle):
+    """kv_len_add / pos0 with device positions: a step that appends at lens + j and attends to lens + j + 1 keys gives
+    the rows and outputs of the same step run with the lengths updated on the device."""
+    from candle_rocm_vulkan_b200.turbo_quant import _kv_append
+    b, hq, hkv, d, cap = 6, 8, 2, 128, 700
+    f = fmt(P, 2, 4)
+    kq, vq = P.TurboQuantizer(f, d, "none", 42), P.TurboQuantizer(f, d, "none", 44)
+    g = torch.Generator(device="cuda:0").manual_seed(9)
+    kx = torch.randn((b, hkv, cap, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    vx = torch.randn((b, hkv, cap, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    q = torch.randn((b, hq, 1, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    lens0 = torch.tensor([600, 0, 33, 257, 1, 512], dtype=torch.int32, device="cuda:0")
+    cfg = P.FlashAttnConfig(d ** -0.5).causal()
+
+    def fresh():
+        kc = torch.zeros((b, hkv, cap, kq.row_words()), dtype=torch.int32, device="cuda:0")
+        vc = torch.zeros_like(kc)
+        _kv_append(kx, vx, kc, vc, kq, vq, 0)
+        return kc, vc
+
+    kn = torch.randn((3, b, hkv, 1, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    vn = torch.randn((3, b, hkv, 1, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    # lengths updated on the device before every step
+    kc1, vc1 = fresh()
+    lens = lens0.clone()
+    want = []
+    for j in range(3):
+        _kv_append(kn[j], vn[j], kc1, vc1, kq, vq, lens)
+        lens.add_(1)
+        want.append(P.PackedAttention(q, kc1, vc1, lens, kq, vq, cfg).run().clone())
+    # lengths left alone, offsets in the arguments
+    kc2, vc2 = fresh()
+    for j in range(3):
+        _kv_append(kn[j], vn[j], kc2, vc2, kq, vq, lens0, pos_add=j)
+        got = P.PackedAttention(q, kc2, vc2, lens0, kq, vq, cfg, kv_len_add=j + 1, after_prev=True).run()
+        torch.cuda.synchronize()
+        assert torch.equal(got, want[j]), f"step {j}"
+    assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+
+
 @pytest.mark.parametrize("lq,wl,wr,softcap,use_alibi", [(3, -1, 0, 0.0, False), (4, 50, 0, 0.0, False), (2, -1, -1, 15.0, False),
                                                          (1, -1, 0, 0.0, True), (5, 20, 3, 30.0, True), (3, 0, 0, 0.0, False)])
 def test_masks_softcap_alibi_multi_query(P, oracle, lq, wl, wr, softcap, use_alibi):
