@@ -262,7 +262,8 @@ def run_ours(args, w, rank, world, local_rank):
                                         peer_gather._state.data_ptr(), peer_gather._state.data_ptr() + 4)
     # the timed steps stand for the layers of one decode step (lengths fixed before the step): each attention may take
     # its place on the GPU while the previous layer's last kernel ends (B200_TQ_AFTER_PREV)
-    calls = [P.PackedAttention(q, kc, vc, kv_len, kq, vq, cfg, out=out, gather=peer_gather, after_prev=True) for kc, vc in caches]
+    calls = [P.PackedAttention(q, kc, vc, kv_len, kq, vq, cfg, out=out, gather=peer_gather, after_prev=True, fresh_rows=0)
+             for kc, vc in caches]
 
     def eager_step(i):
         calls[i % nbuf].run()
@@ -383,7 +384,7 @@ def run_ours(args, w, rank, world, local_rank):
             j = i - first
             _kv_append(kn, vn, kc, vc, kq, vq, lens_dev, pos_add=j)
             P.PackedAttention(qv, kc, vc, lens_dev, kq, vq, cfg, out=out_dev[pb], gather=peer_gather, kv_len_add=j + 1,
-                              after_prev=True).run()
+                              after_prev=True, fresh_rows=1).run()
             if world > 1 and peer_gather is None:
                 dist.all_gather_into_tensor(gathered, out_dev[pb])
             ev_done[i] = torch.cuda.Event()

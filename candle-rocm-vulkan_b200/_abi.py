@@ -50,7 +50,7 @@ class KvAppendArgs(C.Structure):
                 ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("k_cache_strides", u64x3),
                 ("v_cache_strides", u64x3), ("pos", C.c_void_p), ("pos0", C.c_int32), ("b", C.c_uint32),
                 ("hkv", C.c_uint32), ("t", C.c_uint32), ("d", C.c_uint32), ("src_dtype", C.c_int32),
-                ("kq", QuantSide), ("vq", QuantSide)]
+                ("kq", QuantSide), ("vq", QuantSide), ("cap", C.c_uint32), ("status", C.c_void_p)]
 
 
 class Page(C.Structure):
@@ -59,6 +59,7 @@ class Page(C.Structure):
 
 
 TQ_AFTER_PREV = 1  # B200_TQ_AFTER_PREV
+TQ_INPUTS_FINAL = 2  # B200_TQ_INPUTS_FINAL
 
 
 class TqAttnArgs(C.Structure):
@@ -69,12 +70,13 @@ class TqAttnArgs(C.Structure):
                 ("hq", C.c_uint32), ("hkv", C.c_uint32), ("d", C.c_uint32), ("kq", QuantSide), ("vq", QuantSide),
                 ("scale", C.c_float), ("softcap", C.c_float), ("wl", C.c_int32), ("wr", C.c_int32),
                 ("alibi", C.c_void_p), ("alibi_bstride", C.c_uint32), ("splits", C.c_int32),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p), ("flags", C.c_uint32), ("kv_len_add", C.c_int32)]
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p), ("flags", C.c_uint32), ("kv_len_add", C.c_int32),
+                ("fresh_rows", C.c_uint32)]
 
 
 class PeerGather(C.Structure):
     _fields_ = [("peer_bufs", C.c_void_p), ("peer_flags", C.c_void_p), ("world", C.c_uint32), ("rank", C.c_uint32),
-                ("step", C.c_void_p), ("done_ctr", C.c_void_p)]
+                ("step", C.c_void_p), ("done_ctr", C.c_void_p), ("max_polls", C.c_uint32), ("pad", C.c_uint32)]
 
 
 class FaArgs(C.Structure):

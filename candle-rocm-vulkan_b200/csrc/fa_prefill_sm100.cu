@@ -1149,8 +1149,13 @@ using namespace b200;
 
 // 1 when a bounded device-side wait of the attention kernels has run out since the library was
 // loaded (the call that met it wrote zeros or partial rows); synchronizes the device.
+namespace b200 {
+int decode_wait_status();  // tq_decode.cu: the same flag of the kernels over packed rows
+}
 extern "C" int b200_device_wait_status(void) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_wait_failed, sizeof(int)) != cudaSuccess) return -1;
-    return v;
+    const int d = b200::decode_wait_status();
+    if (d < 0) return -1;
+    return (v != 0 || d != 0) ? 1 : 0;
 }

@@ -2,13 +2,14 @@
 // format dispatch and the combine launch.
 #include <algorithm>
 #include <cstdlib>
+#include <atomic>
 #include <mutex>
 
 #include "tq_decode.cuh"
 
 namespace b200 {
 
-template <int KM, int VM, int HD>
+template <int KM, int VM, int HD, bool NAT>
 int launch_decode(const DecodeParams &p, dim3 grid, size_t smem, cudaStream_t stream);
 
 struct DecodePlan {
@@ -18,6 +19,8 @@ struct DecodePlan {
     size_t off_lse, off_meta, ws_bytes;
     uint32_t blocks;
     int hd_idx;
+    bool nat;        // rows packed back to back on both sides: the instantiation with compile-time row strides
+    bool in_kernel;  // the decode grid merges the segments itself (arrival counters), no combine grid
 };
 
 static int sm_count_cached() {
@@ -107,13 +110,11 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
     p.v_stage_bytes = (uint32_t)((WK * p.v_ss * 4 + 16 + 15) / 16 * 16);
     // shared memory: barriers and pair tables, per-warp key metadata, per-warp query staging (rotated
     // caches only), then the stage rings
-    p.qstage_bytes = a->kq.rotation == B200_ROT_HADAMARD ? (uint32_t)(DW * PACK * a->d * 4) : 0u;
+    p.qstage_bytes = (a->kq.rotation == B200_ROT_HADAMARD || a->vq.rotation == B200_ROT_HADAMARD) ? (uint32_t)(DW * PACK * a->d * 4) : 0u;
     const size_t fixed = FIXED_SMEM + (size_t)DW * meta_bytes(a->kq.mode, a->vq.mode, (int)a->d) + p.qstage_bytes;
     const size_t stage = (size_t)p.k_stage_bytes + p.v_stage_bytes;
     // stages per warp and blocks per SM: as many bytes in flight as possible (a warp computes on one
     // stage while the others load), more blocks on a tie
-    static const long env_ns = [] { const char *e = getenv("B200_DECODE_STAGES"); return e ? atol(e) : 0l; }();
-    static const long env_bps = [] { const char *e = getenv("B200_DECODE_BLOCKS_PER_SM"); return e ? atol(e) : 0l; }();
     int bps = 1;
     p.ns = 2;
     size_t best = 0;
@@ -129,11 +130,6 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
             bps = fit;
         }
     }
-    if (env_ns >= 2 && env_ns <= NS_MAX) {
-        p.ns = (uint32_t)env_ns;
-        bps = (int)std::min<size_t>(B200_DECODE_MIN_BLOCKS, (228 * 1024) / (fixed + DW * p.ns * stage + 1024));
-    }
-    if (env_bps > 0) bps = (int)env_bps;
     bps = std::max(bps, 1);
     pl.smem = fixed + DW * p.ns * stage;
     if (pl.smem > 227 * 1024) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: %zu bytes of shared memory", pl.smem);
@@ -142,8 +138,7 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
     if (p.k_ss && p.v_ss && p.k_sh % p.k_ss == 0 && p.v_sh % p.v_ss == 0 && (a->hkv > 1 || a->b > 1))
         p.rows_cap = (uint32_t)std::min<uint64_t>(std::min(p.k_sh / p.k_ss, p.v_sh / p.v_ss), 0x7fffffffu);
 
-    static const long env_cc = [] { const char *e = getenv("B200_DECODE_COL_COST"); return e ? atol(e) : -1l; }();
-    p.col_cost = env_cc >= 0 ? (uint32_t)env_cc : 4u;
+    p.col_cost = B200_DECODE_COL_COST;
     // persistent blocks of DW independent warps: as many as fit on the device at once, at most one
     // warp per tile of keys
     const uint64_t lk = std::max<uint32_t>(a->lk, 1);
@@ -152,9 +147,18 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
     if (a->splits > 0) nblocks = std::min<uint64_t>(nblocks, ((uint64_t)a->b * pl.ny * a->splits + DW - 1) / DW);
     pl.blocks = (uint32_t)std::max<uint64_t>(std::min(nblocks, (max_tiles + DW - 1) / DW), 1);
 
-    // paged rows: the compaction kernel of this call writes the lengths right before the attention
-    p.after_prev = (a->flags & B200_TQ_AFTER_PREV) && !a->pages ? 1u : 0u;
+    p.after_prev = (a->flags & B200_TQ_AFTER_PREV) ? 1u : 0u;
+    p.prefetch = (p.after_prev && (a->flags & B200_TQ_INPUTS_FINAL)) ? 1u : 0u;
+    p.fresh_rows = std::min<uint32_t>(a->fresh_rows, 0x7fffffffu);
     const size_t ncols = (size_t)a->b * pl.ny;
+    pl.nat = p.k_ss == (uint64_t)kl.row_words && p.v_ss == (uint64_t)vl.row_words && a->kq.mode == a->vq.mode && a->d == 128;
+    // Few segments per column (the workers outnumber the columns by less than eight to one): the last worker of a
+    // column merges it inside the decode grid. Many segments per column (a few long sequences), or more columns
+    // than there are arrival counters: a combine grid, whose blocks share a row's segments, follows.
+    pl.in_kernel = (size_t)pl.blocks * DW < 8 * ncols && ncols <= (size_t)CTR_COLS;
+#ifdef B200_FORCE_COMBINE  // measurement builds only: always the separate combine grid
+    pl.in_kernel = false;
+#endif
     const size_t prow = std::min<size_t>(PACK, p.rows_per_kv);
     const size_t slots = ((size_t)pl.blocks * DW + ncols) * prow;
     const size_t part_o = slots * a->d * 4;
@@ -168,15 +172,22 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
 
 template <int KM, int VM>
 static int dispatch_hd(const DecodePlan &pl, dim3 grid, cudaStream_t stream) {
+    if constexpr (KM == VM)
+        if (pl.nat && pl.hd_idx == 1) return launch_decode<KM, VM, 128, true>(pl.p, grid, pl.smem, stream);
     switch (pl.hd_idx) {
-    case 0: return launch_decode<KM, VM, 64>(pl.p, grid, pl.smem, stream);
-    case 1: return launch_decode<KM, VM, 128>(pl.p, grid, pl.smem, stream);
-    default: return launch_decode<KM, VM, 256>(pl.p, grid, pl.smem, stream);
+    case 0: return launch_decode<KM, VM, 64, false>(pl.p, grid, pl.smem, stream);
+    case 1: return launch_decode<KM, VM, 128, false>(pl.p, grid, pl.smem, stream);
+    default: return launch_decode<KM, VM, 256, false>(pl.p, grid, pl.smem, stream);
     }
 }
 
 template <int KM>
 static int dispatch_v(const DecodePlan &pl, dim3 grid, cudaStream_t stream) {
+#ifdef B200_ONLY_SAME_FORMAT  // measurement builds only: keys and values in one format, the other pairs are left out
+    if (pl.p.v.mode != KM || pl.hd_idx != 1) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "measurement build");
+    if (pl.nat) return launch_decode<KM, KM, 128, true>(pl.p, grid, pl.smem, stream);
+    return launch_decode<KM, KM, 128, false>(pl.p, grid, pl.smem, stream);
+#else
     switch (pl.p.v.mode) {
     case B200_TURBO_MSE: return dispatch_hd<KM, B200_TURBO_MSE>(pl, grid, stream);
     case B200_MXFP4: return dispatch_hd<KM, B200_MXFP4>(pl, grid, stream);
@@ -184,39 +195,70 @@ static int dispatch_v(const DecodePlan &pl, dim3 grid, cudaStream_t stream) {
     case B200_MXFP8: return dispatch_hd<KM, B200_MXFP8>(pl, grid, stream);
     default: return dispatch_hd<KM, B200_FP8_ROW>(pl, grid, stream);
     }
+#endif
 }
 
-// Launched behind the combine grid when the outputs are gathered: one warp publishes this rank's step in
-// every rank's flags and waits, with a bound, until all ranks have published it. The rows stored by the
-// combine grid (a completed grid) are visible system-wide before anything this kernel writes.
+// Launched behind the combine grid when the outputs are gathered by that grid: one warp publishes this rank's step
+// in every rank's flags and waits, with a bound, until all ranks have published it. The rows stored by the combine
+// grid (a completed grid) are visible system-wide before anything this kernel writes.
 __global__ void __launch_bounds__(32) tq_gather_publish_kernel(uint32_t *const *peer_flags, uint32_t world, uint32_t rank, uint32_t *step,
-                                                                int32_t *status) {
-    const int lane = threadIdx.x;
+                                                                uint32_t polls, int32_t *status, int32_t *lib_status) {
     // launched with programmatic stream serialization: the combine grid has completed, and its stores are visible,
     // once this returns
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t g_step = *reinterpret_cast<volatile uint32_t *>(step) + 1u;
-    bool ok = true;
-    for (uint32_t pr = lane; pr < world; pr += 32) {
-        __threadfence_system();
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flags[pr] + rank), "r"(g_step) : "memory");
+    gather_publish(peer_flags, world, rank, step, g_step, polls, status, lib_status, (int)threadIdx.x);
+}
+
+// Library-owned device words. g_col_ctr: arrival counters of the columns of the calls in flight, one slab per
+// call, taken in turn; every counter is back at zero when its call ends (the last arrival wraps it), so the slabs
+// need no clearing between calls. g_decode_wait_failed: set when a bounded wait of a decode kernel ran out.
+static __device__ uint32_t g_col_ctr[CTR_SLABS][CTR_COLS];
+static __device__ int32_t g_decode_wait_failed;
+
+#ifdef B200_TRACE
+static unsigned long long *g_trace_host = nullptr;
+extern "C" int b200_dbg_trace(unsigned long long *out) {  // measurement builds only
+    return g_trace_host ? (int)cudaMemcpy(out, g_trace_host, 2 * 2048 * 8 * 8, cudaMemcpyDeviceToHost) : -1;
+}
+#endif
+
+struct DeviceWords {
+    uint32_t *ctr;
+    int32_t *wait_failed;
+};
+static DeviceWords g_device_words[64];
+static bool g_device_words_ok[64];
+static std::mutex g_device_words_mutex;
+static std::atomic<uint32_t> g_next_slab{0};
+
+// Device addresses of the words above on the current device. In host code the arrays' names are handles for the
+// runtime, not addresses a kernel can use: cudaGetSymbolAddress, once per device, with that device current.
+static int device_words(DeviceWords &w) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) return set_error(B200_ERR_LAUNCH, "tq_attention: no usable current device (%s)", cudaGetErrorString(e));
+    std::lock_guard<std::mutex> lock(g_device_words_mutex);
+    if (!g_device_words_ok[dev]) {
+        void *c = nullptr, *f = nullptr;
+        e = cudaGetSymbolAddress(&c, g_col_ctr);
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(&f, g_decode_wait_failed);
+        if (e != cudaSuccess || !c || !f) return set_error(B200_ERR_LAUNCH, "tq_attention: address of the library's device words: %s", cudaGetErrorString(e));
+        g_device_words[dev].ctr = reinterpret_cast<uint32_t *>(c);
+        g_device_words[dev].wait_failed = reinterpret_cast<int32_t *>(f);
+        g_device_words_ok[dev] = true;
     }
-    for (uint32_t pr = lane; pr < world; pr += 32) {
-        const uint32_t *flag = peer_flags[rank] + pr;
-        uint32_t seen = 0;
-        // steps only grow; a rank that is one step ahead has already passed this one
-        for (uint32_t spin = 0; spin < (1u << 21); ++spin) {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
-            if ((int32_t)(seen - g_step) >= 0) break;
-            __nanosleep(32);
-        }
-        if ((int32_t)(seen - g_step) < 0) ok = false;
-    }
-    ok = __all_sync(0xffffffffu, ok);
-    if (lane == 0) {
-        if (!ok && status) atomicExch(status, 2);
-        *reinterpret_cast<volatile uint32_t *>(step) = g_step;
-    }
+    w = g_device_words[dev];
+    return B200_OK;
+}
+
+// 1 when a bounded wait of a decode kernel has run out on the current device since the library was loaded
+int decode_wait_status() {
+    DeviceWords w;
+    if (device_words(w)) return -1;
+    int32_t v = 0;
+    if (cudaMemcpy(&v, w.wait_failed, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    return v != 0;
 }
 
 // n words from src to dst by the 256 threads of a block: 16-byte vectors where both sides sit at the same offset inside
@@ -323,6 +365,9 @@ static bool paged_fast_plan(const B200TqAttnArgs *a, PagedFast &f) {
     f.dense.kv_len_dev = reinterpret_cast<const int32_t *>(a->q);
     f.dense.workspace = nullptr;
     f.dense.workspace_bytes = 0;
+    // the compaction kernel of the call writes the rows and the lengths right before the attention: the attention
+    // must not start as that kernel's programmatic dependent
+    f.dense.flags &= ~(B200_TQ_AFTER_PREV | B200_TQ_INPUTS_FINAL);
     if (tq_generic_takes(&f.dense)) return false;
     DecodePlan pl;
     if (make_plan(&f.dense, pl)) return false;
@@ -381,6 +426,7 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
         pl.p.rank = tl_gather->rank;
         pl.p.step = tl_gather->step;
         pl.p.done_ctr = tl_gather->done_ctr;
+        pl.p.gather_polls = tl_gather->max_polls;
     }
     cudaStream_t stream = (cudaStream_t)stream_;
     if ((uint64_t)a->b * a->hq * a->lq == 0) return B200_OK;
@@ -394,6 +440,21 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
     p.part_o = reinterpret_cast<float *>(ws);
     p.part_lse = reinterpret_cast<float *>(ws + pl.off_lse);
     p.meta = reinterpret_cast<int32_t *>(ws + pl.off_meta);
+    DeviceWords dw;
+    const int wrc = device_words(dw);
+    if (wrc) return wrc;
+    p.lib_status = dw.wait_failed;
+#ifdef B200_TRACE
+    {
+        static unsigned long long *tr = nullptr;
+        static uint32_t calls = 0;
+        if (!tr) { cudaMalloc(&tr, 2 * 2048 * 8 * 8); cudaMemset(tr, 0, 2 * 2048 * 8 * 8); }
+        p.trace = tr + (size_t)(calls++ & 1u) * 2048 * 8;
+        g_trace_host = tr;
+    }
+#endif
+    // calls in flight at the same time must not share a slab: 32 slabs taken in turn
+    p.ctr = pl.in_kernel ? dw.ctr + (size_t)(g_next_slab.fetch_add(1, std::memory_order_relaxed) % CTR_SLABS) * CTR_COLS : nullptr;
     const dim3 grid(pl.blocks);
     int lrc;
     switch (p.k.mode) {
@@ -403,12 +464,11 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
     case B200_MXFP8: lrc = dispatch_v<B200_MXFP8>(pl, grid, stream); break;
     default: lrc = dispatch_v<B200_FP8_ROW>(pl, grid, stream); break;
     }
-    if (lrc) return lrc;
+    if (lrc || pl.in_kernel) return lrc;
     {
         const size_t rows = (size_t)a->b * a->hq * a->lq;
-        // Few segments per row (the workers outnumber the columns by less than eight to one): one warp per row, four
-        // rows per block, a grid that is resident at once (further rows are looped over). Many segments per row: one
-        // block per row, its warps share the segments.
+        // Few segments per row: one warp per row, four rows per block, a grid that is resident at once (further rows
+        // are looped over). Many segments per row: one block per row, its warps share the segments.
         const bool per_row = (size_t)pl.blocks * DW < 8 * (size_t)a->b * pl.ny;
         const unsigned gx = per_row ? (unsigned)std::max<size_t>(std::min<size_t>((rows + 3) / 4, (size_t)sm_count_cached() * 6), 1)
                                     : (unsigned)std::max<size_t>(std::min<size_t>(rows, (size_t)sm_count_cached() * 16), 1);
@@ -435,7 +495,7 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
         if (p.world) {
             cfg.gridDim = dim3(1);
             cfg.blockDim = dim3(32);
-            e = cudaLaunchKernelEx(&cfg, tq_gather_publish_kernel, p.peer_flags, p.world, p.rank, p.step, p.status);
+            e = cudaLaunchKernelEx(&cfg, tq_gather_publish_kernel, p.peer_flags, p.world, p.rank, p.step, p.gather_polls, p.status, p.lib_status);
             if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "tq_gather_publish: %s", cudaGetErrorString(e));
             return check_launch("tq_gather_publish");
         }

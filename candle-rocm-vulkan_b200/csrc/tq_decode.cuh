@@ -1,11 +1,13 @@
 // Decode attention over packed K/V rows (FP8, MXFP8, MXFP4, NVFP4, TurboQuant 4-bit): kernel body.
 //
-// Work split: block = (key chunk, pack of up to 8 query rows that share a kv head, batch entry).
-// Each of the 4 warps streams its own 32-key tiles of the chunk through a private ring of shared
-// memory stages filled by bulk copies (cp.async.bulk + mbarrier, no multicast), so no block-wide
-// barrier sits in the key loop. Per tile the warp first derives the per-key scalars once (lane =
-// key): f32 key scales, the value scale sigma = rsc0_v * 2^(largest block exponent) with its log2,
-// and the f16 block scales of V relative to that exponent. Then per 16 keys it
+// Work split: the visible keys of every column (batch entry, kv head, pack of up to 8 query rows that
+// share that kv head) are cut into 32-key tiles; the tiles of all columns form one list that the
+// warps of the persistent blocks share in cost order. Every warp is a worker of its own: it streams
+// its tiles through a private ring of shared memory stages filled by bulk copies (cp.async.bulk +
+// mbarrier, no multicast), so no block-wide barrier sits in the key loop. Per tile the warp first
+// derives the per-key scalars once (lane = key): f32 key scales, the value scale sigma = rsc0_v *
+// 2^(largest block exponent) with its log2, and the f16 block scales of V relative to that exponent.
+// Then per 16 keys it
 //   1. dequantizes K in registers to f16 (packed cvt from e2m1 / e4m3, or a 256-entry pair table
 //      for the codebook format) as the A operand of mma.sync m16n8k16 (rows = keys g and g + 8 of
 //      lane (g, c)), with the f16 query fragments as B (columns = query rows). The contraction
@@ -21,12 +23,16 @@
 //      dequantizes V as A = V^T (lane (g, c) owns keys {2c, 2c+1, 2c+8, 2c+9} x dims
 //      [g D/8, (g+1) D/8); bytes or nibbles of two keys are interleaved before the packed cvt so
 //      that the f16 pairs run along the contraction index): O^T += V^T P^T.
-// The warps' states are merged through shared memory; the block writes either the final rows
-// (one chunk) or a normalized partial and its log-sum-exp for the combine kernel.
+// A worker's piece of a column (a segment) ends in a normalized partial result and its log-sum-exp.
+// A column that one worker covers alone is stored straight from the registers; otherwise the
+// partial goes to the workspace and the worker counts itself on the column's arrival counter: the
+// last of the column's workers to arrive merges the partials (in segment order, so the result does
+// not depend on who arrives last), rotates back, casts and stores the rows. Columns with very many
+// segments (few long sequences) are merged by a separate combine grid instead.
 //
 // Semantics: candle-core/kernels/turbo_quant_impl.h:232-401 (tq_attn): score = scale * rsc0_k *
 // sum_d elem_k q_d, softcap, ALiBi, bottom-right aligned windows, value weight p * rsc0_v, zeros
-// for rows without keys.
+// for rows without keys; merge of partials: turbo_quant_impl.h:659-685.
 #pragma once
 #include "common.cuh"
 
@@ -40,6 +46,14 @@ constexpr int WK = 32;        // keys per warp tile
 constexpr int NS_MAX = 3;     // stages per warp (fewer when the rows are large)
 constexpr float MAX_SLACK = 8.0f;  // log2 of how far a score may exceed the running maximum before it moves
 constexpr int PACK = 8;       // query rows per block
+#ifndef B200_DECODE_COL_COST
+#define B200_DECODE_COL_COST 4  // cost of starting a column, in tiles, in the split of the work between the workers
+#endif
+#ifndef B200_ABL
+#define B200_ABL 0  // measurement builds only: leaves parts of a tile's work out (results are void)
+#endif
+constexpr int CTR_SLABS = 32;    // arrival-counter slabs of the library (consecutive calls take them in turn)
+constexpr int CTR_COLS = 8192;   // columns a call may have for the decode grid to merge them itself
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
@@ -76,12 +90,27 @@ struct DecodeParams {
     uint32_t col_cost;      // cost of starting a column, in tiles, for the split of the work between the warps
     uint32_t qstage_bytes;  // query staging for the rotation (0 without it)
     uint32_t after_prev;    // launched as a programmatic dependent of the stream's previous kernel
+    uint32_t prefetch;      // with after_prev: rows below kv_len - fresh_rows may be copied while that kernel still runs
+    uint32_t fresh_rows;
     // outputs gathered on every GPU by the combine kernel (world == 0: off)
     void *const *peer_bufs;
     uint32_t *const *peer_flags;
     uint32_t world, rank;
     uint32_t *step, *done_ctr;
+    uint32_t gather_polls;  // polls of the wait for the other ranks' flags (0: 2^21)
+    // arrival counters of the columns, one word each, zero between calls (the last arrival wraps its
+    // counter back to zero): the last worker of a column merges it. Null: the combine grid merges.
+    uint32_t *ctr;
+    int32_t *lib_status;    // library-wide flag: set when a bounded wait of a kernel of this call runs out
+#ifdef B200_TRACE
+    unsigned long long *trace;  // measurement builds only: [worker][8] timestamps
+#endif
 };
+#ifdef B200_TRACE
+#define B200_T(i) do { if (lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.trace[(size_t)wid * 8 + (i)] = t_; } } while (0)
+#else
+#define B200_T(i) do { } while (0)
+#endif
 
 __host__ __device__ constexpr bool fmt_is4(int m) { return m == B200_MXFP4 || m == B200_NVFP4 || m == B200_TURBO_MSE; }
 __host__ __device__ constexpr bool fmt_is_mx(int m) { return m == B200_MXFP4 || m == B200_MXFP8; }
@@ -277,7 +306,253 @@ __device__ __forceinline__ bool next_segment(Segment &s, const DecodeParams &p, 
     return true;
 }
 
-template <int KM, int VM, int HD>
+// ---- row layout of a format at head dim HD (candle-core/src/accel/formats.rs:206-242), in bytes
+__host__ __device__ constexpr int code_bytes(int m, int hd) { return fmt_is4(m) ? hd / 2 : hd; }
+__host__ __device__ constexpr int aux_words_of(int m, int hd) {
+    return fmt_is_mx(m) ? (hd / 32 + 3) / 4 : (m == B200_NVFP4 ? (hd / 16 + 3) / 4 : 0);
+}
+__host__ __device__ constexpr int rsc_byte_off(int m, int hd) { return code_bytes(m, hd) + 4 * aux_words_of(m, hd); }
+__host__ __device__ constexpr int nat_row_bytes(int m, int hd) { return rsc_byte_off(m, hd) + 8; }
+// bytes of a stage's K (or V) part: WK rows plus the slack of a copy that starts below its first row
+__host__ __device__ constexpr uint32_t stage_part_bytes(uint32_t row_bytes) { return (WK * row_bytes + 16u + 15u) / 16u * 16u; }
+
+// Output offset (elements) of row rr of column (b, y), and its index among the rows of the call in
+// (batch, head, token) order; false for a row that the pack does not have.
+__device__ __forceinline__ bool row_addr(const DecodeParams &p, uint32_t b, uint32_t y, uint32_t rr, size_t &obase, size_t &grow) {
+    const uint32_t hk = y / p.packs, pack = y % p.packs, r = pack * PACK + rr;
+    if (r >= p.rows_per_kv) return false;
+    const uint32_t i = p.lq == 1 ? 0u : r / p.group, h = hk * p.group + (p.lq == 1 ? r : r % p.group);
+    obase = (size_t)b * p.o_sb + (size_t)h * p.o_sh + (size_t)i * p.o_ss;
+    grow = ((size_t)b * p.hq + h) * p.lq + i;
+    return true;
+}
+
+// EPL consecutive elements of a row, cast to the output type: one vector store for 16-bit types on an 8-byte boundary
+template <int EPL>
+__device__ __forceinline__ void store_row_piece(void *out, size_t off, const float (&v)[EPL], int dt) {
+    if constexpr (EPL % 4 == 0) {
+        if ((dt == B200_F16 || dt == B200_BF16) && ((reinterpret_cast<uintptr_t>(out) + 2 * off) & 7u) == 0) {
+            uint16_t *o16 = reinterpret_cast<uint16_t *>(out) + off;
+#pragma unroll
+            for (int q = 0; q < EPL / 4; ++q) {
+                uint32_t w[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t lo = dt == B200_F16 ? f_to_f16_bits(v[4 * q + 2 * h]) : f_to_bf16_bits(v[4 * q + 2 * h]);
+                    const uint32_t hi = dt == B200_F16 ? f_to_f16_bits(v[4 * q + 2 * h + 1]) : f_to_bf16_bits(v[4 * q + 2 * h + 1]);
+                    w[h] = lo | (hi << 16);
+                }
+                *reinterpret_cast<uint2 *>(o16 + 4 * q) = make_uint2(w[0], w[1]);
+            }
+            return;
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) store_elem_rt(out, off + k, v[k], dt);
+}
+
+// Merge of the `ns` partial results of one output row (candle-core/kernels/turbo_quant_impl.h:659-685) by one
+// warp: lane l ends with the normalized elements [l HD/32, (l + 1) HD/32) of the row. `po` points at the lane's
+// piece of the first segment's partial row, `pl` at its log-sum-exp; consecutive segments are seg_stride floats
+// (lse_stride words) apart. Loads bypass L1: the partials were written by other SMs during this kernel.
+template <int HD>
+__device__ __forceinline__ void merge_row(const float *po, const float *pl, int ns, size_t seg_stride, size_t lse_stride, int lane,
+                                          float (&acc)[HD / 32]) {
+    constexpr int EPL = HD / 32;
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) acc[k] = 0.0f;
+    // the first four segments' rows are requested before the log-sum-exps are looked at
+    float pre[4][EPL];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (j < ns) {
+#pragma unroll
+            for (int q = 0; q < EPL / 2; ++q) {
+                const float2 v = __ldcg(reinterpret_cast<const float2 *>(po + (size_t)j * seg_stride + 2 * q));
+                pre[j][2 * q] = v.x;
+                pre[j][2 * q + 1] = v.y;
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < EPL; ++k) pre[j][k] = 0.0f;
+        }
+    }
+    float mx = -INFINITY;
+    for (int s0 = lane; s0 < ns; s0 += 32) mx = fmaxf(mx, __ldcg(pl + (size_t)s0 * lse_stride));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float wsum = 0.0f;
+    for (int base = 0; base < ns; base += 32) {  // lane l weighs segment base + l
+        const int sl = base + lane;
+        float wl = 0.0f;
+        if (sl < ns) {
+            const float e = __ldcg(pl + (size_t)sl * lse_stride);
+            wl = e == -INFINITY ? 0.0f : expf(e - mx);
+        }
+        wsum += wl;
+        const int cnt = min(32, ns - base);
+        int j = 0;
+        if (base == 0) {
+            // the four rows in registers (segments past the last one weigh nothing)
+#pragma unroll
+            for (; j < 4; ++j) {
+                const float w = __shfl_sync(0xffffffffu, wl, j);
+#pragma unroll
+                for (int k = 0; k < EPL; ++k) acc[k] = fmaf(w, pre[j][k], acc[k]);
+            }
+        }
+#pragma unroll 4
+        for (; j < cnt; ++j) {
+            const float w = __shfl_sync(0xffffffffu, wl, j);
+            const float *src = po + (size_t)(base + j) * seg_stride;
+#pragma unroll
+            for (int q = 0; q < EPL / 2; ++q) {
+                const float2 v = __ldcg(reinterpret_cast<const float2 *>(src + 2 * q));
+                acc[2 * q] = fmaf(w, v.x, acc[2 * q]);
+                acc[2 * q + 1] = fmaf(w, v.y, acc[2 * q + 1]);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) acc[k] = wsum > 0.0f ? acc[k] / wsum : 0.0f;
+}
+
+// A finished output row (lane l holds its elements [l HD/32, (l + 1) HD/32) in the rotated domain of the values):
+// rotated back through the warp's staging row `rb` (HD floats of shared memory; only touched when the values
+// were rotated), cast and stored, also into every rank's gathered buffer when the outputs are gathered.
+template <int HD>
+__device__ __forceinline__ void finish_row(const DecodeParams &p, size_t obase, size_t grow, size_t g_base, float (&acc)[HD / 32], float *rb,
+                                           int lane, bool rotate = true) {
+    constexpr int EPL = HD / 32;
+    if (rotate && p.v.rot == B200_ROT_HADAMARD) {
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) rb[lane * EPL + k] = acc[k];
+        __syncwarp();
+        warp_hadamard(rb, HD, p.v.signs, false, lane);
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < EPL; ++k) acc[k] = rb[lane * EPL + k];
+    }
+    store_row_piece<EPL>(p.out, obase + (size_t)lane * EPL, acc, p.out_dtype);
+    // the same row into every rank's gathered buffer: plain stores through the peer mappings
+    for (uint32_t pr = 0; pr < p.world; ++pr) store_row_piece<EPL>(p.peer_bufs[pr], g_base + grow * HD + (size_t)lane * EPL, acc, p.out_dtype);
+}
+
+// Merge of all rows of one column by one warp, inside the decode grid (the last worker of the column to arrive).
+// LPR lanes share a row (lane l: row l / LPR, elements [(l % LPR) HD / LPR, +HD / LPR)), so the rows of the column
+// are merged side by side and the partial rows of two segments are in flight per lane: a column costs two or three
+// trips to L2 instead of a few per row. `slot0`: the first segment's slot; consecutive segments are consecutive slots.
+template <int HD, int LPR>
+__device__ __forceinline__ void merge_column(const DecodeParams &p, uint32_t b, uint32_t y, size_t slot0, int ns, uint32_t prow, size_t g_base,
+                                             float *stage, int lane) {
+    constexpr int EL = HD / LPR;  // elements of a row per lane
+    const uint32_t rr = (uint32_t)lane / LPR, q = (uint32_t)lane % LPR;
+    size_t obase = 0, grow = 0;
+    const bool live = rr < prow && row_addr(p, b, y, rr, obase, grow);
+    const float *pl = p.part_lse + slot0 * prow + rr;
+    const float *po = p.part_o + (slot0 * prow + rr) * HD + q * EL;
+    const size_t seg_stride = (size_t)prow * HD;
+    float acc[EL];
+#pragma unroll
+    for (int k = 0; k < EL; ++k) acc[k] = 0.0f;
+    if (live) {
+        // the first two segments' rows are requested before the log-sum-exps are looked at
+        float4 pre[2][EL / 4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int k = 0; k < EL / 4; ++k)
+                pre[j][k] = j < ns ? __ldcg(reinterpret_cast<const float4 *>(po + (size_t)j * seg_stride) + k) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float mx = -INFINITY;
+#pragma unroll 8
+        for (int s0 = 0; s0 < ns; ++s0) mx = fmaxf(mx, __ldcg(pl + (size_t)s0 * prow));
+        float wsum = 0.0f;
+        for (int s0 = 0; s0 < ns; s0 += 2) {
+            float w[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float e = s0 + j < ns ? __ldcg(pl + (size_t)(s0 + j) * prow) : -INFINITY;
+                w[j] = e == -INFINITY ? 0.0f : expf(e - mx);
+                wsum += w[j];
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int k = 0; k < EL / 4; ++k) {
+                    acc[4 * k] = fmaf(w[j], pre[j][k].x, acc[4 * k]);
+                    acc[4 * k + 1] = fmaf(w[j], pre[j][k].y, acc[4 * k + 1]);
+                    acc[4 * k + 2] = fmaf(w[j], pre[j][k].z, acc[4 * k + 2]);
+                    acc[4 * k + 3] = fmaf(w[j], pre[j][k].w, acc[4 * k + 3]);
+                }
+            // the next two segments
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int k = 0; k < EL / 4; ++k)
+                    if (s0 + 2 + j < ns) pre[j][k] = __ldcg(reinterpret_cast<const float4 *>(po + (size_t)(s0 + 2 + j) * seg_stride) + k);
+        }
+        const float inv = wsum > 0.0f ? 1.0f / wsum : 0.0f;
+#pragma unroll
+        for (int k = 0; k < EL; ++k) acc[k] *= inv;
+    }
+    if (p.v.rot == B200_ROT_HADAMARD) {
+        // rotate back through the warp's staging rows ([row][HD] floats of shared memory)
+        __syncwarp();
+        if (live)
+#pragma unroll
+            for (int k = 0; k < EL; ++k) stage[rr * HD + q * EL + k] = acc[k];
+        __syncwarp();
+        for (uint32_t r2 = 0; r2 < prow; ++r2) warp_hadamard(stage + r2 * HD, HD, p.v.signs, false, lane);
+        __syncwarp();
+        if (live)
+#pragma unroll
+            for (int k = 0; k < EL; ++k) acc[k] = stage[rr * HD + q * EL + k];
+        __syncwarp();
+    }
+    if (live) {
+        store_row_piece<EL>(p.out, obase + q * EL, acc, p.out_dtype);
+        // the same row into every rank's gathered buffer: plain stores through the peer mappings
+        for (uint32_t pr = 0; pr < p.world; ++pr) store_row_piece<EL>(p.peer_bufs[pr], g_base + grow * HD + q * EL, acc, p.out_dtype);
+    }
+}
+
+// Gathered outputs: one warp publishes this rank's step in every rank's flags and waits, with a bound, until all
+// ranks have published it. The caller has made this rank's rows visible system-wide (fence) before. A wait that
+// runs out sets the call's status word to 2 and the library-wide flag; the step is advanced all the same, so the
+// next call does not reuse this step's slot.
+__device__ __forceinline__ void gather_publish(uint32_t *const *peer_flags, uint32_t world, uint32_t rank, uint32_t *step, uint32_t g_step,
+                                               uint32_t polls, int32_t *status, int32_t *lib_status, int lane) {
+    bool ok = true;
+    for (uint32_t pr = lane; pr < world; pr += 32) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flags[pr] + rank), "r"(g_step) : "memory");
+    }
+    const uint32_t limit = polls ? polls : (1u << 21);
+    for (uint32_t pr = lane; pr < world; pr += 32) {
+        const uint32_t *flag = peer_flags[rank] + pr;
+        uint32_t seen = 0;
+        // steps only grow; a rank that is one step ahead has already passed this one
+        for (uint32_t spin = 0; spin < limit; ++spin) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+            if ((int32_t)(seen - g_step) >= 0) break;
+            __nanosleep(32);
+        }
+        if ((int32_t)(seen - g_step) < 0) ok = false;
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (lane == 0) {
+        if (!ok) {
+            if (status) atomicExch(status, 2);
+            if (lib_status) atomicExch(lib_status, 1);
+        }
+        *reinterpret_cast<volatile uint32_t *>(step) = g_step;
+    }
+}
+
+template <int KM, int VM, int HD, bool NAT>
 __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_kernel(const DecodeParams p) {
     constexpr int STEPS = HD / 16;          // k-steps of K Q^T == m-tiles of the output
     constexpr bool K4 = fmt_is4(KM), V4 = fmt_is4(VM);
@@ -286,16 +561,23 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
     constexpr int NBK = HD / 32;            // 32-blocks per row
     constexpr int NBV = vsc_blocks(VM, HD);
     constexpr int META = meta_bytes(KM, VM, HD);
+    constexpr uint32_t k_cw4 = code_bytes(KM, HD), k_rsc4 = rsc_byte_off(KM, HD);  // bytes of the codes, offset of rsc0
+    constexpr uint32_t v_cw4 = code_bytes(VM, HD), v_rsc4 = rsc_byte_off(VM, HD);
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem);  // [DW][NS_MAX]
     const int NS = (int)p.ns;
     const uint32_t sbase = smem_u32(smem);
     const uint32_t lut_k = sbase + 128, lut_v = lut_k + 1024, plane_k = lut_v + 1024, plane_v = plane_k + 32;
-    const uint32_t stage_bytes = p.k_stage_bytes + p.v_stage_bytes;
+    // row strides and stage sizes: compile-time when the rows are packed back to back (NAT)
+    const uint32_t krb = NAT ? (uint32_t)nat_row_bytes(KM, HD) : (uint32_t)p.k_ss * 4u;
+    const uint32_t vrb = NAT ? (uint32_t)nat_row_bytes(VM, HD) : (uint32_t)p.v_ss * 4u;
+    const uint32_t k_stage_bytes = NAT ? stage_part_bytes((uint32_t)nat_row_bytes(KM, HD)) : p.k_stage_bytes;
+    const uint32_t v_stage_bytes = NAT ? stage_part_bytes((uint32_t)nat_row_bytes(VM, HD)) : p.v_stage_bytes;
+    const uint32_t stage_bytes = k_stage_bytes + v_stage_bytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
     const uint32_t G = p.group, R = p.rows_per_kv, ny = p.hkv * p.packs;
-    const uint32_t nw = gridDim.x * DW, wid = blockIdx.x * DW + warp;
+    const uint32_t nw_grid = gridDim.x * DW, wid = blockIdx.x * DW + warp;
 
     // ------------------------------------------------------------------ one time set up (the only block barrier)
     if (tid == 0) {
@@ -315,11 +597,12 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
         sts32(plane_k + 4 * tid, v);
     }
     __syncthreads();
-    // the combine kernel may be scheduled from here on; it waits for this grid's completion itself
+    // the next kernel of the stream may be scheduled from here on (a combine grid, or the next attention launched as
+    // a programmatic dependent); it waits for this grid's completion itself before it touches memory
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    B200_T(0);
 
     // ------------------------------------------------------------------ this warp's share of the work
-
     const uint32_t cc = p.col_cost;
     auto batch_cost = [&](uint32_t bb) -> uint32_t {
         const uint32_t t = (uint32_t)make_column(p, bb).tiles;
@@ -359,52 +642,57 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
             total += u;
         }
     }
-    if (total == 0) return;
-    const uint64_t x_begin = total * wid / nw, x_end = total * (wid + 1) / nw;
-    // batch entry that holds cost position x_begin, and the position of its first column
-    uint32_t b0 = 0;
-    uint64_t b0_start = 0;
-    if (p.kv_len == nullptr) {
-        const uint64_t per_b = batch_cost(0);
-        b0 = (uint32_t)(x_begin / per_b);
-        b0_start = (uint64_t)b0 * per_b;
-    } else if (few) {
-        bool found = false;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const uint32_t hit = __ballot_sync(0xffffffffu, fpre[k] + fincl[k] > x_begin);
-            if (hit && !found) {
-                const int l = __ffs(hit) - 1;
-                b0 = 32 * k + l;
-                b0_start = fpre[k] + __shfl_sync(0xffffffffu, fincl[k] - fu[k], l);
-                found = true;
-            }
-        }
-    } else {
-        uint64_t carry = 0;
-        for (uint32_t base = 0; base < p.b; base += 32) {
-            const uint32_t bb = base + lane;
-            const uint32_t u = bb < p.b ? batch_cost(bb) : 0u;
-            uint32_t incl = u;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += t;
-            }
-            const uint32_t hit = __ballot_sync(0xffffffffu, carry + incl > x_begin);
-            if (hit) {
-                const int l = __ffs(hit) - 1;
-                b0 = base + l;
-                b0_start = carry + __shfl_sync(0xffffffffu, incl - u, l);
-                break;
-            }
-            carry += __shfl_sync(0xffffffffu, incl, 31);
-        }
-    }
-    // first segment: the first tile at or after x_begin (a position inside a column's set up cost
-    // snaps to the column's first tile)
+    // never more workers than cost positions: every worker between the owners of two tiles of a column then owns a
+    // tile of that column itself, so a column's segments are the consecutive workers first owner .. last owner
+    const uint32_t nw = (uint32_t)min((uint64_t)nw_grid, total);
+    bool has_work = wid < nw;
+    uint64_t x_begin = 0, x_end = 0;
     Segment seg;
-    {
+    if (has_work) {
+        x_begin = total * wid / nw;
+        x_end = total * (wid + 1) / nw;
+        // batch entry that holds cost position x_begin, and the position of its first column
+        uint32_t b0 = 0;
+        uint64_t b0_start = 0;
+        if (p.kv_len == nullptr) {
+            const uint64_t per_b = batch_cost(0);
+            b0 = (uint32_t)(x_begin / per_b);
+            b0_start = (uint64_t)b0 * per_b;
+        } else if (few) {
+            bool found = false;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t hit = __ballot_sync(0xffffffffu, fpre[k] + fincl[k] > x_begin);
+                if (hit && !found) {
+                    const int l = __ffs(hit) - 1;
+                    b0 = 32 * k + l;
+                    b0_start = fpre[k] + __shfl_sync(0xffffffffu, fincl[k] - fu[k], l);
+                    found = true;
+                }
+            }
+        } else {
+            uint64_t carry = 0;
+            for (uint32_t base = 0; base < p.b; base += 32) {
+                const uint32_t bb = base + lane;
+                const uint32_t u = bb < p.b ? batch_cost(bb) : 0u;
+                uint32_t incl = u;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += t;
+                }
+                const uint32_t hit = __ballot_sync(0xffffffffu, carry + incl > x_begin);
+                if (hit) {
+                    const int l = __ffs(hit) - 1;
+                    b0 = base + l;
+                    b0_start = carry + __shfl_sync(0xffffffffu, incl - u, l);
+                    break;
+                }
+                carry += __shfl_sync(0xffffffffu, incl, 31);
+            }
+        }
+        // first segment: the first tile at or after x_begin (a position inside a column's set up cost
+        // snaps to the column's first tile)
         seg.b = b0;
         seg.col = make_column(p, b0);
         const uint32_t tb = (uint32_t)seg.col.tiles;
@@ -413,39 +701,56 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
         const uint32_t in_col = (uint32_t)(rem % (tb + cc));
         seg.t0 = in_col > cc ? in_col - cc : 0u;
         seg.x = b0_start + (uint64_t)seg.y * (tb + cc) + cc + seg.t0;
-        if (seg.x >= x_end) return;  // the share lies inside a set up gap: no tile
-        seg.t1 = (uint32_t)min((uint64_t)tb, seg.t0 + (x_end - seg.x));
+        if (seg.x >= x_end) has_work = false;  // the share lies inside a set up gap: no tile
+        else seg.t1 = (uint32_t)min((uint64_t)tb, seg.t0 + (x_end - seg.x));
     }
 
-    // Launched as a programmatic dependent (after_prev), the grid got here, with nothing read but the lengths, while the
-    // stream's previous kernel was still running: the query, the rows and the partial results may be in its hands
-    // until this returns. A no-op after a plain launch.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t krb = (uint32_t)p.k_ss * 4u, vrb = (uint32_t)p.v_ss * 4u;  // row bytes
+
+
     const uint32_t meta_s = sbase + FIXED_SMEM + warp * META;    // [WK][KMW] f32
     const uint32_t vmeta_s = meta_s + WK * KMW * 4;              // [WK] (sigma, log2 sigma)
     const uint32_t vsc_s = vmeta_s + WK * 8;                     // [NBV][WK] f16
-    float *qstage = reinterpret_cast<float *>(smem + FIXED_SMEM + DW * META) + (size_t)warp * PACK * HD;  // only with a rotated cache
     const uint32_t wstage_s = sbase + FIXED_SMEM + DW * META + p.qstage_bytes + (uint32_t)warp * NS * stage_bytes;
     const uint32_t wbar_s = smem_u32(bars + warp * NS_MAX);
-    const uint32_t k_cw4 = (uint32_t)p.k.code_words * 4u, k_rsc4 = (uint32_t)p.k.rsc_off * 4u;
-    const uint32_t v_cw4 = (uint32_t)p.v.code_words * 4u, v_rsc4 = (uint32_t)p.v.rsc_off * 4u;
     const bool plain = p.softcap <= 0.0f && p.alibi == nullptr;  // tiles inside every row's range take the unmasked path
-    const uint32_t prow = min((uint32_t)PACK, R);                // rows of a partial result
     bool wait_failed = false;
 
+    // Launched as a programmatic dependent (after_prev), the grid got here, with nothing read but the lengths, while the
+    // stream's previous kernel was still running. What that kernel may still have in its hands (the outputs, the partial
+    // results, the gather's step word; without the caller's word that the inputs are final also the query and the rows)
+    // is not touched before prev_done() has returned: griddepcontrol.wait returns when the previous kernel has completed
+    // and its writes are visible, and is a no-op after a plain launch. With final inputs a worker gets through the tiles
+    // of its first segment before it has to ask: the step's first keys stream while the previous kernel's last blocks
+    // finish, and only the rows it must not read yet (the last fresh_rows of a sequence) and all stores wait.
+    bool waited = false;
+    uint32_t g_step = 0;   // gathered outputs: this step's number, read once the previous kernel is done
+    size_t g_base = 0;     // and the offset of this rank's rows in the step's slot of every rank's buffer
+    auto prev_done = [&]() {
+        if (waited) return;
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        waited = true;
+        B200_T(2);
+        if (p.ctr && p.world) {
+            g_step = *reinterpret_cast<volatile uint32_t *>(p.step) + 1u;
+            g_base = ((size_t)(g_step & 1u) * p.world + p.rank) * ((size_t)p.b * p.hq * p.lq) * HD;
+        }
+    };
+    if (!p.prefetch) prev_done();
+
     // ------------------------------------------------------------------ the copy side
-    // runs up to NS tiles ahead of the compute side through the same list of segments
+    // runs up to NS tiles ahead of the compute side through the same list of segments; tile t of the worker's list
+    // lives in stage t mod NS, so the copy issued after a tile is consumed goes into the stage just read
     Segment iseg = seg;
     int i_left = 0;          // tiles still to copy in the copy side's segment
+    int i_simple = 0;        // of those, whole tiles that do not end their column: constant copy sizes, no tail handling
     bool i_more = true;      // the copy side has segments left
     uintptr_t i_k = 0, i_v = 0;        // 16-byte aligned global addresses of the next tile's copies
     uint32_t i_koff = 0, i_voff = 0;   // offset of the tile's first row inside its copy
+    uint32_t i_kb = 0, i_vb = 0;       // bytes of a whole tile's copies
     int i_key = 0;                     // first key of the next tile
-    uint32_t i_st = wstage_s, i_bar = wbar_s;  // stage and barrier of the next copy
-    int i_stage = 0;
     auto copy_enter = [&]() {  // per-segment constants of the copy side
         i_left = (int)(iseg.t1 - iseg.t0);
+        i_simple = i_left - (iseg.t1 == (uint32_t)iseg.col.tiles ? 1 : 0);
         const uint32_t hk = iseg.y / p.packs;
         i_key = iseg.col.lo + (int)iseg.t0 * WK;
         const uintptr_t ka = reinterpret_cast<uintptr_t>(p.k_rows + (size_t)iseg.b * p.k_sb + (size_t)hk * p.k_sh) + (uintptr_t)(uint32_t)i_key * krb;
@@ -454,62 +759,118 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
         i_voff = (uint32_t)(va & 15u);
         i_k = ka - i_koff;
         i_v = va - i_voff;
+        i_kb = (i_koff + (uint32_t)WK * krb + 15u) & ~15u;
+        i_vb = (i_voff + (uint32_t)WK * vrb + 15u) & ~15u;
     };
-    copy_enter();
-    // copies the next tile (the caller checked i_left > 0) and moves on
-    auto copy_tile = [&]() {
-        const int nkeys = min(WK, iseg.col.hi - i_key);
-        // Rows below lk are readable, and so is the row after a tile when the cache has spare rows
-        // (rows_cap): the 16-byte round up of a copy may then run into the next row. Otherwise the
-        // last tile of a sequence copies the round down and fetches the few remaining words with
-        // plain loads.
-        const bool tail = i_key + nkeys >= iseg.col.lk && i_key + nkeys >= (int)p.rows_cap;
-        uint32_t kb = (i_koff + (uint32_t)nkeys * krb + 15u) & ~15u, vb = (i_voff + (uint32_t)nkeys * vrb + 15u) & ~15u;
-        if (tail) {
-            const uint32_t ke = i_koff + (uint32_t)nkeys * krb, ve = i_voff + (uint32_t)nkeys * vrb;  // ends, from the copy start
-            kb = ke & ~15u;
-            vb = ve & ~15u;
-            if (lane < 4) {
-                const uint32_t o = kb + 4u * lane;
-                if (o >= i_koff && o < ke) sts32(i_st + o, *reinterpret_cast<const uint32_t *>(i_k + o));
-            } else if (lane < 8) {
-                const uint32_t o = vb + 4u * (lane - 4);
-                if (o >= i_voff && o < ve) sts32(i_st + p.k_stage_bytes + o, *reinterpret_cast<const uint32_t *>(i_v + o));
+    if (has_work) copy_enter();
+    // copies the next tile into stage `st` with barrier `bar` (the caller checked i_left > 0) and moves on
+    auto copy_tile = [&](uint32_t st, uint32_t bar) {
+        if (!waited && i_key + min(WK, iseg.col.hi - i_key) > iseg.col.lk - (int)p.fresh_rows) prev_done();
+        if (i_simple > 0) {
+            --i_simple;
+            if (lane == 0) {
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(i_kb + i_vb) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(st), "l"(i_k),
+                             "r"(i_kb), "r"(bar)
+                             : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(st + k_stage_bytes),
+                             "l"(i_v), "r"(i_vb), "r"(bar)
+                             : "memory");
             }
-            __syncwarp();
-        }
-        if (lane == 0) {
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(i_bar), "r"(kb + vb) : "memory");
-            if (kb)
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(i_st),
-                             "l"(i_k), "r"(kb), "r"(i_bar)
-                             : "memory");
-            if (vb)
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                 i_st + p.k_stage_bytes),
-                             "l"(i_v), "r"(vb), "r"(i_bar)
-                             : "memory");
+        } else {
+            // the last tile of its column
+            const int nkeys = min(WK, iseg.col.hi - i_key);
+            // Rows below lk are readable, and so is the row after a tile when the cache has spare rows
+            // (rows_cap): the 16-byte round up of a copy may then run into the next row. Otherwise the
+            // last tile of a sequence copies the round down and fetches the few remaining words with
+            // plain loads.
+            const bool tail = i_key + nkeys >= iseg.col.lk && i_key + nkeys >= (int)p.rows_cap;
+            uint32_t kb = (i_koff + (uint32_t)nkeys * krb + 15u) & ~15u, vb = (i_voff + (uint32_t)nkeys * vrb + 15u) & ~15u;
+            if (tail) {
+                const uint32_t ke = i_koff + (uint32_t)nkeys * krb, ve = i_voff + (uint32_t)nkeys * vrb;  // ends, from the copy start
+                kb = ke & ~15u;
+                vb = ve & ~15u;
+                if (lane < 4) {
+                    const uint32_t o = kb + 4u * lane;
+                    if (o >= i_koff && o < ke) sts32(st + o, *reinterpret_cast<const uint32_t *>(i_k + o));
+                } else if (lane < 8) {
+                    const uint32_t o = vb + 4u * (lane - 4);
+                    if (o >= i_voff && o < ve) sts32(st + k_stage_bytes + o, *reinterpret_cast<const uint32_t *>(i_v + o));
+                }
+                __syncwarp();
+            }
+            if (lane == 0) {
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kb + vb) : "memory");
+                if (kb)
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(st),
+                                 "l"(i_k), "r"(kb), "r"(bar)
+                                 : "memory");
+                if (vb)
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                     st + k_stage_bytes),
+                                 "l"(i_v), "r"(vb), "r"(bar)
+                                 : "memory");
+            }
         }
         // WK rows are a multiple of 16 bytes: the next tile keeps its offset inside its copy
         i_k += (uintptr_t)WK * krb;
         i_v += (uintptr_t)WK * vrb;
         i_key += WK;
-        i_st += stage_bytes;
-        i_bar += 8;
-        if (++i_stage == NS) {
-            i_stage = 0;
-            i_st = wstage_s;
-            i_bar = wbar_s;
-        }
         if (--i_left == 0 && i_more) {
             i_more = next_segment(iseg, p, ny, x_end);
             if (i_more) copy_enter();
         }
     };
-    // The first tile alone, the other stages once the first query rows are loaded: with every worker of the grid asking
-    // for all its stages at once, the first tiles would arrive behind 26 MB of later ones.
-    int prime = NS - 1;
-    if (i_left > 0) copy_tile();
+    // Filling the ring. With the caller's word that the inputs are final (prefetch) all stages are asked for right away.
+    // Otherwise the first tile alone, and the other stages once the first query rows are loaded: with every worker of
+    // the grid asking for all its stages at once, the first tiles would arrive behind 26 MB of later ones.
+    int primed = 0;
+    auto prime = [&](int upto) {
+        for (; primed < upto && i_left > 0; ++primed) copy_tile(wstage_s + (uint32_t)primed * stage_bytes, wbar_s + 8u * (uint32_t)primed);
+    };
+    if (has_work) prime(p.prefetch ? NS : 1);
+
+    const uint32_t prow = min((uint32_t)PACK, R);                // rows of a partial result
+    float *qstage = reinterpret_cast<float *>(smem + FIXED_SMEM + DW * META) + (size_t)warp * PACK * HD;  // only with a rotated cache
+    const uint32_t ncols = p.b * ny;
+    // a column of this call is finished (its rows are stored): with gathered outputs the worker that finishes the last
+    // one publishes the step to the other ranks
+    auto column_done = [&]() {
+        if (!p.world) return;
+        __threadfence_system();
+        __syncwarp();
+        uint32_t last = 0;
+        if (lane == 0) last = atomicInc(p.done_ctr, ncols - 1u) == ncols - 1u ? 1u : 0u;
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+            __threadfence_system();
+            gather_publish(p.peer_flags, p.world, p.rank, p.step, g_step, p.gather_polls, p.status, p.lib_status, lane);
+        }
+    };
+    // columns without a visible key get no worker: their rows are zeros, written once the previous kernel is done
+    auto zero_columns = [&]() {
+        if (!(p.ctr && (p.kv_len != nullptr || !has_work))) return;
+        prev_done();
+        for (uint32_t col = wid; col < ncols; col += nw_grid) {
+            const uint32_t b = col / ny, y = col - b * ny;
+            if (make_column(p, b).tiles != 0) continue;
+            float z[HD / 32];
+#pragma unroll
+            for (int k = 0; k < HD / 32; ++k) z[k] = 0.0f;
+            for (uint32_t rr = 0; rr < prow; ++rr) {
+                size_t obase, grow;
+                if (!row_addr(p, b, y, rr, obase, grow)) break;
+                store_row_piece<HD / 32>(p.out, obase + (size_t)lane * (HD / 32), z, p.out_dtype);
+                for (uint32_t pr = 0; pr < p.world; ++pr)
+                    store_row_piece<HD / 32>(p.peer_bufs[pr], g_base + grow * HD + (size_t)lane * (HD / 32), z, p.out_dtype);
+            }
+            column_done();
+        }
+    };
+    if (!has_work) {
+        zero_columns();
+        return;
+    }
 
     // ------------------------------------------------------------------ the compute side
     // lane offsets inside a tile: K rows g (and g + 8), V rows 2c (and 2c + 1, 2c + 8, 2c + 9)
@@ -518,7 +879,7 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
     const uint32_t mrow_g = meta_s + g * KMW * 4, vmeta_g = vmeta_s + g * 8, vsc_c = vsc_s + 4 * c;
     uint32_t c_st = wstage_s, c_bar = wbar_s;
     int c_stage = 0;
-    uint32_t phases = 0;  // bit s: parity to wait for on stage s
+    uint32_t par = 0;  // parity to wait for on the current stage: flips every time the ring wraps
 
     uint32_t qb0[STEPS], qb1[STEPS];
     float qs[2], qs2[2];
@@ -679,6 +1040,9 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
         }
     };
 
+#ifdef B200_TRACE
+    bool traced_first = false;
+#endif
     bool more = true;
     while (more) {
         // ================================================================ segment set up
@@ -704,6 +1068,12 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
             row_range(pack * PACK, lo, hi, pos);
             HImin = hi;
         }
+        // running maxima (log2 domain, value scale folded in) and partial normalizers of rows 2c, 2c + 1
+        float M[2] = {-1e30f, -1e30f}, lsum[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int mt = 0; mt < STEPS; ++mt) oacc[mt][0] = oacc[mt][1] = oacc[mt][2] = oacc[mt][3] = 0.0f;
+
+        if (!wait_failed) {
         // query row g of the pack: power of two normalization, then the f16 B fragments of K Q^T. Per
         // k-step the four contraction slots of this lane are the consecutive dims dbase(s) ... + 3,
         // so the four lanes of a quad hold the whole row between them.
@@ -789,23 +1159,18 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
             }
         }
 
-        for (; prime > 0; --prime)
-            if (i_left > 0) copy_tile();
-        // running maxima (log2 domain, value scale folded in) and partial normalizers of rows 2c, 2c + 1
-        float M[2] = {-1e30f, -1e30f}, lsum[2] = {0.0f, 0.0f};
-#pragma unroll
-        for (int mt = 0; mt < STEPS; ++mt) oacc[mt][0] = oacc[mt][1] = oacc[mt][2] = oacc[mt][3] = 0.0f;
+        // the other stages of the ring (first segment only)
+        prime(NS);
 
         // ================================================================ the tiles of the segment
         const int n_t = (int)(seg.t1 - seg.t0);
         int key0 = col.lo + (int)seg.t0 * WK;
         const uint32_t koff = (uint32_t)((reinterpret_cast<uintptr_t>(p.k_rows + (size_t)seg.b * p.k_sb + (size_t)hk * p.k_sh) + (uintptr_t)(uint32_t)key0 * krb) & 15u);
         const uint32_t voff = (uint32_t)((reinterpret_cast<uintptr_t>(p.v_rows + (size_t)seg.b * p.v_sb + (size_t)hk * p.v_sh) + (uintptr_t)(uint32_t)key0 * vrb) & 15u);
-        const uint32_t kt_off = koff + k_lane, vt_off = p.k_stage_bytes + voff + v_lane;
-        const uint32_t kr_off = koff + lane * krb, vr_off = p.k_stage_bytes + voff + lane * vrb;
-        for (int n = 0; n < n_t && !wait_failed; ++n, key0 += WK) {
+        const uint32_t kt_off = koff + k_lane, vt_off = k_stage_bytes + voff + v_lane;
+        const uint32_t kr_off = koff + lane * krb, vr_off = k_stage_bytes + voff + lane * vrb;
+        for (int n = 0; n < n_t; ++n, key0 += WK) {
             {
-                const uint32_t par = (phases >> c_stage) & 1u;
                 uint32_t ok = 0;
                 for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin)
                     asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
@@ -813,22 +1178,29 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                                  : "r"(c_bar), "r"(par)
                                  : "memory");
                 if (!ok) {
+                    // the copy never landed: give up on the keys (the outputs are void, the status says so), stop
+                    // copying, but keep counting this worker's segments so that no column waits for it
                     wait_failed = true;
+                    i_left = 0;
+                    i_more = false;
                     break;
                 }
-                phases ^= 1u << c_stage;
             }
 
+#ifdef B200_TRACE
+            if (!traced_first) { traced_first = true; B200_T(3); }
+#endif
             const uint32_t st_s = c_st;
             const int nkeys = min(WK, col.hi - key0);
             if (nkeys < WK) {
                 // rows past the column hold stale bytes: clear them so that masked keys decode to finite values
-                const uint32_t kt = st_s + koff, vt = st_s + p.k_stage_bytes + voff;
+                const uint32_t kt = st_s + koff, vt = st_s + k_stage_bytes + voff;
                 for (uint32_t w = nkeys * (krb >> 2) + lane; w < WK * (krb >> 2); w += 32) sts32(kt + 4 * w, 0u);
                 for (uint32_t w = nkeys * (vrb >> 2) + lane; w < WK * (vrb >> 2); w += 32) sts32(vt + 4 * w, 0u);
                 __syncwarp();
             }
             // ---- per-key scalars of the tile, lane = key
+#if !(B200_ABL & 4)
             {
                 const uint32_t kr = st_s + kr_off, vr = st_s + vr_off;
                 const float k0 = u2f(lds32(kr + k_rsc4));
@@ -837,9 +1209,16 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                     for (int w = 0; w < (NBK + 3) / 4; ++w) {
                         const uint32_t aux = lds32(kr + k_cw4 + 4 * w);
                         // rsc0 * 2^(e - 127); a zero code gives +0 (its block holds zero codes)
+                        float sc[4];
 #pragma unroll
-                        for (int i = 0; i < 4 && 4 * w + i < KMW; ++i)
-                            sts32(meta_s + (lane * KMW + 4 * w + i) * 4, f2u(k0 * u2f(((aux >> (8 * i)) & 0xffu) << 23)));
+                        for (int i = 0; i < 4; ++i) sc[i] = k0 * u2f(((aux >> (8 * i)) & 0xffu) << 23);
+                        if constexpr (KMW >= 4) {
+                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(meta_s + (lane * KMW + 4 * w) * 4), "f"(sc[0]), "f"(sc[1]),
+                                         "f"(sc[2]), "f"(sc[3])
+                                         : "memory");
+                        } else {
+                            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(meta_s + lane * KMW * 4), "f"(sc[0]), "f"(sc[1]) : "memory");
+                        }
                     }
                 } else {
                     sts32(meta_s + lane * 4, f2u(k0));
@@ -874,20 +1253,29 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                 // sigma in [2^-100, 2^100], or 0 (then log2 = -inf: the key only counts in the normalizer)
                 float sc = fminf(fmaxf(sigma, 7.8886091e-31f), 1.2676506e30f);
                 sc = sigma > 0.0f ? sc : 0.0f;
-                sts32(vmeta_s + lane * 8, f2u(sc));
-                sts32(vmeta_s + lane * 8 + 4, f2u(fast_log2(sc)));
+                asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(vmeta_s + lane * 8), "f"(sc), "f"(fast_log2(sc)) : "memory");
                 __syncwarp();
             }
+#endif
             // ---- scores of the 32 keys: sr[u][2 k + e] = key 16 u + g + 8 k, row 2c + e
             float sr[2][4];
+#if (B200_ABL & 1)
+            for (int u = 0; u < 2; ++u) for (int e = 0; e < 4; ++e) sr[u][e] = 0.001f * (float)(lane + e);
+#else
             k_scores(st_s + kt_off, mrow_g, sr[0]);
             k_scores(st_s + kt_off + 16 * krb, mrow_g + 16 * KMW * 4, sr[1]);
+#endif
             // ---- online softmax
             float2 vm[4];  // (sigma, log2 sigma) of the keys g, g + 8, g + 16, g + 24
 #pragma unroll
             for (int k = 0; k < 4; ++k) vm[k] = lds64f(vmeta_g + k * 64);
             uint32_t pb[4];
+#if (B200_ABL & 8)
+            for (int k = 0; k < 4; ++k) pb[k] = f2u(sr[k >> 1][k & 1] + vm[k].x);
+            if (false) {
+#else
             if (plain && nkeys == WK && key0 >= LOmax && key0 + WK <= HImin) {
+#endif
                 // every key visible to every row: scale, maximum check and exponent in fused multiply-adds
                 float c0 = fmaxf(fmaxf(fmaf(sr[0][0], qs2[0], vm[0].y), fmaf(sr[0][2], qs2[0], vm[1].y)),
                                  fmaxf(fmaf(sr[1][0], qs2[0], vm[2].y), fmaf(sr[1][2], qs2[0], vm[3].y)));
@@ -974,40 +1362,65 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                 }
             }
             // ---- O^T += V^T P^T
+#if (B200_ABL & 2)
+            oacc[0][0] += u2f(pb[0] ^ pb[1] ^ pb[2] ^ pb[3]);
+#else
             v_accum(st_s + vt_off, vsc_c, pb[0], pb[1]);
             v_accum(st_s + vt_off + 16 * vrb, vsc_c + 32, pb[2], pb[3]);
+#endif
             // the stage was read (and possibly patched) through the generic proxy: order that before the
             // bulk copy of the next tile into it
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
+            if (i_left > 0) copy_tile(c_st, c_bar);
             c_st += stage_bytes;
             c_bar += 8;
             if (++c_stage == NS) {
                 c_stage = 0;
                 c_st = wstage_s;
                 c_bar = wbar_s;
+                par ^= 1u;
             }
-            if (i_left > 0) copy_tile();
         }
+        }  // !wait_failed
 
         // ================================================================ this warp's partial result of the column
+        B200_T(4);
+        prev_done();
 #pragma unroll
         for (int o = 4; o < 32; o <<= 1) {
             lsum[0] += __shfl_xor_sync(0xffffffffu, lsum[0], o);
             lsum[1] += __shfl_xor_sync(0xffffffffu, lsum[1], o);
         }
         const uint32_t colidx = seg.b * ny + seg.y;
-        if (seg.t0 == 0 && lane == 0) {
-            // the worker that owns the first tile of a column publishes where its segments are
-            const uint32_t last_owner = owner_of(seg.x + col.tiles - 1, total, nw);
-            p.meta[2 * (size_t)colidx] = (int32_t)(wid + colidx);
-            p.meta[2 * (size_t)colidx + 1] = (int32_t)(last_owner - wid + 1);
-        }
-        {
+        const float inv0 = lsum[0] > 0.0f ? 1.0f / lsum[0] : 0.0f, inv1 = lsum[1] > 0.0f ? 1.0f / lsum[1] : 0.0f;
+        const uint32_t rr0 = 2 * c, rr1 = 2 * c + 1;
+        const bool w0 = rr0 < prow && pack * PACK + rr0 < R, w1 = rr1 < prow && pack * PACK + rr1 < R;
+        // the column's segments are the workers first .. last (consecutive, every one of them owns a tile of it)
+        const uint64_t x_col = seg.x - seg.t0;  // cost position of the column's first tile
+        const uint32_t first = seg.t0 == 0 ? wid : owner_of(x_col, total, nw);
+        const uint32_t last = seg.t1 == (uint32_t)col.tiles ? wid : owner_of(x_col + col.tiles - 1, total, nw);
+        const uint32_t nseg = last - first + 1;
+        if (p.ctr && nseg == 1 && p.v.rot != B200_ROT_HADAMARD) {
+            // the whole column in this worker's registers: rows 2c, 2c + 1, dims [g HD/8, (g + 1) HD/8)
+            float o0[HD / 8], o1[HD / 8];
+#pragma unroll
+            for (int mt = 0; mt < STEPS; ++mt) {
+                o0[2 * mt] = oacc[mt][0] * inv0; o0[2 * mt + 1] = oacc[mt][2] * inv0;
+                o1[2 * mt] = oacc[mt][1] * inv1; o1[2 * mt + 1] = oacc[mt][3] * inv1;
+            }
+            size_t obase, grow;
+            if (w0 && row_addr(p, seg.b, seg.y, rr0, obase, grow)) {
+                store_row_piece<HD / 8>(p.out, obase + g * (HD / 8), o0, p.out_dtype);
+                for (uint32_t pr = 0; pr < p.world; ++pr) store_row_piece<HD / 8>(p.peer_bufs[pr], g_base + grow * HD + g * (HD / 8), o0, p.out_dtype);
+            }
+            if (w1 && row_addr(p, seg.b, seg.y, rr1, obase, grow)) {
+                store_row_piece<HD / 8>(p.out, obase + g * (HD / 8), o1, p.out_dtype);
+                for (uint32_t pr = 0; pr < p.world; ++pr) store_row_piece<HD / 8>(p.peer_bufs[pr], g_base + grow * HD + g * (HD / 8), o1, p.out_dtype);
+            }
+            column_done();
+        } else {
             const size_t slot = (size_t)wid + colidx;
-            const float inv0 = lsum[0] > 0.0f ? 1.0f / lsum[0] : 0.0f, inv1 = lsum[1] > 0.0f ? 1.0f / lsum[1] : 0.0f;
-            const uint32_t rr0 = 2 * c, rr1 = 2 * c + 1;
-            const bool w0 = rr0 < prow && pack * PACK + rr0 < R, w1 = rr1 < prow && pack * PACK + rr1 < R;
             float *po0 = p.part_o + (slot * prow + rr0) * HD + g * (HD / 8);
             float *po1 = p.part_o + (slot * prow + rr1) * HD + g * (HD / 8);
 #pragma unroll
@@ -1019,11 +1432,35 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                 if (w0) p.part_lse[slot * prow + rr0] = lsum[0] > 0.0f ? M[0] * LN2 + logf(lsum[0]) : -INFINITY;
                 if (w1) p.part_lse[slot * prow + rr1] = lsum[1] > 0.0f ? M[1] * LN2 + logf(lsum[1]) : -INFINITY;
             }
+            if (p.ctr) {
+                // count this segment; the last of the column's workers to get here merges them all
+                __threadfence();
+                __syncwarp();
+                uint32_t merge = 0;
+                if (lane == 0) merge = atomicInc(p.ctr + colidx, nseg - 1u) == nseg - 1u ? 1u : 0u;
+                merge = __shfl_sync(0xffffffffu, merge, 0);
+                if (merge) {
+                    __threadfence();
+                    const size_t slot0 = (size_t)first + colidx;
+                    if (prow <= 4) merge_column<HD, 8>(p, seg.b, seg.y, slot0, (int)nseg, prow, g_base, qstage, lane);
+                    else merge_column<HD, 4>(p, seg.b, seg.y, slot0, (int)nseg, prow, g_base, qstage, lane);
+                    column_done();
+                }
+            } else if (seg.t0 == 0 && lane == 0) {
+                // the worker that owns the first tile of a column publishes where its segments are (for the combine grid)
+                p.meta[2 * (size_t)colidx] = (int32_t)(wid + colidx);
+                p.meta[2 * (size_t)colidx + 1] = (int32_t)nseg;
+            }
         }
 
         more = next_segment(seg, p, ny, x_end);
     }
-    if (wait_failed && p.status) atomicExch(p.status, 1);
+    zero_columns();
+    B200_T(5);
+    if (wait_failed) {
+        if (p.status) atomicExch(p.status, 1);
+        if (p.lib_status) atomicExch(p.lib_status, 1);
+    }
 }
 
 // Merges the partial results of one output row (candle-core/kernels/turbo_quant_impl.h:659-685),
@@ -1142,37 +1579,12 @@ __global__ void __launch_bounds__(128) tq_combine_kernel(const DecodeParams p) {
     }
 }
 
-// The same merge for rows with few segments (the host picks it when the workers outnumber the columns by less
-// than eight to one). One warp per output row, four rows per block: lane l owns the elements [l HD/32, (l + 1) HD/32)
-// of the row, so a
-// segment's partial row is one vector load per lane, the loads of the first segments are issued before the
-// weights are known, and no barrier or shared memory sits between the warps. The grid fits on the device at once
-// (rows beyond that are looped over): the blocks are resident, waiting, when the decode grid ends.
-
-// EPL consecutive elements of a row, cast to the output type: one vector store for 16-bit types on an 8-byte boundary
-template <int EPL>
-__device__ __forceinline__ void store_row_piece(void *out, size_t off, const float (&v)[EPL], int dt) {
-    if constexpr (EPL % 4 == 0) {
-        if ((dt == B200_F16 || dt == B200_BF16) && ((reinterpret_cast<uintptr_t>(out) + 2 * off) & 7u) == 0) {
-            uint16_t *o16 = reinterpret_cast<uint16_t *>(out) + off;
-#pragma unroll
-            for (int q = 0; q < EPL / 4; ++q) {
-                uint32_t w[2];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint32_t lo = dt == B200_F16 ? f_to_f16_bits(v[4 * q + 2 * h]) : f_to_bf16_bits(v[4 * q + 2 * h]);
-                    const uint32_t hi = dt == B200_F16 ? f_to_f16_bits(v[4 * q + 2 * h + 1]) : f_to_bf16_bits(v[4 * q + 2 * h + 1]);
-                    w[h] = lo | (hi << 16);
-                }
-                *reinterpret_cast<uint2 *>(o16 + 4 * q) = make_uint2(w[0], w[1]);
-            }
-            return;
-        }
-    }
-#pragma unroll
-    for (int k = 0; k < EPL; ++k) store_elem_rt(out, off + k, v[k], dt);
-}
-
+// The same merge for rows with few segments, as a grid of its own (the host picks it when the decode grid cannot
+// merge in place: more columns than it has arrival counters for). One warp per output row, four rows per block:
+// lane l owns the elements [l HD/32, (l + 1) HD/32) of the row, so a segment's partial row is one vector load per
+// lane, the loads of the first segments are issued before the weights are known, and no barrier or shared memory
+// sits between the warps. The grid fits on the device at once (rows beyond that are looped over): the blocks are
+// resident, waiting, when the decode grid ends.
 template <int HD>
 __global__ void __launch_bounds__(128) tq_combine_rows_kernel(const DecodeParams p) {
     constexpr int EPL = HD / 32;  // consecutive elements of a row per lane
@@ -1198,88 +1610,19 @@ __global__ void __launch_bounds__(128) tq_combine_rows_kernel(const DecodeParams
         const uint32_t b = (uint32_t)(row / ((size_t)p.lq * p.hq));
         const uint32_t hk = h / p.group, r = i * p.group + h % p.group;
         const uint32_t y = hk * p.packs + r / PACK, rr = r % PACK;
-        const size_t obase = b * p.o_sb + h * p.o_sh + i * p.o_ss + (size_t)lane * EPL;
+        const size_t obase = b * p.o_sb + h * p.o_sh + i * p.o_ss;
         const size_t col = (size_t)b * ny + y;
         float acc[EPL];
-#pragma unroll
-        for (int k = 0; k < EPL; ++k) acc[k] = 0.0f;
-        if (make_column(p, b).tiles != 0) {  // otherwise nothing was written for the row: zeros
+        const bool any = make_column(p, b).tiles != 0;  // otherwise nothing was written for the row: zeros
+        if (any) {
             const int2 fm = *reinterpret_cast<const int2 *>(p.meta + 2 * col);
-            const int first = fm.x, ns = fm.y;
-            const size_t slot0 = (size_t)first * prow + rr;
-            const float *po = p.part_o + slot0 * HD + lane * EPL;
-            const size_t seg_stride = (size_t)prow * HD;
-            // the first four segments' rows are requested before the log-sum-exps are looked at
-            float pre[4][EPL];
+            const size_t slot0 = (size_t)fm.x * prow + rr;
+            merge_row<HD>(p.part_o + slot0 * HD + lane * EPL, p.part_lse + slot0, fm.y, (size_t)prow * HD, prow, lane, acc);
+        } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (j < ns) {
-#pragma unroll
-                    for (int q = 0; q < EPL / 2; ++q) {
-                        const float2 v = *reinterpret_cast<const float2 *>(po + (size_t)j * seg_stride + 2 * q);
-                        pre[j][2 * q] = v.x;
-                        pre[j][2 * q + 1] = v.y;
-                    }
-                } else {
-#pragma unroll
-                    for (int k = 0; k < EPL; ++k) pre[j][k] = 0.0f;
-                }
-            }
-            float mx = -INFINITY;
-            for (int s0 = lane; s0 < ns; s0 += 32) mx = fmaxf(mx, p.part_lse[slot0 + (size_t)s0 * prow]);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            float wsum = 0.0f;
-            for (int base = 0; base < ns; base += 32) {  // lane l weighs segment base + l
-                const int sl = base + lane;
-                float wl = 0.0f;
-                if (sl < ns) {
-                    const float e = p.part_lse[slot0 + (size_t)sl * prow];
-                    wl = e == -INFINITY ? 0.0f : expf(e - mx);
-                }
-                wsum += wl;
-                const int cnt = min(32, ns - base);
-                int j = 0;
-                if (base == 0) {
-                    // the four rows in registers (segments past the last one weigh nothing)
-#pragma unroll
-                    for (; j < 4; ++j) {
-                        const float w = __shfl_sync(0xffffffffu, wl, j);
-#pragma unroll
-                        for (int k = 0; k < EPL; ++k) acc[k] = fmaf(w, pre[j][k], acc[k]);
-                    }
-                }
-#pragma unroll 4
-                for (; j < cnt; ++j) {
-                    const float w = __shfl_sync(0xffffffffu, wl, j);
-                    const float *src = po + (size_t)(base + j) * seg_stride;
-#pragma unroll
-                    for (int q = 0; q < EPL / 2; ++q) {
-                        const float2 v = *reinterpret_cast<const float2 *>(src + 2 * q);
-                        acc[2 * q] = fmaf(w, v.x, acc[2 * q]);
-                        acc[2 * q + 1] = fmaf(w, v.y, acc[2 * q + 1]);
-                    }
-                }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
-#pragma unroll
-            for (int k = 0; k < EPL; ++k) acc[k] = wsum > 0.0f ? acc[k] / wsum : 0.0f;
-            if (p.v.rot == B200_ROT_HADAMARD) {
-                float *rb = rot[warp];
-                __syncwarp();
-#pragma unroll
-                for (int k = 0; k < EPL; ++k) rb[lane * EPL + k] = acc[k];
-                __syncwarp();
-                warp_hadamard(rb, HD, p.v.signs, false, lane);
-                __syncwarp();
-#pragma unroll
-                for (int k = 0; k < EPL; ++k) acc[k] = rb[lane * EPL + k];
-            }
+            for (int k = 0; k < EPL; ++k) acc[k] = 0.0f;
         }
-        store_row_piece<EPL>(p.out, obase, acc, p.out_dtype);
-        // the same row into every rank's gathered buffer: plain stores through the peer mappings
-        for (uint32_t pr = 0; pr < p.world; ++pr) store_row_piece<EPL>(p.peer_bufs[pr], g_base + row * HD + (size_t)lane * EPL, acc, p.out_dtype);
+        finish_row<HD>(p, obase, row, g_base, acc, rot[warp], lane, any);
     }
 }
 

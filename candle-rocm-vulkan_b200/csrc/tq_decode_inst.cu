@@ -8,9 +8,9 @@
 
 namespace b200 {
 
-template <int KM, int VM, int HD>
+template <int KM, int VM, int HD, bool NAT>
 int launch_decode(const DecodeParams &p, dim3 grid, size_t smem, cudaStream_t stream) {
-    auto kern = tq_decode_kernel<KM, VM, HD>;
+    auto kern = tq_decode_kernel<KM, VM, HD, NAT>;
     static thread_local size_t configured[16] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -38,15 +38,21 @@ int launch_decode(const DecodeParams &p, dim3 grid, size_t smem, cudaStream_t st
     return check_launch("tq_attention");
 }
 
-#define INST(VM)                                                                                \
-    template int launch_decode<B200_KM, VM, 64>(const DecodeParams &, dim3, size_t, cudaStream_t);  \
-    template int launch_decode<B200_KM, VM, 128>(const DecodeParams &, dim3, size_t, cudaStream_t); \
-    template int launch_decode<B200_KM, VM, 256>(const DecodeParams &, dim3, size_t, cudaStream_t);
+#define INST(VM)                                                                                       \
+    template int launch_decode<B200_KM, VM, 64, false>(const DecodeParams &, dim3, size_t, cudaStream_t);  \
+    template int launch_decode<B200_KM, VM, 128, false>(const DecodeParams &, dim3, size_t, cudaStream_t); \
+    template int launch_decode<B200_KM, VM, 256, false>(const DecodeParams &, dim3, size_t, cudaStream_t);
 
+#ifdef B200_ONLY_SAME_FORMAT  // measurement builds only
+template int launch_decode<B200_KM, B200_KM, 128, false>(const DecodeParams &, dim3, size_t, cudaStream_t);
+#else
 INST(B200_TURBO_MSE)
 INST(B200_MXFP4)
 INST(B200_NVFP4)
 INST(B200_MXFP8)
 INST(B200_FP8_ROW)
+#endif
+// rows packed back to back, keys and values in the same format, head dim 128: row strides as compile-time constants
+template int launch_decode<B200_KM, B200_KM, 128, true>(const DecodeParams &, dim3, size_t, cudaStream_t);
 
 }  // namespace b200

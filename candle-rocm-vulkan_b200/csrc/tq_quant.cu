@@ -27,6 +27,8 @@ struct QuantSideParams {
     int32_t pos0;
     int32_t mode, cb, code_words, aux_words, row_words;
     int32_t rot;
+    uint32_t cap;      // rows per (batch entry, head) slab of the destination; 0 = not given, positions are not checked
+    int32_t *status;   // set to 3 when a row's position lies outside [0, cap): that row is not written
 };
 
 struct QuantParams {
@@ -70,6 +72,11 @@ __global__ void __launch_bounds__(QW * 32) quant_rows_kernel(const QuantParams p
         }
         const char *src = reinterpret_cast<const char *>(sp.src) + (b * sp.s_b + h * sp.s_h + t * sp.s_t) * (uint64_t)dtype_size(DT);
         const int64_t pos = (sp.pos ? (int64_t)sp.pos[b] + sp.pos0 : (int64_t)sp.pos0) + (int64_t)t;
+        if (pos < 0 || (sp.cap && pos >= (int64_t)sp.cap)) {
+            // a stale or corrupt device position: nothing is written outside the slab (the whole warp takes this branch)
+            if (lane == 0 && sp.status) atomicExch(sp.status, 3);
+            continue;
+        }
         uint32_t *orow = sp.dst + b * sp.c_b + h * sp.c_h + (uint64_t)pos * sp.c_t;
 
         float x[EPL];
@@ -320,11 +327,18 @@ __global__ void __launch_bounds__(Q128_WARPS * 32) quant_rows128_kernel(const Qu
     const uint32_t rows = p.nb * p.nh * p.nt;
     const uint32_t mode = sp.mode;
     for (uint32_t base = (blockIdx.x * Q128_WARPS + (threadIdx.x >> 5)) * Q128_RPW; base < rows; base += gridDim.x * Q128_WARPS * Q128_RPW) {
-        const bool live = base + (lane >> 3) < rows;  // a row past the end repeats the last one and stores nothing
+        bool live = base + (lane >> 3) < rows;  // a row past the end repeats the last one and stores nothing
         const uint32_t row = live ? base + (lane >> 3) : rows - 1;
         const uint32_t bh = fastdiv(row, p.nt_mul, p.nt_shr), t = row - bh * p.nt, b = fastdiv(bh, p.nh_mul, p.nh_shr), h = bh - b * p.nh;
         const char *src = reinterpret_cast<const char *>(sp.src) + (b * sp.s_b + h * sp.s_h + t * sp.s_t) * (uint64_t)dtype_size(DT);
-        const int64_t pos = (sp.pos ? (int64_t)sp.pos[b] + sp.pos0 : (int64_t)sp.pos0) + (int64_t)t;
+        int64_t pos = (sp.pos ? (int64_t)sp.pos[b] + sp.pos0 : (int64_t)sp.pos0) + (int64_t)t;
+        if (pos < 0 || (sp.cap && pos >= (int64_t)sp.cap)) {
+            // a stale or corrupt device position: the row is computed like the others (the lanes of a row shuffle among
+            // themselves) but nothing is written outside the slab
+            if (live && l8 == 0 && sp.status) atomicExch(sp.status, 3);
+            live = false;
+            pos = 0;
+        }
         uint32_t *orow = sp.dst + b * sp.c_b + h * sp.c_h + (uint64_t)pos * sp.c_t;
         float x[16];
         load16<DT>(src, l8, x);
@@ -626,6 +640,9 @@ extern "C" int b200_kv_append(const B200KvAppendArgs *a, b200_stream_t stream) {
     if (a->src_dtype != B200_F32 && a->src_dtype != B200_F16 && a->src_dtype != B200_BF16)
         return set_error(B200_ERR_BAD_ARG, "kv_append: source dtype must be f32, f16 or bf16");
     if (!a->pos && a->pos0 < 0) return set_error(B200_ERR_BAD_ARG, "kv_append: negative position");
+    if (!a->pos && a->cap && (uint64_t)a->pos0 + a->t > (uint64_t)a->cap)
+        return set_error(B200_ERR_BAD_ARG, "kv_append: rows [%d, %llu) do not fit a cache of %u rows", a->pos0,
+                         (unsigned long long)a->pos0 + a->t, a->cap);
     QuantParams p;
     memset(&p, 0, sizeof(p));
     int rc = fill_side(p.side[0], a->kq, a->d);
@@ -648,6 +665,8 @@ extern "C" int b200_kv_append(const B200KvAppendArgs *a, b200_stream_t stream) {
         sp.c_t = cs[s][2];
         sp.pos = a->pos;
         sp.pos0 = a->pos0;
+        sp.cap = a->cap;
+        sp.status = a->status;
         if (sp.c_t < (uint64_t)sp.row_words) return set_error(B200_ERR_BAD_ARG, "kv_append: cache row stride below the row size");
     }
     p.nb = a->b;

@@ -222,9 +222,10 @@ class TurboQuantizer:
         return self.dequantize_rows(q.data).reshape(q.shape).to(q.dtype)
 
 
-def _kv_append(k, v, k_cache, v_cache, kq: TurboQuantizer, vq: TurboQuantizer, pos, pos_add: int = 0):
+def _kv_append(k, v, k_cache, v_cache, kq: TurboQuantizer, vq: TurboQuantizer, pos, pos_add: int = 0, status=None):
     """b200_kv_append over (b, hkv, t, d) tensors and (b, hkv, cap, words) caches. `pos`: int or an
-    int32 device tensor with one position per batch entry, to which `pos_add` is added."""
+    int32 device tensor with one position per batch entry, to which `pos_add` is added. Rows whose
+    device position falls outside the cache are skipped (`status`, an int32 device tensor, is set to 3)."""
     b, h, t, d = k.shape
     if k.stride(3) != 1:
         k = k.contiguous()
@@ -235,7 +236,8 @@ def _kv_append(k, v, k_cache, v_cache, kq: TurboQuantizer, vq: TurboQuantizer, p
         k.data_ptr(), v.data_ptr(), A.u64x3(*k.stride()[:3]), A.u64x3(*v.stride()[:3]),
         k_cache.data_ptr(), v_cache.data_ptr(), A.u64x3(*k_cache.stride()[:3]), A.u64x3(*v_cache.stride()[:3]),
         pos_t.data_ptr() if pos_t is not None else None, int(pos_add) if pos_t is not None else int(pos) + int(pos_add),
-        b, h, t, d, _dtype_id(k), kq.side(), vq.side())
+        b, h, t, d, _dtype_id(k), kq.side(), vq.side(), min(k_cache.shape[2], v_cache.shape[2]),
+        status.data_ptr() if status is not None else None)
     A.check(A.lib().b200_kv_append(C.byref(args), _stream(k.device)))
 
 
@@ -290,9 +292,13 @@ class PackedAttention:
 
     def __init__(self, q: torch.Tensor, k_rows: torch.Tensor, v_rows: torch.Tensor, kv_len, kq: TurboQuantizer,
                  vq: TurboQuantizer, cfg: FlashAttnConfig, out: Optional[torch.Tensor] = None,
-                 gather: Optional["OutputGather"] = None, after_prev: bool = False, kv_len_add: int = 0):
+                 gather: Optional["OutputGather"] = None, after_prev: bool = False, kv_len_add: int = 0,
+                 fresh_rows: Optional[int] = None, status: Optional[torch.Tensor] = None):
         # after_prev: B200_TQ_AFTER_PREV of include/b200attn.h (the call may start while the stream's previous kernel
-        # still runs; only for callers whose kv_len is not written by that kernel)
+        # still runs; only for callers whose kv_len is not written by that kernel). fresh_rows (with after_prev):
+        # B200_TQ_INPUTS_FINAL, the previous kernel writes none of the inputs but at most that many rows at the end
+        # of every sequence (q included: it must be final before that kernel starts).
+        # status: an int32 device word that the kernels set when a bounded device wait runs out.
         _need_cuda(q, "q")
         b, hq, lq, d = q.shape
         bk, hkv, cap, kw = k_rows.shape
@@ -340,11 +346,14 @@ class PackedAttention:
             A.check(A.lib().b200_tq_attention(C.byref(args), None))  # reports why the call cannot be planned
         ws = _workspace(q.device, nbytes)
         args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
-        args.status = None
+        args.status = status.data_ptr() if status is not None else None
         args.flags = A.TQ_AFTER_PREV if after_prev else 0
+        if after_prev and fresh_rows is not None:
+            args.flags |= A.TQ_INPUTS_FINAL
+            args.fresh_rows = int(fresh_rows)
         args.kv_len_add = int(kv_len_add) if ragged else 0  # tokens appended since the device lengths were written
         self.args, self.out, self.device = args, out, q.device
-        self._keep = (q, k_rows, v_rows, kv_len, kq, vq, alibi, ws)
+        self._keep = (q, k_rows, v_rows, kv_len, kq, vq, alibi, ws, status)
         self._fn, self._ref = A.lib().b200_tq_attention, C.byref(args)
         self._gather = gather
         if gather is not None:

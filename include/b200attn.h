@@ -153,7 +153,11 @@ int b200_tq_rotate(const float *in, float *out, const float *signs, uint64_t row
  * to_dtype(F32) -> matmul with the rotation -> tq_quant -> Cache::append / slice_set
  * (candle-nn/src/kv_cache.rs:68-96), by one launch that reads K and V (b, hkv, t, d), rotates in
  * registers (Hadamard) and writes the packed rows at positions [pos, pos + t) of the capacity
- * buffers (b, hkv, cap, row_words). Without rotation the rows are bit-exact with tq_quant. */
+ * buffers (b, hkv, cap, row_words). Without rotation the rows are bit-exact with tq_quant.
+ * The reference's cache grows or fails before it writes (kv_cache.rs:60-96); here the caller owns the
+ * buffers, so the call is told their capacity: with host positions a write past `cap` is refused
+ * (B200_ERR_BAD_ARG); with device positions a row whose position lies outside [0, cap) is skipped
+ * by the kernel and `status` (if given) is set to 3. cap = 0: positions are not checked. */
 typedef struct B200KvAppendArgs {
     const void *k, *v;        /* device, element strides below, last dim contiguous */
     uint64_t k_strides[3];    /* (batch, head, token) in elements */
@@ -166,6 +170,8 @@ typedef struct B200KvAppendArgs {
     uint32_t b, hkv, t, d;
     int32_t src_dtype;
     B200QuantSide kq, vq;
+    uint32_t cap;             /* rows per (batch entry, head) of both caches; 0 = unchecked */
+    int32_t *status;          /* optional device word, set to 3 when a device position was out of range */
 } B200KvAppendArgs;
 int b200_kv_append(const B200KvAppendArgs *args, b200_stream_t stream);
 
@@ -221,6 +227,8 @@ typedef struct B200TqAttnArgs {
     int32_t kv_len_add;                    /* added to every kv_len_dev entry: the tokens appended since the device
                                             * lengths were written (a serving loop updates them once per graph of
                                             * steps, not per token); sums must not exceed lk; unused without kv_len_dev */
+    uint32_t fresh_rows;                   /* with B200_TQ_INPUTS_FINAL: rows at the end of every sequence that the stream's
+                                            * previous kernel may still be writing (1 after the append of a decode step) */
 } B200TqAttnArgs;
 /* The attention may start while the stream's previous kernel is still running (programmatic dependent launch): its
  * blocks take their places and work out their shares of the keys from kv_len_dev during that kernel's last
@@ -229,6 +237,15 @@ typedef struct B200TqAttnArgs {
  * stream writes kv_len_dev (or the page table: paged calls ignore the flag). The reference has no counterpart: it
  * launches every kernel after the previous one has finished (candle-core/src/cuda_backend/accel.rs:190-252). */
 #define B200_TQ_AFTER_PREV 1u
+/* Together with B200_TQ_AFTER_PREV: the stream's previous kernel writes none of this call's inputs (q, alibi, the
+ * codebooks and signs, kv_len_dev) except the last `fresh_rows` rows of every sequence (rows kv_len - fresh_rows ..
+ * kv_len - 1); everything else was final before that kernel started. The attention then does not wait for that kernel
+ * before it reads: its first keys stream, and its first scores are computed, while the previous kernel's last blocks
+ * still run; it waits before it copies a tile that reaches into the fresh rows and before it stores anything (outputs,
+ * workspace). True for a decode step, whose previous kernel is the quantize-on-append of the step's one new token
+ * (fresh_rows = 1: q was produced before that kernel), and for attention calls that follow one another over caches
+ * nobody writes (fresh_rows = 0). The outputs are those of the plain call. */
+#define B200_TQ_INPUTS_FINAL 2u
 /* Paged calls (pages != NULL): the size returned covers a compacted copy of all valid rows; with that much workspace
  * (256-byte aligned) one copy kernel gathers the blocks and the tensor-core kernel runs, with less (16 bytes are
  * enough) the general kernel reads the blocks in place. lk is an upper bound of the sum of the blocks' rows. */
@@ -264,10 +281,12 @@ int b200_tq_attention_static(const B200TqAttnArgs *args, b200_stream_t stream);
 /* ---- attention over packed rows, outputs gathered on every GPU ---------------------------------- */
 /* The all-gather of the outputs that follows a sharded decode step (every rank holds its own batch
  * entries or kv heads, and the layer's outputs are assembled on every rank: one all-gather per
- * layer when done with NCCL), fused into the epilogue of the attention: the kernel that merges the key
- * splits stores every finished output row into the gathered buffer of every rank (plain peer
- * stores over NVLink, no multicast), the last block of the grid publishes this rank's step number
- * in every rank's flag array and waits, with a bound, until every rank has published the same step.
+ * layer when done with NCCL), fused into the epilogue of the attention: the warp that finishes an
+ * output row (the one that merges its key splits) stores it into the gathered buffer of every rank
+ * (plain peer stores over NVLink, no multicast); the warp that finishes the call's last row publishes
+ * this rank's step number in every rank's flag array and waits, with a bound, until every rank has
+ * published the same step. One launch when the attention merges its splits itself, else the
+ * combine grid stores the rows and a one-warp grid publishes.
  * When the call has completed in stream order, slot (step & 1) of this rank's gathered buffer
  * holds the rows of all ranks: [world][b * hq * lq][d] elements of out_dtype, rank r's rows in
  * block r, each in (batch, head, token) order. Two slots, because a rank may run one step ahead.
@@ -275,15 +294,21 @@ int b200_tq_attention_static(const B200TqAttnArgs *args, b200_stream_t stream);
  *               mapped into this process (symmetric memory / IPC); peer_bufs[rank] is the local one
  *   peer_flags  device array of `world` pointers: each rank's `world` flag words, zeroed once
  *   step        device word of this rank, zero before the first call: steps completed so far
- *   done_ctr    device word of this rank, zero before the first call
+ *   done_ctr    device word of this rank, zero before the first call: counts the finished columns of
+ *               the call in flight and is back at zero when the call ends
+ *   max_polls   polls of every flag before the wait for the other ranks gives up (0 = 2^21, about a
+ *               tenth of a second)
  * All ranks must make the same sequence of calls. The wait for the other ranks is bounded; if it
- * runs out, args->status (if given) is set to 2 and the buffer is incomplete for that step. */
+ * runs out, args->status (if given) is set to 2, b200_device_wait_status() reports 1 from then on
+ * and the buffer is incomplete for that step; the call still completes and later calls work. */
 typedef struct B200PeerGather {
     void *const *peer_bufs;
     uint32_t *const *peer_flags;
     uint32_t world, rank;
     uint32_t *step;
     uint32_t *done_ctr;
+    uint32_t max_polls;
+    uint32_t pad;
 } B200PeerGather;
 int b200_tq_attention_gather(const B200TqAttnArgs *args, const B200PeerGather *gather, b200_stream_t stream);
 

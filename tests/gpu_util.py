@@ -40,6 +40,8 @@ def assert_close(got, want, atol=ATOL, rtol=RTOL, what="", out="f32"):
     got = np.asarray(got, dtype=np.float32)
     want = np.asarray(want, dtype=np.float32)
     err = np.abs(got - want)
-    bad = err > atol + (rtol + HALF_ULP[out]) * np.abs(want)
-    assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} out of tolerance, max abs err {err.max():.3e}"
-    return float(err.max())
+    # "not (err <= tol)" rather than "err > tol": a NaN (an output row that was never written, or a broken one) fails
+    bad = ~(err <= atol + (rtol + HALF_ULP[out]) * np.abs(want))
+    bad &= ~(np.isnan(got) & np.isnan(want))
+    assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} out of tolerance or not finite, max abs err {np.nanmax(err):.3e}"
+    return float(np.nanmax(err)) if err.size else 0.0

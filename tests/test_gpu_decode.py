@@ -288,6 +288,85 @@ def test_length_and_position_offsets(P, oracle):
     assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
 
 
+def test_rows_copied_while_the_append_of_the_step_still_runs(P, oracle):
+    """B200_TQ_INPUTS_FINAL with fresh_rows = 1: behind the append of a decode step, the attention may copy every row but
+    the sequence's last one before that kernel has finished. Poison sits where the new rows go until the append writes
+    them, so a tile copied too early would show in the outputs. Several steps in a row, ragged lengths among which a
+    sequence of one key, one that ends exactly on a tile boundary and one that starts a tile."""
+    from candle_rocm_vulkan_b200.turbo_quant import _kv_append
+    b, hq, hkv, d, cap = 8, 16, 4, 128, 2100
+    f = fmt(P, 2, 4)
+    kq, vq = P.TurboQuantizer(f, d, "none", 42), P.TurboQuantizer(f, d, "none", 44)
+    g = torch.Generator(device="cuda:0").manual_seed(11)
+    kx = torch.randn((b, hkv, cap, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    vx = torch.randn((b, hkv, cap, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    lens0 = torch.tensor([2000, 0, 31, 32, 63, 1999, 640, 1024], dtype=torch.int32, device="cuda:0")
+    cfg = P.FlashAttnConfig(d ** -0.5).causal()
+    steps = 4
+    kn = torch.randn((steps, b, hkv, 1, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    vn = torch.randn((steps, b, hkv, 1, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    qs = torch.randn((steps, b, hq, 1, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+
+    def fresh():
+        kc = torch.zeros((b, hkv, cap, kq.row_words()), dtype=torch.int32, device="cuda:0")
+        vc = torch.zeros_like(kc)
+        _kv_append(kx, vx, kc, vc, kq, vq, 0)
+        for bi in range(b):  # rows past the lengths: NaN scales until a step writes them
+            kc[bi, :, int(lens0[bi]):] = 0x7fc00000
+            vc[bi, :, int(lens0[bi]):] = 0x7fc00000
+        return kc, vc
+
+    kc1, vc1 = fresh()
+    want = []
+    for j in range(steps):
+        _kv_append(kn[j], vn[j], kc1, vc1, kq, vq, lens0, pos_add=j)
+        want.append(P.PackedAttention(qs[j], kc1, vc1, lens0, kq, vq, cfg, kv_len_add=j + 1).run().clone())
+    kc2, vc2 = fresh()
+    torch.cuda.synchronize()
+    for j in range(steps):
+        _kv_append(kn[j], vn[j], kc2, vc2, kq, vq, lens0, pos_add=j)
+        got = P.PackedAttention(qs[j], kc2, vc2, lens0, kq, vq, cfg, kv_len_add=j + 1, after_prev=True, fresh_rows=1).run()
+        torch.cuda.synchronize()
+        assert torch.isfinite(got.float()).all(), f"step {j}"
+        assert torch.equal(got, want[j]), f"step {j}"
+    # and layer after layer over caches nobody writes (fresh_rows = 0), each call behind the one before
+    out = [torch.empty_like(want[0]) for _ in range(3)]
+    calls = [P.PackedAttention(qs[i], kc2, vc2, lens0, kq, vq, cfg, out=out[i], kv_len_add=steps, after_prev=True, fresh_rows=0) for i in range(3)]
+    ref = [P.PackedAttention(qs[i], kc2, vc2, lens0, kq, vq, cfg, kv_len_add=steps).run().clone() for i in range(3)]
+    torch.cuda.synchronize()
+    for _ in range(3):
+        for c in calls:
+            c.run()
+    torch.cuda.synchronize()
+    for i in range(3):
+        assert torch.equal(out[i], ref[i]), f"layer {i}"
+    assert P._abi.lib().b200_device_wait_status() == 0
+
+
+@pytest.mark.parametrize("b", [3, 120])  # few columns: the combine grid merges; many: the decode grid itself
+def test_far_more_workers_than_tiles(P, oracle, b):
+    """A capacity of thousands of rows sizes the grid, but the sequences hold a handful of keys: most workers own no
+    tile, and the segments of a column must still be the consecutive workers that own one (a merge that counted the idle
+    workers in between would read partial results that nobody wrote). Poisoned workspace, ragged lengths."""
+    hq, hkv, d, cap = 16, 2, 128, 6000
+    lens = np.array([70, 1, 33], np.int32) if b == 3 else np.random.default_rng(b).integers(0, 71, size=b).astype(np.int32)
+    kd, vd, tab = make_rows(oracle, 911, b, hkv, 80, d, (2, 4), (2, 4), cap=cap)
+    q = oracle.normal(912, b * hq * d).reshape(b, hq, 1, d)
+    kq, vq = P.TurboQuantizer(fmt(P, 2, 4), d, "none", 42), P.TurboQuantizer(fmt(P, 2, 4), d, "none", 44)
+    from candle_rocm_vulkan_b200 import turbo_quant as TQ
+    for key, ws in list(TQ._WORKSPACES.items()):
+        ws.view(torch.int32).fill_(0x7fc00000)  # NaN in every partial result left over from earlier calls
+    torch.cuda.synchronize()
+    want = oracle.tq_attention(oracle.round_to(q, "bf16"), kd, vd, cap, (2, 4), (2, 4), d ** -0.5, tab, kv_len=lens, wr=0)
+    for splits in (0, 1, 7):
+        cfg = P.FlashAttnConfig(d ** -0.5).causal()
+        cfg.splits = splits
+        call = P.PackedAttention(to_dev(q, "bf16"), rows_dev(kd), rows_dev(vd), torch.from_numpy(lens).to("cuda:0"), kq, vq, cfg)
+        call._keep[7].view(torch.int32).fill_(0x7fc00000)
+        got = call.run().float().cpu().numpy()
+        assert_close(got, want, what=f"sparse work, splits={splits}", out="bf16")
+
+
 @pytest.mark.parametrize("lq,wl,wr,softcap,use_alibi", [(3, -1, 0, 0.0, False), (4, 50, 0, 0.0, False), (2, -1, -1, 15.0, False),
                                                          (1, -1, 0, 0.0, True), (5, 20, 3, 30.0, True), (3, 0, 0, 0.0, False)])
 def test_masks_softcap_alibi_multi_query(P, oracle, lq, wl, wr, softcap, use_alibi):

@@ -149,6 +149,47 @@ def test_append_per_sequence_positions(P, oracle):
     assert int((kc != 0).any(dim=-1).sum()) == b * h
 
 
+@pytest.mark.parametrize("mode", [0, 2])  # the general kernel (codebook rows) and the 128-element fast path
+def test_append_positions_outside_the_cache_write_nothing(P, oracle, mode):
+    """A device position below zero or at / past the capacity (a stale length word) must not make the kernel
+    store outside its slab: the row is skipped and the status word says so; host positions are refused."""
+    import ctypes as C
+    from candle_rocm_vulkan_b200.turbo_quant import _kv_append
+    A = P._abi
+    b, h, d, cap = 4, 2, 128, 8
+    kq, vq = P.TurboQuantizer(fmt(P, mode), d, "none", 1), P.TurboQuantizer(fmt(P, mode), d, "none", 3)
+    rw = kq.row_words()
+    # guard rows before and after every cache catch a store outside of it
+    big_k = torch.full((b * h * cap + 2 * cap, rw), 0x5a5a5a5a, dtype=torch.int32, device="cuda:0")
+    big_v = torch.full_like(big_k, 0x5a5a5a5a)
+    kc = big_k[cap:cap + b * h * cap].view(b, h, cap, rw)
+    vc = big_v[cap:cap + b * h * cap].view(b, h, cap, rw)
+    kc.zero_()
+    vc.zero_()
+    pos = torch.tensor([2, cap, -1, cap + 1000], dtype=torch.int32, device="cuda:0")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+    k = oracle.normal(1, b * h * d).reshape(b, h, 1, d)
+    v = oracle.normal(2, b * h * d).reshape(b, h, 1, d)
+    _kv_append(to_dev(k, "bf16"), to_dev(v, "bf16"), kc, vc, kq, vq, pos, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 3
+    tab = kq.tab.cpu().numpy()
+    wk = oracle.quantize_rows(oracle.round_to(k, "bf16").reshape(-1, d), mode, 4, tab).reshape(b, h, -1)
+    assert np.array_equal(words(kc[0, :, 2]), wk[0])            # the one valid position was written
+    assert int((kc != 0).any(dim=-1).sum()) == h and int((vc != 0).any(dim=-1).sum()) == h   # and nothing else
+    for big in (big_k, big_v):
+        assert bool((big[:cap] == 0x5a5a5a5a).all()) and bool((big[cap + b * h * cap:] == 0x5a5a5a5a).all())
+    # positions in range leave the status alone
+    status.zero_()
+    _kv_append(to_dev(k, "bf16"), to_dev(v, "bf16"), kc, vc, kq, vq, torch.tensor([0, 1, 7, 3], dtype=torch.int32, device="cuda:0"),
+               status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    # a host position past the end is refused before any launch
+    with pytest.raises(A.B200Error):
+        _kv_append(to_dev(k, "bf16"), to_dev(v, "bf16"), kc, vc, kq, vq, cap)
+
+
 @pytest.mark.parametrize("mode,bits", [(0, 4), (3, 4), (2, 4), (5, 4)])
 def test_hadamard_append_stages(P, oracle, mode, bits):
     """With rotation on, parity is per stage: the butterflies agree with the reference's matmul to
