@@ -96,7 +96,7 @@ SYMBOLS = [
     "b200_describe", "b200_last_error", "b200_tq_rotate", "b200_tq_quantize", "b200_tq_dequantize", "b200_kv_append",
     "b200_tq_attention_workspace_bytes", "b200_tq_attention", "b200_tq_attention_static", "b200_tq_attention_gather",
     "b200_flash_attn_workspace_bytes",
-    "b200_flash_attn", "b200_fa_prefill_append", "b200_device_wait_status",
+    "b200_flash_attn", "b200_fa_prefill_append", "b200_device_wait_status", "b200_device_wait_check",
 ]
 
 _lib = None
@@ -136,6 +136,7 @@ def lib():
         l.b200_flash_attn_workspace_bytes.restype = C.c_size_t
         l.b200_flash_attn.argtypes = [C.POINTER(FaArgs), C.c_void_p]
         l.b200_fa_prefill_append.argtypes = [C.POINTER(FaArgs), C.POINTER(KvAppendArgs), C.c_void_p]
+        l.b200_device_wait_check.argtypes = [C.c_int]
         _lib = l
     return _lib
 

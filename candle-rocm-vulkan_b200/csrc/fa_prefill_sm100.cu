@@ -1151,6 +1151,7 @@ using namespace b200;
 // loaded (the call that met it wrote zeros or partial rows); synchronizes the device.
 namespace b200 {
 int decode_wait_status();  // tq_decode.cu: the same flag of the kernels over packed rows
+int decode_wait_clear();
 }
 extern "C" int b200_device_wait_status(void) {
     int v = 0;
@@ -1158,4 +1159,19 @@ extern "C" int b200_device_wait_status(void) {
     const int d = b200::decode_wait_status();
     if (d < 0) return -1;
     return (v != 0 || d != 0) ? 1 : 0;
+}
+
+// B200_ERR_DEVICE_WAIT when a bounded device-side wait has run out on the current device since the library was loaded
+// (or since the flag was last cleared), B200_OK otherwise; clear != 0 resets the flag, after which the tensor-core
+// prefill kernels run again (they return at once, writing nothing, while it is set).
+extern "C" int b200_device_wait_check(int clear) {
+    const int st = b200_device_wait_status();
+    if (st < 0) return set_error(B200_ERR_LAUNCH, "device_wait_check: the flag cannot be read (%s)", cudaGetErrorString(cudaGetLastError()));
+    if (clear) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(g_wait_failed, &zero, sizeof(int)) != cudaSuccess || b200::decode_wait_clear() != 0)
+            return set_error(B200_ERR_LAUNCH, "device_wait_check: the flag cannot be cleared");
+    }
+    if (st) return set_error(B200_ERR_DEVICE_WAIT, "a bounded device-side wait ran out: the outputs of the call that met it are incomplete");
+    return B200_OK;
 }

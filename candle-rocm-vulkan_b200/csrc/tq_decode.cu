@@ -11,6 +11,8 @@ namespace b200 {
 
 template <int KM, int VM, int HD, bool NAT>
 int launch_decode(const DecodeParams &p, dim3 grid, size_t smem, cudaStream_t stream);
+template <int KM, int VM, int HD, bool NAT>
+int launch_decode_pair(const DecodeParams &p, dim3 grid, size_t smem, cudaStream_t stream);
 
 struct DecodePlan {
     DecodeParams p;
@@ -19,6 +21,8 @@ struct DecodePlan {
     size_t off_lse, off_meta, ws_bytes;
     uint32_t blocks;
     int hd_idx;
+    uint32_t workers;  // warps (or pairs of warps) that share the tiles
+    bool pair;       // the kernel whose workers are pairs of warps (4-bit formats)
     bool nat;        // rows packed back to back on both sides: the instantiation with compile-time row strides
     bool in_kernel;  // the decode grid merges the segments itself (arrival counters), no combine grid
 };
@@ -132,7 +136,25 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
     }
     bps = std::max(bps, 1);
     pl.smem = fixed + DW * p.ns * stage;
-    if (pl.smem > 227 * 1024) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: %zu bytes of shared memory", pl.smem);
+    pl.pair = false;
+    int wpb = DW;  // workers per block
+    if (pair_formats(a->kq.mode, a->vq.mode)) {
+        // codebook formats: a worker is a pair of warps, two blocks of four pairs per SM; as many stages as fit
+        const size_t pq = p.qstage_bytes ? (size_t)2 * PW * PACK * a->d * 4 : 0;
+        const size_t pfixed = PAIR_FIXED + (size_t)PW * pair_meta_bytes(a->kq.mode, a->vq.mode, (int)a->d) + pq;
+        const size_t per_block = (228 * 1024) / 2 - 1024;
+        int ns = 0;
+        for (int n = 2; n <= PNS_MAX; ++n)
+            if (pfixed + PW * n * stage <= per_block) ns = n;
+        if (ns) {
+            pl.pair = true;
+            p.ns = (uint32_t)ns;
+            p.qstage_bytes = (uint32_t)pq;
+            pl.smem = pfixed + PW * ns * stage;
+            bps = 2;
+            wpb = PW;
+        }
+    }
     // rows that certainly exist after the visible ones: the head stride spans them
     p.rows_cap = 0;
     if (p.k_ss && p.v_ss && p.k_sh % p.k_ss == 0 && p.v_sh % p.v_ss == 0 && (a->hkv > 1 || a->b > 1))
@@ -144,8 +166,9 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
     const uint64_t lk = std::max<uint32_t>(a->lk, 1);
     const uint64_t max_tiles = (uint64_t)a->b * pl.ny * ((lk + WK - 1) / WK);
     uint64_t nblocks = (uint64_t)sm_count_cached() * bps;
-    if (a->splits > 0) nblocks = std::min<uint64_t>(nblocks, ((uint64_t)a->b * pl.ny * a->splits + DW - 1) / DW);
-    pl.blocks = (uint32_t)std::max<uint64_t>(std::min(nblocks, (max_tiles + DW - 1) / DW), 1);
+    if (a->splits > 0) nblocks = std::min<uint64_t>(nblocks, ((uint64_t)a->b * pl.ny * a->splits + wpb - 1) / wpb);
+    pl.blocks = (uint32_t)std::max<uint64_t>(std::min(nblocks, (max_tiles + wpb - 1) / wpb), 1);
+    pl.workers = pl.blocks * (uint32_t)wpb;
 
     p.after_prev = (a->flags & B200_TQ_AFTER_PREV) ? 1u : 0u;
     p.prefetch = (p.after_prev && (a->flags & B200_TQ_INPUTS_FINAL)) ? 1u : 0u;
@@ -155,12 +178,12 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
     // Few segments per column (the workers outnumber the columns by less than eight to one): the last worker of a
     // column merges it inside the decode grid. Many segments per column (a few long sequences), or more columns
     // than there are arrival counters: a combine grid, whose blocks share a row's segments, follows.
-    pl.in_kernel = (size_t)pl.blocks * DW < 8 * ncols && ncols <= (size_t)CTR_COLS;
+    pl.in_kernel = (size_t)pl.workers < 8 * ncols && ncols <= (size_t)CTR_COLS;
 #ifdef B200_FORCE_COMBINE  // measurement builds only: always the separate combine grid
     pl.in_kernel = false;
 #endif
     const size_t prow = std::min<size_t>(PACK, p.rows_per_kv);
-    const size_t slots = ((size_t)pl.blocks * DW + ncols) * prow;
+    const size_t slots = ((size_t)pl.workers + ncols) * prow;
     const size_t part_o = slots * a->d * 4;
     const size_t part_l = slots * 4;
     pl.off_lse = (part_o + 255) / 256 * 256;
@@ -172,6 +195,17 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
 
 template <int KM, int VM>
 static int dispatch_hd(const DecodePlan &pl, dim3 grid, cudaStream_t stream) {
+    if constexpr (pair_formats(KM, VM)) {
+        if (pl.pair) {
+            if constexpr (KM == VM)
+                if (pl.nat && pl.hd_idx == 1) return launch_decode_pair<KM, VM, 128, true>(pl.p, grid, pl.smem, stream);
+            switch (pl.hd_idx) {
+            case 0: return launch_decode_pair<KM, VM, 64, false>(pl.p, grid, pl.smem, stream);
+            case 1: return launch_decode_pair<KM, VM, 128, false>(pl.p, grid, pl.smem, stream);
+            default: return launch_decode_pair<KM, VM, 256, false>(pl.p, grid, pl.smem, stream);
+            }
+        }
+    }
     if constexpr (KM == VM)
         if (pl.nat && pl.hd_idx == 1) return launch_decode<KM, VM, 128, true>(pl.p, grid, pl.smem, stream);
     switch (pl.hd_idx) {
@@ -184,9 +218,11 @@ static int dispatch_hd(const DecodePlan &pl, dim3 grid, cudaStream_t stream) {
 template <int KM>
 static int dispatch_v(const DecodePlan &pl, dim3 grid, cudaStream_t stream) {
 #ifdef B200_ONLY_SAME_FORMAT  // measurement builds only: keys and values in one format, the other pairs are left out
-    if (pl.p.v.mode != KM || pl.hd_idx != 1) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "measurement build");
-    if (pl.nat) return launch_decode<KM, KM, 128, true>(pl.p, grid, pl.smem, stream);
-    return launch_decode<KM, KM, 128, false>(pl.p, grid, pl.smem, stream);
+    if (pl.p.v.mode != KM || pl.hd_idx != 1 || !pl.nat) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "measurement build");
+    if constexpr (pair_formats(KM, KM)) {
+        if (pl.pair) return launch_decode_pair<KM, KM, 128, true>(pl.p, grid, pl.smem, stream);
+    }
+    return launch_decode<KM, KM, 128, true>(pl.p, grid, pl.smem, stream);
 #else
     switch (pl.p.v.mode) {
     case B200_TURBO_MSE: return dispatch_hd<KM, B200_TURBO_MSE>(pl, grid, stream);
@@ -216,13 +252,6 @@ __global__ void __launch_bounds__(32) tq_gather_publish_kernel(uint32_t *const *
 static __device__ uint32_t g_col_ctr[CTR_SLABS][CTR_COLS];
 static __device__ int32_t g_decode_wait_failed;
 
-#ifdef B200_TRACE
-static unsigned long long *g_trace_host = nullptr;
-extern "C" int b200_dbg_trace(unsigned long long *out) {  // measurement builds only
-    return g_trace_host ? (int)cudaMemcpy(out, g_trace_host, 2 * 2048 * 8 * 8, cudaMemcpyDeviceToHost) : -1;
-}
-#endif
-
 struct DeviceWords {
     uint32_t *ctr;
     int32_t *wait_failed;
@@ -250,6 +279,12 @@ static int device_words(DeviceWords &w) {
     }
     w = g_device_words[dev];
     return B200_OK;
+}
+
+int decode_wait_clear() {
+    DeviceWords w;
+    if (device_words(w)) return -1;
+    return cudaMemset(w.wait_failed, 0, sizeof(int32_t)) == cudaSuccess ? 0 : -1;
 }
 
 // 1 when a bounded wait of a decode kernel has run out on the current device since the library was loaded
@@ -444,15 +479,6 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
     const int wrc = device_words(dw);
     if (wrc) return wrc;
     p.lib_status = dw.wait_failed;
-#ifdef B200_TRACE
-    {
-        static unsigned long long *tr = nullptr;
-        static uint32_t calls = 0;
-        if (!tr) { cudaMalloc(&tr, 2 * 2048 * 8 * 8); cudaMemset(tr, 0, 2 * 2048 * 8 * 8); }
-        p.trace = tr + (size_t)(calls++ & 1u) * 2048 * 8;
-        g_trace_host = tr;
-    }
-#endif
     // calls in flight at the same time must not share a slab: 32 slabs taken in turn
     p.ctr = pl.in_kernel ? dw.ctr + (size_t)(g_next_slab.fetch_add(1, std::memory_order_relaxed) % CTR_SLABS) * CTR_COLS : nullptr;
     const dim3 grid(pl.blocks);
@@ -469,7 +495,7 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
         const size_t rows = (size_t)a->b * a->hq * a->lq;
         // Few segments per row: one warp per row, four rows per block, a grid that is resident at once (further rows
         // are looped over). Many segments per row: one block per row, its warps share the segments.
-        const bool per_row = (size_t)pl.blocks * DW < 8 * (size_t)a->b * pl.ny;
+        const bool per_row = (size_t)pl.workers < 8 * (size_t)a->b * pl.ny;
         const unsigned gx = per_row ? (unsigned)std::max<size_t>(std::min<size_t>((rows + 3) / 4, (size_t)sm_count_cached() * 6), 1)
                                     : (unsigned)std::max<size_t>(std::min<size_t>(rows, (size_t)sm_count_cached() * 16), 1);
         // the combine grid is launched while the decode grid still runs and waits on the device for

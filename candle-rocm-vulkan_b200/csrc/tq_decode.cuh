@@ -49,9 +49,6 @@ constexpr int PACK = 8;       // query rows per block
 #ifndef B200_DECODE_COL_COST
 #define B200_DECODE_COL_COST 4  // cost of starting a column, in tiles, in the split of the work between the workers
 #endif
-#ifndef B200_ABL
-#define B200_ABL 0  // measurement builds only: leaves parts of a tile's work out (results are void)
-#endif
 constexpr int CTR_SLABS = 32;    // arrival-counter slabs of the library (consecutive calls take them in turn)
 constexpr int CTR_COLS = 8192;   // columns a call may have for the decode grid to merge them itself
 constexpr float LOG2E = 1.4426950408889634f;
@@ -102,15 +99,7 @@ struct DecodeParams {
     // counter back to zero): the last worker of a column merges it. Null: the combine grid merges.
     uint32_t *ctr;
     int32_t *lib_status;    // library-wide flag: set when a bounded wait of a kernel of this call runs out
-#ifdef B200_TRACE
-    unsigned long long *trace;  // measurement builds only: [worker][8] timestamps
-#endif
 };
-#ifdef B200_TRACE
-#define B200_T(i) do { if (lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.trace[(size_t)wid * 8 + (i)] = t_; } } while (0)
-#else
-#define B200_T(i) do { } while (0)
-#endif
 
 __host__ __device__ constexpr bool fmt_is4(int m) { return m == B200_MXFP4 || m == B200_NVFP4 || m == B200_TURBO_MSE; }
 __host__ __device__ constexpr bool fmt_is_mx(int m) { return m == B200_MXFP4 || m == B200_MXFP8; }
@@ -442,80 +431,84 @@ __device__ __forceinline__ void finish_row(const DecodeParams &p, size_t obase, 
 }
 
 // Merge of all rows of one column by one warp, inside the decode grid (the last worker of the column to arrive).
-// LPR lanes share a row (lane l: row l / LPR, elements [(l % LPR) HD / LPR, +HD / LPR)), so the rows of the column
-// are merged side by side and the partial rows of two segments are in flight per lane: a column costs two or three
-// trips to L2 instead of a few per row. `slot0`: the first segment's slot; consecutive segments are consecutive slots.
-template <int HD, int LPR>
+// Eight lanes share a row (lane l: row l / 8 of a group of four rows, elements [(l % 8) HD / 8, +HD / 8)), so four
+// rows are merged side by side and the partial rows of two segments are in flight per lane: a group of rows costs two
+// or three trips to L2 instead of a few per row. `slot0`: the first segment's slot; consecutive segments are
+// consecutive slots. `stage`: PACK x HD floats of shared memory of this warp (touched only when the values are rotated).
+template <int HD>
 __device__ __forceinline__ void merge_column(const DecodeParams &p, uint32_t b, uint32_t y, size_t slot0, int ns, uint32_t prow, size_t g_base,
                                              float *stage, int lane) {
-    constexpr int EL = HD / LPR;  // elements of a row per lane
-    const uint32_t rr = (uint32_t)lane / LPR, q = (uint32_t)lane % LPR;
-    size_t obase = 0, grow = 0;
-    const bool live = rr < prow && row_addr(p, b, y, rr, obase, grow);
-    const float *pl = p.part_lse + slot0 * prow + rr;
-    const float *po = p.part_o + (slot0 * prow + rr) * HD + q * EL;
+    constexpr int LPR = 8, EL = HD / LPR;  // lanes per row, elements of a row per lane
+    const uint32_t q = (uint32_t)lane % LPR;
     const size_t seg_stride = (size_t)prow * HD;
-    float acc[EL];
+    for (uint32_t rbase = 0; rbase < prow; rbase += 32 / LPR) {
+        const uint32_t rr = rbase + (uint32_t)lane / LPR;
+        size_t obase = 0, grow = 0;
+        const bool live = rr < prow && row_addr(p, b, y, rr, obase, grow);
+        const float *pl = p.part_lse + slot0 * prow + rr;
+        const float *po = p.part_o + (slot0 * prow + rr) * HD + q * EL;
+        float acc[EL];
 #pragma unroll
-    for (int k = 0; k < EL; ++k) acc[k] = 0.0f;
-    if (live) {
-        // the first two segments' rows are requested before the log-sum-exps are looked at
-        float4 pre[2][EL / 4];
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int k = 0; k < EL / 4; ++k)
-                pre[j][k] = j < ns ? __ldcg(reinterpret_cast<const float4 *>(po + (size_t)j * seg_stride) + k) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        float mx = -INFINITY;
-#pragma unroll 8
-        for (int s0 = 0; s0 < ns; ++s0) mx = fmaxf(mx, __ldcg(pl + (size_t)s0 * prow));
-        float wsum = 0.0f;
-        for (int s0 = 0; s0 < ns; s0 += 2) {
-            float w[2];
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const float e = s0 + j < ns ? __ldcg(pl + (size_t)(s0 + j) * prow) : -INFINITY;
-                w[j] = e == -INFINITY ? 0.0f : expf(e - mx);
-                wsum += w[j];
-            }
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-#pragma unroll
-                for (int k = 0; k < EL / 4; ++k) {
-                    acc[4 * k] = fmaf(w[j], pre[j][k].x, acc[4 * k]);
-                    acc[4 * k + 1] = fmaf(w[j], pre[j][k].y, acc[4 * k + 1]);
-                    acc[4 * k + 2] = fmaf(w[j], pre[j][k].z, acc[4 * k + 2]);
-                    acc[4 * k + 3] = fmaf(w[j], pre[j][k].w, acc[4 * k + 3]);
-                }
-            // the next two segments
+        for (int k = 0; k < EL; ++k) acc[k] = 0.0f;
+        if (live) {
+            // the first two segments' rows are requested before the log-sum-exps are looked at
+            float4 pre[2][EL / 4];
 #pragma unroll
             for (int j = 0; j < 2; ++j)
 #pragma unroll
                 for (int k = 0; k < EL / 4; ++k)
-                    if (s0 + 2 + j < ns) pre[j][k] = __ldcg(reinterpret_cast<const float4 *>(po + (size_t)(s0 + 2 + j) * seg_stride) + k);
+                    pre[j][k] = j < ns ? __ldcg(reinterpret_cast<const float4 *>(po + (size_t)j * seg_stride) + k) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            float mx = -INFINITY;
+#pragma unroll 8
+            for (int s0 = 0; s0 < ns; ++s0) mx = fmaxf(mx, __ldcg(pl + (size_t)s0 * prow));
+            float wsum = 0.0f;
+            for (int s0 = 0; s0 < ns; s0 += 2) {
+                float w[2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const float e = s0 + j < ns ? __ldcg(pl + (size_t)(s0 + j) * prow) : -INFINITY;
+                    w[j] = e == -INFINITY ? 0.0f : expf(e - mx);
+                    wsum += w[j];
+                }
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int k = 0; k < EL / 4; ++k) {
+                        acc[4 * k] = fmaf(w[j], pre[j][k].x, acc[4 * k]);
+                        acc[4 * k + 1] = fmaf(w[j], pre[j][k].y, acc[4 * k + 1]);
+                        acc[4 * k + 2] = fmaf(w[j], pre[j][k].z, acc[4 * k + 2]);
+                        acc[4 * k + 3] = fmaf(w[j], pre[j][k].w, acc[4 * k + 3]);
+                    }
+                // the next two segments
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int k = 0; k < EL / 4; ++k)
+                        if (s0 + 2 + j < ns) pre[j][k] = __ldcg(reinterpret_cast<const float4 *>(po + (size_t)(s0 + 2 + j) * seg_stride) + k);
+            }
+            const float inv = wsum > 0.0f ? 1.0f / wsum : 0.0f;
+#pragma unroll
+            for (int k = 0; k < EL; ++k) acc[k] *= inv;
         }
-        const float inv = wsum > 0.0f ? 1.0f / wsum : 0.0f;
+        if (p.v.rot == B200_ROT_HADAMARD) {
+            // rotate back through the warp's staging rows ([row][HD] floats of shared memory)
+            __syncwarp();
+            if (live)
 #pragma unroll
-        for (int k = 0; k < EL; ++k) acc[k] *= inv;
-    }
-    if (p.v.rot == B200_ROT_HADAMARD) {
-        // rotate back through the warp's staging rows ([row][HD] floats of shared memory)
-        __syncwarp();
-        if (live)
+                for (int k = 0; k < EL; ++k) stage[(rr - rbase) * HD + q * EL + k] = acc[k];
+            __syncwarp();
+            for (uint32_t r2 = 0; r2 < 32 / LPR; ++r2) warp_hadamard(stage + r2 * HD, HD, p.v.signs, false, lane);
+            __syncwarp();
+            if (live)
 #pragma unroll
-            for (int k = 0; k < EL; ++k) stage[rr * HD + q * EL + k] = acc[k];
-        __syncwarp();
-        for (uint32_t r2 = 0; r2 < prow; ++r2) warp_hadamard(stage + r2 * HD, HD, p.v.signs, false, lane);
-        __syncwarp();
-        if (live)
-#pragma unroll
-            for (int k = 0; k < EL; ++k) acc[k] = stage[rr * HD + q * EL + k];
-        __syncwarp();
-    }
-    if (live) {
-        store_row_piece<EL>(p.out, obase + q * EL, acc, p.out_dtype);
-        // the same row into every rank's gathered buffer: plain stores through the peer mappings
-        for (uint32_t pr = 0; pr < p.world; ++pr) store_row_piece<EL>(p.peer_bufs[pr], g_base + grow * HD + q * EL, acc, p.out_dtype);
+                for (int k = 0; k < EL; ++k) acc[k] = stage[(rr - rbase) * HD + q * EL + k];
+            __syncwarp();
+        }
+        if (live) {
+            store_row_piece<EL>(p.out, obase + q * EL, acc, p.out_dtype);
+            // the same row into every rank's gathered buffer: plain stores through the peer mappings
+            for (uint32_t pr = 0; pr < p.world; ++pr) store_row_piece<EL>(p.peer_bufs[pr], g_base + grow * HD + q * EL, acc, p.out_dtype);
+        }
     }
 }
 
@@ -552,57 +545,440 @@ __device__ __forceinline__ void gather_publish(uint32_t *const *peer_flags, uint
     }
 }
 
-template <int KM, int VM, int HD, bool NAT>
-__global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_kernel(const DecodeParams p) {
-    constexpr int STEPS = HD / 16;          // k-steps of K Q^T == m-tiles of the output
-    constexpr bool K4 = fmt_is4(KM), V4 = fmt_is4(VM);
-    constexpr bool KMX = fmt_is_mx(KM);     // block-wise accumulation, contraction order A
+// Online softmax of a tile in the log2 domain, on the score fragments sr[u][2 k + e] = key 16 u + g + 8 k, row 2c + e.
+// vm[k] = (sigma, log2 sigma) of key g + 8 k: the value scale is folded into the running maxima M (which track
+// s_j + log2 sigma_j), so the f16 weights w_j = exp2(s_j - M) sigma_j stay in range for value scales of any
+// magnitude while the normalizers lsum add exp2(s_j - M) in f32. M only moves when a score exceeds it by 2^MAX_SLACK
+// (one warp vote per tile); the function then returns true with the factors al[e] = exp2(M_old - M_new) for
+// everything accumulated so far (lsum is already scaled). pb: the weights as B fragments of the second product.
+// Plain form: every key of the tile is visible to every row, no soft-capping, no ALiBi.
+__device__ __forceinline__ bool softmax_plain(const float (&sr)[2][4], const float2 (&vm)[4], const float (&qs2)[2], float (&M)[2],
+                                              float (&lsum)[2], uint32_t (&pb)[4], float (&al)[2]) {
+    // scale, maximum check and exponent in fused multiply-adds
+    float c0 = fmaxf(fmaxf(fmaf(sr[0][0], qs2[0], vm[0].y), fmaf(sr[0][2], qs2[0], vm[1].y)),
+                     fmaxf(fmaf(sr[1][0], qs2[0], vm[2].y), fmaf(sr[1][2], qs2[0], vm[3].y)));
+    float c1 = fmaxf(fmaxf(fmaf(sr[0][1], qs2[1], vm[0].y), fmaf(sr[0][3], qs2[1], vm[1].y)),
+                     fmaxf(fmaf(sr[1][1], qs2[1], vm[2].y), fmaf(sr[1][3], qs2[1], vm[3].y)));
+    const bool moved = __any_sync(0xffffffffu, c0 > M[0] + MAX_SLACK || c1 > M[1] + MAX_SLACK);
+    if (moved) {
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, o));
+            c1 = fmaxf(c1, __shfl_xor_sync(0xffffffffu, c1, o));
+        }
+        const float n0 = fmaxf(M[0], c0), n1 = fmaxf(M[1], c1);
+        al[0] = fast_exp2(M[0] - n0);
+        al[1] = fast_exp2(M[1] - n1);
+        M[0] = n0;
+        M[1] = n1;
+        lsum[0] *= al[0];
+        lsum[1] *= al[1];
+    }
+    const float nm0 = -M[0], nm1 = -M[1];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float pa = fast_exp2(fmaf(sr[k >> 1][2 * (k & 1)], qs2[0], nm0));
+        const float pc = fast_exp2(fmaf(sr[k >> 1][2 * (k & 1) + 1], qs2[1], nm1));
+        lsum[0] += pa;
+        lsum[1] += pc;
+        pb[k] = movmatrix_trans(pack_f16x2(pa * vm[k].x, pc * vm[k].x));
+    }
+    return moved;
+}
+
+// Visible keys [lo, hi), key position and ALiBi slope of the two query rows (2c, 2c + 1) whose scores a lane holds
+struct RowMask {
+    int lo[2], hi[2], pos[2];
+    float slope[2];
+};
+
+// General form: masks, soft-capping, ALiBi. `key_g`: index of the tile's key g (the lane's keys are key_g + 8 k);
+// qs[e]: score scale of row 2c + e.
+__device__ __forceinline__ bool softmax_masked(const float (&sr)[2][4], const float2 (&vm)[4], const float (&qs)[2], float softcap, int key_g,
+                                               const RowMask &rm, float (&M)[2], float (&lsum)[2], uint32_t (&pb)[4], float (&al)[2]) {
+    float s2[8];  // s2[2 k + e]
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int j = key_g + 8 * k;
+            float sx = sr[k >> 1][2 * (k & 1) + e] * qs[e];
+            if (softcap > 0.0f) sx = softcap * tanhf(sx / softcap);
+            if (rm.slope[e] != 0.0f) sx -= rm.slope[e] * fabsf((float)(rm.pos[e] - j));
+            s2[2 * k + e] = (j >= rm.lo[e] && j < rm.hi[e]) ? sx * LOG2E : -INFINITY;
+        }
+    }
+    float c0 = fmaxf(fmaxf(s2[0] + vm[0].y, s2[2] + vm[1].y), fmaxf(s2[4] + vm[2].y, s2[6] + vm[3].y));
+    float c1 = fmaxf(fmaxf(s2[1] + vm[0].y, s2[3] + vm[1].y), fmaxf(s2[5] + vm[2].y, s2[7] + vm[3].y));
+    const bool moved = __any_sync(0xffffffffu, c0 > M[0] + MAX_SLACK || c1 > M[1] + MAX_SLACK);
+    if (moved) {
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, o));
+            c1 = fmaxf(c1, __shfl_xor_sync(0xffffffffu, c1, o));
+        }
+        const float n0 = fmaxf(M[0], c0), n1 = fmaxf(M[1], c1);
+        al[0] = fast_exp2(M[0] - n0);
+        al[1] = fast_exp2(M[1] - n1);
+        M[0] = n0;
+        M[1] = n1;
+        lsum[0] *= al[0];
+        lsum[1] *= al[1];
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float pa = fast_exp2(s2[2 * k] - M[0]), pc = fast_exp2(s2[2 * k + 1] - M[1]);
+        lsum[0] += pa;
+        lsum[1] += pc;
+        pb[k] = movmatrix_trans(pack_f16x2(pa * vm[k].x, pc * vm[k].x));
+    }
+    return moved;
+}
+
+// Query rows of pack `pack` of kv head `hk` of batch entry `b` as the B fragments of K Q^T: row g of the pack for the
+// lanes of quad row g, rotated with the key signs when the cache is rotated (through the warp's staging rows), then
+// normalized by a power of two and rounded to f16. Per k-step the four contraction slots of a lane are the
+// consecutive dims dbase(s) ... + 3, so the four lanes of a quad hold the whole row between them. qs[e]: the score
+// scale of row 2c + e (softmax scale times the power of two taken out), qs2[e] the same in the log2 domain.
+template <int KM, int HD>
+__device__ __forceinline__ void load_query(const DecodeParams &p, uint32_t b, uint32_t hk, uint32_t pack, float *qstage, int lane,
+                                           uint32_t (&qb0)[HD / 16], uint32_t (&qb1)[HD / 16], float (&qs)[2], float (&qs2)[2]) {
+    constexpr int STEPS = HD / 16;
+    constexpr bool KMX = fmt_is_mx(KM);
+    const int g = lane >> 2, c = lane & 3;
+    const uint32_t G = p.group, R = p.rows_per_kv;
+    const uint32_t r = pack * PACK + g;
+    float qv[STEPS][4];
+    if (p.k.rot == B200_ROT_HADAMARD) {
+        __syncwarp();
+        for (int idx = lane; idx < PACK * HD; idx += 32) {
+            const uint32_t rr = idx / HD, dd = idx % HD, r2 = pack * PACK + rr;
+            float v = 0.0f;
+            if (r2 < R) {
+                const uint32_t i = p.lq == 1 ? 0u : r2 / G, h = hk * G + (p.lq == 1 ? r2 : r2 % G);
+                v = load_elem_rt(p.q, b * p.q_sb + h * p.q_sh + i * p.q_ss + dd, p.q_dtype);
+            }
+            qstage[idx] = v;
+        }
+        __syncwarp();
+        for (int rr = 0; rr < PACK; ++rr) warp_hadamard(qstage + rr * HD, HD, p.k.signs, true, lane);
+        __syncwarp();
+#pragma unroll
+        for (int s = 0; s < STEPS; ++s) {
+            const int dbase = KMX ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : c * (HD / 4) + 4 * s;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) qv[s][j] = qstage[g * HD + dbase + j];
+        }
+    } else {
+        const uint32_t i = p.lq == 1 ? 0u : r / G, h = hk * G + (p.lq == 1 ? r : r % G);
+        const size_t qoff = b * p.q_sb + h * p.q_sh + i * p.q_ss;
+        const bool q16 = p.q_dtype == B200_F16 || p.q_dtype == B200_BF16;
+        if (q16 && r < R && ((reinterpret_cast<uintptr_t>(p.q) + 2 * qoff) & 7u) == 0) {
+            // 16-bit rows on an 8-byte boundary: the four contraction slots of a k-step in one load, all
+            // loads of the row issued before the first conversion
+            const uint16_t *q16p = reinterpret_cast<const uint16_t *>(p.q) + qoff;
+            uint2 raw[STEPS];
+#pragma unroll
+            for (int s = 0; s < STEPS; ++s) {
+                const int dbase = KMX ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : c * (HD / 4) + 4 * s;
+                raw[s] = __ldg(reinterpret_cast<const uint2 *>(q16p + dbase));
+            }
+            if (p.q_dtype == B200_BF16) {
+#pragma unroll
+                for (int s = 0; s < STEPS; ++s) {
+                    qv[s][0] = u2f(raw[s].x << 16); qv[s][1] = u2f(raw[s].x & 0xffff0000u);
+                    qv[s][2] = u2f(raw[s].y << 16); qv[s][3] = u2f(raw[s].y & 0xffff0000u);
+                }
+            } else {
+#pragma unroll
+                for (int s = 0; s < STEPS; ++s) {
+                    qv[s][0] = f16_bits_to_f((uint16_t)(raw[s].x & 0xffffu)); qv[s][1] = f16_bits_to_f((uint16_t)(raw[s].x >> 16));
+                    qv[s][2] = f16_bits_to_f((uint16_t)(raw[s].y & 0xffffu)); qv[s][3] = f16_bits_to_f((uint16_t)(raw[s].y >> 16));
+                }
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < STEPS; ++s) {
+                const int dbase = KMX ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : c * (HD / 4) + 4 * s;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) qv[s][j] = r < R ? load_elem_rt(p.q, qoff + dbase + j, p.q_dtype) : 0.0f;
+            }
+        }
+    }
+    float am = 0.0f;
+#pragma unroll
+    for (int s = 0; s < STEPS; ++s)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) am = fmaxf(am, fabsf(qv[s][j]));
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+    int e = 0;
+    if (am > 0.0f && am < INFINITY) e = (int)((f2u(am) >> 23) & 0xffu) - 127 - 7;
+    e = max(min(e, 100), -100);
+    const float down = u2f((uint32_t)(127 - e) << 23), up = u2f((uint32_t)(127 + e) << 23);
+    const float qscale = p.scale * up;
+    qs[0] = __shfl_sync(0xffffffffu, qscale, (2 * c) * 4);
+    qs[1] = __shfl_sync(0xffffffffu, qscale, (2 * c + 1) * 4);
+    qs2[0] = qs[0] * LOG2E;
+    qs2[1] = qs[1] * LOG2E;
+#pragma unroll
+    for (int s = 0; s < STEPS; ++s) {
+        qb0[s] = pack_f16x2(qv[s][0] * down, qv[s][1] * down);
+        qb1[s] = pack_f16x2(qv[s][2] * down, qv[s][3] * down);
+    }
+}
+
+// Per-key scalars of a tile, lane = key. `kr` / `vr`: the lane's K and V row in the stage. Written for the tile's
+// consumers: f32 key scales (rsc0 times the block scales of the MX formats) at meta_s [key][KMW], the value scale
+// sigma = rsc0_v * 2^(largest block exponent) and its log2 at vmeta_s [key], f16 block scales of V relative to that
+// exponent at vsc_s [block][key].
+template <int KM, int VM, int HD>
+__device__ __forceinline__ void tile_meta(uint32_t kr, uint32_t vr, uint32_t meta_s, uint32_t vmeta_s, uint32_t vsc_s, int lane) {
+    constexpr bool KMX = fmt_is_mx(KM);
     constexpr int KMW = kmeta_words(KM, HD);
-    constexpr int NBK = HD / 32;            // 32-blocks per row
+    constexpr int NBK = HD / 32;
     constexpr int NBV = vsc_blocks(VM, HD);
-    constexpr int META = meta_bytes(KM, VM, HD);
-    constexpr uint32_t k_cw4 = code_bytes(KM, HD), k_rsc4 = rsc_byte_off(KM, HD);  // bytes of the codes, offset of rsc0
+    constexpr uint32_t k_cw4 = code_bytes(KM, HD), k_rsc4 = rsc_byte_off(KM, HD);
     constexpr uint32_t v_cw4 = code_bytes(VM, HD), v_rsc4 = rsc_byte_off(VM, HD);
-    extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);  // [DW][NS_MAX]
-    const int NS = (int)p.ns;
-    const uint32_t sbase = smem_u32(smem);
-    const uint32_t lut_k = sbase + 128, lut_v = lut_k + 1024, plane_k = lut_v + 1024, plane_v = plane_k + 32;
-    // row strides and stage sizes: compile-time when the rows are packed back to back (NAT)
-    const uint32_t krb = NAT ? (uint32_t)nat_row_bytes(KM, HD) : (uint32_t)p.k_ss * 4u;
-    const uint32_t vrb = NAT ? (uint32_t)nat_row_bytes(VM, HD) : (uint32_t)p.v_ss * 4u;
-    const uint32_t k_stage_bytes = NAT ? stage_part_bytes((uint32_t)nat_row_bytes(KM, HD)) : p.k_stage_bytes;
-    const uint32_t v_stage_bytes = NAT ? stage_part_bytes((uint32_t)nat_row_bytes(VM, HD)) : p.v_stage_bytes;
-    const uint32_t stage_bytes = k_stage_bytes + v_stage_bytes;
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
-    const uint32_t G = p.group, R = p.rows_per_kv, ny = p.hkv * p.packs;
-    const uint32_t nw_grid = gridDim.x * DW, wid = blockIdx.x * DW + warp;
-
-    // ------------------------------------------------------------------ one time set up (the only block barrier)
-    if (tid == 0) {
-        for (int i = 0; i < DW * NS_MAX; ++i) mbar_init(&bars[i], 1);
-        mbar_fence_init();
+        const float k0 = u2f(lds32(kr + k_rsc4));
+    if constexpr (KMX) {
+#pragma unroll
+        for (int w = 0; w < (NBK + 3) / 4; ++w) {
+            const uint32_t aux = lds32(kr + k_cw4 + 4 * w);
+            // rsc0 * 2^(e - 127); a zero code gives +0 (its block holds zero codes)
+            float sc[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sc[i] = k0 * u2f(((aux >> (8 * i)) & 0xffu) << 23);
+            if constexpr (KMW >= 4) {
+                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(meta_s + (lane * KMW + 4 * w) * 4), "f"(sc[0]), "f"(sc[1]),
+                             "f"(sc[2]), "f"(sc[3])
+                             : "memory");
+            } else {
+                asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(meta_s + lane * KMW * 4), "f"(sc[0]), "f"(sc[1]) : "memory");
+            }
+        }
+    } else {
+        sts32(meta_s + lane * 4, f2u(k0));
     }
-    if constexpr (KM == B200_TURBO_MSE)
-        for (int i = tid; i < 256; i += DW * 32) sts32(lut_k + 4 * i, pack_f16x2(p.k.tab[i & 15], p.k.tab[i >> 4]));
-    if constexpr (VM == B200_TURBO_MSE)
-        for (int i = tid; i < 256; i += DW * 32) sts32(lut_v + 4 * i, pack_f16x2(p.v.tab[i & 15], p.v.tab[i >> 4]));
-    if (tid < 16 && ((tid < 8) ? KM == B200_TURBO_MSE : VM == B200_TURBO_MSE)) {
-        // byte planes of the codebook: words 0..3 low bytes, 4..7 high bytes
-        const float *tab = tid < 8 ? p.k.tab : p.v.tab;
-        const int w = tid & 7, sh = w < 4 ? 0 : 8;
-        uint32_t v = 0;
-        for (int j = 0; j < 4; ++j) v |= ((pack_f16x2(tab[4 * (w & 3) + j], 0.0f) >> sh) & 0xffu) << (8 * j);
-        sts32(plane_k + 4 * tid, v);
+    float sigma = u2f(lds32(vr + v_rsc4));
+    if constexpr (fmt_is_mx(VM)) {
+        uint32_t aux[(NBV + 3) / 4];
+        uint32_t em = 0;
+#pragma unroll
+        for (int w = 0; w < (NBV + 3) / 4; ++w) {
+            aux[w] = lds32(vr + v_cw4 + 4 * w);
+            em = w == 0 ? aux[w] : __vmaxu4(em, aux[w]);
+        }
+        const uint32_t emax = max_byte(em);
+        sigma *= u2f(emax << 23);
+#pragma unroll
+        for (int bk = 0; bk < NBV; ++bk) {
+            const int e = (int)((aux[bk >> 2] >> (8 * (bk & 3))) & 0xffu);
+            sts16(vsc_s + (bk * WK + lane) * 2, pow2_f16(e - (int)emax));
+        }
+    } else if constexpr (VM == B200_NVFP4) {
+#pragma unroll
+        for (int w = 0; w < NBV / 4; ++w) {
+            const uint32_t aux = lds32(vr + v_cw4 + 4 * w);
+            const uint32_t lo = cvt_e4m3x2_f16x2(aux), hi = cvt_e4m3x2_hi_f16x2(aux);
+            sts16(vsc_s + ((4 * w) * WK + lane) * 2, lo & 0xffffu);
+            sts16(vsc_s + ((4 * w + 1) * WK + lane) * 2, lo >> 16);
+            sts16(vsc_s + ((4 * w + 2) * WK + lane) * 2, hi & 0xffffu);
+            sts16(vsc_s + ((4 * w + 3) * WK + lane) * 2, hi >> 16);
+        }
     }
-    __syncthreads();
-    // the next kernel of the stream may be scheduled from here on (a combine grid, or the next attention launched as
-    // a programmatic dependent); it waits for this grid's completion itself before it touches memory
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    B200_T(0);
+    // sigma in [2^-100, 2^100], or 0 (then log2 = -inf: the key only counts in the normalizer)
+    float sc = fminf(fmaxf(sigma, 7.8886091e-31f), 1.2676506e30f);
+    sc = sigma > 0.0f ? sc : 0.0f;
+    asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(vmeta_s + lane * 8), "f"(sc), "f"(fast_log2(sc)) : "memory");
+    __syncwarp();
+}
 
-    // ------------------------------------------------------------------ this warp's share of the work
+// Scores of keys g and g + 8 of the 16 keys at `ka` (the lane's first code byte of key g; rows krb bytes apart)
+// against the query rows 2c, 2c + 1: sr[2 k + e] = key g + 8 k, row 2c + e. `mrow`: the f32 key scales of key g
+// (per-key scalars of the tile), qb0 / qb1: the query fragments.
+template <int KM, int HD>
+__device__ __forceinline__ void k_scores16(uint32_t ka, uint32_t krb, uint32_t mrow, const uint32_t (&qb0)[HD / 16], const uint32_t (&qb1)[HD / 16],
+                                           uint32_t lut_k, uint32_t plane_k, int c, float (&sr)[4]) {
+    constexpr int STEPS = HD / 16;
+    constexpr bool K4 = fmt_is4(KM), KMX = fmt_is_mx(KM);
+    constexpr int KMW = kmeta_words(KM, HD);
+    constexpr int NBK = HD / 32;
+    constexpr uint32_t k_cw4 = code_bytes(KM, HD);
+    const uint32_t ka8 = ka + 8 * krb;
+    if constexpr (KMX) {
+        float ks0[KMW], ks8[KMW];
+        if constexpr (KMW == 2) {
+            const float2 a = lds64f(mrow), b8 = lds64f(mrow + 8 * KMW * 4);
+            ks0[0] = a.x; ks0[1] = a.y; ks8[0] = b8.x; ks8[1] = b8.y;
+        } else {
+#pragma unroll
+            for (int w = 0; w < KMW / 4; ++w) {
+                const float4 a = lds128f(mrow + 16 * w), b8 = lds128f(mrow + 8 * KMW * 4 + 16 * w);
+                ks0[4 * w] = a.x; ks0[4 * w + 1] = a.y; ks0[4 * w + 2] = a.z; ks0[4 * w + 3] = a.w;
+                ks8[4 * w] = b8.x; ks8[4 * w + 1] = b8.y; ks8[4 * w + 2] = b8.z; ks8[4 * w + 3] = b8.w;
+            }
+        }
+#pragma unroll
+        for (int bk = 0; bk < NBK; ++bk) {
+            float acc[4];
+            if constexpr (K4) {
+                const uint32_t x0 = lds32(ka + 16 * bk), x8 = lds32(ka8 + 16 * bk);
+                uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                cvt_e2m1x8_f16x2(x0, a0, a1, a2, a3);
+                cvt_e2m1x8_f16x2(x8, b0, b1, b2, b3);
+                mma_f16_16816_z(acc, a0, b0, a1, b1, qb0[2 * bk], qb1[2 * bk]);
+                mma_f16_16816(acc, a2, b2, a3, b3, qb0[2 * bk + 1], qb1[2 * bk + 1]);
+            } else {
+                const uint32_t x0 = lds32(ka + 32 * bk), x8 = lds32(ka8 + 32 * bk);
+                const uint32_t y0 = lds32(ka + 32 * bk + 4), y8 = lds32(ka8 + 32 * bk + 4);
+                mma_f16_16816_z(acc, cvt_e4m3x2_f16x2(x0), cvt_e4m3x2_f16x2(x8), cvt_e4m3x2_hi_f16x2(x0),
+                                cvt_e4m3x2_hi_f16x2(x8), qb0[2 * bk], qb1[2 * bk]);
+                mma_f16_16816(acc, cvt_e4m3x2_f16x2(y0), cvt_e4m3x2_f16x2(y8), cvt_e4m3x2_hi_f16x2(y0),
+                              cvt_e4m3x2_hi_f16x2(y8), qb0[2 * bk + 1], qb1[2 * bk + 1]);
+            }
+            if (bk == 0) {
+                sr[0] = acc[0] * ks0[0]; sr[1] = acc[1] * ks0[0]; sr[2] = acc[2] * ks8[0]; sr[3] = acc[3] * ks8[0];
+            } else {
+                sr[0] = fmaf(acc[0], ks0[bk], sr[0]);
+                sr[1] = fmaf(acc[1], ks0[bk], sr[1]);
+                sr[2] = fmaf(acc[2], ks8[bk], sr[2]);
+                sr[3] = fmaf(acc[3], ks8[bk], sr[3]);
+            }
+        }
+    } else {
+        if constexpr (K4) {
+            constexpr int WPL = HD / 32;  // words of this lane per key
+            uint32_t sg[HD / 64], sg8[HD / 64];
+            if constexpr (KM == B200_NVFP4) {
+                // E4M3 block scales of the lane's 16-blocks c * (HD / 64) ..., as f16x2 {s, s}
+#pragma unroll
+                for (int i = 0; i < HD / 64; ++i) {
+                    const int blk = c * (HD / 64) + i;
+                    const uint32_t off = k_cw4 + (uint32_t)(blk & ~3) - c * (HD / 8);  // from the lane's first code byte
+                    const uint32_t w0 = lds32(ka + off), w8 = lds32(ka8 + off);
+                    const uint32_t b0 = (w0 >> (8 * (blk & 3))) & 0xffu, b8 = (w8 >> (8 * (blk & 3))) & 0xffu;
+                    sg[i] = cvt_e4m3x2_f16x2(b0 | (b0 << 8));
+                    sg8[i] = cvt_e4m3x2_f16x2(b8 | (b8 << 8));
+                }
+            }
+            constexpr bool KPL = KM == B200_TURBO_MSE && (B200_TURBO_PRMT & 1);
+            Tab16 kt;
+            if constexpr (KPL) kt = load_tab16(plane_k);
+#pragma unroll
+            for (int w = 0; w < WPL; ++w) {
+                const uint32_t x0 = lds32(ka + 4 * w), x8 = lds32(ka8 + 4 * w);
+                uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                if constexpr (KPL) {
+                    tab16_dq8(kt, x0, a0, a1, a2, a3);
+                    tab16_dq8(kt, x8, b0, b1, b2, b3);
+                } else {
+                    dq4<KM>(x0, lut_k, a0, a1, a2, a3);
+                    dq4<KM>(x8, lut_k, b0, b1, b2, b3);
+                }
+                if constexpr (KM == B200_NVFP4) {
+                    const uint32_t s0 = sg[w / 2], s8 = sg8[w / 2];
+                    a0 = hmul2_u32(a0, s0); a1 = hmul2_u32(a1, s0); a2 = hmul2_u32(a2, s0); a3 = hmul2_u32(a3, s0);
+                    b0 = hmul2_u32(b0, s8); b1 = hmul2_u32(b1, s8); b2 = hmul2_u32(b2, s8); b3 = hmul2_u32(b3, s8);
+                }
+                if (w == 0) mma_f16_16816_z(sr, a0, b0, a1, b1, qb0[0], qb1[0]);
+                else mma_f16_16816(sr, a0, b0, a1, b1, qb0[2 * w], qb1[2 * w]);
+                mma_f16_16816(sr, a2, b2, a3, b3, qb0[2 * w + 1], qb1[2 * w + 1]);
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < STEPS; ++s) {
+                const uint32_t x0 = lds32(ka + 4 * s), x8 = lds32(ka8 + 4 * s);
+                if (s == 0)
+                    mma_f16_16816_z(sr, cvt_e4m3x2_f16x2(x0), cvt_e4m3x2_f16x2(x8), cvt_e4m3x2_hi_f16x2(x0),
+                                    cvt_e4m3x2_hi_f16x2(x8), qb0[0], qb1[0]);
+                else
+                    mma_f16_16816(sr, cvt_e4m3x2_f16x2(x0), cvt_e4m3x2_f16x2(x8), cvt_e4m3x2_hi_f16x2(x0),
+                                  cvt_e4m3x2_hi_f16x2(x8), qb0[s], qb1[s]);
+            }
+        }
+        const float kp0 = u2f(lds32(mrow)), kp8 = u2f(lds32(mrow + 8 * 4));
+        sr[0] *= kp0; sr[1] *= kp0; sr[2] *= kp8; sr[3] *= kp8;
+    }
+}
+
+// O^T += V^T P^T for the 16 keys at `va` (the lane's first code byte of key 2c; rows vrb bytes apart): keys 2c, 2c+1 |
+// 2c+8, 2c+9, dims [g HD/8, (g+1) HD/8). `vsc_row`: the f16 block scales of the keys 2c, 2c + 1 (+ 16 bytes: 2c + 8,
+// 2c + 9), pb0 / pb1: the weights as B fragments.
+template <int VM, int HD>
+__device__ __forceinline__ void v_accum16(uint32_t va, uint32_t vrb, uint32_t vsc_row, uint32_t pb0, uint32_t pb1, float (&oacc)[HD / 16][4],
+                                          uint32_t lut_v, uint32_t plane_v, int g) {
+    constexpr bool V4 = fmt_is4(VM);
+    constexpr int NBV = vsc_blocks(VM, HD);
+#pragma unroll
+    for (int w = 0; w < (V4 ? (HD / 64 > 0 ? HD / 64 : 1) : HD / 32); ++w) {
+        const uint32_t xa = lds32(va + 4 * w), xb = lds32(va + vrb + 4 * w);
+        const uint32_t xc = lds32(va + 8 * vrb + 4 * w), xd = lds32(va + 9 * vrb + 4 * w);
+        if constexpr (V4) {
+            // nibbles of two keys side by side: byte i = (a[2i], b[2i]) and (a[2i+1], b[2i+1])
+            const uint32_t tl0 = (xa & 0x0f0f0f0fu) | ((xb & 0x0f0f0f0fu) << 4);
+            const uint32_t th0 = ((xa >> 4) & 0x0f0f0f0fu) | (xb & 0xf0f0f0f0u);
+            const uint32_t tl1 = (xc & 0x0f0f0f0fu) | ((xd & 0x0f0f0f0fu) << 4);
+            const uint32_t th1 = ((xc >> 4) & 0x0f0f0f0fu) | (xd & 0xf0f0f0f0u);
+            uint32_t l0[4], h0[4], l1[4], h1[4];
+            if constexpr (VM == B200_TURBO_MSE && (B200_TURBO_PRMT & 2)) {
+                const Tab16 vt = load_tab16(plane_v);
+                tab16_dq8(vt, tl0, l0[0], l0[1], l0[2], l0[3]);
+                tab16_dq8(vt, th0, h0[0], h0[1], h0[2], h0[3]);
+                tab16_dq8(vt, tl1, l1[0], l1[1], l1[2], l1[3]);
+                tab16_dq8(vt, th1, h1[0], h1[1], h1[2], h1[3]);
+            } else {
+                dq4<VM>(tl0, lut_v, l0[0], l0[1], l0[2], l0[3]);
+                dq4<VM>(th0, lut_v, h0[0], h0[1], h0[2], h0[3]);
+                dq4<VM>(tl1, lut_v, l1[0], l1[1], l1[2], l1[3]);
+                dq4<VM>(th1, lut_v, h1[0], h1[1], h1[2], h1[3]);
+            }
+            if constexpr (NBV > 0) {
+                const int blk = (g * (HD / 8) + 8 * w) / (HD / NBV);
+                const uint32_t sa = lds32(vsc_row + blk * WK * 2), sb = lds32(vsc_row + blk * WK * 2 + 16);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    l0[i] = hmul2_u32(l0[i], sa); h0[i] = hmul2_u32(h0[i], sa);
+                    l1[i] = hmul2_u32(l1[i], sb); h1[i] = hmul2_u32(h1[i], sb);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) mma_f16_16816(oacc[4 * w + i], l0[i], h0[i], l1[i], h1[i], pb0, pb1);
+        } else {
+            const uint32_t ta0 = __byte_perm(xa, xb, 0x5140), ta1 = __byte_perm(xa, xb, 0x7362);
+            const uint32_t tb0 = __byte_perm(xc, xd, 0x5140), tb1 = __byte_perm(xc, xd, 0x7362);
+            uint32_t l0 = cvt_e4m3x2_f16x2(ta0), h0 = cvt_e4m3x2_hi_f16x2(ta0);
+            uint32_t l1 = cvt_e4m3x2_f16x2(tb0), h1 = cvt_e4m3x2_hi_f16x2(tb0);
+            uint32_t l2 = cvt_e4m3x2_f16x2(ta1), h2 = cvt_e4m3x2_hi_f16x2(ta1);
+            uint32_t l3 = cvt_e4m3x2_f16x2(tb1), h3 = cvt_e4m3x2_hi_f16x2(tb1);
+            if constexpr (NBV > 0) {
+                const int blk = (g * (HD / 8) + 4 * w) / 32;
+                const uint32_t sa = lds32(vsc_row + blk * WK * 2), sb = lds32(vsc_row + blk * WK * 2 + 16);
+                l0 = hmul2_u32(l0, sa); h0 = hmul2_u32(h0, sa); l2 = hmul2_u32(l2, sa); h2 = hmul2_u32(h2, sa);
+                l1 = hmul2_u32(l1, sb); h1 = hmul2_u32(h1, sb); l3 = hmul2_u32(l3, sb); h3 = hmul2_u32(h3, sb);
+            }
+            mma_f16_16816(oacc[2 * w], l0, h0, l1, h1, pb0, pb1);
+            mma_f16_16816(oacc[2 * w + 1], l2, h2, l3, h3, pb0, pb1);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// A worker's share of the work
+// ---------------------------------------------------------------------------------------------
+struct Share {
+    uint64_t total;   // cost of the whole call
+    uint64_t x_end;   // end of this worker's range of cost positions
+    uint32_t nw;      // workers that own cost positions (never more than there are positions)
+    bool has_work;    // the worker owns at least one tile
+    Segment seg;      // its first segment
+};
+
+// Computed by every worker (warp) from the lengths alone. Never more workers than cost positions: every worker
+// between the owners of two tiles of a column then owns a tile of that column itself, so a column's segments are
+// the consecutive workers first owner .. last owner.
+__device__ __forceinline__ Share worker_share(const DecodeParams &p, uint32_t ny, uint32_t wid, uint32_t nw_grid, int lane) {
+    Share sh;
     const uint32_t cc = p.col_cost;
     auto batch_cost = [&](uint32_t bb) -> uint32_t {
         const uint32_t t = (uint32_t)make_column(p, bb).tiles;
@@ -642,200 +1018,107 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
             total += u;
         }
     }
-    // never more workers than cost positions: every worker between the owners of two tiles of a column then owns a
-    // tile of that column itself, so a column's segments are the consecutive workers first owner .. last owner
-    const uint32_t nw = (uint32_t)min((uint64_t)nw_grid, total);
-    bool has_work = wid < nw;
-    uint64_t x_begin = 0, x_end = 0;
-    Segment seg;
-    if (has_work) {
-        x_begin = total * wid / nw;
-        x_end = total * (wid + 1) / nw;
-        // batch entry that holds cost position x_begin, and the position of its first column
-        uint32_t b0 = 0;
-        uint64_t b0_start = 0;
-        if (p.kv_len == nullptr) {
-            const uint64_t per_b = batch_cost(0);
-            b0 = (uint32_t)(x_begin / per_b);
-            b0_start = (uint64_t)b0 * per_b;
-        } else if (few) {
-            bool found = false;
+    sh.total = total;
+    sh.nw = (uint32_t)min((uint64_t)nw_grid, total);
+    sh.has_work = wid < sh.nw;
+    sh.x_end = 0;
+    if (!sh.has_work) return sh;
+    const uint64_t x_begin = total * wid / sh.nw;
+    sh.x_end = total * (wid + 1) / sh.nw;
+    // batch entry that holds cost position x_begin, and the position of its first column
+    uint32_t b0 = 0;
+    uint64_t b0_start = 0;
+    if (p.kv_len == nullptr) {
+        const uint64_t per_b = batch_cost(0);
+        b0 = (uint32_t)(x_begin / per_b);
+        b0_start = (uint64_t)b0 * per_b;
+    } else if (few) {
+        bool found = false;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const uint32_t hit = __ballot_sync(0xffffffffu, fpre[k] + fincl[k] > x_begin);
-                if (hit && !found) {
-                    const int l = __ffs(hit) - 1;
-                    b0 = 32 * k + l;
-                    b0_start = fpre[k] + __shfl_sync(0xffffffffu, fincl[k] - fu[k], l);
-                    found = true;
-                }
-            }
-        } else {
-            uint64_t carry = 0;
-            for (uint32_t base = 0; base < p.b; base += 32) {
-                const uint32_t bb = base + lane;
-                const uint32_t u = bb < p.b ? batch_cost(bb) : 0u;
-                uint32_t incl = u;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (lane >= o) incl += t;
-                }
-                const uint32_t hit = __ballot_sync(0xffffffffu, carry + incl > x_begin);
-                if (hit) {
-                    const int l = __ffs(hit) - 1;
-                    b0 = base + l;
-                    b0_start = carry + __shfl_sync(0xffffffffu, incl - u, l);
-                    break;
-                }
-                carry += __shfl_sync(0xffffffffu, incl, 31);
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t hit = __ballot_sync(0xffffffffu, fpre[k] + fincl[k] > x_begin);
+            if (hit && !found) {
+                const int l = __ffs(hit) - 1;
+                b0 = 32 * k + l;
+                b0_start = fpre[k] + __shfl_sync(0xffffffffu, fincl[k] - fu[k], l);
+                found = true;
             }
         }
-        // first segment: the first tile at or after x_begin (a position inside a column's set up cost
-        // snaps to the column's first tile)
-        seg.b = b0;
-        seg.col = make_column(p, b0);
-        const uint32_t tb = (uint32_t)seg.col.tiles;
-        const uint64_t rem = x_begin - b0_start;
-        seg.y = (uint32_t)(rem / (tb + cc));
-        const uint32_t in_col = (uint32_t)(rem % (tb + cc));
-        seg.t0 = in_col > cc ? in_col - cc : 0u;
-        seg.x = b0_start + (uint64_t)seg.y * (tb + cc) + cc + seg.t0;
-        if (seg.x >= x_end) has_work = false;  // the share lies inside a set up gap: no tile
-        else seg.t1 = (uint32_t)min((uint64_t)tb, seg.t0 + (x_end - seg.x));
+    } else {
+        uint64_t carry = 0;
+        for (uint32_t base = 0; base < p.b; base += 32) {
+            const uint32_t bb = base + lane;
+            const uint32_t u = bb < p.b ? batch_cost(bb) : 0u;
+            uint32_t incl = u;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            const uint32_t hit = __ballot_sync(0xffffffffu, carry + incl > x_begin);
+            if (hit) {
+                const int l = __ffs(hit) - 1;
+                b0 = base + l;
+                b0_start = carry + __shfl_sync(0xffffffffu, incl - u, l);
+                break;
+            }
+            carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
     }
+    // first segment: the first tile at or after x_begin (a position inside a column's set up cost
+    // snaps to the column's first tile)
+    Segment &seg = sh.seg;
+    seg.b = b0;
+    seg.col = make_column(p, b0);
+    const uint32_t tb = (uint32_t)seg.col.tiles;
+    const uint64_t rem = x_begin - b0_start;
+    seg.y = (uint32_t)(rem / (tb + cc));
+    const uint32_t in_col = (uint32_t)(rem % (tb + cc));
+    seg.t0 = in_col > cc ? in_col - cc : 0u;
+    seg.x = b0_start + (uint64_t)seg.y * (tb + cc) + cc + seg.t0;
+    if (seg.x >= sh.x_end) sh.has_work = false;  // the share lies inside a set up gap: no tile
+    else seg.t1 = (uint32_t)min((uint64_t)tb, seg.t0 + (sh.x_end - seg.x));
+    return sh;
+}
 
+// ---------------------------------------------------------------------------------------------
+// What a worker does outside its tiles: the dependency on the stream's previous kernel, finished columns,
+// gathered outputs
+// ---------------------------------------------------------------------------------------------
+// Launched as a programmatic dependent (after_prev), the grid runs, with nothing read but the lengths, while the
+// stream's previous kernel is still running. What that kernel may still have in its hands (the outputs, the partial
+// results, the gather's step word; without the caller's word that the inputs are final also the query and the rows)
+// is not touched before prev_done() has returned: griddepcontrol.wait returns when the previous kernel has completed
+// and its writes are visible, and is a no-op after a plain launch. With final inputs a worker gets through the tiles
+// of its first segment before it has to ask: the step's first keys stream while the previous kernel's last blocks
+// finish, and only the rows it must not read yet (the last fresh_rows of a sequence) and all stores wait.
+struct Worker {
+    const DecodeParams &p;
+    int lane;
+    uint32_t wid, nw_grid, ny, ncols, prow;
+    uint64_t total;
+    uint32_t nw;
+    bool waited;
+    uint32_t g_step;  // gathered outputs: this step's number, read once the previous kernel is done
+    size_t g_base;    // and the offset of this rank's rows in the step's slot of every rank's buffer
 
+    __device__ __forceinline__ Worker(const DecodeParams &p_, int lane_, uint32_t wid_, uint32_t nw_grid_, uint32_t ny_, const Share &sh)
+        : p(p_), lane(lane_), wid(wid_), nw_grid(nw_grid_), ny(ny_), ncols(p_.b * ny_), prow(min((uint32_t)PACK, p_.rows_per_kv)),
+          total(sh.total), nw(sh.nw), waited(false), g_step(0), g_base(0) {}
 
-    const uint32_t meta_s = sbase + FIXED_SMEM + warp * META;    // [WK][KMW] f32
-    const uint32_t vmeta_s = meta_s + WK * KMW * 4;              // [WK] (sigma, log2 sigma)
-    const uint32_t vsc_s = vmeta_s + WK * 8;                     // [NBV][WK] f16
-    const uint32_t wstage_s = sbase + FIXED_SMEM + DW * META + p.qstage_bytes + (uint32_t)warp * NS * stage_bytes;
-    const uint32_t wbar_s = smem_u32(bars + warp * NS_MAX);
-    const bool plain = p.softcap <= 0.0f && p.alibi == nullptr;  // tiles inside every row's range take the unmasked path
-    bool wait_failed = false;
-
-    // Launched as a programmatic dependent (after_prev), the grid got here, with nothing read but the lengths, while the
-    // stream's previous kernel was still running. What that kernel may still have in its hands (the outputs, the partial
-    // results, the gather's step word; without the caller's word that the inputs are final also the query and the rows)
-    // is not touched before prev_done() has returned: griddepcontrol.wait returns when the previous kernel has completed
-    // and its writes are visible, and is a no-op after a plain launch. With final inputs a worker gets through the tiles
-    // of its first segment before it has to ask: the step's first keys stream while the previous kernel's last blocks
-    // finish, and only the rows it must not read yet (the last fresh_rows of a sequence) and all stores wait.
-    bool waited = false;
-    uint32_t g_step = 0;   // gathered outputs: this step's number, read once the previous kernel is done
-    size_t g_base = 0;     // and the offset of this rank's rows in the step's slot of every rank's buffer
-    auto prev_done = [&]() {
+    __device__ __forceinline__ void prev_done() {
         if (waited) return;
         asm volatile("griddepcontrol.wait;" ::: "memory");
         waited = true;
-        B200_T(2);
         if (p.ctr && p.world) {
             g_step = *reinterpret_cast<volatile uint32_t *>(p.step) + 1u;
-            g_base = ((size_t)(g_step & 1u) * p.world + p.rank) * ((size_t)p.b * p.hq * p.lq) * HD;
+            g_base = ((size_t)(g_step & 1u) * p.world + p.rank) * ((size_t)p.b * p.hq * p.lq) * p.d;
         }
-    };
-    if (!p.prefetch) prev_done();
+    }
 
-    // ------------------------------------------------------------------ the copy side
-    // runs up to NS tiles ahead of the compute side through the same list of segments; tile t of the worker's list
-    // lives in stage t mod NS, so the copy issued after a tile is consumed goes into the stage just read
-    Segment iseg = seg;
-    int i_left = 0;          // tiles still to copy in the copy side's segment
-    int i_simple = 0;        // of those, whole tiles that do not end their column: constant copy sizes, no tail handling
-    bool i_more = true;      // the copy side has segments left
-    uintptr_t i_k = 0, i_v = 0;        // 16-byte aligned global addresses of the next tile's copies
-    uint32_t i_koff = 0, i_voff = 0;   // offset of the tile's first row inside its copy
-    uint32_t i_kb = 0, i_vb = 0;       // bytes of a whole tile's copies
-    int i_key = 0;                     // first key of the next tile
-    auto copy_enter = [&]() {  // per-segment constants of the copy side
-        i_left = (int)(iseg.t1 - iseg.t0);
-        i_simple = i_left - (iseg.t1 == (uint32_t)iseg.col.tiles ? 1 : 0);
-        const uint32_t hk = iseg.y / p.packs;
-        i_key = iseg.col.lo + (int)iseg.t0 * WK;
-        const uintptr_t ka = reinterpret_cast<uintptr_t>(p.k_rows + (size_t)iseg.b * p.k_sb + (size_t)hk * p.k_sh) + (uintptr_t)(uint32_t)i_key * krb;
-        const uintptr_t va = reinterpret_cast<uintptr_t>(p.v_rows + (size_t)iseg.b * p.v_sb + (size_t)hk * p.v_sh) + (uintptr_t)(uint32_t)i_key * vrb;
-        i_koff = (uint32_t)(ka & 15u);
-        i_voff = (uint32_t)(va & 15u);
-        i_k = ka - i_koff;
-        i_v = va - i_voff;
-        i_kb = (i_koff + (uint32_t)WK * krb + 15u) & ~15u;
-        i_vb = (i_voff + (uint32_t)WK * vrb + 15u) & ~15u;
-    };
-    if (has_work) copy_enter();
-    // copies the next tile into stage `st` with barrier `bar` (the caller checked i_left > 0) and moves on
-    auto copy_tile = [&](uint32_t st, uint32_t bar) {
-        if (!waited && i_key + min(WK, iseg.col.hi - i_key) > iseg.col.lk - (int)p.fresh_rows) prev_done();
-        if (i_simple > 0) {
-            --i_simple;
-            if (lane == 0) {
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(i_kb + i_vb) : "memory");
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(st), "l"(i_k),
-                             "r"(i_kb), "r"(bar)
-                             : "memory");
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(st + k_stage_bytes),
-                             "l"(i_v), "r"(i_vb), "r"(bar)
-                             : "memory");
-            }
-        } else {
-            // the last tile of its column
-            const int nkeys = min(WK, iseg.col.hi - i_key);
-            // Rows below lk are readable, and so is the row after a tile when the cache has spare rows
-            // (rows_cap): the 16-byte round up of a copy may then run into the next row. Otherwise the
-            // last tile of a sequence copies the round down and fetches the few remaining words with
-            // plain loads.
-            const bool tail = i_key + nkeys >= iseg.col.lk && i_key + nkeys >= (int)p.rows_cap;
-            uint32_t kb = (i_koff + (uint32_t)nkeys * krb + 15u) & ~15u, vb = (i_voff + (uint32_t)nkeys * vrb + 15u) & ~15u;
-            if (tail) {
-                const uint32_t ke = i_koff + (uint32_t)nkeys * krb, ve = i_voff + (uint32_t)nkeys * vrb;  // ends, from the copy start
-                kb = ke & ~15u;
-                vb = ve & ~15u;
-                if (lane < 4) {
-                    const uint32_t o = kb + 4u * lane;
-                    if (o >= i_koff && o < ke) sts32(st + o, *reinterpret_cast<const uint32_t *>(i_k + o));
-                } else if (lane < 8) {
-                    const uint32_t o = vb + 4u * (lane - 4);
-                    if (o >= i_voff && o < ve) sts32(st + k_stage_bytes + o, *reinterpret_cast<const uint32_t *>(i_v + o));
-                }
-                __syncwarp();
-            }
-            if (lane == 0) {
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kb + vb) : "memory");
-                if (kb)
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(st),
-                                 "l"(i_k), "r"(kb), "r"(bar)
-                                 : "memory");
-                if (vb)
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                     st + k_stage_bytes),
-                                 "l"(i_v), "r"(vb), "r"(bar)
-                                 : "memory");
-            }
-        }
-        // WK rows are a multiple of 16 bytes: the next tile keeps its offset inside its copy
-        i_k += (uintptr_t)WK * krb;
-        i_v += (uintptr_t)WK * vrb;
-        i_key += WK;
-        if (--i_left == 0 && i_more) {
-            i_more = next_segment(iseg, p, ny, x_end);
-            if (i_more) copy_enter();
-        }
-    };
-    // Filling the ring. With the caller's word that the inputs are final (prefetch) all stages are asked for right away.
-    // Otherwise the first tile alone, and the other stages once the first query rows are loaded: with every worker of
-    // the grid asking for all its stages at once, the first tiles would arrive behind 26 MB of later ones.
-    int primed = 0;
-    auto prime = [&](int upto) {
-        for (; primed < upto && i_left > 0; ++primed) copy_tile(wstage_s + (uint32_t)primed * stage_bytes, wbar_s + 8u * (uint32_t)primed);
-    };
-    if (has_work) prime(p.prefetch ? NS : 1);
-
-    const uint32_t prow = min((uint32_t)PACK, R);                // rows of a partial result
-    float *qstage = reinterpret_cast<float *>(smem + FIXED_SMEM + DW * META) + (size_t)warp * PACK * HD;  // only with a rotated cache
-    const uint32_t ncols = p.b * ny;
-    // a column of this call is finished (its rows are stored): with gathered outputs the worker that finishes the last
-    // one publishes the step to the other ranks
-    auto column_done = [&]() {
+    // a column of this call is finished (its rows are stored): with gathered outputs the worker that finishes the
+    // call's last column publishes the step to the other ranks
+    __device__ __forceinline__ void column_done() {
         if (!p.world) return;
         __threadfence_system();
         __syncwarp();
@@ -846,9 +1129,11 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
             __threadfence_system();
             gather_publish(p.peer_flags, p.world, p.rank, p.step, g_step, p.gather_polls, p.status, p.lib_status, lane);
         }
-    };
+    }
+
     // columns without a visible key get no worker: their rows are zeros, written once the previous kernel is done
-    auto zero_columns = [&]() {
+    template <int HD>
+    __device__ __forceinline__ void zero_columns(bool has_work) {
         if (!(p.ctr && (p.kv_len != nullptr || !has_work))) return;
         prev_done();
         for (uint32_t col = wid; col < ncols; col += nw_grid) {
@@ -866,532 +1151,21 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
             }
             column_done();
         }
-    };
-    if (!has_work) {
-        zero_columns();
-        return;
     }
 
-    // ------------------------------------------------------------------ the compute side
-    // lane offsets inside a tile: K rows g (and g + 8), V rows 2c (and 2c + 1, 2c + 8, 2c + 9)
-    const uint32_t k_lane = g * krb + (KMX ? (K4 ? 4u * c : 8u * c) : (K4 ? c * (HD / 8) : c * (HD / 4)));
-    const uint32_t v_lane = 2 * c * vrb + (V4 ? g * (HD / 16) : g * (HD / 8));
-    const uint32_t mrow_g = meta_s + g * KMW * 4, vmeta_g = vmeta_s + g * 8, vsc_c = vsc_s + 4 * c;
-    uint32_t c_st = wstage_s, c_bar = wbar_s;
-    int c_stage = 0;
-    uint32_t par = 0;  // parity to wait for on the current stage: flips every time the ring wraps
-
-    uint32_t qb0[STEPS], qb1[STEPS];
-    float qs[2], qs2[2];
-    float oacc[STEPS][4];
-
-    // scores of keys g and g + 8 of the 16 keys at `ka` against the rows 2c, 2c + 1:
-    // sr[2 k + e] = key g + 8 k, row 2c + e
-    auto k_scores = [&](uint32_t ka, uint32_t mrow, float (&sr)[4]) {
-        const uint32_t ka8 = ka + 8 * krb;
-        if constexpr (KMX) {
-            float ks0[KMW], ks8[KMW];
-            if constexpr (KMW == 2) {
-                const float2 a = lds64f(mrow), b8 = lds64f(mrow + 8 * KMW * 4);
-                ks0[0] = a.x; ks0[1] = a.y; ks8[0] = b8.x; ks8[1] = b8.y;
-            } else {
-#pragma unroll
-                for (int w = 0; w < KMW / 4; ++w) {
-                    const float4 a = lds128f(mrow + 16 * w), b8 = lds128f(mrow + 8 * KMW * 4 + 16 * w);
-                    ks0[4 * w] = a.x; ks0[4 * w + 1] = a.y; ks0[4 * w + 2] = a.z; ks0[4 * w + 3] = a.w;
-                    ks8[4 * w] = b8.x; ks8[4 * w + 1] = b8.y; ks8[4 * w + 2] = b8.z; ks8[4 * w + 3] = b8.w;
-                }
-            }
-#pragma unroll
-            for (int bk = 0; bk < NBK; ++bk) {
-                float acc[4];
-                if constexpr (K4) {
-                    const uint32_t x0 = lds32(ka + 16 * bk), x8 = lds32(ka8 + 16 * bk);
-                    uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
-                    cvt_e2m1x8_f16x2(x0, a0, a1, a2, a3);
-                    cvt_e2m1x8_f16x2(x8, b0, b1, b2, b3);
-                    mma_f16_16816_z(acc, a0, b0, a1, b1, qb0[2 * bk], qb1[2 * bk]);
-                    mma_f16_16816(acc, a2, b2, a3, b3, qb0[2 * bk + 1], qb1[2 * bk + 1]);
-                } else {
-                    const uint32_t x0 = lds32(ka + 32 * bk), x8 = lds32(ka8 + 32 * bk);
-                    const uint32_t y0 = lds32(ka + 32 * bk + 4), y8 = lds32(ka8 + 32 * bk + 4);
-                    mma_f16_16816_z(acc, cvt_e4m3x2_f16x2(x0), cvt_e4m3x2_f16x2(x8), cvt_e4m3x2_hi_f16x2(x0),
-                                    cvt_e4m3x2_hi_f16x2(x8), qb0[2 * bk], qb1[2 * bk]);
-                    mma_f16_16816(acc, cvt_e4m3x2_f16x2(y0), cvt_e4m3x2_f16x2(y8), cvt_e4m3x2_hi_f16x2(y0),
-                                  cvt_e4m3x2_hi_f16x2(y8), qb0[2 * bk + 1], qb1[2 * bk + 1]);
-                }
-                if (bk == 0) {
-                    sr[0] = acc[0] * ks0[0]; sr[1] = acc[1] * ks0[0]; sr[2] = acc[2] * ks8[0]; sr[3] = acc[3] * ks8[0];
-                } else {
-                    sr[0] = fmaf(acc[0], ks0[bk], sr[0]);
-                    sr[1] = fmaf(acc[1], ks0[bk], sr[1]);
-                    sr[2] = fmaf(acc[2], ks8[bk], sr[2]);
-                    sr[3] = fmaf(acc[3], ks8[bk], sr[3]);
-                }
-            }
-        } else {
-            if constexpr (K4) {
-                constexpr int WPL = HD / 32;  // words of this lane per key
-                uint32_t sg[HD / 64], sg8[HD / 64];
-                if constexpr (KM == B200_NVFP4) {
-                    // E4M3 block scales of the lane's 16-blocks c * (HD / 64) ..., as f16x2 {s, s}
-#pragma unroll
-                    for (int i = 0; i < HD / 64; ++i) {
-                        const int blk = c * (HD / 64) + i;
-                        const uint32_t off = k_cw4 + (uint32_t)(blk & ~3) - c * (HD / 8);  // from the lane's first code byte
-                        const uint32_t w0 = lds32(ka + off), w8 = lds32(ka8 + off);
-                        const uint32_t b0 = (w0 >> (8 * (blk & 3))) & 0xffu, b8 = (w8 >> (8 * (blk & 3))) & 0xffu;
-                        sg[i] = cvt_e4m3x2_f16x2(b0 | (b0 << 8));
-                        sg8[i] = cvt_e4m3x2_f16x2(b8 | (b8 << 8));
-                    }
-                }
-                constexpr bool KPL = KM == B200_TURBO_MSE && (B200_TURBO_PRMT & 1);
-                Tab16 kt;
-                if constexpr (KPL) kt = load_tab16(plane_k);
-#pragma unroll
-                for (int w = 0; w < WPL; ++w) {
-                    const uint32_t x0 = lds32(ka + 4 * w), x8 = lds32(ka8 + 4 * w);
-                    uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
-                    if constexpr (KPL) {
-                        tab16_dq8(kt, x0, a0, a1, a2, a3);
-                        tab16_dq8(kt, x8, b0, b1, b2, b3);
-                    } else {
-                        dq4<KM>(x0, lut_k, a0, a1, a2, a3);
-                        dq4<KM>(x8, lut_k, b0, b1, b2, b3);
-                    }
-                    if constexpr (KM == B200_NVFP4) {
-                        const uint32_t s0 = sg[w / 2], s8 = sg8[w / 2];
-                        a0 = hmul2_u32(a0, s0); a1 = hmul2_u32(a1, s0); a2 = hmul2_u32(a2, s0); a3 = hmul2_u32(a3, s0);
-                        b0 = hmul2_u32(b0, s8); b1 = hmul2_u32(b1, s8); b2 = hmul2_u32(b2, s8); b3 = hmul2_u32(b3, s8);
-                    }
-                    if (w == 0) mma_f16_16816_z(sr, a0, b0, a1, b1, qb0[0], qb1[0]);
-                    else mma_f16_16816(sr, a0, b0, a1, b1, qb0[2 * w], qb1[2 * w]);
-                    mma_f16_16816(sr, a2, b2, a3, b3, qb0[2 * w + 1], qb1[2 * w + 1]);
-                }
-            } else {
-#pragma unroll
-                for (int s = 0; s < STEPS; ++s) {
-                    const uint32_t x0 = lds32(ka + 4 * s), x8 = lds32(ka8 + 4 * s);
-                    if (s == 0)
-                        mma_f16_16816_z(sr, cvt_e4m3x2_f16x2(x0), cvt_e4m3x2_f16x2(x8), cvt_e4m3x2_hi_f16x2(x0),
-                                        cvt_e4m3x2_hi_f16x2(x8), qb0[0], qb1[0]);
-                    else
-                        mma_f16_16816(sr, cvt_e4m3x2_f16x2(x0), cvt_e4m3x2_f16x2(x8), cvt_e4m3x2_hi_f16x2(x0),
-                                      cvt_e4m3x2_hi_f16x2(x8), qb0[s], qb1[s]);
-                }
-            }
-            const float kp0 = u2f(lds32(mrow)), kp8 = u2f(lds32(mrow + 8 * 4));
-            sr[0] *= kp0; sr[1] *= kp0; sr[2] *= kp8; sr[3] *= kp8;
-        }
-    };
-
-    // O^T += V^T P^T for the 16 keys at `va`: keys 2c, 2c+1 | 2c+8, 2c+9, dims [g HD/8, (g+1) HD/8)
-    auto v_accum = [&](uint32_t va, uint32_t vsc_row, uint32_t pb0, uint32_t pb1) {
-#pragma unroll
-        for (int w = 0; w < (V4 ? (HD / 64 > 0 ? HD / 64 : 1) : HD / 32); ++w) {
-            const uint32_t xa = lds32(va + 4 * w), xb = lds32(va + vrb + 4 * w);
-            const uint32_t xc = lds32(va + 8 * vrb + 4 * w), xd = lds32(va + 9 * vrb + 4 * w);
-            if constexpr (V4) {
-                // nibbles of two keys side by side: byte i = (a[2i], b[2i]) and (a[2i+1], b[2i+1])
-                const uint32_t tl0 = (xa & 0x0f0f0f0fu) | ((xb & 0x0f0f0f0fu) << 4);
-                const uint32_t th0 = ((xa >> 4) & 0x0f0f0f0fu) | (xb & 0xf0f0f0f0u);
-                const uint32_t tl1 = (xc & 0x0f0f0f0fu) | ((xd & 0x0f0f0f0fu) << 4);
-                const uint32_t th1 = ((xc >> 4) & 0x0f0f0f0fu) | (xd & 0xf0f0f0f0u);
-                uint32_t l0[4], h0[4], l1[4], h1[4];
-                if constexpr (VM == B200_TURBO_MSE && (B200_TURBO_PRMT & 2)) {
-                    const Tab16 vt = load_tab16(plane_v);
-                    tab16_dq8(vt, tl0, l0[0], l0[1], l0[2], l0[3]);
-                    tab16_dq8(vt, th0, h0[0], h0[1], h0[2], h0[3]);
-                    tab16_dq8(vt, tl1, l1[0], l1[1], l1[2], l1[3]);
-                    tab16_dq8(vt, th1, h1[0], h1[1], h1[2], h1[3]);
-                } else {
-                    dq4<VM>(tl0, lut_v, l0[0], l0[1], l0[2], l0[3]);
-                    dq4<VM>(th0, lut_v, h0[0], h0[1], h0[2], h0[3]);
-                    dq4<VM>(tl1, lut_v, l1[0], l1[1], l1[2], l1[3]);
-                    dq4<VM>(th1, lut_v, h1[0], h1[1], h1[2], h1[3]);
-                }
-                if constexpr (NBV > 0) {
-                    const int blk = (g * (HD / 8) + 8 * w) / (HD / NBV);
-                    const uint32_t sa = lds32(vsc_row + blk * WK * 2), sb = lds32(vsc_row + blk * WK * 2 + 16);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        l0[i] = hmul2_u32(l0[i], sa); h0[i] = hmul2_u32(h0[i], sa);
-                        l1[i] = hmul2_u32(l1[i], sb); h1[i] = hmul2_u32(h1[i], sb);
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < 4; ++i) mma_f16_16816(oacc[4 * w + i], l0[i], h0[i], l1[i], h1[i], pb0, pb1);
-            } else {
-                const uint32_t ta0 = __byte_perm(xa, xb, 0x5140), ta1 = __byte_perm(xa, xb, 0x7362);
-                const uint32_t tb0 = __byte_perm(xc, xd, 0x5140), tb1 = __byte_perm(xc, xd, 0x7362);
-                uint32_t l0 = cvt_e4m3x2_f16x2(ta0), h0 = cvt_e4m3x2_hi_f16x2(ta0);
-                uint32_t l1 = cvt_e4m3x2_f16x2(tb0), h1 = cvt_e4m3x2_hi_f16x2(tb0);
-                uint32_t l2 = cvt_e4m3x2_f16x2(ta1), h2 = cvt_e4m3x2_hi_f16x2(ta1);
-                uint32_t l3 = cvt_e4m3x2_f16x2(tb1), h3 = cvt_e4m3x2_hi_f16x2(tb1);
-                if constexpr (NBV > 0) {
-                    const int blk = (g * (HD / 8) + 4 * w) / 32;
-                    const uint32_t sa = lds32(vsc_row + blk * WK * 2), sb = lds32(vsc_row + blk * WK * 2 + 16);
-                    l0 = hmul2_u32(l0, sa); h0 = hmul2_u32(h0, sa); l2 = hmul2_u32(l2, sa); h2 = hmul2_u32(h2, sa);
-                    l1 = hmul2_u32(l1, sb); h1 = hmul2_u32(h1, sb); l3 = hmul2_u32(l3, sb); h3 = hmul2_u32(h3, sb);
-                }
-                mma_f16_16816(oacc[2 * w], l0, h0, l1, h1, pb0, pb1);
-                mma_f16_16816(oacc[2 * w + 1], l2, h2, l3, h3, pb0, pb1);
-            }
-        }
-    };
-
-#ifdef B200_TRACE
-    bool traced_first = false;
-#endif
-    bool more = true;
-    while (more) {
-        // ================================================================ segment set up
-        const uint32_t hk = seg.y / p.packs, pack = seg.y % p.packs;
-        const Column &col = seg.col;
-        auto row_range = [&](uint32_t r, int &lo, int &hi, int &pos) {
-            const long long i = p.lq == 1 ? 0 : r / G;
-            const long long ps = i + (long long)col.lk - (long long)p.lq;
-            long long l = p.wl >= 0 ? max(ps - p.wl, 0ll) : 0ll;
-            long long h = p.wr >= 0 ? min(ps + p.wr + 1, (long long)col.lk) : (long long)col.lk;
-            l = min(l, (long long)col.lk);
-            h = max(h, l);
-            lo = (int)l;
-            hi = (int)h;
-            pos = (int)max(min(ps, 2147483647ll), -2147483647ll);
-        };
-        // rows are ordered by token: the last row of the pack has the highest lower bound, the first the lowest upper bound
-        int LOmax, HImin;
-        {
-            int lo, hi, pos;
-            row_range(min(pack * PACK + PACK, R) - 1, lo, hi, pos);
-            LOmax = lo;
-            row_range(pack * PACK, lo, hi, pos);
-            HImin = hi;
-        }
-        // running maxima (log2 domain, value scale folded in) and partial normalizers of rows 2c, 2c + 1
-        float M[2] = {-1e30f, -1e30f}, lsum[2] = {0.0f, 0.0f};
-#pragma unroll
-        for (int mt = 0; mt < STEPS; ++mt) oacc[mt][0] = oacc[mt][1] = oacc[mt][2] = oacc[mt][3] = 0.0f;
-
-        if (!wait_failed) {
-        // query row g of the pack: power of two normalization, then the f16 B fragments of K Q^T. Per
-        // k-step the four contraction slots of this lane are the consecutive dims dbase(s) ... + 3,
-        // so the four lanes of a quad hold the whole row between them.
-        {
-            const uint32_t r = pack * PACK + g;
-            float qv[STEPS][4];
-            if (p.k.rot == B200_ROT_HADAMARD) {
-                __syncwarp();
-                for (int idx = lane; idx < PACK * HD; idx += 32) {
-                    const uint32_t rr = idx / HD, dd = idx % HD, r2 = pack * PACK + rr;
-                    float v = 0.0f;
-                    if (r2 < R) {
-                        const uint32_t i = p.lq == 1 ? 0u : r2 / G, h = hk * G + (p.lq == 1 ? r2 : r2 % G);
-                        v = load_elem_rt(p.q, seg.b * p.q_sb + h * p.q_sh + i * p.q_ss + dd, p.q_dtype);
-                    }
-                    qstage[idx] = v;
-                }
-                __syncwarp();
-                for (int rr = 0; rr < PACK; ++rr) warp_hadamard(qstage + rr * HD, HD, p.k.signs, true, lane);
-                __syncwarp();
-#pragma unroll
-                for (int s = 0; s < STEPS; ++s) {
-                    const int dbase = KMX ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : c * (HD / 4) + 4 * s;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) qv[s][j] = qstage[g * HD + dbase + j];
-                }
-            } else {
-                const uint32_t i = p.lq == 1 ? 0u : r / G, h = hk * G + (p.lq == 1 ? r : r % G);
-                const size_t qoff = seg.b * p.q_sb + h * p.q_sh + i * p.q_ss;
-                const bool q16 = p.q_dtype == B200_F16 || p.q_dtype == B200_BF16;
-                if (q16 && r < R && ((reinterpret_cast<uintptr_t>(p.q) + 2 * qoff) & 7u) == 0) {
-                    // 16-bit rows on an 8-byte boundary: the four contraction slots of a k-step in one load, all
-                    // loads of the row issued before the first conversion
-                    const uint16_t *q16p = reinterpret_cast<const uint16_t *>(p.q) + qoff;
-                    uint2 raw[STEPS];
-#pragma unroll
-                    for (int s = 0; s < STEPS; ++s) {
-                        const int dbase = KMX ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : c * (HD / 4) + 4 * s;
-                        raw[s] = __ldg(reinterpret_cast<const uint2 *>(q16p + dbase));
-                    }
-                    if (p.q_dtype == B200_BF16) {
-#pragma unroll
-                        for (int s = 0; s < STEPS; ++s) {
-                            qv[s][0] = u2f(raw[s].x << 16); qv[s][1] = u2f(raw[s].x & 0xffff0000u);
-                            qv[s][2] = u2f(raw[s].y << 16); qv[s][3] = u2f(raw[s].y & 0xffff0000u);
-                        }
-                    } else {
-#pragma unroll
-                        for (int s = 0; s < STEPS; ++s) {
-                            qv[s][0] = f16_bits_to_f((uint16_t)(raw[s].x & 0xffffu)); qv[s][1] = f16_bits_to_f((uint16_t)(raw[s].x >> 16));
-                            qv[s][2] = f16_bits_to_f((uint16_t)(raw[s].y & 0xffffu)); qv[s][3] = f16_bits_to_f((uint16_t)(raw[s].y >> 16));
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int s = 0; s < STEPS; ++s) {
-                        const int dbase = KMX ? 32 * (s >> 1) + 8 * c + 4 * (s & 1) : c * (HD / 4) + 4 * s;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) qv[s][j] = r < R ? load_elem_rt(p.q, qoff + dbase + j, p.q_dtype) : 0.0f;
-                    }
-                }
-            }
-            float am = 0.0f;
-#pragma unroll
-            for (int s = 0; s < STEPS; ++s)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) am = fmaxf(am, fabsf(qv[s][j]));
-            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
-            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
-            int e = 0;
-            if (am > 0.0f && am < INFINITY) e = (int)((f2u(am) >> 23) & 0xffu) - 127 - 7;
-            e = max(min(e, 100), -100);
-            const float down = u2f((uint32_t)(127 - e) << 23), up = u2f((uint32_t)(127 + e) << 23);
-            const float qscale = p.scale * up;
-            qs[0] = __shfl_sync(0xffffffffu, qscale, (2 * c) * 4);
-            qs[1] = __shfl_sync(0xffffffffu, qscale, (2 * c + 1) * 4);
-            qs2[0] = qs[0] * LOG2E;
-            qs2[1] = qs[1] * LOG2E;
-#pragma unroll
-            for (int s = 0; s < STEPS; ++s) {
-                qb0[s] = pack_f16x2(qv[s][0] * down, qv[s][1] * down);
-                qb1[s] = pack_f16x2(qv[s][2] * down, qv[s][3] * down);
-            }
-        }
-
-        // the other stages of the ring (first segment only)
-        prime(NS);
-
-        // ================================================================ the tiles of the segment
-        const int n_t = (int)(seg.t1 - seg.t0);
-        int key0 = col.lo + (int)seg.t0 * WK;
-        const uint32_t koff = (uint32_t)((reinterpret_cast<uintptr_t>(p.k_rows + (size_t)seg.b * p.k_sb + (size_t)hk * p.k_sh) + (uintptr_t)(uint32_t)key0 * krb) & 15u);
-        const uint32_t voff = (uint32_t)((reinterpret_cast<uintptr_t>(p.v_rows + (size_t)seg.b * p.v_sb + (size_t)hk * p.v_sh) + (uintptr_t)(uint32_t)key0 * vrb) & 15u);
-        const uint32_t kt_off = koff + k_lane, vt_off = k_stage_bytes + voff + v_lane;
-        const uint32_t kr_off = koff + lane * krb, vr_off = k_stage_bytes + voff + lane * vrb;
-        for (int n = 0; n < n_t; ++n, key0 += WK) {
-            {
-                uint32_t ok = 0;
-                for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin)
-                    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                                 : "=r"(ok)
-                                 : "r"(c_bar), "r"(par)
-                                 : "memory");
-                if (!ok) {
-                    // the copy never landed: give up on the keys (the outputs are void, the status says so), stop
-                    // copying, but keep counting this worker's segments so that no column waits for it
-                    wait_failed = true;
-                    i_left = 0;
-                    i_more = false;
-                    break;
-                }
-            }
-
-#ifdef B200_TRACE
-            if (!traced_first) { traced_first = true; B200_T(3); }
-#endif
-            const uint32_t st_s = c_st;
-            const int nkeys = min(WK, col.hi - key0);
-            if (nkeys < WK) {
-                // rows past the column hold stale bytes: clear them so that masked keys decode to finite values
-                const uint32_t kt = st_s + koff, vt = st_s + k_stage_bytes + voff;
-                for (uint32_t w = nkeys * (krb >> 2) + lane; w < WK * (krb >> 2); w += 32) sts32(kt + 4 * w, 0u);
-                for (uint32_t w = nkeys * (vrb >> 2) + lane; w < WK * (vrb >> 2); w += 32) sts32(vt + 4 * w, 0u);
-                __syncwarp();
-            }
-            // ---- per-key scalars of the tile, lane = key
-#if !(B200_ABL & 4)
-            {
-                const uint32_t kr = st_s + kr_off, vr = st_s + vr_off;
-                const float k0 = u2f(lds32(kr + k_rsc4));
-                if constexpr (KMX) {
-#pragma unroll
-                    for (int w = 0; w < (NBK + 3) / 4; ++w) {
-                        const uint32_t aux = lds32(kr + k_cw4 + 4 * w);
-                        // rsc0 * 2^(e - 127); a zero code gives +0 (its block holds zero codes)
-                        float sc[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) sc[i] = k0 * u2f(((aux >> (8 * i)) & 0xffu) << 23);
-                        if constexpr (KMW >= 4) {
-                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(meta_s + (lane * KMW + 4 * w) * 4), "f"(sc[0]), "f"(sc[1]),
-                                         "f"(sc[2]), "f"(sc[3])
-                                         : "memory");
-                        } else {
-                            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(meta_s + lane * KMW * 4), "f"(sc[0]), "f"(sc[1]) : "memory");
-                        }
-                    }
-                } else {
-                    sts32(meta_s + lane * 4, f2u(k0));
-                }
-                float sigma = u2f(lds32(vr + v_rsc4));
-                if constexpr (fmt_is_mx(VM)) {
-                    uint32_t aux[(NBV + 3) / 4];
-                    uint32_t em = 0;
-#pragma unroll
-                    for (int w = 0; w < (NBV + 3) / 4; ++w) {
-                        aux[w] = lds32(vr + v_cw4 + 4 * w);
-                        em = w == 0 ? aux[w] : __vmaxu4(em, aux[w]);
-                    }
-                    const uint32_t emax = max_byte(em);
-                    sigma *= u2f(emax << 23);
-#pragma unroll
-                    for (int bk = 0; bk < NBV; ++bk) {
-                        const int e = (int)((aux[bk >> 2] >> (8 * (bk & 3))) & 0xffu);
-                        sts16(vsc_s + (bk * WK + lane) * 2, pow2_f16(e - (int)emax));
-                    }
-                } else if constexpr (VM == B200_NVFP4) {
-#pragma unroll
-                    for (int w = 0; w < NBV / 4; ++w) {
-                        const uint32_t aux = lds32(vr + v_cw4 + 4 * w);
-                        const uint32_t lo = cvt_e4m3x2_f16x2(aux), hi = cvt_e4m3x2_hi_f16x2(aux);
-                        sts16(vsc_s + ((4 * w) * WK + lane) * 2, lo & 0xffffu);
-                        sts16(vsc_s + ((4 * w + 1) * WK + lane) * 2, lo >> 16);
-                        sts16(vsc_s + ((4 * w + 2) * WK + lane) * 2, hi & 0xffffu);
-                        sts16(vsc_s + ((4 * w + 3) * WK + lane) * 2, hi >> 16);
-                    }
-                }
-                // sigma in [2^-100, 2^100], or 0 (then log2 = -inf: the key only counts in the normalizer)
-                float sc = fminf(fmaxf(sigma, 7.8886091e-31f), 1.2676506e30f);
-                sc = sigma > 0.0f ? sc : 0.0f;
-                asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(vmeta_s + lane * 8), "f"(sc), "f"(fast_log2(sc)) : "memory");
-                __syncwarp();
-            }
-#endif
-            // ---- scores of the 32 keys: sr[u][2 k + e] = key 16 u + g + 8 k, row 2c + e
-            float sr[2][4];
-#if (B200_ABL & 1)
-            for (int u = 0; u < 2; ++u) for (int e = 0; e < 4; ++e) sr[u][e] = 0.001f * (float)(lane + e);
-#else
-            k_scores(st_s + kt_off, mrow_g, sr[0]);
-            k_scores(st_s + kt_off + 16 * krb, mrow_g + 16 * KMW * 4, sr[1]);
-#endif
-            // ---- online softmax
-            float2 vm[4];  // (sigma, log2 sigma) of the keys g, g + 8, g + 16, g + 24
-#pragma unroll
-            for (int k = 0; k < 4; ++k) vm[k] = lds64f(vmeta_g + k * 64);
-            uint32_t pb[4];
-#if (B200_ABL & 8)
-            for (int k = 0; k < 4; ++k) pb[k] = f2u(sr[k >> 1][k & 1] + vm[k].x);
-            if (false) {
-#else
-            if (plain && nkeys == WK && key0 >= LOmax && key0 + WK <= HImin) {
-#endif
-                // every key visible to every row: scale, maximum check and exponent in fused multiply-adds
-                float c0 = fmaxf(fmaxf(fmaf(sr[0][0], qs2[0], vm[0].y), fmaf(sr[0][2], qs2[0], vm[1].y)),
-                                 fmaxf(fmaf(sr[1][0], qs2[0], vm[2].y), fmaf(sr[1][2], qs2[0], vm[3].y)));
-                float c1 = fmaxf(fmaxf(fmaf(sr[0][1], qs2[1], vm[0].y), fmaf(sr[0][3], qs2[1], vm[1].y)),
-                                 fmaxf(fmaf(sr[1][1], qs2[1], vm[2].y), fmaf(sr[1][3], qs2[1], vm[3].y)));
-                if (__any_sync(0xffffffffu, c0 > M[0] + MAX_SLACK || c1 > M[1] + MAX_SLACK)) {
-#pragma unroll
-                    for (int o = 4; o < 32; o <<= 1) {
-                        c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, o));
-                        c1 = fmaxf(c1, __shfl_xor_sync(0xffffffffu, c1, o));
-                    }
-                    const float n0 = fmaxf(M[0], c0), n1 = fmaxf(M[1], c1);
-                    const float al0 = fast_exp2(M[0] - n0), al1 = fast_exp2(M[1] - n1);
-                    M[0] = n0;
-                    M[1] = n1;
-                    lsum[0] *= al0;
-                    lsum[1] *= al1;
-#pragma unroll
-                    for (int mt = 0; mt < STEPS; ++mt) {
-                        oacc[mt][0] *= al0;
-                        oacc[mt][1] *= al1;
-                        oacc[mt][2] *= al0;
-                        oacc[mt][3] *= al1;
-                    }
-                }
-                const float nm0 = -M[0], nm1 = -M[1];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float pa = fast_exp2(fmaf(sr[k >> 1][2 * (k & 1)], qs2[0], nm0));
-                    const float pc = fast_exp2(fmaf(sr[k >> 1][2 * (k & 1) + 1], qs2[1], nm1));
-                    lsum[0] += pa;
-                    lsum[1] += pc;
-                    pb[k] = movmatrix_trans(pack_f16x2(pa * vm[k].x, pc * vm[k].x));
-                }
-            } else {
-                // masks, soft-capping, ALiBi: the two query rows whose scores this lane holds (columns 2c, 2c + 1)
-                float s2[8];  // s2[2 k + e]
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const uint32_t r = pack * PACK + 2 * c + e;
-                    int r_lo = 0, r_hi = 0, r_pos = 0;
-                    float slope = 0.0f;
-                    if (r < R) {
-                        row_range(r, r_lo, r_hi, r_pos);
-                        if (p.alibi) slope = p.alibi[(size_t)seg.b * p.alibi_bs + hk * G + (p.lq == 1 ? r : r % G)];
-                    }
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const int j = key0 + g + 8 * k;
-                        float sx = sr[k >> 1][2 * (k & 1) + e] * qs[e];
-                        if (p.softcap > 0.0f) sx = p.softcap * tanhf(sx / p.softcap);
-                        if (slope != 0.0f) sx -= slope * fabsf((float)(r_pos - j));
-                        s2[2 * k + e] = (j >= r_lo && j < r_hi) ? sx * LOG2E : -INFINITY;
-                    }
-                }
-                float c0 = fmaxf(fmaxf(s2[0] + vm[0].y, s2[2] + vm[1].y), fmaxf(s2[4] + vm[2].y, s2[6] + vm[3].y));
-                float c1 = fmaxf(fmaxf(s2[1] + vm[0].y, s2[3] + vm[1].y), fmaxf(s2[5] + vm[2].y, s2[7] + vm[3].y));
-                if (__any_sync(0xffffffffu, c0 > M[0] + MAX_SLACK || c1 > M[1] + MAX_SLACK)) {
-#pragma unroll
-                    for (int o = 4; o < 32; o <<= 1) {
-                        c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, o));
-                        c1 = fmaxf(c1, __shfl_xor_sync(0xffffffffu, c1, o));
-                    }
-                    const float n0 = fmaxf(M[0], c0), n1 = fmaxf(M[1], c1);
-                    const float al0 = fast_exp2(M[0] - n0), al1 = fast_exp2(M[1] - n1);
-                    M[0] = n0;
-                    M[1] = n1;
-                    lsum[0] *= al0;
-                    lsum[1] *= al1;
-#pragma unroll
-                    for (int mt = 0; mt < STEPS; ++mt) {
-                        oacc[mt][0] *= al0;
-                        oacc[mt][1] *= al1;
-                        oacc[mt][2] *= al0;
-                        oacc[mt][3] *= al1;
-                    }
-                }
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float pa = fast_exp2(s2[2 * k] - M[0]), pc = fast_exp2(s2[2 * k + 1] - M[1]);
-                    lsum[0] += pa;
-                    lsum[1] += pc;
-                    pb[k] = movmatrix_trans(pack_f16x2(pa * vm[k].x, pc * vm[k].x));
-                }
-            }
-            // ---- O^T += V^T P^T
-#if (B200_ABL & 2)
-            oacc[0][0] += u2f(pb[0] ^ pb[1] ^ pb[2] ^ pb[3]);
-#else
-            v_accum(st_s + vt_off, vsc_c, pb[0], pb[1]);
-            v_accum(st_s + vt_off + 16 * vrb, vsc_c + 32, pb[2], pb[3]);
-#endif
-            // the stage was read (and possibly patched) through the generic proxy: order that before the
-            // bulk copy of the next tile into it
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (i_left > 0) copy_tile(c_st, c_bar);
-            c_st += stage_bytes;
-            c_bar += 8;
-            if (++c_stage == NS) {
-                c_stage = 0;
-                c_st = wstage_s;
-                c_bar = wbar_s;
-                par ^= 1u;
-            }
-        }
-        }  // !wait_failed
-
-        // ================================================================ this warp's partial result of the column
-        B200_T(4);
+    // The end of a segment: oacc holds the unnormalized output rows 2c, 2c + 1 (dims [g HD/8, (g + 1) HD/8)) of the
+    // segment's keys, M / lsum their running maxima (log2 domain) and normalizers, summed over the warp. A column
+    // that this worker covers alone is stored straight from the registers; otherwise the normalized partial result
+    // and its log-sum-exp go to the workspace and the worker counts itself on the column's arrival counter: the last
+    // to arrive merges the column. Without arrival counters the combine grid merges. `stage`: PACK x HD floats of
+    // shared memory of this warp (touched only when the values are rotated).
+    template <int HD>
+    __device__ __forceinline__ void finish_segment(const Segment &seg, const float (&oacc)[HD / 16][4], const float (&M)[2], const float (&lsum)[2],
+                                                   float *stage) {
+        constexpr int STEPS = HD / 16;
+        const int g = lane >> 2, c = lane & 3;
+        const uint32_t R = p.rows_per_kv, pack = seg.y % p.packs;
         prev_done();
-#pragma unroll
-        for (int o = 4; o < 32; o <<= 1) {
-            lsum[0] += __shfl_xor_sync(0xffffffffu, lsum[0], o);
-            lsum[1] += __shfl_xor_sync(0xffffffffu, lsum[1], o);
-        }
         const uint32_t colidx = seg.b * ny + seg.y;
         const float inv0 = lsum[0] > 0.0f ? 1.0f / lsum[0] : 0.0f, inv1 = lsum[1] > 0.0f ? 1.0f / lsum[1] : 0.0f;
         const uint32_t rr0 = 2 * c, rr1 = 2 * c + 1;
@@ -1399,10 +1173,10 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
         // the column's segments are the workers first .. last (consecutive, every one of them owns a tile of it)
         const uint64_t x_col = seg.x - seg.t0;  // cost position of the column's first tile
         const uint32_t first = seg.t0 == 0 ? wid : owner_of(x_col, total, nw);
-        const uint32_t last = seg.t1 == (uint32_t)col.tiles ? wid : owner_of(x_col + col.tiles - 1, total, nw);
+        const uint32_t last = seg.t1 == (uint32_t)seg.col.tiles ? wid : owner_of(x_col + seg.col.tiles - 1, total, nw);
         const uint32_t nseg = last - first + 1;
         if (p.ctr && nseg == 1 && p.v.rot != B200_ROT_HADAMARD) {
-            // the whole column in this worker's registers: rows 2c, 2c + 1, dims [g HD/8, (g + 1) HD/8)
+            // the whole column in this worker's registers
             float o0[HD / 8], o1[HD / 8];
 #pragma unroll
             for (int mt = 0; mt < STEPS; ++mt) {
@@ -1419,44 +1193,646 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                 for (uint32_t pr = 0; pr < p.world; ++pr) store_row_piece<HD / 8>(p.peer_bufs[pr], g_base + grow * HD + g * (HD / 8), o1, p.out_dtype);
             }
             column_done();
-        } else {
-            const size_t slot = (size_t)wid + colidx;
-            float *po0 = p.part_o + (slot * prow + rr0) * HD + g * (HD / 8);
-            float *po1 = p.part_o + (slot * prow + rr1) * HD + g * (HD / 8);
+            return;
+        }
+        const size_t slot = (size_t)wid + colidx;
+        float *po0 = p.part_o + (slot * prow + rr0) * HD + g * (HD / 8);
+        float *po1 = p.part_o + (slot * prow + rr1) * HD + g * (HD / 8);
 #pragma unroll
-            for (int mt = 0; mt < STEPS; ++mt) {
-                if (w0) *reinterpret_cast<float2 *>(po0 + 2 * mt) = make_float2(oacc[mt][0] * inv0, oacc[mt][2] * inv0);
-                if (w1) *reinterpret_cast<float2 *>(po1 + 2 * mt) = make_float2(oacc[mt][1] * inv1, oacc[mt][3] * inv1);
-            }
-            if (g == 0) {
-                if (w0) p.part_lse[slot * prow + rr0] = lsum[0] > 0.0f ? M[0] * LN2 + logf(lsum[0]) : -INFINITY;
-                if (w1) p.part_lse[slot * prow + rr1] = lsum[1] > 0.0f ? M[1] * LN2 + logf(lsum[1]) : -INFINITY;
-            }
-            if (p.ctr) {
-                // count this segment; the last of the column's workers to get here merges them all
+        for (int mt = 0; mt < STEPS; ++mt) {
+            if (w0) *reinterpret_cast<float2 *>(po0 + 2 * mt) = make_float2(oacc[mt][0] * inv0, oacc[mt][2] * inv0);
+            if (w1) *reinterpret_cast<float2 *>(po1 + 2 * mt) = make_float2(oacc[mt][1] * inv1, oacc[mt][3] * inv1);
+        }
+        if (g == 0) {
+            if (w0) p.part_lse[slot * prow + rr0] = lsum[0] > 0.0f ? M[0] * LN2 + logf(lsum[0]) : -INFINITY;
+            if (w1) p.part_lse[slot * prow + rr1] = lsum[1] > 0.0f ? M[1] * LN2 + logf(lsum[1]) : -INFINITY;
+        }
+        if (p.ctr) {
+            // count this segment; the last of the column's workers to get here merges them all
+            __threadfence();
+            __syncwarp();
+            uint32_t merge = 0;
+            if (lane == 0) merge = atomicInc(p.ctr + colidx, nseg - 1u) == nseg - 1u ? 1u : 0u;
+            merge = __shfl_sync(0xffffffffu, merge, 0);
+            if (merge) {
                 __threadfence();
-                __syncwarp();
-                uint32_t merge = 0;
-                if (lane == 0) merge = atomicInc(p.ctr + colidx, nseg - 1u) == nseg - 1u ? 1u : 0u;
-                merge = __shfl_sync(0xffffffffu, merge, 0);
-                if (merge) {
-                    __threadfence();
-                    const size_t slot0 = (size_t)first + colidx;
-                    if (prow <= 4) merge_column<HD, 8>(p, seg.b, seg.y, slot0, (int)nseg, prow, g_base, qstage, lane);
-                    else merge_column<HD, 4>(p, seg.b, seg.y, slot0, (int)nseg, prow, g_base, qstage, lane);
-                    column_done();
+                const size_t slot0 = (size_t)first + colidx;
+                merge_column<HD>(p, seg.b, seg.y, slot0, (int)nseg, prow, g_base, stage, lane);
+                column_done();
+            }
+        } else if (seg.t0 == 0 && lane == 0) {
+            // the worker that owns the first tile of a column publishes where its segments are (for the combine grid)
+            p.meta[2 * (size_t)colidx] = (int32_t)(wid + colidx);
+            p.meta[2 * (size_t)colidx + 1] = (int32_t)nseg;
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// The copy side of a worker: bulk copies of its tiles into the stages of its ring
+// ---------------------------------------------------------------------------------------------
+// Runs up to NS tiles ahead of the compute side through the same list of segments; tile t of the worker's list lives
+// in stage t mod NS, so the copy issued after a tile is consumed goes into the stage just read. Rows are 72-140
+// bytes: a copy starts at the 16-byte boundary below the tile's first row and ends at the one above its last.
+struct CopySide {
+    Segment iseg;
+    int left;        // tiles still to copy in the copy side's segment
+    int simple;      // of those, whole tiles that do not end their column: constant copy sizes, no tail handling
+    bool more;       // the copy side has segments left
+    uintptr_t k, v;  // 16-byte aligned global addresses of the next tile's copies
+    uint32_t koff, voff;  // offset of the tile's first row inside its copy
+    uint32_t kb, vb;      // bytes of a whole tile's copies
+    int key;              // first key of the next tile
+
+    // per-segment constants
+    __device__ __forceinline__ void enter(const DecodeParams &p, uint32_t krb, uint32_t vrb) {
+        left = (int)(iseg.t1 - iseg.t0);
+        simple = left - (iseg.t1 == (uint32_t)iseg.col.tiles ? 1 : 0);
+        const uint32_t hk = iseg.y / p.packs;
+        key = iseg.col.lo + (int)iseg.t0 * WK;
+        const uintptr_t ka = reinterpret_cast<uintptr_t>(p.k_rows + (size_t)iseg.b * p.k_sb + (size_t)hk * p.k_sh) + (uintptr_t)(uint32_t)key * krb;
+        const uintptr_t va = reinterpret_cast<uintptr_t>(p.v_rows + (size_t)iseg.b * p.v_sb + (size_t)hk * p.v_sh) + (uintptr_t)(uint32_t)key * vrb;
+        koff = (uint32_t)(ka & 15u);
+        voff = (uint32_t)(va & 15u);
+        k = ka - koff;
+        v = va - voff;
+        kb = (koff + (uint32_t)WK * krb + 15u) & ~15u;
+        vb = (voff + (uint32_t)WK * vrb + 15u) & ~15u;
+    }
+
+    __device__ __forceinline__ void start(const DecodeParams &p, const Segment &seg, uint32_t krb, uint32_t vrb) {
+        iseg = seg;
+        more = true;
+        enter(p, krb, vrb);
+    }
+
+    // copies the next tile into stage `st` with barrier `bar` (the caller checked left > 0) and moves on
+    __device__ __forceinline__ void tile(Worker &w, uint32_t st, uint32_t bar, uint32_t krb, uint32_t vrb, uint32_t k_stage_bytes, uint64_t x_end) {
+        const DecodeParams &p = w.p;
+        const int lane = w.lane;
+        // rows that the stream's previous kernel may still be writing are not copied before it is done
+        if (!w.waited && key + min(WK, iseg.col.hi - key) > iseg.col.lk - (int)p.fresh_rows) w.prev_done();
+        if (simple > 0) {
+            --simple;
+            if (lane == 0) {
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kb + vb) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(st), "l"(k),
+                             "r"(kb), "r"(bar)
+                             : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(st + k_stage_bytes),
+                             "l"(v), "r"(vb), "r"(bar)
+                             : "memory");
+            }
+        } else {
+            // the last tile of its column
+            const int nkeys = min(WK, iseg.col.hi - key);
+            // Rows below lk are readable, and so is the row after a tile when the cache has spare rows
+            // (rows_cap): the 16-byte round up of a copy may then run into the next row. Otherwise the
+            // last tile of a sequence copies the round down and fetches the few remaining words with
+            // plain loads.
+            const bool tail = key + nkeys >= iseg.col.lk && key + nkeys >= (int)p.rows_cap;
+            uint32_t kbt = (koff + (uint32_t)nkeys * krb + 15u) & ~15u, vbt = (voff + (uint32_t)nkeys * vrb + 15u) & ~15u;
+            if (tail) {
+                const uint32_t ke = koff + (uint32_t)nkeys * krb, ve = voff + (uint32_t)nkeys * vrb;  // ends, from the copy start
+                kbt = ke & ~15u;
+                vbt = ve & ~15u;
+                if (lane < 4) {
+                    const uint32_t o = kbt + 4u * lane;
+                    if (o >= koff && o < ke) sts32(st + o, *reinterpret_cast<const uint32_t *>(k + o));
+                } else if (lane < 8) {
+                    const uint32_t o = vbt + 4u * (lane - 4);
+                    if (o >= voff && o < ve) sts32(st + k_stage_bytes + o, *reinterpret_cast<const uint32_t *>(v + o));
                 }
-            } else if (seg.t0 == 0 && lane == 0) {
-                // the worker that owns the first tile of a column publishes where its segments are (for the combine grid)
-                p.meta[2 * (size_t)colidx] = (int32_t)(wid + colidx);
-                p.meta[2 * (size_t)colidx + 1] = (int32_t)nseg;
+                __syncwarp();
+            }
+            if (lane == 0) {
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kbt + vbt) : "memory");
+                if (kbt)
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(st), "l"(k),
+                                 "r"(kbt), "r"(bar)
+                                 : "memory");
+                if (vbt)
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                     st + k_stage_bytes),
+                                 "l"(v), "r"(vbt), "r"(bar)
+                                 : "memory");
+            }
+        }
+        // WK rows are a multiple of 16 bytes: the next tile keeps its offset inside its copy
+        k += (uintptr_t)WK * krb;
+        v += (uintptr_t)WK * vrb;
+        key += WK;
+        if (--left == 0 && more) {
+            more = next_segment(iseg, p, w.ny, x_end);
+            if (more) enter(p, krb, vrb);
+        }
+    }
+
+    __device__ __forceinline__ void stop() {
+        left = 0;
+        more = false;
+    }
+};
+
+// Bounded wait for the phase of parity `par` of the mbarrier at `bar`: false when it did not complete in time
+__device__ __forceinline__ bool stage_wait(uint32_t bar, uint32_t par) {
+    uint32_t ok = 0;
+    for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin)
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok)
+                     : "r"(bar), "r"(par)
+                     : "memory");
+    return ok != 0;
+}
+
+// Visible keys of row r of a column's rows (ordered by token), bottom-right aligned masks
+__device__ __forceinline__ void row_range(const DecodeParams &p, const Column &col, uint32_t r, int &lo, int &hi, int &pos) {
+    const long long i = p.lq == 1 ? 0 : r / p.group;
+    const long long ps = i + (long long)col.lk - (long long)p.lq;
+    long long l = p.wl >= 0 ? max(ps - p.wl, 0ll) : 0ll;
+    long long h = p.wr >= 0 ? min(ps + p.wr + 1, (long long)col.lk) : (long long)col.lk;
+    l = min(l, (long long)col.lk);
+    h = max(h, l);
+    lo = (int)l;
+    hi = (int)h;
+    pos = (int)max(min(ps, 2147483647ll), -2147483647ll);
+}
+
+// Scores of a tile -> weights: vm from the tile's per-key scalars, plain or masked softmax. Returns whether the
+// running maxima moved (al then holds the factors for what was accumulated before).
+struct SegMask {
+    int LOmax, HImin;  // every key in [LOmax, HImin) is visible to every row of the pack
+    bool plain;        // no soft-capping, no ALiBi
+};
+
+__device__ __forceinline__ bool tile_softmax(const DecodeParams &p, const Segment &seg, const SegMask &sm, int key0, int nkeys, uint32_t vmeta_g,
+                                             const float (&sr)[2][4], const float (&qs)[2], const float (&qs2)[2], float (&M)[2], float (&lsum)[2],
+                                             uint32_t (&pb)[4], float (&al)[2], int lane) {
+    const int g = lane >> 2, c = lane & 3;
+    float2 vm[4];  // (sigma, log2 sigma) of the keys g, g + 8, g + 16, g + 24
+#pragma unroll
+    for (int k = 0; k < 4; ++k) vm[k] = lds64f(vmeta_g + k * 64);
+    if (sm.plain && nkeys == WK && key0 >= sm.LOmax && key0 + WK <= sm.HImin) return softmax_plain(sr, vm, qs2, M, lsum, pb, al);
+    // masks, soft-capping, ALiBi: the two query rows whose scores this lane holds (columns 2c, 2c + 1)
+    const uint32_t hk = seg.y / p.packs, pack = seg.y % p.packs, G = p.group;
+    RowMask rm;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const uint32_t r = pack * PACK + 2 * c + e;
+        rm.lo[e] = rm.hi[e] = rm.pos[e] = 0;
+        rm.slope[e] = 0.0f;
+        if (r < p.rows_per_kv) {
+            row_range(p, seg.col, r, rm.lo[e], rm.hi[e], rm.pos[e]);
+            if (p.alibi) rm.slope[e] = p.alibi[(size_t)seg.b * p.alibi_bs + hk * G + (p.lq == 1 ? r : r % G)];
+        }
+    }
+    return softmax_masked(sr, vm, qs, p.softcap, key0 + g, rm, M, lsum, pb, al);
+}
+
+__device__ __forceinline__ SegMask segment_mask(const DecodeParams &p, const Segment &seg) {
+    // rows are ordered by token: the last row of the pack has the highest lower bound, the first the lowest upper bound
+    SegMask sm;
+    const uint32_t pack = seg.y % p.packs;
+    int lo, hi, pos;
+    row_range(p, seg.col, min(pack * PACK + PACK, p.rows_per_kv) - 1, lo, hi, pos);
+    sm.LOmax = lo;
+    row_range(p, seg.col, pack * PACK, lo, hi, pos);
+    sm.HImin = hi;
+    sm.plain = p.softcap <= 0.0f && p.alibi == nullptr;
+    return sm;
+}
+
+// rows past the end of a column's last tile hold stale bytes: cleared so that masked keys decode to finite values
+__device__ __forceinline__ void clear_stale_rows(uint32_t kt, uint32_t vt, int nkeys, uint32_t krb, uint32_t vrb, int lane) {
+    for (uint32_t w = nkeys * (krb >> 2) + lane; w < WK * (krb >> 2); w += 32) sts32(kt + 4 * w, 0u);
+    for (uint32_t w = nkeys * (vrb >> 2) + lane; w < WK * (vrb >> 2); w += 32) sts32(vt + 4 * w, 0u);
+    __syncwarp();
+}
+
+// one time set up of a block: codebook tables of the TurboQuant formats in shared memory
+template <int KM, int VM>
+__device__ __forceinline__ void load_codebooks(const DecodeParams &p, uint32_t lut_k, uint32_t lut_v, uint32_t plane_k, int tid, int nthreads) {
+    if constexpr (KM == B200_TURBO_MSE)
+        for (int i = tid; i < 256; i += nthreads) sts32(lut_k + 4 * i, pack_f16x2(p.k.tab[i & 15], p.k.tab[i >> 4]));
+    if constexpr (VM == B200_TURBO_MSE)
+        for (int i = tid; i < 256; i += nthreads) sts32(lut_v + 4 * i, pack_f16x2(p.v.tab[i & 15], p.v.tab[i >> 4]));
+    if (tid < 16 && ((tid < 8) ? KM == B200_TURBO_MSE : VM == B200_TURBO_MSE)) {
+        // byte planes of the codebook: words 0..3 low bytes, 4..7 high bytes
+        const float *tab = tid < 8 ? p.k.tab : p.v.tab;
+        const int w = tid & 7, sh = w < 4 ? 0 : 8;
+        uint32_t v = 0;
+        for (int j = 0; j < 4; ++j) v |= ((pack_f16x2(tab[4 * (w & 3) + j], 0.0f) >> sh) & 0xffu) << (8 * j);
+        sts32(plane_k + 4 * tid, v);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Kernel 1: every warp a worker
+// ---------------------------------------------------------------------------------------------
+template <int KM, int VM, int HD, bool NAT>
+__global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_kernel(const DecodeParams p) {
+    constexpr int STEPS = HD / 16;          // k-steps of K Q^T == m-tiles of the output
+    constexpr bool K4 = fmt_is4(KM), V4 = fmt_is4(VM);
+    constexpr bool KMX = fmt_is_mx(KM);     // block-wise accumulation, contraction order A
+    constexpr int KMW = kmeta_words(KM, HD);
+    constexpr int META = meta_bytes(KM, VM, HD);
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);  // [DW][NS_MAX]
+    const int NS = (int)p.ns;
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t lut_k = sbase + 128, lut_v = lut_k + 1024, plane_k = lut_v + 1024, plane_v = plane_k + 32;
+    // row strides and stage sizes: compile-time when the rows are packed back to back (NAT)
+    const uint32_t krb = NAT ? (uint32_t)nat_row_bytes(KM, HD) : (uint32_t)p.k_ss * 4u;
+    const uint32_t vrb = NAT ? (uint32_t)nat_row_bytes(VM, HD) : (uint32_t)p.v_ss * 4u;
+    const uint32_t k_stage_bytes = NAT ? stage_part_bytes((uint32_t)nat_row_bytes(KM, HD)) : p.k_stage_bytes;
+    const uint32_t v_stage_bytes = NAT ? stage_part_bytes((uint32_t)nat_row_bytes(VM, HD)) : p.v_stage_bytes;
+    const uint32_t stage_bytes = k_stage_bytes + v_stage_bytes;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+    const uint32_t ny = p.hkv * p.packs;
+    const uint32_t nw_grid = gridDim.x * DW, wid = blockIdx.x * DW + warp;
+
+    // ------------------------------------------------------------------ one time set up (the only block barrier)
+    if (tid == 0) {
+        for (int i = 0; i < DW * NS_MAX; ++i) mbar_init(&bars[i], 1);
+        mbar_fence_init();
+    }
+    load_codebooks<KM, VM>(p, lut_k, lut_v, plane_k, tid, DW * 32);
+    __syncthreads();
+    // the next kernel of the stream may be scheduled from here on (a combine grid, or the next attention launched as
+    // a programmatic dependent); it waits for this grid's completion itself before it touches memory
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const Share sh = worker_share(p, ny, wid, nw_grid, lane);
+    Worker wk(p, lane, wid, nw_grid, ny, sh);
+    if (!p.prefetch) wk.prev_done();
+    if (!sh.has_work) {
+        wk.zero_columns<HD>(false);
+        return;
+    }
+
+    const uint32_t meta_s = sbase + FIXED_SMEM + warp * META;    // [WK][KMW] f32
+    const uint32_t vmeta_s = meta_s + WK * KMW * 4;              // [WK] (sigma, log2 sigma)
+    const uint32_t vsc_s = vmeta_s + WK * 8;                     // [NBV][WK] f16
+    float *qstage = reinterpret_cast<float *>(smem + FIXED_SMEM + DW * META) + (size_t)warp * PACK * HD;  // only with a rotated cache
+    const uint32_t wstage_s = sbase + FIXED_SMEM + DW * META + p.qstage_bytes + (uint32_t)warp * NS * stage_bytes;
+    const uint32_t wbar_s = smem_u32(bars + warp * NS_MAX);
+    bool wait_failed = false;
+
+    // Filling the ring. With the caller's word that the inputs are final (prefetch) all stages are asked for right away.
+    // Otherwise the first tile alone, and the other stages once the first query rows are loaded: with every worker of
+    // the grid asking for all its stages at once, the first tiles would arrive behind 26 MB of later ones.
+    CopySide cs;
+    cs.start(p, sh.seg, krb, vrb);
+    int primed = 0;
+    auto prime = [&](int upto) {
+        for (; primed < upto && cs.left > 0; ++primed)
+            cs.tile(wk, wstage_s + (uint32_t)primed * stage_bytes, wbar_s + 8u * (uint32_t)primed, krb, vrb, k_stage_bytes, sh.x_end);
+    };
+    prime(p.prefetch ? NS : 1);
+
+    // ------------------------------------------------------------------ the compute side
+    // lane offsets inside a tile: K rows g (and g + 8), V rows 2c (and 2c + 1, 2c + 8, 2c + 9)
+    const uint32_t k_lane = g * krb + (KMX ? (K4 ? 4u * c : 8u * c) : (K4 ? c * (HD / 8) : c * (HD / 4)));
+    const uint32_t v_lane = 2 * c * vrb + (V4 ? g * (HD / 16) : g * (HD / 8));
+    const uint32_t mrow_g = meta_s + g * KMW * 4, vmeta_g = vmeta_s + g * 8, vsc_c = vsc_s + 4 * c;
+    uint32_t c_st = wstage_s, c_bar = wbar_s;
+    int c_stage = 0;
+    uint32_t par = 0;  // parity to wait for on the current stage: flips every time the ring wraps
+
+    uint32_t qb0[STEPS], qb1[STEPS];
+    float qs[2], qs2[2];
+    float oacc[STEPS][4];
+
+    Segment seg = sh.seg;
+    bool more = true;
+    while (more) {
+        // ================================================================ segment set up
+        const uint32_t hk = seg.y / p.packs, pack = seg.y % p.packs;
+        const Column &col = seg.col;
+        const SegMask sm = segment_mask(p, seg);
+        // running maxima (log2 domain, value scale folded in) and partial normalizers of rows 2c, 2c + 1
+        float M[2] = {-1e30f, -1e30f}, lsum[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int mt = 0; mt < STEPS; ++mt) oacc[mt][0] = oacc[mt][1] = oacc[mt][2] = oacc[mt][3] = 0.0f;
+
+        if (!wait_failed) {
+            load_query<KM, HD>(p, seg.b, hk, pack, qstage, lane, qb0, qb1, qs, qs2);
+            // the other stages of the ring (first segment only)
+            prime(NS);
+
+            // ============================================================ the tiles of the segment
+            const int n_t = (int)(seg.t1 - seg.t0);
+            int key0 = col.lo + (int)seg.t0 * WK;
+            const uint32_t koff = (uint32_t)((reinterpret_cast<uintptr_t>(p.k_rows + (size_t)seg.b * p.k_sb + (size_t)hk * p.k_sh) + (uintptr_t)(uint32_t)key0 * krb) & 15u);
+            const uint32_t voff = (uint32_t)((reinterpret_cast<uintptr_t>(p.v_rows + (size_t)seg.b * p.v_sb + (size_t)hk * p.v_sh) + (uintptr_t)(uint32_t)key0 * vrb) & 15u);
+            const uint32_t kt_off = koff + k_lane, vt_off = k_stage_bytes + voff + v_lane;
+            const uint32_t kr_off = koff + lane * krb, vr_off = k_stage_bytes + voff + lane * vrb;
+            for (int n = 0; n < n_t; ++n, key0 += WK) {
+                if (!stage_wait(c_bar, par)) {
+                    // the copy never landed: give up on the keys (the outputs are void, the status says so), stop
+                    // copying, but keep counting this worker's segments so that no column waits for it
+                    wait_failed = true;
+                    cs.stop();
+                    break;
+                }
+                const uint32_t st_s = c_st;
+                const int nkeys = min(WK, col.hi - key0);
+                if (nkeys < WK) clear_stale_rows(st_s + koff, st_s + k_stage_bytes + voff, nkeys, krb, vrb, lane);
+                // ---- per-key scalars of the tile, lane = key
+                tile_meta<KM, VM, HD>(st_s + kr_off, st_s + vr_off, meta_s, vmeta_s, vsc_s, lane);
+                // ---- scores of the 32 keys: sr[u][2 k + e] = key 16 u + g + 8 k, row 2c + e
+                float sr[2][4];
+                k_scores16<KM, HD>(st_s + kt_off, krb, mrow_g, qb0, qb1, lut_k, plane_k, c, sr[0]);
+                k_scores16<KM, HD>(st_s + kt_off + 16 * krb, krb, mrow_g + 16 * KMW * 4, qb0, qb1, lut_k, plane_k, c, sr[1]);
+                // ---- online softmax
+                uint32_t pb[4];
+                float al[2];
+                if (tile_softmax(p, seg, sm, key0, nkeys, vmeta_g, sr, qs, qs2, M, lsum, pb, al, lane)) {
+#pragma unroll
+                    for (int mt = 0; mt < STEPS; ++mt) {
+                        oacc[mt][0] *= al[0];
+                        oacc[mt][1] *= al[1];
+                        oacc[mt][2] *= al[0];
+                        oacc[mt][3] *= al[1];
+                    }
+                }
+                // ---- O^T += V^T P^T
+                v_accum16<VM, HD>(st_s + vt_off, vrb, vsc_c, pb[0], pb[1], oacc, lut_v, plane_v, g);
+                v_accum16<VM, HD>(st_s + vt_off + 16 * vrb, vrb, vsc_c + 32, pb[2], pb[3], oacc, lut_v, plane_v, g);
+                // the stage was read (and possibly patched) through the generic proxy: order that before the
+                // bulk copy of the next tile into it
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (cs.left > 0) cs.tile(wk, c_st, c_bar, krb, vrb, k_stage_bytes, sh.x_end);
+                c_st += stage_bytes;
+                c_bar += 8;
+                if (++c_stage == NS) {
+                    c_stage = 0;
+                    c_st = wstage_s;
+                    c_bar = wbar_s;
+                    par ^= 1u;
+                }
             }
         }
 
-        more = next_segment(seg, p, ny, x_end);
+        // ================================================================ this warp's partial result of the column
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            lsum[0] += __shfl_xor_sync(0xffffffffu, lsum[0], o);
+            lsum[1] += __shfl_xor_sync(0xffffffffu, lsum[1], o);
+        }
+        wk.finish_segment<HD>(seg, oacc, M, lsum, qstage);
+        more = next_segment(seg, p, ny, sh.x_end);
     }
-    zero_columns();
-    B200_T(5);
+    wk.zero_columns<HD>(true);
+    if (wait_failed) {
+        if (p.status) atomicExch(p.status, 1);
+        if (p.lib_status) atomicExch(p.lib_status, 1);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Kernel 2: a worker is a pair of warps (codebook formats, whose table look-ups bind the kernel to instruction issue)
+// ---------------------------------------------------------------------------------------------
+// The keys' warp computes the scores and the softmax of a tile and hands the weights (as B fragments), the value
+// block scales and, when the running maxima moved, the rescale factors to the values' warp through a two-slot queue
+// in shared memory; the values' warp accumulates the outputs, releases the stage and issues the copy of the tile
+// that takes its place. Each warp holds half the state of a whole worker (query fragments and softmax state on one
+// side, output accumulators and the copy side on the other), so twice as many warps fit on an SM at 128 registers
+// each, and a pair works on two tiles at once: more instructions in flight for a kernel that is bound by their
+// issue, with the same number of bytes in flight. The segment's last message carries the maxima and normalizers.
+// Which format pairs take this kernel: 4-bit rows of which at least one side is a codebook format. Measured on B200:
+// the table look-ups of the codebook formats gain 15 % from the split (TurboQuant-4 decode, 32768 keys per sequence),
+// the packed conversions of MXFP4 / NVFP4 gain nothing (the extra warps make up for the messages' cost, no more).
+__host__ __device__ constexpr bool pair_formats(int km, int vm) {
+    return fmt_is4(km) && fmt_is4(vm) && (km == B200_TURBO_MSE || vm == B200_TURBO_MSE);
+}
+constexpr int PW = 4;        // pairs per block: warps 0..3 keys, 4..7 values
+constexpr int PQ = 2;        // slots of a pair's queue
+constexpr int PNS_MAX = 4;   // stages per pair
+constexpr int PAIR_FIXED = 256 + 2048 + 128;  // barriers, pair tables, byte-plane tables
+// one message: weights [lane][4] u32, rescale factors [lane][2] f32, their flag, f16 block scales of V [block][key]
+__host__ __device__ constexpr int pair_msg_bytes(int vm, int hd) { return 512 + 256 + 16 + vsc_blocks(vm, hd) * WK * 2; }
+// per pair: key scales and (sigma, log2 sigma) of a tile (the keys' warp's own), then the queue
+__host__ __device__ constexpr int pair_meta_bytes(int km, int vm, int hd) { return WK * kmeta_words(km, hd) * 4 + WK * 8 + PQ * pair_msg_bytes(vm, hd); }
+
+template <int KM, int VM, int HD, bool NAT>
+__global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const DecodeParams p) {
+    constexpr int STEPS = HD / 16;
+    constexpr bool K4 = fmt_is4(KM), V4 = fmt_is4(VM);
+    constexpr bool KMX = fmt_is_mx(KM);
+    constexpr int KMW = kmeta_words(KM, HD);
+    constexpr int MSG = pair_msg_bytes(VM, HD);
+    constexpr int PMETA = pair_meta_bytes(KM, VM, HD);
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);  // [PW][8]: stages full 0..3, messages full 4..5, messages free 6..7
+    const int NS = (int)p.ns;
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t lut_k = sbase + 256, lut_v = lut_k + 1024, plane_k = lut_v + 1024, plane_v = plane_k + 32;
+    const uint32_t krb = NAT ? (uint32_t)nat_row_bytes(KM, HD) : (uint32_t)p.k_ss * 4u;
+    const uint32_t vrb = NAT ? (uint32_t)nat_row_bytes(VM, HD) : (uint32_t)p.v_ss * 4u;
+    const uint32_t k_stage_bytes = NAT ? stage_part_bytes((uint32_t)nat_row_bytes(KM, HD)) : p.k_stage_bytes;
+    const uint32_t v_stage_bytes = NAT ? stage_part_bytes((uint32_t)nat_row_bytes(VM, HD)) : p.v_stage_bytes;
+    const uint32_t stage_bytes = k_stage_bytes + v_stage_bytes;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+    const int pair = warp & (PW - 1);
+    const bool keys_side = warp < PW;
+    const uint32_t ny = p.hkv * p.packs;
+    const uint32_t nw_grid = gridDim.x * PW, wid = blockIdx.x * PW + pair;
+
+    if (tid == 0) {
+        for (int i = 0; i < PW * 8; ++i) mbar_init(&bars[i], 1);
+        mbar_fence_init();
+    }
+    load_codebooks<KM, VM>(p, lut_k, lut_v, plane_k, tid, PW * 64);
+    __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    // both warps of a pair work out the pair's share
+    const Share sh = worker_share(p, ny, wid, nw_grid, lane);
+    Worker wk(p, lane, wid, nw_grid, ny, sh);
+    if (!p.prefetch) wk.prev_done();
+    if (!sh.has_work) {
+        if (!keys_side) wk.zero_columns<HD>(false);
+        return;
+    }
+
+    const uint32_t pmeta_s = sbase + PAIR_FIXED + pair * PMETA;
+    const uint32_t meta_s = pmeta_s;                       // [WK][KMW] f32
+    const uint32_t vmeta_s = meta_s + WK * KMW * 4;        // [WK] (sigma, log2 sigma)
+    const uint32_t queue_s = vmeta_s + WK * 8;             // [PQ] messages
+    // rotation staging: the keys' warp rotates the queries in its rows, the values' warp the outputs in its own
+    float *qstage = reinterpret_cast<float *>(smem + PAIR_FIXED + PW * PMETA) + (size_t)(keys_side ? pair : PW + pair) * PACK * HD;
+    const uint32_t wstage_s = sbase + PAIR_FIXED + PW * PMETA + p.qstage_bytes + (uint32_t)pair * NS * stage_bytes;
+    const uint32_t wbar_s = smem_u32(bars + pair * 8);     // stages
+    const uint32_t qfull_s = wbar_s + 32, qfree_s = wbar_s + 48;
+
+    uint32_t c_st = wstage_s, c_bar = wbar_s;
+    int c_stage = 0;
+    uint32_t par = 0;      // parity of the current stage's barrier
+    uint32_t msgs = 0;     // messages sent (keys' side) or taken (values' side) so far: slot = msgs % PQ
+    bool wait_failed = false;
+    Segment seg = sh.seg;
+    bool more = true;
+
+    if (keys_side) {
+        // ============================================================== the keys' warp
+        const uint32_t k_lane = g * krb + (KMX ? (K4 ? 4u * c : 8u * c) : (K4 ? c * (HD / 8) : c * (HD / 4)));
+        const uint32_t mrow_g = meta_s + g * KMW * 4, vmeta_g = vmeta_s + g * 8;
+        uint32_t qb0[STEPS], qb1[STEPS];
+        float qs[2], qs2[2];
+        // a free slot for message `msgs`: the values' warp has taken message msgs - PQ
+        auto slot_wait = [&]() -> bool {
+            if (msgs < (uint32_t)PQ) return true;
+            return stage_wait(qfree_s + 8u * (msgs % PQ), ((msgs / PQ) - 1u) & 1u);
+        };
+        auto slot_send = [&]() {
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qfull_s + 8u * (msgs % PQ)) : "memory");
+            ++msgs;
+        };
+        while (more && !wait_failed) {
+            const uint32_t hk = seg.y / p.packs, pack = seg.y % p.packs;
+            const Column &col = seg.col;
+            const SegMask sm = segment_mask(p, seg);
+            float M[2] = {-1e30f, -1e30f}, lsum[2] = {0.0f, 0.0f};
+            load_query<KM, HD>(p, seg.b, hk, pack, qstage, lane, qb0, qb1, qs, qs2);
+            const int n_t = (int)(seg.t1 - seg.t0);
+            int key0 = col.lo + (int)seg.t0 * WK;
+            const uint32_t koff = (uint32_t)((reinterpret_cast<uintptr_t>(p.k_rows + (size_t)seg.b * p.k_sb + (size_t)hk * p.k_sh) + (uintptr_t)(uint32_t)key0 * krb) & 15u);
+            const uint32_t voff = (uint32_t)((reinterpret_cast<uintptr_t>(p.v_rows + (size_t)seg.b * p.v_sb + (size_t)hk * p.v_sh) + (uintptr_t)(uint32_t)key0 * vrb) & 15u);
+            const uint32_t kt_off = koff + k_lane;
+            const uint32_t kr_off = koff + lane * krb, vr_off = k_stage_bytes + voff + lane * vrb;
+            for (int n = 0; n < n_t; ++n, key0 += WK) {
+                if (!stage_wait(c_bar, par) || !slot_wait()) {
+                    wait_failed = true;
+                    break;
+                }
+                const uint32_t st_s = c_st, msg_s = queue_s + (msgs % PQ) * MSG;
+                const int nkeys = min(WK, col.hi - key0);
+                if (nkeys < WK) clear_stale_rows(st_s + koff, st_s + k_stage_bytes + voff, nkeys, krb, vrb, lane);
+                tile_meta<KM, VM, HD>(st_s + kr_off, st_s + vr_off, meta_s, vmeta_s, msg_s + 784, lane);
+                float sr[2][4];
+                k_scores16<KM, HD>(st_s + kt_off, krb, mrow_g, qb0, qb1, lut_k, plane_k, c, sr[0]);
+                k_scores16<KM, HD>(st_s + kt_off + 16 * krb, krb, mrow_g + 16 * KMW * 4, qb0, qb1, lut_k, plane_k, c, sr[1]);
+                uint32_t pb[4];
+                float al[2];
+                const bool moved = tile_softmax(p, seg, sm, key0, nkeys, vmeta_g, sr, qs, qs2, M, lsum, pb, al, lane);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(msg_s + lane * 16), "r"(pb[0]), "r"(pb[1]), "r"(pb[2]), "r"(pb[3]) : "memory");
+                if (moved) asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(msg_s + 512 + lane * 8), "f"(al[0]), "f"(al[1]) : "memory");
+                if (lane == 0) sts32(msg_s + 768, moved ? 1u : 0u);
+                slot_send();
+                c_st += stage_bytes;
+                c_bar += 8;
+                if (++c_stage == NS) {
+                    c_stage = 0;
+                    c_st = wstage_s;
+                    c_bar = wbar_s;
+                    par ^= 1u;
+                }
+            }
+            if (wait_failed) break;
+            // the segment's last message: maxima and normalizers (summed over the warp) of the rows 2c, 2c + 1
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) {
+                lsum[0] += __shfl_xor_sync(0xffffffffu, lsum[0], o);
+                lsum[1] += __shfl_xor_sync(0xffffffffu, lsum[1], o);
+            }
+            if (!slot_wait()) {
+                wait_failed = true;
+                break;
+            }
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(queue_s + (msgs % PQ) * MSG + lane * 16), "f"(M[0]), "f"(M[1]), "f"(lsum[0]),
+                         "f"(lsum[1])
+                         : "memory");
+            slot_send();
+            more = next_segment(seg, p, ny, sh.x_end);
+        }
+    } else {
+        // ============================================================== the values' warp
+        const uint32_t v_lane = 2 * c * vrb + (V4 ? g * (HD / 16) : g * (HD / 8));
+        float oacc[STEPS][4];
+        CopySide cs;
+        cs.start(p, sh.seg, krb, vrb);
+        for (int i = 0; i < NS && cs.left > 0; ++i)
+            cs.tile(wk, wstage_s + (uint32_t)i * stage_bytes, wbar_s + 8u * (uint32_t)i, krb, vrb, k_stage_bytes, sh.x_end);
+        auto msg_wait = [&]() -> bool { return stage_wait(qfull_s + 8u * (msgs % PQ), (msgs / PQ) & 1u); };
+        auto msg_done = [&]() {
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(qfree_s + 8u * (msgs % PQ)) : "memory");
+            ++msgs;
+        };
+        while (more) {
+            const uint32_t hk = seg.y / p.packs;
+            const Column &col = seg.col;
+            float M[2] = {-1e30f, -1e30f}, lsum[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int mt = 0; mt < STEPS; ++mt) oacc[mt][0] = oacc[mt][1] = oacc[mt][2] = oacc[mt][3] = 0.0f;
+            if (!wait_failed) {
+                const int n_t = (int)(seg.t1 - seg.t0);
+                const int key0 = col.lo + (int)seg.t0 * WK;
+                const uint32_t voff = (uint32_t)((reinterpret_cast<uintptr_t>(p.v_rows + (size_t)seg.b * p.v_sb + (size_t)hk * p.v_sh) + (uintptr_t)(uint32_t)key0 * vrb) & 15u);
+                const uint32_t vt_off = k_stage_bytes + voff + v_lane;
+                for (int n = 0; n < n_t; ++n) {
+                    // the message implies the stage (the keys' warp waited for it); the wait on the stage's own barrier
+                    // makes the copied bytes visible to this warp too
+                    if (!msg_wait() || !stage_wait(c_bar, par)) {
+                        wait_failed = true;
+                        cs.stop();
+                        break;
+                    }
+                    const uint32_t st_s = c_st, msg_s = queue_s + (msgs % PQ) * MSG;
+                    if (lds32(msg_s + 768)) {
+                        const float2 al = lds64f(msg_s + 512 + lane * 8);
+#pragma unroll
+                        for (int mt = 0; mt < STEPS; ++mt) {
+                            oacc[mt][0] *= al.x;
+                            oacc[mt][1] *= al.y;
+                            oacc[mt][2] *= al.x;
+                            oacc[mt][3] *= al.y;
+                        }
+                    }
+                    uint32_t pb[4];
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(pb[0]), "=r"(pb[1]), "=r"(pb[2]), "=r"(pb[3]) : "r"(msg_s + lane * 16));
+                    const uint32_t vsc_c = msg_s + 784 + 4 * c;
+                    v_accum16<VM, HD>(st_s + vt_off, vrb, vsc_c, pb[0], pb[1], oacc, lut_v, plane_v, g);
+                    v_accum16<VM, HD>(st_s + vt_off + 16 * vrb, vrb, vsc_c + 32, pb[2], pb[3], oacc, lut_v, plane_v, g);
+                    // the stage was read through the generic proxy (by both warps: the keys' warp before it sent the
+                    // message): order that before the bulk copy of the next tile into it
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    msg_done();
+                    if (cs.left > 0) cs.tile(wk, c_st, c_bar, krb, vrb, k_stage_bytes, sh.x_end);
+                    c_st += stage_bytes;
+                    c_bar += 8;
+                    if (++c_stage == NS) {
+                        c_stage = 0;
+                        c_st = wstage_s;
+                        c_bar = wbar_s;
+                        par ^= 1u;
+                    }
+                }
+                if (!wait_failed) {
+                    if (msg_wait()) {
+                        const float4 ml = lds128f(queue_s + (msgs % PQ) * MSG + lane * 16);
+                        M[0] = ml.x; M[1] = ml.y; lsum[0] = ml.z; lsum[1] = ml.w;
+                        msg_done();
+                    } else {
+                        wait_failed = true;
+                        cs.stop();
+                    }
+                }
+            }
+            if (wait_failed) {
+                // void outputs (the status says so); the segment is still counted, so that no column waits for it
+                lsum[0] = lsum[1] = 0.0f;
+            }
+            wk.finish_segment<HD>(seg, oacc, M, lsum, qstage);
+            more = next_segment(seg, p, ny, sh.x_end);
+        }
+        wk.zero_columns<HD>(true);
+    }
     if (wait_failed) {
         if (p.status) atomicExch(p.status, 1);
         if (p.lib_status) atomicExch(p.lib_status, 1);

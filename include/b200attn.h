@@ -348,10 +348,18 @@ int b200_flash_attn(const B200FaArgs *args, b200_stream_t stream);
 int b200_fa_prefill_append(const B200FaArgs *fa, const B200KvAppendArgs *append, b200_stream_t stream);
 
 /* Health check: 1 when a bounded device-side wait of the attention kernels (an mbarrier that a copy or
- * a tensor core commit should have completed) has run out since the library was loaded, 0 otherwise,
- * -1 when the device cannot be read. Synchronizes the device. The reference has no counterpart: its
- * kernels hold no device-side waits (candle-core/kernels/flash_attn_impl.h uses block barriers only). */
+ * a tensor core commit should have completed, the flag of another rank in the gathered attention) has run out
+ * on the current device since the library was loaded or the flag was last cleared, 0 otherwise, -1 when the
+ * device cannot be read. Synchronizes the device. The flag is sticky: while it is set, the tensor-core prefill
+ * kernels return at once without writing their outputs (b200_flash_attn / b200_fa_prefill_append still return
+ * B200_OK: the launch itself succeeded), so a caller of those polls this after a step whose results matter. The
+ * reference has no counterpart: its kernels hold no device-side waits (candle-core/kernels/flash_attn_impl.h
+ * uses block barriers only). */
 int b200_device_wait_status(void);
+
+/* The same as a status code: B200_ERR_DEVICE_WAIT (with a message for b200_last_error) when the flag is set,
+ * B200_OK otherwise; clear != 0 also resets it, after which all kernels run normally again. */
+int b200_device_wait_check(int clear);
 
 #ifdef __cplusplus
 }

@@ -283,6 +283,20 @@ def row_group(hq, hkv):
     return lib().orc_row_group(hq, hkv)
 
 
+def cpu_decode_step(k_rows, v_rows, q, mode, bits, k_tab, v_tab, cache_dtype: str, scale: float):
+    """The reference's CPU path for one decode step of one sequence, all in one C call: k_rows / v_rows (hkv, L, words)
+    packed rows, q (hq, d) f32 -> (hq, d) f32. Dequantizes the cached rows to `cache_dtype`, then unfused attention."""
+    k_rows, v_rows, q = _c(k_rows, np.uint32), _c(v_rows, np.uint32), _c(q, np.float32)
+    hkv, L, _ = k_rows.shape
+    hq, d = q.shape
+    out = np.empty((hq, d), dtype=np.float32)
+    dt = {"f32": 0, "f16": 1, "bf16": 2}[cache_dtype]
+    rc = lib().orc_cpu_decode_step(_p(k_rows), _p(v_rows), C.c_size_t(L), hkv, hq, d, mode, bits, _p(_c(k_tab, np.float32)),
+                                   _p(_c(v_tab, np.float32)), dt, _p(q), C.c_float(scale), _p(out))
+    assert rc == 0
+    return out
+
+
 def num_threads():
     return lib().orc_num_threads()
 

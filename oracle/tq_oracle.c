@@ -660,6 +660,70 @@ void orc_unfused_attention(const float *q, const float *k, const float *v, const
         }
 }
 
+/* One decode step of the reference's CPU path over a compressed cache, for the timed CPU baseline: dequantize every
+ * cached row and cast it to the cache dtype (TurboKvCache::keys_values, candle-nn/src/turbo_quant.rs:947-966), then the
+ * unfused attention of the single query token (candle-nn/src/flash_attn.rs:930-1000: all scores, softmax over the whole
+ * key axis, p v). k_rows / v_rows: (hkv, L, row words) packed rows of one sequence, q: (hq, d) f32, out: (hq, d) f32.
+ * cache_dtype: 0 f32, 1 f16, 2 bf16. Scratch of 2 hkv L d floats is allocated inside (as the reference materializes K
+ * and V). Returns 0, or -1 for an unknown format / no memory. */
+static inline float round_cache(float x, int dt) {
+    if (dt == 1) return (float)(_Float16)x;
+    if (dt == 2) {
+        uint32_t u = f2u(x);
+        if ((u & 0x7fffffffu) > 0x7f800000u) return u2f(u | 0x00400000u);
+        u += 0x7fffu + ((u >> 16) & 1u);
+        return u2f(u & 0xffff0000u);
+    }
+    return x;
+}
+
+int orc_cpu_decode_step(const uint32_t *k_rows, const uint32_t *v_rows, size_t L, int hkv, int hq, int d, int mode, int bits,
+                        const float *k_tab, const float *v_tab, int cache_dtype, const float *q, float scale, float *out) {
+    int lay[5];
+    if (orc_row_layout(mode, bits, d, lay)) return -1;
+    const size_t rw = (size_t)lay[3], n = (size_t)hkv * L;
+    float *kd = malloc(sizeof(float) * n * d), *vd = malloc(sizeof(float) * n * d);
+    if (!kd || !vd) { free(kd); free(vd); return -1; }
+#pragma omp parallel for schedule(static)
+    for (size_t r = 0; r < n; ++r) {
+        const uint32_t *kr = k_rows + r * rw, *vr = v_rows + r * rw;
+        const float k0 = u2f(kr[lay[4]]), v0 = u2f(vr[lay[4]]);
+        for (int j = 0; j < d; ++j) {
+            kd[r * d + j] = round_cache(k0 * row_elem(kr, j, mode, lay[0], lay[1], k_tab), cache_dtype);
+            vd[r * d + j] = round_cache(v0 * row_elem(vr, j, mode, lay[0], lay[1], v_tab), cache_dtype);
+        }
+    }
+    const int group = hq / hkv;
+    int bad = 0;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int h = 0; h < hq; ++h) {
+        const float *kb = kd + (size_t)(h / group) * L * d, *vb = vd + (size_t)(h / group) * L * d, *qv = q + (size_t)h * d;
+        float *s = malloc(sizeof(float) * (L ? L : 1)), *o = out + (size_t)h * d;
+        if (!s) { bad = 1; continue; }
+        float m = -INFINITY;
+        for (size_t j = 0; j < L; ++j) {
+            float dot = 0.0f;  /* the order of this sum is the matmul library's in the reference: vector lanes here */
+#pragma omp simd reduction(+ : dot)
+            for (int t = 0; t < d; ++t) dot += qv[t] * kb[j * d + t];
+            s[j] = dot * scale;
+            if (s[j] > m) m = s[j];
+        }
+        float sum = 0.0f;
+        for (size_t j = 0; j < L; ++j) { s[j] = expf(s[j] - m); sum += s[j]; }
+        for (int t = 0; t < d; ++t) o[t] = 0.0f;
+        for (size_t j = 0; j < L; ++j) {
+            const float w = s[j] / sum;
+#pragma omp simd
+            for (int t = 0; t < d; ++t) o[t] += w * vb[j * d + t];
+        }
+        if (L == 0) for (int t = 0; t < d; ++t) o[t] = 0.0f;
+        free(s);
+    }
+    free(kd);
+    free(vd);
+    return bad ? -1 : 0;
+}
+
 /* turbo_quant_impl.h:659-685 / flash_attn_impl.h:445-473 */
 void orc_combine(const float *part_o, const float *part_lse, size_t rows, int d, int n_splits, float *o) {
     for (size_t row = 0; row < rows; ++row) {

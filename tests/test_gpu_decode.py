@@ -612,6 +612,92 @@ def test_gather_epilogue_on_one_rank(P, oracle):
         P.PackedAttention(q, k_rows, v_rows, kv_len, kq, vq, cfg, gather=g).run()
 
 
+def _local_gather(P, world, rows, d, dev, max_polls=0):
+    """What OutputGather provides, without symmetric memory: every rank's buffer and flags are plain local allocations."""
+    A = P._abi
+
+    class G:
+        pass
+    g = G()
+    g.buf = torch.full((2, world, rows, d), 7.0, dtype=torch.bfloat16, device=dev)
+    g.peer_bufs = [g.buf] + [torch.full_like(g.buf, 9.0) for _ in range(world - 1)]
+    g.flags = [torch.zeros(max(world, 4), dtype=torch.int32, device=dev) for _ in range(world)]
+    g.state = torch.zeros(2, dtype=torch.int32, device=dev)
+    g.ptrs = torch.tensor([t.data_ptr() for t in g.peer_bufs] + [t.data_ptr() for t in g.flags], dtype=torch.int64, device=dev)
+    g.args = A.PeerGather(g.ptrs.data_ptr(), g.ptrs.data_ptr() + 8 * world, world, 0, g.state.data_ptr(), g.state.data_ptr() + 4, max_polls, 0)
+    return g
+
+
+def test_gather_epilogue_inside_the_decode_grid(P, oracle):
+    """Many columns: the decode grid merges its segments itself and the workers that finish the rows store them into
+    the gathered buffer; the worker that finishes the call's last column publishes the step. Ragged lengths with empty
+    sequences (their zero rows are gathered too)."""
+    A = P._abi
+    dev = torch.device("cuda:0")
+    b, hq, hkv, d, cap = 96, 8, 2, 128, 300
+    kq = P.TurboQuantizer(fmt(P, A.MXFP4), d, "none", 42, dev)
+    vq = P.TurboQuantizer(fmt(P, A.MXFP4), d, "none", 44, dev)
+    g0 = torch.Generator(device=dev).manual_seed(3)
+    k_rows = kq.quantize_rows(torch.randn((b * hkv * cap, d), generator=g0, device=dev, dtype=torch.bfloat16)).view(b, hkv, cap, -1)
+    v_rows = vq.quantize_rows(torch.randn((b * hkv * cap, d), generator=g0, device=dev, dtype=torch.bfloat16)).view(b, hkv, cap, -1)
+    lens = np.random.default_rng(1).integers(1, cap + 1, size=b).astype(np.int32)
+    lens[3] = lens[40] = 0
+    kv_len = torch.from_numpy(lens).to(dev)
+    cfg = P.FlashAttnConfig(d ** -0.5).causal()
+    g = _local_gather(P, 1, b * hq, d, dev)
+    for step in (1, 2, 3):
+        q = torch.randn((b, hq, 1, d), generator=g0, device=dev, dtype=torch.bfloat16)
+        want = P.attention_packed(q, k_rows, v_rows, kv_len, kq, vq, cfg)
+        got = P.PackedAttention(q, k_rows, v_rows, kv_len, kq, vq, cfg, gather=g).run()
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+        assert g.state.tolist() == [step, 0] and g.flags[0].tolist()[0] == step
+        assert torch.equal(g.buf[step & 1, 0].view(b, hq, 1, d), want)
+        assert bool((got[3] == 0).all())
+
+
+@pytest.mark.parametrize("b", [3, 96])  # the publish step as a grid of its own behind the combine grid / inside the decode grid
+def test_gather_wait_for_a_rank_that_never_answers(P, oracle, b):
+    """Failure detection without a fault: a world of two whose second rank does not exist (its buffer and flags are
+    local allocations that nobody writes). The wait for its flag runs out after max_polls polls: the call returns, the
+    status word says 2, the library-wide flag is raised, this rank's own rows are complete, and the next call (a world
+    of one on the same state words) works."""
+    A = P._abi
+    dev = torch.device("cuda:0")
+    hq, hkv, d, cap = 8, 2, 128, 300
+    kq = P.TurboQuantizer(fmt(P, A.MXFP4), d, "none", 42, dev)
+    vq = P.TurboQuantizer(fmt(P, A.MXFP4), d, "none", 44, dev)
+    g0 = torch.Generator(device=dev).manual_seed(4)
+    k_rows = kq.quantize_rows(torch.randn((b * hkv * cap, d), generator=g0, device=dev, dtype=torch.bfloat16)).view(b, hkv, cap, -1)
+    v_rows = vq.quantize_rows(torch.randn((b * hkv * cap, d), generator=g0, device=dev, dtype=torch.bfloat16)).view(b, hkv, cap, -1)
+    kv_len = torch.from_numpy(np.random.default_rng(2).integers(1, cap + 1, size=b).astype(np.int32)).to(dev)
+    cfg = P.FlashAttnConfig(d ** -0.5).causal()
+    q = torch.randn((b, hq, 1, d), generator=g0, device=dev, dtype=torch.bfloat16)
+    want = P.attention_packed(q, k_rows, v_rows, kv_len, kq, vq, cfg)
+    assert A.lib().b200_device_wait_check(1) == A.OK
+    g = _local_gather(P, 2, b * hq, d, dev, max_polls=2000)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    got = P.PackedAttention(q, k_rows, v_rows, kv_len, kq, vq, cfg, gather=g, status=status).run()
+    torch.cuda.synchronize()                                   # returns: the wait is bounded
+    assert int(status.item()) == 2
+    assert torch.equal(got, want)                              # the attention itself is complete
+    assert torch.equal(g.buf[1, 0].view(b, hq, 1, d), want)    # and so are this rank's rows, in both ranks' buffers
+    assert torch.equal(g.peer_bufs[1][1, 0].view(b, hq, 1, d), want)
+    assert g.flags[1].tolist()[0] == 1 and g.flags[0].tolist()[1] == 0
+    assert g.state.tolist() == [1, 0]                          # the step advanced, the column counter is back at zero
+    assert A.lib().b200_device_wait_status() == 1
+    assert A.lib().b200_device_wait_check(1) == A.ERR_DEVICE_WAIT and b"wait" in A.lib().b200_last_error()
+    assert A.lib().b200_device_wait_status() == 0
+    # the same state words, a world of one: works, and takes the next step's slot
+    g.args.world = 1
+    status.zero_()
+    got = P.PackedAttention(q, k_rows, v_rows, kv_len, kq, vq, cfg, gather=g, status=status).run()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and torch.equal(got, want)
+    assert g.state.tolist() == [2, 0] and torch.equal(g.buf[0, 0].view(b, hq, 1, d), want)
+    assert A.lib().b200_device_wait_status() == 0
+
+
 @pytest.mark.parametrize("kf,vf", [((2, 4), (2, 4)), ((0, 4), (0, 3)), ((5, 4), (4, 4))])
 def test_paged_blocks_equal_the_concatenated_rows(P, oracle, kf, vf):
     """attention_packed_blocks over four cache blocks of different capacities and fill levels (one of them empty)
