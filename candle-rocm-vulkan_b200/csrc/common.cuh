@@ -15,6 +15,16 @@ namespace b200 {
 int set_error(int code, const char *fmt, ...);
 int check_launch(const char *what);
 
+// Diagnostic switches select between code paths that give the same results, so that each can be tested and timed
+// alone. They exist only in builds with -DB200_DIAG (read from the environment, once per process); the library
+// proper reads no environment variable.
+#ifdef B200_DIAG
+#include <cstdlib>
+inline const char *diag_env(const char *name) { return getenv(name); }
+#else
+inline const char *diag_env(const char *) { return nullptr; }
+#endif
+
 // ---------------------------------------------------------------------------------------------
 // bit casts
 // ---------------------------------------------------------------------------------------------

@@ -13,6 +13,7 @@
 // right aligned windows, softcap, ALiBi, k / v descale, varlen through cumulative offsets, zeros
 // for rows without a visible key; output row (token, head) of d contiguous elements.
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 #include <cuda_bf16.h>
 
@@ -489,14 +490,18 @@ extern "C" int b200_flash_attn(const B200FaArgs *a, b200_stream_t stream_) {
     return bf ? fa_launch<128, true>(pl, stream) : fa_launch<128, false>(pl, stream);
 }
 
-// One auxiliary stream and two events per device for b200_fa_prefill_append (created on first use, kept for the life
-// of the process).
+// Auxiliary streams of b200_fa_prefill_append: a few per device, each with its fork / join events (created on first
+// use, kept for the life of the process). A call holds one of them while it enqueues its work (event records and waits
+// of two calls on one pair of events must not interleave), so calls from several host threads, on several streams,
+// run side by side; with more concurrent callers than slots a caller waits for a slot.
 struct PrefillFork {
     cudaStream_t aux = nullptr;
     cudaEvent_t fork = nullptr, join = nullptr;
+    std::mutex busy;
 };
-static PrefillFork g_fork[16];
-static std::mutex g_fork_mutex;
+constexpr int FORK_SLOTS = 4;
+static PrefillFork g_fork[16][FORK_SLOTS];
+static std::atomic<unsigned> g_fork_next{0};
 
 extern "C" int b200_fa_prefill_append(const B200FaArgs *fa, const B200KvAppendArgs *append, b200_stream_t stream_) {
     // The attention reads the uncompressed k / v and is bound by the tensor core; the cache write reads the same
@@ -510,16 +515,21 @@ extern "C" int b200_fa_prefill_append(const B200FaArgs *fa, const B200KvAppendAr
         const int rc = b200_flash_attn(fa, stream_);
         return rc ? rc : b200_kv_append(append, stream_);
     }
-    PrefillFork *f = &g_fork[dev];
-    {
-        std::lock_guard<std::mutex> lock(g_fork_mutex);
-        if (!f->aux) {
-            if (cudaStreamCreateWithFlags(&f->aux, cudaStreamNonBlocking) != cudaSuccess ||
-                cudaEventCreateWithFlags(&f->fork, cudaEventDisableTiming) != cudaSuccess ||
-                cudaEventCreateWithFlags(&f->join, cudaEventDisableTiming) != cudaSuccess) {
-                f->aux = nullptr;
-                return set_error(B200_ERR_LAUNCH, "fa_prefill_append: cannot create the auxiliary stream");
-            }
+    // a free slot, or the next one in turn
+    PrefillFork *f = nullptr;
+    for (int i = 0; i < FORK_SLOTS && !f; ++i)
+        if (g_fork[dev][i].busy.try_lock()) f = &g_fork[dev][i];
+    if (!f) {
+        f = &g_fork[dev][g_fork_next.fetch_add(1, std::memory_order_relaxed) % FORK_SLOTS];
+        f->busy.lock();
+    }
+    std::lock_guard<std::mutex> held(f->busy, std::adopt_lock);
+    if (!f->aux) {
+        if (cudaStreamCreateWithFlags(&f->aux, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&f->fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&f->join, cudaEventDisableTiming) != cudaSuccess) {
+            f->aux = nullptr;
+            return set_error(B200_ERR_LAUNCH, "fa_prefill_append: cannot create the auxiliary stream");
         }
     }
     if (cudaEventRecord(f->fork, stream) != cudaSuccess || cudaStreamWaitEvent(f->aux, f->fork, 0) != cudaSuccess)

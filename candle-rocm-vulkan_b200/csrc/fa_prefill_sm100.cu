@@ -1024,7 +1024,7 @@ bool fa_prefill_sm100_supported(const FaParams &p, bool kv16) {
     if ((uint64_t)p.lq * p.group < 4 * PF_BM) return false;  // short chunks and decode stay on the mma.sync kernel
     // 16-byte chunks of q rows
     if ((reinterpret_cast<uintptr_t>(p.q) & 15) || ((p.q_sb | p.q_ss | p.q_sh) & 7)) return false;
-    static const bool off = [] { const char *e = getenv("B200_FA_NO_TCGEN05"); return e && *e == '1'; }();
+    static const bool off = [] { const char *e = diag_env("B200_FA_NO_TCGEN05"); return e && *e == '1'; }();
     return !off;
 }
 
@@ -1111,7 +1111,7 @@ int fa_prefill_sm100_launch(const FaParams &p, bool bf16, cudaStream_t stream) {
         done[dev][bf16] = true;
     }
     const uint64_t rows = (uint64_t)p.lq * p.group;
-    static const long force = [] { const char *e = getenv("B200_FA_TC_ROWS"); return e ? atol(e) : 0l; }();  // 128 or 256: tile height
+    static const long force = [] { const char *e = diag_env("B200_FA_TC_ROWS"); return e ? atol(e) : 0l; }();  // 128 or 256: tile height
     // 256-row blocks halve the K / V traffic per product and overlap softmax with products inside the block; they
     // need enough blocks to fill the device
     bool two = rows >= 1024;
@@ -1121,8 +1121,8 @@ int fa_prefill_sm100_launch(const FaParams &p, bool bf16, cudaStream_t stream) {
         const dim3 grid((unsigned)((rows + P2_ROWS - 1) / P2_ROWS), p.hkv, p.b);
         // K / V through tensor copies when the tensors can be described by a map (fixed-length batches, 16-byte aligned
         // strides); otherwise 16-byte chunks
-        static const bool no_tma = [] { const char *e = getenv("B200_FA_NO_TMA"); return e && *e == '1'; }();
-        static const bool no_qtma = [] { const char *e = getenv("B200_FA_NO_QTMA"); return e && *e == '1'; }();
+        static const bool no_tma = [] { const char *e = diag_env("B200_FA_NO_TMA"); return e && *e == '1'; }();
+        static const bool no_qtma = [] { const char *e = diag_env("B200_FA_NO_QTMA"); return e && *e == '1'; }();
         CUtensorMap tm_k, tm_v, tm_q;
         uint32_t ok_ = 0, ov_ = 0;
         const bool tma = !no_tma && !p.varlen && make_kv_map(&tm_k, &ok_, p.k, bf16, p.b, p.hkv, p.lk, p.k_sb, p.k_sh, p.k_ss) &&

@@ -9,7 +9,7 @@
 
 namespace b200 {
 
-template <int KM, int VM, int HD, bool NAT>
+template <int KM, int VM, int HD, bool NAT, bool PAGED>
 int launch_decode(const DecodeParams &p, dim3 grid, size_t smem, cudaStream_t stream);
 template <int KM, int VM, int HD, bool NAT>
 int launch_decode_pair(const DecodeParams &p, dim3 grid, size_t smem, cudaStream_t stream);
@@ -62,13 +62,15 @@ static int fill_decode_side(DecodeSide &s, const B200QuantSide &q, uint32_t d, c
     return B200_OK;
 }
 
-static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
+// paged: the plan of a call whose rows are read in the blocks of its page table (the tensor-core kernel walks the table)
+static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl, bool paged = false) {
     if (!a) return set_error(B200_ERR_BAD_ARG, "tq_attention: null args");
     if (a->hkv == 0 || a->hq % a->hkv != 0)
         return set_error(B200_ERR_BAD_ARG, "tq_attention: %u query heads are not a multiple of %u kv heads", a->hq, a->hkv);
     if (a->d != 64 && a->d != 128 && a->d != 256)
         return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: head dim %u (fused kernel: 64, 128, 256)", a->d);
-    if (a->pages) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: paged rows with per-sequence lengths or without blocks");
+    if ((a->pages != nullptr) != paged || (paged && (a->n_pages == 0 || a->kq.mode != a->vq.mode)))
+        return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: paged rows without blocks, or with per-sequence lengths on a path that cannot take them");
     DecodeParams &p = pl.p;
     memset(&p, 0, sizeof(p));
     int rc = fill_decode_side(p.k, a->kq, a->d, "key");
@@ -135,10 +137,10 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
         }
     }
     bps = std::max(bps, 1);
-    pl.smem = fixed + DW * p.ns * stage;
+    pl.smem = fixed + DW * p.ns * stage + DW * NS_MAX * 16;  // + the tile descriptions of paged rows
     pl.pair = false;
     int wpb = DW;  // workers per block
-    if (pair_formats(a->kq.mode, a->vq.mode)) {
+    if (!paged && pair_formats(a->kq.mode, a->vq.mode)) {
         // codebook formats: a worker is a pair of warps, two blocks of four pairs per SM; as many stages as fit
         const size_t pq = p.qstage_bytes ? (size_t)2 * PW * PACK * a->d * 4 : 0;
         const size_t pfixed = PAIR_FIXED + (size_t)PW * pair_meta_bytes(a->kq.mode, a->vq.mode, (int)a->d) + pq;
@@ -164,7 +166,8 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
     // persistent blocks of DW independent warps: as many as fit on the device at once, at most one
     // warp per tile of keys
     const uint64_t lk = std::max<uint32_t>(a->lk, 1);
-    const uint64_t max_tiles = (uint64_t)a->b * pl.ny * ((lk + WK - 1) / WK);
+    // paged rows: every block may end in a short tile
+    const uint64_t max_tiles = (uint64_t)a->b * pl.ny * ((lk + WK - 1) / WK + (paged ? a->n_pages : 0u));
     uint64_t nblocks = (uint64_t)sm_count_cached() * bps;
     if (a->splits > 0) nblocks = std::min<uint64_t>(nblocks, ((uint64_t)a->b * pl.ny * a->splits + wpb - 1) / wpb);
     pl.blocks = (uint32_t)std::max<uint64_t>(std::min(nblocks, (max_tiles + wpb - 1) / wpb), 1);
@@ -174,7 +177,9 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
     p.prefetch = (p.after_prev && (a->flags & B200_TQ_INPUTS_FINAL)) ? 1u : 0u;
     p.fresh_rows = std::min<uint32_t>(a->fresh_rows, 0x7fffffffu);
     const size_t ncols = (size_t)a->b * pl.ny;
-    pl.nat = p.k_ss == (uint64_t)kl.row_words && p.v_ss == (uint64_t)vl.row_words && a->kq.mode == a->vq.mode && a->d == 128;
+    pl.nat = !paged && p.k_ss == (uint64_t)kl.row_words && p.v_ss == (uint64_t)vl.row_words && a->kq.mode == a->vq.mode && a->d == 128;
+    p.pages = paged ? a->pages : nullptr;
+    p.n_pages = paged ? a->n_pages : 0u;
     // Few segments per column (the workers outnumber the columns by less than eight to one): the last worker of a
     // column merges it inside the decode grid. Many segments per column (a few long sequences), or more columns
     // than there are arrival counters: a combine grid, whose blocks share a row's segments, follows.
@@ -207,22 +212,32 @@ static int dispatch_hd(const DecodePlan &pl, dim3 grid, cudaStream_t stream) {
         }
     }
     if constexpr (KM == VM)
-        if (pl.nat && pl.hd_idx == 1) return launch_decode<KM, VM, 128, true>(pl.p, grid, pl.smem, stream);
+        if (pl.nat && pl.hd_idx == 1) return launch_decode<KM, VM, 128, true, false>(pl.p, grid, pl.smem, stream);
     switch (pl.hd_idx) {
-    case 0: return launch_decode<KM, VM, 64, false>(pl.p, grid, pl.smem, stream);
-    case 1: return launch_decode<KM, VM, 128, false>(pl.p, grid, pl.smem, stream);
-    default: return launch_decode<KM, VM, 256, false>(pl.p, grid, pl.smem, stream);
+    case 0: return launch_decode<KM, VM, 64, false, false>(pl.p, grid, pl.smem, stream);
+    case 1: return launch_decode<KM, VM, 128, false, false>(pl.p, grid, pl.smem, stream);
+    default: return launch_decode<KM, VM, 256, false, false>(pl.p, grid, pl.smem, stream);
+    }
+}
+
+template <int KM>
+static int dispatch_paged(const DecodePlan &pl, dim3 grid, cudaStream_t stream) {
+    switch (pl.hd_idx) {
+    case 0: return launch_decode<KM, KM, 64, false, true>(pl.p, grid, pl.smem, stream);
+    case 1: return launch_decode<KM, KM, 128, false, true>(pl.p, grid, pl.smem, stream);
+    default: return launch_decode<KM, KM, 256, false, true>(pl.p, grid, pl.smem, stream);
     }
 }
 
 template <int KM>
 static int dispatch_v(const DecodePlan &pl, dim3 grid, cudaStream_t stream) {
+    if (pl.p.pages) return dispatch_paged<KM>(pl, grid, stream);
 #ifdef B200_ONLY_SAME_FORMAT  // measurement builds only: keys and values in one format, the other pairs are left out
     if (pl.p.v.mode != KM || pl.hd_idx != 1 || !pl.nat) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "measurement build");
     if constexpr (pair_formats(KM, KM)) {
         if (pl.pair) return launch_decode_pair<KM, KM, 128, true>(pl.p, grid, pl.smem, stream);
     }
-    return launch_decode<KM, KM, 128, true>(pl.p, grid, pl.smem, stream);
+    return launch_decode<KM, KM, 128, true, false>(pl.p, grid, pl.smem, stream);
 #else
     switch (pl.p.v.mode) {
     case B200_TURBO_MSE: return dispatch_hd<KM, B200_TURBO_MSE>(pl, grid, stream);
@@ -294,6 +309,38 @@ int decode_wait_status() {
     int32_t v = 0;
     if (cudaMemcpy(&v, w.wait_failed, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     return v != 0;
+}
+
+// Keys and tiles before every block of a page table (n_pages + 1 entries each): one block of 256 threads.
+__global__ void __launch_bounds__(256) tq_page_prefix_kernel(const B200Page *__restrict__ pages, uint32_t n_pages, uint32_t *__restrict__ pg_keys,
+                                                              uint32_t *__restrict__ pg_tiles) {
+    __shared__ uint32_t sk[256], st[256];
+    uint32_t base_k = 0, base_t = 0;
+    for (uint32_t start = 0; start < n_pages; start += 256) {
+        const uint32_t i = start + threadIdx.x;
+        const uint32_t r = i < n_pages ? pages[i].rows : 0u;
+        sk[threadIdx.x] = r;
+        st[threadIdx.x] = (r + WK - 1) / WK;
+        __syncthreads();
+        for (int o = 1; o < 256; o <<= 1) {  // inclusive scans
+            const uint32_t ak = threadIdx.x >= (unsigned)o ? sk[threadIdx.x - o] : 0u, at = threadIdx.x >= (unsigned)o ? st[threadIdx.x - o] : 0u;
+            __syncthreads();
+            sk[threadIdx.x] += ak;
+            st[threadIdx.x] += at;
+            __syncthreads();
+        }
+        if (i < n_pages) {
+            pg_keys[i] = base_k + sk[threadIdx.x] - r;
+            pg_tiles[i] = base_t + st[threadIdx.x] - (r + WK - 1) / WK;
+        }
+        base_k += sk[255];
+        base_t += st[255];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        pg_keys[n_pages] = base_k;
+        pg_tiles[n_pages] = base_t;
+    }
 }
 
 // n words from src to dst by the 256 threads of a block: 16-byte vectors where both sides sit at the same offset inside
@@ -376,7 +423,7 @@ struct PagedFast {
     uint32_t cap, kw, vw;
 };
 static bool paged_fast_plan(const B200TqAttnArgs *a, PagedFast &f) {
-    static const bool off = getenv("B200_PAGED_IN_PLACE") != nullptr;
+    static const bool off = diag_env("B200_PAGED_IN_PLACE") != nullptr;
     if (off || !a || !a->pages || a->n_pages == 0 || a->kv_len_dev || a->lk == 0 || a->b == 0 || a->hkv == 0) return false;
     B200RowLayout kl, vl;
     if (b200_row_layout(a->kq.mode, a->kq.bits, (int)a->d, &kl) || b200_row_layout(a->vq.mode, a->vq.bits, (int)a->d, &vl)) return false;
@@ -410,7 +457,25 @@ static bool paged_fast_plan(const B200TqAttnArgs *a, PagedFast &f) {
     return true;
 }
 
+// A paged call that the tensor-core kernel serves by walking the page table itself: keys and values in one format of
+// that kernel. Workspace: the keys and tiles before every block (written by a one-block kernel in front of the
+// attention), then the attention's own.
+static size_t paged_prefix_bytes(uint32_t n_pages) { return ((size_t)(n_pages + 1) * 8 + 255) / 256 * 256; }
+static bool paged_direct_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
+    static const bool off = diag_env("B200_PAGED_NO_WALK") != nullptr;  // diagnostic: paged rows on the compaction / general paths
+    if (off || !a || !a->pages || a->n_pages == 0 || a->lk == 0 || a->b == 0 || a->kq.mode != a->vq.mode) return false;
+    B200TqAttnArgs t = *a;
+    t.flags &= ~(B200_TQ_AFTER_PREV | B200_TQ_INPUTS_FINAL);  // the prefix kernel of the call runs right before the attention
+    if (tq_generic_takes(&t) && (a->d != 64 && a->d != 128 && a->d != 256)) return false;
+    if (a->kq.mode == B200_TURBO_MSE && (a->kq.bits != 4 || a->vq.bits != 4)) return false;
+    return make_plan(&t, pl, true) == B200_OK;
+}
+
 extern "C" size_t b200_tq_attention_workspace_bytes(const B200TqAttnArgs *a) {
+    {
+        DecodePlan pl;
+        if (paged_direct_plan(a, pl)) return paged_prefix_bytes(a->n_pages) + pl.ws_bytes;
+    }
     {
         // paged rows: with this much workspace the blocks are compacted into it and the tensor-core kernel runs; with
         // less (16 bytes are enough) the general kernel reads the blocks in place
@@ -426,7 +491,27 @@ extern "C" size_t b200_tq_attention_workspace_bytes(const B200TqAttnArgs *a) {
 // set by b200_tq_attention_gather around its call of b200_tq_attention (same thread)
 static thread_local const B200PeerGather *tl_gather = nullptr;
 
+static int run_plan(const B200TqAttnArgs *a, DecodePlan &pl, char *ws, size_t ws_bytes, cudaStream_t stream);
+
 extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_) {
+    {
+        // paged rows, keys and values in one format of the tensor-core kernel: that kernel walks the page table
+        DecodePlan pl;
+        if (paged_direct_plan(a, pl)) {
+            const size_t pre = paged_prefix_bytes(a->n_pages);
+            if (a->workspace && a->workspace_bytes >= pre + pl.ws_bytes && !(reinterpret_cast<uintptr_t>(a->workspace) & 15) &&
+                (uint64_t)a->b * a->hq * a->lq != 0 && a->q && a->out) {
+                char *ws = reinterpret_cast<char *>(a->workspace);
+                uint32_t *pg_keys = reinterpret_cast<uint32_t *>(ws), *pg_tiles = pg_keys + (a->n_pages + 1);
+                tq_page_prefix_kernel<<<1, 256, 0, (cudaStream_t)stream_>>>(a->pages, a->n_pages, pg_keys, pg_tiles);
+                const int rc = check_launch("tq_page_prefix");
+                if (rc) return rc;
+                pl.p.pg_keys = pg_keys;
+                pl.p.pg_tiles = pg_tiles;
+                return run_plan(a, pl, ws + pre, a->workspace_bytes - pre, (cudaStream_t)stream_);
+            }
+        }
+    }
     {
         PagedFast f;
         if (paged_fast_plan(a, f) && a->workspace && a->workspace_bytes >= f.need && !(reinterpret_cast<uintptr_t>(a->workspace) & 255) &&
@@ -454,6 +539,14 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
     DecodePlan pl;
     const int rc = make_plan(a, pl);
     if (rc) return rc;
+    if ((uint64_t)a->b * a->hq * a->lq == 0) return B200_OK;
+    if (!a->k_rows || !a->v_rows) return set_error(B200_ERR_BAD_ARG, "tq_attention: null pointer");
+    return run_plan(a, pl, reinterpret_cast<char *>(a->workspace), a->workspace ? a->workspace_bytes : 0, (cudaStream_t)stream_);
+}
+
+// The launches of a planned call: the decode grid, and the combine (and publish) grids where that grid does not merge
+// its segments itself. `ws`: the attention's own part of the workspace.
+static int run_plan(const B200TqAttnArgs *a, DecodePlan &pl, char *ws, size_t ws_bytes, cudaStream_t stream) {
     if (tl_gather) {
         pl.p.peer_bufs = tl_gather->peer_bufs;
         pl.p.peer_flags = tl_gather->peer_flags;
@@ -463,15 +556,12 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
         pl.p.done_ctr = tl_gather->done_ctr;
         pl.p.gather_polls = tl_gather->max_polls;
     }
-    cudaStream_t stream = (cudaStream_t)stream_;
     if ((uint64_t)a->b * a->hq * a->lq == 0) return B200_OK;
-    if (!a->q || !a->out || !a->k_rows || !a->v_rows) return set_error(B200_ERR_BAD_ARG, "tq_attention: null pointer");
-    if (!a->workspace || a->workspace_bytes < pl.ws_bytes)
-        return set_error(B200_ERR_WORKSPACE, "tq_attention: workspace of %zu bytes needed, %zu given", pl.ws_bytes,
-                         a->workspace ? a->workspace_bytes : (size_t)0);
-    if (reinterpret_cast<uintptr_t>(a->workspace) & 15) return set_error(B200_ERR_BAD_ARG, "tq_attention: workspace must be 16-byte aligned");
+    if (!a->q || !a->out) return set_error(B200_ERR_BAD_ARG, "tq_attention: null pointer");
+    if (!ws || ws_bytes < pl.ws_bytes)
+        return set_error(B200_ERR_WORKSPACE, "tq_attention: workspace of %zu bytes needed, %zu given", pl.ws_bytes, ws ? ws_bytes : (size_t)0);
+    if (reinterpret_cast<uintptr_t>(ws) & 15) return set_error(B200_ERR_BAD_ARG, "tq_attention: workspace must be 16-byte aligned");
     DecodeParams &p = pl.p;
-    char *ws = reinterpret_cast<char *>(a->workspace);
     p.part_o = reinterpret_cast<float *>(ws);
     p.part_lse = reinterpret_cast<float *>(ws + pl.off_lse);
     p.meta = reinterpret_cast<int32_t *>(ws + pl.off_meta);

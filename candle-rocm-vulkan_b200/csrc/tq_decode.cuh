@@ -99,6 +99,11 @@ struct DecodeParams {
     // counter back to zero): the last worker of a column merges it. Null: the combine grid merges.
     uint32_t *ctr;
     int32_t *lib_status;    // library-wide flag: set when a bounded wait of a kernel of this call runs out
+    // paged rows (null: dense rows): the block table, and for every block the keys and the 32-key tiles of the
+    // blocks before it (n_pages + 1 entries each, written by tq_page_prefix_kernel right before this grid)
+    const B200Page *pages;
+    uint32_t n_pages;
+    const uint32_t *pg_keys, *pg_tiles;
 };
 
 __host__ __device__ constexpr bool fmt_is4(int m) { return m == B200_MXFP4 || m == B200_NVFP4 || m == B200_TURBO_MSE; }
@@ -245,11 +250,36 @@ __device__ __forceinline__ void warp_hadamard(float *row, int n, const float *si
 // sits between the warps.
 struct Column {
     int lo, hi, lk, tiles;
+    uint32_t t_lo;  // paged rows: index of the column's first tile in the block table's list of tiles
 };
+
+// Paged rows: tiles never straddle blocks (as the reference's windows never do, candle-core/kernels/
+// flash_attn_impl.h:135-151): block g holds ceil(rows_g / WK) tiles, the last one short. The block that holds key
+// position `key` (< the total number of keys): the last g with pg_keys[g] <= key.
+__device__ __forceinline__ uint32_t page_of_key(const DecodeParams &p, uint32_t key) {
+    uint32_t lo = 0, hi = p.n_pages;  // invariant: pg_keys[lo] <= key < pg_keys[hi]
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (p.pg_keys[mid] <= key) lo = mid;
+        else hi = mid;
+    }
+    return lo;
+}
+// the block that holds tile T of the table's list (< the total number of tiles)
+__device__ __forceinline__ uint32_t page_of_tile(const DecodeParams &p, uint32_t T) {
+    uint32_t lo = 0, hi = p.n_pages;
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (p.pg_tiles[mid] <= T) lo = mid;
+        else hi = mid;
+    }
+    return lo;
+}
 
 __device__ __forceinline__ Column make_column(const DecodeParams &p, uint32_t b) {
     Column c;
     c.lk = p.kv_len ? min(max(p.kv_len[b] + p.kv_len_add, 0), (int)p.lk) : (int)p.lk;
+    if (p.pages) c.lk = (int)min((uint32_t)c.lk, p.pg_keys[p.n_pages]);  // never more keys than the blocks hold
     // union of the rows' ranges: first query token gives the lowest, the last the highest key
     const long long pos0 = (long long)c.lk - (long long)p.lq, pos1 = (long long)c.lk - 1;
     long long lo = p.wl >= 0 ? max(pos0 - p.wl, 0ll) : 0ll;
@@ -258,7 +288,16 @@ __device__ __forceinline__ Column make_column(const DecodeParams &p, uint32_t b)
     hi = max(hi, lo);
     c.lo = (int)lo;
     c.hi = (int)hi;
-    c.tiles = (c.hi - c.lo + WK - 1) / WK;
+    c.t_lo = 0;
+    if (p.pages == nullptr) {
+        c.tiles = (c.hi - c.lo + WK - 1) / WK;
+    } else if (c.hi > c.lo) {
+        const uint32_t g0 = page_of_key(p, (uint32_t)c.lo), g1 = page_of_key(p, (uint32_t)c.hi - 1);
+        c.t_lo = p.pg_tiles[g0] + ((uint32_t)c.lo - p.pg_keys[g0]) / WK;
+        c.tiles = (int)(p.pg_tiles[g1] + ((uint32_t)c.hi - 1 - p.pg_keys[g1]) / WK + 1 - c.t_lo);
+    } else {
+        c.tiles = 0;
+    }
     return c;
 }
 
@@ -1243,6 +1282,10 @@ struct CopySide {
     uint32_t koff, voff;  // offset of the tile's first row inside its copy
     uint32_t kb, vb;      // bytes of a whole tile's copies
     int key;              // first key of the next tile
+    // paged rows: the block of the next tile, the tile's first row in it, the block's rows and capacities, and the
+    // addresses of the (batch entry, kv head) slabs of the block
+    uint32_t pg, off, pg_rows, k_cap, v_cap;
+    uintptr_t pk, pv;
 
     // per-segment constants
     __device__ __forceinline__ void enter(const DecodeParams &p, uint32_t krb, uint32_t vrb) {
@@ -1264,6 +1307,82 @@ struct CopySide {
         iseg = seg;
         more = true;
         enter(p, krb, vrb);
+    }
+
+    // ---- paged rows: a tile's source is (block, row in the block) instead of rows + key * stride
+    __device__ __forceinline__ void load_page(const DecodeParams &p, uint32_t krb, uint32_t vrb) {
+        const B200Page pgd = p.pages[pg];
+        const uint32_t hk = iseg.y / p.packs;
+        pg_rows = pgd.rows;
+        k_cap = pgd.k_cap;
+        v_cap = pgd.v_cap;
+        // block layout (batch entry, kv head, capacity, words): head stride = capacity rows, batch stride = hkv heads
+        pk = reinterpret_cast<uintptr_t>(pgd.k) + ((uintptr_t)iseg.b * p.hkv + hk) * pgd.k_cap * krb;
+        pv = reinterpret_cast<uintptr_t>(pgd.v) + ((uintptr_t)iseg.b * p.hkv + hk) * pgd.v_cap * vrb;
+    }
+    __device__ __forceinline__ void enter_paged(const DecodeParams &p, uint32_t krb, uint32_t vrb) {
+        left = (int)(iseg.t1 - iseg.t0);
+        const uint32_t T = iseg.col.t_lo + iseg.t0;
+        pg = page_of_tile(p, T);
+        off = (T - p.pg_tiles[pg]) * WK;
+        load_page(p, krb, vrb);
+    }
+    __device__ __forceinline__ void start_paged(const DecodeParams &p, const Segment &seg, uint32_t krb, uint32_t vrb) {
+        iseg = seg;
+        more = true;
+        enter_paged(p, krb, vrb);
+    }
+    // Copies the next tile into stage `st` and leaves its description (offsets of the first row inside the copies, first
+    // key, number of keys) at `desc` for the compute side.
+    __device__ __forceinline__ void tile_paged(Worker &w, uint32_t st, uint32_t bar, uint32_t desc, uint32_t krb, uint32_t vrb, uint32_t k_stage_bytes,
+                                               uint64_t x_end) {
+        const DecodeParams &p = w.p;
+        const int lane = w.lane;
+        const int key0 = (int)(p.pg_keys[pg] + off);
+        const int nkeys = min(min(WK, (int)(pg_rows - off)), iseg.col.hi - key0);
+        if (!w.waited && key0 + nkeys > iseg.col.lk - (int)p.fresh_rows) w.prev_done();
+        const uintptr_t ka = pk + (uintptr_t)off * krb, va = pv + (uintptr_t)off * vrb;
+        const uint32_t ko = (uint32_t)(ka & 15u), vo = (uint32_t)(va & 15u);
+        const uintptr_t k0 = ka - ko, v0 = va - vo;
+        const uint32_t ke = ko + (uint32_t)nkeys * krb, ve = vo + (uint32_t)nkeys * vrb;  // ends, from the copy start
+        // A copy ends at the 16-byte boundary above its last row; where that may lie past the block's slab (the tile
+        // reaches the slab's last row) it ends at the boundary below and the last words come by plain loads.
+        const bool ktail = off + (uint32_t)nkeys >= k_cap, vtail = off + (uint32_t)nkeys >= v_cap;
+        const uint32_t kbt = ktail ? (ke & ~15u) : ((ke + 15u) & ~15u), vbt = vtail ? (ve & ~15u) : ((ve + 15u) & ~15u);
+        if (ktail && lane < 4) {
+            const uint32_t o = kbt + 4u * lane;
+            if (o >= ko && o < ke) sts32(st + o, *reinterpret_cast<const uint32_t *>(k0 + o));
+        }
+        if (vtail && lane >= 4 && lane < 8) {
+            const uint32_t o = vbt + 4u * (lane - 4);
+            if (o >= vo && o < ve) sts32(st + k_stage_bytes + o, *reinterpret_cast<const uint32_t *>(v0 + o));
+        }
+        if (lane == 0)
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(desc), "r"(ko), "r"(vo), "r"((uint32_t)key0), "r"((uint32_t)nkeys) : "memory");
+        __syncwarp();
+        if (lane == 0) {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kbt + vbt) : "memory");
+            if (kbt)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(st), "l"(k0), "r"(kbt),
+                             "r"(bar)
+                             : "memory");
+            if (vbt)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(st + k_stage_bytes),
+                             "l"(v0), "r"(vbt), "r"(bar)
+                             : "memory");
+        }
+        off += WK;
+        if (--left == 0) {
+            if (more) {
+                more = next_segment(iseg, p, w.ny, x_end);
+                if (more) enter_paged(p, krb, vrb);
+            }
+        } else if (off >= pg_rows) {
+            // the next block that holds rows (there is one: tiles are left in this column)
+            do ++pg; while (p.pages[pg].rows == 0);
+            off = 0;
+            load_page(p, krb, vrb);
+        }
     }
 
     // copies the next tile into stage `st` with barrier `bar` (the caller checked left > 0) and moves on
@@ -1383,6 +1502,7 @@ __device__ __forceinline__ bool tile_softmax(const DecodeParams &p, const Segmen
         rm.slope[e] = 0.0f;
         if (r < p.rows_per_kv) {
             row_range(p, seg.col, r, rm.lo[e], rm.hi[e], rm.pos[e]);
+            rm.hi[e] = min(rm.hi[e], key0 + nkeys);  // a short tile inside a column (the end of a cache block): its spare rows hold no keys
             if (p.alibi) rm.slope[e] = p.alibi[(size_t)seg.b * p.alibi_bs + hk * G + (p.lq == 1 ? r : r % G)];
         }
     }
@@ -1429,7 +1549,9 @@ __device__ __forceinline__ void load_codebooks(const DecodeParams &p, uint32_t l
 // ---------------------------------------------------------------------------------------------
 // Kernel 1: every warp a worker
 // ---------------------------------------------------------------------------------------------
-template <int KM, int VM, int HD, bool NAT>
+// PAGED: the rows live in the blocks of a page table; tiles are cut at the blocks' ends, the copy side leaves a
+// description of every tile beside its stage, and the row strides are those of the call (NAT is not combined with it).
+template <int KM, int VM, int HD, bool NAT, bool PAGED = false>
 __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_kernel(const DecodeParams p) {
     constexpr int STEPS = HD / 16;          // k-steps of K Q^T == m-tiles of the output
     constexpr bool K4 = fmt_is4(KM), V4 = fmt_is4(VM);
@@ -1477,17 +1599,24 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
     float *qstage = reinterpret_cast<float *>(smem + FIXED_SMEM + DW * META) + (size_t)warp * PACK * HD;  // only with a rotated cache
     const uint32_t wstage_s = sbase + FIXED_SMEM + DW * META + p.qstage_bytes + (uint32_t)warp * NS * stage_bytes;
     const uint32_t wbar_s = smem_u32(bars + warp * NS_MAX);
+    // paged rows: one description per stage, behind the rings of all warps
+    const uint32_t wdesc_s = sbase + FIXED_SMEM + DW * META + p.qstage_bytes + (uint32_t)DW * NS * stage_bytes + (uint32_t)warp * NS_MAX * 16;
     bool wait_failed = false;
 
     // Filling the ring. With the caller's word that the inputs are final (prefetch) all stages are asked for right away.
     // Otherwise the first tile alone, and the other stages once the first query rows are loaded: with every worker of
     // the grid asking for all its stages at once, the first tiles would arrive behind 26 MB of later ones.
     CopySide cs;
-    cs.start(p, sh.seg, krb, vrb);
+    if constexpr (PAGED) cs.start_paged(p, sh.seg, krb, vrb);
+    else cs.start(p, sh.seg, krb, vrb);
+    auto copy_tile = [&](uint32_t st, uint32_t bar, uint32_t desc) {
+        if constexpr (PAGED) cs.tile_paged(wk, st, bar, desc, krb, vrb, k_stage_bytes, sh.x_end);
+        else cs.tile(wk, st, bar, krb, vrb, k_stage_bytes, sh.x_end);
+    };
     int primed = 0;
     auto prime = [&](int upto) {
         for (; primed < upto && cs.left > 0; ++primed)
-            cs.tile(wk, wstage_s + (uint32_t)primed * stage_bytes, wbar_s + 8u * (uint32_t)primed, krb, vrb, k_stage_bytes, sh.x_end);
+            copy_tile(wstage_s + (uint32_t)primed * stage_bytes, wbar_s + 8u * (uint32_t)primed, wdesc_s + 16u * (uint32_t)primed);
     };
     prime(p.prefetch ? NS : 1);
 
@@ -1524,10 +1653,11 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
             // ============================================================ the tiles of the segment
             const int n_t = (int)(seg.t1 - seg.t0);
             int key0 = col.lo + (int)seg.t0 * WK;
-            const uint32_t koff = (uint32_t)((reinterpret_cast<uintptr_t>(p.k_rows + (size_t)seg.b * p.k_sb + (size_t)hk * p.k_sh) + (uintptr_t)(uint32_t)key0 * krb) & 15u);
-            const uint32_t voff = (uint32_t)((reinterpret_cast<uintptr_t>(p.v_rows + (size_t)seg.b * p.v_sb + (size_t)hk * p.v_sh) + (uintptr_t)(uint32_t)key0 * vrb) & 15u);
-            const uint32_t kt_off = koff + k_lane, vt_off = k_stage_bytes + voff + v_lane;
-            const uint32_t kr_off = koff + lane * krb, vr_off = k_stage_bytes + voff + lane * vrb;
+            // offsets of the tiles' first rows inside their copies (paged rows: per tile, from the tile's description)
+            const uint32_t koff = PAGED ? 0u : (uint32_t)((reinterpret_cast<uintptr_t>(p.k_rows + (size_t)seg.b * p.k_sb + (size_t)hk * p.k_sh) + (uintptr_t)(uint32_t)key0 * krb) & 15u);
+            const uint32_t voff = PAGED ? 0u : (uint32_t)((reinterpret_cast<uintptr_t>(p.v_rows + (size_t)seg.b * p.v_sb + (size_t)hk * p.v_sh) + (uintptr_t)(uint32_t)key0 * vrb) & 15u);
+            uint32_t kt_off = koff + k_lane, vt_off = k_stage_bytes + voff + v_lane;
+            uint32_t kr_off = koff + lane * krb, vr_off = k_stage_bytes + voff + lane * vrb;
             for (int n = 0; n < n_t; ++n, key0 += WK) {
                 if (!stage_wait(c_bar, par)) {
                     // the copy never landed: give up on the keys (the outputs are void, the status says so), stop
@@ -1537,8 +1667,22 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                     break;
                 }
                 const uint32_t st_s = c_st;
-                const int nkeys = min(WK, col.hi - key0);
-                if (nkeys < WK) clear_stale_rows(st_s + koff, st_s + k_stage_bytes + voff, nkeys, krb, vrb, lane);
+                int nkeys = min(WK, col.hi - key0);
+                uint32_t tk_off = koff, tv_off = voff;
+                if constexpr (PAGED) {
+                    // the tile as the copy side described it
+                    uint32_t dk, dv, d0, dn;
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(dk), "=r"(dv), "=r"(d0), "=r"(dn) : "r"(wdesc_s + 16u * (uint32_t)c_stage));
+                    tk_off = dk;
+                    tv_off = dv;
+                    key0 = (int)d0;
+                    nkeys = (int)dn;
+                    kt_off = dk + k_lane;
+                    vt_off = k_stage_bytes + dv + v_lane;
+                    kr_off = dk + lane * krb;
+                    vr_off = k_stage_bytes + dv + lane * vrb;
+                }
+                if (nkeys < WK) clear_stale_rows(st_s + tk_off, st_s + k_stage_bytes + tv_off, nkeys, krb, vrb, lane);
                 // ---- per-key scalars of the tile, lane = key
                 tile_meta<KM, VM, HD>(st_s + kr_off, st_s + vr_off, meta_s, vmeta_s, vsc_s, lane);
                 // ---- scores of the 32 keys: sr[u][2 k + e] = key 16 u + g + 8 k, row 2c + e
@@ -1564,7 +1708,7 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                 // bulk copy of the next tile into it
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (cs.left > 0) cs.tile(wk, c_st, c_bar, krb, vrb, k_stage_bytes, sh.x_end);
+                if (cs.left > 0) copy_tile(c_st, c_bar, wdesc_s + 16u * (uint32_t)c_stage);
                 c_st += stage_bytes;
                 c_bar += 8;
                 if (++c_stage == NS) {

@@ -8,9 +8,9 @@
 
 namespace b200 {
 
-template <int KM, int VM, int HD, bool NAT>
+template <int KM, int VM, int HD, bool NAT, bool PAGED>
 int launch_decode(const DecodeParams &p, dim3 grid, size_t smem, cudaStream_t stream) {
-    auto kern = tq_decode_kernel<KM, VM, HD, NAT>;
+    auto kern = tq_decode_kernel<KM, VM, HD, NAT, PAGED>;
     static thread_local size_t configured[16] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -39,9 +39,9 @@ int launch_decode(const DecodeParams &p, dim3 grid, size_t smem, cudaStream_t st
 }
 
 #define INST(VM)                                                                                       \
-    template int launch_decode<B200_KM, VM, 64, false>(const DecodeParams &, dim3, size_t, cudaStream_t);  \
-    template int launch_decode<B200_KM, VM, 128, false>(const DecodeParams &, dim3, size_t, cudaStream_t); \
-    template int launch_decode<B200_KM, VM, 256, false>(const DecodeParams &, dim3, size_t, cudaStream_t);
+    template int launch_decode<B200_KM, VM, 64, false, false>(const DecodeParams &, dim3, size_t, cudaStream_t);  \
+    template int launch_decode<B200_KM, VM, 128, false, false>(const DecodeParams &, dim3, size_t, cudaStream_t); \
+    template int launch_decode<B200_KM, VM, 256, false, false>(const DecodeParams &, dim3, size_t, cudaStream_t);
 
 template <int KM, int VM, int HD, bool NAT>
 int launch_decode_pair(const DecodeParams &p, dim3 grid, size_t smem, cudaStream_t stream) {
@@ -94,6 +94,10 @@ INST_PAIR(B200_TURBO_MSE)
 #endif
 #endif
 // rows packed back to back, keys and values in the same format, head dim 128: row strides as compile-time constants
-template int launch_decode<B200_KM, B200_KM, 128, true>(const DecodeParams &, dim3, size_t, cudaStream_t);
+template int launch_decode<B200_KM, B200_KM, 128, true, false>(const DecodeParams &, dim3, size_t, cudaStream_t);
+// rows in the blocks of a page table, read where they are: keys and values in the same format
+template int launch_decode<B200_KM, B200_KM, 64, false, true>(const DecodeParams &, dim3, size_t, cudaStream_t);
+template int launch_decode<B200_KM, B200_KM, 128, false, true>(const DecodeParams &, dim3, size_t, cudaStream_t);
+template int launch_decode<B200_KM, B200_KM, 256, false, true>(const DecodeParams &, dim3, size_t, cudaStream_t);
 
 }  // namespace b200

@@ -552,7 +552,7 @@ static void fastdiv_init(uint32_t d, uint32_t &mul, uint32_t &shr) {
 
 // rows of 128 block-scaled elements whose source rows can be read as 16-byte vectors
 static bool rows128_takes(const QuantParams &p, int sides) {
-    static const bool off = getenv("B200_QUANT_GENERIC") != nullptr;
+    static const bool off = diag_env("B200_QUANT_GENERIC") != nullptr;
     if (off || p.d != 128 || (uint64_t)p.nb * p.nh * p.nt >= 0x7fffff00ull) return false;
     const uint64_t vec = p.src_dtype == B200_F32 ? 3 : 7;  // elements per 16 bytes - 1
     for (int s = 0; s < sides; ++s) {

@@ -388,70 +388,92 @@ class KvBlockRef:
     rows: int
 
 
-def attention_packed_blocks(q: torch.Tensor, blocks, kq: TurboQuantizer, vq: TurboQuantizer, cfg: FlashAttnConfig, in_place: bool = False) -> torch.Tensor:
+class PackedBlocksAttention:
+    """A prepared `attention_packed_blocks` call: the block table is built and copied to the device once, `run()` only
+    launches (capturable in a CUDA graph after one warm-up call). The tensors given here are read / written by every
+    `run()`; keep them alive. Arguments as `attention_packed_blocks`."""
+
+    def __init__(self, q: torch.Tensor, blocks, kq: TurboQuantizer, vq: TurboQuantizer, cfg: FlashAttnConfig, in_place: bool = False,
+                 kv_len: Optional[torch.Tensor] = None, after_prev: bool = False, out: Optional[torch.Tensor] = None):
+        _need_cuda(q, "q")
+        if len(blocks) == 0:
+            raise ValueError("turbo-quant blocks: no blocks")
+        b, hq, lq, d = q.shape
+        hkv = blocks[0].k.shape[1]
+        kw, vw = blocks[0].k.shape[3], blocks[0].v.shape[3]
+        if kw != kq.row_words() or vw != vq.row_words() or d != kq.dim or d != vq.dim:
+            raise ValueError(f"turbo-quant blocks: rows of {kw} / {vw} words and head dim {d} do not match the quantizers "
+                             f"({kq.row_words()} / {vq.row_words()} words, dim {kq.dim})")
+        table = np.zeros(len(blocks), dtype=np.dtype([("k", "<u8"), ("v", "<u8"), ("rows", "<u4"), ("k_cap", "<u4"), ("v_cap", "<u4"), ("pad", "<u4")]))
+        lk = 0
+        for n, blk in enumerate(blocks):
+            for t, w, what in ((blk.k, kw, "k"), (blk.v, vw, "v")):
+                # paged_block_layout (flash_attn.rs:618-646): contiguous rows, head stride = whole rows, batch stride = hkv heads
+                if t.dtype != torch.int32 or t.dim() != 4 or t.shape[0] != b or t.shape[1] != hkv or t.shape[3] != w or not t.is_contiguous():
+                    raise ValueError(f"turbo-quant blocks: block {n} ({what}) must be a contiguous int32 ({b}, {hkv}, capacity, {w}) tensor")
+                if t.device != q.device:
+                    raise ValueError("turbo-quant blocks: blocks live on another device")
+            if not 0 <= blk.rows <= min(blk.k.shape[2], blk.v.shape[2]):
+                raise ValueError(f"turbo-quant blocks: block {n} holds {blk.rows} rows, capacity {blk.k.shape[2]} / {blk.v.shape[2]}")
+            table[n] = (blk.k.data_ptr(), blk.v.data_ptr(), blk.rows, blk.k.shape[2], blk.v.shape[2], 0)
+            lk += blk.rows
+        if lk == 0:
+            raise ValueError("turbo-quant blocks: no valid rows")
+        pages = torch.from_numpy(table.view(np.uint8)).to(q.device)
+        if q.stride(3) != 1:
+            q = q.contiguous()
+        if out is None:
+            out = torch.empty((b, hq, lq, d), dtype=q.dtype, device=q.device)
+        wl, wr = cfg.window_i32()
+        alibi, abs_ = None, 0
+        if cfg.alibi_slopes is not None:
+            alibi = cfg.alibi_slopes.to(device=q.device, dtype=torch.float32).contiguous()
+            if alibi.shape not in ((hq,), (b, hq)):
+                raise ValueError(f"flash-attn: alibi slopes must be ({hq}) or ({b}, {hq}), got {tuple(alibi.shape)}")
+            abs_ = hq if alibi.dim() == 2 else 0
+        args = A.TqAttnArgs()
+        args.q, args.out = q.data_ptr(), out.data_ptr()
+        args.q_dtype, args.out_dtype = _dtype_id(q), _dtype_id(out)
+        args.q_strides, args.out_strides = A.u64x3(*q.stride()[:3]), A.u64x3(*out.stride()[:3])
+        args.k_rows = args.v_rows = None
+        args.k_strides, args.v_strides = A.u64x3(0, 0, kw), A.u64x3(0, 0, vw)  # only the row stride is common to the blocks
+        args.pages, args.n_pages = pages.data_ptr(), len(blocks)
+        args.kv_len_dev = kv_len.data_ptr() if kv_len is not None else None
+        args.flags = A.TQ_AFTER_PREV if after_prev else 0
+        args.b, args.lq, args.lk, args.hq, args.hkv, args.d = b, lq, lk, hq, hkv, d
+        args.kq, args.vq = kq.side(), vq.side()
+        args.scale, args.softcap = cfg.softmax_scale, cfg.softcap or 0.0
+        args.wl, args.wr = wl, wr
+        args.alibi, args.alibi_bstride = (alibi.data_ptr() if alibi is not None else None), abs_
+        args.workspace, args.workspace_bytes, args.status = None, 0, None
+        # with the workspace the library asks for, the tensor-core kernel walks the table (or the blocks are compacted
+        # into the workspace first); `in_place=True` keeps the general kernel that reads the blocks where they are
+        need = 16 if in_place else int(A.lib().b200_tq_attention_workspace_bytes(C.byref(args)))
+        if need == 0:
+            A.check(A.lib().b200_tq_attention(C.byref(args), _stream(q.device)))  # raises with the library's reason
+        ws = _workspace(q.device, need)
+        args.workspace, args.workspace_bytes = ws.data_ptr(), need
+        self.args, self.out, self.device = args, out, q.device
+        self._keep = (q, blocks, pages, kv_len, kq, vq, alibi, ws)
+        self._ref = C.byref(args)
+
+    def run(self) -> torch.Tensor:
+        rc = A.lib().b200_tq_attention(self._ref, torch.cuda.current_stream(self.device).cuda_stream)
+        if rc:
+            A.check(rc)
+        return self.out
+
+
+def attention_packed_blocks(q: torch.Tensor, blocks, kq: TurboQuantizer, vq: TurboQuantizer, cfg: FlashAttnConfig, in_place: bool = False,
+                            kv_len: Optional[torch.Tensor] = None, after_prev: bool = False) -> torch.Tensor:
     """Attention of `q: (batch, q_heads, seq_q, head_dim)` over packed rows that live in paged cache blocks, given as
     a block table in device memory (candle-nn/src/turbo_quant.rs:1074-1114; no limit of 128 blocks). The keys are the
-    valid rows of the blocks, one block after the other; masks are bottom-right aligned over them. Formats and head
-    dims of the tensor-core kernel: the blocks are compacted into the workspace by one copy kernel and that kernel
-    runs; everything else, and `in_place=True`: the general kernel reads the blocks where they are."""
-    _need_cuda(q, "q")
-    if len(blocks) == 0:
-        raise ValueError("turbo-quant blocks: no blocks")
-    b, hq, lq, d = q.shape
-    hkv = blocks[0].k.shape[1]
-    kw, vw = blocks[0].k.shape[3], blocks[0].v.shape[3]
-    if kw != kq.row_words() or vw != vq.row_words() or d != kq.dim or d != vq.dim:
-        raise ValueError(f"turbo-quant blocks: rows of {kw} / {vw} words and head dim {d} do not match the quantizers "
-                         f"({kq.row_words()} / {vq.row_words()} words, dim {kq.dim})")
-    table = np.zeros(len(blocks), dtype=np.dtype([("k", "<u8"), ("v", "<u8"), ("rows", "<u4"), ("k_cap", "<u4"), ("v_cap", "<u4"), ("pad", "<u4")]))
-    lk = 0
-    for n, blk in enumerate(blocks):
-        for t, w, what in ((blk.k, kw, "k"), (blk.v, vw, "v")):
-            # paged_block_layout (flash_attn.rs:618-646): contiguous rows, head stride = whole rows, batch stride = hkv heads
-            if t.dtype != torch.int32 or t.dim() != 4 or t.shape[0] != b or t.shape[1] != hkv or t.shape[3] != w or not t.is_contiguous():
-                raise ValueError(f"turbo-quant blocks: block {n} ({what}) must be a contiguous int32 ({b}, {hkv}, capacity, {w}) tensor")
-            if t.device != q.device:
-                raise ValueError("turbo-quant blocks: blocks live on another device")
-        if not 0 <= blk.rows <= min(blk.k.shape[2], blk.v.shape[2]):
-            raise ValueError(f"turbo-quant blocks: block {n} holds {blk.rows} rows, capacity {blk.k.shape[2]} / {blk.v.shape[2]}")
-        table[n] = (blk.k.data_ptr(), blk.v.data_ptr(), blk.rows, blk.k.shape[2], blk.v.shape[2], 0)
-        lk += blk.rows
-    if lk == 0:
-        raise ValueError("turbo-quant blocks: no valid rows")
-    pages = torch.from_numpy(table.view(np.uint8)).to(q.device)
-    if q.stride(3) != 1:
-        q = q.contiguous()
-    out = torch.empty((b, hq, lq, d), dtype=q.dtype, device=q.device)
-    wl, wr = cfg.window_i32()
-    alibi, abs_ = None, 0
-    if cfg.alibi_slopes is not None:
-        alibi = cfg.alibi_slopes.to(device=q.device, dtype=torch.float32).contiguous()
-        if alibi.shape not in ((hq,), (b, hq)):
-            raise ValueError(f"flash-attn: alibi slopes must be ({hq}) or ({b}, {hq}), got {tuple(alibi.shape)}")
-        abs_ = hq if alibi.dim() == 2 else 0
-    args = A.TqAttnArgs()
-    args.q, args.out = q.data_ptr(), out.data_ptr()
-    args.q_dtype = args.out_dtype = _dtype_id(q)
-    args.q_strides, args.out_strides = A.u64x3(*q.stride()[:3]), A.u64x3(*out.stride()[:3])
-    args.k_rows = args.v_rows = None
-    args.k_strides, args.v_strides = A.u64x3(0, 0, kw), A.u64x3(0, 0, vw)  # only the row stride is common to the blocks
-    args.pages, args.n_pages = pages.data_ptr(), len(blocks)
-    args.kv_len_dev = None
-    args.b, args.lq, args.lk, args.hq, args.hkv, args.d = b, lq, lk, hq, hkv, d
-    args.kq, args.vq = kq.side(), vq.side()
-    args.scale, args.softcap = cfg.softmax_scale, cfg.softcap or 0.0
-    args.wl, args.wr = wl, wr
-    args.alibi, args.alibi_bstride = (alibi.data_ptr() if alibi is not None else None), abs_
-    args.workspace, args.workspace_bytes, args.status = None, 0, None
-    # with the workspace the library asks for, the blocks are compacted into it and the tensor-core kernel runs;
-    # `in_place=True` keeps the general kernel that reads the blocks where they are
-    need = 16 if in_place else int(A.lib().b200_tq_attention_workspace_bytes(C.byref(args)))
-    if need == 0:
-        A.check(A.lib().b200_tq_attention(C.byref(args), _stream(q.device)))  # raises with the library's reason
-    ws = _workspace(q.device, need)
-    args.workspace, args.workspace_bytes = ws.data_ptr(), need
-    A.check(A.lib().b200_tq_attention(C.byref(args), _stream(q.device)))
-    return out
+    valid rows of the blocks, one block after the other; masks are bottom-right aligned over them. Keys and values in
+    one format of the tensor-core kernel: that kernel walks the block table itself (tiles end where blocks end). Other
+    format pairs of that kernel: the blocks are compacted into the workspace by one copy kernel first; everything else,
+    and `in_place=True`: the general kernel reads the blocks where they are. `kv_len` (int32 device tensor, one entry
+    per batch entry; only where the kernel walks the table): sequence b attends to the first kv_len[b] keys."""
+    return PackedBlocksAttention(q, blocks, kq, vq, cfg, in_place, kv_len, after_prev).run()
 
 
 class TurboKvCache:

@@ -477,8 +477,12 @@ def test_full_size_properties_config2(P, oracle):
     lens = (512 + oracle.u64s(2002, b) % np.uint64(7681)).astype(np.int32)
     cap = int(lens.max())
     g = torch.Generator(device="cuda:0").manual_seed(5)
-    k = torch.randn((b, hkv, cap, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
-    v = torch.randn((b, hkv, cap, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    # the configuration's value distribution: N(0, 1) with 1 % of the (kv head, channel) pairs scaled by 8
+    chan = torch.ones(hkv * d, device="cuda:0", dtype=torch.bfloat16)
+    chan[torch.from_numpy(np.random.default_rng(2003).choice(hkv * d, size=(hkv * d + 99) // 100, replace=False)).to("cuda:0")] = 8
+    chan = chan.view(1, hkv, 1, d)
+    k = torch.randn((b, hkv, cap, d), generator=g, device="cuda:0", dtype=torch.bfloat16) * chan
+    v = torch.randn((b, hkv, cap, d), generator=g, device="cuda:0", dtype=torch.bfloat16) * chan
     q = torch.randn((b, hq, 1, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
     cache = P.TurboKvCache(fmt(P, 2), fmt(P, 2), d, "none", 42, cap)
     cache.append(k, v)
@@ -504,8 +508,13 @@ def test_full_size_properties_config2(P, oracle):
         cache.v[bi, :, int(lens[bi]):] = 0x7FC07FC0
     out3 = P.attention_packed(q, cache.k, cache.v, kvl, cache.kq, cache.vq, cfg)
     assert torch.equal(out3, out)
-    # 4. linearity in V: attention over 2 * V rows (scale word doubled) is twice the output
+    # 4. linearity in V: every E8M0 block scale of the value rows one step up (word 16 of a row holds the four scale
+    # bytes) doubles every value exactly, so the outputs double (to the rounding of the weights, whose running maxima
+    # move by one)
     assert torch.isfinite(out).all()
+    cache.v[:, :, :, 16] += 0x01010101
+    out4 = P.attention_packed(q, cache.k, cache.v, kvl, cache.kq, cache.vq, cfg)
+    assert_close(out4.float().cpu().numpy(), 2.0 * out.float().cpu().numpy(), atol=2e-3, rtol=8e-3, what="linearity in V")
 
 
 def _fill_cache(P, cache, b, hkv, ctx, d, dtype, seed):
@@ -732,3 +741,72 @@ def test_paged_blocks_equal_the_concatenated_rows(P, oracle, kf, vf):
             assert_close(got, want, what=f"paged wl={wl} wr={wr} in_place={in_place}")
     with pytest.raises(ValueError, match="no blocks"):
         P.attention_packed_blocks(to_dev(q), [], kq, vq, c)
+    # B200_TQ_AFTER_PREV on a paged call: the kernels that prepare the table run right before the attention, which
+    # must not start as their programmatic dependent; the rows are those of the plain call
+    c = P.FlashAttnConfig(d ** -0.5).causal()
+    plain = P.attention_packed_blocks(to_dev(q), blocks, kq, vq, c)
+    for _ in range(3):
+        assert torch.equal(P.attention_packed_blocks(to_dev(q), blocks, kq, vq, c, after_prev=True), plain)
+
+
+@pytest.mark.parametrize("f,d", [((2, 4), 128), ((4, 4), 128), ((0, 4), 64), ((5, 4), 256), ((3, 4), 128)])
+def test_paged_rows_read_where_they_are(P, oracle, f, d):
+    """The tensor-core kernel walking the block table: blocks of odd fill levels (tiles end where blocks end, so most
+    blocks end in a short tile), an empty block, a full one whose last row is the last row of its allocation, a batch
+    with per-sequence lengths (one of them zero, one ending inside the first block, one taking every key), windows.
+    Against the oracle on the concatenated rows with the same lengths."""
+    b, hq, hkv, lq = 5, 8, 2, 1
+    kq, vq = P.TurboQuantizer(fmt(P, *f), d, "none", 42), P.TurboQuantizer(fmt(P, *f), d, "none", 44)
+    caps, fills = [40, 64, 8, 32, 200, 33], [37, 64, 0, 32, 131, 1]
+    blocks, kcat, vcat = [], [], []
+    g = torch.Generator(device="cuda:0").manual_seed(d + f[0])
+    for cap, rows in zip(caps, fills):
+        kb = kq.quantize_rows(torch.randn((b * hkv * cap, d), generator=g, device="cuda:0")).view(b, hkv, cap, -1).contiguous()
+        vb = vq.quantize_rows(torch.randn((b * hkv * cap, d), generator=g, device="cuda:0")).view(b, hkv, cap, -1).contiguous()
+        blocks.append(P.KvBlockRef(kb, vb, rows))
+        kcat.append(words(kb)[:, :, :rows])
+        vcat.append(words(vb)[:, :, :rows])
+    kd, vd = np.ascontiguousarray(np.concatenate(kcat, axis=2)), np.ascontiguousarray(np.concatenate(vcat, axis=2))
+    lk = sum(fills)
+    tab = np.zeros(64, np.float32)
+    tab[:32] = tab[32:] = MG.tab_for(f[0], f[1], d)
+    q = torch.randn((b, hq, lq, d), generator=g, device="cuda:0")
+    lens = np.array([lk, 0, 20, 102, 265], np.int32)
+    for wl, wr in ((-1, 0), (70, 0)):
+        c = P.FlashAttnConfig(d ** -0.5)
+        c.window_size_left = None if wl < 0 else wl
+        c.window_size_right = None if wr < 0 else wr
+        want = oracle.tq_attention(q.cpu().numpy(), kd, vd, lk, f, f, d ** -0.5, tab, wl=wl, wr=wr)
+        got = P.attention_packed_blocks(q, blocks, kq, vq, c).cpu().numpy()
+        assert_close(got, want, what=f"paged walk wl={wl}")
+        want = oracle.tq_attention(q.cpu().numpy(), kd, vd, lk, f, f, d ** -0.5, tab, kv_len=lens, wl=wl, wr=wr)
+        got = P.attention_packed_blocks(q, blocks, kq, vq, c, kv_len=torch.from_numpy(lens).to("cuda:0")).cpu().numpy()
+        assert np.all(got[1] == 0)
+        assert_close(got, want, what=f"ragged paged walk wl={wl}")
+    # several query tokens per sequence (chunked prefill over a paged cache)
+    q3 = torch.randn((b, hq, 3, d), generator=g, device="cuda:0")
+    c = P.FlashAttnConfig(d ** -0.5).causal()
+    want = oracle.tq_attention(q3.cpu().numpy(), kd, vd, lk, f, f, d ** -0.5, tab, wr=0)
+    assert_close(P.attention_packed_blocks(q3, blocks, kq, vq, c).cpu().numpy(), want, what="paged walk lq=3")
+
+
+def test_paged_rows_with_whole_tiles_give_the_bits_of_the_dense_call(P, oracle):
+    """Blocks whose fill levels are multiples of the tile (512 rows): the walk over the table cuts the keys into the
+    same tiles as the call over the concatenated rows, so the outputs are the same bits."""
+    b, hq, hkv, d, nblk, rows = 16, 32, 8, 128, 8, 512
+    f = fmt(P, 2, 4)
+    kq, vq = P.TurboQuantizer(f, d, "none", 42), P.TurboQuantizer(f, d, "none", 44)
+    g = torch.Generator(device="cuda:0").manual_seed(77)
+    blocks = []
+    for _ in range(nblk):
+        kb = kq.quantize_rows(torch.randn((b * hkv * rows, d), generator=g, device="cuda:0", dtype=torch.bfloat16)).view(b, hkv, rows, -1)
+        vb = vq.quantize_rows(torch.randn((b * hkv * rows, d), generator=g, device="cuda:0", dtype=torch.bfloat16)).view(b, hkv, rows, -1)
+        blocks.append(P.KvBlockRef(kb, vb, rows))
+    q = torch.randn((b, hq, 1, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+    cfg = P.FlashAttnConfig(d ** -0.5).causal()
+    dense_k = torch.cat([blk.k for blk in blocks], dim=2).contiguous()
+    dense_v = torch.cat([blk.v for blk in blocks], dim=2).contiguous()
+    want = P.attention_packed(q, dense_k, dense_v, nblk * rows, kq, vq, cfg)
+    got = P.attention_packed_blocks(q, blocks, kq, vq, cfg)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)

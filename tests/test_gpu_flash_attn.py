@@ -273,6 +273,49 @@ def test_prefill_append_gives_both_reference_results(P, oracle, rotation):
         assert not got[:, :, :pos].any() and not got[:, :, pos + s:].any()
 
 
+def test_prefill_append_from_two_host_threads(P, oracle):
+    """b200_fa_prefill_append is re-entrant: two host threads, each on its own stream and its own caches, call it side
+    by side many times; every call's output and cache rows are those of the same call made alone."""
+    import threading
+    b, s, hq, hkv, d = 1, 1024, 8, 2, 128
+    nv = fmt(P, 3)
+    cfg = P.FlashAttnConfig(d ** -0.5).causal()
+    work = []
+    for t in range(2):
+        g = torch.Generator(device="cuda:0").manual_seed(50 + t)
+        q = torch.randn((b, s, hq, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+        k = torch.randn((b, s, hkv, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+        v = torch.randn((b, s, hkv, d), generator=g, device="cuda:0", dtype=torch.bfloat16)
+        kq, vq = P.TurboQuantizer(nv, d, "none", 42), P.TurboQuantizer(nv, d, "none", 44)
+        kc = torch.zeros((b, hkv, s, kq.row_words()), dtype=torch.int32, device="cuda:0")
+        vc = torch.zeros_like(kc)
+        want = P.flash_attn.prefill_append(q, k, v, cfg, kc, vc, kq, vq, 0).clone()
+        torch.cuda.synchronize()
+        work.append(dict(q=q, k=k, v=v, kq=kq, vq=vq, kc=kc, vc=vc, want=want, want_k=kc.clone(), want_v=vc.clone(),
+                         stream=torch.cuda.Stream("cuda:0"), bad=[]))
+    torch.cuda.synchronize()
+    start = threading.Barrier(2)
+
+    def run(w):
+        with torch.cuda.stream(w["stream"]):
+            start.wait()
+            for it in range(40):
+                w["kc"].zero_()
+                w["vc"].zero_()
+                out = P.flash_attn.prefill_append(w["q"], w["k"], w["v"], cfg, w["kc"], w["vc"], w["kq"], w["vq"], 0)
+                w["stream"].synchronize()
+                if not (torch.equal(out, w["want"]) and torch.equal(w["kc"], w["want_k"]) and torch.equal(w["vc"], w["want_v"])):
+                    w["bad"].append(it)
+
+    threads = [threading.Thread(target=run, args=(w,)) for w in work]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not work[0]["bad"] and not work[1]["bad"], (work[0]["bad"], work[1]["bad"])
+    assert P._abi.lib().b200_device_wait_status() == 0
+
+
 def test_argument_errors(P):
     A = P._abi
     F = P.flash_attn
