@@ -42,7 +42,18 @@ class TqQuantArgs(C.Structure):
 
 class TqDequantArgs(C.Structure):
     _fields_ = [("data", C.c_void_p), ("out", C.c_void_p), ("tab", C.c_void_p), ("rows", C.c_uint64),
-                ("dim", C.c_uint32), ("data_stride", C.c_uint64), ("mode", C.c_int32), ("bits", C.c_int32)]
+                ("dim", C.c_uint32), ("data_stride", C.c_uint64), ("mode", C.c_int32), ("bits", C.c_int32), ("zs", C.c_void_p)]
+
+
+class TqResidArgs(C.Structure):
+    _fields_ = [("src", C.c_void_p), ("data", C.c_void_p), ("tab", C.c_void_p), ("resid", C.c_void_p), ("rows", C.c_uint64),
+                ("dim", C.c_uint32), ("src_stride", C.c_uint64), ("data_stride", C.c_uint64), ("src_dtype", C.c_int32),
+                ("bits", C.c_int32)]
+
+
+class TqSignsArgs(C.Structure):
+    _fields_ = [("in_", C.c_void_p), ("proj", C.c_void_p), ("resid", C.c_void_p), ("out", C.c_void_p), ("rows", C.c_uint64),
+                ("dim", C.c_uint32), ("bits", C.c_int32)]
 
 
 class KvAppendArgs(C.Structure):
@@ -92,7 +103,8 @@ class FaArgs(C.Structure):
 
 # every symbol that include/b200attn.h declares
 SYMBOLS = [
-    "b200_row_layout", "b200_codebook", "b200_hadamard_signs", "b200_row_group", "b200_split_count_grouped",
+    "b200_row_layout", "b200_codebook", "b200_hadamard_signs", "b200_qjl_matrix", "b200_row_group", "b200_split_count_grouped",
+    "b200_tq_residual", "b200_tq_signs",
     "b200_describe", "b200_last_error", "b200_tq_rotate", "b200_tq_quantize", "b200_tq_dequantize", "b200_kv_append",
     "b200_tq_attention_workspace_bytes", "b200_tq_attention", "b200_tq_attention_static", "b200_tq_attention_gather",
     "b200_flash_attn_workspace_bytes",
@@ -120,6 +132,9 @@ def lib():
         l.b200_row_layout.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(RowLayout)]
         l.b200_codebook.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_float)]
         l.b200_hadamard_signs.argtypes = [C.c_int, C.c_uint64, C.POINTER(C.c_float)]
+        l.b200_qjl_matrix.argtypes = [C.c_int, C.c_uint64, C.POINTER(C.c_float)]
+        l.b200_tq_residual.argtypes = [C.POINTER(TqResidArgs), C.c_void_p]
+        l.b200_tq_signs.argtypes = [C.POINTER(TqSignsArgs), C.c_void_p]
         l.b200_row_group.argtypes = [C.c_int, C.c_int]
         l.b200_split_count_grouped.argtypes = [C.c_int64, C.c_int, C.c_int64, C.c_int]
         l.b200_describe.argtypes = [C.c_int, C.POINTER(Profile)]

@@ -137,6 +137,27 @@ extern "C" int b200_hadamard_signs(int dim, uint64_t seed, float *signs) {
     return B200_OK;
 }
 
+// candle-core/src/accel/turbo.rs:148-176,236-239: row-major dim x dim standard normals (Box-Muller in f64 over
+// SplitMix64(seed + 1 ^ "QJL_SKET")), the projection S of the prod format's sketch
+extern "C" int b200_qjl_matrix(int dim, uint64_t seed, float *s_out) {
+    if (!s_out) return set_error(B200_ERR_BAD_ARG, "qjl_matrix: null output");
+    if (dim <= 0 || dim > 1024) return set_error(B200_ERR_BAD_ARG, "qjl_matrix: dim %d outside 1..1024", dim);
+    uint64_t s = (seed + 1) ^ 0x514a4c5f534b4554ull;
+    auto next_f64 = [&]() {
+        s += 0x9e3779b97f4a7c15ull;
+        uint64_t z = s;
+        z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+        z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+        z ^= z >> 31;
+        return ((double)(z >> 11) + 0.5) / 9007199254740992.0;
+    };
+    for (size_t i = 0; i < (size_t)dim * dim; ++i) {
+        const double u1 = next_f64(), u2 = next_f64();
+        s_out[i] = (float)(sqrt(-2.0 * log(u1)) * cos(2.0 * 3.14159265358979323846 * u2));
+    }
+    return B200_OK;
+}
+
 // candle-core/src/accel/attention.rs:586-592
 extern "C" int b200_row_group(int hq, int hkv) {
     const int group = hq / (hkv > 0 ? hkv : 1);

@@ -315,6 +315,9 @@ int decode_wait_status() {
 __global__ void __launch_bounds__(256) tq_page_prefix_kernel(const B200Page *__restrict__ pages, uint32_t n_pages, uint32_t *__restrict__ pg_keys,
                                                               uint32_t *__restrict__ pg_tiles) {
     __shared__ uint32_t sk[256], st[256];
+    // the attention that follows is launched as this kernel's programmatic dependent: its blocks may take their places
+    // now (they wait for this kernel's completion before they read the sums)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     uint32_t base_k = 0, base_t = 0;
     for (uint32_t start = 0; start < n_pages; start += 256) {
         const uint32_t i = start + threadIdx.x;
@@ -508,6 +511,7 @@ extern "C" int b200_tq_attention(const B200TqAttnArgs *a, b200_stream_t stream_)
                 if (rc) return rc;
                 pl.p.pg_keys = pg_keys;
                 pl.p.pg_tiles = pg_tiles;
+                pl.p.after_prev = 1;  // launched as the prefix kernel's programmatic dependent (the paged kernel waits at its start)
                 return run_plan(a, pl, ws + pre, a->workspace_bytes - pre, (cudaStream_t)stream_);
             }
         }

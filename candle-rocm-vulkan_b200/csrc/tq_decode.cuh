@@ -1585,9 +1585,12 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
     // a programmatic dependent); it waits for this grid's completion itself before it touches memory
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
+    // paged rows: the kernel that wrote the table's prefix sums is the stream's previous kernel, and this grid was
+    // launched as its programmatic dependent (its launch latency is hidden): the sums are read from here on
+    if constexpr (PAGED) asm volatile("griddepcontrol.wait;" ::: "memory");
     const Share sh = worker_share(p, ny, wid, nw_grid, lane);
     Worker wk(p, lane, wid, nw_grid, ny, sh);
-    if (!p.prefetch) wk.prev_done();
+    if (PAGED || !p.prefetch) wk.prev_done();
     if (!sh.has_work) {
         wk.zero_columns<HD>(false);
         return;

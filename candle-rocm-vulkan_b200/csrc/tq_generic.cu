@@ -25,7 +25,7 @@ __device__ __forceinline__ float tq_elem(const uint32_t *r, uint32_t j, const Ge
     if (sh + s.bits > 32u) c |= r[wi + 1] << (32u - sh);
     c &= (1u << s.bits) - 1u;
     const uint32_t *aux = r + s.code_words;
-    if (s.mode == B200_TURBO_MSE) return tab[c];
+    if (s.mode <= B200_TURBO_PROD) return tab[c];
     if (s.mode == B200_MXFP4) return __fmul_rn(fp4_to_f(c), e8m0_to_f((aux[j >> 7] >> (((j >> 5) & 3u) * 8u)) & 0xffu));
     if (s.mode == B200_NVFP4) return __fmul_rn(fp4_to_f(c), e4m3_to_f((aux[j >> 6] >> (((j >> 4) & 3u) * 8u)) & 0xffu));
     if (s.mode == B200_MXFP8) return __fmul_rn(e4m3_to_f(c), e8m0_to_f((aux[j >> 7] >> (((j >> 5) & 3u) * 8u)) & 0xffu));
@@ -35,6 +35,7 @@ __device__ __forceinline__ float tq_elem(const uint32_t *r, uint32_t j, const Ge
 __global__ void __launch_bounds__(GW * 32) tq_generic_kernel(const DecodeParams p, const GenericSide ks, const GenericSide vs,
                                                              const B200Page *__restrict__ pages, const uint32_t n_pages) {
     __shared__ float qrow[GMAX * 32];
+    __shared__ float qsrow[GMAX * 32];  // prod keys: S q
     __shared__ float part[GW][GMAX * 32 + 2];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t D = p.d, nk = D / 32;
@@ -52,17 +53,24 @@ __global__ void __launch_bounds__(GW * 32) tq_generic_kernel(const DecodeParams 
     long long lo = p.wl >= 0 ? max(pos - p.wl, 0ll) : 0ll, hi = p.wr >= 0 ? min(pos + p.wr + 1, (long long)lk) : (long long)lk;
     lo = min(lo, (long long)lk);
     hi = max(hi, lo);
-    // query row, rotated like the keys
+    // query row, rotated like the keys (prod keys: the caller's rotated query, followed by S q)
+    const bool prod = ks.mode == B200_TURBO_PROD;
     if (warp == 0) {
-        for (uint32_t k = 0; k < nk; ++k)
+        for (uint32_t k = 0; k < nk; ++k) {
             qrow[lane + 32 * k] = load_elem_rt(p.q, b * p.q_sb + h * p.q_sh + i * p.q_ss + lane + 32 * k, p.q_dtype);
+            qsrow[lane + 32 * k] = prod ? load_elem_rt(p.q, b * p.q_sb + h * p.q_sh + i * p.q_ss + D + lane + 32 * k, p.q_dtype) : 0.0f;
+        }
         __syncwarp();
         if (p.k.rot == B200_ROT_HADAMARD) warp_hadamard(qrow, (int)D, p.k.signs, true, lane);
     }
     __syncthreads();
-    float q[GMAX];
+    float q[GMAX], qs[GMAX];
 #pragma unroll
-    for (int k = 0; k < GMAX; ++k) q[k] = (uint32_t)k < nk ? qrow[lane + 32 * k] * p.scale : 0.0f;
+    for (int k = 0; k < GMAX; ++k) {
+        q[k] = (uint32_t)k < nk ? qrow[lane + 32 * k] * p.scale : 0.0f;
+        // sqrt(pi / 2) / d of the sketch's term folded into S q (candle-core/kernels/turbo_quant_impl.h:268-277)
+        qs[k] = (uint32_t)k < nk ? qsrow[lane + 32 * k] * (p.scale * 1.2533141f / (float)D) : 0.0f;
+    }
     const float slope = p.alibi ? p.alibi[(size_t)b * p.alibi_bs + h] : 0.0f;
     float m = -INFINITY, l = 0.0f, acc[GMAX];
 #pragma unroll
@@ -93,6 +101,14 @@ __global__ void __launch_bounds__(GW * 32) tq_generic_kernel(const DecodeParams 
 #pragma unroll
         for (int k = 0; k < GMAX; ++k)
             if ((uint32_t)k < nk) s = fmaf(tq_elem(kr, lane + 32 * k, ks, p.k.tab), q[k], s);
+        if (prod) {
+            // + rsc1 * signed sum of S q over the key's sign bits (word k of the sketch holds the lane's dims lane + 32 k)
+            float sd = 0.0f;
+#pragma unroll
+            for (int k = 0; k < GMAX; ++k)
+                if ((uint32_t)k < nk) sd += ((kr[ks.code_words + k] >> lane) & 1u) ? qs[k] : -qs[k];
+            s = fmaf(u2f(kr[ks.rsc_off + 1]), sd, s);
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         s *= u2f(kr[ks.rsc_off]);
@@ -154,10 +170,11 @@ int tq_generic_plan(const B200TqAttnArgs *a, DecodeParams &p, GenericSide &ks, G
     bool needed = (a->d != 64 && a->d != 128 && a->d != 256) || a->pages != nullptr;
     for (int s = 0; s < 2; ++s) {
         const B200QuantSide &q = *sides[s];
-        if (q.mode == B200_TURBO_PROD) return 1;
+        if (q.mode == B200_TURBO_PROD && (s == 1 || q.rotation != B200_ROT_NONE)) return 1;  // keys only; the caller rotates and projects the query
+        if (q.mode == B200_TURBO_PROD) needed = true;
         B200RowLayout lay;
         if (b200_row_layout(q.mode, q.bits, (int)a->d, &lay)) return 1;
-        if (q.mode == B200_TURBO_MSE && !q.tab) return 1;
+        if (q.mode <= B200_TURBO_PROD && !q.tab) return 1;
         if (q.rotation == B200_ROT_HADAMARD ? (!q.signs || (a->d & (a->d - 1))) : q.rotation != B200_ROT_NONE) return 1;
         if (q.mode == B200_TURBO_MSE && q.bits != 4) needed = true;
         gs[s]->mode = q.mode;

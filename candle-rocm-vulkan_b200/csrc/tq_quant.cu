@@ -455,7 +455,7 @@ __global__ void __launch_bounds__(Q128_WARPS * 32) quant_rows128_kernel(const Qu
 __global__ void __launch_bounds__(256) dequant_rows_kernel(const uint32_t *__restrict__ data, const float *__restrict__ tab,
                                                           float *__restrict__ out, uint64_t rows, uint32_t D,
                                                           uint64_t stride, uint32_t mode, uint32_t cb,
-                                                          uint32_t code_words, uint32_t rsc_off) {
+                                                          uint32_t code_words, uint32_t rsc_off, float *__restrict__ zs) {
     const uint64_t n = rows * D;
     for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t row = idx / D;
@@ -473,6 +473,69 @@ __global__ void __launch_bounds__(256) dequant_rows_kernel(const uint32_t *__res
         else if (mode == B200_MXFP8) e = __fmul_rn(e4m3_to_f(c), e8m0_to_f((aux[j >> 7] >> (((j >> 5) & 3u) * 8u)) & 0xffu));
         else e = e4m3_to_f(c);
         out[idx] = __fmul_rn(u2f(r[rsc_off]), e);
+        if (zs) {
+            // prod rows: the QJL coefficient of element j (candle-core/kernels/turbo_quant_impl.h:219-222)
+            const float c = __fdiv_rn(__fmul_rn(__fmul_rn(u2f(r[rsc_off]), u2f(r[rsc_off + 1])), 1.2533141f), (float)D);
+            zs[idx] = ((r[code_words + (j >> 5)] >> (j & 31u)) & 1u) ? c : -c;
+        }
+    }
+}
+
+// Residual of the unit vectors to their codebook values (candle-core/kernels/turbo_quant_impl.h:161-177), with that
+// kernel's roundings: inv = 1 / rsc0 (0 for a zero row), u = x * inv, resid = u - centroid, none of them fused.
+template <int DT>
+__global__ void __launch_bounds__(256) resid_rows_kernel(const void *__restrict__ src, const uint32_t *__restrict__ data, const float *__restrict__ tab,
+                                                        float *__restrict__ resid, uint64_t rows, uint32_t D, uint64_t src_stride,
+                                                        uint64_t data_stride, uint32_t cb, uint32_t rsc_off) {
+    const uint64_t n = rows * D;
+    for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t row = idx / D;
+        const uint32_t j = (uint32_t)(idx % D);
+        const uint32_t *r = data + row * data_stride;
+        const float norm = u2f(r[rsc_off]);
+        const float inv = norm > 0.0f ? __fdiv_rn(1.0f, norm) : 0.0f;
+        const float u = __fmul_rn(load_elem<DT>(reinterpret_cast<const char *>(src) + row * src_stride * dtype_size(DT), j), inv);
+        const uint32_t pos = j * cb, wi = pos >> 5, sh = pos & 31u;
+        uint32_t c = r[wi] >> sh;
+        if (sh + cb > 32u) c |= r[wi + 1] << (32u - sh);
+        c &= (1u << cb) - 1u;
+        resid[idx] = __fsub_rn(u, tab[c]);
+    }
+}
+
+// Sign bits of the projected residual and the residual's norm into prod rows (candle-core/kernels/
+// turbo_quant_impl.h:179-206). One warp per row; the sum of squares runs in the order of the reference's 128 lanes
+// (lane t adds j = t, t + 128, ..., then the halving tree), so rsc1 is bit-identical.
+__global__ void __launch_bounds__(128) signs_rows_kernel(const uint32_t *__restrict__ in, const float *__restrict__ proj, const float *__restrict__ resid,
+                                                        uint32_t *__restrict__ out, uint64_t rows, uint32_t D, uint32_t code_words,
+                                                        uint32_t row_words) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t sign_words = (D + 31u) / 32u;
+    for (uint64_t row = (uint64_t)blockIdx.x * 4 + warp; row < rows; row += (uint64_t)gridDim.x * 4) {
+        // reference lane t = (lane + 32 k) mod 128 holds part[k & 3] of this lane
+        float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (uint32_t k = 0; lane + 32u * k < D; ++k) {
+            const float v = resid[row * D + lane + 32u * k];
+            part[k & 3] = __fadd_rn(part[k & 3], __fmul_rn(v, v));
+        }
+        float ss = __fadd_rn(__fadd_rn(part[0], part[2]), __fadd_rn(part[1], part[3]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, o));
+        ss = __shfl_sync(0xffffffffu, ss, 0);
+        const uint32_t *ir = in + row * row_words;
+        uint32_t *orow = out + row * row_words;
+        for (uint32_t w = lane; w < row_words; w += 32) {
+            uint32_t word = ir[w];
+            if (w >= code_words && w < code_words + sign_words) {
+                word = 0;
+                const uint32_t base = (w - code_words) * 32u;
+                for (uint32_t e = 0; e < 32u && base + e < D; ++e)
+                    if (proj[row * D + base + e] >= 0.0f) word |= 1u << e;
+            } else if (w == code_words + sign_words + 1u) {
+                word = f2u(__fsqrt_rn(ss));
+            }
+            orow[w] = word;
+        }
     }
 }
 
@@ -522,8 +585,6 @@ static int fill_side(QuantSideParams &sp, const B200QuantSide &q, uint32_t d) {
     B200RowLayout l;
     const int rc = b200_row_layout(q.mode, q.bits, (int)d, &l);
     if (rc) return rc;
-    if (q.mode == B200_TURBO_PROD)
-        return set_error(B200_ERR_UNSUPPORTED_SHAPE, "turbo prod (QJL) rows are not implemented by the fused quantizer");
     if (q.mode <= B200_TURBO_PROD && !q.tab) return set_error(B200_ERR_BAD_ARG, "turbo formats need the codebook table");
     if (q.rotation == B200_ROT_HADAMARD) {
         if (!q.signs) return set_error(B200_ERR_BAD_ARG, "hadamard rotation needs the sign vector");
@@ -688,9 +749,45 @@ extern "C" int b200_tq_dequantize(const B200TqDequantArgs *a, b200_stream_t stre
     const uint64_t stride = a->data_stride ? a->data_stride : (uint64_t)l.row_words;
     const uint64_t n = a->rows * a->dim;
     const unsigned grid = (unsigned)std::min<uint64_t>((n + 255) / 256, 148ull * 32);
+    if (a->zs && a->mode != B200_TURBO_PROD) return set_error(B200_ERR_BAD_ARG, "tq_dequantize: QJL coefficients exist for prod rows only");
     dequant_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a->data, a->tab, a->out, a->rows, a->dim, stride, a->mode,
-                                                               l.code_bits, l.code_words, l.rsc_offset);
+                                                               l.code_bits, l.code_words, l.rsc_offset, a->zs);
     return check_launch("tq_dequantize");
+}
+
+extern "C" int b200_tq_residual(const B200TqResidArgs *a, b200_stream_t stream) {
+    if (!a) return set_error(B200_ERR_BAD_ARG, "tq_residual: null args");
+    if (a->rows == 0) return B200_OK;
+    if (!a->src || !a->data || !a->tab || !a->resid) return set_error(B200_ERR_BAD_ARG, "tq_residual: null pointer");
+    B200RowLayout l;
+    const int rc = b200_row_layout(B200_TURBO_PROD, a->bits, (int)a->dim, &l);
+    if (rc) return rc;
+    const uint64_t ds = a->data_stride ? a->data_stride : (uint64_t)l.row_words;
+    if (ds < (uint64_t)l.row_words) return set_error(B200_ERR_BAD_ARG, "tq_residual: row stride below the row size");
+    const uint64_t n = a->rows * a->dim;
+    const unsigned grid = (unsigned)std::min<uint64_t>((n + 255) / 256, 148ull * 32);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (a->src_dtype == B200_F32)
+        resid_rows_kernel<B200_F32><<<grid, 256, 0, st>>>(a->src, a->data, a->tab, a->resid, a->rows, a->dim, a->src_stride, ds, l.code_bits, l.rsc_offset);
+    else if (a->src_dtype == B200_F16)
+        resid_rows_kernel<B200_F16><<<grid, 256, 0, st>>>(a->src, a->data, a->tab, a->resid, a->rows, a->dim, a->src_stride, ds, l.code_bits, l.rsc_offset);
+    else if (a->src_dtype == B200_BF16)
+        resid_rows_kernel<B200_BF16><<<grid, 256, 0, st>>>(a->src, a->data, a->tab, a->resid, a->rows, a->dim, a->src_stride, ds, l.code_bits, l.rsc_offset);
+    else
+        return set_error(B200_ERR_BAD_ARG, "tq_residual: source dtype must be f32, f16 or bf16");
+    return check_launch("tq_residual");
+}
+
+extern "C" int b200_tq_signs(const B200TqSignsArgs *a, b200_stream_t stream) {
+    if (!a) return set_error(B200_ERR_BAD_ARG, "tq_signs: null args");
+    if (a->rows == 0) return B200_OK;
+    if (!a->in || !a->proj || !a->resid || !a->out) return set_error(B200_ERR_BAD_ARG, "tq_signs: null pointer");
+    B200RowLayout l;
+    const int rc = b200_row_layout(B200_TURBO_PROD, a->bits, (int)a->dim, &l);
+    if (rc) return rc;
+    const unsigned grid = (unsigned)std::min<uint64_t>((a->rows + 3) / 4, 148ull * 16);
+    signs_rows_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(a->in, a->proj, a->resid, a->out, a->rows, a->dim, l.code_words, l.row_words);
+    return check_launch("tq_signs");
 }
 
 extern "C" int b200_tq_rotate(const float *in, float *out, const float *signs, uint64_t rows, uint32_t dim, int inverse,

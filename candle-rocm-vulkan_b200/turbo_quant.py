@@ -125,8 +125,6 @@ class TurboQuantizer:
     def __init__(self, format: QuantFormat, dim: int, rotation: str = "auto", seed: int = 42, device="cuda"):
         self.format, self.dim, self.device = format, dim, torch.device(device)
         self.layout = A.row_layout(format.mode, format.bits, dim)
-        if format.mode == A.TURBO_PROD:
-            raise A.B200Error(A.ERR_UNSUPPORTED_SHAPE, "turbo prod (QJL) rows are not implemented by the fused kernels")
         pow2 = dim & (dim - 1) == 0
         if rotation == "auto":
             rotation = "hadamard" if pow2 else "none"
@@ -136,8 +134,16 @@ class TurboQuantizer:
         self.seed = seed
         tab = (C.c_float * 32)()
         if format.is_turbo():
-            A.check(A.lib().b200_codebook(dim, format.bits, tab))
+            # prod rows spend one of their bits on the sketch: codes of bits - 1 bits (formats.rs code_bits)
+            A.check(A.lib().b200_codebook(dim, self.layout.code_bits, tab))
         self.tab = torch.tensor(list(tab), dtype=torch.float32, device=self.device)
+        # prod rows: S and S^T of the 1-bit sketch of the residual (turbo_quant.rs:111-118)
+        self.qjl = None
+        if format.mode == A.TURBO_PROD:
+            m = (C.c_float * (dim * dim))()
+            A.check(A.lib().b200_qjl_matrix(dim, seed, m))
+            s_mat = torch.frombuffer(m, dtype=torch.float32).view(dim, dim).to(self.device)
+            self.qjl = (s_mat, s_mat.t().contiguous())
         self.signs = None
         if rotation == "hadamard":
             s = (C.c_float * dim)()
@@ -193,6 +199,18 @@ class TurboQuantizer:
         rows, d = x.shape
         if d != self.dim:
             raise ValueError(f"turbo-quant: expected rows of {self.dim} values, got {d}")
+        if self.qjl is not None:
+            # prod rows (turbo_quant.rs:214-236): stage one, residual, projection with S^T (the host's matmul), sign bits
+            y = self.rotate(x)
+            packed = self.quantize_rotated_rows(y)
+            resid = torch.empty((rows, d), dtype=torch.float32, device=x.device)
+            ra = A.TqResidArgs(y.data_ptr(), packed.data_ptr(), self.tab.data_ptr(), resid.data_ptr(), rows, d, y.stride(0), 0,
+                               A.F32, self.format.bits)
+            A.check(A.lib().b200_tq_residual(C.byref(ra), _stream(x.device)))
+            proj = resid.matmul(self.qjl[1])
+            sa = A.TqSignsArgs(packed.data_ptr(), proj.data_ptr(), resid.data_ptr(), packed.data_ptr(), rows, d, self.format.bits)
+            A.check(A.lib().b200_tq_signs(C.byref(sa), _stream(x.device)))
+            return packed
         if self.rotation == "none":
             return self.quantize_rotated_rows(x)
         out = torch.empty((1, 1, rows, self.layout.row_words), dtype=torch.int32, device=x.device)
@@ -207,9 +225,12 @@ class TurboQuantizer:
             raise ValueError(f"turbo-quant: expected rows of {self.layout.row_words} words, got {rw}")
         data = data.contiguous()
         out = torch.empty((rows, self.dim), dtype=torch.float32, device=data.device)
+        zs = torch.empty_like(out) if self.qjl is not None else None
         args = A.TqDequantArgs(data.data_ptr(), out.data_ptr(), self.tab.data_ptr(), rows, self.dim, 0,
-                               self.format.mode, self.format.bits)
+                               self.format.mode, self.format.bits, zs.data_ptr() if zs is not None else None)
         A.check(A.lib().b200_tq_dequantize(C.byref(args), _stream(data.device)))
+        if zs is not None:
+            out = out + zs.matmul(self.qjl[0])  # the sketch's part of the estimate (turbo_quant.rs:281-284)
         return self.unrotate(out)
 
     def quantize(self, x: torch.Tensor) -> QuantizedTensor:
@@ -301,6 +322,16 @@ class PackedAttention:
         # status: an int32 device word that the kernels set when a bounded device wait runs out.
         _need_cuda(q, "q")
         b, hq, lq, d = q.shape
+        kside = kq.side()
+        if kq.qjl is not None:
+            # prod keys (turbo_quant.rs:1161-1168): the rotated query followed by S q, f32; the keys' side of the call
+            # then says "not rotated"
+            qr = kq.rotate(q.reshape(-1, d)).view(b, hq, lq, d)
+            q_out_dtype = q.dtype
+            q = torch.cat([qr, qr.matmul(kq.qjl[1])], dim=3).contiguous()
+            kside.rotation, kside.signs = A.ROT_NONE, None
+            if out is None:
+                out = torch.empty((b, hq, lq, d), dtype=q_out_dtype, device=q.device)
         bk, hkv, cap, kw = k_rows.shape
         bv, hv, capv, vw = v_rows.shape
         ragged = isinstance(kv_len, torch.Tensor)
@@ -336,7 +367,7 @@ class PackedAttention:
         args.pages, args.n_pages = None, 0
         args.kv_len_dev = kv_len.data_ptr() if ragged else None
         args.b, args.lq, args.lk, args.hq, args.hkv, args.d = b, lq, lk, hq, hkv, d
-        args.kq, args.vq = kq.side(), vq.side()
+        args.kq, args.vq = kside, vq.side()
         args.scale, args.softcap = cfg.softmax_scale, cfg.softcap or 0.0
         args.wl, args.wr = wl, wr
         args.alibi, args.alibi_bstride = (alibi.data_ptr() if alibi is not None else None), abs_
@@ -540,7 +571,15 @@ class TurboKvCache:
             nk[:, :, : self.cap] = self.k
             nv[:, :, : self.cap] = self.v
             self.k, self.v, self.cap = nk, nv, cap
-        _kv_append(k, v, self.k, self.v, self.kq, self.vq, self.len)
+        if self.kq.qjl is not None:
+            # prod keys are finished in stages (quantize, residual, sketch): rows first, then copied to their place;
+            # the values go through the fused append
+            rows = self.kq.quantize_rows(k.reshape(-1, d).contiguous() if k.is_contiguous() else k.contiguous().view(-1, d))
+            self.k[:, :, self.len:self.len + t] = rows.view(b, h, t, -1)
+            scratch = torch.empty_like(self.v)
+            _kv_append(v, v, scratch, self.v, self.vq, self.vq, self.len)
+        else:
+            _kv_append(k, v, self.k, self.v, self.kq, self.vq, self.len)
         self.len += t
 
     def keys_values(self):

@@ -78,6 +78,10 @@ int b200_codebook(int dim, int bits, float tab[32]);
  * cache seed, values seed + 2 (candle-nn/src/turbo_quant.rs:148-153,868). */
 int b200_hadamard_signs(int dim, uint64_t seed, float *signs);
 
+/* Row-major dim x dim matrix S of i.i.d. standard normals: the projection of the prod format's 1-bit sketch of the
+ * residual (QJL). Host memory. Replaces accel::turbo::qjl_matrix (turbo.rs:236-239). */
+int b200_qjl_matrix(int dim, uint64_t seed, float *s);
+
 /* Query heads that share one kv head per work group (8, 4, 2 or 1) and the reference's key split
  * count for a device of `compute_units` SMs. Replace accel::attention::row_group and
  * split_count_grouped with SplitKv::Auto (candle-core/src/accel/attention.rs:486-506,586-592). */
@@ -138,8 +142,45 @@ typedef struct B200TqDequantArgs {
     uint32_t dim;
     uint64_t data_stride; /* words; 0 = row_words */
     int32_t mode, bits;
+    float *zs;            /* optional, prod rows only: (rows, dim) QJL coefficients +-(rsc0 rsc1 sqrt(pi/2) / dim) by sign bit
+                           * (the second part of the reference's output, accel.rs:639-684 with_qjl) */
 } B200TqDequantArgs;
 int b200_tq_dequantize(const B200TqDequantArgs *args, b200_stream_t stream);
+
+/* ---- prod (QJL) rows, stage two ------------------------------------------------------------------ */
+/* b200_tq_quantize with mode B200_TURBO_PROD writes stage one: codes of bits - 1 bits, rsc0 = norm, an empty
+ * sketch and rsc1 = 0 (turbo_quant_impl.h:71-159). The two calls below finish the rows as the reference does
+ * (candle-nn/src/turbo_quant.rs:214-236): residual -> (the host's matmul with S^T) -> sign bits.
+ *
+ * Replaces CudaStorage::tq_residual (accel.rs:555-598) and the kernel tq_resid (turbo_quant_impl.h:161-177):
+ * resid[r][j] = src[r][j] / rsc0 - centroid[code j], f32, rows in the rotated domain. */
+typedef struct B200TqResidArgs {
+    const void *src;      /* device, (rows, dim) of src_dtype, row stride src_stride elements */
+    const uint32_t *data; /* device, stage-one rows, (rows, data_stride) u32 */
+    const float *tab;     /* device, 32 floats: the codebook of bits - 1 bits */
+    float *resid;         /* device, (rows, dim) contiguous */
+    uint64_t rows;
+    uint32_t dim;
+    uint64_t src_stride;  /* elements */
+    uint64_t data_stride; /* words; 0 = row_words */
+    int32_t src_dtype;    /* B200_F32 / B200_F16 / B200_BF16 */
+    int32_t bits;         /* width of the prod format (2-5) */
+} B200TqResidArgs;
+int b200_tq_residual(const B200TqResidArgs *args, b200_stream_t stream);
+
+/* Replaces CudaStorage::tq_signs (accel.rs:600-636) and the kernel tq_signs (turbo_quant_impl.h:179-206): copies
+ * the rows and fills in the sketch (bit j set when proj[r][j] >= 0, proj = resid S^T) and rsc1 = |resid| (sum of
+ * squares in the order of the reference kernel's 128-lane tree: bit-exact). in == out is allowed. */
+typedef struct B200TqSignsArgs {
+    const uint32_t *in;   /* device, (rows, row_words) stage-one rows */
+    const float *proj;    /* device, (rows, dim) */
+    const float *resid;   /* device, (rows, dim) */
+    uint32_t *out;        /* device, (rows, row_words) */
+    uint64_t rows;
+    uint32_t dim;
+    int32_t bits;
+} B200TqSignsArgs;
+int b200_tq_signs(const B200TqSignsArgs *args, b200_stream_t stream);
 
 /* Rows into (inverse = 0: y = x Pi^T) or out of (inverse = 1: x = y Pi) the rotated domain of the
  * randomized Hadamard rotation Pi = H diag(signs) / sqrt(dim), f32, in place allowed. Replaces the
@@ -202,7 +243,12 @@ typedef struct B200Page {
  * out_dtype = B200_F32 the call is exactly the reference's tq_attention.
  *
  * Extension for ragged batches (the reference has one seq_len per cache, turbo_quant.rs:895-897):
- * kv_len_dev, one length per batch entry in device memory; lk is then the maximum length. */
+ * kv_len_dev, one length per batch entry in device memory; lk is then the maximum length.
+ *
+ * Prod keys (kq.mode = B200_TURBO_PROD; turbo_quant_impl.h:268-277): every query row holds 2 d values, the query in
+ * the rotated domain followed by S times it (the caller rotates and projects, as the reference's tq_prepare does,
+ * candle-nn/src/turbo_quant.rs:1161-1168), kq.rotation must be B200_ROT_NONE, and every score gains
+ * rsc0 rsc1 sqrt(pi / 2) / d times the signed sum of S q over the key's sign bits. Served by the general kernel. */
 typedef struct B200TqAttnArgs {
     const void *q;
     void *out;

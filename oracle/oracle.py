@@ -196,6 +196,59 @@ def quantize_rows(y, mode, bits=4, tab=None, norm_order=1):
     return out
 
 
+def qjl_matrix(dim: int, seed: int):
+    """Row-major dim x dim matrix of standard normals: the QJL projection S of prod rows (turbo.rs:236-239)."""
+    m = np.empty((dim, dim), dtype=np.float32)
+    lib().orc_qjl_matrix(dim, C.c_uint64(seed), _p(m))
+    return m
+
+
+def tq_residual(y, data, bits, tab):
+    """resid = y / rsc0 - centroid[code] of prod rows after stage one (turbo_quant_impl.h:161-177)."""
+    y, data = _c(y, np.float32), _c(data, np.uint32)
+    rows, d = y.shape
+    out = np.empty((rows, d), dtype=np.float32)
+    assert lib().orc_tq_residual(_p(y), _p(data), C.c_size_t(rows), d, bits, _p(_c(tab, np.float32)), _p(out)) == 0
+    return out
+
+
+def tq_signs(data, proj, resid, bits):
+    """Sign bits of proj = S resid and rsc1 = |resid| filled into prod rows (turbo_quant_impl.h:179-206)."""
+    data, proj, resid = _c(data, np.uint32), _c(proj, np.float32), _c(resid, np.float32)
+    rows, d = proj.shape
+    out = np.empty_like(data)
+    assert lib().orc_tq_signs(_p(data), _p(proj), _p(resid), C.c_size_t(rows), d, bits, _p(out)) == 0
+    return out
+
+
+def quantize_rows_prod(y, bits, tab, s_matrix, norm_order=1):
+    """Prod rows of rotated vectors y: stage one (codes of bits - 1 bits, norm), residual, projection with S, sign bits
+    and residual norm (candle-nn/src/turbo_quant.rs:214-236)."""
+    y = _c(y, np.float32)
+    stage1 = quantize_rows(y, PROD, bits, tab, norm_order)
+    resid = tq_residual(y, stage1, bits, tab)
+    proj = resid @ np.ascontiguousarray(s_matrix.T)
+    return tq_signs(stage1, proj, resid, bits)
+
+
+def dequantize_qjl(data, dim, bits):
+    """QJL coefficients of prod rows: +-(rsc0 rsc1 sqrt(pi / 2) / dim) by sign bit (turbo_quant_impl.h:219-222)."""
+    data = _c(data, np.uint32)
+    out = np.empty((data.shape[0], dim), dtype=np.float32)
+    assert lib().orc_dequantize_qjl(_p(data), C.c_size_t(data.shape[0]), dim, bits, _p(out)) == 0
+    return out
+
+
+def ref_tq_signs(data, proj, resid, bits, gx=3):
+    """tq_signs on the host emulator of the reference's kernels."""
+    data, proj, resid = _c(data, np.uint32), _c(proj, np.float32), _c(resid, np.float32)
+    rows, d = proj.shape
+    lay = row_layout(PROD, bits, d)
+    params = np.array([rows, d, lay["code_words"], lay["row_words"], gx], dtype=np.uint32)
+    out = ref_run({"op": "tq_signs", "data": data.ravel(), "proj": proj.ravel(), "resid": resid.ravel(), "params": params})
+    return out["out"].reshape(rows, lay["row_words"])
+
+
 def dequantize_rows(data, dim, mode, bits=4, tab=None):
     data = _c(data, np.uint32)
     rows, rw = data.shape
@@ -239,6 +292,8 @@ def tq_attention(q, kd, vd, lk, k_fmt, v_fmt, scale, tab=None, kv_len=None, wl=-
     """q (b, hq, lq, d) f32; kd / vd (b, hkv, cap, words) u32; *_fmt = (mode, bits). Out (b, hq, lq, d)."""
     q, kd, vd = _c(q, np.float32), _c(kd, np.uint32), _c(vd, np.uint32)
     b, hq, lq, d = q.shape
+    if k_fmt[0] == PROD:
+        d //= 2  # prod keys: the rotated query followed by S q
     _, hkv, kcap, kw = kd.shape
     _, _, vcap, vw = vd.shape
     tab = _c(tab if tab is not None else np.zeros(64), np.float32)
@@ -373,7 +428,8 @@ def ref_tq_attn(q, kd, vd, lk, k_fmt, v_fmt, scale, tab, splits=1, group=1, wl=-
                 alibi=None, fp8=False, gx=None):
     """tq_attn / tq_attn_fp8 / tq_attng{G}[_fp8] (+ tq_combine) on the host emulator."""
     q, kd, vd = _c(q, np.float32), _c(kd, np.uint32), _c(vd, np.uint32)
-    b, hq, lq, d = q.shape
+    b, hq, lq, w = q.shape
+    d = w // 2 if k_fmt[0] == PROD else w  # prod keys: the rotated query followed by S q
     _, hkv, kcap, kw = kd.shape
     _, _, vcap, vw = vd.shape
     kl, vl = row_layout(k_fmt[0], k_fmt[1], d), row_layout(v_fmt[0], v_fmt[1], d)
@@ -388,7 +444,7 @@ def ref_tq_attn(q, kd, vd, lk, k_fmt, v_fmt, scale, tab, splits=1, group=1, wl=-
     arrays["uparams"] = np.array([b, lq, lk, hq, hkv, d, k_fmt[0], kl["code_bits"], kl["code_words"],
                                   kl["rsc_offset"], v_fmt[0], vl["code_bits"], vl["code_words"],
                                   vl["rsc_offset"], splits, gx, abs_, int(fp8), group], dtype=np.uint32)
-    arrays["strides"] = np.array([hq * lq * d, lq * d, d, hkv * kcap * kw, kcap * kw, kw,
+    arrays["strides"] = np.array([hq * lq * w, lq * w, w, hkv * kcap * kw, kcap * kw, kw,
                                   hkv * vcap * vw, vcap * vw, vw], dtype=np.uint64)
     arrays["fparams"] = np.array([scale, softcap], dtype=np.float32)
     arrays["iparams"] = np.array([wl, wr], dtype=np.int32)

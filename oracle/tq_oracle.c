@@ -32,6 +32,7 @@
 
 #define ORC_MSE 0
 #define ORC_PROD 1
+#define ORC_QJL 1.2533141f /* sqrt(pi / 2): turbo_quant_impl.h:26 */
 #define ORC_MXFP4 2
 #define ORC_NVFP4 3
 #define ORC_MXFP8 4
@@ -466,6 +467,64 @@ int orc_dequantize_rows(const uint32_t *data, size_t rows, size_t row_stride_wor
     return 0;
 }
 
+/* Prod rows, stage two (turbo_quant_impl.h:161-206; CPU twin turbo.rs:320-345).
+ * Residual of the unit vector to its codebook value: resid = x / rsc0 - centroid[code]. */
+int orc_tq_residual(const float *y, const uint32_t *data, size_t rows, int dim, int bits, const float *tab, float *resid) {
+    int lay[5];
+    if (orc_row_layout(ORC_PROD, bits, dim, lay)) return -1;
+#pragma omp parallel for schedule(static)
+    for (size_t r = 0; r < rows; ++r) {
+        const uint32_t *row = data + r * lay[3];
+        const float norm = u2f(row[lay[4]]);
+        const float inv = norm > 0.0f ? 1.0f / norm : 0.0f;
+        for (int j = 0; j < dim; ++j) {
+            const float u = y[r * dim + j] * inv;
+            resid[r * dim + j] = u - tab[get_bits(row, (size_t)j * lay[0], lay[0])];
+        }
+    }
+    return 0;
+}
+
+/* Copies packed rows and fills in the QJL sign bits (bit j: proj_j >= 0, proj = S resid) and rsc1 = |resid|, the sum of
+ * squares in the order of the kernel's 128-lane tree. */
+int orc_tq_signs(const uint32_t *in, const float *proj, const float *resid, size_t rows, int dim, int bits, uint32_t *out) {
+    int lay[5];
+    if (orc_row_layout(ORC_PROD, bits, dim, lay)) return -1;
+    const int sign_words = (dim + 31) / 32;
+#pragma omp parallel for schedule(static)
+    for (size_t r = 0; r < rows; ++r) {
+        const uint32_t *ir = in + r * lay[3];
+        uint32_t *orow = out + r * lay[3];
+        for (int w = 0; w < lay[3]; ++w) orow[w] = ir[w];
+        for (int w = 0; w < sign_words; ++w) {
+            uint32_t word = 0;
+            for (int e = 0; e < 32 && w * 32 + e < dim; ++e)
+                if (proj[r * dim + w * 32 + e] >= 0.0f) word |= 1u << e;
+            orow[lay[1] + w] = word;
+        }
+        orow[lay[1] + sign_words + 1] = f2u(sqrtf(sumsq_tree(resid + r * dim, dim)));
+    }
+    return 0;
+}
+
+/* turbo.rs:236-239: row-major dim x dim matrix of standard normals, the QJL projection S. */
+void orc_qjl_matrix(int dim, uint64_t seed, float *s) {
+    orc_rng r = {(seed + 1) ^ 0x514a4c5f534b4554ull};
+    for (size_t i = 0; i < (size_t)dim * dim; ++i) s[i] = (float)rng_normal(&r);
+}
+
+/* QJL coefficients of prod rows (turbo_quant_impl.h:219-222): +-c with c = rsc0 rsc1 sqrt(pi / 2) / d. */
+int orc_dequantize_qjl(const uint32_t *data, size_t rows, int dim, int bits, float *zs) {
+    int lay[5];
+    if (orc_row_layout(ORC_PROD, bits, dim, lay)) return -1;
+    for (size_t r = 0; r < rows; ++r) {
+        const uint32_t *row = data + r * lay[3];
+        const float c = u2f(row[lay[4]]) * u2f(row[lay[4] + 1]) * ORC_QJL / (float)dim;
+        for (int j = 0; j < dim; ++j) zs[r * dim + j] = ((row[lay[1] + (j >> 5)] >> (j & 31)) & 1u) ? c : -c;
+    }
+    return 0;
+}
+
 /* ------------------------------------------------------------------ attention */
 
 /* attention.rs:82-92 */
@@ -554,13 +613,16 @@ typedef struct {
     size_t k_sb, k_sh, k_ss, v_sb, v_sh, v_ss;
 } orc_packed_sides;
 
+
 /* Attention of (rotated) f32 queries (b, hq, lq, d) over packed K / V rows with the arithmetic
  * of tq_attn (turbo_quant_impl.h:232-401): score = scale * rsc0_k * sum_d elem_k * q_d, softcap,
  * ALiBi, softmax, value weight p * rsc0_v, value element without rsc0. One pass per row in key
  * order (no windows of 128, no splits: those only change the summation order). kv_len: NULL
  * (every sequence has p->lk keys) or one length per batch entry (ragged batch: sequence b
  * attends keys [0, kv_len[b]) with its queries as the last lq positions). tab: 64 floats, key
- * centroids at [0, 16), value centroids at [32, 48). out: (b, hq, lq, d) f32. */
+ * centroids at [0, 16), value centroids at [32, 48). out: (b, hq, lq, d) f32. Prod keys
+ * (turbo_quant_impl.h:268-277): the query rows are 2 d wide, the rotated query followed by S q, and
+ * every score gains rsc0 rsc1 sqrt(pi / 2) / d times the signed sum of S q over the key's sign bits. */
 int orc_tq_attention(const float *q, const uint32_t *kd, const uint32_t *vd, const int32_t *kv_len,
                      const float *tab, const float *alibi, int alibi_bs, const orc_attn_params *p,
                      const orc_packed_sides *sd, float *out) {
@@ -580,7 +642,8 @@ int orc_tq_attention(const float *q, const uint32_t *kd, const uint32_t *vd, con
         long long lo, hi;
         key_range(i, lq, lk, p->wl, p->wr, &lo, &hi);
         if (lo >= hi) continue;
-        const float *qr = q + row * d;
+        const int prod = sd->k_mode == ORC_PROD;
+        const float *qr = q + row * (prod ? 2 * d : d), *qs = qr + d;
         const float slope = alibi ? alibi[b * alibi_bs + h] : 0.0f;
         const long long pos = (long long)i + lk - lq;
         const uint32_t *kbase = kd + b * sd->k_sb + (size_t)hk * sd->k_sh;
@@ -592,6 +655,11 @@ int orc_tq_attention(const float *q, const uint32_t *kd, const uint32_t *vd, con
             float dot = 0.0f;
             for (int t = 0; t < d; ++t) dot += row_elem(kr, t, sd->k_mode, kl[0], kl[1], kc) * qr[t];
             float sc = u2f(kr[kl[4]]) * dot;
+            if (prod) {
+                float sdot = 0.0f;
+                for (int t = 0; t < d; ++t) sdot += ((kr[kl[1] + (t >> 5)] >> (t & 31)) & 1u) ? qs[t] : -qs[t];
+                sc += u2f(kr[kl[4]]) * u2f(kr[kl[4] + 1]) * ORC_QJL / (float)d * sdot;
+            }
             sc *= p->scale;
             if (p->softcap > 0.0f) sc = p->softcap * tanhf(sc / p->softcap);
             if (slope != 0.0f) sc -= slope * (float)llabs(pos - j);

@@ -154,6 +154,71 @@ def gen_fa():
     np.savez_compressed(HERE / "flash_attn.npz", **out)
 
 
+# prod (QJL) rows: (bits, dim); the sketch uses the quantizer's seed
+PROD_CASES = [(4, 128), (2, 64), (5, 256), (3, 96)]
+PROD_SEED = 42
+# (name, bits, b, lq, lk, hq, hkv, d, splits, group, wl, wr): prod keys, 4-bit codebook values
+PROD_ATTN_CASES = [("prod4_g2_s3", 4, 1, 2, 150, 4, 2, 128, 3, 2, -1, 0), ("prod3_window", 3, 2, 1, 77, 4, 1, 64, 1, 1, 30, 0)]
+
+
+def prod_rows(y, bits, dim):
+    """Stage one by the reference's tq_quant kernel, the residual and its projection by the oracle (the reference
+    computes them with tensor operations on the host side), sign bits and residual norm by the reference's tq_signs."""
+    tab = O.codebook(dim, bits - 1)
+    s = O.qjl_matrix(dim, PROD_SEED)
+    stage1 = O.ref_tq_quant(y, O.PROD, bits, tab)
+    resid = O.tq_residual(y, stage1, bits, tab)
+    proj = (resid.astype(np.float64) @ s.T.astype(np.float64)).astype(np.float32)
+    return stage1, resid, proj, O.ref_tq_signs(stage1, proj, resid, bits), tab, s
+
+
+def prod_attn_inputs(case):
+    name, bits, b, lq, lk, hq, hkv, d = case[:8]
+    seed = 6000 + sum(ord(c) for c in name)
+    kx = O.normal(seed, b * hkv * lk * d, 1.5).reshape(-1, d)
+    vx = O.normal(seed + 1, b * hkv * lk * d).reshape(-1, d)
+    q = O.normal(seed + 2, b * hq * lq * d).reshape(b, hq, lq, d)
+    _, _, _, kd, ktab, s = prod_rows(kx, bits, d)
+    vtab = O.codebook(d, 4)
+    vd = O.quantize_rows(vx, O.MSE, 4, vtab)
+    tab = np.zeros(64, np.float32)
+    tab[:32], tab[32:] = ktab, vtab
+    qx = np.concatenate([q, (q.astype(np.float64) @ s.T.astype(np.float64)).astype(np.float32)], axis=-1)
+    return qx, kd.reshape(b, hkv, lk, -1), vd.reshape(b, hkv, lk, -1), tab
+
+
+def prod_attn_inputs_from(kd, case):
+    """The inputs of a prod attention case with the key rows taken from the fixture (the reference's own rows): needs
+    neither the reference tree nor a bit-identical host matmul for the keys."""
+    name, bits, b, lq, lk, hq, hkv, d = case[:8]
+    seed = 6000 + sum(ord(c) for c in name)
+    vx = O.normal(seed + 1, b * hkv * lk * d).reshape(-1, d)
+    q = O.normal(seed + 2, b * hq * lq * d).reshape(b, hq, lq, d)
+    s = O.qjl_matrix(d, PROD_SEED)
+    vtab = O.codebook(d, 4)
+    tab = np.zeros(64, np.float32)
+    tab[:32], tab[32:] = O.codebook(d, bits - 1), vtab
+    qx = np.concatenate([q, (q.astype(np.float64) @ s.T.astype(np.float64)).astype(np.float32)], axis=-1)
+    return qx, kd, O.quantize_rows(vx, O.MSE, 4, vtab).reshape(b, hkv, lk, -1), tab
+
+
+def gen_prod():
+    out = {}
+    for bits, dim in PROD_CASES:
+        y = quant_input(O.PROD, bits, dim)
+        stage1, resid, proj, rows, tab, s = prod_rows(y, bits, dim)
+        key = f"b{bits}_d{dim}"
+        out[key + "_stage1"], out[key + "_resid"], out[key + "_proj"], out[key + "_rows"] = stage1, resid, proj, rows
+    for case in PROD_ATTN_CASES:
+        name, bits, b, lq, lk, hq, hkv, d, splits, group, wl, wr = case
+        qx, kd, vd, tab = prod_attn_inputs(case)
+        out[name + "_kd"] = kd
+        out[name] = O.ref_tq_attn(qx, kd, vd, lk, (O.PROD, bits), (O.MSE, 4), 1.0 / np.sqrt(d), tab, splits=splits, group=group, wl=wl, wr=wr)
+        print(" prod attn", name, out[name].shape)
+    np.savez_compressed(HERE / "tq_prod.npz", **out)
+    print("tq_prod.npz", len(out), "arrays")
+
+
 def gen_misc():
     dec = O.ref_run({"op": "decoders"})
     rows, d, s = 5, 128, 4
@@ -176,4 +241,5 @@ if __name__ == "__main__":
     gen_quant()
     gen_attn()
     gen_fa()
+    gen_prod()
     gen_misc()

@@ -33,7 +33,8 @@ def test_struct_sizes_match_header(pkg):
     A = pkg._abi
     names = {"B200RowLayout": A.RowLayout, "B200Profile": A.Profile, "B200QuantSide": A.QuantSide,
              "B200TqQuantArgs": A.TqQuantArgs, "B200TqDequantArgs": A.TqDequantArgs, "B200KvAppendArgs": A.KvAppendArgs,
-             "B200Page": A.Page, "B200TqAttnArgs": A.TqAttnArgs, "B200FaArgs": A.FaArgs, "B200PeerGather": A.PeerGather}
+             "B200Page": A.Page, "B200TqAttnArgs": A.TqAttnArgs, "B200FaArgs": A.FaArgs, "B200PeerGather": A.PeerGather,
+             "B200TqResidArgs": A.TqResidArgs, "B200TqSignsArgs": A.TqSignsArgs}
     src = '#include <stdio.h>\n#include "b200attn.h"\nint main(void){' + "".join(
         f'printf("{n} %zu\\n", sizeof({n}));' for n in names) + "return 0;}"
     with tempfile.TemporaryDirectory() as td:

@@ -621,6 +621,42 @@ def test_gather_epilogue_on_one_rank(P, oracle):
         P.PackedAttention(q, k_rows, v_rows, kv_len, kq, vq, cfg, gather=g).run()
 
 
+@pytest.mark.parametrize("case", MG.PROD_ATTN_CASES, ids=lambda c: c[0])
+def test_prod_keys_against_reference_kernel_outputs(P, oracle, golden, case):
+    """TurboProd keys (codebook codes + the 1-bit sketch of the residual): the attention over the reference's own rows
+    against the outputs of its tq_attn kernels; then a cache that quantizes the keys itself against the oracle."""
+    A = P._abi
+    name, bits, b, lq, lk, hq, hkv, d, splits, group, wl, wr = case
+    qx, kd, vd, tab = MG.prod_attn_inputs_from(golden["tq_prod"][name + "_kd"], case)
+    kq = P.TurboQuantizer(P.QuantFormat(A.TURBO_PROD, bits), d, "none", MG.PROD_SEED)
+    vq = P.TurboQuantizer(fmt(P, 0, 4), d, "none", MG.PROD_SEED + 2)
+    c = P.FlashAttnConfig(d ** -0.5)
+    c.window_size_left = None if wl < 0 else wl
+    c.window_size_right = None if wr < 0 else wr
+    got = P.attention_packed(to_dev(qx[..., :d]), rows_dev(kd), rows_dev(vd), lk, kq, vq, c).cpu().numpy()
+    assert_close(got, golden["tq_prod"][name], what=name)
+    # end to end: rows written by the cache (device matmuls in the sketch), attention against the oracle on those rows
+    cache = P.TurboKvCache(P.QuantFormat(A.TURBO_PROD, bits), fmt(P, 0, 4), d, "none", MG.PROD_SEED, lk)
+    g = torch.Generator(device="cuda:0").manual_seed(bits)
+    kx = torch.randn((b, hkv, lk, d), generator=g, device="cuda:0")
+    vx = torch.randn((b, hkv, lk, d), generator=g, device="cuda:0")
+    cache.append(kx, vx)
+    q = torch.randn((b, hq, lq, d), generator=g, device="cuda:0")
+    got = cache.attention(q, c).cpu().numpy()
+    s = oracle.qjl_matrix(d, MG.PROD_SEED)
+    qn = q.cpu().numpy()
+    qxx = np.concatenate([qn, qn @ s.T], axis=-1)
+    want = oracle.tq_attention(qxx, words(cache.k[:, :, :lk]), words(cache.v[:, :, :lk]), lk, (oracle.PROD, bits), (oracle.MSE, 4), d ** -0.5,
+                               tab, wl=wl, wr=wr)
+    assert_close(got, want, what=name + " cache")
+    # and the estimate is the unbiased one: far closer to exact attention than the codebook part alone
+    lay = oracle.row_layout(oracle.PROD, bits, d)
+    k0 = words(cache.k[:, :, :lk]).copy()
+    k0[..., lay["rsc_offset"] + 1] = 0
+    no_sketch = oracle.tq_attention(qxx, k0, words(cache.v[:, :, :lk]), lk, (oracle.PROD, bits), (oracle.MSE, 4), d ** -0.5, tab, wl=wl, wr=wr)
+    assert np.abs(no_sketch - want).max() > 1e-3
+
+
 def _local_gather(P, world, rows, d, dev, max_polls=0):
     """What OutputGather provides, without symmetric memory: every rank's buffer and flags are plain local allocations."""
     A = P._abi

@@ -212,3 +212,43 @@ def test_hadamard_append_stages(P, oracle, mode, bits):
     lay = oracle.row_layout(mode, bits, d)
     diff_codes = np.unpackbits((fused[:, : lay["code_words"]] ^ ref[:, : lay["code_words"]]).view(np.uint8)).sum()
     assert diff_codes <= rows * d * lay["code_bits"] // 500
+
+
+@pytest.mark.parametrize("bits,dim", [(4, 128), (2, 64), (5, 256), (3, 96)])
+def test_prod_rows_bit_exact_with_reference_kernels(P, oracle, golden, bits, dim):
+    """TurboProd (QJL) rows, stage by stage through the C ABI: stage one against the reference's tq_quant kernel, the
+    residual against the oracle's bits, sign bits and residual norm against the reference's tq_signs kernel (on the
+    fixture's projection, so that no matmul sits in the comparison); then the whole chain with the device's matmul."""
+    import ctypes as C
+    A = P._abi
+    g, key = golden["tq_prod"], f"b{bits}_d{dim}"
+    y = MG.quant_input(oracle.PROD, bits, dim)
+    qz = P.TurboQuantizer(P.QuantFormat(A.TURBO_PROD, bits), dim, "none", MG.PROD_SEED)
+    assert np.array_equal(qz.tab.cpu().numpy(), oracle.codebook(dim, bits - 1))
+    assert np.array_equal(qz.qjl[0].cpu().numpy(), oracle.qjl_matrix(dim, MG.PROD_SEED))
+    yd = to_dev(y)
+    stage1 = qz.quantize_rotated_rows(yd)
+    assert np.array_equal(words(stage1), g[key + "_stage1"])
+    rows = y.shape[0]
+    resid = torch.empty((rows, dim), dtype=torch.float32, device="cuda:0")
+    ra = A.TqResidArgs(yd.data_ptr(), stage1.data_ptr(), qz.tab.data_ptr(), resid.data_ptr(), rows, dim, dim, 0, A.F32, bits)
+    A.check(A.lib().b200_tq_residual(C.byref(ra), None))
+    assert np.array_equal(resid.cpu().numpy().view(np.uint32), g[key + "_resid"].view(np.uint32))
+    proj = to_dev(g[key + "_proj"])
+    out = torch.empty_like(stage1)
+    sa = A.TqSignsArgs(stage1.data_ptr(), proj.data_ptr(), resid.data_ptr(), out.data_ptr(), rows, dim, bits)
+    A.check(A.lib().b200_tq_signs(C.byref(sa), None))
+    assert np.array_equal(words(out), g[key + "_rows"])
+    # the whole chain: sign bits may differ only where a projection is at rounding distance of zero
+    full = words(qz.quantize_rows(yd))
+    lay = oracle.row_layout(oracle.PROD, bits, dim)
+    sw = slice(lay["code_words"], lay["code_words"] + (dim + 31) // 32)
+    assert np.unpackbits((full ^ g[key + "_rows"])[:, sw].view(np.uint8)).sum() <= 3
+    rest = np.ones(lay["row_words"], bool)
+    rest[sw] = False
+    assert np.array_equal(full[:, rest], g[key + "_rows"][:, rest])
+    # dequantized estimate: codebook part + sketch part, against the oracle on the same rows
+    want = (oracle.dequantize_rows(g[key + "_rows"], dim, oracle.PROD, bits, oracle.codebook(dim, bits - 1))
+            + oracle.dequantize_qjl(g[key + "_rows"], dim, bits) @ oracle.qjl_matrix(dim, MG.PROD_SEED))
+    got = qz.dequantize_rows(rows_dev(g[key + "_rows"])).cpu().numpy()
+    assert np.allclose(got, want, atol=2e-5 * max(1.0, float(np.abs(want).max())), rtol=1e-5)

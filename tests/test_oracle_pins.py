@@ -214,3 +214,34 @@ def test_unfused_path_equals_reference_attention(oracle):
         a = oracle.reference_attention(q, k, v, 0.125, wl=wl, wr=wr)
         u = oracle.unfused_attention(q, k, v, 0.125, wl=wl, wr=wr)
         assert np.allclose(a, u, atol=1e-5)
+
+
+@pytest.mark.parametrize("bits,dim", MG.PROD_CASES)
+def test_prod_rows_pinned_to_reference_kernels(oracle, golden, bits, dim):
+    """TurboProd rows: stage one against the reference's tq_quant kernel, sign bits and residual norm against its
+    tq_signs kernel (on the fixture's residual and projection, so that no host matmul sits in the comparison)."""
+    g, key = golden["tq_prod"], f"b{bits}_d{dim}"
+    y = MG.quant_input(oracle.PROD, bits, dim)
+    tab = oracle.codebook(dim, bits - 1)
+    stage1 = oracle.quantize_rows(y, oracle.PROD, bits, tab)
+    assert np.array_equal(stage1, g[key + "_stage1"])
+    resid = oracle.tq_residual(y, stage1, bits, tab)
+    assert np.array_equal(resid.view(np.uint32), g[key + "_resid"].view(np.uint32))
+    assert np.array_equal(oracle.tq_signs(stage1, g[key + "_proj"], resid, bits), g[key + "_rows"])
+    # the whole chain (with this machine's matmul): sign bits may differ only where a projection is at rounding distance of zero
+    rows = oracle.quantize_rows_prod(y, bits, tab, oracle.qjl_matrix(dim, MG.PROD_SEED))
+    lay = oracle.row_layout(oracle.PROD, bits, dim)
+    flips = np.unpackbits((rows ^ g[key + "_rows"])[:, lay["code_words"]:lay["code_words"] + (dim + 31) // 32].view(np.uint8)).sum()
+    assert flips <= 2
+    # QJL coefficients: +-c by sign bit
+    zs = oracle.dequantize_qjl(g[key + "_rows"], dim, bits)
+    c = g[key + "_rows"][:, lay["rsc_offset"]].view(np.float32) * g[key + "_rows"][:, lay["rsc_offset"] + 1].view(np.float32)
+    assert np.allclose(np.abs(zs), (c * np.float32(1.2533141) / np.float32(dim))[:, None], rtol=1e-6)
+
+
+@pytest.mark.parametrize("case", MG.PROD_ATTN_CASES, ids=lambda c: c[0])
+def test_prod_attention_pinned_to_reference_kernels(oracle, golden, case):
+    name, bits, b, lq, lk, hq, hkv, d, splits, group, wl, wr = case
+    qx, kd, vd, tab = MG.prod_attn_inputs_from(golden["tq_prod"][name + "_kd"], case)
+    got = oracle.tq_attention(qx, kd, vd, lk, (oracle.PROD, bits), (oracle.MSE, 4), 1.0 / np.sqrt(d), tab, wl=wl, wr=wr)
+    assert np.allclose(got, golden["tq_prod"][name], atol=1e-4, rtol=2e-5)
