@@ -597,7 +597,7 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from the ncu capture of the same
 # workload (profiles/): filled in for the workloads that have a committed capture
-TRAFFIC = {"c2": (366_272_256, "ncu capture of this workload, profiles/tq_decode_pair_kernel_c2_mxfp4.md")}
+TRAFFIC = {"c2": (366_696_192, "ncu capture of this workload, profiles/tq_decode_kernel_c2_mxfp4.md")}
 
 
 def prefill_leg(env, steps, warmup):
@@ -728,7 +728,11 @@ def run_ours(args, rank, world, local_rank):
     if head == "c3":
         headline = prefill_leg(env, args.steps, args.warmup) if rank == 0 else None
     else:
-        headline = decode_leg(env, head, dict(WORKLOADS[head]), args.steps, args.warmup, layers=32 if head == "c5" else 1)
+        wl = dict(WORKLOADS[head])
+        if args.batch > 0:
+            wl["b"] = args.batch
+            wl["desc"] += f" [batch reduced to {args.batch}]"
+        headline = decode_leg(env, head, wl, args.steps, args.warmup, layers=32 if head == "c5" else 1)
         if headline is not None and head in TRAFFIC and world == 1:
             headline["roofline"]["traffic"], headline["roofline"]["traffic_source"] = TRAFFIC[head]
     if not args.only:
@@ -771,6 +775,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c3"], help="the headline workload (last line printed)")
     ap.add_argument("--only", action="store_true", help="time the headline workload alone")
+    ap.add_argument("--batch", type=int, default=0, help="sequences of the headline workload (default: the configuration's); a "
+                    "smaller batch keeps a profiler capture of the large configurations within a few GB")
     ap.add_argument("--verbose", action="store_true", help="print stage markers to stderr")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
