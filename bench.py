@@ -289,6 +289,50 @@ class Env:
         self.torch.cuda.synchronize()
 
 
+def ref_gpu_decode(env, w, lens, caches, kq, vq, steps):
+    """The reference's own GPU kernels (its kernel headers compiled for sm_100a, its launch plan replayed: baseline/ref_cuda.cu)
+    on the same cached rows of the same device: attention and combine launches alone, f32 queries already rotated, no
+    rotation, cast or allocation timed. A ragged batch is one call per sequence (the reference's cache has one length).
+    Returns the "ref_gpu_kernels" object or None when the library was not built."""
+    torch, dev = env.torch, env.dev
+    from baseline import ref_cuda as R
+    if not R.available():
+        return None
+    b, hq, hkv, d = w["b"], w["hq"], w["hkv"], w["d"]
+    q32 = torch.randn((b, hq, 1, d), device=dev, dtype=torch.float32)
+    tab = torch.cat([kq.tab, vq.tab])
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    refs = [R.TqAttention(torch, q32, kc, vc, lens, kq.layout, vq.layout, kq.format.mode, vq.format.mode, tab, d ** -0.5, sms)
+            for kc, vc in caches]
+    stream = torch.cuda.current_stream(dev)
+    for r in refs:
+        r.run(stream.cuda_stream)
+    torch.cuda.synchronize()
+    graphs = []
+    for r in refs:
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            r.run(torch.cuda.current_stream(dev).cuda_stream)
+        graphs.append(gr)
+    n = max(2, min(steps, 20))
+    for i in range(len(graphs)):
+        graphs[i].replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(n):
+        graphs[i % len(graphs)].replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    r0 = refs[0]
+    return {"value": algorithmic_bytes(w, lens) / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms, "steps": n,
+            "launches_per_step": r0.launches, "kernel": f"tq_attn{'g%d' % r0.group if r0.group > 1 else ''}{'_fp8' if w['mode'] == 5 else ''} + tq_combine",
+            "what": (f"the reference's kernels compiled for sm_100a, its launch plan ({len(r0.calls)} call(s) per step, key splits "
+                     f"{min(r0.splits)}-{max(r0.splits)}), CUDA graph replay; attention and combine launches only")}
+
+
+
 def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, layers=1):
     """Times workload `w_full` (sharded over the ranks when it says so): exactly `steps` steps between two events.
     Returns the result line (rank 0) or None."""
@@ -582,6 +626,10 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
             line["e2e"] = {"value": job_bytes / (e2e_ms_r / steps * 1e-3) / 1e9, "unit": "GB/s",
                            "h2d_bytes_per_step": int(nq + 2 * nkv) * 2, "d2h_bytes_per_step": int(nq) * 2,
                            "ms_per_step": e2e_ms_r / steps, "tokens_per_s": (w_full["b"] if strong else world * b) / (e2e_ms_r / steps * 1e-3)}
+    if line is not None and world == 1 and with_cpu:
+        ref_gpu = ref_gpu_decode(env, w, lens, caches, kq, vq, steps)
+        if ref_gpu is not None:
+            line["ref_gpu_kernels"] = ref_gpu
     # release what the leg holds before the next one allocates
     graphs.clear()
     long_graph = None
@@ -692,6 +740,31 @@ def prefill_leg(env, steps, warmup):
                          "traffic": 4 * 53_400_000, "traffic_unit": "bytes per launch",
                          "traffic_source": "ncu capture at B=1 scaled by 4, profiles/fa_prefill_sm100_kernel2_b1_s4096.md"},
             "cpu_baseline": cpu, "clocks": clocks}
+    from baseline import ref_cuda as R
+    if R.available():
+        # the reference's tile kernel of the tier a B200 selects, on the same tensors (attention alone; its append is a
+        # second call in the reference and is not timed here)
+        q, k, v = sets[0]
+        o = torch.empty_like(q)
+        st = torch.cuda.current_stream(dev).cuda_stream
+        rc = R.lib().refcu_fa_prefill_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), b, s, hq, hkv, d ** -0.5, st)
+        torch.cuda.synchronize()
+        if rc == 0:
+            e0.record()
+            for i in range(2):
+                q, k, v = sets[(i + 1) % nbuf]
+                R.lib().refcu_fa_prefill_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), b, s, hq, hkv, d ** -0.5, st)
+            e1.record()
+            torch.cuda.synchronize()
+            rms = e0.elapsed_time(e1) / 2
+            ours = F.flash_attn_with_config(sets[0][0], sets[0][1], sets[0][2], cfg)
+            R.lib().refcu_fa_prefill_bf16(sets[0][0].data_ptr(), sets[0][1].data_ptr(), sets[0][2].data_ptr(), o.data_ptr(), b, s, hq,
+                                          hkv, d ** -0.5, st)
+            torch.cuda.synchronize()
+            line["ref_gpu_kernels"] = {"value": flops / (rms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": rms, "steps": 2,
+                                       "launches_per_step": 1, "kernel": "fa3_d128_bf16_bf16 (BR 32, BC 64, grid 128 x 32 x 4)",
+                                       "max_abs_diff_to_ours": float((ours.float() - o.float()).abs().max()),
+                                       "what": "the reference's tile kernel compiled for sm_100a with its launch plan; attention alone"}
     sets.clear()
     torch.cuda.empty_cache()
     return line
@@ -713,6 +786,8 @@ def compact(line):
         c["e2e"] = {"value": round(line["e2e"]["value"], 1), "ms_per_step": round(line["e2e"]["ms_per_step"], 5)}
     if line.get("cpu_baseline"):
         c["cpu_baseline"] = {"value": round(line["cpu_baseline"]["value"], 3), "cores": line["cpu_baseline"]["cores"]}
+    if line.get("ref_gpu_kernels"):
+        c["ref_gpu_kernels"] = {"value": round(line["ref_gpu_kernels"]["value"], 2), "ms_per_step": round(line["ref_gpu_kernels"]["ms_per_step"], 4)}
     if line.get("clocks"):
         c["clocks"] = {"sm_mhz": line["clocks"]["sm_mhz"], "reasons": line["clocks"]["reasons"]}
     c["batch_per_gpu"] = line["config"].get("batch_per_gpu")

@@ -96,6 +96,12 @@ __device__ __forceinline__ uint32_t f_to_fp4(float f) {
 }
 
 __device__ __forceinline__ float e8m0_to_f(uint32_t c) { return c == 0 ? u2f(0x00400000u) : u2f(c << 23); }
+// 1 / e8m0_to_f(c) = 2^(127 - c), itself a float (2^-127 is a subnormal, 1 / inf is 0): the product x * e8m0_recip(c) and
+// the IEEE quotient x / e8m0_to_f(c) round the same real number, so they agree bit for bit, overflow and subnormal
+// results included
+__device__ __forceinline__ float e8m0_recip(uint32_t c) {
+    return c >= 254u ? (c == 254u ? u2f(0x00400000u) : 0.0f) : u2f((254u - c) << 23);
+}
 
 __device__ __forceinline__ uint32_t mx_scale_code(float amax, int emax_elem) {
     int e = -127;

@@ -6,7 +6,8 @@
 // the packed row goes straight to its slot of the capacity buffer. Codes, block scales and rsc0
 // are bit-exact with that kernel: maxima do not depend on the reduction order, the sum of
 // squares of the codebook formats reproduces the order of its 128-lane tree
-// (candle-core/kernels/accel_common.h:255-267), all divisions are IEEE.
+// (candle-core/kernels/accel_common.h:255-267), all divisions are IEEE (by a power of two: the
+// exact product with its reciprocal).
 #include <algorithm>
 #include <cstdlib>
 
@@ -149,8 +150,7 @@ __global__ void __launch_bounds__(QW * 32) quant_rows_kernel(const QuantParams p
             for (int k = 0; k < EPL; ++k) {
                 const float bm = warp_max(fabsf(x[k]));  // block k = elements [32 k, 32 k + 32)
                 const uint32_t code = mx_scale_code(bm, emax);
-                const float s = e8m0_to_f(code);
-                const float qv = __fdiv_rn(x[k], s);
+                const float qv = __fmul_rn(x[k], e8m0_recip(code));  // = x / e8m0_to_f(code), bit for bit
                 c[k] = code == 0 ? 0u : (mode == B200_MXFP4 ? f_to_fp4(qv) : f_to_e4m3(qv));
                 if (lane == 0 && k < nk) sc[k] = code;
             }
@@ -270,24 +270,28 @@ __device__ __forceinline__ uint32_t fp4x2_hw(float lo, float hi) {
     asm("{\n .reg .b8 t;\n cvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n cvt.u32.u8 %0, t;\n}" : "=r"(d) : "f"(hi), "f"(lo));
     return d;
 }
+// x / s as the reference computes it. MUL: s is a power of two and `s` holds its reciprocal (e8m0_recip): the product is
+// the same float as the IEEE quotient and costs one instruction instead of a division sequence.
+template <bool MUL>
+__device__ __forceinline__ float scaled(float x, float s) { return MUL ? __fmul_rn(x, s) : __fdiv_rn(x, s); }
 // the lane's 16 elements divided by s -> 16 e2m1 codes (two words)
-template <bool FIX>
+template <bool FIX, bool MUL = false>
 __device__ __forceinline__ void fp4x16_div(const float (&x)[16], float s, uint32_t (&w)[2]) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         uint32_t v = 0;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) v |= fp4x2_hw<FIX>(__fdiv_rn(x[8 * h + 2 * i], s), __fdiv_rn(x[8 * h + 2 * i + 1], s)) << (8 * i);
+        for (int i = 0; i < 4; ++i) v |= fp4x2_hw<FIX>(scaled<MUL>(x[8 * h + 2 * i], s), scaled<MUL>(x[8 * h + 2 * i + 1], s)) << (8 * i);
         w[h] = v;
     }
 }
 // ... -> 16 e4m3 codes (four words)
-template <bool FIX>
+template <bool FIX, bool MUL = false>
 __device__ __forceinline__ void e4m3x16_div(const float (&x)[16], float s, uint32_t (&w)[4]) {
 #pragma unroll
     for (int h = 0; h < 4; ++h)
-        w[h] = e4m3x2_hw<FIX>(__fdiv_rn(x[4 * h], s), __fdiv_rn(x[4 * h + 1], s)) |
-               (e4m3x2_hw<FIX>(__fdiv_rn(x[4 * h + 2], s), __fdiv_rn(x[4 * h + 3], s)) << 16);
+        w[h] = e4m3x2_hw<FIX>(scaled<MUL>(x[4 * h], s), scaled<MUL>(x[4 * h + 1], s)) |
+               (e4m3x2_hw<FIX>(scaled<MUL>(x[4 * h + 2], s), scaled<MUL>(x[4 * h + 3], s)) << 16);
 }
 
 template <int DT>
@@ -424,21 +428,21 @@ __global__ void __launch_bounds__(Q128_WARPS * 32) quant_rows128_kernel(const Qu
             // MXFP4 / MXFP8: a block of 32 = two neighbouring lanes
             bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
             const uint32_t code = mx_scale_code(bm, mode == B200_MXFP4 ? 2 : 8);
-            const float s = e8m0_to_f(code);
+            const float s = e8m0_recip(code);  // the divisor is a power of two: multiply by its reciprocal, same bits
             if (mode == B200_MXFP4) {
                 cw = 16;
                 uint32_t w[2] = {0u, 0u};
                 if (code != 0) {
-                    if (special) fp4x16_div<true>(x, s, w);
-                    else fp4x16_div<false>(x, s, w);
+                    if (special) fp4x16_div<true, true>(x, s, w);
+                    else fp4x16_div<false, true>(x, s, w);
                 }
                 if (live) orow[2 * l8] = w[0], orow[2 * l8 + 1] = w[1];  // rows of 19 words: 4-byte alignment only
             } else {
                 cw = 32;
                 uint32_t w[4] = {0u, 0u, 0u, 0u};
                 if (code != 0) {
-                    if (special) e4m3x16_div<true>(x, s, w);
-                    else e4m3x16_div<false>(x, s, w);
+                    if (special) e4m3x16_div<true, true>(x, s, w);
+                    else e4m3x16_div<false, true>(x, s, w);
                 }
                 if (live) {
 #pragma unroll
