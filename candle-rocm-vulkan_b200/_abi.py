@@ -71,6 +71,7 @@ class Page(C.Structure):
 
 TQ_AFTER_PREV = 1  # B200_TQ_AFTER_PREV
 TQ_INPUTS_FINAL = 2  # B200_TQ_INPUTS_FINAL
+TQ_IN_PLACE = 4  # B200_TQ_IN_PLACE
 
 
 class TqAttnArgs(C.Structure):

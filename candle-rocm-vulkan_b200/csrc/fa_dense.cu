@@ -65,14 +65,17 @@ __device__ __forceinline__ uint16_t to16(float f) {
     return BF16 ? f_to_bf16_bits(f) : f_to_f16_bits(f);
 }
 
-// HD: head dim (64 or 128); BF16: the mma operand type (bf16, else f16). Queries, keys and values of
-// another dtype (f32 everywhere, E4M3 or f32 keys and values) are rounded to it on their way into
-// shared memory.
+// HD: the head dim bucket (64, 128 or 256: the smallest one that holds p.d, like the dmax of the reference's tile
+// kernels, candle-core/src/accel/attention.rs:428-435); the rows' elements d .. HD - 1 are zeros in shared memory and
+// are not stored. BF16: the mma operand type (bf16, else f16). Queries, keys and values of another dtype (f32
+// everywhere, E4M3 or f32 keys and values) are rounded to it on their way into shared memory.
 template <int HD, bool BF16>
 __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams p) {
     constexpr int ROWB = HD * 2 + 16;          // padded row bytes in shared memory
     constexpr int KSTEPS = HD / 16, NT = HD / 8;
     constexpr int CH = HD / 8;                 // 16-byte chunks per row
+    constexpr bool QREG = HD <= 128;           // the Q fragments stay in registers; at 256 they are re-read per k step
+    const uint32_t D = p.d;                    // elements per row in memory (a multiple of 8, at most HD)
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sQ = smem_u32(smem);                       // [FA_BM][ROWB]
     const uint32_t sK = sQ + FA_BM * ROWB;                    // 2 x [FA_BN][ROWB]
@@ -124,7 +127,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
         if (r < R) {
             const uint32_t i = r / G, h = hk * G + r % G;
             const uint64_t off = (p.varlen ? (q0 + i) * p.q_ss : b * p.q_sb + i * p.q_ss) + h * p.q_sh + dd;
-            v = (p.q_dtype == B200_F32) ? to16<BF16>(reinterpret_cast<const float *>(qb)[off]) : reinterpret_cast<const uint16_t *>(qb)[off];
+            if (dd < D) v = (p.q_dtype == B200_F32) ? to16<BF16>(reinterpret_cast<const float *>(qb)[off]) : reinterpret_cast<const uint16_t *>(qb)[off];
         }
         *reinterpret_cast<uint16_t *>(smem + rr * ROWB + dd * 2) = v;
     }
@@ -136,8 +139,8 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
             for (int idx = tid; idx < FA_BN * CH; idx += FA_WARPS * 32) {
                 const int rr = idx / CH, ch = idx % CH;
                 const long long j = j0 + rr;
-                const bool ok = j < s_hi;
-                const long long jj = ok ? j : s_lo;
+                const bool ok = j < s_hi && (uint32_t)ch * 8 < D;
+                const long long jj = j < s_hi ? j : s_lo;
                 cp_async16(dk + rr * ROWB + ch * 16, kb + ((uint64_t)jj * p.k_ss) * 2 + ch * 16, ok);
                 cp_async16(dv + rr * ROWB + ch * 16, vb + ((uint64_t)jj * p.v_ss) * 2 + ch * 16, ok);
             }
@@ -147,7 +150,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
                 const int rr = idx / CH, ch = idx % CH;
                 const long long j = j0 + rr;
                 uint32_t ko[4] = {0, 0, 0, 0}, vo[4] = {0, 0, 0, 0};
-                if (j < s_hi) {
+                if (j < s_hi && (uint32_t)ch * 8 < D) {
                     const float *ks = reinterpret_cast<const float *>(kb) + (uint64_t)j * p.k_ss + ch * 8;
                     const float *vs = reinterpret_cast<const float *>(vb) + (uint64_t)j * p.v_ss + ch * 8;
 #pragma unroll
@@ -165,7 +168,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
                 const int rr = idx / CH, ch = idx % CH;
                 const long long j = j0 + rr;
                 uint32_t ko[4] = {0, 0, 0, 0}, vo[4] = {0, 0, 0, 0};
-                if (j < s_hi) {
+                if (j < s_hi && (uint32_t)ch * 8 < D) {
                     const uint8_t *ks = reinterpret_cast<const uint8_t *>(kb) + (uint64_t)j * p.k_ss + ch * 8;
                     const uint8_t *vs = reinterpret_cast<const uint8_t *>(vb) + (uint64_t)j * p.v_ss + ch * 8;
 #pragma unroll
@@ -182,12 +185,12 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
     };
     if (ntiles > 0) load_tile(0);
     __syncthreads();
-    uint32_t qa[KSTEPS][4];
-    {
-        // ldmatrix x4: rows (lane & 15) of the warp's 16 rows, column halves by lane >> 4
-        const uint32_t base = sQ + (warp * 16 + (lane & 15)) * ROWB + (lane >> 4) * 16;
+    // ldmatrix x4: rows (lane & 15) of the warp's 16 rows, column halves by lane >> 4
+    const uint32_t q_base = sQ + (warp * 16 + (lane & 15)) * ROWB + (lane >> 4) * 16;
+    uint32_t qa[QREG ? KSTEPS : 1][4];
+    if (QREG) {
 #pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) ldsm_x4(base + ks * 32, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
+        for (int ks = 0; ks < (QREG ? KSTEPS : 1); ++ks) ldsm_x4(q_base + ks * 32, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
     }
 
     // rows of this lane: warp * 16 + g and + 8
@@ -239,14 +242,17 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
         for (int n = 0; n < FA_BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
+            uint32_t a0, a1, a2, a3;
+            if (QREG) a0 = qa[QREG ? ks : 0][0], a1 = qa[QREG ? ks : 0][1], a2 = qa[QREG ? ks : 0][2], a3 = qa[QREG ? ks : 0][3];
+            else ldsm_x4(q_base + ks * 32, a0, a1, a2, a3);
 #pragma unroll
             for (int np = 0; np < FA_BN / 16; ++np) {
                 // matrices: keys np*16 + (0..7 | 8..15), dims ks*16 + (0..7 | 8..15)
                 uint32_t b0, b1, b2, b3;
                 const uint32_t addr = tk + (np * 16 + (lane & 7) + ((lane >> 4) << 3)) * ROWB + ks * 32 + ((lane >> 3) & 1) * 16;
                 ldsm_x4(addr, b0, b1, b2, b3);
-                mma16816<BF16>(s[2 * np], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
-                mma16816<BF16>(s[2 * np + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
+                mma16816<BF16>(s[2 * np], a0, a1, a2, a3, b0, b1);
+                mma16816<BF16>(s[2 * np + 1], a0, a1, a2, a3, b2, b3);
             }
         }
         // ---- scale, masks, online softmax (rows g and g + 8; columns 8 n + 2 c, + 1)
@@ -327,21 +333,23 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
         if (p.n_splits == 1) {
             const float inv = l[e] > 0.0f ? p.vd / l[e] : 0.0f;
             if (p.q_dtype == B200_F32) {
-                float *o = reinterpret_cast<float *>(p.o) + orow * HD;
-#pragma unroll
-                for (int n = 0; n < NT; ++n) *reinterpret_cast<float2 *>(o + 8 * n + 2 * c) = make_float2(oacc[n][2 * e] * inv, oacc[n][2 * e + 1] * inv);
-            } else {
-                uint16_t *o = reinterpret_cast<uint16_t *>(p.o) + orow * HD;
+                float *o = reinterpret_cast<float *>(p.o) + orow * D;
 #pragma unroll
                 for (int n = 0; n < NT; ++n)
-                    *reinterpret_cast<uint32_t *>(o + 8 * n + 2 * c) = pack2<BF16>(oacc[n][2 * e] * inv, oacc[n][2 * e + 1] * inv);
+                    if ((uint32_t)8 * n < D) *reinterpret_cast<float2 *>(o + 8 * n + 2 * c) = make_float2(oacc[n][2 * e] * inv, oacc[n][2 * e + 1] * inv);
+            } else {
+                uint16_t *o = reinterpret_cast<uint16_t *>(p.o) + orow * D;
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+                    if ((uint32_t)8 * n < D) *reinterpret_cast<uint32_t *>(o + 8 * n + 2 * c) = pack2<BF16>(oacc[n][2 * e] * inv, oacc[n][2 * e + 1] * inv);
             }
         } else {
             const float inv = l[e] > 0.0f ? p.vd / l[e] : 0.0f;
             const uint64_t prow = (uint64_t)split * p.rows_total + orow;
-            float *po = p.part_o + prow * HD;
+            float *po = p.part_o + prow * D;
 #pragma unroll
-            for (int n = 0; n < NT; ++n) *reinterpret_cast<float2 *>(po + 8 * n + 2 * c) = make_float2(oacc[n][2 * e] * inv, oacc[n][2 * e + 1] * inv);
+            for (int n = 0; n < NT; ++n)
+                if ((uint32_t)8 * n < D) *reinterpret_cast<float2 *>(po + 8 * n + 2 * c) = make_float2(oacc[n][2 * e] * inv, oacc[n][2 * e + 1] * inv);
             if (c == 0) p.part_lse[prow] = l[e] > 0.0f ? m[e] + logf(l[e]) : -INFINITY;
         }
     }
@@ -388,7 +396,9 @@ static int fa_plan(const B200FaArgs *a, FaPlan &pl) {
     const bool kv16 = a->kv_dtype == B200_F16 || a->kv_dtype == B200_BF16;
     if (a->kv_dtype != a->q_dtype && a->kv_dtype != B200_FP8 && !(a->q_dtype == B200_F32 && kv16))
         return set_error(B200_ERR_BAD_ARG, "flash-attn: k/v dtype must match q or be F8E4M3");
-    if (a->d != 64 && a->d != 128) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "flash_attn: head dim %u (fused kernel: 64, 128)", a->d);
+    // the reference's kernels take any head dim up to 256 (candle-core/src/accel/attention.rs:283-290); the tensor core tiles
+    // here take the multiples of 8 among them (16-byte chunks of 16-bit elements)
+    if (a->d == 0 || a->d > 256 || a->d % 8) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "flash_attn: head dim %u (fused kernel: multiples of 8 up to 256)", a->d);
     if (a->varlen && (!a->cu_q || !a->cu_k)) return set_error(B200_ERR_BAD_ARG, "flash_attn: varlen needs cu_q and cu_k");
     const bool fp8 = a->kv_dtype == B200_FP8;
     if (kv16) {
@@ -429,7 +439,7 @@ static int fa_plan(const B200FaArgs *a, FaPlan &pl) {
     if (!fa_prefill_sm100_supported(p, kv16)) p.n_splits = std::max(splits, 1u);
     if ((uint64_t)a->b * p.n_splits > 65535) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "flash_attn: batch x splits too large");
     pl.grid = dim3(row_tiles, a->hkv, a->b * p.n_splits);
-    const size_t rowb = a->d * 2 + 16;
+    const size_t rowb = (a->d <= 64 ? 64 : (a->d <= 128 ? 128 : 256)) * 2 + 16;
     pl.smem = (FA_BM + 4 * FA_BN) * rowb;
     const size_t part_o = p.n_splits > 1 ? (size_t)p.n_splits * p.rows_total * a->d * 4 : 0;
     pl.off_lse = (part_o + 255) / 256 * 256;
@@ -453,7 +463,7 @@ static int fa_launch(const FaPlan &pl, cudaStream_t stream) {
     if (rc) return rc;
     if (pl.p.n_splits > 1) {
         const unsigned gx = (unsigned)std::min<uint64_t>((pl.p.rows_total + 3) / 4, 148ull * 16);
-        fa_combine_kernel<<<gx, 128, 0, stream>>>(pl.p.part_o, pl.p.part_lse, pl.p.o, pl.p.q_dtype, pl.p.rows_total, HD, pl.p.n_splits);
+        fa_combine_kernel<<<gx, 128, 0, stream>>>(pl.p.part_o, pl.p.part_lse, pl.p.o, pl.p.q_dtype, pl.p.rows_total, pl.p.d, pl.p.n_splits);
         rc = check_launch("fa_combine");
     }
     return rc;
@@ -486,8 +496,9 @@ extern "C" int b200_flash_attn(const B200FaArgs *a, b200_stream_t stream_) {
     const bool bf = pl.bf16;
     // long prefill chunks: tiles on the tcgen05 tensor cores
     if (fa_prefill_sm100_supported(pl.p, pl.p.kv_kind == 0)) return fa_prefill_sm100_launch(pl.p, bf, stream);
-    if (a->d == 64) return bf ? fa_launch<64, true>(pl, stream) : fa_launch<64, false>(pl, stream);
-    return bf ? fa_launch<128, true>(pl, stream) : fa_launch<128, false>(pl, stream);
+    if (a->d <= 64) return bf ? fa_launch<64, true>(pl, stream) : fa_launch<64, false>(pl, stream);
+    if (a->d <= 128) return bf ? fa_launch<128, true>(pl, stream) : fa_launch<128, false>(pl, stream);
+    return bf ? fa_launch<256, true>(pl, stream) : fa_launch<256, false>(pl, stream);
 }
 
 // Auxiliary streams of b200_fa_prefill_append: a few per device, each with its fork / join events (created on first

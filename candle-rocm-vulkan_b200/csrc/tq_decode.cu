@@ -415,6 +415,7 @@ namespace b200 {
 // tq_generic.cu: formats and head dims outside the tensor-core kernel
 int tq_generic_launch(const B200TqAttnArgs *a, cudaStream_t stream);
 bool tq_generic_takes(const B200TqAttnArgs *a);
+size_t tq_generic_workspace_bytes(const B200TqAttnArgs *a);
 }  // namespace b200
 
 // A paged call that the tensor-core kernel can serve once the blocks are compacted: the dense twin of the call (rows in
@@ -428,6 +429,7 @@ struct PagedFast {
 static bool paged_fast_plan(const B200TqAttnArgs *a, PagedFast &f) {
     static const bool off = diag_env("B200_PAGED_IN_PLACE") != nullptr;
     if (off || !a || !a->pages || a->n_pages == 0 || a->kv_len_dev || a->lk == 0 || a->b == 0 || a->hkv == 0) return false;
+    if (a->flags & B200_TQ_IN_PLACE) return false;
     B200RowLayout kl, vl;
     if (b200_row_layout(a->kq.mode, a->kq.bits, (int)a->d, &kl) || b200_row_layout(a->vq.mode, a->vq.bits, (int)a->d, &vl)) return false;
     f.kw = (uint32_t)kl.row_words;
@@ -467,6 +469,7 @@ static size_t paged_prefix_bytes(uint32_t n_pages) { return ((size_t)(n_pages + 
 static bool paged_direct_plan(const B200TqAttnArgs *a, DecodePlan &pl) {
     static const bool off = diag_env("B200_PAGED_NO_WALK") != nullptr;  // diagnostic: paged rows on the compaction / general paths
     if (off || !a || !a->pages || a->n_pages == 0 || a->lk == 0 || a->b == 0 || a->kq.mode != a->vq.mode) return false;
+    if (a->flags & B200_TQ_IN_PLACE) return false;  // the caller asked for the general kernel
     B200TqAttnArgs t = *a;
     t.flags &= ~(B200_TQ_AFTER_PREV | B200_TQ_INPUTS_FINAL);  // the prefix kernel of the call runs right before the attention
     if (tq_generic_takes(&t) && (a->d != 64 && a->d != 128 && a->d != 256)) return false;
@@ -485,7 +488,7 @@ extern "C" size_t b200_tq_attention_workspace_bytes(const B200TqAttnArgs *a) {
         PagedFast f;
         if (paged_fast_plan(a, f)) return f.need;
     }
-    if (tq_generic_takes(a)) return 16;  // the general kernel needs no scratch; 0 is reserved for "cannot be planned"
+    if (tq_generic_takes(a)) return tq_generic_workspace_bytes(a);
     DecodePlan pl;
     if (make_plan(a, pl)) return 0;
     return pl.ws_bytes;

@@ -4,8 +4,12 @@
 // candle-core/kernels/turbo_quant_impl.h tq_attnp*). Same semantics as
 // tq_decode.cuh (candle-core/kernels/turbo_quant_impl.h:232-619), plain f32 arithmetic: one block per output
 // row, its 8 warps take every 8th key, a lane holds the dims lane, lane + 32, ...; scores by warp reduction,
-// one online softmax per warp, the 8 partial results merged in shared memory. Not a fast path: it exists so
-// that every row format the quantizer can write can also be attended over.
+// one online softmax per warp, the 8 partial results merged in shared memory. Calls with few output rows are
+// split along the keys (grid y): every split leaves an unnormalised partial row with its maximum and sum in the
+// workspace and tq_generic_merge_kernel finishes the rows. Not a fast path: it exists so that every row format
+// the quantizer can write can also be attended over.
+#include <algorithm>
+
 #include "common.cuh"
 #include "tq_decode.cuh"
 
@@ -32,8 +36,24 @@ __device__ __forceinline__ float tq_elem(const uint32_t *r, uint32_t j, const Ge
     return e4m3_to_f(c);
 }
 
+// normalise, rotate back and store one output row held as o[k] = dims lane + 32 k of a warp (row: scratch of D floats)
+__device__ __forceinline__ void generic_store_row(const DecodeParams &p, float *row, const float (&o)[GMAX], float inv, uint32_t b,
+                                                  uint32_t h, uint32_t i, int lane) {
+    const uint32_t D = p.d, nk = D / 32;
+    for (uint32_t k = 0; k < nk; ++k) row[lane + 32 * k] = o[k] * inv;
+    __syncwarp();
+    if (p.v.rot == B200_ROT_HADAMARD) {
+        warp_hadamard(row, (int)D, p.v.signs, false, lane);
+        __syncwarp();
+    }
+    const size_t obase = b * p.o_sb + h * p.o_sh + i * p.o_ss;
+    for (uint32_t k = 0; k < nk; ++k) store_elem_rt(p.out, obase + lane + 32 * k, row[lane + 32 * k], p.out_dtype);
+}
+
+// partial rows of the key splits: [row][split][D + 2] floats (the D sums, then the maximum and the sum of weights)
 __global__ void __launch_bounds__(GW * 32) tq_generic_kernel(const DecodeParams p, const GenericSide ks, const GenericSide vs,
-                                                             const B200Page *__restrict__ pages, const uint32_t n_pages) {
+                                                             const B200Page *__restrict__ pages, const uint32_t n_pages,
+                                                             float *__restrict__ partial) {
     __shared__ float qrow[GMAX * 32];
     __shared__ float qsrow[GMAX * 32];  // prod keys: S q
     __shared__ float part[GW][GMAX * 32 + 2];
@@ -53,6 +73,11 @@ __global__ void __launch_bounds__(GW * 32) tq_generic_kernel(const DecodeParams 
     long long lo = p.wl >= 0 ? max(pos - p.wl, 0ll) : 0ll, hi = p.wr >= 0 ? min(pos + p.wr + 1, (long long)lk) : (long long)lk;
     lo = min(lo, (long long)lk);
     hi = max(hi, lo);
+    if (gridDim.y > 1) {  // this split's share of the visible keys
+        const long long chunk = (hi - lo + gridDim.y - 1) / gridDim.y;
+        lo = min(lo + (long long)blockIdx.y * chunk, hi);
+        hi = min(lo + chunk, hi);
+    }
     // query row, rotated like the keys (prod keys: the caller's rotated query, followed by S q)
     const bool prod = ks.mode == B200_TURBO_PROD;
     if (warp == 0) {
@@ -148,16 +173,41 @@ __global__ void __launch_bounds__(GW * 32) tq_generic_kernel(const DecodeParams 
             for (int k = 0; k < GMAX; ++k)
                 if ((uint32_t)k < nk) o[k] = fmaf(f, part[w][lane + 32 * k], o[k]);
         }
-        const float inv = lt > 0.0f ? 1.0f / lt : 0.0f;
-        for (uint32_t k = 0; k < nk; ++k) qrow[lane + 32 * k] = o[k] * inv;
-        __syncwarp();
-        if (p.v.rot == B200_ROT_HADAMARD) {
-            warp_hadamard(qrow, (int)D, p.v.signs, false, lane);
-            __syncwarp();
+        if (gridDim.y > 1) {
+            float *dst = partial + (row * gridDim.y + blockIdx.y) * (size_t)(D + 2);
+            for (uint32_t k = 0; k < nk; ++k) dst[lane + 32 * k] = o[k];
+            if (lane == 0) dst[D] = mx, dst[D + 1] = lt;
+            return;
         }
-        const size_t obase = b * p.o_sb + h * p.o_sh + i * p.o_ss;
-        for (uint32_t k = 0; k < nk; ++k) store_elem_rt(p.out, obase + lane + 32 * k, qrow[lane + 32 * k], p.out_dtype);
+        generic_store_row(p, qrow, o, lt > 0.0f ? 1.0f / lt : 0.0f, b, h, i, lane);
     }
+}
+
+// one warp per output row: the splits' partial rows weighted by exp(max_s - max), normalised, rotated back, stored
+__global__ void __launch_bounds__(GW * 32) tq_generic_merge_kernel(const DecodeParams p, const float *__restrict__ partial,
+                                                                   const uint32_t nsplit, const uint64_t rows) {
+    __shared__ float scratch[GW][GMAX * 32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint64_t row = (uint64_t)blockIdx.x * GW + warp;
+    if (row >= rows) return;
+    const uint32_t D = p.d, nk = D / 32;
+    const uint32_t i = (uint32_t)(row % p.lq), h = (uint32_t)((row / p.lq) % p.hq), b = (uint32_t)(row / ((size_t)p.lq * p.hq));
+    const float *src = partial + row * nsplit * (size_t)(D + 2);
+    float mx = -INFINITY;
+    for (uint32_t s = 0; s < nsplit; ++s) mx = fmaxf(mx, src[s * (size_t)(D + 2) + D]);
+    float lt = 0.0f, o[GMAX];
+#pragma unroll
+    for (int k = 0; k < GMAX; ++k) o[k] = 0.0f;
+    for (uint32_t s = 0; s < nsplit; ++s) {
+        const float *ps = src + s * (size_t)(D + 2);
+        const float ms = ps[D];
+        const float f = ms == -INFINITY ? 0.0f : expf(ms - mx);
+        lt += f * ps[D + 1];
+#pragma unroll
+        for (int k = 0; k < GMAX; ++k)
+            if ((uint32_t)k < nk) o[k] = fmaf(f, ps[lane + 32 * k], o[k]);
+    }
+    generic_store_row(p, scratch[warp], o, lt > 0.0f ? 1.0f / lt : 0.0f, b, h, i, lane);
 }
 
 // 0 when the call is one this kernel takes (and the tensor-core kernel does not)
@@ -200,6 +250,22 @@ int tq_generic_plan(const B200TqAttnArgs *a, DecodeParams &p, GenericSide &ks, G
     return 0;
 }
 
+// Key splits of a call: enough blocks for four per SM, at least 256 keys per split (a->lk: the capacity bound of a
+// ragged call, the sum of the blocks' rows of a paged one), at most 64. Depends on the shape only, so a paged call and
+// the dense call over the same rows split alike.
+static uint32_t generic_splits(const B200TqAttnArgs *a) {
+    const uint64_t rows = (uint64_t)a->b * a->hq * a->lq;
+    if (rows == 0 || rows >= 4ull * 148) return 1;
+    const uint64_t by_blocks = (4ull * 148 + rows - 1) / rows, by_keys = std::max<uint64_t>(a->lk / 256, 1);
+    return (uint32_t)std::min<uint64_t>(std::min(by_blocks, by_keys), 64);
+}
+
+size_t tq_generic_workspace_bytes(const B200TqAttnArgs *a) {
+    const uint32_t ns = generic_splits(a);
+    // 16: the general kernel needs no scratch without splits; 0 is reserved for "cannot be planned"
+    return ns > 1 ? (size_t)a->b * a->hq * a->lq * ns * (a->d + 2) * sizeof(float) : 16;
+}
+
 int tq_generic_launch(const B200TqAttnArgs *a, cudaStream_t stream) {
     DecodeParams p;
     GenericSide ks, vs;
@@ -208,8 +274,15 @@ int tq_generic_launch(const B200TqAttnArgs *a, cudaStream_t stream) {
     if (rows == 0) return B200_OK;
     if (!a->q || !a->out || (!a->pages && (!a->k_rows || !a->v_rows))) return set_error(B200_ERR_BAD_ARG, "tq_attention: null pointer");
     if (rows > 0x7fffffffull) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "tq_attention: too many output rows");
-    tq_generic_kernel<<<(unsigned)rows, GW * 32, 0, stream>>>(p, ks, vs, a->pages, a->n_pages);
-    return check_launch("tq_attention (general kernel)");
+    uint32_t ns = generic_splits(a);
+    // a caller that sized its workspace for no splits (or passed none) still gets its result, from one block per row
+    if (ns > 1 && (!a->workspace || a->workspace_bytes < tq_generic_workspace_bytes(a))) ns = 1;
+    float *partial = ns > 1 ? reinterpret_cast<float *>(a->workspace) : nullptr;
+    tq_generic_kernel<<<dim3((unsigned)rows, ns), GW * 32, 0, stream>>>(p, ks, vs, a->pages, a->n_pages, partial);
+    int rc = check_launch("tq_attention (general kernel)");
+    if (rc || ns == 1) return rc;
+    tq_generic_merge_kernel<<<(unsigned)((rows + GW - 1) / GW), GW * 32, 0, stream>>>(p, partial, ns, rows);
+    return check_launch("tq_attention (general kernel, merge)");
 }
 
 bool tq_generic_takes(const B200TqAttnArgs *a) {

@@ -470,7 +470,7 @@ class PackedBlocksAttention:
         args.k_strides, args.v_strides = A.u64x3(0, 0, kw), A.u64x3(0, 0, vw)  # only the row stride is common to the blocks
         args.pages, args.n_pages = pages.data_ptr(), len(blocks)
         args.kv_len_dev = kv_len.data_ptr() if kv_len is not None else None
-        args.flags = A.TQ_AFTER_PREV if after_prev else 0
+        args.flags = (A.TQ_AFTER_PREV if after_prev else 0) | (A.TQ_IN_PLACE if in_place else 0)
         args.b, args.lq, args.lk, args.hq, args.hkv, args.d = b, lq, lk, hq, hkv, d
         args.kq, args.vq = kq.side(), vq.side()
         args.scale, args.softcap = cfg.softmax_scale, cfg.softcap or 0.0
@@ -478,8 +478,9 @@ class PackedBlocksAttention:
         args.alibi, args.alibi_bstride = (alibi.data_ptr() if alibi is not None else None), abs_
         args.workspace, args.workspace_bytes, args.status = None, 0, None
         # with the workspace the library asks for, the tensor-core kernel walks the table (or the blocks are compacted
-        # into the workspace first); `in_place=True` keeps the general kernel that reads the blocks where they are
-        need = 16 if in_place else int(A.lib().b200_tq_attention_workspace_bytes(C.byref(args)))
+        # into the workspace first); `in_place=True` (B200_TQ_IN_PLACE) keeps the general kernel that reads the blocks
+        # where they are
+        need = int(A.lib().b200_tq_attention_workspace_bytes(C.byref(args)))
         if need == 0:
             A.check(A.lib().b200_tq_attention(C.byref(args), _stream(q.device)))  # raises with the library's reason
         ws = _workspace(q.device, need)
@@ -592,7 +593,23 @@ class TurboKvCache:
             b, h, self.len, self.dim).to(dt)
         return deq(self.kq, self.k), deq(self.vq, self.v)
 
+    # query rows per kv head (tokens x heads of the group) from which a chunk of prefill over the cache goes through
+    # the dequantized rows and the tensor-core prefill tiles instead of the decode kernel, which re-reads the packed
+    # rows once per pack of eight query rows
+    PREFILL_ROWS = 512
+
     def attention(self, q: torch.Tensor, cfg: FlashAttnConfig) -> torch.Tensor:
+        """Attention of `q: (batch, q_heads, seq_q, head_dim)` over the cache (turbo_quant.rs:968-990). Decode and
+        short chunks: the fused kernel over the packed rows. Long chunks (chunked prefill over an already compressed
+        cache): the reference's own second route, `keys_values()` + `flash_attn_bhsd` (turbo_quant.rs:986-990), whose
+        attention here runs on the tcgen05 prefill tiles."""
         if self.k is None:
             raise RuntimeError("turbo-quant cache: attention on an empty cache")
+        b, hq, lq, d = q.shape
+        hkv = self.k.shape[1]
+        if (d == 128 and q.dtype in (torch.float16, torch.bfloat16) and hkv and hq % hkv == 0
+                and lq * (hq // hkv) >= self.PREFILL_ROWS and self.kq.qjl is None):
+            from .flash_attn import flash_attn_bhsd
+            k, v = self.keys_values()
+            return flash_attn_bhsd(q, k.to(q.dtype), v.to(q.dtype), cfg)
         return attention_packed(q, self.k, self.v, self.len, self.kq, self.vq, cfg)

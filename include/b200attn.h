@@ -292,9 +292,15 @@ typedef struct B200TqAttnArgs {
  * (fresh_rows = 1: q was produced before that kernel), and for attention calls that follow one another over caches
  * nobody writes (fresh_rows = 0). The outputs are those of the plain call. */
 #define B200_TQ_INPUTS_FINAL 2u
-/* Paged calls (pages != NULL): the size returned covers a compacted copy of all valid rows; with that much workspace
- * (256-byte aligned) one copy kernel gathers the blocks and the tensor-core kernel runs, with less (16 bytes are
- * enough) the general kernel reads the blocks in place. lk is an upper bound of the sum of the blocks' rows. */
+/* Paged calls (pages != NULL): the blocks are read where they are, without a copy, by the general kernel; by the
+ * tensor-core kernel too when keys and values share one of its formats (it walks the block table). Other format pairs
+ * of the tensor-core kernel are compacted into the workspace by one copy kernel first, unless this flag is set: then
+ * the general kernel serves the call (split along the keys when the output rows are few) and the workspace asked
+ * for is only that of its partial rows. */
+#define B200_TQ_IN_PLACE 4u
+/* Paged calls: the size returned covers what the route above needs (the block prefix table of the walking kernel, or a
+ * compacted copy of all valid rows, or the general kernel's partial rows); with less the call still runs, on the general
+ * kernel with one block per output row (16 bytes are enough). lk is an upper bound of the sum of the blocks' rows. */
 size_t b200_tq_attention_workspace_bytes(const B200TqAttnArgs *args);
 int b200_tq_attention(const B200TqAttnArgs *args, b200_stream_t stream);
 
@@ -364,7 +370,9 @@ int b200_tq_attention_gather(const B200TqAttnArgs *args, const B200PeerGather *g
  * side of candle_flash_attn::flash_attn / flash_attn_varlen (candle-flash-attn/src/lib.rs:149-345).
  * Arguments are the kernel parameter list FA_PARAMS (flash_attn_impl.h:29-35): q (b, lq, hq, d),
  * k / v (b, lk, hkv, d) with (batch, seq, head) element strides; varlen: q (total_q, hq, d) with
- * cu_q / cu_k u32 offsets (b + 1 entries), lq / lk the maxima. o: (token, head, d) contiguous. */
+ * cu_q / cu_k u32 offsets (b + 1 entries), lq / lk the maxima. o: (token, head, d) contiguous.
+ * Head dims: every multiple of 8 up to 256 (kernel_supported of candle-core/src/accel/attention.rs:283-290 takes any
+ * d <= 256; others return B200_ERR_UNSUPPORTED_SHAPE and the caller's unfused path serves them). */
 typedef struct B200FaArgs {
     const void *q, *k, *v;
     void *o;

@@ -69,6 +69,10 @@ GENERAL_CASES = [
     ("turbo1_turbo4_d64", (0, 1), (0, 4), 1, 3, 90, 2, 1, 64, 20, 0, 0.0, "none"),
     ("mxfp4_d96", (2, 4), (2, 4), 2, 1, 200, 4, 2, 96, -1, 0, 15.0, "none"),
     ("fp8_nvfp4_d32", (5, 4), (3, 4), 1, 2, 77, 2, 2, 32, -1, -1, 0.0, "none"),
+    # few output rows over many keys: the call is split along the keys and a second kernel merges the partial rows
+    ("split_turbo2_hadamard", (0, 2), (0, 2), 2, 1, 2600, 4, 2, 128, -1, 0, 0.0, "hadamard"),
+    ("split_mxfp8_d96_window", (4, 4), (4, 4), 3, 2, 1500, 2, 1, 96, 700, 0, 0.0, "none"),
+    ("split_turbo3_softcap", (0, 3), (0, 1), 1, 1, 5000, 8, 8, 64, -1, 0, 10.0, "none"),
 ]
 
 
@@ -783,6 +787,35 @@ def test_paged_blocks_equal_the_concatenated_rows(P, oracle, kf, vf):
     plain = P.attention_packed_blocks(to_dev(q), blocks, kq, vq, c)
     for _ in range(3):
         assert torch.equal(P.attention_packed_blocks(to_dev(q), blocks, kq, vq, c, after_prev=True), plain)
+
+
+def test_long_paged_rows_in_place_on_the_general_kernel(P, oracle):
+    """B200_TQ_IN_PLACE: keys and values in different formats over 30 blocks, read where they are by the general kernel,
+    which splits the 2 400 keys of the few output rows; against the oracle on the concatenated rows, and the same
+    call without a workspace (one block per row) within rounding of it."""
+    b, hq, hkv, d, lq = 1, 4, 2, 128, 1
+    kf, vf = (5, 4), (2, 4)
+    kq, vq = P.TurboQuantizer(fmt(P, *kf), d, "none", 42), P.TurboQuantizer(fmt(P, *vf), d, "none", 44)
+    blocks, kcat, vcat = [], [], []
+    g = torch.Generator(device="cuda:0").manual_seed(5)
+    for n in range(30):
+        cap, rows = 96, 96 - (n % 5) * 8
+        kb = kq.quantize_rows(torch.randn((b * hkv * cap, d), generator=g, device="cuda:0")).view(b, hkv, cap, -1).contiguous()
+        vb = vq.quantize_rows(torch.randn((b * hkv * cap, d), generator=g, device="cuda:0")).view(b, hkv, cap, -1).contiguous()
+        blocks.append(P.KvBlockRef(kb, vb, rows))
+        kcat.append(words(kb)[:, :, :rows])
+        vcat.append(words(vb)[:, :, :rows])
+    kd, vd = np.concatenate(kcat, axis=2), np.concatenate(vcat, axis=2)
+    lk = kd.shape[2]
+    q = oracle.normal(19, b * hq * lq * d).reshape(b, hq, lq, d)
+    c = P.FlashAttnConfig(d ** -0.5).causal()
+    want = oracle.tq_attention(q, np.ascontiguousarray(kd), np.ascontiguousarray(vd), lk, kf, vf, d ** -0.5, np.zeros(64, np.float32), wr=0)
+    call = P.PackedBlocksAttention(to_dev(q), blocks, kq, vq, c, in_place=True)
+    assert call.args.workspace_bytes > 16  # partial rows of the key splits
+    got = call.run().cpu().numpy()
+    assert_close(got, want, what="paged in place, split")
+    call.args.workspace_bytes = 16  # too small for the splits: one block per output row
+    assert_close(call.run().cpu().numpy(), want, what="paged in place, no split")
 
 
 @pytest.mark.parametrize("f,d", [((2, 4), 128), ((4, 4), 128), ((0, 4), 64), ((5, 4), 256), ((3, 4), 128)])

@@ -89,6 +89,14 @@ ORACLE_CASES = [
     # 1024 packed rows and more: blocks of two row tiles
     ("tc2_ragged_rows", "bf16", 1, 530, 900, 4, 2, 128, -1, 0, 0.0, False, False),
     ("tc2_window", "f16", 2, 300, 640, 8, 2, 128, 70, 0, 0.0, False, False),
+    # every head dim that is a multiple of 8 up to 256 (the reference takes any d <= 256): buckets 64 / 128 / 256
+    ("d256_decode", "bf16", 2, 1, 2200, 8, 2, 256, -1, 0, 0.0, False, False),
+    ("d256_prefill", "f16", 1, 140, 200, 4, 2, 256, -1, 0, 0.0, False, False),
+    ("d256_fp8_window", "bf16", 1, 70, 300, 4, 1, 256, 50, 0, 0.0, False, True),
+    ("d192_f32_alibi", "f32", 1, 66, 130, 6, 3, 192, -1, 0, 15.0, True, False),
+    ("d96_prefill", "f16", 2, 90, 90, 4, 2, 96, -1, 0, 0.0, False, False),
+    ("d40_decode", "bf16", 1, 2, 1300, 4, 4, 40, -1, 0, 0.0, False, False),
+    ("d8_noncausal", "f16", 1, 33, 47, 2, 1, 8, -1, -1, 0.0, False, False),
 ]
 
 
@@ -323,10 +331,11 @@ def test_argument_errors(P):
     k = torch.zeros((1, 4, 4, 128), device="cuda:0", dtype=torch.float16)
     with pytest.raises(ValueError, match="not a multiple"):
         F.flash_attn(q, k, k, 1.0, False)
-    q96 = torch.zeros((1, 4, 4, 96), device="cuda:0", dtype=torch.float16)
-    with pytest.raises(A.B200Error) as e:
-        F.flash_attn(q96, q96, q96, 1.0, False)
-    assert e.value.code == A.ERR_UNSUPPORTED_SHAPE
+    for d_bad in (100, 264):  # not a multiple of 8; above 256
+        qb = torch.zeros((1, 4, 4, d_bad), device="cuda:0", dtype=torch.float16)
+        with pytest.raises(A.B200Error) as e:
+            F.flash_attn(qb, qb, qb, 1.0, False)
+        assert e.value.code == A.ERR_UNSUPPORTED_SHAPE
     with pytest.raises(A.B200Error, match="must match q"):
         F.flash_attn(q[:, :, :4], k.to(torch.bfloat16), k.to(torch.bfloat16), 1.0, False)
     with pytest.raises(RuntimeError, match="no CPU path"):
