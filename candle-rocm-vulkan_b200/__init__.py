@@ -7,5 +7,7 @@ so load it with `__graft_entry__.load_package()`, which registers it as `candle_
 """
 from . import _abi  # noqa: F401
 from . import flash_attn  # noqa: F401
+from . import offload  # noqa: F401
+from .offload import CopyEvent, CopyStream, PinnedHostBuffer  # noqa: F401
 from .turbo_quant import (FlashAttnConfig, KvBlockRef, OutputGather, PackedAttention, PackedBlocksAttention, QuantFormat,  # noqa: F401
                           QuantizedTensor, TurboKvCache, TurboQuantizer, attention_packed, attention_packed_blocks)

@@ -110,6 +110,9 @@ SYMBOLS = [
     "b200_tq_attention_workspace_bytes", "b200_tq_attention", "b200_tq_attention_static", "b200_tq_attention_gather",
     "b200_flash_attn_workspace_bytes",
     "b200_flash_attn", "b200_fa_prefill_append", "b200_device_wait_status", "b200_device_wait_check",
+    "b200_pinned_alloc", "b200_pinned_free", "b200_pinned_len", "b200_pinned_wait_idle", "b200_pinned_ptr",
+    "b200_copy_upload", "b200_copy_download", "b200_copy_event_wait_on_compute", "b200_copy_event_synchronize",
+    "b200_copy_event_is_complete", "b200_copy_event_free", "b200_copy_stream_synchronize",
 ]
 
 _lib = None
@@ -153,6 +156,19 @@ def lib():
         l.b200_flash_attn.argtypes = [C.POINTER(FaArgs), C.c_void_p]
         l.b200_fa_prefill_append.argtypes = [C.POINTER(FaArgs), C.POINTER(KvAppendArgs), C.c_void_p]
         l.b200_device_wait_check.argtypes = [C.c_int]
+        l.b200_pinned_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]
+        l.b200_pinned_free.argtypes = [C.c_void_p]
+        l.b200_pinned_len.argtypes = [C.c_void_p]
+        l.b200_pinned_len.restype = C.c_size_t
+        l.b200_pinned_wait_idle.argtypes = [C.c_void_p]
+        l.b200_pinned_ptr.argtypes = [C.c_void_p]
+        l.b200_pinned_ptr.restype = C.c_void_p
+        l.b200_copy_upload.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.POINTER(C.c_void_p)]
+        l.b200_copy_download.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.POINTER(C.c_void_p)]
+        l.b200_copy_event_wait_on_compute.argtypes = [C.c_void_p, C.c_void_p]
+        l.b200_copy_event_synchronize.argtypes = [C.c_void_p]
+        l.b200_copy_event_is_complete.argtypes = [C.c_void_p]
+        l.b200_copy_event_free.argtypes = [C.c_void_p, C.c_void_p]
         _lib = l
     return _lib
 

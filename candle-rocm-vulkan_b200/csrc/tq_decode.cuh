@@ -54,6 +54,11 @@ constexpr int CTR_COLS = 8192;   // columns a call may have for the decode grid 
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
+// branch hints: the rare side of a branch inside the tile loop is laid out behind the loop, which keeps the loop's
+// instructions close together (the loop is larger than the instruction cache nearest to the schedulers)
+#define B200_LIKELY(x) __builtin_expect(!!(x), 1)
+#define B200_UNLIKELY(x) __builtin_expect(!!(x), 0)
+
 struct DecodeSide {
     int32_t mode, code_words, rsc_off;
     int32_t rot;
@@ -599,7 +604,7 @@ __device__ __forceinline__ bool softmax_plain(const float (&sr)[2][4], const flo
     float c1 = fmaxf(fmaxf(fmaf(sr[0][1], qs2[1], vm[0].y), fmaf(sr[0][3], qs2[1], vm[1].y)),
                      fmaxf(fmaf(sr[1][1], qs2[1], vm[2].y), fmaf(sr[1][3], qs2[1], vm[3].y)));
     const bool moved = __any_sync(0xffffffffu, c0 > M[0] + MAX_SLACK || c1 > M[1] + MAX_SLACK);
-    if (moved) {
+    if (B200_UNLIKELY(moved)) {
 #pragma unroll
         for (int o = 4; o < 32; o <<= 1) {
             c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, o));
@@ -650,7 +655,7 @@ __device__ __forceinline__ bool softmax_masked(const float (&sr)[2][4], const fl
     float c0 = fmaxf(fmaxf(s2[0] + vm[0].y, s2[2] + vm[1].y), fmaxf(s2[4] + vm[2].y, s2[6] + vm[3].y));
     float c1 = fmaxf(fmaxf(s2[1] + vm[0].y, s2[3] + vm[1].y), fmaxf(s2[5] + vm[2].y, s2[7] + vm[3].y));
     const bool moved = __any_sync(0xffffffffu, c0 > M[0] + MAX_SLACK || c1 > M[1] + MAX_SLACK);
-    if (moved) {
+    if (B200_UNLIKELY(moved)) {
 #pragma unroll
         for (int o = 4; o < 32; o <<= 1) {
             c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, o));
@@ -1390,8 +1395,8 @@ struct CopySide {
         const DecodeParams &p = w.p;
         const int lane = w.lane;
         // rows that the stream's previous kernel may still be writing are not copied before it is done
-        if (!w.waited && key + min(WK, iseg.col.hi - key) > iseg.col.lk - (int)p.fresh_rows) w.prev_done();
-        if (simple > 0) {
+        if (B200_UNLIKELY(!w.waited && key + min(WK, iseg.col.hi - key) > iseg.col.lk - (int)p.fresh_rows)) w.prev_done();
+        if (B200_LIKELY(simple > 0)) {
             --simple;
             if (lane == 0) {
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kb + vb) : "memory");
@@ -1441,7 +1446,7 @@ struct CopySide {
         k += (uintptr_t)WK * krb;
         v += (uintptr_t)WK * vrb;
         key += WK;
-        if (--left == 0 && more) {
+        if (B200_UNLIKELY(--left == 0 && more)) {
             more = next_segment(iseg, p, w.ny, x_end);
             if (more) enter(p, krb, vrb);
         }
@@ -1491,7 +1496,7 @@ __device__ __forceinline__ bool tile_softmax(const DecodeParams &p, const Segmen
     float2 vm[4];  // (sigma, log2 sigma) of the keys g, g + 8, g + 16, g + 24
 #pragma unroll
     for (int k = 0; k < 4; ++k) vm[k] = lds64f(vmeta_g + k * 64);
-    if (sm.plain && nkeys == WK && key0 >= sm.LOmax && key0 + WK <= sm.HImin) return softmax_plain(sr, vm, qs2, M, lsum, pb, al);
+    if (B200_LIKELY(sm.plain && nkeys == WK && key0 >= sm.LOmax && key0 + WK <= sm.HImin)) return softmax_plain(sr, vm, qs2, M, lsum, pb, al);
     // masks, soft-capping, ALiBi: the two query rows whose scores this lane holds (columns 2c, 2c + 1)
     const uint32_t hk = seg.y / p.packs, pack = seg.y % p.packs, G = p.group;
     RowMask rm;
@@ -1662,7 +1667,7 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
             uint32_t kt_off = koff + k_lane, vt_off = k_stage_bytes + voff + v_lane;
             uint32_t kr_off = koff + lane * krb, vr_off = k_stage_bytes + voff + lane * vrb;
             for (int n = 0; n < n_t; ++n, key0 += WK) {
-                if (!stage_wait(c_bar, par)) {
+                if (B200_UNLIKELY(!stage_wait(c_bar, par))) {
                     // the copy never landed: give up on the keys (the outputs are void, the status says so), stop
                     // copying, but keep counting this worker's segments so that no column waits for it
                     wait_failed = true;
@@ -1685,7 +1690,7 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                     kr_off = dk + lane * krb;
                     vr_off = k_stage_bytes + dv + lane * vrb;
                 }
-                if (nkeys < WK) clear_stale_rows(st_s + tk_off, st_s + k_stage_bytes + tv_off, nkeys, krb, vrb, lane);
+                if (B200_UNLIKELY(nkeys < WK)) clear_stale_rows(st_s + tk_off, st_s + k_stage_bytes + tv_off, nkeys, krb, vrb, lane);
                 // ---- per-key scalars of the tile, lane = key
                 tile_meta<KM, VM, HD>(st_s + kr_off, st_s + vr_off, meta_s, vmeta_s, vsc_s, lane);
                 // ---- scores of the 32 keys: sr[u][2 k + e] = key 16 u + g + 8 k, row 2c + e
@@ -1695,7 +1700,7 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                 // ---- online softmax
                 uint32_t pb[4];
                 float al[2];
-                if (tile_softmax(p, seg, sm, key0, nkeys, vmeta_g, sr, qs, qs2, M, lsum, pb, al, lane)) {
+                if (B200_UNLIKELY(tile_softmax(p, seg, sm, key0, nkeys, vmeta_g, sr, qs, qs2, M, lsum, pb, al, lane))) {
 #pragma unroll
                     for (int mt = 0; mt < STEPS; ++mt) {
                         oacc[mt][0] *= al[0];
@@ -1711,7 +1716,7 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                 // bulk copy of the next tile into it
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (cs.left > 0) copy_tile(c_st, c_bar, wdesc_s + 16u * (uint32_t)c_stage);
+                if (B200_LIKELY(cs.left > 0)) copy_tile(c_st, c_bar, wdesc_s + 16u * (uint32_t)c_stage);
                 c_st += stage_bytes;
                 c_bar += 8;
                 if (++c_stage == NS) {

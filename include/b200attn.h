@@ -415,6 +415,35 @@ int b200_device_wait_status(void);
  * B200_OK otherwise; clear != 0 also resets it, after which all kernels run normally again. */
 int b200_device_wait_check(int clear);
 
+/* ---- offloaded KV blocks: pinned host buffers and the device's copy stream ------------------------------------ */
+/* Replaces candle-core/src/cuda_backend/offload.rs:122-441 (PinnedHostBuffer, CopyStream, CopyEvent;
+ * CudaDevice::alloc_pinned / copy_stream), which the reference offers for packed KV blocks that live in host memory
+ * or on disk and are uploaded per step (candle-nn/src/turbo_quant.rs:999-1004). One non-blocking copy stream per
+ * device, shared by all callers. A copy starts after the work queued so far on `compute` and yields an event:
+ * b200_copy_event_wait_on_compute before kernels that read uploaded bytes (or overwrite / free the source of a
+ * download), b200_copy_event_synchronize before the host reads downloaded bytes. The device buffer must stay alive
+ * until the event was waited on or freed. b200_pinned_ptr waits for the copies queued on the buffer first, so a
+ * reused staging buffer is never rewritten while the DMA engine still reads it. */
+typedef struct B200PinnedBuffer B200PinnedBuffer; /* page-locked host memory, usable with every device */
+typedef struct B200CopyEvent B200CopyEvent;       /* completion of one queued copy */
+int b200_pinned_alloc(size_t bytes, B200PinnedBuffer **out);
+int b200_pinned_free(B200PinnedBuffer *buf);          /* waits for the copies queued on it */
+size_t b200_pinned_len(const B200PinnedBuffer *buf);
+int b200_pinned_wait_idle(B200PinnedBuffer *buf);
+void *b200_pinned_ptr(B200PinnedBuffer *buf);         /* the bytes, after the queued copies completed; NULL on error */
+/* src[src_off .. src_off + bytes) -> dst (device, dst_len bytes) at byte offset dst_off (offload.rs:345-379) */
+int b200_copy_upload(B200PinnedBuffer *src, size_t src_off, void *dst, size_t dst_len, size_t dst_off, size_t bytes,
+                     b200_stream_t compute, B200CopyEvent **event);
+/* src (device, src_len bytes) from byte offset src_off -> dst[dst_off .. dst_off + bytes) (offload.rs:385-419) */
+int b200_copy_download(const void *src, size_t src_len, size_t src_off, B200PinnedBuffer *dst, size_t dst_off, size_t bytes,
+                       b200_stream_t compute, B200CopyEvent **event);
+int b200_copy_event_wait_on_compute(B200CopyEvent *event, b200_stream_t compute); /* on the GPU; the host does not block */
+int b200_copy_event_synchronize(B200CopyEvent *event);                            /* blocks the calling thread */
+int b200_copy_event_is_complete(B200CopyEvent *event);                            /* 1 / 0, does not block */
+/* Releases the event; one that was never waited on first makes `compute` wait for the copy (offload.rs:259-266). */
+int b200_copy_event_free(B200CopyEvent *event, b200_stream_t compute);
+int b200_copy_stream_synchronize(void); /* every copy queued so far on the current device's copy stream */
+
 #ifdef __cplusplus
 }
 #endif

@@ -453,6 +453,28 @@ def test_hadamard_cache_end_to_end(P, oracle, f):
     assert_close(got, want, what=f"hadamard {f}", out="bf16")
 
 
+@pytest.mark.parametrize("f,rot", [((3, 4), "hadamard"), ((4, 4), "none")])
+def test_chunked_prefill_over_the_compressed_cache(P, oracle, f, rot):
+    """A chunk of 160 query tokens (640 rows per kv head) over 900 cached keys: the cache serves it from its dequantized
+    rows on the prefill tiles (the reference's keys_values + flash_attn_bhsd route, turbo_quant.rs:986-990). Against the
+    fused kernel over the packed rows, which computes the same attention pack by pack; the two differ by the rounding
+    of the dequantized rows and of the rotated queries to bf16."""
+    b, hq, hkv, d, lk, lq = 1, 8, 2, 128, 900, 160
+    g = torch.Generator(device="cuda:0").manual_seed(3)
+    k = torch.randn((b, hkv, lk, d), generator=g, device="cuda:0").to(torch.bfloat16)
+    v = torch.randn((b, hkv, lk, d), generator=g, device="cuda:0").to(torch.bfloat16)
+    q = torch.randn((b, hq, lq, d), generator=g, device="cuda:0").to(torch.bfloat16)
+    cache = P.TurboKvCache(fmt(P, *f), fmt(P, *f), d, rot, 42, lk)
+    cache.append(k, v)
+    c = P.FlashAttnConfig(d ** -0.5).causal()
+    assert lq * (hq // hkv) >= cache.PREFILL_ROWS
+    got = cache.attention(q, c).float().cpu().numpy()
+    want = P.attention_packed(q, cache.k, cache.v, cache.seq_len(), cache.kq, cache.vq, c).float().cpu().numpy()
+    assert_close(got, want, atol=3e-2, rtol=2e-2, what=f"chunked prefill {f} {rot}", out="bf16")
+    # and a short chunk stays on the fused kernel: identical to the direct call
+    assert torch.equal(cache.attention(q[:, :, -4:], c), P.attention_packed(q[:, :, -4:].contiguous(), cache.k, cache.v, lk, cache.kq, cache.vq, c))
+
+
 def test_config1_fp8_single_decode(P, oracle):
     """B=1, Hq=32, Hkv=8, D=128, 2048 keys, f16, FP8 rows with one f32 scale per token and head."""
     b, hq, hkv, d, lk = 1, 32, 8, 128, 2048
