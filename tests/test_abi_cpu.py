@@ -47,6 +47,45 @@ def test_struct_sizes_match_header(pkg):
         assert C.sizeof(names[n]) == int(sz), n
 
 
+def test_rust_sys_crate_mirrors_the_header():
+    """rust/b200attn-sys/src/lib.rs (not compiled here: no Rust toolchain) against the header, as text: every export,
+    every struct with its fields in order, every constant, and the struct sizes its own tests assert."""
+    import subprocess, tempfile, os
+    header = (ROOT / "include" / "b200attn.h").read_text()
+    rust = (ROOT / "rust" / "b200attn-sys" / "src" / "lib.rs").read_text()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    assert set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", header)) == set(re.findall(r"pub fn (b200_[a-z0-9_]+)\s*\(", rust))
+    for name, value in re.findall(r"#define (B200_[A-Z0-9_]+) \(?(-?\d+)u?\)?\s*$", header, flags=re.M):
+        m = re.search(rf"pub const {name}: [a-z_0-9]+ = (-?\d+);", rust)
+        assert m and int(m.group(1)) == int(value), name
+    rename = {"in": "input"}  # a Rust keyword
+    for name, body in re.findall(r"typedef struct (B200\w+) \{(.*?)\} \1;", header, flags=re.S):
+        fields = []
+        for decl in body.split(";"):
+            decl = decl.strip()
+            if not decl:
+                continue
+            # "const void *k, *v" / "uint64_t q_strides[3], out_strides[3]" / "char name[64]"
+            first, *rest = decl.split(",")
+            fields.append(re.findall(r"(\w+)(?:\[\d+\])?$", first.strip())[0])
+            fields += [re.findall(r"(\w+)(?:\[\d+\])?$", r.strip())[0] for r in rest]
+        m = re.search(rf"pub struct {name} \{{(.*?)\n\}}", rust, flags=re.S)
+        assert m, name
+        got = re.findall(r"pub (\w+):", m.group(1))
+        assert got == [rename.get(f, f) for f in fields], (name, got, fields)
+    sizes = dict(re.findall(r"size_of::<(B200\w+)>\(\), (\d+)\)", rust))
+    src = '#include <stdio.h>\n#include "b200attn.h"\nint main(void){' + "".join(
+        f'printf("{n} %zu\\n", sizeof({n}));' for n in sizes) + "return 0;}"
+    with tempfile.TemporaryDirectory() as td:
+        c = os.path.join(td, "s.c")
+        open(c, "w").write(src)
+        subprocess.run(["gcc", "-I", str(ROOT / "include"), c, "-o", os.path.join(td, "s")], check=True)
+        out = subprocess.run([os.path.join(td, "s")], check=True, capture_output=True, text=True).stdout
+    for line in out.splitlines():
+        n, sz = line.split()
+        assert int(sizes[n]) == int(sz), n
+
+
 def test_row_layouts_and_errors(pkg, oracle):
     A = pkg._abi
     for mode in (0, 2, 3, 4, 5):
