@@ -105,7 +105,7 @@ class FaArgs(C.Structure):
 # every symbol that include/b200attn.h declares
 SYMBOLS = [
     "b200_row_layout", "b200_codebook", "b200_hadamard_signs", "b200_qjl_matrix", "b200_row_group", "b200_split_count_grouped",
-    "b200_tq_residual", "b200_tq_signs",
+    "b200_tq_residual", "b200_tq_signs", "b200_rotation_matrix", "b200_tq_rotate_dense",
     "b200_describe", "b200_last_error", "b200_tq_rotate", "b200_tq_quantize", "b200_tq_dequantize", "b200_kv_append",
     "b200_tq_attention_workspace_bytes", "b200_tq_attention", "b200_tq_attention_static", "b200_tq_attention_gather",
     "b200_flash_attn_workspace_bytes",
@@ -137,6 +137,8 @@ def lib():
         l.b200_codebook.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_float)]
         l.b200_hadamard_signs.argtypes = [C.c_int, C.c_uint64, C.POINTER(C.c_float)]
         l.b200_qjl_matrix.argtypes = [C.c_int, C.c_uint64, C.POINTER(C.c_float)]
+        l.b200_rotation_matrix.argtypes = [C.c_int, C.c_uint64, C.POINTER(C.c_float)]
+        l.b200_tq_rotate_dense.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint32, C.c_int, C.c_void_p]
         l.b200_tq_residual.argtypes = [C.POINTER(TqResidArgs), C.c_void_p]
         l.b200_tq_signs.argtypes = [C.POINTER(TqSignsArgs), C.c_void_p]
         l.b200_row_group.argtypes = [C.c_int, C.c_int]

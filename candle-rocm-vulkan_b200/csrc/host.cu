@@ -158,6 +158,45 @@ extern "C" int b200_qjl_matrix(int dim, uint64_t seed, float *s_out) {
     return B200_OK;
 }
 
+// candle-core/src/accel/turbo.rs:204-229: the dense rotation for lengths that are not powers of two. Row-major
+// dim x dim: standard normals (Box-Muller in f64 over SplitMix64(seed ^ "ROTATE!!")), made orthonormal by two passes
+// of modified Gram-Schmidt in f64, rounded to f32.
+extern "C" int b200_rotation_matrix(int dim, uint64_t seed, float *m_out) {
+    if (!m_out) return set_error(B200_ERR_BAD_ARG, "rotation_matrix: null output");
+    if (dim <= 0 || dim > 1024) return set_error(B200_ERR_BAD_ARG, "rotation_matrix: dim %d outside 1..1024", dim);
+    uint64_t s = seed ^ 0x524f544154452121ull;
+    auto next_f64 = [&]() {
+        s += 0x9e3779b97f4a7c15ull;
+        uint64_t z = s;
+        z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+        z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+        z ^= z >> 31;
+        return ((double)(z >> 11) + 0.5) / 9007199254740992.0;
+    };
+    const size_t d = (size_t)dim;
+    std::vector<double> rows(d * d);
+    for (size_t i = 0; i < d * d; ++i) {
+        const double u1 = next_f64(), u2 = next_f64();
+        rows[i] = sqrt(-2.0 * log(u1)) * cos(2.0 * 3.14159265358979323846 * u2);
+    }
+    for (int pass = 0; pass < 2; ++pass)
+        for (size_t i = 0; i < d; ++i) {
+            double *ri = &rows[i * d];
+            for (size_t j = 0; j < i; ++j) {
+                const double *rj = &rows[j * d];
+                double dot = 0.0;
+                for (size_t t = 0; t < d; ++t) dot += ri[t] * rj[t];
+                for (size_t t = 0; t < d; ++t) ri[t] -= dot * rj[t];
+            }
+            double n = 0.0;
+            for (size_t t = 0; t < d; ++t) n += ri[t] * ri[t];
+            n = sqrt(n);
+            for (size_t t = 0; t < d; ++t) ri[t] /= n;
+        }
+    for (size_t i = 0; i < d * d; ++i) m_out[i] = (float)rows[i];
+    return B200_OK;
+}
+
 // candle-core/src/accel/attention.rs:586-592
 extern "C" int b200_row_group(int hq, int hkv) {
     const int group = hq / (hkv > 0 ? hkv : 1);

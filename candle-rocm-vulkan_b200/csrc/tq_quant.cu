@@ -804,3 +804,38 @@ extern "C" int b200_tq_rotate(const float *in, float *out, const float *signs, u
     hadamard_rows_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(in, out, signs, rows, dim, inverse);
     return check_launch("tq_rotate");
 }
+
+// y = x Pi^T (inverse: x = y Pi) for a caller-supplied row-major dim x dim matrix: the rotation of head dims that are
+// not powers of two (candle-nn/src/turbo_quant.rs:182-196, a library matmul there). One warp per row, the row in
+// shared memory, lane l computes outputs l, l + 32, ...; products and sums in index order, unfused, so the result has
+// the bits of the plain f32 loop.
+__global__ void __launch_bounds__(128) dense_rotate_rows_kernel(const float *__restrict__ in, float *__restrict__ out,
+                                                               const float *__restrict__ pi, uint64_t rows, uint32_t D, int inverse) {
+    extern __shared__ float xrow[];  // [4][D]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float *x = xrow + (size_t)warp * D;
+    for (uint64_t row = (uint64_t)blockIdx.x * 4 + warp; row < rows; row += (uint64_t)gridDim.x * 4) {
+        __syncwarp();
+        for (uint32_t j = lane; j < D; j += 32) x[j] = in[row * D + j];
+        __syncwarp();
+        for (uint32_t i = lane; i < D; i += 32) {
+            float acc = 0.0f;
+            if (!inverse)
+                for (uint32_t j = 0; j < D; ++j) acc = __fadd_rn(acc, __fmul_rn(__ldg(pi + (size_t)i * D + j), x[j]));
+            else
+                for (uint32_t j = 0; j < D; ++j) acc = __fadd_rn(acc, __fmul_rn(__ldg(pi + (size_t)j * D + i), x[j]));
+            out[row * D + i] = acc;
+        }
+    }
+}
+
+extern "C" int b200_tq_rotate_dense(const float *in, float *out, const float *pi, uint64_t rows, uint32_t dim, int inverse,
+                                    b200_stream_t stream) {
+    if (rows == 0) return B200_OK;
+    if (!in || !out || !pi) return set_error(B200_ERR_BAD_ARG, "tq_rotate_dense: null pointer");
+    if (in == out) return set_error(B200_ERR_BAD_ARG, "tq_rotate_dense: in and out must differ");
+    if (dim == 0 || dim > 1024) return set_error(B200_ERR_BAD_ARG, "tq_rotate_dense: dim %u outside 1..1024", dim);
+    const unsigned grid = (unsigned)std::min<uint64_t>((rows + 3) / 4, 148ull * 16);
+    dense_rotate_rows_kernel<<<grid, 128, 4 * dim * sizeof(float), (cudaStream_t)stream>>>(in, out, pi, rows, dim, inverse);
+    return check_launch("tq_rotate_dense");
+}

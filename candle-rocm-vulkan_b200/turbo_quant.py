@@ -118,18 +118,22 @@ class QuantizedTensor:
 
 
 class TurboQuantizer:
-    """Quantizes vectors of a fixed length in one format (turbo_quant.rs:57-321). `rotation`:
-    "none" or "hadamard" ("auto" resolves to hadamard for powers of two, like RotationKind::Auto;
-    the dense rotation for other lengths is not offered by the fused kernels)."""
+    """Quantizes vectors of a fixed length in one format (turbo_quant.rs:57-321). `rotation`: "none", "hadamard",
+    "dense" or "auto"; auto resolves to hadamard for powers of two and to dense otherwise, hadamard to dense for
+    lengths that are not powers of two (RotationKind::resolve, accel/config.rs:131-138). The Hadamard rotation is
+    fused into the quantize and attention kernels; the dense one (a matrix product with a seeded orthonormal matrix)
+    runs as its own launch before / after them, as every rotation does in the reference."""
 
     def __init__(self, format: QuantFormat, dim: int, rotation: str = "auto", seed: int = 42, device="cuda"):
         self.format, self.dim, self.device = format, dim, torch.device(device)
         self.layout = A.row_layout(format.mode, format.bits, dim)
         pow2 = dim & (dim - 1) == 0
+        if rotation not in ("none", "hadamard", "dense", "auto"):
+            raise ValueError("rotation must be none, hadamard, dense or auto")
         if rotation == "auto":
-            rotation = "hadamard" if pow2 else "none"
-        if rotation not in ("none", "hadamard"):
-            raise ValueError("rotation must be none, hadamard or auto")
+            rotation = "hadamard" if pow2 else "dense"
+        if rotation == "hadamard" and not pow2:
+            rotation = "dense"
         self.rotation = rotation
         self.seed = seed
         tab = (C.c_float * 32)()
@@ -144,6 +148,11 @@ class TurboQuantizer:
             A.check(A.lib().b200_qjl_matrix(dim, seed, m))
             s_mat = torch.frombuffer(m, dtype=torch.float32).view(dim, dim).to(self.device)
             self.qjl = (s_mat, s_mat.t().contiguous())
+        self.pi = None
+        if rotation == "dense":
+            m = (C.c_float * (dim * dim))()
+            A.check(A.lib().b200_rotation_matrix(dim, seed, m))
+            self.pi = torch.frombuffer(m, dtype=torch.float32).view(dim, dim).to(self.device)
         self.signs = None
         if rotation == "hadamard":
             s = (C.c_float * dim)()
@@ -164,6 +173,10 @@ class TurboQuantizer:
         if self.rotation == "none":
             return x
         out = torch.empty_like(x)
+        if self.rotation == "dense":
+            A.check(A.lib().b200_tq_rotate_dense(x.data_ptr(), out.data_ptr(), self.pi.data_ptr(), x.numel() // self.dim,
+                                                 self.dim, 0, _stream(x.device)))
+            return out
         A.check(A.lib().b200_tq_rotate(x.data_ptr(), out.data_ptr(), self.signs.data_ptr(), x.numel() // self.dim,
                                        self.dim, 0, _stream(x.device)))
         return out
@@ -174,6 +187,10 @@ class TurboQuantizer:
             return y
         y = y.to(torch.float32).contiguous()
         out = torch.empty_like(y)
+        if self.rotation == "dense":
+            A.check(A.lib().b200_tq_rotate_dense(y.data_ptr(), out.data_ptr(), self.pi.data_ptr(), y.numel() // self.dim,
+                                                 self.dim, 1, _stream(y.device)))
+            return out
         A.check(A.lib().b200_tq_rotate(y.data_ptr(), out.data_ptr(), self.signs.data_ptr(), y.numel() // self.dim,
                                        self.dim, 1, _stream(y.device)))
         return out
@@ -213,6 +230,8 @@ class TurboQuantizer:
             return packed
         if self.rotation == "none":
             return self.quantize_rotated_rows(x)
+        if self.rotation == "dense":
+            return self.quantize_rotated_rows(self.rotate(x))
         out = torch.empty((1, 1, rows, self.layout.row_words), dtype=torch.int32, device=x.device)
         _kv_append(x.view(1, 1, rows, d), x.view(1, 1, rows, d), out, out.clone(), self, self, 0)
         return out.view(rows, self.layout.row_words)
@@ -248,6 +267,13 @@ def _kv_append(k, v, k_cache, v_cache, kq: TurboQuantizer, vq: TurboQuantizer, p
     int32 device tensor with one position per batch entry, to which `pos_add` is added. Rows whose
     device position falls outside the cache are skipped (`status`, an int32 device tensor, is set to 3)."""
     b, h, t, d = k.shape
+    # the dense rotation is not fused: rows rotated by their own launch (f32), then appended with rotation none
+    if kq.rotation == "dense":
+        k = kq.rotate(k.reshape(-1, d)).view(b, h, t, d)
+    if vq.rotation == "dense":
+        v = vq.rotate(v.reshape(-1, d)).view(b, h, t, d)
+    if k.dtype != v.dtype:
+        k, v = k.to(torch.float32), v.to(torch.float32)
     if k.stride(3) != 1:
         k = k.contiguous()
     if v.stride(3) != 1:
@@ -306,6 +332,29 @@ class OutputGather:
         return self.buf[self.steps_done() & 1]
 
 
+class _DenseRotationIO:
+    """Queries rotated before and outputs rotated back after an attention call whose quantizers use the dense rotation
+    (not fused into the kernels): f32 staging tensors that the kernel reads / writes instead of the caller's."""
+
+    def __init__(self, q: torch.Tensor, out: torch.Tensor, kq: TurboQuantizer, vq: TurboQuantizer):
+        self.kq = kq if (kq.rotation == "dense" and kq.qjl is None) else None  # prod keys rotate their query themselves
+        self.vq = vq if vq.rotation == "dense" else None
+        self.q_user, self.out_user = q, out
+        self.q32 = torch.empty(q.shape, dtype=torch.float32, device=q.device) if self.kq is not None else None
+        self.o32 = torch.empty(out.shape, dtype=torch.float32, device=q.device) if self.vq is not None else None
+
+    def before(self):
+        if self.kq is not None:
+            src = self.q_user.to(torch.float32).contiguous()
+            A.check(A.lib().b200_tq_rotate_dense(src.data_ptr(), self.q32.data_ptr(), self.kq.pi.data_ptr(), src.numel() // self.kq.dim,
+                                                 self.kq.dim, 0, _stream(src.device)))
+
+    def after(self):
+        if self.vq is not None:
+            back = self.vq.unrotate(self.o32.view(-1, self.vq.dim))
+            self.out_user.copy_(back.view(self.out_user.shape))
+
+
 class PackedAttention:
     """A prepared `attention_packed` call: arguments checked and marshalled once, `run()` only
     launches (a few microseconds of host time, and capturable in a CUDA graph after one warm-up
@@ -348,6 +397,12 @@ class PackedAttention:
             raise ValueError("turbo-quant attention: packed rows must be contiguous along the words")
         if out is None:
             out = torch.empty((b, hq, lq, d), dtype=q.dtype, device=q.device)
+        self._dense = _DenseRotationIO(q, out, kq, vq)
+        user_out = out
+        if self._dense.q32 is not None:
+            q = self._dense.q32
+        if self._dense.o32 is not None:
+            out = self._dense.o32
         wl, wr = cfg.window_i32()
         alibi, abs_ = None, 0
         if cfg.alibi_slopes is not None:
@@ -383,10 +438,12 @@ class PackedAttention:
             args.flags |= A.TQ_INPUTS_FINAL
             args.fresh_rows = int(fresh_rows)
         args.kv_len_add = int(kv_len_add) if ragged else 0  # tokens appended since the device lengths were written
-        self.args, self.out, self.device = args, out, q.device
-        self._keep = (q, k_rows, v_rows, kv_len, kq, vq, alibi, ws, status)
+        self.args, self.out, self.device = args, user_out, q.device
+        self._keep = (q, out, k_rows, v_rows, kv_len, kq, vq, alibi, ws, status)
         self._fn, self._ref = A.lib().b200_tq_attention, C.byref(args)
         self._gather = gather
+        if gather is not None and self._dense.o32 is not None:
+            raise ValueError("OutputGather: the gathered rows are stored by the attention kernel, before a dense rotation back")
         if gather is not None:
             # outputs also stored into every rank's gathered buffer by the kernel that merges the key splits
             if out.numel() != gather.buf.shape[2] * gather.buf.shape[3] or out.dtype != gather.buf.dtype:
@@ -395,9 +452,11 @@ class PackedAttention:
             self._fn = lambda ref, stream: fn(ref, gref, stream)
 
     def run(self) -> torch.Tensor:
+        self._dense.before()
         rc = self._fn(self._ref, torch.cuda.current_stream(self.device).cuda_stream)
         if rc:
             A.check(rc)
+        self._dense.after()
         return self.out
 
 
@@ -455,6 +514,12 @@ class PackedBlocksAttention:
             q = q.contiguous()
         if out is None:
             out = torch.empty((b, hq, lq, d), dtype=q.dtype, device=q.device)
+        self._dense = _DenseRotationIO(q, out, kq, vq)
+        user_out = out
+        if self._dense.q32 is not None:
+            q = self._dense.q32
+        if self._dense.o32 is not None:
+            out = self._dense.o32
         wl, wr = cfg.window_i32()
         alibi, abs_ = None, 0
         if cfg.alibi_slopes is not None:
@@ -485,14 +550,16 @@ class PackedBlocksAttention:
             A.check(A.lib().b200_tq_attention(C.byref(args), _stream(q.device)))  # raises with the library's reason
         ws = _workspace(q.device, need)
         args.workspace, args.workspace_bytes = ws.data_ptr(), need
-        self.args, self.out, self.device = args, out, q.device
-        self._keep = (q, blocks, pages, kv_len, kq, vq, alibi, ws)
+        self.args, self.out, self.device = args, user_out, q.device
+        self._keep = (q, out, blocks, pages, kv_len, kq, vq, alibi, ws)
         self._ref = C.byref(args)
 
     def run(self) -> torch.Tensor:
+        self._dense.before()
         rc = A.lib().b200_tq_attention(self._ref, torch.cuda.current_stream(self.device).cuda_stream)
         if rc:
             A.check(rc)
+        self._dense.after()
         return self.out
 
 

@@ -189,6 +189,16 @@ int b200_tq_signs(const B200TqSignsArgs *args, b200_stream_t stream);
 int b200_tq_rotate(const float *in, float *out, const float *signs, uint64_t rows, uint32_t dim, int inverse,
                    b200_stream_t stream);
 
+/* The rotation of lengths that are not powers of two (RotationKind::Dense, candle-core/src/accel/turbo.rs:204-229;
+ * RotationKind::Auto resolves to it for such lengths, accel/config.rs:131-138). b200_rotation_matrix: the row-major
+ * dim x dim matrix Pi of a seed (host). b200_tq_rotate_dense: out = in Pi^T (inverse: in Pi) for rows of dim floats on
+ * the device (the reference's matmul, candle-nn/src/turbo_quant.rs:182-196); pi: device, dim x dim. The fused kernels
+ * take rotation none / Hadamard only: a dense-rotated cache is quantized and attended over with rotation none on rows
+ * and queries rotated by this call, and the outputs rotated back by it, as the reference does for every rotation. */
+int b200_rotation_matrix(int dim, uint64_t seed, float *pi);
+int b200_tq_rotate_dense(const float *in, float *out, const float *pi, uint64_t rows, uint32_t dim, int inverse,
+                         b200_stream_t stream);
+
 /* ---- fused quantize-on-append ------------------------------------------------------------------ */
 /* Replaces TurboKvCache::append (candle-nn/src/turbo_quant.rs:916-945), i.e. per tensor the chain
  * to_dtype(F32) -> matmul with the rotation -> tq_quant -> Cache::append / slice_set

@@ -266,6 +266,9 @@ extern "C" {
     pub fn b200_tq_signs(args: *const B200TqSignsArgs, stream: b200_stream_t) -> c_int;
     pub fn b200_tq_rotate(input: *const f32, out: *mut f32, signs: *const f32, rows: u64, dim: u32, inverse: c_int,
                           stream: b200_stream_t) -> c_int;
+    pub fn b200_rotation_matrix(dim: c_int, seed: u64, pi: *mut f32) -> c_int;
+    pub fn b200_tq_rotate_dense(input: *const f32, out: *mut f32, pi: *const f32, rows: u64, dim: u32, inverse: c_int,
+                                stream: b200_stream_t) -> c_int;
     pub fn b200_kv_append(args: *const B200KvAppendArgs, stream: b200_stream_t) -> c_int;
 
     // attention over packed rows (CudaStorage::tq_attention / tq_attention_paged)

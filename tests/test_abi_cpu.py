@@ -126,6 +126,20 @@ def test_codebook_signs_heuristics_match_oracle(pkg, oracle):
         assert lib.b200_split_count_grouped(rows, g, lk, cu) == oracle.split_count_grouped(rows, g, lk, cu)
 
 
+def test_dense_rotation_matrix_matches_the_oracle(pkg, oracle):
+    """b200_rotation_matrix (Gaussian rows + two passes of modified Gram-Schmidt in f64, turbo.rs:204-229) against the
+    oracle's restatement, bit for bit, and orthonormal to f32 precision."""
+    lib = pkg._abi.lib()
+    for dim, seed in ((96, 42), (80, 7), (33, 2**63 + 5), (192, 44)):
+        m = (C.c_float * (dim * dim))()
+        assert lib.b200_rotation_matrix(dim, seed, m) == 0
+        got = np.frombuffer(m, dtype=np.float32).reshape(dim, dim)
+        want = oracle.rotation_matrix(dim, 2, seed)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (dim, seed)
+        assert np.abs(got.astype(np.float64) @ got.astype(np.float64).T - np.eye(dim)).max() < 1e-6
+    assert lib.b200_rotation_matrix(0, 1, (C.c_float * 1)()) == pkg._abi.ERR_BAD_ARG
+
+
 def test_argument_errors_without_gpu(pkg):
     A = pkg._abi
     lib = A.lib()

@@ -475,6 +475,34 @@ def test_chunked_prefill_over_the_compressed_cache(P, oracle, f, rot):
     assert torch.equal(cache.attention(q[:, :, -4:], c), P.attention_packed(q[:, :, -4:].contiguous(), cache.k, cache.v, lk, cache.kq, cache.vq, c))
 
 
+@pytest.mark.parametrize("f,d", [((0, 4), 96), ((2, 4), 96), ((0, 3), 160)])
+def test_dense_rotation_for_head_dims_that_are_not_powers_of_two(P, oracle, f, d):
+    """RotationKind::Auto at a head dim that is not a power of two: the seeded dense rotation (turbo.rs:204-229). The
+    rotated rows have the oracle's bits (sums in index order), so the packed rows are bit-exact; the attention through
+    the cache object (rotate q, kernel, rotate back) against the oracle's matmul rotation."""
+    b, hq, hkv, lk = 2, 4, 2, 300
+    kx = oracle.normal(15, b * hkv * lk * d).reshape(b, hkv, lk, d)
+    vx = oracle.normal(16, b * hkv * lk * d).reshape(b, hkv, lk, d)
+    q = oracle.normal(17, b * hq * d).reshape(b, hq, 1, d)
+    cache = P.TurboKvCache(fmt(P, *f), fmt(P, *f), d, "auto", 42, lk)
+    assert cache.kq.rotation == "dense" and cache.vq.rotation == "dense"
+    cache.append(to_dev(kx), to_dev(vx))
+    pk, pv = oracle.rotation_matrix(d, 2, 42), oracle.rotation_matrix(d, 2, 44)
+    tab = MG.tab_for(f[0], f[1], d)
+    kd = oracle.quantize_rows(oracle.rotate_rows(kx.reshape(-1, d), pk), f[0], f[1], tab).reshape(b, hkv, lk, -1)
+    vd = oracle.quantize_rows(oracle.rotate_rows(vx.reshape(-1, d), pv), f[0], f[1], tab).reshape(b, hkv, lk, -1)
+    assert np.array_equal(words(cache.k[:, :, :lk]), kd) and np.array_equal(words(cache.v[:, :, :lk]), vd)
+    got = cache.attention(to_dev(q), P.FlashAttnConfig(d ** -0.5).causal()).cpu().numpy()
+    qr = oracle.rotate_rows(q.reshape(-1, d), pk).reshape(q.shape)
+    o = oracle.tq_attention(qr, kd, vd, lk, f, f, d ** -0.5, np.concatenate([tab, tab]), wr=0)
+    want = oracle.rotate_rows(o.reshape(-1, d), pv, transpose=True).reshape(o.shape)
+    assert_close(got, want, what=f"dense rotation {f} d={d}")
+    # dequantized keys come back in the original domain
+    k_back, _ = cache.keys_values()
+    assert_close(k_back.float().cpu().numpy(), oracle.rotate_rows(oracle.dequantize_rows(kd.reshape(-1, kd.shape[-1]), d, f[0], f[1], tab), pk, transpose=True).reshape(b, hkv, lk, d),
+                 atol=1e-5, rtol=1e-5, what="keys_values")
+
+
 def test_config1_fp8_single_decode(P, oracle):
     """B=1, Hq=32, Hkv=8, D=128, 2048 keys, f16, FP8 rows with one f32 scale per token and head."""
     b, hq, hkv, d, lk = 1, 32, 8, 128, 2048
