@@ -6,6 +6,7 @@ path of Qntology/candle-rocm-vulkan).
 so load it with `__graft_entry__.load_package()`, which registers it as `candle_rocm_vulkan_b200`.
 """
 from . import _abi  # noqa: F401
+from . import config  # noqa: F401
 from . import flash_attn  # noqa: F401
 from . import offload  # noqa: F401
 from .offload import CopyEvent, CopyStream, PinnedHostBuffer  # noqa: F401
