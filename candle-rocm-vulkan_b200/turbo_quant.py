@@ -440,6 +440,7 @@ class PackedAttention:
         args.kv_len_add = int(kv_len_add) if ragged else 0  # tokens appended since the device lengths were written
         self.args, self.out, self.device = args, user_out, q.device
         self._keep = (q, out, k_rows, v_rows, kv_len, kq, vq, alibi, ws, status)
+        self.workspace = ws  # the scratch buffer of the call (shared by the calls of one stream)
         self._fn, self._ref = A.lib().b200_tq_attention, C.byref(args)
         self._gather = gather
         if gather is not None and self._dense.o32 is not None:

@@ -366,7 +366,7 @@ def test_far_more_workers_than_tiles(P, oracle, b):
         cfg = P.FlashAttnConfig(d ** -0.5).causal()
         cfg.splits = splits
         call = P.PackedAttention(to_dev(q, "bf16"), rows_dev(kd), rows_dev(vd), torch.from_numpy(lens).to("cuda:0"), kq, vq, cfg)
-        call._keep[7].view(torch.int32).fill_(0x7fc00000)
+        call.workspace.view(torch.int32).fill_(0x7fc00000)
         got = call.run().float().cpu().numpy()
         assert_close(got, want, what=f"sparse work, splits={splits}", out="bf16")
 
