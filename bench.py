@@ -479,42 +479,57 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
     if with_e2e:
         # ---- end to end through the public API with host buffers: H2D of the step's inputs, append of the new token,
         # attention, D2H of the outputs. A serving loop overlaps the copies of neighbouring steps with the kernels: inputs
-        # and outputs are double buffered, the host-to-device copy of step i + 1 and the device-to-host copy of step i - 1
-        # run on their own streams beside the kernels of step i. Every step still copies its own inputs in and its own
-        # result out.
+        # are triple and outputs double buffered, the host-to-device copy of step i + 1 and the device-to-host copy of
+        # step i - 1 run on their own streams beside the kernels of step i. Every step still copies its own inputs in and
+        # its own result out.
         lens_dev = kv_len.clone()
-        in_dev = [step_dev, torch.empty_like(step_dev)]
+        in_dev = [step_dev, torch.empty_like(step_dev), torch.empty_like(step_dev)]
         out_dev = [out, torch.empty_like(out)]
         out_hosts = [out_host, torch.empty_like(out_host).pin_memory()]
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
 
         def e2e_steps(first, count):
-            """Steps first .. first + count - 1 as a three-stage pipeline over the current stream and two copy streams."""
+            """Steps first .. first + count - 1 as a pipeline over the current stream and two copy streams. Inputs are triple
+            buffered: the copy of step i + 1 is queued before the kernels of step i and waited for between the append and the
+            attention of step i, so that nothing stands between the attention of a step and the append of the next one, which
+            is launched while that attention drains (B200_KV_AFTER_PREV; an event wait in front of a kernel makes it wait for
+            the whole of its predecessor)."""
             main = torch.cuda.current_stream(dev)
             fork = torch.cuda.Event()
             fork.record(main)
             s_in.wait_event(fork)
             s_out.wait_event(fork)
             ev_in, ev_done, ev_out = {}, {}, {}
-            for i in range(first, first + count):
-                pb = i & 1
-                kc, vc = caches[i % nbuf]
-                qv = in_dev[pb][:nq].view(b, hq, 1, d)
-                kn = in_dev[pb][nq:nq + nkv].view(b, hkv, 1, d)
-                vn = in_dev[pb][nq + nkv:].view(b, hkv, 1, d)
+
+            def h2d(i):
                 with torch.cuda.stream(s_in):
-                    if i - 2 in ev_done:
-                        s_in.wait_event(ev_done[i - 2])       # the kernels of step i - 2 have read this input buffer
-                    in_dev[pb].copy_(step_host, non_blocking=True)
+                    if i - 3 in ev_done:
+                        s_in.wait_event(ev_done[i - 3])       # the kernels of step i - 3 have read this input buffer
+                    in_dev[i % 3].copy_(step_host, non_blocking=True)
                     ev_in[i] = torch.cuda.Event()
                     ev_in[i].record(s_in)
-                main.wait_event(ev_in[i])
+
+            h2d(first)
+            main.wait_event(ev_in[first])
+            for i in range(first, first + count):
+                pb, ib = i & 1, i % 3
+                kc, vc = caches[i % nbuf]
+                qv = in_dev[ib][:nq].view(b, hq, 1, d)
+                kn = in_dev[ib][nq:nq + nkv].view(b, hkv, 1, d)
+                vn = in_dev[ib][nq + nkv:].view(b, hkv, 1, d)
+                if i + 1 < first + count:
+                    h2d(i + 1)                                # runs beside the kernels of this step
+                # the device lengths are those at the start of this group of steps: step j appends at lens + j and attends
+                # to lens + j + 1 keys (offsets in the call arguments), so no kernel sits between append and attention.
+                # The append of every step but the group's first takes its place while the previous step's attention drains
+                # (that attention reads none of the row written here; the first step follows the kernel that wrote the
+                # lengths, which the append reads)
+                j = i - first
+                _kv_append(kn, vn, kc, vc, kq, vq, lens_dev, pos_add=j, status=status, after_prev=(j > 0))
+                if i + 1 in ev_in:
+                    main.wait_event(ev_in[i + 1])             # the next step's inputs: its append then needs no wait
                 if i - 2 in ev_out:
                     main.wait_event(ev_out[i - 2])            # the result of step i - 2 has left this output buffer
-                # the device lengths are those at the start of this group of steps: step j appends at lens + j and attends
-                # to lens + j + 1 keys (offsets in the call arguments), so no kernel sits between append and attention
-                j = i - first
-                _kv_append(kn, vn, kc, vc, kq, vq, lens_dev, pos_add=j, status=status)
                 P.PackedAttention(qv, kc, vc, lens_dev, kq, vq, cfg, out=out_dev[pb], gather=peer_gather, kv_len_add=j + 1,
                                   after_prev=True, fresh_rows=1, status=status).run()
                 if world > 1 and peer_gather is None:
@@ -537,7 +552,10 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
         env.barrier()
         # the same calls captured once (copies and stream dependencies included): a serving loop replays its steps
         # instead of paying the host's call path every token
-        e2e_group = nbuf * max(1, 8 // nbuf)
+        # like the device-timed loop: the timed steps are one graph when they are few, groups of 32 otherwise (a multiple of
+        # the caches cycled, so that every replay starts on the same one)
+        e2e_group = steps if steps <= 128 else 32
+        e2e_group = max(nbuf, e2e_group - e2e_group % nbuf)
         e2e_graph = None
         if graphs:
             try:

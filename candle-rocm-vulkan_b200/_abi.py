@@ -61,7 +61,8 @@ class KvAppendArgs(C.Structure):
                 ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("k_cache_strides", u64x3),
                 ("v_cache_strides", u64x3), ("pos", C.c_void_p), ("pos0", C.c_int32), ("b", C.c_uint32),
                 ("hkv", C.c_uint32), ("t", C.c_uint32), ("d", C.c_uint32), ("src_dtype", C.c_int32),
-                ("kq", QuantSide), ("vq", QuantSide), ("cap", C.c_uint32), ("status", C.c_void_p)]
+                ("kq", QuantSide), ("vq", QuantSide), ("cap", C.c_uint32), ("status", C.c_void_p),
+                ("flags", C.c_uint32), ("pad", C.c_uint32)]
 
 
 class Page(C.Structure):
@@ -69,6 +70,7 @@ class Page(C.Structure):
                 ("v_cap", C.c_uint32), ("pad", C.c_uint32)]
 
 
+KV_AFTER_PREV = 1  # B200_KV_AFTER_PREV
 TQ_AFTER_PREV = 1  # B200_TQ_AFTER_PREV
 TQ_INPUTS_FINAL = 2  # B200_TQ_INPUTS_FINAL
 TQ_IN_PLACE = 4  # B200_TQ_IN_PLACE

@@ -37,7 +37,18 @@ struct QuantParams {
     uint32_t nb, nh, nt, d;
     int32_t src_dtype;
     uint32_t nt_mul, nt_shr, nh_mul, nh_shr;  // fastdiv invariants of nt and nh (rows128 kernel)
+    uint32_t after_prev;  // launched as a programmatic dependent of the stream's previous kernel (B200_KV_AFTER_PREV)
 };
+
+// A grid launched while the stream's previous kernel still runs (that kernel neither reads the rows written here nor
+// writes this call's inputs) lets its own dependents be scheduled at once, and before it ends waits for that kernel:
+// so this grid's completion still implies the completion of everything before it in the stream.
+__device__ __forceinline__ void after_prev_begin(const QuantParams &p) {
+    if (p.after_prev) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void after_prev_end(const QuantParams &p) {
+    if (p.after_prev) asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -57,6 +68,7 @@ __global__ void __launch_bounds__(QW * 32) quant_rows_kernel(const QuantParams p
     const uint64_t rows = (uint64_t)p.nb * p.nh * p.nt;
     uint8_t *codes = s_codes[warp];
     uint32_t *sc = s_scales[warp];
+    after_prev_begin(p);
 
     const bool small = rows < 0x80000000ull;  // 32-bit row arithmetic (the 64-bit divisions cost more than the codecs)
     for (uint64_t row = (uint64_t)blockIdx.x * QW + warp; row < rows; row += (uint64_t)gridDim.x * QW) {
@@ -227,6 +239,7 @@ __global__ void __launch_bounds__(QW * 32) quant_rows_kernel(const QuantParams p
         }
         __syncwarp();
     }
+    after_prev_end(p);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -330,6 +343,7 @@ __global__ void __launch_bounds__(Q128_WARPS * 32) quant_rows128_kernel(const Qu
     const int lane = threadIdx.x & 31, l8 = lane & 7;
     const uint32_t rows = p.nb * p.nh * p.nt;
     const uint32_t mode = sp.mode;
+    after_prev_begin(p);
     for (uint32_t base = (blockIdx.x * Q128_WARPS + (threadIdx.x >> 5)) * Q128_RPW; base < rows; base += gridDim.x * Q128_WARPS * Q128_RPW) {
         bool live = base + (lane >> 3) < rows;  // a row past the end repeats the last one and stores nothing
         const uint32_t row = live ? base + (lane >> 3) : rows - 1;
@@ -453,6 +467,7 @@ __global__ void __launch_bounds__(Q128_WARPS * 32) quant_rows128_kernel(const Qu
         }
         if (live && l8 < 2) orow[cw + (uint32_t)sp.aux_words + l8] = l8 ? 0u : f2u(rsc0);
     }
+    after_prev_end(p);
 }
 
 // rsc0 * element for every element (candle-core/kernels/turbo_quant_impl.h:44-53,208-218)
@@ -631,6 +646,23 @@ static bool rows128_takes(const QuantParams &p, int sides) {
     return true;
 }
 
+// a plain launch, or (after_prev) one that may be scheduled while the stream's previous kernel still runs
+static int launch_maybe_after_prev(void (*kern)(const QuantParams), dim3 grid, dim3 block, cudaStream_t stream, const QuantParams &p) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.after_prev ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "tq_quantize: %s", cudaGetErrorString(e));
+    return check_launch("tq_quantize");
+}
+
 static int launch_quant(const QuantParams &p, int sides, cudaStream_t stream) {
     const uint64_t rows = (uint64_t)p.nb * p.nh * p.nt;
     if (rows == 0) return B200_OK;
@@ -648,24 +680,22 @@ static int launch_quant(const QuantParams &p, int sides, cudaStream_t stream) {
             return std::max(per_sm, 1) * std::max(sms, 1);
         }();
         const dim3 grid((unsigned)std::min<uint64_t>((rows + per_block - 1) / per_block, (uint64_t)std::max(resident / sides, 1)), sides), block(Q128_WARPS * 32);
-        if (p.src_dtype == B200_F32) quant_rows128_kernel<B200_F32><<<grid, block, 0, stream>>>(q);
-        else if (p.src_dtype == B200_F16) quant_rows128_kernel<B200_F16><<<grid, block, 0, stream>>>(q);
-        else quant_rows128_kernel<B200_BF16><<<grid, block, 0, stream>>>(q);
-        return check_launch("tq_quantize");
+        if (p.src_dtype == B200_F32) return launch_maybe_after_prev(quant_rows128_kernel<B200_F32>, grid, block, stream, q);
+        if (p.src_dtype == B200_F16) return launch_maybe_after_prev(quant_rows128_kernel<B200_F16>, grid, block, stream, q);
+        return launch_maybe_after_prev(quant_rows128_kernel<B200_BF16>, grid, block, stream, q);
     }
     const unsigned gx = (unsigned)std::min<uint64_t>((rows + QW - 1) / QW, 148ull * 64);
     const dim3 grid(gx, sides), block(QW * 32);
 #define B200_QUANT_LAUNCH(EPL)                                                                      \
     do {                                                                                            \
-        if (p.src_dtype == B200_F32) quant_rows_kernel<EPL, B200_F32><<<grid, block, 0, stream>>>(p);      \
-        else if (p.src_dtype == B200_F16) quant_rows_kernel<EPL, B200_F16><<<grid, block, 0, stream>>>(p); \
-        else quant_rows_kernel<EPL, B200_BF16><<<grid, block, 0, stream>>>(p);                          \
+        if (p.src_dtype == B200_F32) return launch_maybe_after_prev(quant_rows_kernel<EPL, B200_F32>, grid, block, stream, p);      \
+        if (p.src_dtype == B200_F16) return launch_maybe_after_prev(quant_rows_kernel<EPL, B200_F16>, grid, block, stream, p);      \
+        return launch_maybe_after_prev(quant_rows_kernel<EPL, B200_BF16>, grid, block, stream, p);                                  \
     } while (0)
     if (p.d <= 128) B200_QUANT_LAUNCH(4);
     else if (p.d <= 256) B200_QUANT_LAUNCH(8);
     else B200_QUANT_LAUNCH(32);
 #undef B200_QUANT_LAUNCH
-    return check_launch("tq_quantize");
 }
 
 } // namespace b200
@@ -739,6 +769,7 @@ extern "C" int b200_kv_append(const B200KvAppendArgs *a, b200_stream_t stream) {
     p.nt = a->t;
     p.d = a->d;
     p.src_dtype = a->src_dtype;
+    p.after_prev = (a->flags & B200_KV_AFTER_PREV) ? 1u : 0u;
     return launch_quant(p, 2, (cudaStream_t)stream);
 }
 

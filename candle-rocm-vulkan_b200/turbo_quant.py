@@ -262,7 +262,7 @@ class TurboQuantizer:
         return self.dequantize_rows(q.data).reshape(q.shape).to(q.dtype)
 
 
-def _kv_append(k, v, k_cache, v_cache, kq: TurboQuantizer, vq: TurboQuantizer, pos, pos_add: int = 0, status=None):
+def _kv_append(k, v, k_cache, v_cache, kq: TurboQuantizer, vq: TurboQuantizer, pos, pos_add: int = 0, status=None, after_prev: bool = False):
     """b200_kv_append over (b, hkv, t, d) tensors and (b, hkv, cap, words) caches. `pos`: int or an
     int32 device tensor with one position per batch entry, to which `pos_add` is added. Rows whose
     device position falls outside the cache are skipped (`status`, an int32 device tensor, is set to 3)."""
@@ -284,7 +284,9 @@ def _kv_append(k, v, k_cache, v_cache, kq: TurboQuantizer, vq: TurboQuantizer, p
         k_cache.data_ptr(), v_cache.data_ptr(), A.u64x3(*k_cache.stride()[:3]), A.u64x3(*v_cache.stride()[:3]),
         pos_t.data_ptr() if pos_t is not None else None, int(pos_add) if pos_t is not None else int(pos) + int(pos_add),
         b, h, t, d, _dtype_id(k), kq.side(), vq.side(), min(k_cache.shape[2], v_cache.shape[2]),
-        status.data_ptr() if status is not None else None)
+        status.data_ptr() if status is not None else None,
+        # B200_KV_AFTER_PREV: the stream's previous kernel neither reads the rows written here nor writes k, v or pos
+        A.KV_AFTER_PREV if after_prev else 0, 0)
     A.check(A.lib().b200_kv_append(C.byref(args), _stream(k.device)))
 
 

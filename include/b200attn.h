@@ -223,7 +223,16 @@ typedef struct B200KvAppendArgs {
     B200QuantSide kq, vq;
     uint32_t cap;             /* rows per (batch entry, head) of both caches; 0 = unchecked */
     int32_t *status;          /* optional device word, set to 3 when a device position was out of range */
+    uint32_t flags;           /* B200_KV_* below; 0 = none */
+    uint32_t pad;
 } B200KvAppendArgs;
+/* The append may run while the stream's previous kernel is still running (programmatic dependent launch): the caller
+ * states that this kernel neither reads the rows written here nor writes k, v or pos. True for the decode loop, where
+ * the previous kernel is the attention of the step before: it reads the rows below the position this call writes (and
+ * at most the first bytes of that row, which it ignores). The append's own completion still waits for that kernel, so
+ * whatever follows in the stream is ordered behind both; an attention that follows with B200_TQ_AFTER_PREV |
+ * B200_TQ_INPUTS_FINAL and fresh_rows = t then streams its old rows while the previous attention drains. */
+#define B200_KV_AFTER_PREV 1u
 int b200_kv_append(const B200KvAppendArgs *args, b200_stream_t stream);
 
 /* ---- paged rows --------------------------------------------------------------------------------- */

@@ -30,6 +30,7 @@ pub const B200_FP8_ROW: i32 = 5;
 pub const B200_ROT_NONE: i32 = 0;
 pub const B200_ROT_HADAMARD: i32 = 1;
 
+pub const B200_KV_AFTER_PREV: u32 = 1;
 pub const B200_TQ_AFTER_PREV: u32 = 1;
 pub const B200_TQ_INPUTS_FINAL: u32 = 2;
 pub const B200_TQ_IN_PLACE: u32 = 4;
@@ -140,6 +141,8 @@ pub struct B200KvAppendArgs {
     pub vq: B200QuantSide,
     pub cap: u32,
     pub status: *mut i32,
+    pub flags: u32,
+    pub pad: u32,
 }
 
 #[repr(C)]

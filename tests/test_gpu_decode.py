@@ -333,6 +333,37 @@ def test_rows_copied_while_the_append_of_the_step_still_runs(P, oracle):
         torch.cuda.synchronize()
         assert torch.isfinite(got.float()).all(), f"step {j}"
         assert torch.equal(got, want[j]), f"step {j}"
+    # the whole loop without a host synchronization, the append of every step but the first launched behind the
+    # previous step's attention as well (B200_KV_AFTER_PREV): steps chase one another on the device, eagerly and
+    # replayed from a CUDA graph; the outputs are those of the plain loop, bit for bit
+    def chained(kc, vc, outs):
+        for j in range(steps):
+            _kv_append(kn[j], vn[j], kc, vc, kq, vq, lens0, pos_add=j, after_prev=(j > 0))
+            P.PackedAttention(qs[j], kc, vc, lens0, kq, vq, cfg, out=outs[j], kv_len_add=j + 1, after_prev=True, fresh_rows=1).run()
+
+    kc3, vc3 = fresh()
+    outs = [torch.empty_like(want[0]) for _ in range(steps)]
+    chained(kc3, vc3, outs)
+    torch.cuda.synchronize()
+    for j in range(steps):
+        assert torch.equal(outs[j], want[j]), f"chained step {j}"
+    assert torch.equal(kc3, kc1) and torch.equal(vc3, vc1)
+    kc4, vc4 = fresh()
+    outs4 = [torch.zeros_like(want[0]) for _ in range(steps)]
+    chained(kc4, vc4, outs4)  # warm-up: what a first call allocates is allocated outside the capture
+    torch.cuda.synchronize()
+    k0, v0 = fresh()
+    kc4.copy_(k0)
+    vc4.copy_(v0)
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        chained(kc4, vc4, outs4)
+    for o in outs4:
+        o.zero_()
+    gr.replay()
+    torch.cuda.synchronize()
+    for j in range(steps):
+        assert torch.equal(outs4[j], want[j]), f"graph step {j}"
     # and layer after layer over caches nobody writes (fresh_rows = 0), each call behind the one before
     out = [torch.empty_like(want[0]) for _ in range(3)]
     calls = [P.PackedAttention(qs[i], kc2, vc2, lens0, kq, vq, cfg, out=out[i], kv_len_add=steps, after_prev=True, fresh_rows=0) for i in range(3)]
