@@ -69,18 +69,25 @@ __device__ __forceinline__ uint16_t to16(float f) {
 // kernels, candle-core/src/accel/attention.rs:428-435); the rows' elements d .. HD - 1 are zeros in shared memory and
 // are not stored. BF16: the mma operand type (bf16, else f16). Queries, keys and values of another dtype (f32
 // everywhere, E4M3 or f32 keys and values) are rounded to it on their way into shared memory.
-template <int HD, bool BF16>
+// DEC (decode: the kv head's packed rows fit one 16-row group): the four warps share the keys of every tile instead of
+// the tile's rows. Each takes 16 of its 64 keys for the same 16 rows, with a running maximum and partial sums of its
+// own; the four partial results are merged through shared memory when the keys are done. Without it three of the four
+// warps would run the products and the softmax of rows that do not exist.
+template <int HD, bool BF16, bool DEC>
 __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams p) {
     constexpr int ROWB = HD * 2 + 16;          // padded row bytes in shared memory
     constexpr int KSTEPS = HD / 16, NT = HD / 8;
     constexpr int CH = HD / 8;                 // 16-byte chunks per row
     constexpr bool QREG = HD <= 128;           // the Q fragments stay in registers; at 256 they are re-read per k step
+    constexpr int KG = DEC ? 1 : FA_BN / 16;   // groups of 16 keys of a tile that one warp takes
     const uint32_t D = p.d;                    // elements per row in memory (a multiple of 8, at most HD)
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sQ = smem_u32(smem);                       // [FA_BM][ROWB]
     const uint32_t sK = sQ + FA_BM * ROWB;                    // 2 x [FA_BN][ROWB]
     const uint32_t sV = sK + 2 * FA_BN * ROWB;                // 2 x [FA_BN][ROWB]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+    const int wrow = DEC ? 0 : warp;           // the warp's group of 16 rows
+    const int kg0 = DEC ? warp : 0;            // its first group of 16 keys
     const uint32_t hk = blockIdx.y;
     const uint32_t b = blockIdx.z / p.n_splits, split = blockIdx.z % p.n_splits;
     const uint32_t G = p.group;
@@ -186,7 +193,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
     if (ntiles > 0) load_tile(0);
     __syncthreads();
     // ldmatrix x4: rows (lane & 15) of the warp's 16 rows, column halves by lane >> 4
-    const uint32_t q_base = sQ + (warp * 16 + (lane & 15)) * ROWB + (lane >> 4) * 16;
+    const uint32_t q_base = sQ + (wrow * 16 + (lane & 15)) * ROWB + (lane >> 4) * 16;
     uint32_t qa[QREG ? KSTEPS : 1][4];
     if (QREG) {
 #pragma unroll
@@ -199,7 +206,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
     bool r_ok[2];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-        const uint32_t r = row0 + warp * 16 + g + 8 * e;
+        const uint32_t r = row0 + wrow * 16 + g + 8 * e;
         r_ok[e] = r < R;
         r_lo[e] = r_hi[e] = r_pos[e] = 0;
         if (r_ok[e]) {
@@ -213,7 +220,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
     long long w_lomax = 0, w_himin = 0;
     {
         long long a, bq, cpos;
-        const uint32_t rf = row0 + warp * 16, rl = min(row0 + warp * 16 + 16, R);
+        const uint32_t rf = row0 + wrow * 16, rl = min(row0 + wrow * 16 + 16, R);
         if (rf < R) {
             range_of(rl - 1, w_lomax, a, cpos);
             range_of(rf, a, w_himin, cpos);
@@ -236,20 +243,20 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
         __syncthreads();
         const long long j0 = s_lo + (long long)t * FA_BN;
         const uint32_t tk = sK + (t & 1) * FA_BN * ROWB, tv = sV + (t & 1) * FA_BN * ROWB;
-        // ---- S = Q K^T: 8 key groups of 8
-        float s[FA_BN / 8][4];
+        // ---- S = Q K^T: the warp's key groups of 8 (all eight of the tile, or the two of its 16 keys)
+        float s[2 * KG][4];
 #pragma unroll
-        for (int n = 0; n < FA_BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+        for (int n = 0; n < 2 * KG; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
             uint32_t a0, a1, a2, a3;
             if (QREG) a0 = qa[QREG ? ks : 0][0], a1 = qa[QREG ? ks : 0][1], a2 = qa[QREG ? ks : 0][2], a3 = qa[QREG ? ks : 0][3];
             else ldsm_x4(q_base + ks * 32, a0, a1, a2, a3);
 #pragma unroll
-            for (int np = 0; np < FA_BN / 16; ++np) {
-                // matrices: keys np*16 + (0..7 | 8..15), dims ks*16 + (0..7 | 8..15)
+            for (int np = 0; np < KG; ++np) {
+                // matrices: keys (kg0 + np)*16 + (0..7 | 8..15), dims ks*16 + (0..7 | 8..15)
                 uint32_t b0, b1, b2, b3;
-                const uint32_t addr = tk + (np * 16 + (lane & 7) + ((lane >> 4) << 3)) * ROWB + ks * 32 + ((lane >> 3) & 1) * 16;
+                const uint32_t addr = tk + ((kg0 + np) * 16 + (lane & 7) + ((lane >> 4) << 3)) * ROWB + ks * 32 + ((lane >> 3) & 1) * 16;
                 ldsm_x4(addr, b0, b1, b2, b3);
                 mma16816<BF16>(s[2 * np], a0, a1, a2, a3, b0, b1);
                 mma16816<BF16>(s[2 * np + 1], a0, a1, a2, a3, b2, b3);
@@ -259,13 +266,13 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
         const bool full = plain && j0 >= w_lomax && j0 + FA_BN <= w_himin && j0 + FA_BN <= s_hi;
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int n = 0; n < FA_BN / 8; ++n) {
+        for (int n = 0; n < 2 * KG; ++n) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int e = i >> 1;
                 float x = s[n][i] * sc;
                 if (!full) {
-                    const long long j = j0 + 8 * n + 2 * c + (i & 1);
+                    const long long j = j0 + 16 * kg0 + 8 * n + 2 * c + (i & 1);
                     if (p.softcap > 0.0f) x = p.softcap * tanhf(x / p.softcap);
                     if (slope[e] != 0.0f) x -= slope[e] * fabsf((float)(r_pos[e] - j));
                     if (!(r_ok[e] && j >= r_lo[e] && j < r_hi[e] && j < s_hi)) x = -INFINITY;
@@ -292,9 +299,9 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
             oacc[n][2] *= alpha[1];
             oacc[n][3] *= alpha[1];
         }
-        uint32_t pa[FA_BN / 16][4];
+        uint32_t pa[KG][4];
 #pragma unroll
-        for (int n = 0; n < FA_BN / 8; ++n) {
+        for (int n = 0; n < 2 * KG; ++n) {
             const float p0 = fast_exp2((s[n][0] - msafe[0]) * LOG2E_F), p1 = fast_exp2((s[n][1] - msafe[0]) * LOG2E_F);
             const float p2 = fast_exp2((s[n][2] - msafe[1]) * LOG2E_F), p3 = fast_exp2((s[n][3] - msafe[1]) * LOG2E_F);
             l[0] += p0 + p1;
@@ -302,14 +309,14 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
             pa[n >> 1][(n & 1) * 2] = pack2<BF16>(p0, p1);
             pa[n >> 1][(n & 1) * 2 + 1] = pack2<BF16>(p2, p3);
         }
-        // ---- O += P V: contraction over the 64 keys in steps of 16
+        // ---- O += P V: contraction over the warp's keys in steps of 16
 #pragma unroll
-        for (int kk = 0; kk < FA_BN / 16; ++kk) {
+        for (int kk = 0; kk < KG; ++kk) {
 #pragma unroll
             for (int np = 0; np < NT / 2; ++np) {
-                // transposed matrices: keys kk*16 + (0..7 | 8..15), dims np*16 + (0..7 | 8..15)
+                // transposed matrices: keys (kg0 + kk)*16 + (0..7 | 8..15), dims np*16 + (0..7 | 8..15)
                 uint32_t b0, b1, b2, b3;
-                const uint32_t addr = tv + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + np * 32 + (lane >> 4) * 16;
+                const uint32_t addr = tv + ((kg0 + kk) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + np * 32 + (lane >> 4) * 16;
                 ldsm_x4_trans(addr, b0, b1, b2, b3);
                 mma16816<BF16>(oacc[2 * np], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b0, b1);
                 mma16816<BF16>(oacc[2 * np + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b2, b3);
@@ -324,6 +331,45 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
         l[e] += __shfl_xor_sync(0xffffffffu, l[e], 1);
         l[e] += __shfl_xor_sync(0xffffffffu, l[e], 2);
     }
+    if constexpr (DEC) {
+        // The four warps hold partial results of the same 16 rows over different keys: [warp][row][HD sums, maximum, sum
+        // of weights] in the K / V buffers (every tile is consumed: the loop ends with a barrier), then eight threads
+        // per row merge them.
+        constexpr int MS = HD + 2;
+        float *mg = reinterpret_cast<float *>(smem + FA_BM * ROWB);
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            float *dst = mg + ((size_t)warp * 16 + g + 8 * e) * MS;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) *reinterpret_cast<float2 *>(dst + 8 * n + 2 * c) = make_float2(oacc[n][2 * e], oacc[n][2 * e + 1]);
+            if (c == 0) dst[HD] = m[e], dst[HD + 1] = l[e];
+        }
+        __syncthreads();
+        const uint32_t row = tid >> 3, ch = tid & 7, r = row0 + row;
+        if (r >= R) return;
+        float f[FA_WARPS], M = -INFINITY, L = 0.0f;
+#pragma unroll
+        for (int w = 0; w < FA_WARPS; ++w) M = fmaxf(M, mg[((size_t)w * 16 + row) * MS + HD]);
+        const float msafe = M == -INFINITY ? 0.0f : M;
+#pragma unroll
+        for (int w = 0; w < FA_WARPS; ++w) {
+            f[w] = fast_exp2((mg[((size_t)w * 16 + row) * MS + HD] - msafe) * LOG2E_F);
+            L += f[w] * mg[((size_t)w * 16 + row) * MS + HD + 1];
+        }
+        const float inv = L > 0.0f ? p.vd / L : 0.0f;
+        const uint32_t i = r / G, h = hk * G + r % G;
+        const uint64_t orow = (q0 + i) * p.hq + h, prow = (uint64_t)split * p.rows_total + orow;
+#pragma unroll 4
+        for (uint32_t dd = ch * (HD / 8); dd < (ch + 1) * (HD / 8); ++dd) {
+            if (dd >= D) break;
+            float o = 0.0f;
+#pragma unroll
+            for (int w = 0; w < FA_WARPS; ++w) o = fmaf(f[w], mg[((size_t)w * 16 + row) * MS + dd], o);
+            if (p.n_splits == 1) store_elem_rt(p.o, orow * D + dd, o * inv, p.q_dtype);
+            else p.part_o[prow * D + dd] = o * inv;
+        }
+        if (p.n_splits > 1 && ch == 0) p.part_lse[prow] = L > 0.0f ? M + logf(L) : -INFINITY;
+    } else {
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
         const uint32_t r = row0 + warp * 16 + g + 8 * e;
@@ -352,6 +398,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
                 if ((uint32_t)8 * n < D) *reinterpret_cast<float2 *>(po + 8 * n + 2 * c) = make_float2(oacc[n][2 * e] * inv, oacc[n][2 * e + 1] * inv);
             if (c == 0) p.part_lse[prow] = l[e] > 0.0f ? m[e] + logf(l[e]) : -INFINITY;
         }
+    }
     }
 }
 
@@ -433,6 +480,16 @@ static int fa_plan(const B200FaArgs *a, FaPlan &pl) {
     if (ctas < 2ull * sms && a->lk > 2 * FA_BN) {
         const uint64_t by_occ = (2ull * sms + ctas - 1) / ctas, by_keys = (a->lk + 4 * FA_BN - 1) / (4 * FA_BN);
         splits = (uint32_t)std::min<uint64_t>(std::min(by_occ, by_keys), 64);
+    } else if (rows <= 16 && a->lk >= 16 * FA_BN) {
+        // decode with enough blocks to fill the device: up to four key splits where they make the blocks a better fit to
+        // whole waves of resident blocks (two per SM, one at head dim 256)
+        const uint64_t resident = (uint64_t)sms * (a->d > 128 ? 1 : 2);
+        double best = 0.0;
+        for (uint32_t sp = 1; sp <= 4; ++sp) {
+            const uint64_t n = ctas * sp, waves = (n + resident - 1) / resident;
+            const double fill = (double)n / (double)(waves * resident) - 0.02 * (sp - 1);  // a split costs a partial result
+            if (fill > best) best = fill, splits = sp;
+        }
     }
     p.n_splits = 1;
     // long chunks run as whole tiles on the tcgen05 kernel and are never split along the keys
@@ -447,9 +504,9 @@ static int fa_plan(const B200FaArgs *a, FaPlan &pl) {
     return B200_OK;
 }
 
-template <int HD, bool BF16>
-static int fa_launch(const FaPlan &pl, cudaStream_t stream) {
-    auto kern = fa_dense_kernel<HD, BF16>;
+template <int HD, bool BF16, bool DEC>
+static int fa_launch_as(const FaPlan &pl, cudaStream_t stream) {
+    auto kern = fa_dense_kernel<HD, BF16, DEC>;
     static thread_local bool done[16] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -467,6 +524,13 @@ static int fa_launch(const FaPlan &pl, cudaStream_t stream) {
         rc = check_launch("fa_combine");
     }
     return rc;
+}
+
+// decode calls (the packed rows of a kv head fit one group of 16) share the keys of a tile among the warps
+template <int HD, bool BF16>
+static int fa_launch(const FaPlan &pl, cudaStream_t stream) {
+    if ((uint64_t)pl.p.lq * pl.p.group <= 16) return fa_launch_as<HD, BF16, true>(pl, stream);
+    return fa_launch_as<HD, BF16, false>(pl, stream);
 }
 
 }  // namespace b200

@@ -97,6 +97,12 @@ ORACLE_CASES = [
     ("d96_prefill", "f16", 2, 90, 90, 4, 2, 96, -1, 0, 0.0, False, False),
     ("d40_decode", "bf16", 1, 2, 1300, 4, 4, 40, -1, 0, 0.0, False, False),
     ("d8_noncausal", "f16", 1, 33, 47, 2, 1, 8, -1, -1, 0.0, False, False),
+    # decode calls (at most 16 packed rows per kv head): the warps share the keys of a tile and merge at the end
+    ("dec_16_rows_exactly", "bf16", 2, 4, 1000, 8, 2, 128, -1, 0, 0.0, False, False),
+    ("dec_window_softcap_alibi", "f16", 3, 2, 777, 8, 4, 128, 300, 0, 25.0, True, False),
+    ("dec_f32_q_short", "f32", 1, 1, 37, 4, 1, 64, -1, 0, 0.0, False, False),
+    ("dec_fp8_many_blocks", "bf16", 40, 1, 1100, 8, 8, 128, -1, 0, 0.0, False, True),
+    ("dec_lq_longer_than_lk", "f16", 1, 5, 3, 2, 1, 128, -1, 0, 0.0, False, False),
 ]
 
 
