@@ -80,10 +80,11 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
     constexpr int CH = HD / 8;                 // 16-byte chunks per row
     constexpr bool QREG = HD <= 128;           // the Q fragments stay in registers; at 256 they are re-read per k step
     constexpr int KG = DEC ? 1 : FA_BN / 16;   // groups of 16 keys of a tile that one warp takes
+    constexpr int QROWS = DEC ? 16 : FA_BM;    // rows of the Q tile in shared memory
     const uint32_t D = p.d;                    // elements per row in memory (a multiple of 8, at most HD)
     extern __shared__ __align__(128) uint8_t smem[];
-    const uint32_t sQ = smem_u32(smem);                       // [FA_BM][ROWB]
-    const uint32_t sK = sQ + FA_BM * ROWB;                    // 2 x [FA_BN][ROWB]
+    const uint32_t sQ = smem_u32(smem);                       // [QROWS][ROWB]
+    const uint32_t sK = sQ + QROWS * ROWB;                    // 2 x [FA_BN][ROWB]
     const uint32_t sV = sK + 2 * FA_BN * ROWB;                // 2 x [FA_BN][ROWB]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
     const int wrow = DEC ? 0 : warp;           // the warp's group of 16 rows
@@ -128,7 +129,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
     const int ntiles = s_hi > s_lo ? (int)((s_hi - s_lo + FA_BN - 1) / FA_BN) : 0;
 
     // ---- Q tile -> shared memory (any alignment), then A fragments in registers
-    for (int idx = tid; idx < FA_BM * HD; idx += FA_WARPS * 32) {
+    for (int idx = tid; idx < QROWS * HD; idx += FA_WARPS * 32) {
         const uint32_t rr = idx / HD, dd = idx % HD, r = row0 + rr;
         uint16_t v = 0;
         if (r < R) {
@@ -336,7 +337,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
         // of weights] in the K / V buffers (every tile is consumed: the loop ends with a barrier), then eight threads
         // per row merge them.
         constexpr int MS = HD + 2;
-        float *mg = reinterpret_cast<float *>(smem + FA_BM * ROWB);
+        float *mg = reinterpret_cast<float *>(smem + QROWS * ROWB);
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
             float *dst = mg + ((size_t)warp * 16 + g + 8 * e) * MS;
@@ -482,8 +483,8 @@ static int fa_plan(const B200FaArgs *a, FaPlan &pl) {
         splits = (uint32_t)std::min<uint64_t>(std::min(by_occ, by_keys), 64);
     } else if (rows <= 16 && a->lk >= 16 * FA_BN) {
         // decode with enough blocks to fill the device: up to four key splits where they make the blocks a better fit to
-        // whole waves of resident blocks (two per SM, one at head dim 256)
-        const uint64_t resident = (uint64_t)sms * (a->d > 128 ? 1 : 2);
+        // whole waves of resident blocks (four per SM up to head dim 64, three up to 128, one at 256)
+        const uint64_t resident = (uint64_t)sms * (a->d > 128 ? 1 : (a->d > 64 ? 3 : 4));
         double best = 0.0;
         for (uint32_t sp = 1; sp <= 4; ++sp) {
             const uint64_t n = ctas * sp, waves = (n + resident - 1) / resident;
@@ -497,7 +498,8 @@ static int fa_plan(const B200FaArgs *a, FaPlan &pl) {
     if ((uint64_t)a->b * p.n_splits > 65535) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "flash_attn: batch x splits too large");
     pl.grid = dim3(row_tiles, a->hkv, a->b * p.n_splits);
     const size_t rowb = (a->d <= 64 ? 64 : (a->d <= 128 ? 128 : 256)) * 2 + 16;
-    pl.smem = (FA_BM + 4 * FA_BN) * rowb;
+    // a decode call keeps one group of 16 query rows in shared memory, which lets a third block share the SM
+    pl.smem = ((rows <= 16 ? 16 : FA_BM) + 4 * FA_BN) * rowb;
     const size_t part_o = p.n_splits > 1 ? (size_t)p.n_splits * p.rows_total * a->d * 4 : 0;
     pl.off_lse = (part_o + 255) / 256 * 256;
     pl.ws_bytes = p.n_splits > 1 ? pl.off_lse + (size_t)p.n_splits * p.rows_total * 4 : 0;

@@ -101,7 +101,7 @@ ORACLE_CASES = [
     ("dec_16_rows_exactly", "bf16", 2, 4, 1000, 8, 2, 128, -1, 0, 0.0, False, False),
     ("dec_window_softcap_alibi", "f16", 3, 2, 777, 8, 4, 128, 300, 0, 25.0, True, False),
     ("dec_f32_q_short", "f32", 1, 1, 37, 4, 1, 64, -1, 0, 0.0, False, False),
-    ("dec_fp8_many_blocks", "bf16", 40, 1, 1100, 8, 8, 128, -1, 0, 0.0, False, True),
+    ("dec_many_blocks", "bf16", 38, 1, 1030, 8, 8, 64, -1, 0, 0.0, False, False),
     ("dec_lq_longer_than_lk", "f16", 1, 5, 3, 2, 1, 128, -1, 0, 0.0, False, False),
 ]
 
