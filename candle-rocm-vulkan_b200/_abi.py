@@ -110,7 +110,7 @@ SYMBOLS = [
     "b200_tq_residual", "b200_tq_signs", "b200_rotation_matrix", "b200_tq_rotate_dense",
     "b200_describe", "b200_last_error", "b200_tq_rotate", "b200_tq_quantize", "b200_tq_dequantize", "b200_kv_append",
     "b200_tq_attention_workspace_bytes", "b200_tq_attention", "b200_tq_attention_static", "b200_tq_attention_gather",
-    "b200_flash_attn_workspace_bytes",
+    "b200_flash_attn_workspace_bytes", "b200_flash_attn_paged_workspace_bytes", "b200_flash_attn_paged",
     "b200_flash_attn", "b200_fa_prefill_append", "b200_device_wait_status", "b200_device_wait_check",
     "b200_pinned_alloc", "b200_pinned_free", "b200_pinned_len", "b200_pinned_wait_idle", "b200_pinned_ptr",
     "b200_copy_upload", "b200_copy_download", "b200_copy_event_wait_on_compute", "b200_copy_event_synchronize",
@@ -158,6 +158,9 @@ def lib():
         l.b200_flash_attn_workspace_bytes.argtypes = [C.POINTER(FaArgs)]
         l.b200_flash_attn_workspace_bytes.restype = C.c_size_t
         l.b200_flash_attn.argtypes = [C.POINTER(FaArgs), C.c_void_p]
+        l.b200_flash_attn_paged_workspace_bytes.argtypes = [C.POINTER(FaArgs), C.c_uint32]
+        l.b200_flash_attn_paged_workspace_bytes.restype = C.c_size_t
+        l.b200_flash_attn_paged.argtypes = [C.POINTER(FaArgs), C.c_void_p, C.c_uint32, C.c_void_p]
         l.b200_fa_prefill_append.argtypes = [C.POINTER(FaArgs), C.POINTER(KvAppendArgs), C.c_void_p]
         l.b200_device_wait_check.argtypes = [C.c_int]
         l.b200_pinned_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]

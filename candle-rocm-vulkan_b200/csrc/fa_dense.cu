@@ -100,6 +100,7 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
         k0 = p.cu_k[b];
         lk = p.cu_k[b + 1] - p.cu_k[b];
     }
+    if (p.pages) lk = min(lk, p.pg_keys[p.n_pages]);  // the keys of a paged call are the valid rows of its blocks
     const uint32_t R = lq * G;  // packed rows of this kv head
     const uint32_t row0 = blockIdx.x * FA_BM;
     if (row0 >= R) return;
@@ -139,18 +140,60 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
         }
         *reinterpret_cast<uint16_t *>(smem + rr * ROWB + dd * 2) = v;
     }
+    // Paged K / V: the addresses of a tile's 64 rows, found by its first 64 threads in the block table (block i holds
+    // the keys pg_keys[i] .. pg_keys[i + 1] - 1 at rows 0 .. of its (batch entry, kv head) slab) and left in shared memory
+    // behind the tiles; `cursor` is a block at or before the tile's first key (tiles are loaded in ascending order).
+    const char **row_k = reinterpret_cast<const char **>(smem + QROWS * ROWB + 4 * FA_BN * ROWB);
+    const char **row_v = row_k + FA_BN;
+    uint32_t *cursor = reinterpret_cast<uint32_t *>(row_v + FA_BN);
+    if (p.pages && tid == 0) {
+        // the block that holds the split's first key: binary search over the prefix sums, once per block of threads
+        uint32_t lo = 0, hi = p.n_pages;
+        while (lo + 1 < hi) {
+            const uint32_t mid = (lo + hi) / 2;
+            if ((long long)p.pg_keys[mid] <= s_lo) lo = mid;
+            else hi = mid;
+        }
+        *cursor = lo;
+    }
+    auto locate_rows = [&](long long j0) {
+        __syncthreads();  // the table of the previous tile has been read, the cursor is visible
+        if (tid < FA_BN) {
+            const long long j = j0 + tid;
+            const char *kr = nullptr, *vr = nullptr;
+            uint32_t pg = *cursor;
+            if (j < s_hi) {
+                while (pg + 1 < p.n_pages && (long long)p.pg_keys[pg + 1] <= j) ++pg;
+                const B200Page pd = p.pages[pg];
+                const uint64_t row = (uint64_t)(j - p.pg_keys[pg]), slab = (uint64_t)b * p.hkv + hk;
+                kr = reinterpret_cast<const char *>(pd.k) + ((slab * pd.k_cap + row) * p.k_ss) * kv_esize;
+                vr = reinterpret_cast<const char *>(pd.v) + ((slab * pd.v_cap + row) * p.v_ss) * kv_esize;
+            }
+            row_k[tid] = kr;
+            row_v[tid] = vr;
+            __syncwarp();
+            if (tid == FA_BN - 1 && j < s_hi) *cursor = pg;  // at or before the next tile's first key
+        }
+        __syncthreads();
+    };
     // K / V tile loader: tile t of this split into buffer (t & 1)
     auto load_tile = [&](int t) {
         const long long j0 = s_lo + (long long)t * FA_BN;
         const uint32_t dk = sK + (t & 1) * FA_BN * ROWB, dv = sV + (t & 1) * FA_BN * ROWB;
+        const bool paged = p.pages != nullptr;
+        if (paged) locate_rows(j0);
+        // row rr of the tile (key j): where its elements start
+        auto k_row = [&](int rr, long long j) { return paged ? row_k[rr] : kb + ((uint64_t)j * p.k_ss) * kv_esize; };
+        auto v_row = [&](int rr, long long j) { return paged ? row_v[rr] : vb + ((uint64_t)j * p.v_ss) * kv_esize; };
         if (p.kv_kind == 0) {
             for (int idx = tid; idx < FA_BN * CH; idx += FA_WARPS * 32) {
                 const int rr = idx / CH, ch = idx % CH;
                 const long long j = j0 + rr;
                 const bool ok = j < s_hi && (uint32_t)ch * 8 < D;
                 const long long jj = j < s_hi ? j : s_lo;
-                cp_async16(dk + rr * ROWB + ch * 16, kb + ((uint64_t)jj * p.k_ss) * 2 + ch * 16, ok);
-                cp_async16(dv + rr * ROWB + ch * 16, vb + ((uint64_t)jj * p.v_ss) * 2 + ch * 16, ok);
+                const int rj = j < s_hi ? rr : 0;  // a row past the end copies nothing: any valid address will do
+                cp_async16(dk + rr * ROWB + ch * 16, k_row(rj, jj) + ch * 16, ok);
+                cp_async16(dv + rr * ROWB + ch * 16, v_row(rj, jj) + ch * 16, ok);
             }
         } else if (p.kv_kind == 2) {
             // f32 -> mma type: 8 elements per step
@@ -159,8 +202,8 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
                 const long long j = j0 + rr;
                 uint32_t ko[4] = {0, 0, 0, 0}, vo[4] = {0, 0, 0, 0};
                 if (j < s_hi && (uint32_t)ch * 8 < D) {
-                    const float *ks = reinterpret_cast<const float *>(kb) + (uint64_t)j * p.k_ss + ch * 8;
-                    const float *vs = reinterpret_cast<const float *>(vb) + (uint64_t)j * p.v_ss + ch * 8;
+                    const float *ks = reinterpret_cast<const float *>(k_row(rr, j)) + ch * 8;
+                    const float *vs = reinterpret_cast<const float *>(v_row(rr, j)) + ch * 8;
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         ko[e] = pack2<BF16>(ks[2 * e], ks[2 * e + 1]);
@@ -177,8 +220,8 @@ __global__ void __launch_bounds__(FA_WARPS * 32) fa_dense_kernel(const FaParams 
                 const long long j = j0 + rr;
                 uint32_t ko[4] = {0, 0, 0, 0}, vo[4] = {0, 0, 0, 0};
                 if (j < s_hi && (uint32_t)ch * 8 < D) {
-                    const uint8_t *ks = reinterpret_cast<const uint8_t *>(kb) + (uint64_t)j * p.k_ss + ch * 8;
-                    const uint8_t *vs = reinterpret_cast<const uint8_t *>(vb) + (uint64_t)j * p.v_ss + ch * 8;
+                    const uint8_t *ks = reinterpret_cast<const uint8_t *>(k_row(rr, j)) + ch * 8;
+                    const uint8_t *vs = reinterpret_cast<const uint8_t *>(v_row(rr, j)) + ch * 8;
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         ko[e] = pack2<BF16>(e4m3_to_f(ks[2 * e]), e4m3_to_f(ks[2 * e + 1]));
@@ -434,7 +477,30 @@ struct FaPlan {
     bool bf16;  // mma operand type
 };
 
-static int fa_plan(const B200FaArgs *a, FaPlan &pl) {
+// keys before every block of a paged call, and their total behind them: one block of threads, a running sum over
+// chunks of 256 blocks
+__global__ void __launch_bounds__(256) fa_page_prefix_kernel(const B200Page *__restrict__ pages, uint32_t n_pages, uint32_t *__restrict__ pg_keys) {
+    __shared__ uint32_t sk[256];
+    uint32_t base = 0;
+    for (uint32_t start = 0; start < n_pages; start += 256) {
+        const uint32_t i = start + threadIdx.x;
+        const uint32_t r = i < n_pages ? pages[i].rows : 0u;
+        sk[threadIdx.x] = r;
+        __syncthreads();
+        for (int o = 1; o < 256; o <<= 1) {  // inclusive scan
+            const uint32_t add = threadIdx.x >= (unsigned)o ? sk[threadIdx.x - o] : 0u;
+            __syncthreads();
+            sk[threadIdx.x] += add;
+            __syncthreads();
+        }
+        if (i < n_pages) pg_keys[i] = base + sk[threadIdx.x] - r;
+        base += sk[255];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) pg_keys[n_pages] = base;
+}
+
+static int fa_plan(const B200FaArgs *a, FaPlan &pl, bool paged = false) {
     if (!a) return set_error(B200_ERR_BAD_ARG, "flash_attn: null args");
     if (a->hkv == 0 || a->hq % a->hkv != 0)
         return set_error(B200_ERR_BAD_ARG, "flash-attn: %u query heads are not a multiple of %u kv heads", a->hq, a->hkv);
@@ -449,12 +515,17 @@ static int fa_plan(const B200FaArgs *a, FaPlan &pl) {
     if (a->d == 0 || a->d > 256 || a->d % 8) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "flash_attn: head dim %u (fused kernel: multiples of 8 up to 256)", a->d);
     if (a->varlen && (!a->cu_q || !a->cu_k)) return set_error(B200_ERR_BAD_ARG, "flash_attn: varlen needs cu_q and cu_k");
     const bool fp8 = a->kv_dtype == B200_FP8;
-    if (kv16) {
+    if (paged && a->varlen) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "flash_attn_paged: cumulative lengths are not offered over paged blocks");
+    if (kv16 && !paged) {
         // cp.async moves 16-byte chunks: rows must start on 16-byte boundaries
         const uint64_t al = reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v);
         if ((al & 15) || ((a->k_strides[0] | a->k_strides[1] | a->k_strides[2] | a->v_strides[0] | a->v_strides[1] | a->v_strides[2]) & 7))
             return set_error(B200_ERR_UNSUPPORTED_SHAPE, "flash_attn: k / v rows must be 16-byte aligned");
     }
+    if (kv16 && paged && ((a->k_strides[1] | a->v_strides[1]) & 7))
+        return set_error(B200_ERR_UNSUPPORTED_SHAPE, "flash_attn_paged: k / v rows must be 16-byte aligned");
+    if (paged && (a->k_strides[1] < a->d || a->v_strides[1] < a->d))
+        return set_error(B200_ERR_BAD_ARG, "flash_attn_paged: row strides below the head dim");
     FaParams &p = pl.p;
     memset(&p, 0, sizeof(p));
     p.q = a->q; p.k = a->k; p.v = a->v; p.o = a->o;
@@ -494,12 +565,13 @@ static int fa_plan(const B200FaArgs *a, FaPlan &pl) {
     }
     p.n_splits = 1;
     // long chunks run as whole tiles on the tcgen05 kernel and are never split along the keys
-    if (!fa_prefill_sm100_supported(p, kv16)) p.n_splits = std::max(splits, 1u);
+    if (paged || !fa_prefill_sm100_supported(p, kv16)) p.n_splits = std::max(splits, 1u);
     if ((uint64_t)a->b * p.n_splits > 65535) return set_error(B200_ERR_UNSUPPORTED_SHAPE, "flash_attn: batch x splits too large");
     pl.grid = dim3(row_tiles, a->hkv, a->b * p.n_splits);
     const size_t rowb = (a->d <= 64 ? 64 : (a->d <= 128 ? 128 : 256)) * 2 + 16;
     // a decode call keeps one group of 16 query rows in shared memory, which lets a third block share the SM
     pl.smem = ((rows <= 16 ? 16 : FA_BM) + 4 * FA_BN) * rowb;
+    if (paged) pl.smem += 2 * FA_BN * sizeof(void *) + 16;  // the row addresses of a tile and the block cursor
     const size_t part_o = p.n_splits > 1 ? (size_t)p.n_splits * p.rows_total * a->d * 4 : 0;
     pl.off_lse = (part_o + 255) / 256 * 256;
     pl.ws_bytes = p.n_splits > 1 ? pl.off_lse + (size_t)p.n_splits * p.rows_total * 4 : 0;
@@ -513,7 +585,9 @@ static int fa_launch_as(const FaPlan &pl, cudaStream_t stream) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 16 && !done[dev]) {
-        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+        // the most this instantiation ever asks for: its tiles plus the row addresses of a paged call
+        const int most = ((DEC ? 16 : FA_BM) + 4 * FA_BN) * (HD * 2 + 16) + 2 * FA_BN * (int)sizeof(void *) + 16;
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
         if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "flash_attn: shared memory opt-in: %s", cudaGetErrorString(e));
         done[dev] = true;
     }
@@ -562,6 +636,47 @@ extern "C" int b200_flash_attn(const B200FaArgs *a, b200_stream_t stream_) {
     const bool bf = pl.bf16;
     // long prefill chunks: tiles on the tcgen05 tensor cores
     if (fa_prefill_sm100_supported(pl.p, pl.p.kv_kind == 0)) return fa_prefill_sm100_launch(pl.p, bf, stream);
+    if (a->d <= 64) return bf ? fa_launch<64, true>(pl, stream) : fa_launch<64, false>(pl, stream);
+    if (a->d <= 128) return bf ? fa_launch<128, true>(pl, stream) : fa_launch<128, false>(pl, stream);
+    return bf ? fa_launch<256, true>(pl, stream) : fa_launch<256, false>(pl, stream);
+}
+
+// Decoding attention over the dense K / V of paged cache blocks, read where they are (candle-core/src/cuda_backend/
+// accel.rs:391-506, kernels fa_rowp* / fa_rowpg*). Workspace: the keys before every block, then the split buffers.
+static size_t fa_paged_prefix_bytes(uint32_t n_pages) { return ((size_t)(n_pages + 1) * 4 + 255) / 256 * 256; }
+
+extern "C" size_t b200_flash_attn_paged_workspace_bytes(const B200FaArgs *a, uint32_t n_pages) {
+    FaPlan pl;
+    if (n_pages == 0 || fa_plan(a, pl, true)) return 0;
+    return fa_paged_prefix_bytes(n_pages) + pl.ws_bytes;
+}
+
+extern "C" int b200_flash_attn_paged(const B200FaArgs *a, const B200Page *pages, uint32_t n_pages, b200_stream_t stream_) {
+    if (!pages || n_pages == 0) return set_error(B200_ERR_BAD_ARG, "flash_attn_paged: no blocks");
+    FaPlan pl;
+    const int rc = fa_plan(a, pl, true);
+    if (rc) return rc;
+    if (a->total_q * a->hq == 0 || a->b == 0) return B200_OK;
+    if (!a->q || !a->o) return set_error(B200_ERR_BAD_ARG, "flash_attn_paged: null pointer");
+    const size_t pre = fa_paged_prefix_bytes(n_pages);
+    if (!a->workspace || a->workspace_bytes < pre + pl.ws_bytes)
+        return set_error(B200_ERR_WORKSPACE, "flash_attn_paged: workspace of %zu bytes needed, %zu given", pre + pl.ws_bytes,
+                         a->workspace ? a->workspace_bytes : (size_t)0);
+    if (reinterpret_cast<uintptr_t>(a->workspace) & 15) return set_error(B200_ERR_BAD_ARG, "flash_attn_paged: workspace must be 16-byte aligned");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    char *ws = reinterpret_cast<char *>(a->workspace);
+    uint32_t *pg_keys = reinterpret_cast<uint32_t *>(ws);
+    fa_page_prefix_kernel<<<1, 256, 0, stream>>>(pages, n_pages, pg_keys);
+    int lrc = check_launch("flash_attn_paged (prefix)");
+    if (lrc) return lrc;
+    pl.p.pages = pages;
+    pl.p.pg_keys = pg_keys;
+    pl.p.n_pages = n_pages;
+    if (pl.ws_bytes) {
+        pl.p.part_o = reinterpret_cast<float *>(ws + pre);
+        pl.p.part_lse = reinterpret_cast<float *>(ws + pre + pl.off_lse);
+    }
+    const bool bf = pl.bf16;
     if (a->d <= 64) return bf ? fa_launch<64, true>(pl, stream) : fa_launch<64, false>(pl, stream);
     if (a->d <= 128) return bf ? fa_launch<128, true>(pl, stream) : fa_launch<128, false>(pl, stream);
     return bf ? fa_launch<256, true>(pl, stream) : fa_launch<256, false>(pl, stream);

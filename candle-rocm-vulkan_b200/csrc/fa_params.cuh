@@ -19,6 +19,11 @@ struct FaParams {
     int32_t q_dtype;  // dtype of q and o
     int32_t kv_kind;  // 0: 16-bit elements of the mma type, 1: E4M3 bytes, 2: f32
     uint64_t rows_total;  // total_q * hq
+    // paged K / V (b200_flash_attn_paged): the blocks, and the keys before every block (n_pages + 1 entries, the last one
+    // the total), written by a prefix kernel in front of the attention; null for dense tensors
+    const B200Page *pages;
+    const uint32_t *pg_keys;
+    uint32_t n_pages;
 };
 
 // prefill tiles on the 5th generation tensor cores (fa_prefill_sm100.cu)

@@ -10,6 +10,7 @@ reference under `strict`, flash_attn.rs:529-540).
 import ctypes as C
 from typing import Optional
 
+import numpy as np
 import torch
 
 from . import _abi as A
@@ -194,22 +195,64 @@ def flash_attn_blocks(q, blocks, cfg: FlashAttnConfig) -> torch.Tensor:
     """Attention of `q: (batch, q_heads, seq_q, head_dim)` over the dense K / V of paged cache blocks (`KvBlockRef` with
     (batch, kv_heads, capacity, head_dim) tensors of which the first `rows` positions are valid); masks, soft-capping
     and ALiBi are bottom-right aligned over the concatenated keys; output (batch, q_heads, seq_q, head_dim) in the query
-    dtype (candle-nn/src/flash_attn.rs:691-727). The valid rows are concatenated on the device and the call runs
-    `flash_attn_bhsd`: the path the reference takes for every call that its in-place row kernel does not serve (more
-    than 4 query tokens, more than 128 blocks, other layouts), with the same results up to the summation order."""
+    dtype (candle-nn/src/flash_attn.rs:691-727). The blocks are read where they are (b200_flash_attn_paged: a block table
+    in device memory, any number of blocks and of query tokens; the reference's in-place kernel serves up to 4 query
+    tokens and 128 blocks and concatenates otherwise). Blocks that the kernel cannot read in place (rows that are not
+    contiguous along the head dim or do not start on 16-byte boundaries, row strides that differ between blocks) are
+    concatenated on the device and the call runs `flash_attn_bhsd`."""
     if q.dim() != 4:
         raise ValueError(f"flash-attn blocks: q must be (batch, q_heads, seq_q, head_dim), got {tuple(q.shape)}")
-    b, _, _, d = q.shape
-    _check_blocks(blocks, b, "flash-attn blocks")
+    b, hq, lq, d = q.shape
+    hkv, lk = _check_blocks(blocks, b, "flash-attn blocks")
     if blocks[0].k.shape[3] != d or blocks[0].v.shape[3] != d:
         raise ValueError(f"flash-attn blocks: k {tuple(blocks[0].k.shape)} / v {tuple(blocks[0].v.shape)} do not match the head dim {d} of q")
     live = [blk for blk in blocks if blk.rows > 0]
-    if len(live) == 1:
-        k, v = live[0].k[:, :, : live[0].rows], live[0].v[:, :, : live[0].rows]
-    else:
-        k = torch.cat([blk.k[:, :, : blk.rows].to(q.device) for blk in live], dim=2)
-        v = torch.cat([blk.v[:, :, : blk.rows].to(q.device) for blk in live], dim=2)
-    return flash_attn_bhsd(q, k, v, cfg)
+
+    def in_place(t, ref):
+        # layout of paged_block_layout (flash_attn.rs:618-646): contiguous last dim, head stride = whole rows, batch
+        # stride = kv_heads head strides, one row stride for all blocks
+        return (t.is_cuda and t.device == q.device and t.stride(3) == 1 and t.stride(2) == ref.stride(2)
+                and t.stride(1) == t.shape[2] * t.stride(2) and t.stride(0) == t.shape[1] * t.stride(1)
+                and t.data_ptr() % 16 == 0 and (t.stride(2) * t.element_size()) % 16 == 0)
+
+    if not all(in_place(blk.k, live[0].k) and in_place(blk.v, live[0].v) for blk in live) or hq % hkv != 0:
+        if len(live) == 1:
+            k, v = live[0].k[:, :, : live[0].rows], live[0].v[:, :, : live[0].rows]
+        else:
+            k = torch.cat([blk.k[:, :, : blk.rows].to(q.device) for blk in live], dim=2)
+            v = torch.cat([blk.v[:, :, : blk.rows].to(q.device) for blk in live], dim=2)
+        return flash_attn_bhsd(q, k, v, cfg)
+    _need_cuda(q, "q")
+    if cfg.softcap is not None and not cfg.softcap > 0.0:
+        raise ValueError("flash-attn: softcap must be > 0")
+    qt = q.transpose(1, 2)  # (batch, seq, heads, head_dim) view, as the C ABI describes queries
+    if qt.stride(-1) != 1:
+        qt = qt.contiguous()
+    out = torch.empty((b, lq, hq, d), dtype=q.dtype, device=q.device)
+    table = np.zeros(len(live), dtype=np.dtype([("k", "<u8"), ("v", "<u8"), ("rows", "<u4"), ("k_cap", "<u4"), ("v_cap", "<u4"), ("pad", "<u4")]))
+    for n, blk in enumerate(live):
+        table[n] = (blk.k.data_ptr(), blk.v.data_ptr(), blk.rows, blk.k.shape[2], blk.v.shape[2], 0)
+    pages = torch.from_numpy(table.view(np.uint8)).to(q.device)
+    alibi, abs_ = _alibi(cfg, qt, b, hq)
+    wl, wr = cfg.window_i32()
+    a = A.FaArgs()
+    a.q, a.k, a.v, a.o = qt.data_ptr(), None, None, out.data_ptr()
+    a.q_dtype, a.kv_dtype = _dtype_id(qt), _kv_dtype_id(live[0].k)
+    a.b, a.lq, a.lk, a.hq, a.hkv, a.d = b, lq, lk, hq, hkv, d
+    a.q_strides = A.u64x3(*qt.stride()[:3])
+    a.k_strides, a.v_strides = A.u64x3(0, live[0].k.stride(2), 0), A.u64x3(0, live[0].v.stride(2), 0)
+    a.scale, a.softcap = cfg.softmax_scale, cfg.softcap or 0.0
+    a.wl, a.wr = wl, wr
+    a.k_descale, a.v_descale = cfg.k_descale, cfg.v_descale
+    a.alibi, a.alibi_bstride = (alibi.data_ptr() if alibi is not None else None), abs_
+    a.varlen, a.total_q = 0, b * lq
+    nbytes = A.lib().b200_flash_attn_paged_workspace_bytes(C.byref(a), len(live))
+    if nbytes == 0:
+        A.check(A.lib().b200_flash_attn_paged(C.byref(a), pages.data_ptr(), len(live), _stream(q.device)))  # raises with the reason
+    ws = _workspace(q.device, nbytes)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    A.check(A.lib().b200_flash_attn_paged(C.byref(a), pages.data_ptr(), len(live), _stream(q.device)))
+    return out.transpose(1, 2)
 
 
 def flash_attn_varlen_paged_windowed(q, k, v, seqlens_q, seqlens_k, block_table, mm_prefix_ranges, max_seqlen_q: int, max_seqlen_k: int,

@@ -413,6 +413,17 @@ typedef struct B200FaArgs {
 size_t b200_flash_attn_workspace_bytes(const B200FaArgs *args);
 int b200_flash_attn(const B200FaArgs *args, b200_stream_t stream);
 
+/* Replaces CudaStorage::flash_attn_paged (accel.rs:391-506; kernels fa_rowp*, fa_rowpg*): attention over the dense K / V
+ * of paged cache blocks, read where they are (no limit on the number of blocks or of query tokens). Block i (B200Page)
+ * holds rows[i] keys at rows 0 .. of its (batch entry, kv head) slabs, laid out (batch, kv head, capacity, row) with
+ * k_cap[i] / v_cap[i] rows per slab; the keys of the call are the blocks' valid rows in order (candle-nn/src/
+ * flash_attn.rs:608-646). args: q, o, dtypes, masks as for b200_flash_attn; k and v are ignored; k_strides[1] /
+ * v_strides[1] are the row strides of every block in elements (16-byte multiples for 16-bit elements, block pointers
+ * 16-byte aligned); lk bounds the number of keys (the blocks' total if smaller); varlen must be 0. `pages`: device array.
+ * The workspace holds the keys before every block (written by a one-block kernel in front) and the split buffers. */
+size_t b200_flash_attn_paged_workspace_bytes(const B200FaArgs *args, uint32_t n_pages);
+int b200_flash_attn_paged(const B200FaArgs *args, const B200Page *pages, uint32_t n_pages, b200_stream_t stream);
+
 /* Causal / windowed prefill with the new keys and values written into the compressed cache in
  * the same call. Replaces the pair flash_attn(q, k, v, scale, causal) + TurboKvCache::append(k, v)
  * (candle-flash-attn/src/lib.rs:149-157, candle-nn/src/turbo_quant.rs:916-945). `fa` describes the

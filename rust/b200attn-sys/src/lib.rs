@@ -283,6 +283,8 @@ extern "C" {
     // dense attention (CudaStorage::flash_attn / flash_attn_paged) and prefill with the cache write
     pub fn b200_flash_attn_workspace_bytes(args: *const B200FaArgs) -> usize;
     pub fn b200_flash_attn(args: *const B200FaArgs, stream: b200_stream_t) -> c_int;
+    pub fn b200_flash_attn_paged_workspace_bytes(args: *const B200FaArgs, n_pages: u32) -> usize;
+    pub fn b200_flash_attn_paged(args: *const B200FaArgs, pages: *const B200Page, n_pages: u32, stream: b200_stream_t) -> c_int;
     pub fn b200_fa_prefill_append(fa: *const B200FaArgs, append: *const B200KvAppendArgs, stream: b200_stream_t) -> c_int;
 
     // health of the bounded device waits

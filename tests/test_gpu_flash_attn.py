@@ -200,6 +200,50 @@ def test_blocks_match_the_oracle_on_the_concatenated_rows(P, oracle):
         assert_close(got.float().cpu().numpy().transpose(0, 2, 1, 3), want, what=f"blocks lq={lq}", out="bf16")
 
 
+@pytest.mark.parametrize("dt,d,page,nblk,lq,wl", [(torch.bfloat16, 128, 16, 300, 1, -1), (torch.float16, 64, 32, 70, 3, 500),
+                                                   (torch.float32, 256, 8, 90, 1, -1), ("fp8", 128, 16, 150, 2, -1),
+                                                   (torch.bfloat16, 128, 64, 40, 300, -1)])
+def test_many_blocks_read_in_place_equal_the_concatenated_call(P, dt, d, page, nblk, lq, wl):
+    """b200_flash_attn_paged over hundreds of blocks of one page each, carved out of one pool in shuffled order (so
+    that consecutive keys live far apart), the last block partly filled, one block empty: decode with key splits, a
+    few query tokens, a chunk of prefill. Against b200_flash_attn on the same rows concatenated, which reads the same
+    values in the same tiles: identical bits. Rows of the pool are wider than the head dim (a row stride of its own)."""
+    F = P.flash_attn
+    b, hq, hkv = 3, 8, 2
+    g = torch.Generator(device="cuda:0").manual_seed(nblk)
+    fp8 = dt == "fp8"
+    store = torch.float32 if fp8 else dt
+    pool_k = torch.randn((nblk, b, hkv, page, d + 16), generator=g, device="cuda:0").to(store)
+    pool_v = torch.randn((nblk, b, hkv, page, d + 16), generator=g, device="cuda:0").to(store)
+    if fp8:
+        pool_k, pool_v = (pool_k * 0.5).to(torch.float8_e4m3fn), (pool_v * 0.5).to(torch.float8_e4m3fn)
+    order = torch.randperm(nblk, generator=g, device="cuda:0").tolist()
+    blocks = []
+    for n, i in enumerate(order):
+        rows = page if n < nblk - 1 else max(1, page // 3)
+        if n == nblk // 2:
+            rows = 0
+        blocks.append(P.KvBlockRef(pool_k[i, :, :, :, :d], pool_v[i, :, :, :, :d], rows))
+    qdt = torch.bfloat16 if fp8 else dt
+    q = torch.randn((b, hq, lq, d), generator=g, device="cuda:0").to(qdt)
+    cfg = P.FlashAttnConfig(d ** -0.5).causal()
+    if wl >= 0:
+        cfg = cfg.window(wl, 0)
+    if fp8:
+        cfg.k_descale, cfg.v_descale = 2.0, 2.0
+    got = F.flash_attn_blocks(q, blocks, cfg)
+    k = torch.cat([blk.k[:, :, : blk.rows] for blk in blocks], dim=2)
+    v = torch.cat([blk.v[:, :, : blk.rows] for blk in blocks], dim=2)
+    want = F.flash_attn_bhsd(q, k, v, cfg)
+    torch.cuda.synchronize()
+    assert got.shape == want.shape and torch.isfinite(got.float()).all()
+    if lq * (hq // hkv) >= 512 and d == 128:
+        # the concatenated call of this size runs on the tcgen05 tiles, the paged one on the general kernel
+        assert_close(got.float().cpu().numpy(), want.float().cpu().numpy(), what="paged prefill chunk", out="bf16")
+    else:
+        assert torch.equal(got, want)
+
+
 def test_paged_varlen_equals_varlen_on_gathered_pages(P):
     torch.manual_seed(9)
     hq, hkv, d, page, nblk = 8, 2, 128, 16, 40
