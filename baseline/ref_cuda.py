@@ -6,12 +6,14 @@ The plan restated here: heads per workgroup `row_group` (candle-core/src/accel/a
 for packed workgroups, at most 64 splits), FP8 specialisation when both sides are FP8 rows
 (candle-core/src/accel/turbo.rs:537-552)."""
 import ctypes as C
+import os
 import subprocess
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 LIB = HERE / "_ref_cuda" / "libref_cuda.so"
-KERNELS = Path("/root/reference/candle-core/kernels")
+# the reference tree is expected beside the repository (or where REFERENCE points)
+KERNELS = Path(os.environ.get("REFERENCE", HERE.parent.parent / "reference")) / "candle-core" / "kernels"
 FA_MAX_SPLITS, SPLIT_WORKGROUPS_PER_CU, THREADS = 64, 64, 128
 MODE_FP8 = 5
 
