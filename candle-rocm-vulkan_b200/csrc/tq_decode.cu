@@ -140,10 +140,36 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl, bool paged = false
     pl.smem = fixed + DW * p.ns * stage + DW * NS_MAX * 16;  // + the tile descriptions of paged rows
     pl.pair = false;
     int wpb = DW;  // workers per block
+    // persistent blocks of independent workers: as many as fit on the device at once, at most one worker per tile of keys
+    const uint64_t lk = std::max<uint32_t>(a->lk, 1);
+    // paged rows: every block may end in a short tile
+    const uint64_t max_tiles = (uint64_t)a->b * pl.ny * ((lk + WK - 1) / WK + (paged ? a->n_pages : 0u));
+    const size_t ncols = (size_t)a->b * pl.ny;
+    auto blocks_for = [&](int per_sm, int workers_per_block) {
+        uint64_t nblocks = (uint64_t)sm_count_cached() * per_sm;
+        if (a->splits > 0) nblocks = std::min<uint64_t>(nblocks, ((uint64_t)a->b * pl.ny * a->splits + workers_per_block - 1) / workers_per_block);
+        return (uint32_t)std::max<uint64_t>(std::min(nblocks, (max_tiles + workers_per_block - 1) / workers_per_block), 1);
+    };
+    // Few segments per column (the workers outnumber the columns by less than eight to one): the last worker of a
+    // column merges it inside the decode grid. Many segments per column (a few long sequences), or more columns
+    // than there are arrival counters: a combine grid, whose blocks share a row's segments, follows.
+    auto merges_itself = [&](uint32_t blocks, int workers_per_block) {
+#ifdef B200_FORCE_COMBINE  // measurement builds only: always the separate combine grid
+        return false;
+#else
+        return (size_t)blocks * workers_per_block < 8 * ncols && ncols <= (size_t)CTR_COLS;
+#endif
+    };
     if (!paged && pair_formats(a->kq.mode, a->vq.mode)) {
-        // codebook formats: a worker is a pair of warps, two blocks of four pairs per SM; as many stages as fit
-        const size_t pq = p.qstage_bytes ? (size_t)2 * PW * PACK * a->d * 4 : 0;
-        const size_t pfixed = PAIR_FIXED + (size_t)PW * pair_meta_bytes(a->kq.mode, a->vq.mode, (int)a->d) + pq;
+        // codebook formats: a worker is a pair of warps, two blocks of four pairs per SM; as many stages as fit.
+        // Rotation staging: the keys' warps rotate the queries in it; the values' warps need rows of their own only
+        // when the grid merges its columns itself (the merging worker rotates the outputs back)
+        const bool pair_merges = merges_itself(blocks_for(2, PW), PW);
+        const int vslots = (a->vq.rotation == B200_ROT_HADAMARD && pair_merges) ? 1 : 0;
+        // up to head dim 128 the queries are rotated in registers; above, the keys' rows come first in the layout
+        const int kslots = (a->d > 128 && (a->kq.rotation == B200_ROT_HADAMARD || vslots)) ? 1 : 0;
+        const size_t pq = (size_t)(kslots + vslots) * PW * PACK * a->d * 4;
+        const size_t pfixed = pair_fixed_bytes(a->kq.mode, a->vq.mode) + (size_t)PW * pair_meta_bytes(a->kq.mode, a->vq.mode, (int)a->d) + pq;
         const size_t per_block = (228 * 1024) / 2 - 1024;
         int ns = 0;
         for (int n = 2; n <= PNS_MAX; ++n)
@@ -163,30 +189,16 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl, bool paged = false
         p.rows_cap = (uint32_t)std::min<uint64_t>(std::min(p.k_sh / p.k_ss, p.v_sh / p.v_ss), 0x7fffffffu);
 
     p.col_cost = B200_DECODE_COL_COST;
-    // persistent blocks of DW independent warps: as many as fit on the device at once, at most one
-    // warp per tile of keys
-    const uint64_t lk = std::max<uint32_t>(a->lk, 1);
-    // paged rows: every block may end in a short tile
-    const uint64_t max_tiles = (uint64_t)a->b * pl.ny * ((lk + WK - 1) / WK + (paged ? a->n_pages : 0u));
-    uint64_t nblocks = (uint64_t)sm_count_cached() * bps;
-    if (a->splits > 0) nblocks = std::min<uint64_t>(nblocks, ((uint64_t)a->b * pl.ny * a->splits + wpb - 1) / wpb);
-    pl.blocks = (uint32_t)std::max<uint64_t>(std::min(nblocks, (max_tiles + wpb - 1) / wpb), 1);
+    pl.blocks = blocks_for(bps, wpb);
     pl.workers = pl.blocks * (uint32_t)wpb;
 
     p.after_prev = (a->flags & B200_TQ_AFTER_PREV) ? 1u : 0u;
     p.prefetch = (p.after_prev && (a->flags & B200_TQ_INPUTS_FINAL)) ? 1u : 0u;
     p.fresh_rows = std::min<uint32_t>(a->fresh_rows, 0x7fffffffu);
-    const size_t ncols = (size_t)a->b * pl.ny;
     pl.nat = !paged && p.k_ss == (uint64_t)kl.row_words && p.v_ss == (uint64_t)vl.row_words && a->kq.mode == a->vq.mode && a->d == 128;
     p.pages = paged ? a->pages : nullptr;
     p.n_pages = paged ? a->n_pages : 0u;
-    // Few segments per column (the workers outnumber the columns by less than eight to one): the last worker of a
-    // column merges it inside the decode grid. Many segments per column (a few long sequences), or more columns
-    // than there are arrival counters: a combine grid, whose blocks share a row's segments, follows.
-    pl.in_kernel = (size_t)pl.workers < 8 * ncols && ncols <= (size_t)CTR_COLS;
-#ifdef B200_FORCE_COMBINE  // measurement builds only: always the separate combine grid
-    pl.in_kernel = false;
-#endif
+    pl.in_kernel = merges_itself(pl.blocks, wpb);
     const size_t prow = std::min<size_t>(PACK, p.rows_per_kv);
     const size_t slots = ((size_t)pl.workers + ncols) * prow;
     const size_t part_o = slots * a->d * 4;

@@ -197,9 +197,16 @@ __device__ __forceinline__ void tab16_dq8(const Tab16 &t, uint32_t x, uint32_t &
 #endif
 
 // f16x2 pair table lookups (codebook format) or packed cvt of the four bytes of x
-template <int M>
+// WIDE: the pair table holds one copy of every entry per lane ([256][32] words, `lut` already points at the lane's
+// column), so that the random look-ups of a warp never meet on a bank
+template <int M, bool WIDE = false>
 __device__ __forceinline__ void dq4(uint32_t x, uint32_t lut, uint32_t &h0, uint32_t &h1, uint32_t &h2, uint32_t &h3) {
-    if constexpr (M == B200_TURBO_MSE) {
+    if constexpr (M == B200_TURBO_MSE && WIDE) {
+        h0 = lds32(lut + ((x & 0xffu) << 7));
+        h1 = lds32(lut + ((x >> 1) & 0x7f80u));
+        h2 = lds32(lut + ((x >> 9) & 0x7f80u));
+        h3 = lds32(lut + ((x >> 17) & 0x7f80u));
+    } else if constexpr (M == B200_TURBO_MSE) {
         h0 = lds32(lut + ((x & 0xffu) << 2));
         h1 = lds32(lut + ((x >> 6) & 0x3fcu));
         h2 = lds32(lut + ((x >> 14) & 0x3fcu));
@@ -693,7 +700,73 @@ __device__ __forceinline__ void load_query(const DecodeParams &p, uint32_t b, ui
     const uint32_t G = p.group, R = p.rows_per_kv;
     const uint32_t r = pack * PACK + g;
     float qv[STEPS][4];
-    if (p.k.rot == B200_ROT_HADAMARD) {
+    if (HD <= 128 && p.k.rot == B200_ROT_HADAMARD) {
+        // Rotation in registers. The four lanes of quad row g hold row g between them, each the HD / 4 elements that its
+        // own fragments need: element e of the lane is dim d(e) = c HD/4 + e (the codebook, FP8 and NVFP4 orders) or
+        // 32 (e / 8) + 8 c + e % 8 (the MX order), so that slot j of k-step s is element 4 s + j either way. The
+        // butterflies of the index bits that e carries run inside the lane, those of the two bits that c carries
+        // across the quad; no shared memory, no pass per row.
+        constexpr int EPL = HD / 4;
+        float x[EPL];
+        const uint32_t i = p.lq == 1 ? 0u : r / G, h = hk * G + (p.lq == 1 ? r : r % G);
+        const size_t qoff = b * p.q_sb + h * p.q_sh + i * p.q_ss;
+        const bool q16 = p.q_dtype == B200_F16 || p.q_dtype == B200_BF16;
+        if (r >= R) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) x[e] = 0.0f;
+        } else if (q16 && ((reinterpret_cast<uintptr_t>(p.q) + 2 * qoff) & 15u) == 0 && (reinterpret_cast<uintptr_t>(p.k.signs) & 15u) == 0) {
+            // 16-bit rows on a 16-byte boundary: the lane's elements come as runs of eight (one 16-byte load each), all
+            // loads issued before the first conversion
+            const uint16_t *q16p = reinterpret_cast<const uint16_t *>(p.q) + qoff;
+            uint4 raw[EPL / 8];
+#pragma unroll
+            for (int t = 0; t < EPL / 8; ++t) raw[t] = __ldg(reinterpret_cast<const uint4 *>(q16p + (KMX ? 32 * t + 8 * c : c * EPL + 8 * t)));
+#pragma unroll
+            for (int t = 0; t < EPL / 8; ++t) {
+                const int d0 = KMX ? 32 * t + 8 * c : c * EPL + 8 * t;
+                const float4 s0 = __ldg(reinterpret_cast<const float4 *>(p.k.signs + d0)), s1 = __ldg(reinterpret_cast<const float4 *>(p.k.signs + d0 + 4));
+                const uint32_t w[4] = {raw[t].x, raw[t].y, raw[t].z, raw[t].w};
+                const float sg[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float lo = p.q_dtype == B200_BF16 ? u2f(w[j] << 16) : f16_bits_to_f((uint16_t)(w[j] & 0xffffu));
+                    const float hi = p.q_dtype == B200_BF16 ? u2f(w[j] & 0xffff0000u) : f16_bits_to_f((uint16_t)(w[j] >> 16));
+                    x[8 * t + 2 * j] = lo * sg[2 * j];
+                    x[8 * t + 2 * j + 1] = hi * sg[2 * j + 1];
+                }
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+                const int dd = KMX ? 32 * (e / 8) + 8 * c + (e % 8) : c * EPL + e;
+                x[e] = load_elem_rt(p.q, qoff + dd, p.q_dtype) * __ldg(p.k.signs + dd);
+            }
+        }
+#pragma unroll
+        for (int o = 1; o < EPL; o <<= 1) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+                if (!(e & o)) {
+                    const float a = x[e], d2 = x[e | o];
+                    x[e] = a + d2;
+                    x[e | o] = a - d2;
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 1; o < 4; o <<= 1) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+                const float y = __shfl_xor_sync(0xffffffffu, x[e], o);
+                x[e] = (lane & o) ? y - x[e] : x[e] + y;
+            }
+        }
+        const float hs = 1.0f / sqrtf((float)HD);
+#pragma unroll
+        for (int s2 = 0; s2 < STEPS; ++s2)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) qv[s2][j] = x[4 * s2 + j] * hs;
+    } else if (p.k.rot == B200_ROT_HADAMARD) {
         __syncwarp();
         for (int idx = lane; idx < PACK * HD; idx += 32) {
             const uint32_t rr = idx / HD, dd = idx % HD, r2 = pack * PACK + rr;
@@ -841,7 +914,7 @@ __device__ __forceinline__ void tile_meta(uint32_t kr, uint32_t vr, uint32_t met
 // Scores of keys g and g + 8 of the 16 keys at `ka` (the lane's first code byte of key g; rows krb bytes apart)
 // against the query rows 2c, 2c + 1: sr[2 k + e] = key g + 8 k, row 2c + e. `mrow`: the f32 key scales of key g
 // (per-key scalars of the tile), qb0 / qb1: the query fragments.
-template <int KM, int HD>
+template <int KM, int HD, bool WIDE = false>
 __device__ __forceinline__ void k_scores16(uint32_t ka, uint32_t krb, uint32_t mrow, const uint32_t (&qb0)[HD / 16], const uint32_t (&qb1)[HD / 16],
                                            uint32_t lut_k, uint32_t plane_k, int c, float (&sr)[4]) {
     constexpr int STEPS = HD / 16;
@@ -906,7 +979,7 @@ __device__ __forceinline__ void k_scores16(uint32_t ka, uint32_t krb, uint32_t m
                     sg8[i] = cvt_e4m3x2_f16x2(b8 | (b8 << 8));
                 }
             }
-            constexpr bool KPL = KM == B200_TURBO_MSE && (B200_TURBO_PRMT & 1);
+            constexpr bool KPL = KM == B200_TURBO_MSE && (B200_TURBO_PRMT & 1) && !WIDE;
             Tab16 kt;
             if constexpr (KPL) kt = load_tab16(plane_k);
 #pragma unroll
@@ -917,8 +990,8 @@ __device__ __forceinline__ void k_scores16(uint32_t ka, uint32_t krb, uint32_t m
                     tab16_dq8(kt, x0, a0, a1, a2, a3);
                     tab16_dq8(kt, x8, b0, b1, b2, b3);
                 } else {
-                    dq4<KM>(x0, lut_k, a0, a1, a2, a3);
-                    dq4<KM>(x8, lut_k, b0, b1, b2, b3);
+                    dq4<KM, WIDE>(x0, lut_k, a0, a1, a2, a3);
+                    dq4<KM, WIDE>(x8, lut_k, b0, b1, b2, b3);
                 }
                 if constexpr (KM == B200_NVFP4) {
                     const uint32_t s0 = sg[w / 2], s8 = sg8[w / 2];
@@ -949,7 +1022,7 @@ __device__ __forceinline__ void k_scores16(uint32_t ka, uint32_t krb, uint32_t m
 // O^T += V^T P^T for the 16 keys at `va` (the lane's first code byte of key 2c; rows vrb bytes apart): keys 2c, 2c+1 |
 // 2c+8, 2c+9, dims [g HD/8, (g+1) HD/8). `vsc_row`: the f16 block scales of the keys 2c, 2c + 1 (+ 16 bytes: 2c + 8,
 // 2c + 9), pb0 / pb1: the weights as B fragments.
-template <int VM, int HD>
+template <int VM, int HD, bool WIDE = false>
 __device__ __forceinline__ void v_accum16(uint32_t va, uint32_t vrb, uint32_t vsc_row, uint32_t pb0, uint32_t pb1, float (&oacc)[HD / 16][4],
                                           uint32_t lut_v, uint32_t plane_v, int g) {
     constexpr bool V4 = fmt_is4(VM);
@@ -965,17 +1038,17 @@ __device__ __forceinline__ void v_accum16(uint32_t va, uint32_t vrb, uint32_t vs
             const uint32_t tl1 = (xc & 0x0f0f0f0fu) | ((xd & 0x0f0f0f0fu) << 4);
             const uint32_t th1 = ((xc >> 4) & 0x0f0f0f0fu) | (xd & 0xf0f0f0f0u);
             uint32_t l0[4], h0[4], l1[4], h1[4];
-            if constexpr (VM == B200_TURBO_MSE && (B200_TURBO_PRMT & 2)) {
+            if constexpr (VM == B200_TURBO_MSE && (B200_TURBO_PRMT & 2) && !WIDE) {
                 const Tab16 vt = load_tab16(plane_v);
                 tab16_dq8(vt, tl0, l0[0], l0[1], l0[2], l0[3]);
                 tab16_dq8(vt, th0, h0[0], h0[1], h0[2], h0[3]);
                 tab16_dq8(vt, tl1, l1[0], l1[1], l1[2], l1[3]);
                 tab16_dq8(vt, th1, h1[0], h1[1], h1[2], h1[3]);
             } else {
-                dq4<VM>(tl0, lut_v, l0[0], l0[1], l0[2], l0[3]);
-                dq4<VM>(th0, lut_v, h0[0], h0[1], h0[2], h0[3]);
-                dq4<VM>(tl1, lut_v, l1[0], l1[1], l1[2], l1[3]);
-                dq4<VM>(th1, lut_v, h1[0], h1[1], h1[2], h1[3]);
+                dq4<VM, WIDE>(tl0, lut_v, l0[0], l0[1], l0[2], l0[3]);
+                dq4<VM, WIDE>(th0, lut_v, h0[0], h0[1], h0[2], h0[3]);
+                dq4<VM, WIDE>(tl1, lut_v, l1[0], l1[1], l1[2], l1[3]);
+                dq4<VM, WIDE>(th1, lut_v, h1[0], h1[1], h1[2], h1[3]);
             }
             if constexpr (NBV > 0) {
                 const int blk = (g * (HD / 8) + 8 * w) / (HD / NBV);
@@ -1764,6 +1837,13 @@ constexpr int PW = 4;        // pairs per block: warps 0..3 keys, 4..7 values
 constexpr int PQ = 2;        // slots of a pair's queue
 constexpr int PNS_MAX = 4;   // stages per pair
 constexpr int PAIR_FIXED = 256 + 2048 + 128;  // barriers, pair tables, byte-plane tables
+// Keys and values both in the 4-bit codebook format: one pair table with a copy of every entry per lane (32 KB) instead
+// of two of 1 KB, so that the look-ups of a warp never collide on a bank; both sides are decoded from it.
+#ifndef B200_WIDE_LUT
+#define B200_WIDE_LUT 1
+#endif
+__host__ __device__ constexpr bool pair_wide_lut(int km, int vm) { return B200_WIDE_LUT && km == B200_TURBO_MSE && vm == B200_TURBO_MSE; }
+__host__ __device__ constexpr int pair_fixed_bytes(int km, int vm) { return pair_wide_lut(km, vm) ? 256 + 32768 + 128 : PAIR_FIXED; }
 // one message: weights [lane][4] u32, rescale factors [lane][2] f32, their flag, f16 block scales of V [block][key]
 __host__ __device__ constexpr int pair_msg_bytes(int vm, int hd) { return 512 + 256 + 16 + vsc_blocks(vm, hd) * WK * 2; }
 // per pair: key scales and (sigma, log2 sigma) of a tile (the keys' warp's own), then the queue
@@ -1781,14 +1861,19 @@ __global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const Decode
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem);  // [PW][8]: stages full 0..3, messages full 4..5, messages free 6..7
     const int NS = (int)p.ns;
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t lut_k = sbase + 256, lut_v = lut_k + 1024, plane_k = lut_v + 1024, plane_v = plane_k + 32;
+    constexpr bool WIDE = pair_wide_lut(KM, VM);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+    // WIDE: one table of [256][32] words for keys and values (both sides decode with the same codebook), every lane
+    // reading its own column
+    const uint32_t lut_base = sbase + 256;
+    const uint32_t lut_k = WIDE ? lut_base + 4u * lane : lut_base, lut_v = WIDE ? lut_k : lut_k + 1024;
+    const uint32_t plane_k = lut_base + (WIDE ? 32768u : 2048u), plane_v = plane_k + 32;
     const uint32_t krb = NAT ? (uint32_t)nat_row_bytes(KM, HD) : (uint32_t)p.k_ss * 4u;
     const uint32_t vrb = NAT ? (uint32_t)nat_row_bytes(VM, HD) : (uint32_t)p.v_ss * 4u;
     const uint32_t k_stage_bytes = NAT ? stage_part_bytes((uint32_t)nat_row_bytes(KM, HD)) : p.k_stage_bytes;
     const uint32_t v_stage_bytes = NAT ? stage_part_bytes((uint32_t)nat_row_bytes(VM, HD)) : p.v_stage_bytes;
     const uint32_t stage_bytes = k_stage_bytes + v_stage_bytes;
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
     const int pair = warp & (PW - 1);
     const bool keys_side = warp < PW;
     const uint32_t ny = p.hkv * p.packs;
@@ -1798,7 +1883,12 @@ __global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const Decode
         for (int i = 0; i < PW * 8; ++i) mbar_init(&bars[i], 1);
         mbar_fence_init();
     }
-    load_codebooks<KM, VM>(p, lut_k, lut_v, plane_k, tid, PW * 64);
+    if constexpr (WIDE) {
+        // entry i (two codes) of the keys' codebook, once per lane; the values' codebook must be the same table
+        for (int idx = tid; idx < 256 * 32; idx += PW * 64) sts32(lut_base + 4u * idx, pack_f16x2(p.k.tab[(idx >> 5) & 15], p.k.tab[idx >> 9]));
+    } else {
+        load_codebooks<KM, VM>(p, lut_k, lut_v, plane_k, tid, PW * 64);
+    }
     __syncthreads();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -1811,13 +1901,16 @@ __global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const Decode
         return;
     }
 
-    const uint32_t pmeta_s = sbase + PAIR_FIXED + pair * PMETA;
+    constexpr int PFIX = pair_fixed_bytes(KM, VM);
+    const uint32_t pmeta_s = sbase + PFIX + pair * PMETA;
     const uint32_t meta_s = pmeta_s;                       // [WK][KMW] f32
     const uint32_t vmeta_s = meta_s + WK * KMW * 4;        // [WK] (sigma, log2 sigma)
     const uint32_t queue_s = vmeta_s + WK * 8;             // [PQ] messages
-    // rotation staging: the keys' warp rotates the queries in its rows, the values' warp the outputs in its own
-    float *qstage = reinterpret_cast<float *>(smem + PAIR_FIXED + PW * PMETA) + (size_t)(keys_side ? pair : PW + pair) * PACK * HD;
-    const uint32_t wstage_s = sbase + PAIR_FIXED + PW * PMETA + p.qstage_bytes + (uint32_t)pair * NS * stage_bytes;
+    // rotation staging: the keys' warp rotates the queries in its rows (head dims above 128 only: up to 128 the rotation
+    // runs in registers), the values' warp the outputs in its own (only when the grid merges its columns itself)
+    constexpr int KSLOTS = HD > 128 ? PW : 0;
+    float *qstage = reinterpret_cast<float *>(smem + PFIX + PW * PMETA) + (size_t)(keys_side ? pair : KSLOTS + pair) * PACK * HD;
+    const uint32_t wstage_s = sbase + PFIX + PW * PMETA + p.qstage_bytes + (uint32_t)pair * NS * stage_bytes;
     const uint32_t wbar_s = smem_u32(bars + pair * 8);     // stages
     const uint32_t qfull_s = wbar_s + 32, qfree_s = wbar_s + 48;
 
@@ -1867,8 +1960,8 @@ __global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const Decode
                 if (nkeys < WK) clear_stale_rows(st_s + koff, st_s + k_stage_bytes + voff, nkeys, krb, vrb, lane);
                 tile_meta<KM, VM, HD>(st_s + kr_off, st_s + vr_off, meta_s, vmeta_s, msg_s + 784, lane);
                 float sr[2][4];
-                k_scores16<KM, HD>(st_s + kt_off, krb, mrow_g, qb0, qb1, lut_k, plane_k, c, sr[0]);
-                k_scores16<KM, HD>(st_s + kt_off + 16 * krb, krb, mrow_g + 16 * KMW * 4, qb0, qb1, lut_k, plane_k, c, sr[1]);
+                k_scores16<KM, HD, WIDE>(st_s + kt_off, krb, mrow_g, qb0, qb1, lut_k, plane_k, c, sr[0]);
+                k_scores16<KM, HD, WIDE>(st_s + kt_off + 16 * krb, krb, mrow_g + 16 * KMW * 4, qb0, qb1, lut_k, plane_k, c, sr[1]);
                 uint32_t pb[4];
                 float al[2];
                 const bool moved = tile_softmax(p, seg, sm, key0, nkeys, vmeta_g, sr, qs, qs2, M, lsum, pb, al, lane);
@@ -1949,8 +2042,8 @@ __global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const Decode
                     uint32_t pb[4];
                     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(pb[0]), "=r"(pb[1]), "=r"(pb[2]), "=r"(pb[3]) : "r"(msg_s + lane * 16));
                     const uint32_t vsc_c = msg_s + 784 + 4 * c;
-                    v_accum16<VM, HD>(st_s + vt_off, vrb, vsc_c, pb[0], pb[1], oacc, lut_v, plane_v, g);
-                    v_accum16<VM, HD>(st_s + vt_off + 16 * vrb, vrb, vsc_c + 32, pb[2], pb[3], oacc, lut_v, plane_v, g);
+                    v_accum16<VM, HD, WIDE>(st_s + vt_off, vrb, vsc_c, pb[0], pb[1], oacc, lut_v, plane_v, g);
+                    v_accum16<VM, HD, WIDE>(st_s + vt_off + 16 * vrb, vrb, vsc_c + 32, pb[2], pb[3], oacc, lut_v, plane_v, g);
                     // the stage was read through the generic proxy (by both warps: the keys' warp before it sent the
                     // message): order that before the bulk copy of the next tile into it
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
