@@ -116,7 +116,9 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl, bool paged = false
     p.v_stage_bytes = (uint32_t)((WK * p.v_ss * 4 + 16 + 15) / 16 * 16);
     // shared memory: barriers and pair tables, per-warp key metadata, per-warp query staging (rotated
     // caches only), then the stage rings
-    p.qstage_bytes = (a->kq.rotation == B200_ROT_HADAMARD || a->vq.rotation == B200_ROT_HADAMARD) ? (uint32_t)(DW * PACK * a->d * 4) : 0u;
+    // staging rows for the rotation of the queries: head dims above 128 only (up to 128 it runs in registers, like the
+    // rotation back of the outputs at every head dim)
+    p.qstage_bytes = (a->kq.rotation == B200_ROT_HADAMARD && a->d > 128) ? (uint32_t)(DW * PACK * a->d * 4) : 0u;
     const size_t fixed = FIXED_SMEM + (size_t)DW * meta_bytes(a->kq.mode, a->vq.mode, (int)a->d) + p.qstage_bytes;
     const size_t stage = (size_t)p.k_stage_bytes + p.v_stage_bytes;
     // stages per warp and blocks per SM: as many bytes in flight as possible (a warp computes on one
@@ -161,14 +163,8 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl, bool paged = false
 #endif
     };
     if (!paged && pair_formats(a->kq.mode, a->vq.mode)) {
-        // codebook formats: a worker is a pair of warps, two blocks of four pairs per SM; as many stages as fit.
-        // Rotation staging: the keys' warps rotate the queries in it; the values' warps need rows of their own only
-        // when the grid merges its columns itself (the merging worker rotates the outputs back)
-        const bool pair_merges = merges_itself(blocks_for(2, PW), PW);
-        const int vslots = (a->vq.rotation == B200_ROT_HADAMARD && pair_merges) ? 1 : 0;
-        // up to head dim 128 the queries are rotated in registers; above, the keys' rows come first in the layout
-        const int kslots = (a->d > 128 && (a->kq.rotation == B200_ROT_HADAMARD || vslots)) ? 1 : 0;
-        const size_t pq = (size_t)(kslots + vslots) * PW * PACK * a->d * 4;
+        // codebook formats: a worker is a pair of warps, two blocks of four pairs per SM; as many stages as fit
+        const size_t pq = p.qstage_bytes ? (size_t)PW * PACK * a->d * 4 : 0;  // staging rows of the keys' warps
         const size_t pfixed = pair_fixed_bytes(a->kq.mode, a->vq.mode) + (size_t)PW * pair_meta_bytes(a->kq.mode, a->vq.mode, (int)a->d) + pq;
         const size_t per_block = (228 * 1024) / 2 - 1024;
         int ns = 0;

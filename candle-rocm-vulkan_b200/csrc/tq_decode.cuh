@@ -255,6 +255,37 @@ __device__ __forceinline__ void warp_hadamard(float *row, int n, const float *si
     }
 }
 
+// The rotation back (x = diag(s) H y / sqrt(n)) of an output row of n = 8 EL elements that eight lanes hold between them,
+// lane part p (0..7) the elements [p EL, (p + 1) EL): the butterflies of the index bits inside a lane run on its
+// registers, those of the three bits that the part carries across the lanes, where bit i of the part is bit `m[i]` of the
+// lane number. All 32 lanes call it (lanes without a row carry zeros). No shared memory, no pass per row.
+template <int EL>
+__device__ __forceinline__ void hadamard_back_parts(float (&x)[EL], int lane, int m0, int m1, int m2, const float *signs, int d0) {
+#pragma unroll
+    for (int o = 1; o < EL; o <<= 1) {
+#pragma unroll
+        for (int e = 0; e < EL; ++e) {
+            if (!(e & o)) {
+                const float a = x[e], c2 = x[e | o];
+                x[e] = a + c2;
+                x[e | o] = a - c2;
+            }
+        }
+    }
+    const int masks[3] = {m0, m1, m2};
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+#pragma unroll
+        for (int e = 0; e < EL; ++e) {
+            const float y = __shfl_xor_sync(0xffffffffu, x[e], masks[i]);
+            x[e] = (lane & masks[i]) ? y - x[e] : x[e] + y;
+        }
+    }
+    const float sc = 1.0f / sqrtf((float)(8 * EL));
+#pragma unroll
+    for (int e = 0; e < EL; ++e) x[e] *= sc * __ldg(signs + d0 + e);
+}
+
 // One column = the keys of one (batch entry, kv head, pack of query rows). Its visible keys
 // [lo, hi) are cut into tiles of WK keys; the tiles of all columns, in (batch, column, tile) order,
 // form the work list that the warps of the persistent blocks share: every warp is a worker of
@@ -485,10 +516,10 @@ __device__ __forceinline__ void finish_row(const DecodeParams &p, size_t obase, 
 // Eight lanes share a row (lane l: row l / 8 of a group of four rows, elements [(l % 8) HD / 8, +HD / 8)), so four
 // rows are merged side by side and the partial rows of two segments are in flight per lane: a group of rows costs two
 // or three trips to L2 instead of a few per row. `slot0`: the first segment's slot; consecutive segments are
-// consecutive slots. `stage`: PACK x HD floats of shared memory of this warp (touched only when the values are rotated).
+// consecutive slots. Rotated values are rotated back in registers.
 template <int HD>
 __device__ __forceinline__ void merge_column(const DecodeParams &p, uint32_t b, uint32_t y, size_t slot0, int ns, uint32_t prow, size_t g_base,
-                                             float *stage, int lane) {
+                                             int lane) {
     constexpr int LPR = 8, EL = HD / LPR;  // lanes per row, elements of a row per lane
     const uint32_t q = (uint32_t)lane % LPR;
     const size_t seg_stride = (size_t)prow * HD;
@@ -541,20 +572,8 @@ __device__ __forceinline__ void merge_column(const DecodeParams &p, uint32_t b, 
 #pragma unroll
             for (int k = 0; k < EL; ++k) acc[k] *= inv;
         }
-        if (p.v.rot == B200_ROT_HADAMARD) {
-            // rotate back through the warp's staging rows ([row][HD] floats of shared memory)
-            __syncwarp();
-            if (live)
-#pragma unroll
-                for (int k = 0; k < EL; ++k) stage[(rr - rbase) * HD + q * EL + k] = acc[k];
-            __syncwarp();
-            for (uint32_t r2 = 0; r2 < 32 / LPR; ++r2) warp_hadamard(stage + r2 * HD, HD, p.v.signs, false, lane);
-            __syncwarp();
-            if (live)
-#pragma unroll
-                for (int k = 0; k < EL; ++k) acc[k] = stage[(rr - rbase) * HD + q * EL + k];
-            __syncwarp();
-        }
+        // rotate back: the eight lanes of a row are consecutive (part = lane % 8)
+        if (p.v.rot == B200_ROT_HADAMARD) hadamard_back_parts<EL>(acc, lane, 1, 2, 4, p.v.signs, (int)(q * EL));
         if (live) {
             store_row_piece<EL>(p.out, obase + q * EL, acc, p.out_dtype);
             // the same row into every rank's gathered buffer: plain stores through the peer mappings
@@ -1274,11 +1293,10 @@ struct Worker {
     // segment's keys, M / lsum their running maxima (log2 domain) and normalizers, summed over the warp. A column
     // that this worker covers alone is stored straight from the registers; otherwise the normalized partial result
     // and its log-sum-exp go to the workspace and the worker counts itself on the column's arrival counter: the last
-    // to arrive merges the column. Without arrival counters the combine grid merges. `stage`: PACK x HD floats of
-    // shared memory of this warp (touched only when the values are rotated).
+    // to arrive merges the column. Without arrival counters the combine grid merges. Rotated values are rotated back in
+    // registers, wherever a row is finished.
     template <int HD>
-    __device__ __forceinline__ void finish_segment(const Segment &seg, const float (&oacc)[HD / 16][4], const float (&M)[2], const float (&lsum)[2],
-                                                   float *stage) {
+    __device__ __forceinline__ void finish_segment(const Segment &seg, const float (&oacc)[HD / 16][4], const float (&M)[2], const float (&lsum)[2]) {
         constexpr int STEPS = HD / 16;
         const int g = lane >> 2, c = lane & 3;
         const uint32_t R = p.rows_per_kv, pack = seg.y % p.packs;
@@ -1292,13 +1310,18 @@ struct Worker {
         const uint32_t first = seg.t0 == 0 ? wid : owner_of(x_col, total, nw);
         const uint32_t last = seg.t1 == (uint32_t)seg.col.tiles ? wid : owner_of(x_col + seg.col.tiles - 1, total, nw);
         const uint32_t nseg = last - first + 1;
-        if (p.ctr && nseg == 1 && p.v.rot != B200_ROT_HADAMARD) {
+        if (p.ctr && nseg == 1) {
             // the whole column in this worker's registers
             float o0[HD / 8], o1[HD / 8];
 #pragma unroll
             for (int mt = 0; mt < STEPS; ++mt) {
                 o0[2 * mt] = oacc[mt][0] * inv0; o0[2 * mt + 1] = oacc[mt][2] * inv0;
                 o1[2 * mt] = oacc[mt][1] * inv1; o1[2 * mt + 1] = oacc[mt][3] * inv1;
+            }
+            if (p.v.rot == B200_ROT_HADAMARD) {
+                // rows 2c and 2c + 1, each spread over the eight lanes g = 0..7 of this c (part = lane >> 2)
+                hadamard_back_parts<HD / 8>(o0, lane, 4, 8, 16, p.v.signs, g * (HD / 8));
+                hadamard_back_parts<HD / 8>(o1, lane, 4, 8, 16, p.v.signs, g * (HD / 8));
             }
             size_t obase, grow;
             if (w0 && row_addr(p, seg.b, seg.y, rr0, obase, grow)) {
@@ -1334,7 +1357,7 @@ struct Worker {
             if (merge) {
                 __threadfence();
                 const size_t slot0 = (size_t)first + colidx;
-                merge_column<HD>(p, seg.b, seg.y, slot0, (int)nseg, prow, g_base, stage, lane);
+                merge_column<HD>(p, seg.b, seg.y, slot0, (int)nseg, prow, g_base, lane);
                 column_done();
             }
         } else if (seg.t0 == 0 && lane == 0) {
@@ -1677,7 +1700,7 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
     const uint32_t meta_s = sbase + FIXED_SMEM + warp * META;    // [WK][KMW] f32
     const uint32_t vmeta_s = meta_s + WK * KMW * 4;              // [WK] (sigma, log2 sigma)
     const uint32_t vsc_s = vmeta_s + WK * 8;                     // [NBV][WK] f16
-    float *qstage = reinterpret_cast<float *>(smem + FIXED_SMEM + DW * META) + (size_t)warp * PACK * HD;  // only with a rotated cache
+    float *qstage = reinterpret_cast<float *>(smem + FIXED_SMEM + DW * META) + (size_t)warp * PACK * HD;  // only with rotated keys of a head dim above 128
     const uint32_t wstage_s = sbase + FIXED_SMEM + DW * META + p.qstage_bytes + (uint32_t)warp * NS * stage_bytes;
     const uint32_t wbar_s = smem_u32(bars + warp * NS_MAX);
     // paged rows: one description per stage, behind the rings of all warps
@@ -1807,7 +1830,7 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
             lsum[0] += __shfl_xor_sync(0xffffffffu, lsum[0], o);
             lsum[1] += __shfl_xor_sync(0xffffffffu, lsum[1], o);
         }
-        wk.finish_segment<HD>(seg, oacc, M, lsum, qstage);
+        wk.finish_segment<HD>(seg, oacc, M, lsum);
         more = next_segment(seg, p, ny, sh.x_end);
     }
     wk.zero_columns<HD>(true);
@@ -1906,10 +1929,9 @@ __global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const Decode
     const uint32_t meta_s = pmeta_s;                       // [WK][KMW] f32
     const uint32_t vmeta_s = meta_s + WK * KMW * 4;        // [WK] (sigma, log2 sigma)
     const uint32_t queue_s = vmeta_s + WK * 8;             // [PQ] messages
-    // rotation staging: the keys' warp rotates the queries in its rows (head dims above 128 only: up to 128 the rotation
-    // runs in registers), the values' warp the outputs in its own (only when the grid merges its columns itself)
-    constexpr int KSLOTS = HD > 128 ? PW : 0;
-    float *qstage = reinterpret_cast<float *>(smem + PFIX + PW * PMETA) + (size_t)(keys_side ? pair : KSLOTS + pair) * PACK * HD;
+    // rotation staging of the keys' warp for the queries: head dims above 128 only (up to 128 the rotation runs in
+    // registers, like the rotation back of the outputs at every head dim)
+    float *qstage = reinterpret_cast<float *>(smem + PFIX + PW * PMETA) + (size_t)pair * PACK * HD;
     const uint32_t wstage_s = sbase + PFIX + PW * PMETA + p.qstage_bytes + (uint32_t)pair * NS * stage_bytes;
     const uint32_t wbar_s = smem_u32(bars + pair * 8);     // stages
     const uint32_t qfull_s = wbar_s + 32, qfree_s = wbar_s + 48;
@@ -2073,7 +2095,7 @@ __global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const Decode
                 // void outputs (the status says so); the segment is still counted, so that no column waits for it
                 lsum[0] = lsum[1] = 0.0f;
             }
-            wk.finish_segment<HD>(seg, oacc, M, lsum, qstage);
+            wk.finish_segment<HD>(seg, oacc, M, lsum);
             more = next_segment(seg, p, ny, sh.x_end);
         }
         wk.zero_columns<HD>(true);
