@@ -611,13 +611,12 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
             dt = min(sample.run() for _ in range(2))
             cpu = {"value": sample.bytes / dt / 1e9, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
                    "sample": f"{sample.describe()}; best of two passes ({dt:.2f} s)"}
-        fused = world == 1 or peer_gather is not None
         # one decode grid per step when it merges its segments itself (few segments per column: c2, c5); else a combine
-        # grid follows (and with N > 1 a one-warp grid that publishes the gathered step)
+        # grid follows (with N > 1 its last block publishes the gathered step)
         ncols = b * hkv * max(1, (hq // hkv + 7) // 8)
         pair = w["mode"] == 0  # the codebook formats run on the kernel whose workers are pairs of warps
         in_kernel = ncols * 8 > 148 * (2 if pair else 3) * 4
-        launches_per_step = 1 if in_kernel else (2 + (1 if (fused and world > 1) else 0))
+        launches_per_step = 1 if in_kernel else 2
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,

@@ -257,18 +257,6 @@ static int dispatch_v(const DecodePlan &pl, dim3 grid, cudaStream_t stream) {
 #endif
 }
 
-// Launched behind the combine grid when the outputs are gathered by that grid: one warp publishes this rank's step
-// in every rank's flags and waits, with a bound, until all ranks have published it. The rows stored by the combine
-// grid (a completed grid) are visible system-wide before anything this kernel writes.
-__global__ void __launch_bounds__(32) tq_gather_publish_kernel(uint32_t *const *peer_flags, uint32_t world, uint32_t rank, uint32_t *step,
-                                                                uint32_t polls, int32_t *status, int32_t *lib_status) {
-    // launched with programmatic stream serialization: the combine grid has completed, and its stores are visible,
-    // once this returns
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t g_step = *reinterpret_cast<volatile uint32_t *>(step) + 1u;
-    gather_publish(peer_flags, world, rank, step, g_step, polls, status, lib_status, (int)threadIdx.x);
-}
-
 // Library-owned device words. g_col_ctr: arrival counters of the columns of the calls in flight, one slab per
 // call, taken in turn; every counter is back at zero when its call ends (the last arrival wraps it), so the slabs
 // need no clearing between calls. g_decode_wait_failed: set when a bounded wait of a decode kernel ran out.
@@ -623,13 +611,6 @@ static int run_plan(const B200TqAttnArgs *a, DecodePlan &pl, char *ws, size_t ws
         else if (a->d == 128) e = cudaLaunchKernelEx(&cfg, tq_combine_kernel<128>, p);
         else e = cudaLaunchKernelEx(&cfg, tq_combine_kernel<256>, p);
         if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "tq_combine: %s", cudaGetErrorString(e));
-        if (p.world) {
-            cfg.gridDim = dim3(1);
-            cfg.blockDim = dim3(32);
-            e = cudaLaunchKernelEx(&cfg, tq_gather_publish_kernel, p.peer_flags, p.world, p.rank, p.step, p.gather_polls, p.status, p.lib_status);
-            if (e != cudaSuccess) return set_error(B200_ERR_LAUNCH, "tq_gather_publish: %s", cudaGetErrorString(e));
-            return check_launch("tq_gather_publish");
-        }
         return check_launch("tq_combine");
     }
 }

@@ -615,6 +615,21 @@ __device__ __forceinline__ void gather_publish(uint32_t *const *peer_flags, uint
     }
 }
 
+// The end of a combine grid whose rows are gathered: every block makes its rows (local and peer stores) visible
+// system-wide and counts itself on the call's counter (which wraps to zero); the warp 0 of the last block to arrive
+// publishes the step to the other ranks and waits for theirs. Called by all threads of the block.
+__device__ __forceinline__ void combine_publish(const DecodeParams &p, uint32_t g_step) {
+    __shared__ uint32_t last_block;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) last_block = atomicInc(p.done_ctr, gridDim.x - 1u) == gridDim.x - 1u ? 1u : 0u;
+    __syncthreads();
+    if (last_block && threadIdx.x < 32) {
+        __threadfence_system();
+        gather_publish(p.peer_flags, p.world, p.rank, p.step, g_step, p.gather_polls, p.status, p.lib_status, (int)threadIdx.x);
+    }
+}
+
 // Online softmax of a tile in the log2 domain, on the score fragments sr[u][2 k + e] = key 16 u + g + 8 k, row 2c + e.
 // vm[k] = (sigma, log2 sigma) of key g + 8 k: the value scale is folded into the running maxima M (which track
 // s_j + log2 sigma_j), so the f16 weights w_j = exp2(s_j - M) sigma_j stay in range for value scales of any
@@ -2123,10 +2138,10 @@ __global__ void __launch_bounds__(128) tq_combine_kernel(const DecodeParams p) {
     // launched with programmatic stream serialization: wait here until the decode grid has finished
     // and its partial results are visible
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // a grid launched as this one's programmatic dependent (the gather's publish step) may be scheduled now; it waits
-    // for this grid's completion itself
+    // a grid launched as this one's programmatic dependent (the next attention) may be scheduled now; it waits for this
+    // grid's completion itself
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    // gathered outputs: this step's number (the same for all blocks: only the last block of the grid
+    // gathered outputs: this step's number (the same for all blocks: only the last block of the grid to finish
     // advances it, at its very end) selects one of the two slots of every rank's buffer
     const uint32_t g_step = p.world ? *reinterpret_cast<volatile uint32_t *>(p.step) + 1u : 0u;
     const size_t g_base = p.world ? ((size_t)(g_step & 1u) * p.world + p.rank) * rows * HD : 0;
@@ -2220,6 +2235,7 @@ __global__ void __launch_bounds__(128) tq_combine_kernel(const DecodeParams p) {
         }
         __syncthreads();
     }
+    if (p.world) combine_publish(p, g_step);
 }
 
 // The same merge for rows with few segments, as a grid of its own (the host picks it when the decode grid cannot
@@ -2240,11 +2256,11 @@ __global__ void __launch_bounds__(128) tq_combine_rows_kernel(const DecodeParams
     // launched with programmatic stream serialization: wait here until the decode grid has finished
     // and its partial results are visible
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // a grid launched as this one's programmatic dependent (the gather's publish step) may be scheduled now; it waits
-    // for this grid's completion itself
+    // a grid launched as this one's programmatic dependent (the next attention) may be scheduled now; it waits for this
+    // grid's completion itself
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    // gathered outputs: this step's number (the same for all blocks: only the publish step that follows this grid
-    // advances it) selects one of the two slots of every rank's buffer
+    // gathered outputs: this step's number (the same for all blocks: only the last block of the grid to finish
+    // advances it, at its very end) selects one of the two slots of every rank's buffer
     const uint32_t g_step = p.world ? *reinterpret_cast<volatile uint32_t *>(p.step) + 1u : 0u;
     const size_t g_base = p.world ? ((size_t)(g_step & 1u) * p.world + p.rank) * rows * HD : 0;
     for (size_t row = (size_t)blockIdx.x * CW + warp; row < rows; row += (size_t)gridDim.x * CW) {
@@ -2267,6 +2283,7 @@ __global__ void __launch_bounds__(128) tq_combine_rows_kernel(const DecodeParams
         }
         finish_row<HD>(p, obase, row, g_base, acc, rot[warp], lane, any);
     }
+    if (p.world) combine_publish(p, g_step);
 }
 
 }  // namespace b200

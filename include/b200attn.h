@@ -357,7 +357,7 @@ int b200_tq_attention_static(const B200TqAttnArgs *args, b200_stream_t stream);
  * (plain peer stores over NVLink, no multicast); the warp that finishes the call's last row publishes
  * this rank's step number in every rank's flag array and waits, with a bound, until every rank has
  * published the same step. One launch when the attention merges its splits itself, else the
- * combine grid stores the rows and a one-warp grid publishes.
+ * combine grid stores the rows and its last block to finish publishes.
  * When the call has completed in stream order, slot (step & 1) of this rank's gathered buffer
  * holds the rows of all ranks: [world][b * hq * lq][d] elements of out_dtype, rank r's rows in
  * block r, each in (batch, head, token) order. Two slots, because a rank may run one step ahead.
