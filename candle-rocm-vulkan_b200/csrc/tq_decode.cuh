@@ -202,15 +202,16 @@ __device__ __forceinline__ void tab16_dq8(const Tab16 &t, uint32_t x, uint32_t &
 template <int M, bool WIDE = false>
 __device__ __forceinline__ void dq4(uint32_t x, uint32_t lut, uint32_t &h0, uint32_t &h1, uint32_t &h2, uint32_t &h3) {
     if constexpr (M == B200_TURBO_MSE && WIDE) {
-        h0 = lds32(lut + ((x & 0xffu) << 7));
-        h1 = lds32(lut + ((x >> 1) & 0x7f80u));
-        h2 = lds32(lut + ((x >> 9) & 0x7f80u));
-        h3 = lds32(lut + ((x >> 17) & 0x7f80u));
+        // byte k of x by a byte permute, then one shift-and-add: three instructions per look-up with the load
+        h0 = lds32(lut + (prmt(x, 0u, 0x4440u) << 7));
+        h1 = lds32(lut + (prmt(x, 0u, 0x4441u) << 7));
+        h2 = lds32(lut + (prmt(x, 0u, 0x4442u) << 7));
+        h3 = lds32(lut + (prmt(x, 0u, 0x4443u) << 7));
     } else if constexpr (M == B200_TURBO_MSE) {
-        h0 = lds32(lut + ((x & 0xffu) << 2));
-        h1 = lds32(lut + ((x >> 6) & 0x3fcu));
-        h2 = lds32(lut + ((x >> 14) & 0x3fcu));
-        h3 = lds32(lut + ((x >> 22) & 0x3fcu));
+        h0 = lds32(lut + (prmt(x, 0u, 0x4440u) << 2));
+        h1 = lds32(lut + (prmt(x, 0u, 0x4441u) << 2));
+        h2 = lds32(lut + (prmt(x, 0u, 0x4442u) << 2));
+        h3 = lds32(lut + (prmt(x, 0u, 0x4443u) << 2));
     } else {
         cvt_e2m1x8_f16x2(x, h0, h1, h2, h3);
     }
@@ -582,6 +583,10 @@ __device__ __forceinline__ void merge_column(const DecodeParams &p, uint32_t b, 
     }
 }
 
+// Release / acquire fence at system scope (peer stores included): orders as much as the sequentially consistent
+// `__threadfence_system()` does for the publish protocol below (rows, then a counter, then a flag), and costs less.
+__device__ __forceinline__ void fence_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+
 // Gathered outputs: one warp publishes this rank's step in every rank's flags and waits, with a bound, until all
 // ranks have published it. The caller has made this rank's rows visible system-wide (fence) before. A wait that
 // runs out sets the call's status word to 2 and the library-wide flag; the step is advanced all the same, so the
@@ -589,10 +594,8 @@ __device__ __forceinline__ void merge_column(const DecodeParams &p, uint32_t b, 
 __device__ __forceinline__ void gather_publish(uint32_t *const *peer_flags, uint32_t world, uint32_t rank, uint32_t *step, uint32_t g_step,
                                                uint32_t polls, int32_t *status, int32_t *lib_status, int lane) {
     bool ok = true;
-    for (uint32_t pr = lane; pr < world; pr += 32) {
-        __threadfence_system();
+    for (uint32_t pr = lane; pr < world; pr += 32)
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flags[pr] + rank), "r"(g_step) : "memory");
-    }
     const uint32_t limit = polls ? polls : (1u << 21);
     for (uint32_t pr = lane; pr < world; pr += 32) {
         const uint32_t *flag = peer_flags[rank] + pr;
@@ -620,12 +623,12 @@ __device__ __forceinline__ void gather_publish(uint32_t *const *peer_flags, uint
 // publishes the step to the other ranks and waits for theirs. Called by all threads of the block.
 __device__ __forceinline__ void combine_publish(const DecodeParams &p, uint32_t g_step) {
     __shared__ uint32_t last_block;
-    __threadfence_system();
+    fence_sys();
     __syncthreads();
     if (threadIdx.x == 0) last_block = atomicInc(p.done_ctr, gridDim.x - 1u) == gridDim.x - 1u ? 1u : 0u;
     __syncthreads();
     if (last_block && threadIdx.x < 32) {
-        __threadfence_system();
+        fence_sys();
         gather_publish(p.peer_flags, p.world, p.rank, p.step, g_step, p.gather_polls, p.status, p.lib_status, (int)threadIdx.x);
     }
 }
@@ -1271,13 +1274,13 @@ struct Worker {
     // call's last column publishes the step to the other ranks
     __device__ __forceinline__ void column_done() {
         if (!p.world) return;
-        __threadfence_system();
+        fence_sys();
         __syncwarp();
         uint32_t last = 0;
         if (lane == 0) last = atomicInc(p.done_ctr, ncols - 1u) == ncols - 1u ? 1u : 0u;
         last = __shfl_sync(0xffffffffu, last, 0);
         if (last) {
-            __threadfence_system();
+            fence_sys();
             gather_publish(p.peer_flags, p.world, p.rank, p.step, g_step, p.gather_polls, p.status, p.lib_status, lane);
         }
     }
