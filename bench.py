@@ -640,7 +640,7 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
                                        else (f"batch shard x{world}, {gather_note}" if world > 1 else "single GPU"))},
             "tokens_per_s": (w_full["b"] if strong else world * b) / (ms * 1e-3),
             "pct_of_8000_gbs_nominal": 100.0 * value / (8000.0 * world),
-            "gpu_launches": steps * launches_per_step,
+            "gpu_launches": steps * launches_per_step * world,  # of all ranks, like `value`
             "roofline": {"bound": "hbm", "kernel": "tq_decode_pair_kernel" if pair else "tq_decode_kernel",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_kind, "traffic": None, "traffic_unit": "bytes per launch", "traffic_source": None},
@@ -677,14 +677,29 @@ TRAFFIC = {"c2": (366_696_192, "ncu capture of this workload, profiles/tq_decode
 
 def prefill_leg(env, steps, warmup):
     """Workload c3: causal prefill of B=4 x S=4096 (Hq 32, Hkv 8, D 128, bf16) with the new K / V written into an
-    NVFP4 cache in the same call. Metric: attention TFLOP/s (4 B Hq S^2 D / 2 flop per step); single GPU."""
-    torch, P, dev = env.torch, env.P, env.dev
+    NVFP4 cache in the same call. Metric: attention TFLOP/s (4 B Hq S^2 D / 2 flop per step). Several ranks split the
+    batch entries (2 or 4 ranks) or the kv heads with their query heads (8 ranks): strong scaling, no exchange (the
+    outputs and the cache rows stay with the rank that owns the sequence or the head). Returns the line on rank 0."""
+    torch, P, dev, world = env.torch, env.P, env.dev, env.world
     F = P.flash_attn
     b, s, hq, hkv, d = 4, 4096, 32, 8, 128
+    b_all, hq_all = b, hq
+    shard = "single GPU"
+    if world > 1:
+        if b % world == 0:
+            b //= world
+            shard = f"batch entries split over {world} ranks ({b} per rank), no exchange"
+        elif hkv % world == 0:
+            hq, hkv = hq // world, hkv // world
+            shard = f"kv heads split over {world} ranks ({hkv} per rank with their {hq} query heads), no exchange"
+        else:
+            return None
     nv = P.QuantFormat.parse("nvfp4")
     kq, vq = P.TurboQuantizer(nv, d, "none", 42, dev), P.TurboQuantizer(nv, d, "none", 44, dev)
     cfg = P.FlashAttnConfig(d ** -0.5).causal()
-    nbuf = 3  # q/k/v/out sets cycled: 3 x 335 MB, so that no step finds its inputs in L2
+    # q / k / v sets cycled (335 MB each on one GPU, a share of it on several): at least 400 MB pass before a set comes
+    # round again, so that no step finds its inputs in L2
+    nbuf = max(3, -(-400 * world // 335))
     sets = []
     for i in range(nbuf):
         g = torch.Generator(device=dev).manual_seed(77 + i)
@@ -700,15 +715,16 @@ def prefill_leg(env, steps, warmup):
 
     for i in range(warmup):
         step(i)
-    torch.cuda.synchronize()
+    env.barrier()
     sampler = ClockSampler(env.local_rank)
-    sampler.start()
+    if env.rank == 0:
+        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(steps):
         step(i)
     e1.record()
-    torch.cuda.synchronize()
+    env.barrier()
     ms = e0.elapsed_time(e1) / steps
     # attention alone (the dominant kernel), for the roofline
     a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -719,6 +735,7 @@ def prefill_leg(env, steps, warmup):
     a1.record()
     torch.cuda.synchronize()
     attn_ms = a0.elapsed_time(a1) / steps
+    env.barrier()
     # end to end: host q / k / v in, host output back
     hq_, hk_, hv_ = [t.cpu().pin_memory() for t in sets[0]]
     out_host = torch.empty((b, s, hq, d), dtype=torch.bfloat16).pin_memory()
@@ -731,44 +748,51 @@ def prefill_leg(env, steps, warmup):
         out_host.copy_(F.prefill_append(dq, dk, dv, cfg, kc, vc, kq, vq, 0), non_blocking=True)
 
     e2e_step()
-    torch.cuda.synchronize()
+    env.barrier()
     n_e2e = max(2, min(steps, 5))
     e0.record()
     for _ in range(n_e2e):
         e2e_step()
     e1.record()
-    torch.cuda.synchronize()
+    env.barrier()
     e2e_ms = e0.elapsed_time(e1) / n_e2e
+    # the slowest rank's times; every rank runs the same number of untimed steps for the clock sampler
+    (ms, attn_ms, e2e_ms), _ = aggregate_over_ranks((ms, attn_ms, e2e_ms), 0, world, dev)
     for i in range(clock_sample_steps(ms, seconds=0.4, cap=400)):
         step(i)
     torch.cuda.synchronize()
-    clocks = sampler.stop()
+    clocks = sampler.stop() if env.rank == 0 else None
     if P._abi.lib().b200_device_wait_status() != 0:
         raise SystemExit("bench: a bounded device wait ran out; the numbers are void")
-    flops = 4.0 * b * hq * s * s * d / 2
+    if env.rank != 0:
+        sets.clear()
+        torch.cuda.empty_cache()
+        return None
+    flops = 4.0 * b_all * hq_all * s * s * d / 2  # the whole job
     pk = peaks()
     peak, kind = (pk["bf16_tflops"], "measured cuBLAS bf16 burst (MEASURED_PEAKS.json)") if "bf16_tflops" in pk else (1590.0, "fallback")
-    cpu, _ = cpu_prefill_sample()
+    cpu = cpu_prefill_sample()[0] if world == 1 else None
     achieved = flops / (attn_ms * 1e-3) / 1e12
-    line = {"metric": "prefill_attention_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps,
-            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+    peak *= world
+    line = {"metric": "prefill_attention_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
             "dtype": "bf16 mma / f32 softmax", "data": "synthetic",
             "config": {"workload": "c3: causal prefill B=4 S=4096 Hq=32 Hkv=8 D=128 bf16 + NVFP4 cache append",
-                       "l2": f"{nbuf} input sets of 335 MB cycled (L2 is 126 MB)", "parallelism": "single GPU"},
-            "tokens_per_s": b * s / (ms * 1e-3),
+                       "l2": f"{nbuf} input sets of {335 // world} MB cycled (L2 is 126 MB)", "parallelism": shard},
+            "tokens_per_s": b_all * s / (ms * 1e-3),
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": int(sum(t.numel() for t in sets[0])) * 2, "d2h_bytes_per_step": int(out_host.numel()) * 2},
-            "gpu_launches": steps * 2,  # the attention kernel and the quantize-on-append kernel (K and V in one grid)
+                    "h2d_bytes_per_step": int(sum(t.numel() for t in sets[0])) * 2 * world, "d2h_bytes_per_step": int(out_host.numel()) * 2 * world},
+            "gpu_launches": steps * 2 * world,  # the attention kernel and the quantize-on-append kernel (K and V in one grid)
             "roofline": {"bound": "tensor", "kernel": "fa_prefill_sm100_kernel2 (attention alone)", "achieved": achieved,
-                         "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": kind,
-                         "frac_of_sustained": achieved / pk["bf16_tflops_sustained"] if "bf16_tflops_sustained" in pk else None,
+                         "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": kind + (f" x {world} GPUs" if world > 1 else ""),
+                         "frac_of_sustained": achieved / (pk["bf16_tflops_sustained"] * world) if "bf16_tflops_sustained" in pk else None,
                          # dram read + write of one launch at B = 1 (50.4 + 3.0 MB, part of q / k / v still in L2 from the
                          # call before), times the 4 batch entries of c3, whose blocks do not share data
-                         "traffic": 4 * 53_400_000, "traffic_unit": "bytes per launch",
+                         "traffic": 4 * 53_400_000 if world == 1 else None, "traffic_unit": "bytes per launch",
                          "traffic_source": "ncu capture at B=1 scaled by 4, profiles/fa_prefill_sm100_kernel2_b1_s4096.md"},
             "cpu_baseline": cpu, "clocks": clocks}
     from baseline import ref_cuda as R
-    if R.available():
+    if R.available() and world == 1:
         # the reference's tile kernel of the tier a B200 selects, on the same tensors (attention alone; its append is a
         # second call in the reference and is not timed here)
         q, k, v = sets[0]
@@ -828,7 +852,7 @@ def run_ours(args, rank, world, local_rank):
     head = args.workload
     lines = []
     if head == "c3":
-        headline = prefill_leg(env, args.steps, args.warmup) if rank == 0 else None
+        headline = prefill_leg(env, args.steps, args.warmup)
     else:
         wl = dict(WORKLOADS[head])
         if args.batch > 0:
@@ -838,14 +862,14 @@ def run_ours(args, rank, world, local_rank):
         if headline is not None and head in TRAFFIC and world == 1:
             headline["roofline"]["traffic"], headline["roofline"]["traffic_source"] = TRAFFIC[head]
     if not args.only:
-        # the other configurations, shorter: c5 and c4 as strong scaling over the ranks, c1 and c3 on one GPU
+        # the other configurations, shorter: c5, c4 and c3 as strong scaling over the ranks, c1 on one GPU
         short = max(8, min(args.steps, 48))
         for name in ("c5", "c4", "c1"):
             if name == head or (name == "c1" and world > 1):
                 continue
             lines.append(compact(decode_leg(env, name, dict(WORKLOADS[name]), short, max(3, min(args.warmup, 6)), with_e2e=(name != "c5"),
                                             with_cpu=(world == 1), layers=32 if name == "c5" else 1)))
-        if head != "c3" and world == 1:
+        if head != "c3":
             lines.append(compact(prefill_leg(env, max(3, min(args.steps, 10)), 3)))
     if rank == 0:
         for l in lines:
