@@ -192,6 +192,13 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl, bool paged = false
     p.prefetch = (p.after_prev && (a->flags & B200_TQ_INPUTS_FINAL)) ? 1u : 0u;
     p.fresh_rows = std::min<uint32_t>(a->fresh_rows, 0x7fffffffu);
     pl.nat = !paged && p.k_ss == (uint64_t)kl.row_words && p.v_ss == (uint64_t)vl.row_words && a->kq.mode == a->vq.mode && a->d == 128;
+    if (pl.nat) {
+        // the native-row kernels read a lane's codes with 8- or 16-byte loads where the row length allows: every
+        // (batch entry, kv head) slab must then start at such a multiple (caches allocated as whole rows do)
+        const uint64_t al = (uint64_t)nat_row_align((int)a->kq.mode, 128);
+        auto aligned = [&](const void *ptr, uint64_t sb, uint64_t sh) { return reinterpret_cast<uintptr_t>(ptr) % al == 0 && (sb * 4) % al == 0 && (sh * 4) % al == 0; };
+        pl.nat = aligned(a->k_rows, p.k_sb, p.k_sh) && aligned(a->v_rows, p.v_sb, p.v_sh);
+    }
     p.pages = paged ? a->pages : nullptr;
     p.n_pages = paged ? a->n_pages : 0u;
     pl.in_kernel = merges_itself(pl.blocks, wpb);

@@ -137,6 +137,23 @@ __device__ __forceinline__ float4 lds128f(uint32_t a) {
     asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
     return v;
 }
+// N consecutive words of shared memory at `a`, which is known to be a multiple of AL bytes: the widest loads that
+// alignment and count allow. Rows of 72 or 80 bytes (an even number of words) put the 4-byte loads of a warp, eight
+// rows x four chunks, four to a bank; a lane's whole chunk in one or two loads halves the trips through the banks.
+template <int N, int AL>
+__device__ __forceinline__ void lds_words(uint32_t a, uint32_t (&x)[N]) {
+    if constexpr (AL >= 16 && N % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < N / 4; ++i)
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(x[4 * i]), "=r"(x[4 * i + 1]), "=r"(x[4 * i + 2]), "=r"(x[4 * i + 3]) : "r"(a + 16 * i));
+    } else if constexpr (AL >= 8 && N % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < N / 2; ++i) asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(x[2 * i]), "=r"(x[2 * i + 1]) : "r"(a + 8 * i));
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(x[i]) : "r"(a + 4 * i));
+    }
+}
 __device__ __forceinline__ void sts32(uint32_t a, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
 __device__ __forceinline__ void sts16(uint32_t a, uint32_t v) {
     asm volatile("{\n .reg .b16 t;\n cvt.u16.u32 t, %1;\n st.shared.u16 [%0], t;\n}" ::"r"(a), "r"(v) : "memory");
@@ -385,6 +402,9 @@ __host__ __device__ constexpr int aux_words_of(int m, int hd) {
 }
 __host__ __device__ constexpr int rsc_byte_off(int m, int hd) { return code_bytes(m, hd) + 4 * aux_words_of(m, hd); }
 __host__ __device__ constexpr int nat_row_bytes(int m, int hd) { return rsc_byte_off(m, hd) + 8; }
+// what every native row's address is a multiple of when the first one's is a multiple of 16 (4, 8 or 16 bytes)
+__host__ __device__ constexpr int nat_row_align(int m, int hd) { return nat_row_bytes(m, hd) % 16 == 0 ? 16 : (nat_row_bytes(m, hd) % 8 == 0 ? 8 : 4); }
+__host__ __device__ constexpr int min_i(int a, int b) { return a < b ? a : b; }
 // bytes of a stage's K (or V) part: WK rows plus the slack of a copy that starts below its first row
 __host__ __device__ constexpr uint32_t stage_part_bytes(uint32_t row_bytes) { return (WK * row_bytes + 16u + 15u) / 16u * 16u; }
 
@@ -951,7 +971,8 @@ __device__ __forceinline__ void tile_meta(uint32_t kr, uint32_t vr, uint32_t met
 // Scores of keys g and g + 8 of the 16 keys at `ka` (the lane's first code byte of key g; rows krb bytes apart)
 // against the query rows 2c, 2c + 1: sr[2 k + e] = key g + 8 k, row 2c + e. `mrow`: the f32 key scales of key g
 // (per-key scalars of the tile), qb0 / qb1: the query fragments.
-template <int KM, int HD, bool WIDE = false>
+// AL: what the rows' addresses in shared memory are known to be multiples of (bytes).
+template <int KM, int HD, bool WIDE = false, int AL = 4>
 __device__ __forceinline__ void k_scores16(uint32_t ka, uint32_t krb, uint32_t mrow, const uint32_t (&qb0)[HD / 16], const uint32_t (&qb1)[HD / 16],
                                            uint32_t lut_k, uint32_t plane_k, int c, float (&sr)[4]) {
     constexpr int STEPS = HD / 16;
@@ -1019,9 +1040,13 @@ __device__ __forceinline__ void k_scores16(uint32_t ka, uint32_t krb, uint32_t m
             constexpr bool KPL = KM == B200_TURBO_MSE && (B200_TURBO_PRMT & 1) && !WIDE;
             Tab16 kt;
             if constexpr (KPL) kt = load_tab16(plane_k);
+            // the lane's chunk of a row: HD / 8 bytes at a multiple of HD / 8
+            uint32_t xs0[WPL], xs8[WPL];
+            lds_words<WPL, min_i(AL, HD / 8)>(ka, xs0);
+            lds_words<WPL, min_i(AL, HD / 8)>(ka8, xs8);
 #pragma unroll
             for (int w = 0; w < WPL; ++w) {
-                const uint32_t x0 = lds32(ka + 4 * w), x8 = lds32(ka8 + 4 * w);
+                const uint32_t x0 = xs0[w], x8 = xs8[w];
                 uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
                 if constexpr (KPL) {
                     tab16_dq8(kt, x0, a0, a1, a2, a3);
@@ -1040,9 +1065,12 @@ __device__ __forceinline__ void k_scores16(uint32_t ka, uint32_t krb, uint32_t m
                 mma_f16_16816(sr, a2, b2, a3, b3, qb0[2 * w + 1], qb1[2 * w + 1]);
             }
         } else {
+            uint32_t xs0[STEPS], xs8[STEPS];  // the lane's chunk of a row: HD / 4 bytes at a multiple of HD / 4
+            lds_words<STEPS, min_i(AL, HD / 4)>(ka, xs0);
+            lds_words<STEPS, min_i(AL, HD / 4)>(ka8, xs8);
 #pragma unroll
             for (int s = 0; s < STEPS; ++s) {
-                const uint32_t x0 = lds32(ka + 4 * s), x8 = lds32(ka8 + 4 * s);
+                const uint32_t x0 = xs0[s], x8 = xs8[s];
                 if (s == 0)
                     mma_f16_16816_z(sr, cvt_e4m3x2_f16x2(x0), cvt_e4m3x2_f16x2(x8), cvt_e4m3x2_hi_f16x2(x0),
                                     cvt_e4m3x2_hi_f16x2(x8), qb0[0], qb1[0]);
@@ -1059,15 +1087,21 @@ __device__ __forceinline__ void k_scores16(uint32_t ka, uint32_t krb, uint32_t m
 // O^T += V^T P^T for the 16 keys at `va` (the lane's first code byte of key 2c; rows vrb bytes apart): keys 2c, 2c+1 |
 // 2c+8, 2c+9, dims [g HD/8, (g+1) HD/8). `vsc_row`: the f16 block scales of the keys 2c, 2c + 1 (+ 16 bytes: 2c + 8,
 // 2c + 9), pb0 / pb1: the weights as B fragments.
-template <int VM, int HD, bool WIDE = false>
+template <int VM, int HD, bool WIDE = false, int AL = 4>
 __device__ __forceinline__ void v_accum16(uint32_t va, uint32_t vrb, uint32_t vsc_row, uint32_t pb0, uint32_t pb1, float (&oacc)[HD / 16][4],
                                           uint32_t lut_v, uint32_t plane_v, int g) {
     constexpr bool V4 = fmt_is4(VM);
     constexpr int NBV = vsc_blocks(VM, HD);
+    // the lane's chunk of each of its four rows: NW words at a multiple of 4 NW bytes
+    constexpr int NW = V4 ? (HD / 64 > 0 ? HD / 64 : 1) : HD / 32;
+    uint32_t xas[NW], xbs[NW], xcs[NW], xds[NW];
+    lds_words<NW, min_i(AL, 4 * NW)>(va, xas);
+    lds_words<NW, min_i(AL, 4 * NW)>(va + vrb, xbs);
+    lds_words<NW, min_i(AL, 4 * NW)>(va + 8 * vrb, xcs);
+    lds_words<NW, min_i(AL, 4 * NW)>(va + 9 * vrb, xds);
 #pragma unroll
-    for (int w = 0; w < (V4 ? (HD / 64 > 0 ? HD / 64 : 1) : HD / 32); ++w) {
-        const uint32_t xa = lds32(va + 4 * w), xb = lds32(va + vrb + 4 * w);
-        const uint32_t xc = lds32(va + 8 * vrb + 4 * w), xd = lds32(va + 9 * vrb + 4 * w);
+    for (int w = 0; w < NW; ++w) {
+        const uint32_t xa = xas[w], xb = xbs[w], xc = xcs[w], xd = xds[w];
         if constexpr (V4) {
             // nibbles of two keys side by side: byte i = (a[2i], b[2i]) and (a[2i+1], b[2i+1])
             const uint32_t tl0 = (xa & 0x0f0f0f0fu) | ((xb & 0x0f0f0f0fu) << 4);
@@ -1685,6 +1719,8 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
     // row strides and stage sizes: compile-time when the rows are packed back to back (NAT)
     const uint32_t krb = NAT ? (uint32_t)nat_row_bytes(KM, HD) : (uint32_t)p.k_ss * 4u;
     const uint32_t vrb = NAT ? (uint32_t)nat_row_bytes(VM, HD) : (uint32_t)p.v_ss * 4u;
+    // native rows start at multiples of this many bytes (the host checks the base addresses and the slab strides)
+    constexpr int KAL = NAT ? nat_row_align(KM, HD) : 4, VAL = NAT ? nat_row_align(VM, HD) : 4;
     const uint32_t k_stage_bytes = NAT ? stage_part_bytes((uint32_t)nat_row_bytes(KM, HD)) : p.k_stage_bytes;
     const uint32_t v_stage_bytes = NAT ? stage_part_bytes((uint32_t)nat_row_bytes(VM, HD)) : p.v_stage_bytes;
     const uint32_t stage_bytes = k_stage_bytes + v_stage_bytes;
@@ -1809,8 +1845,8 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                 tile_meta<KM, VM, HD>(st_s + kr_off, st_s + vr_off, meta_s, vmeta_s, vsc_s, lane);
                 // ---- scores of the 32 keys: sr[u][2 k + e] = key 16 u + g + 8 k, row 2c + e
                 float sr[2][4];
-                k_scores16<KM, HD>(st_s + kt_off, krb, mrow_g, qb0, qb1, lut_k, plane_k, c, sr[0]);
-                k_scores16<KM, HD>(st_s + kt_off + 16 * krb, krb, mrow_g + 16 * KMW * 4, qb0, qb1, lut_k, plane_k, c, sr[1]);
+                k_scores16<KM, HD, false, KAL>(st_s + kt_off, krb, mrow_g, qb0, qb1, lut_k, plane_k, c, sr[0]);
+                k_scores16<KM, HD, false, KAL>(st_s + kt_off + 16 * krb, krb, mrow_g + 16 * KMW * 4, qb0, qb1, lut_k, plane_k, c, sr[1]);
                 // ---- online softmax
                 uint32_t pb[4];
                 float al[2];
@@ -1824,8 +1860,8 @@ __global__ void __launch_bounds__(DW * 32, B200_DECODE_MIN_BLOCKS) tq_decode_ker
                     }
                 }
                 // ---- O^T += V^T P^T
-                v_accum16<VM, HD>(st_s + vt_off, vrb, vsc_c, pb[0], pb[1], oacc, lut_v, plane_v, g);
-                v_accum16<VM, HD>(st_s + vt_off + 16 * vrb, vrb, vsc_c + 32, pb[2], pb[3], oacc, lut_v, plane_v, g);
+                v_accum16<VM, HD, false, VAL>(st_s + vt_off, vrb, vsc_c, pb[0], pb[1], oacc, lut_v, plane_v, g);
+                v_accum16<VM, HD, false, VAL>(st_s + vt_off + 16 * vrb, vrb, vsc_c + 32, pb[2], pb[3], oacc, lut_v, plane_v, g);
                 // the stage was read (and possibly patched) through the generic proxy: order that before the
                 // bulk copy of the next tile into it
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1911,6 +1947,8 @@ __global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const Decode
     const uint32_t plane_k = lut_base + (WIDE ? 32768u : 2048u), plane_v = plane_k + 32;
     const uint32_t krb = NAT ? (uint32_t)nat_row_bytes(KM, HD) : (uint32_t)p.k_ss * 4u;
     const uint32_t vrb = NAT ? (uint32_t)nat_row_bytes(VM, HD) : (uint32_t)p.v_ss * 4u;
+    // native rows start at multiples of this many bytes (the host checks the base addresses and the slab strides)
+    constexpr int KAL = NAT ? nat_row_align(KM, HD) : 4, VAL = NAT ? nat_row_align(VM, HD) : 4;
     const uint32_t k_stage_bytes = NAT ? stage_part_bytes((uint32_t)nat_row_bytes(KM, HD)) : p.k_stage_bytes;
     const uint32_t v_stage_bytes = NAT ? stage_part_bytes((uint32_t)nat_row_bytes(VM, HD)) : p.v_stage_bytes;
     const uint32_t stage_bytes = k_stage_bytes + v_stage_bytes;
@@ -2000,8 +2038,8 @@ __global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const Decode
                 if (nkeys < WK) clear_stale_rows(st_s + koff, st_s + k_stage_bytes + voff, nkeys, krb, vrb, lane);
                 tile_meta<KM, VM, HD>(st_s + kr_off, st_s + vr_off, meta_s, vmeta_s, msg_s + 784, lane);
                 float sr[2][4];
-                k_scores16<KM, HD, WIDE>(st_s + kt_off, krb, mrow_g, qb0, qb1, lut_k, plane_k, c, sr[0]);
-                k_scores16<KM, HD, WIDE>(st_s + kt_off + 16 * krb, krb, mrow_g + 16 * KMW * 4, qb0, qb1, lut_k, plane_k, c, sr[1]);
+                k_scores16<KM, HD, WIDE, KAL>(st_s + kt_off, krb, mrow_g, qb0, qb1, lut_k, plane_k, c, sr[0]);
+                k_scores16<KM, HD, WIDE, KAL>(st_s + kt_off + 16 * krb, krb, mrow_g + 16 * KMW * 4, qb0, qb1, lut_k, plane_k, c, sr[1]);
                 uint32_t pb[4];
                 float al[2];
                 const bool moved = tile_softmax(p, seg, sm, key0, nkeys, vmeta_g, sr, qs, qs2, M, lsum, pb, al, lane);
@@ -2082,8 +2120,8 @@ __global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const Decode
                     uint32_t pb[4];
                     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(pb[0]), "=r"(pb[1]), "=r"(pb[2]), "=r"(pb[3]) : "r"(msg_s + lane * 16));
                     const uint32_t vsc_c = msg_s + 784 + 4 * c;
-                    v_accum16<VM, HD, WIDE>(st_s + vt_off, vrb, vsc_c, pb[0], pb[1], oacc, lut_v, plane_v, g);
-                    v_accum16<VM, HD, WIDE>(st_s + vt_off + 16 * vrb, vrb, vsc_c + 32, pb[2], pb[3], oacc, lut_v, plane_v, g);
+                    v_accum16<VM, HD, WIDE, VAL>(st_s + vt_off, vrb, vsc_c, pb[0], pb[1], oacc, lut_v, plane_v, g);
+                    v_accum16<VM, HD, WIDE, VAL>(st_s + vt_off + 16 * vrb, vrb, vsc_c + 32, pb[2], pb[3], oacc, lut_v, plane_v, g);
                     // the stage was read through the generic proxy (by both warps: the keys' warp before it sent the
                     // message): order that before the bulk copy of the next tile into it
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
