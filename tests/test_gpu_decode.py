@@ -446,6 +446,33 @@ def test_unaligned_views_and_row_padding(P, oracle):
         assert_close(got.cpu().numpy(), want, what=f"offset {off}")
 
 
+@pytest.mark.parametrize("f", [(0, 4), (3, 4), (5, 8)])
+def test_native_rows_at_any_word_offset(P, oracle, f):
+    """Rows packed back to back (the cache's own layout) whose first row sits at any word offset: rows of 72, 80 or
+    136 bytes are read with 8- or 16-byte loads only where every row is aligned to that, so an odd offset must take
+    the other instantiation and give the same rows."""
+    b, hq, hkv, d, lk = 2, 8, 2, 128, 333
+    kd, vd, tab = make_rows(oracle, 3300 + f[0], b, hkv, lk, d, f, f)
+    q = oracle.normal(84, b * hq * d).reshape(b, hq, 1, d)
+    want = oracle.tq_attention(q, kd, vd, lk, f, f, 0.0884, tab, wr=0)
+    kq = P.TurboQuantizer(fmt(P, *f), d, "none", 1)
+    vq = P.TurboQuantizer(fmt(P, *f), d, "none", 3)
+    rw = kd.shape[-1]
+    first = None
+    for off in (0, 1, 2, 3, 4):
+        kbuf = torch.full((off + b * hkv * lk * rw,), 0x7FC00000, dtype=torch.int32, device="cuda:0")
+        vbuf = torch.full((off + b * hkv * lk * rw,), 0x7FC00000, dtype=torch.int32, device="cuda:0")
+        kv = kbuf[off:].view(b, hkv, lk, rw)
+        vv = vbuf[off:].view(b, hkv, lk, rw)
+        kv.copy_(rows_dev(kd))
+        vv.copy_(rows_dev(vd))
+        got = P.attention_packed(to_dev(q), kv, vv, lk, kq, vq, P.FlashAttnConfig(0.0884).causal()).cpu().numpy()
+        assert_close(got, want, what=f"format {f}, offset {off}")
+        if first is None:
+            first = got
+        assert np.array_equal(got, first), f"format {f}: offset {off} changes the bits"
+
+
 def test_value_scales_of_any_magnitude(P, oracle):
     """The per-key value scale is folded into the exponent of the second product: rows whose scale
     is far outside the f16 range must not lose accuracy."""
