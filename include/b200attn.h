@@ -261,6 +261,10 @@ typedef struct B200Page {
  * key signs and the output rotated back with the value signs; with B200_ROT_NONE, q_dtype =
  * out_dtype = B200_F32 the call is exactly the reference's tq_attention.
  *
+ * Any word-aligned row address and any row stride are accepted. Rows packed back to back (stride = the format's row
+ * words) whose slabs start at multiples of 16 bytes, as a cache allocated in whole rows has them, take the
+ * instantiations with constant row geometry and, for rows of 72, 80 or 136 bytes, wider shared-memory loads.
+ *
  * Extension for ragged batches (the reference has one seq_len per cache, turbo_quant.rs:895-897):
  * kv_len_dev, one length per batch entry in device memory; lk is then the maximum length.
  *
