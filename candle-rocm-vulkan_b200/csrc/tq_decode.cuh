@@ -702,6 +702,7 @@ struct RowMask {
 
 // General form: masks, soft-capping, ALiBi. `key_g`: index of the tile's key g (the lane's keys are key_g + 8 k);
 // qs[e]: score scale of row 2c + e.
+template <bool PERM = false>
 __device__ __forceinline__ bool softmax_masked(const float (&sr)[2][4], const float2 (&vm)[4], const float (&qs)[2], float softcap, int key_g,
                                                const RowMask &rm, float (&M)[2], float (&lsum)[2], uint32_t (&pb)[4], float (&al)[2]) {
     float s2[8];  // s2[2 k + e]
@@ -709,7 +710,7 @@ __device__ __forceinline__ bool softmax_masked(const float (&sr)[2][4], const fl
     for (int e = 0; e < 2; ++e) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const int j = key_g + 8 * k;
+            const int j = key_g + (PERM ? 2 * (k & 1) + 16 * (k >> 1) : 8 * k);  // the lane's keys: g + 8 k, or in the other order
             float sx = sr[k >> 1][2 * (k & 1) + e] * qs[e];
             if (softcap > 0.0f) sx = softcap * tanhf(sx / softcap);
             if (rm.slope[e] != 0.0f) sx -= rm.slope[e] * fabsf((float)(rm.pos[e] - j));
@@ -972,7 +973,9 @@ __device__ __forceinline__ void tile_meta(uint32_t kr, uint32_t vr, uint32_t met
 // against the query rows 2c, 2c + 1: sr[2 k + e] = key g + 8 k, row 2c + e. `mrow`: the f32 key scales of key g
 // (per-key scalars of the tile), qb0 / qb1: the query fragments.
 // AL: what the rows' addresses in shared memory are known to be multiples of (bytes).
-template <int KM, int HD, bool WIDE = false, int AL = 4>
+// PERM: the tile's keys are dealt to the lanes in another order (perm_key below): the lane's second key is 2 rows
+// after its first instead of 8.
+template <int KM, int HD, bool WIDE = false, int AL = 4, bool PERM = false>
 __device__ __forceinline__ void k_scores16(uint32_t ka, uint32_t krb, uint32_t mrow, const uint32_t (&qb0)[HD / 16], const uint32_t (&qb1)[HD / 16],
                                            uint32_t lut_k, uint32_t plane_k, int c, float (&sr)[4]) {
     constexpr int STEPS = HD / 16;
@@ -980,7 +983,8 @@ __device__ __forceinline__ void k_scores16(uint32_t ka, uint32_t krb, uint32_t m
     constexpr int KMW = kmeta_words(KM, HD);
     constexpr int NBK = HD / 32;
     constexpr uint32_t k_cw4 = code_bytes(KM, HD);
-    const uint32_t ka8 = ka + 8 * krb;
+    static_assert(!PERM || !fmt_is_mx(KM), "the other order of keys is for rows without block scales");
+    const uint32_t ka8 = ka + (PERM ? 2 : 8) * krb;
     if constexpr (KMX) {
         float ks0[KMW], ks8[KMW];
         if constexpr (KMW == 2) {
@@ -1079,7 +1083,7 @@ __device__ __forceinline__ void k_scores16(uint32_t ka, uint32_t krb, uint32_t m
                                   cvt_e4m3x2_hi_f16x2(x8), qb0[s], qb1[s]);
             }
         }
-        const float kp0 = u2f(lds32(mrow)), kp8 = u2f(lds32(mrow + 8 * 4));
+        const float kp0 = u2f(lds32(mrow)), kp8 = u2f(lds32(mrow + (PERM ? 2 : 8) * 4));
         sr[0] *= kp0; sr[1] *= kp0; sr[2] *= kp8; sr[3] *= kp8;
     }
 }
@@ -1087,7 +1091,8 @@ __device__ __forceinline__ void k_scores16(uint32_t ka, uint32_t krb, uint32_t m
 // O^T += V^T P^T for the 16 keys at `va` (the lane's first code byte of key 2c; rows vrb bytes apart): keys 2c, 2c+1 |
 // 2c+8, 2c+9, dims [g HD/8, (g+1) HD/8). `vsc_row`: the f16 block scales of the keys 2c, 2c + 1 (+ 16 bytes: 2c + 8,
 // 2c + 9), pb0 / pb1: the weights as B fragments.
-template <int VM, int HD, bool WIDE = false, int AL = 4>
+// PERM: the lane's four keys are four consecutive rows from `va` on (perm_key below) instead of 2c, 2c + 1, 2c + 8, 2c + 9.
+template <int VM, int HD, bool WIDE = false, int AL = 4, bool PERM = false>
 __device__ __forceinline__ void v_accum16(uint32_t va, uint32_t vrb, uint32_t vsc_row, uint32_t pb0, uint32_t pb1, float (&oacc)[HD / 16][4],
                                           uint32_t lut_v, uint32_t plane_v, int g) {
     constexpr bool V4 = fmt_is4(VM);
@@ -1097,8 +1102,9 @@ __device__ __forceinline__ void v_accum16(uint32_t va, uint32_t vrb, uint32_t vs
     uint32_t xas[NW], xbs[NW], xcs[NW], xds[NW];
     lds_words<NW, min_i(AL, 4 * NW)>(va, xas);
     lds_words<NW, min_i(AL, 4 * NW)>(va + vrb, xbs);
-    lds_words<NW, min_i(AL, 4 * NW)>(va + 8 * vrb, xcs);
-    lds_words<NW, min_i(AL, 4 * NW)>(va + 9 * vrb, xds);
+    static_assert(!PERM || NBV == 0, "the other order of keys is for rows without block scales");
+    lds_words<NW, min_i(AL, 4 * NW)>(va + (PERM ? 2 : 8) * vrb, xcs);
+    lds_words<NW, min_i(AL, 4 * NW)>(va + (PERM ? 3 : 9) * vrb, xds);
 #pragma unroll
     for (int w = 0; w < NW; ++w) {
         const uint32_t xa = xas[w], xb = xbs[w], xc = xcs[w], xd = xds[w];
@@ -1637,13 +1643,20 @@ struct SegMask {
     bool plain;        // no soft-capping, no ALiBi
 };
 
+// Which key of a 16-key half a lane's row g (0..7) stands for when the keys are dealt in the other order, for packed rows
+// of 18 words: the four rows that a half warp reads together then start 0, 2, 16 and 18 banks apart (keys' side, 8-byte
+// loads of four chunks per row) or 8 banks apart (values' side, eight lanes per row), so no load meets another on a
+// bank. Row g + 8 of the product is the key 2 rows further; the values' lanes hold four consecutive keys.
+__host__ __device__ constexpr int perm_key(int g) { return (g & 1) + 8 * ((g >> 1) & 1) + 4 * (g >> 2); }
+
+template <bool PERM = false>
 __device__ __forceinline__ bool tile_softmax(const DecodeParams &p, const Segment &seg, const SegMask &sm, int key0, int nkeys, uint32_t vmeta_g,
                                              const float (&sr)[2][4], const float (&qs)[2], const float (&qs2)[2], float (&M)[2], float (&lsum)[2],
                                              uint32_t (&pb)[4], float (&al)[2], int lane) {
     const int g = lane >> 2, c = lane & 3;
-    float2 vm[4];  // (sigma, log2 sigma) of the keys g, g + 8, g + 16, g + 24
+    float2 vm[4];  // (sigma, log2 sigma) of the keys g, g + 8, g + 16, g + 24 (the other order: vmeta_g is the key's, then + 2, + 16, + 18)
 #pragma unroll
-    for (int k = 0; k < 4; ++k) vm[k] = lds64f(vmeta_g + k * 64);
+    for (int k = 0; k < 4; ++k) vm[k] = lds64f(vmeta_g + (PERM ? 16 * (k & 1) + 128 * (k >> 1) : k * 64));
     if (B200_LIKELY(sm.plain && nkeys == WK && key0 >= sm.LOmax && key0 + WK <= sm.HImin)) return softmax_plain(sr, vm, qs2, M, lsum, pb, al);
     // masks, soft-capping, ALiBi: the two query rows whose scores this lane holds (columns 2c, 2c + 1)
     const uint32_t hk = seg.y / p.packs, pack = seg.y % p.packs, G = p.group;
@@ -1659,7 +1672,7 @@ __device__ __forceinline__ bool tile_softmax(const DecodeParams &p, const Segmen
             if (p.alibi) rm.slope[e] = p.alibi[(size_t)seg.b * p.alibi_bs + hk * G + (p.lq == 1 ? r : r % G)];
         }
     }
-    return softmax_masked(sr, vm, qs, p.softcap, key0 + g, rm, M, lsum, pb, al);
+    return softmax_masked<PERM>(sr, vm, qs, p.softcap, key0 + (PERM ? perm_key(g) : g), rm, M, lsum, pb, al);
 }
 
 __device__ __forceinline__ SegMask segment_mask(const DecodeParams &p, const Segment &seg) {
@@ -1939,6 +1952,8 @@ __global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const Decode
     const int NS = (int)p.ns;
     const uint32_t sbase = smem_u32(smem);
     constexpr bool WIDE = pair_wide_lut(KM, VM);
+    // packed rows of 18 words (both sides 4-bit codebook rows): keys dealt to the lanes so that no code load meets another on a bank
+    constexpr bool PERM = WIDE && NAT && nat_row_bytes(KM, HD) == 72 && nat_row_bytes(VM, HD) == 72;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
     // WIDE: one table of [256][32] words for keys and values (both sides decode with the same codebook), every lane
     // reading its own column
@@ -2002,8 +2017,9 @@ __global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const Decode
 
     if (keys_side) {
         // ============================================================== the keys' warp
-        const uint32_t k_lane = g * krb + (KMX ? (K4 ? 4u * c : 8u * c) : (K4 ? c * (HD / 8) : c * (HD / 4)));
-        const uint32_t mrow_g = meta_s + g * KMW * 4, vmeta_g = vmeta_s + g * 8;
+        const uint32_t kg = PERM ? (uint32_t)perm_key(g) : (uint32_t)g;  // the key (of 16) behind the lane's row g
+        const uint32_t k_lane = kg * krb + (KMX ? (K4 ? 4u * c : 8u * c) : (K4 ? c * (HD / 8) : c * (HD / 4)));
+        const uint32_t mrow_g = meta_s + kg * KMW * 4, vmeta_g = vmeta_s + kg * 8;
         uint32_t qb0[STEPS], qb1[STEPS];
         float qs[2], qs2[2];
         // a free slot for message `msgs`: the values' warp has taken message msgs - PQ
@@ -2038,11 +2054,11 @@ __global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const Decode
                 if (nkeys < WK) clear_stale_rows(st_s + koff, st_s + k_stage_bytes + voff, nkeys, krb, vrb, lane);
                 tile_meta<KM, VM, HD>(st_s + kr_off, st_s + vr_off, meta_s, vmeta_s, msg_s + 784, lane);
                 float sr[2][4];
-                k_scores16<KM, HD, WIDE, KAL>(st_s + kt_off, krb, mrow_g, qb0, qb1, lut_k, plane_k, c, sr[0]);
-                k_scores16<KM, HD, WIDE, KAL>(st_s + kt_off + 16 * krb, krb, mrow_g + 16 * KMW * 4, qb0, qb1, lut_k, plane_k, c, sr[1]);
+                k_scores16<KM, HD, WIDE, KAL, PERM>(st_s + kt_off, krb, mrow_g, qb0, qb1, lut_k, plane_k, c, sr[0]);
+                k_scores16<KM, HD, WIDE, KAL, PERM>(st_s + kt_off + 16 * krb, krb, mrow_g + 16 * KMW * 4, qb0, qb1, lut_k, plane_k, c, sr[1]);
                 uint32_t pb[4];
                 float al[2];
-                const bool moved = tile_softmax(p, seg, sm, key0, nkeys, vmeta_g, sr, qs, qs2, M, lsum, pb, al, lane);
+                const bool moved = tile_softmax<PERM>(p, seg, sm, key0, nkeys, vmeta_g, sr, qs, qs2, M, lsum, pb, al, lane);
                 asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(msg_s + lane * 16), "r"(pb[0]), "r"(pb[1]), "r"(pb[2]), "r"(pb[3]) : "memory");
                 if (moved) asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(msg_s + 512 + lane * 8), "f"(al[0]), "f"(al[1]) : "memory");
                 if (lane == 0) sts32(msg_s + 768, moved ? 1u : 0u);
@@ -2075,7 +2091,7 @@ __global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const Decode
         }
     } else {
         // ============================================================== the values' warp
-        const uint32_t v_lane = 2 * c * vrb + (V4 ? g * (HD / 16) : g * (HD / 8));
+        const uint32_t v_lane = (PERM ? (uint32_t)perm_key(2 * c) : 2u * c) * vrb + (V4 ? g * (HD / 16) : g * (HD / 8));
         float oacc[STEPS][4];
         CopySide cs;
         cs.start(p, sh.seg, krb, vrb);
@@ -2120,8 +2136,8 @@ __global__ void __launch_bounds__(PW * 64, 2) tq_decode_pair_kernel(const Decode
                     uint32_t pb[4];
                     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(pb[0]), "=r"(pb[1]), "=r"(pb[2]), "=r"(pb[3]) : "r"(msg_s + lane * 16));
                     const uint32_t vsc_c = msg_s + 784 + 4 * c;
-                    v_accum16<VM, HD, WIDE, VAL>(st_s + vt_off, vrb, vsc_c, pb[0], pb[1], oacc, lut_v, plane_v, g);
-                    v_accum16<VM, HD, WIDE, VAL>(st_s + vt_off + 16 * vrb, vrb, vsc_c + 32, pb[2], pb[3], oacc, lut_v, plane_v, g);
+                    v_accum16<VM, HD, WIDE, VAL, PERM>(st_s + vt_off, vrb, vsc_c, pb[0], pb[1], oacc, lut_v, plane_v, g);
+                    v_accum16<VM, HD, WIDE, VAL, PERM>(st_s + vt_off + 16 * vrb, vrb, vsc_c + 32, pb[2], pb[3], oacc, lut_v, plane_v, g);
                     // the stage was read through the generic proxy (by both warps: the keys' warp before it sent the
                     // message): order that before the bulk copy of the next tile into it
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
