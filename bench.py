@@ -410,14 +410,26 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
         dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)
         if int(ok_all.item()) == 0:
             peer_gather = None
-    # the timed steps stand for the layers of one decode step (caches and lengths fixed before the step): each attention
-    # takes its place on the GPU, and streams its first keys, while the previous layer's kernel ends
-    # (B200_TQ_AFTER_PREV | B200_TQ_INPUTS_FINAL)
-    calls = [P.PackedAttention(q, kc, vc, kv_len, kq, vq, cfg, out=out, gather=peer_gather, after_prev=True, fresh_rows=0, status=status)
-             for kc, vc in caches]
+    # the timed steps stand for attention calls over caches that nobody writes meanwhile (lengths fixed before): each
+    # attention takes its place on the GPU, and streams its first keys, while the previous one's kernel ends
+    # (B200_TQ_AFTER_PREV | B200_TQ_INPUTS_FINAL). On one GPU the calls also come in runs with an output and a workspace
+    # of their own each (B200_TQ_OUTPUTS_FREE), so that no store waits for the call before; a run is the steps of one graph
+    # replay and starts with a plain launch, behind which nothing earlier is still running. With gathered outputs (several ranks) every call's stores
+    # wait for the previous call, whose step word they follow.
+    # one run = the steps of one graph replay (a replay starts when the one before has completed)
+    group = steps if steps <= 128 else 32
+    group = max(nbuf, group // nbuf * nbuf)  # whole rounds of the caches: a replay does not start on the cache that the one before ended on
+    run_len = group if world == 1 else nbuf
+    if world == 1:
+        outs = [out] + [torch.empty_like(out) for _ in range(run_len - 1)]
+        calls = [P.PackedAttention(q, caches[j % nbuf][0], caches[j % nbuf][1], kv_len, kq, vq, cfg, out=outs[j], after_prev=j > 0,
+                                   fresh_rows=0 if j > 0 else None, status=status, outputs_free=j > 0) for j in range(run_len)]
+    else:
+        calls = [P.PackedAttention(q, kc, vc, kv_len, kq, vq, cfg, out=out, gather=peer_gather, after_prev=True, fresh_rows=0, status=status)
+                 for kc, vc in caches]
 
     def eager_step(i):
-        calls[i % nbuf].run()
+        calls[i % run_len].run()
         if world > 1 and peer_gather is None:
             dist.all_gather_into_tensor(gathered, out)
 
@@ -429,9 +441,6 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
     # dependent of the one before; between two replays there is no such edge, so the timed steps are one graph when
     # they are few (up to 128), groups of 32 otherwise.
     graphs, long_graph = [], None
-    group = steps if steps <= 128 else 32
-    if nbuf > 1 and group % nbuf == 1:
-        group += 1 if steps > 128 else 0  # a replay must not start on the cache that the one before ended on
     try:
         for i in range(nbuf):
             gr = torch.cuda.CUDAGraph()
@@ -634,7 +643,7 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
             "config": {"workload": f"{name}: {w_full['desc'] if not (name == 'c4' and world == 1) else w['desc']}",
                        "batch_per_gpu": b, "hq": hq, "hkv": hkv, "head_dim": d,
                        "kv_format": w["fmt"], "rotation": w["rot"], "total_keys_per_gpu": int(lens.sum()),
-                       "launch": (f"CUDA graph replay ({group} steps per graph)" if graphs else "eager C ABI calls") + "; every attention is launched as a programmatic dependent of the previous one with its inputs declared final (B200_TQ_AFTER_PREV | B200_TQ_INPUTS_FINAL): it streams its first keys while the previous kernel drains",
+                       "launch": (f"CUDA graph replay ({group} steps per graph)" if graphs else "eager C ABI calls") + "; every attention is launched as a programmatic dependent of the previous one with its inputs declared final (B200_TQ_AFTER_PREV | B200_TQ_INPUTS_FINAL): it streams its first keys while the previous kernel drains" + (f"; runs of {run_len} calls with an output and a workspace of their own each (B200_TQ_OUTPUTS_FREE: no store waits for the call before), every run begun by a plain launch" if world == 1 else ""),
                        "l2": f"{nbuf} caches of {cache_bytes / 1e6:.0f} MB cycled (each step reads other rows than the last; L2 is 126 MB)",
                        "parallelism": (f"{'kv heads' if w_full['shard'] == 'kv_head' else 'batch'} split x{world}, {gather_note}" if strong
                                        else (f"batch shard x{world}, {gather_note}" if world > 1 else "single GPU"))},

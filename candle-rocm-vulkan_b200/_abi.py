@@ -74,6 +74,7 @@ KV_AFTER_PREV = 1  # B200_KV_AFTER_PREV
 TQ_AFTER_PREV = 1  # B200_TQ_AFTER_PREV
 TQ_INPUTS_FINAL = 2  # B200_TQ_INPUTS_FINAL
 TQ_IN_PLACE = 4  # B200_TQ_IN_PLACE
+TQ_OUTPUTS_FREE = 8  # B200_TQ_OUTPUTS_FREE
 
 
 class TqAttnArgs(C.Structure):

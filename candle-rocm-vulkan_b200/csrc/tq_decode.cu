@@ -190,6 +190,7 @@ static int make_plan(const B200TqAttnArgs *a, DecodePlan &pl, bool paged = false
 
     p.after_prev = (a->flags & B200_TQ_AFTER_PREV) ? 1u : 0u;
     p.prefetch = (p.after_prev && (a->flags & B200_TQ_INPUTS_FINAL)) ? 1u : 0u;
+    p.out_free = (p.after_prev && (a->flags & B200_TQ_OUTPUTS_FREE)) ? 1u : 0u;
     p.fresh_rows = std::min<uint32_t>(a->fresh_rows, 0x7fffffffu);
     pl.nat = !paged && p.k_ss == (uint64_t)kl.row_words && p.v_ss == (uint64_t)vl.row_words && a->kq.mode == a->vq.mode && a->d == 128;
     if (pl.nat) {
@@ -565,6 +566,7 @@ static int run_plan(const B200TqAttnArgs *a, DecodePlan &pl, char *ws, size_t ws
         pl.p.step = tl_gather->step;
         pl.p.done_ctr = tl_gather->done_ctr;
         pl.p.gather_polls = tl_gather->max_polls;
+        pl.p.out_free = 0;  // the step word of the gather is the previous call's to write: stores wait for that call
     }
     if ((uint64_t)a->b * a->hq * a->lq == 0) return B200_OK;
     if (!a->q || !a->out) return set_error(B200_ERR_BAD_ARG, "tq_attention: null pointer");

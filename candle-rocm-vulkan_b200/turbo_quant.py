@@ -365,11 +365,13 @@ class PackedAttention:
     def __init__(self, q: torch.Tensor, k_rows: torch.Tensor, v_rows: torch.Tensor, kv_len, kq: TurboQuantizer,
                  vq: TurboQuantizer, cfg: FlashAttnConfig, out: Optional[torch.Tensor] = None,
                  gather: Optional["OutputGather"] = None, after_prev: bool = False, kv_len_add: int = 0,
-                 fresh_rows: Optional[int] = None, status: Optional[torch.Tensor] = None):
+                 fresh_rows: Optional[int] = None, status: Optional[torch.Tensor] = None, outputs_free: bool = False):
         # after_prev: B200_TQ_AFTER_PREV of include/b200attn.h (the call may start while the stream's previous kernel
         # still runs; only for callers whose kv_len is not written by that kernel). fresh_rows (with after_prev):
         # B200_TQ_INPUTS_FINAL, the previous kernel writes none of the inputs but at most that many rows at the end
         # of every sequence (q included: it must be final before that kernel starts).
+        # outputs_free (with after_prev): B200_TQ_OUTPUTS_FREE, no kernel that may still be running on the stream reads or
+        # writes `out` or this call's workspace (consecutive calls with different outputs and their own workspaces).
         # status: an int32 device word that the kernels set when a bounded device wait runs out.
         _need_cuda(q, "q")
         b, hq, lq, d = q.shape
@@ -439,6 +441,8 @@ class PackedAttention:
         if after_prev and fresh_rows is not None:
             args.flags |= A.TQ_INPUTS_FINAL
             args.fresh_rows = int(fresh_rows)
+        if after_prev and outputs_free:
+            args.flags |= A.TQ_OUTPUTS_FREE
         args.kv_len_add = int(kv_len_add) if ragged else 0  # tokens appended since the device lengths were written
         self.args, self.out, self.device = args, user_out, q.device
         self._keep = (q, out, k_rows, v_rows, kv_len, kq, vq, alibi, ws, status)

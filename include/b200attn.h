@@ -315,6 +315,17 @@ typedef struct B200TqAttnArgs {
  * (fresh_rows = 1: q was produced before that kernel), and for attention calls that follow one another over caches
  * nobody writes (fresh_rows = 0). The outputs are those of the plain call. */
 #define B200_TQ_INPUTS_FINAL 2u
+/* Together with B200_TQ_AFTER_PREV: this call's `out` and its workspace are touched by no kernel launched on the stream
+ * since the last kernel that was launched without B200_TQ_AFTER_PREV (an attention without the flag, or any other plain
+ * launch: it starts when all earlier work has completed). A caller that runs several attentions back to back gives
+ * each run of flagged calls outputs and workspaces of their own and starts every run with a call without
+ * B200_TQ_AFTER_PREV. The attention then stores partial results and finished rows without waiting for the previous
+ * kernel, so that consecutive calls overlap for as long as the device has room for both (a worker that finishes its
+ * first column early no longer sits on its place until the whole previous grid has gone); a tile that reaches into the
+ * fresh rows still waits, and one block of the grid waits for the previous kernel before it leaves, so that a kernel of
+ * such a run never completes before its predecessor. Ignored by calls with gathered outputs (their step word is the previous
+ * call's to write). The outputs are those of the plain call. */
+#define B200_TQ_OUTPUTS_FREE 8u
 /* Paged calls (pages != NULL): the blocks are read where they are, without a copy, by the general kernel; by the
  * tensor-core kernel too when keys and values share one of its formats (it walks the block table). Other format pairs
  * of the tensor-core kernel are compacted into the workspace by one copy kernel first, unless this flag is set: then

@@ -34,6 +34,7 @@ pub const B200_KV_AFTER_PREV: u32 = 1;
 pub const B200_TQ_AFTER_PREV: u32 = 1;
 pub const B200_TQ_INPUTS_FINAL: u32 = 2;
 pub const B200_TQ_IN_PLACE: u32 = 4;
+pub const B200_TQ_OUTPUTS_FREE: u32 = 8;
 pub const B200_STATIC_SCRATCH_BYTES: usize = 8 << 20;
 
 #[repr(C)]

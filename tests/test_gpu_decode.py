@@ -252,6 +252,52 @@ def test_launch_behind_a_running_kernel_gives_the_same_rows(P, oracle):
     assert P._abi.lib().b200_device_wait_status() == 0
 
 
+@pytest.mark.parametrize("f", [(2, 4), (0, 4)])
+def test_calls_that_overlap_their_predecessors_give_the_same_rows(P, oracle, f):
+    """B200_TQ_AFTER_PREV | B200_TQ_INPUTS_FINAL | B200_TQ_OUTPUTS_FREE: calls over caches nobody writes, each with an
+    output and a workspace of its own, neither read nor stored behind the call before. A chain of them, eager and as a
+    CUDA graph, gives the rows of the plain calls (ragged lengths, so that columns are merged inside the grid)."""
+    b, hq, hkv, d, cap = 16, 16, 4, 128, 3000
+    fm = fmt(P, *f)
+    kq, vq = P.TurboQuantizer(fm, d, "none", 42), P.TurboQuantizer(fm, d, "none", 44)
+    g = torch.Generator(device="cuda:0").manual_seed(6)
+    lens = torch.randint(1, cap, (b,), generator=g, device="cuda:0", dtype=torch.int32)
+    cfg = P.FlashAttnConfig(d ** -0.5).causal()
+    n = 4
+    caches, qs = [], []
+    for i in range(n):
+        kx = torch.randn((b * hkv * cap, d), generator=g, device="cuda:0")
+        vx = torch.randn((b * hkv * cap, d), generator=g, device="cuda:0")
+        caches.append((kq.quantize_rows(kx).view(b, hkv, cap, -1), vq.quantize_rows(vx).view(b, hkv, cap, -1)))
+        qs.append(torch.randn((b, hq, 1, d), generator=g, device="cuda:0", dtype=torch.bfloat16))
+    plain = [P.PackedAttention(qs[i], caches[i][0], caches[i][1], lens, kq, vq, cfg) for i in range(n)]
+    for c in plain:
+        c.run()
+    torch.cuda.synchronize()
+    want = [c.out.clone() for c in plain]
+    chain = [P.PackedAttention(qs[i], caches[i][0], caches[i][1], lens, kq, vq, cfg, after_prev=True, fresh_rows=0, outputs_free=True)
+             for i in range(n)]
+    for rounds in range(2):
+        for c in chain:
+            c.out.fill_(float("nan"))
+        for c in chain:
+            c.run()
+        torch.cuda.synchronize()
+        for i, c in enumerate(chain):
+            assert torch.equal(c.out, want[i]), f"eager chain, round {rounds}, call {i}"
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        for c in chain:
+            c.run()
+    for c in chain:
+        c.out.fill_(float("nan"))
+    gr.replay()
+    torch.cuda.synchronize()
+    for i, c in enumerate(chain):
+        assert torch.equal(c.out, want[i]), f"graph chain, call {i}"
+    assert P._abi.lib().b200_device_wait_status() == 0
+
+
 def test_length_and_position_offsets(P, oracle):
     """kv_len_add / pos0 with device positions: a step that appends at lens + j and attends to lens + j + 1 keys gives
     the rows and outputs of the same step run with the lengths updated on the device."""
