@@ -7,8 +7,10 @@ compressed KV cache is resident in HBM (a ragged batch of 64 sequences with 512-
 by default: 32 query heads, 8 kv heads, head dim 128, bf16 queries). The metric is the achieved HBM
 bandwidth on the algorithmic bytes of the step (packed code and scale bytes of every visible K and
 V row, plus queries and outputs), with tokens/s beside it. With N > 1 every rank holds its own
-batch (weak scaling, no data-path collective; the outputs of all ranks are gathered on every rank
-by the attention's own epilogue).
+batch (weak scaling, no data-path collective: nothing in a rank's step depends on another rank).
+Where one problem is split over the ranks (c4, c5) the outputs of all ranks are assembled on every
+rank inside the step, by the attention's own epilogue; a short line times the headline workload
+with that exchange too.
 
 The last line printed is the headline workload. Before it come short lines for the other
 configurations of the benchmark (unless --only): single FP8 decode (c1), prefill with cache append
@@ -344,11 +346,14 @@ def ref_gpu_decode(env, w, lens, caches, kq, vq, steps):
 
 
 
-def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, layers=1):
+def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, layers=1, gather=None):
     """Times workload `w_full` (sharded over the ranks when it says so): exactly `steps` steps between two events.
-    Returns the result line (rank 0) or None."""
+    `gather`: assemble the outputs of all ranks on every rank inside the step. By default where one problem is split
+    over the ranks (strong scaling: the layer's output has to be put together again); ranks that each hold a batch of
+    their own (weak scaling) have nothing to exchange. Returns the result line (rank 0) or None."""
     torch, dist, P, dev, rank, world = env.torch, env.dist, env.P, env.dev, env.rank, env.world
     strong = w_full["shard"] is not None and world > 1
+    use_gather = world > 1 and (strong if gather is None else bool(gather))
     w = shard_of(w_full, world) if strong else dict(w_full)
     if w is None:
         return None
@@ -393,7 +398,7 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
     out_host = torch.empty((b, hq, 1, d), dtype=tdt).pin_memory()
     q = step_dev[:nq].view(b, hq, 1, d)
     out = torch.empty((b, hq, 1, d), dtype=tdt, device=dev)
-    gathered = torch.empty((world * b, hq, 1, d), dtype=tdt, device=dev) if world > 1 else None
+    gathered = torch.empty((world * b, hq, 1, d), dtype=tdt, device=dev) if use_gather else None
     cfg = P.FlashAttnConfig(d ** -0.5).causal()
     status = torch.zeros(1, dtype=torch.int32, device=dev)  # set by the kernels when a bounded device wait runs out
 
@@ -401,7 +406,7 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
     # (peer stores over NVLink into symmetric memory, b200_tq_attention_gather); if symmetric memory cannot be had, by an
     # NCCL all-gather after the attention
     peer_gather = None
-    if world > 1:
+    if use_gather:
         try:
             peer_gather = P.OutputGather(b * hq, d, tdt, dev)
         except Exception as e:
@@ -419,8 +424,8 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
     # one run = the steps of one graph replay (a replay starts when the one before has completed)
     group = steps if steps <= 128 else 32
     group = max(nbuf, group // nbuf * nbuf)  # whole rounds of the caches: a replay does not start on the cache that the one before ended on
-    run_len = group if world == 1 else nbuf
-    if world == 1:
+    run_len = group if not use_gather else nbuf
+    if not use_gather:
         outs = [out] + [torch.empty_like(out) for _ in range(run_len - 1)]
         calls = [P.PackedAttention(q, caches[j % nbuf][0], caches[j % nbuf][1], kv_len, kq, vq, cfg, out=outs[j], after_prev=j > 0,
                                    fresh_rows=0 if j > 0 else None, status=status, outputs_free=j > 0) for j in range(run_len)]
@@ -430,7 +435,7 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
 
     def eager_step(i):
         calls[i % run_len].run()
-        if world > 1 and peer_gather is None:
+        if use_gather and peer_gather is None:
             dist.all_gather_into_tensor(gathered, out)
 
     for i in range(nbuf):
@@ -485,7 +490,7 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
     total_ms = ev0.elapsed_time(ev1)
     env.stage(f"{name}: timed region done")
     gather_note = "outputs all-gathered over NCCL"
-    if peer_gather is not None and world > 1:
+    if peer_gather is not None and use_gather:
         # the gathered rows of the last step against an NCCL all-gather of the same outputs
         dist.all_gather_into_tensor(gathered, out)
         torch.cuda.synchronize()
@@ -552,7 +557,7 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
                     main.wait_event(ev_out[i - 2])            # the result of step i - 2 has left this output buffer
                 P.PackedAttention(qv, kc, vc, lens_dev, kq, vq, cfg, out=out_dev[pb], gather=peer_gather, kv_len_add=j + 1,
                                   after_prev=True, fresh_rows=1, status=status).run()
-                if world > 1 and peer_gather is None:
+                if use_gather and peer_gather is None:
                     dist.all_gather_into_tensor(gathered, out_dev[pb])
                 ev_done[i] = torch.cuda.Event()
                 ev_done[i].record(main)
@@ -643,10 +648,12 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
             "config": {"workload": f"{name}: {w_full['desc'] if not (name == 'c4' and world == 1) else w['desc']}",
                        "batch_per_gpu": b, "hq": hq, "hkv": hkv, "head_dim": d,
                        "kv_format": w["fmt"], "rotation": w["rot"], "total_keys_per_gpu": int(lens.sum()),
-                       "launch": (f"CUDA graph replay ({group} steps per graph)" if graphs else "eager C ABI calls") + "; every attention is launched as a programmatic dependent of the previous one with its inputs declared final (B200_TQ_AFTER_PREV | B200_TQ_INPUTS_FINAL): it streams its first keys while the previous kernel drains" + (f"; runs of {run_len} calls with an output and a workspace of their own each (B200_TQ_OUTPUTS_FREE: no store waits for the call before), every run begun by a plain launch" if world == 1 else ""),
+                       "launch": (f"CUDA graph replay ({group} steps per graph)" if graphs else "eager C ABI calls") + "; every attention is launched as a programmatic dependent of the previous one with its inputs declared final (B200_TQ_AFTER_PREV | B200_TQ_INPUTS_FINAL): it streams its first keys while the previous kernel drains" + (f"; runs of {run_len} calls with an output and a workspace of their own each (B200_TQ_OUTPUTS_FREE: no store waits for the call before), every run begun by a plain launch" if not use_gather else ""),
                        "l2": f"{nbuf} caches of {cache_bytes / 1e6:.0f} MB cycled (each step reads other rows than the last; L2 is 126 MB)",
                        "parallelism": (f"{'kv heads' if w_full['shard'] == 'kv_head' else 'batch'} split x{world}, {gather_note}" if strong
-                                       else (f"batch shard x{world}, {gather_note}" if world > 1 else "single GPU"))},
+                                       else (f"a batch of its own on each of {world} ranks, " + (gather_note if use_gather else "no exchange (nothing depends on another rank)")
+                                             if world > 1 else "single GPU")),
+                       "output_gather": use_gather},
             "tokens_per_s": (w_full["b"] if strong else world * b) / (ms * 1e-3),
             "pct_of_8000_gbs_nominal": 100.0 * value / (8000.0 * world),
             "gpu_launches": steps * launches_per_step * world,  # of all ranks, like `value`
@@ -851,6 +858,7 @@ def compact(line):
     if line.get("clocks"):
         c["clocks"] = {"sm_mhz": line["clocks"]["sm_mhz"], "reasons": line["clocks"]["reasons"]}
     c["batch_per_gpu"] = line["config"].get("batch_per_gpu")
+    c["output_gather"] = line["config"].get("output_gather")
     c["hkv_per_gpu"] = line["config"].get("hkv")
     return c
 
@@ -880,6 +888,11 @@ def run_ours(args, rank, world, local_rank):
                                             with_cpu=(world == 1), layers=32 if name == "c5" else 1)))
         if head != "c3":
             lines.append(compact(prefill_leg(env, max(3, min(args.steps, 10)), 3)))
+        if head != "c3" and world > 1 and WORKLOADS[head]["shard"] is None:
+            # the headline workload once more with the exchange that its own steps do not need: every rank's outputs
+            # assembled on every rank by the attention's epilogue
+            lines.append(compact(decode_leg(env, head, dict(WORKLOADS[head]), short, max(3, min(args.warmup, 6)), with_e2e=False,
+                                            with_cpu=False, gather=True)))
     if rank == 0:
         for l in lines:
             if l is not None:
