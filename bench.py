@@ -508,70 +508,79 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
         # step i - 1 run on their own streams beside the kernels of step i. Every step still copies its own inputs in and
         # its own result out.
         lens_dev = kv_len.clone()
-        in_dev = [step_dev, torch.empty_like(step_dev), torch.empty_like(step_dev)]
-        out_dev = [out, torch.empty_like(out)]
-        out_hosts = [out_host, torch.empty_like(out_host).pin_memory()]
+        # Rings of input and output buffers, and the main stream's waits for the copy streams taken in batches of RUN
+        # steps: an event wait in front of a kernel makes it wait for the whole of its predecessor, so a wait per step
+        # would keep every attention from starting before the one before has ended. Inside a batch nothing stands between
+        # the kernels: the append of step i + 1 is launched while the attention of step i drains (B200_KV_AFTER_PREV: it
+        # writes a row that this attention does not read), and the attention of step i + 1 behind it streams its old
+        # rows meanwhile (B200_TQ_AFTER_PREV | B200_TQ_INPUTS_FINAL, fresh_rows = 1) and, on one GPU, stores into an
+        # output and a workspace of its own (B200_TQ_OUTPUTS_FREE; the batch's first append is a plain launch behind
+        # the waits). Every step still copies its own inputs in and its own result out; the copies run RUN to 2 RUN
+        # steps ahead of / behind the kernels on their own streams.
+        RUN = 16
+        depth = 3 * RUN
+        in_dev = [step_dev] + [torch.empty_like(step_dev) for _ in range(depth - 1)]
+        out_dev = [out] + [torch.empty_like(out) for _ in range(depth - 1)]
+        out_hosts = [out_host] + [torch.empty_like(out_host).pin_memory() for _ in range(depth - 1)]
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
 
         def e2e_steps(first, count):
-            """Steps first .. first + count - 1 as a pipeline over the current stream and two copy streams. Inputs are triple
-            buffered: the copy of step i + 1 is queued before the kernels of step i and waited for between the append and the
-            attention of step i, so that nothing stands between the attention of a step and the append of the next one, which
-            is launched while that attention drains (B200_KV_AFTER_PREV; an event wait in front of a kernel makes it wait for
-            the whole of its predecessor)."""
+            """Steps first .. first + count - 1 as a pipeline over the current stream and two copy streams."""
             main = torch.cuda.current_stream(dev)
             fork = torch.cuda.Event()
             fork.record(main)
             s_in.wait_event(fork)
             s_out.wait_event(fork)
             ev_in, ev_done, ev_out = {}, {}, {}
+            end = first + count
+            keep = []  # the calls of this group stay alive to its end: each owns its workspace, which no later call of the group may get
 
             def h2d(i):
+                if i >= end or i in ev_in:
+                    return
                 with torch.cuda.stream(s_in):
-                    if i - 3 in ev_done:
-                        s_in.wait_event(ev_done[i - 3])       # the kernels of step i - 3 have read this input buffer
-                    in_dev[i % 3].copy_(step_host, non_blocking=True)
+                    if i - depth in ev_done:
+                        s_in.wait_event(ev_done[i - depth])   # the kernels of step i - depth have read this input buffer
+                    in_dev[i % depth].copy_(step_host, non_blocking=True)
                     ev_in[i] = torch.cuda.Event()
                     ev_in[i].record(s_in)
 
-            h2d(first)
-            main.wait_event(ev_in[first])
             for i in range(first, first + count):
-                pb, ib = i & 1, i % 3
+                j = i - first
+                if j % RUN == 0:
+                    # a batch begins: the copies of the batch after it are queued, this batch's inputs (queued a batch ago)
+                    # and the output buffers it writes (copied out two batches ago) are waited for, all at once
+                    for x in range(i, i + 2 * RUN):
+                        h2d(x)
+                    for x in range(i, min(i + RUN, end)):
+                        main.wait_event(ev_in[x])
+                        if x - depth in ev_out:
+                            main.wait_event(ev_out[x - depth])
+                ob, ib = i % depth, i % depth
                 kc, vc = caches[i % nbuf]
                 qv = in_dev[ib][:nq].view(b, hq, 1, d)
                 kn = in_dev[ib][nq:nq + nkv].view(b, hkv, 1, d)
                 vn = in_dev[ib][nq + nkv:].view(b, hkv, 1, d)
-                if i + 1 < first + count:
-                    h2d(i + 1)                                # runs beside the kernels of this step
                 # the device lengths are those at the start of this group of steps: step j appends at lens + j and attends
-                # to lens + j + 1 keys (offsets in the call arguments), so no kernel sits between append and attention.
-                # The append of every step but the group's first takes its place while the previous step's attention drains
-                # (that attention reads none of the row written here; the first step follows the kernel that wrote the
-                # lengths, which the append reads)
-                j = i - first
-                _kv_append(kn, vn, kc, vc, kq, vq, lens_dev, pos_add=j, status=status, after_prev=(j > 0))
-                if i + 1 in ev_in:
-                    main.wait_event(ev_in[i + 1])             # the next step's inputs: its append then needs no wait
-                if i - 2 in ev_out:
-                    main.wait_event(ev_out[i - 2])            # the result of step i - 2 has left this output buffer
-                P.PackedAttention(qv, kc, vc, lens_dev, kq, vq, cfg, out=out_dev[pb], gather=peer_gather, kv_len_add=j + 1,
-                                  after_prev=True, fresh_rows=1, status=status).run()
+                # to lens + j + 1 keys (offsets in the call arguments), so no kernel sits between append and attention
+                _kv_append(kn, vn, kc, vc, kq, vq, lens_dev, pos_add=j, status=status, after_prev=(j % RUN != 0))
+                keep.append(P.PackedAttention(qv, kc, vc, lens_dev, kq, vq, cfg, out=out_dev[ob], gather=peer_gather, kv_len_add=j + 1,
+                                              after_prev=True, fresh_rows=1, status=status, outputs_free=not use_gather))
+                keep[-1].run()
                 if use_gather and peer_gather is None:
-                    dist.all_gather_into_tensor(gathered, out_dev[pb])
+                    dist.all_gather_into_tensor(gathered, out_dev[ob])
                 ev_done[i] = torch.cuda.Event()
                 ev_done[i].record(main)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(ev_done[i])
-                    out_hosts[pb].copy_(out_dev[pb], non_blocking=True)
+                    out_hosts[ob].copy_(out_dev[ob], non_blocking=True)
                     ev_out[i] = torch.cuda.Event()
                     ev_out[i].record(s_out)
             lens_dev.add_(count)                              # one length update per group of steps
-            last = first + count - 1
-            main.wait_event(ev_in[last])
-            main.wait_event(ev_out[last])
-            if last - 1 in ev_out:
-                main.wait_event(ev_out[last - 1])
+            # the group ends when its copies have ended
+            main.wait_event(ev_in[end - 1])
+            for x in range(max(first, end - depth), end):
+                main.wait_event(ev_out[x])
 
         e2e_steps(0, max(min(warmup, 3), nbuf))
         env.barrier()
