@@ -648,7 +648,9 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
         # grid follows (with N > 1 its last block publishes the gathered step)
         ncols = b * hkv * max(1, (hq // hkv + 7) // 8)
         pair = w["mode"] == 0  # the codebook formats run on the kernel whose workers are pairs of warps
-        in_kernel = ncols * 8 > 148 * (2 if pair else 3) * 4
+        # (up to 128 workers per column for the calls of a run, which are declared independent of the call before)
+        nworkers = min(148 * (2 if pair else 3) * 4, int(((lens.astype(np.int64) + 31) // 32).sum()) * (ncols // b))  # at most one worker per tile
+        in_kernel = ncols * (8 if use_gather else 128) > nworkers
         launches_per_step = 1 if in_kernel else 2
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,

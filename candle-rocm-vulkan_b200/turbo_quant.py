@@ -431,22 +431,24 @@ class PackedAttention:
         args.wl, args.wr = wl, wr
         args.alibi, args.alibi_bstride = (alibi.data_ptr() if alibi is not None else None), abs_
         args.splits = cfg.splits
-        nbytes = A.lib().b200_tq_attention_workspace_bytes(C.byref(args))
-        if nbytes == 0:
-            A.check(A.lib().b200_tq_attention(C.byref(args), None))  # reports why the call cannot be planned
-        ws = _workspace(q.device, nbytes)
-        args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
-        args.status = status.data_ptr() if status is not None else None
         args.flags = A.TQ_AFTER_PREV if after_prev else 0
         if after_prev and fresh_rows is not None:
             args.flags |= A.TQ_INPUTS_FINAL
             args.fresh_rows = int(fresh_rows)
         if after_prev and outputs_free:
             args.flags |= A.TQ_OUTPUTS_FREE
+        nbytes = A.lib().b200_tq_attention_workspace_bytes(C.byref(args))  # the plan, and with it the size, depends on the flags
+        if nbytes == 0:
+            A.check(A.lib().b200_tq_attention(C.byref(args), None))  # reports why the call cannot be planned
+        # calls of a stream share one scratch buffer, which stream order keeps apart; a call that does not wait for the one
+        # before (outputs_free) has a buffer of its own
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device) if (after_prev and outputs_free) else _workspace(q.device, nbytes)
+        args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+        args.status = status.data_ptr() if status is not None else None
         args.kv_len_add = int(kv_len_add) if ragged else 0  # tokens appended since the device lengths were written
         self.args, self.out, self.device = args, user_out, q.device
         self._keep = (q, out, k_rows, v_rows, kv_len, kq, vq, alibi, ws, status)
-        self.workspace = ws  # the scratch buffer of the call (shared by the calls of one stream)
+        self.workspace = ws  # the scratch buffer of the call (shared by the calls of one stream unless outputs_free)
         self._fn, self._ref = A.lib().b200_tq_attention, C.byref(args)
         self._gather = gather
         if gather is not None and self._dense.o32 is not None:
