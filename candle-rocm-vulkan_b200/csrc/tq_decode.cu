@@ -658,6 +658,7 @@ static std::mutex g_static_scratch_mutex;
 extern "C" int b200_tq_attention_static(const B200TqAttnArgs *a, b200_stream_t stream) {
     if (!a) return set_error(B200_ERR_BAD_ARG, "tq_attention_static: null args");
     B200TqAttnArgs args = *a;
+    args.flags &= ~B200_TQ_OUTPUTS_FREE;  // every call of a device shares the built-in buffer: stores keep waiting for the call before
     args.workspace = nullptr;
     args.workspace_bytes = 0;
     size_t need = b200_tq_attention_workspace_bytes(&args);
