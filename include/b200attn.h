@@ -323,8 +323,11 @@ typedef struct B200TqAttnArgs {
  * kernel, so that consecutive calls overlap for as long as the device has room for both (a worker that finishes its
  * first column early no longer sits on its place until the whole previous grid has gone); a tile that reaches into the
  * fresh rows still waits, and one block of the grid waits for the previous kernel before it leaves, so that a kernel of
- * such a run never completes before its predecessor. Ignored by calls with gathered outputs (their step word is the previous
- * call's to write). The outputs are those of the plain call. */
+ * such a run never completes before its predecessor. With no fresh rows either (fresh_rows = 0), a call whose columns are
+ * split over many workers merges them inside its grid rather than in a combine grid behind it, so that nothing between two
+ * calls waits for all workers. Ignored by calls with gathered outputs (their step word is the previous call's to write)
+ * and by b200_tq_attention_static (its buffer is shared). The outputs are those of the plain call up to the order of the
+ * merge's sums. */
 #define B200_TQ_OUTPUTS_FREE 8u
 /* Paged calls (pages != NULL): the blocks are read where they are, without a copy, by the general kernel; by the
  * tensor-core kernel too when keys and values share one of its formats (it walks the block table). Other format pairs
