@@ -489,6 +489,34 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
     env.barrier()
     total_ms = ev0.elapsed_time(ev1)
     env.stage(f"{name}: timed region done")
+    # beside it (not the value): the same K steps as calls that share one output and one workspace, so that the stores of
+    # every call wait for the call before (B200_TQ_AFTER_PREV | B200_TQ_INPUTS_FINAL without B200_TQ_OUTPUTS_FREE)
+    waiting_ms = None
+    if not use_gather and with_cpu:
+        wcalls = [P.PackedAttention(q, kc, vc, kv_len, kq, vq, cfg, out=out, after_prev=True, fresh_rows=0, status=status) for kc, vc in caches]
+        for c in wcalls:
+            c.run()
+        torch.cuda.synchronize()
+        try:
+            wg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(wg):
+                for i in range(group):
+                    wcalls[i % nbuf].run()
+            wg.replay()
+            torch.cuda.synchronize()
+            w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(1, steps // group)
+            w0.record()
+            for _ in range(reps):
+                wg.replay()
+            w1.record()
+            torch.cuda.synchronize()
+            waiting_ms = w0.elapsed_time(w1) / (reps * group)
+            del wg
+        except Exception as e:
+            print(f"bench: the comparison leg could not be captured ({e})", file=sys.stderr)
+            torch.cuda.synchronize()
+        wcalls.clear()
     gather_note = "outputs all-gathered over NCCL"
     if peer_gather is not None and use_gather:
         # the gathered rows of the last step against an NCCL all-gather of the same outputs
@@ -668,6 +696,9 @@ def decode_leg(env, name, w_full, steps, warmup, with_e2e=True, with_cpu=True, l
             "tokens_per_s": (w_full["b"] if strong else world * b) / (ms * 1e-3),
             "pct_of_8000_gbs_nominal": 100.0 * value / (8000.0 * world),
             "gpu_launches": steps * launches_per_step * world,  # of all ranks, like `value`
+            "stores_wait_for_previous_call": (None if waiting_ms is None else
+                                              {"ms_per_step": waiting_ms, "value": algorithmic_bytes(w, lens) / (waiting_ms * 1e-3) / 1e9, "unit": "GB/s",
+                                               "what": "the same steps as calls that share one output and one workspace (no B200_TQ_OUTPUTS_FREE): not the value, beside it"}),
             "roofline": {"bound": "hbm", "kernel": "tq_decode_pair_kernel" if pair else "tq_decode_kernel",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_kind, "traffic": None, "traffic_unit": "bytes per launch", "traffic_source": None},
