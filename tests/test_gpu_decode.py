@@ -299,6 +299,32 @@ def test_calls_that_overlap_their_predecessors_give_the_same_rows(P, oracle, f):
     assert P._abi.lib().b200_device_wait_status() == 0
 
 
+def test_overlapping_calls_with_one_length_and_several_query_tokens(P, oracle):
+    """The same chain over caches of one length, TurboQuant-4 rows and two query tokens per sequence
+    (a combine-free call whose columns are split over many workers), against the oracle and against the plain calls."""
+    b, hq, hkv, d, lk, lq = 2, 8, 1, 128, 5000, 2
+    f = (0, 4)
+    kd, vd, tab = make_rows(oracle, 3500, b, hkv, lk, d, f, f)
+    fm = fmt(P, *f)
+    kq, vq = P.TurboQuantizer(fm, d, "none", 42), P.TurboQuantizer(fm, d, "none", 44)
+    cfg = P.FlashAttnConfig(0.0884).causal()
+    n = 3
+    qs = [oracle.normal(86 + i, b * hq * lq * d).reshape(b, hq, lq, d) for i in range(n)]
+    want = [oracle.tq_attention(q, kd, vd, lk, f, f, 0.0884, tab, wr=0) for q in qs]
+    k_dev, v_dev = rows_dev(kd), rows_dev(vd)
+    chain = [P.PackedAttention(to_dev(qs[i]), k_dev, v_dev, lk, kq, vq, cfg, after_prev=i > 0, fresh_rows=0 if i > 0 else None,
+                               outputs_free=i > 0) for i in range(n)]
+    for rounds in range(2):
+        for c in chain:
+            c.out.fill_(float("nan"))
+        for c in chain:
+            c.run()
+        torch.cuda.synchronize()
+        for i, c in enumerate(chain):
+            assert_close(c.out.float().cpu().numpy(), want[i], what=f"round {rounds}, call {i}")
+    assert P._abi.lib().b200_device_wait_status() == 0
+
+
 def test_length_and_position_offsets(P, oracle):
     """kv_len_add / pos0 with device positions: a step that appends at lens + j and attends to lens + j + 1 keys gives
     the rows and outputs of the same step run with the lengths updated on the device."""
