@@ -86,6 +86,21 @@ def test_rust_sys_crate_mirrors_the_header():
         assert int(sizes[n]) == int(sz), n
 
 
+def test_python_constants_mirror_the_header(pkg):
+    """Every B200_* constant of the header that the Python side names (without the prefix) has the header's value."""
+    header = re.sub(r"/\*.*?\*/", "", (ROOT / "include" / "b200attn.h").read_text(), flags=re.S)
+    defs = {n: int(v) for n, v in re.findall(r"#define B200_([A-Z0-9_]+) \(?(-?\d+)u?\)?\s*$", header, flags=re.M)}
+    A = pkg._abi
+    seen = 0
+    for name, value in defs.items():
+        if hasattr(A, name):
+            assert getattr(A, name) == value, name
+            seen += 1
+    for name in ("TQ_AFTER_PREV", "TQ_INPUTS_FINAL", "TQ_IN_PLACE", "TQ_OUTPUTS_FREE", "KV_AFTER_PREV"):
+        assert name in defs and getattr(A, name) == defs[name], name
+    assert seen >= 10
+
+
 def test_row_layouts_and_errors(pkg, oracle):
     A = pkg._abi
     for mode in (0, 2, 3, 4, 5):
